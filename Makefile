@@ -1,0 +1,59 @@
+# Builds the library and its command-line tools for sm_100a.
+#   make -j8            -> nccl_b200/lib/libnccl_b200.so + bin/ncclparam + bin/ncclras + plugins
+#   make SAN=address    -> host code instrumented (CPU-only tests)
+CUDA_HOME ?= /usr/local/cuda
+NVCC      ?= $(CUDA_HOME)/bin/nvcc
+CXX       ?= g++
+BUILD     ?= build
+LIBDIR    := nccl_b200/lib
+BINDIR    := nccl_b200/bin
+
+GENCODE   := -gencode arch=compute_100a,code=sm_100a
+CXXFLAGS  := -std=c++17 -O2 -g -fPIC -Wall -Wno-unused-function -Wno-sign-compare \
+             -Iinclude -Isrc -I$(CUDA_HOME)/include -pthread
+NVCCFLAGS := -std=c++17 -O3 -lineinfo $(GENCODE) -Xcompiler -fPIC -Iinclude -Isrc \
+             --expt-relaxed-constexpr -Xptxas -v
+ifdef SAN
+CXXFLAGS  += -fsanitize=$(SAN) -fno-omit-frame-pointer
+LDSAN     := -fsanitize=$(SAN)
+endif
+
+HOST_SRCS := $(wildcard src/core/*.cc src/host/*.cc src/comm/*.cc src/mem/*.cc src/sched/*.cc \
+               src/topo/*.cc src/transport/*.cc src/plugin/*.cc src/ras/*.cc src/ep/*.cc src/tp/*.cc \
+               src/contrib/*.cc)
+CU_SRCS   := $(wildcard src/kernels/*.cu src/ep/*.cu src/tp/*.cu src/contrib/*.cu)
+HOST_OBJS := $(HOST_SRCS:%.cc=$(BUILD)/%.o)
+CU_OBJS   := $(CU_SRCS:%.cu=$(BUILD)/%.cu.o)
+
+LIB := $(LIBDIR)/libnccl_b200.so
+TOOLS := $(patsubst tools/%.cc,$(BINDIR)/%,$(wildcard tools/*.cc))
+PLUGIN_SRCS := $(wildcard plugins/*/*.cc)
+PLUGINS := $(patsubst plugins/%.cc,$(LIBDIR)/plugins/%.so,$(PLUGIN_SRCS))
+
+all: $(LIB) $(TOOLS) plugins
+
+$(BUILD)/%.o: %.cc $(wildcard include/*.h src/*/*.h)
+	@mkdir -p $(dir $@)
+	$(CXX) $(CXXFLAGS) -c $< -o $@
+
+$(BUILD)/%.cu.o: %.cu $(wildcard include/*.h include/nccl_device/*.h src/*/*.h src/*/*.cuh)
+	@mkdir -p $(dir $@)
+	$(NVCC) $(NVCCFLAGS) -c $< -o $@ 2> $@.ptxas.log || (cat $@.ptxas.log; exit 1)
+
+$(LIB): $(HOST_OBJS) $(CU_OBJS)
+	@mkdir -p $(LIBDIR)
+	$(NVCC) -shared $(GENCODE) -o $@ $^ -cudart static -Xcompiler -pthread -ldl -lrt $(if $(SAN),-Xcompiler $(LDSAN))
+
+$(BINDIR)/%: tools/%.cc $(LIB)
+	@mkdir -p $(BINDIR)
+	$(CXX) $(CXXFLAGS) $< -o $@ -L$(LIBDIR) -lnccl_b200 -Wl,-rpath,'$$ORIGIN/../lib' -ldl $(LDSAN)
+
+plugins: $(PLUGINS)
+$(LIBDIR)/plugins/%.so: plugins/%.cc $(wildcard include/*.h include/plugin/*.h)
+	@mkdir -p $(dir $@)
+	$(CXX) $(CXXFLAGS) -shared $< -o $@
+
+clean:
+	rm -rf $(BUILD) $(LIBDIR) $(BINDIR)
+
+.PHONY: all clean plugins

@@ -1,0 +1,716 @@
+// GPU data plane: resource window set-up, per-call algorithm choice, kernel launches.
+// Every collective is one kernel launch on the caller's stream (plus local copies when a user
+// buffer is not inside a registered window and has to be staged through the resource window).
+// Reference parity: src/enqueue.cc:1989-2180 (algorithm choice), :2479-2583 (reduction operator
+// lowering), src/sym_kernels.cc:599-641 (kernel pick), src/scheduler/symmetric_sched.cc.
+#include "device_plane.h"
+
+#include <math.h>
+#include <stdio.h>
+
+#include <algorithm>
+
+#include "../host/hosttypes.h"
+
+namespace b200 {
+
+B200_PARAM(ScratchMb, "B200_SCRATCH_MB", 128, "Staging area of the resource window per rank (MiB)")
+B200_PARAM(WaitTimeoutMs, "B200_WAIT_TIMEOUT_MS", 30000, "Budget of one device-side wait before the kernel gives up")
+B200_PARAM(MaxCtas, "MAX_CTAS", 0, "Upper bound on CTAs per collective kernel (0 = from the tuning table)")
+B200_PARAM(MinCtas, "MIN_CTAS", 0, "Lower bound on CTAs per collective kernel")
+B200_PARAM(LLThreshold, "B200_LL_THRESHOLD", -1, "All-reduce payloads up to this many bytes use the one-shot flagged-line kernel")
+B200_PARAM(NvlsThreshold, "B200_NVLS_THRESHOLD", -1, "All-reduce payloads from this many bytes use multimem")
+B200_PARAM(P2pDisable, "P2P_DISABLE", 0, "Never map peer memory; GPU buffers are staged through host sockets")
+B200_PARAM(LaunchPdl, "B200_PDL", 0, "Launch collectives with programmatic stream serialisation")
+
+// ------------------------------------------------------------------------------------ tuning
+void tuningDefaults(TuningTable* t) {
+  for (int n = 0; n <= kMaxRanks; ++n) {
+    t->arLLMax[n] = n <= 2 ? (128 << 10) : n <= 4 ? (64 << 10) : (32 << 10);
+    t->arNvlsMin[n] = 64 << 10;
+    t->agMcMin[n] = 64 << 10;
+    t->rsNvlsMin[n] = 64 << 10;
+  }
+  t->ceMin = 0;
+  t->nvlsCtas = 32;
+  t->p2pCtas = 64;
+  t->copyCtas = 32;
+  t->sendrecvCtas = 8;
+  t->bytesPerCta = 128 << 10;
+}
+
+// Minimal reader for  {"arLLMax": {"2": 131072, ...}, "nvlsCtas": 32, ...}  files written by the sweep tool.
+ncclResult_t tuningLoadFile(TuningTable* t, const char* path) {
+  FILE* f = fopen(path, "r");
+  if (!f) { WARN("tuning file %s: cannot open", path); return ncclInvalidArgument; }
+  std::string s;
+  char buf[4096];
+  size_t r;
+  while ((r = fread(buf, 1, sizeof(buf), f)) > 0) s.append(buf, r);
+  fclose(f);
+  auto scalar = [&](const char* key, long long* out) {
+    size_t p = s.find(std::string("\"") + key + "\"");
+    if (p == std::string::npos) return false;
+    p = s.find(':', p);
+    if (p == std::string::npos) return false;
+    *out = strtoll(s.c_str() + p + 1, nullptr, 10);
+    return true;
+  };
+  auto table = [&](const char* key, size_t* arr) {
+    size_t p = s.find(std::string("\"") + key + "\"");
+    if (p == std::string::npos) return;
+    size_t b = s.find('{', p), e = s.find('}', p);
+    if (b == std::string::npos || e == std::string::npos) return;
+    for (int n = 2; n <= kMaxRanks; ++n) {
+      std::string k = "\"" + std::to_string(n) + "\"";
+      size_t q = s.find(k, b);
+      if (q == std::string::npos || q > e) continue;
+      q = s.find(':', q);
+      arr[n] = (size_t)strtoll(s.c_str() + q + 1, nullptr, 10);
+    }
+  };
+  table("arLLMax", t->arLLMax);
+  table("arNvlsMin", t->arNvlsMin);
+  table("agMcMin", t->agMcMin);
+  table("rsNvlsMin", t->rsNvlsMin);
+  long long v;
+  if (scalar("ceMin", &v)) t->ceMin = (size_t)v;
+  if (scalar("nvlsCtas", &v)) t->nvlsCtas = (int)v;
+  if (scalar("p2pCtas", &v)) t->p2pCtas = (int)v;
+  if (scalar("copyCtas", &v)) t->copyCtas = (int)v;
+  if (scalar("sendrecvCtas", &v)) t->sendrecvCtas = (int)v;
+  if (scalar("bytesPerCta", &v)) t->bytesPerCta = (size_t)v;
+  INFO(SUB_TUNING, "tuning table loaded from %s", path);
+  return ncclSuccess;
+}
+
+// ------------------------------------------------------------------------------------ set-up
+ncclResult_t devPlaneCreate(ncclComm* comm) {
+  DevicePlane* dp = new DevicePlane;
+  comm->devPlane = dp;
+  tuningDefaults(&dp->tune);
+  const char* tf = getEnv("NCCL_TUNING_FILE");
+  if (tf && *tf) tuningLoadFile(&dp->tune, tf);
+  cudaDeviceProp prop;
+  CUDACHECK(cudaGetDeviceProperties(&prop, comm->cudaDev));
+  dp->smCount = prop.multiProcessorCount;
+  dp->timeoutNs = (uint64_t)paramWaitTimeoutMs() * 1000000ull;
+  CUDACHECK(cudaEventCreateWithFlags(&dp->lastEvent, cudaEventDisableTiming));
+  const size_t privWords = kBarrierSlots + 4 + (2 * kMaxRanks + 4) + 2 * kMaxRanks * kSignalsPerPeer;
+  CUDACHECK(cudaMalloc(&dp->priv, privWords * sizeof(uint32_t)));
+  CUDACHECK(cudaMemset(dp->priv, 0, privWords * sizeof(uint32_t)));
+  dp->epochs = dp->priv;
+  dp->llEpoch = dp->priv + kBarrierSlots;
+  dp->p2pSeq = dp->llEpoch + 4;
+  dp->sigSeen = (uint64_t*)(dp->p2pSeq + 2 * kMaxRanks + 4);
+  if (comm->nRanks == 1) return ncclSuccess;
+
+  int usable = comm->lsaAll ? 1 : 0;
+  if (usable) {
+    NCCLCHECK(symInit(comm));
+    dp->stageBytes = (size_t)paramScratchMb() << 20;
+    dp->offLL = kSyncPageBytes;
+    dp->offMailbox = dp->offLL + kLLRegionBytes;
+    dp->offStage = alignUp(dp->offMailbox + kMailboxBytes, (size_t)(2 << 20));
+    dp->resSize = dp->offStage + dp->stageBytes;
+    ncclResult_t r = memAlloc(&dp->resBase, dp->resSize, comm->cudaDev);
+    if (r == ncclSuccess) {
+      // only the control part needs zeroing: flags, flagged lines
+      if (cudaMemset(dp->resBase, 0, dp->offMailbox) != cudaSuccess) { (void)cudaGetLastError(); r = ncclUnhandledCudaError; }
+      cudaDeviceSynchronize();
+    }
+    if (r == ncclSuccess) r = symWindowRegister(comm, dp->resBase, dp->resSize, &dp->resWin, NCCL_WIN_COLL_SYMMETRIC);
+    if (r != ncclSuccess || !dp->resWin || !dp->resWin->symmetric) usable = 0;
+  }
+  // every rank must reach the same verdict
+  std::vector<int> oks(comm->nRanks, 0);
+  oks[comm->rank] = usable;
+  NCCLCHECK(bootstrapAllGather(comm->bootstrap, oks.data(), sizeof(int)));
+  for (int v : oks) usable = usable && v;
+  if (!usable) {
+    if (comm->lsaAll) INFO(SUB_INIT, "peer mappings unavailable: GPU buffers will be staged through host sockets");
+    comm->lsaAll = false;
+    dp->hostStageBytes = 64 << 20;
+    CUDACHECK(cudaHostAlloc(&dp->hostStage, dp->hostStageBytes, cudaHostAllocDefault));
+    if (!comm->hostPlane) NCCLCHECK(hostPlaneCreate(comm));
+  }
+  NCCLCHECK(bootstrapBarrier(comm->bootstrap));
+  return ncclSuccess;
+}
+
+void devPlaneDestroy(ncclComm* comm) {
+  DevicePlane* dp = comm->devPlane;
+  if (!dp) return;
+  cudaDeviceSynchronize();
+  (void)cudaGetLastError();
+  if (comm->sym) symDestroy(comm);   // releases every window, the resource window included
+  if (dp->resBase) memFree(dp->resBase);
+  if (dp->priv) cudaFree(dp->priv);
+  if (dp->lastEvent) cudaEventDestroy(dp->lastEvent);
+  if (dp->hostStage) cudaFreeHost(dp->hostStage);
+  (void)cudaGetLastError();
+  delete dp;
+  comm->devPlane = nullptr;
+}
+
+ncclResult_t devPlaneCheckStatus(ncclComm* comm) {
+  if (!comm->devStatus) return ncclSuccess;
+  uint32_t code = comm->devStatus[0];
+  if (code == DEV_OK) return ncclSuccess;
+  static const char* kinds[] = {"?", "barrier", "flagged line", "mailbox ready flag", "mailbox ack flag", "signal", "tile flag"};
+  uint32_t kind = comm->devStatus[1];
+  WARN("rank %d: device-side wait on a %s of rank %u %s (expected value %u)", comm->rank, kind < 7 ? kinds[kind] : "?",
+       comm->devStatus[2], code == DEV_TIMEOUT ? "timed out" : "was aborted", comm->devStatus[3]);
+  return code == DEV_TIMEOUT ? ncclTimeout : ncclInternalError;
+}
+
+// ------------------------------------------------------------------------------------ helpers
+struct DevOp {
+  int red = RED_SUM;
+  int scaleMode = SCALE_NONE;
+  float scaleF = 1.f;
+  double scaleD = 1.0;
+  long long intDiv = 1;
+  bool premul = false;
+  unsigned long long premulBits = 0;
+  const void* premulPtr = nullptr;
+};
+
+static bool isFloatType(ncclDataType_t t) {
+  return t == ncclFloat16 || t == ncclFloat32 || t == ncclFloat64 || t == ncclBfloat16 || t == ncclFloat8e4m3 || t == ncclFloat8e5m2;
+}
+
+static ncclResult_t lowerOp(ncclComm* comm, const Task& t, DevOp* d) {
+  switch (t.op) {
+    case ncclSum: d->red = RED_SUM; return ncclSuccess;
+    case ncclProd: d->red = RED_PROD; return ncclSuccess;
+    case ncclMax: d->red = RED_MAX; return ncclSuccess;
+    case ncclMin: d->red = RED_MIN; return ncclSuccess;
+    case ncclAvg:
+      d->red = RED_SUM;
+      if (isFloatType(t.type)) { d->scaleMode = SCALE_MUL; d->scaleF = 1.0f / comm->nRanks; d->scaleD = 1.0 / comm->nRanks; }
+      else { d->scaleMode = SCALE_INTDIV; d->intDiv = comm->nRanks; }
+      return ncclSuccess;
+    default: break;
+  }
+  int idx = t.op - ncclNumOps;
+  if (idx < 0 || idx >= (int)comm->userOps.size() || !comm->userOps[idx].used) { WARN("invalid reduction operator %d", t.op); return ncclInvalidArgument; }
+  const UserRedOp& u = comm->userOps[idx];
+  if (u.type != t.type) { WARN("reduction operator was created for %s, used with %s", typeName(u.type), typeName(t.type)); return ncclInvalidArgument; }
+  d->red = RED_SUM;
+  d->premul = true;
+  d->premulBits = u.scalarBits;
+  d->premulPtr = u.residence == ncclScalarDevice ? u.devScalar : nullptr;
+  return ncclSuccess;
+}
+
+static void fillSync(ncclComm* comm, SyncArgs* s) {
+  DevicePlane* dp = comm->devPlane;
+  memset(s, 0, sizeof(*s));
+  for (int p = 0; p < comm->nRanks; ++p) s->inbox[p] = (uint32_t*)dp->resWin->host.peerPtr[p];
+  s->epoch[comm->rank] = dp->epochs;
+  s->status[comm->rank] = comm->devStatusDev;
+  s->abortFlag = comm->abortFlagDev;
+  s->timeoutNs = dp->timeoutNs;
+}
+
+static void baseArgs(ncclComm* comm, CollArgs* a, int func) {
+  DevicePlane* dp = comm->devPlane;
+  memset(a, 0, sizeof(*a));
+  a->rank = comm->rank;
+  a->nRanks = comm->nRanks;
+  a->func = func;
+  fillSync(comm, &a->sync);
+  for (int p = 0; p < comm->nRanks; ++p) a->ll[p] = (char*)dp->resWin->host.peerPtr[p] + dp->offLL;
+  a->llEpoch[comm->rank] = dp->llEpoch;
+}
+
+// Peer-visible aliases of `ptr` when it lies in a symmetric window (same offset on every rank).
+struct Aliases {
+  bool ok = false;
+  void* peer[kMaxRanks] = {};
+  void* mc = nullptr;
+};
+static Aliases aliasesOf(ncclComm* comm, const void* ptr, size_t bytes) {
+  Aliases al;
+  if (!ptr) return al;
+  SymWindow* w = symFindWindow(comm, ptr, bytes ? bytes : 1);
+  if (!w || !w->symmetric) return al;
+  size_t off = (uintptr_t)ptr - (uintptr_t)w->host.userPtr;
+  for (int p = 0; p < comm->nRanks; ++p) al.peer[p] = (char*)w->host.peerPtr[p] + off;
+  if (w->host.mcPtr) al.mc = (char*)w->host.mcPtr + off;
+  al.ok = true;
+  return al;
+}
+static Aliases stageAliases(ncclComm* comm, size_t off) {
+  DevicePlane* dp = comm->devPlane;
+  Aliases al;
+  for (int p = 0; p < comm->nRanks; ++p) al.peer[p] = (char*)dp->resWin->host.peerPtr[p] + dp->offStage + off;
+  if (dp->resWin->host.mcPtr) al.mc = (char*)dp->resWin->host.mcPtr + dp->offStage + off;
+  al.ok = true;
+  return al;
+}
+
+static bool aligned16(const Aliases& al, int n) {
+  for (int p = 0; p < n; ++p) if ((uintptr_t)al.peer[p] & 15) return false;
+  return true;
+}
+
+static int clampCtas(ncclComm* comm, size_t bytes, int cap) {
+  DevicePlane* dp = comm->devPlane;
+  int64_t envMax = paramMaxCtas(), envMin = paramMinCtas();
+  if (comm->config.maxCTAs != NCCL_CONFIG_UNDEF_INT && comm->config.maxCTAs > 0) cap = std::min(cap, comm->config.maxCTAs);
+  if (envMax > 0) cap = (int)std::min<int64_t>(cap, envMax);
+  cap = std::min(cap, std::min(kMaxCtas, dp->smCount));
+  int want = (int)std::min<size_t>((bytes + dp->tune.bytesPerCta - 1) / dp->tune.bytesPerCta, (size_t)cap);
+  int lo = 1;
+  if (comm->config.minCTAs != NCCL_CONFIG_UNDEF_INT && comm->config.minCTAs > 0) lo = comm->config.minCTAs;
+  if (envMin > 0) lo = (int)envMin;
+  want = std::max(want, std::min(lo, cap));
+  return std::max(want, 1);
+}
+
+static bool capturing(cudaStream_t s) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(s, &st) != cudaSuccess) { (void)cudaGetLastError(); return false; }
+  return st != cudaStreamCaptureStatusNone;
+}
+
+// Collectives of one communicator run one after the other even when issued on different streams.
+static ncclResult_t orderStreams(ncclComm* comm, cudaStream_t stream) {
+  DevicePlane* dp = comm->devPlane;
+  if (dp->hasLast && dp->lastStream != stream && !capturing(stream) && !capturing(dp->lastStream)) {
+    CUDACHECK(cudaEventRecord(dp->lastEvent, dp->lastStream));
+    CUDACHECK(cudaStreamWaitEvent(stream, dp->lastEvent, 0));
+  }
+  dp->lastStream = stream;
+  dp->hasLast = true;
+  return ncclSuccess;
+}
+
+static ncclResult_t launchColl(ncclComm* comm, const void* fn, CollArgs* a, int ctas, cudaStream_t stream) {
+  if (!fn) { WARN("no kernel for this data type / operator"); return ncclInvalidUsage; }
+  comm->devPlane->launches++;
+  return launchKernel(fn, dim3(ctas), dim3(kCtaThreads), 0, a, stream, false, paramLaunchPdl() != 0);
+}
+
+static ncclResult_t scaleCopy(ncclComm* comm, ncclDataType_t type, const void* src, void* dst, size_t count, const DevOp& op,
+                              cudaStream_t stream) {
+  ScaleArgs sa{src, dst, count, op.premulBits, op.premulPtr};
+  int ctas = (int)std::min<size_t>((count + 4095) / 4096, 1024);
+  comm->devPlane->launches++;
+  return launchKernel(scaleKernelFn(type), dim3(std::max(ctas, 1)), dim3(256), 0, &sa, stream, false);
+}
+
+static void sliceEven(size_t count, size_t es, int n, size_t* begin, size_t* cnt) {
+  const size_t unit = 16 / es;  // elements per 16 bytes
+  size_t per = (count + n - 1) / n;
+  per = (per + unit - 1) / unit * unit;
+  for (int r = 0; r < n; ++r) {
+    size_t b = std::min(count, (size_t)r * per);
+    begin[r] = b;
+    cnt[r] = std::min(per, count - b);
+  }
+}
+
+// ------------------------------------------------------------------------------------ collectives
+static int forcedAlgo() {
+  const char* e = getEnv("NCCL_ALGO");
+  if (!e || !*e) return ALGO_AUTO;
+  if (!strcasecmp(e, "NVLS")) return ALGO_NVLS;
+  if (!strcasecmp(e, "P2P") || !strcasecmp(e, "TwoShot") || !strcasecmp(e, "Direct")) return ALGO_P2P;
+  if (!strcasecmp(e, "LL") || !strcasecmp(e, "OneShot")) return ALGO_LL_ONESHOT;
+  if (!strcasecmp(e, "Ring")) return ALGO_RING;
+  if (!strcasecmp(e, "Tree")) return ALGO_TREE;
+  if (!strcasecmp(e, "CE")) return ALGO_CE;
+  return ALGO_AUTO;
+}
+
+ncclResult_t ringTreeRun(ncclComm* comm, const Task& t, int algo);   // sched/ring_tree.cc
+ncclResult_t ceCollRun(ncclComm* comm, const Task& t, bool* handled); // sched/ce_coll.cc
+
+static ncclResult_t runReduction(ncclComm* comm, const Task& t) {
+  DevicePlane* dp = comm->devPlane;
+  const int n = comm->nRanks, me = comm->rank;
+  const size_t es = typeSize(t.type);
+  DevOp op;
+  NCCLCHECK(lowerOp(comm, t, &op));
+  // element counts: `total` elements enter the reduction on every rank
+  const size_t total = t.func == FUNC_REDUCESCATTER ? t.count * n : t.count;
+  const size_t bytes = total * es;
+  if (total == 0) return ncclSuccess;
+  const int forced = forcedAlgo();
+
+  if ((forced == ALGO_RING || forced == ALGO_TREE) && !op.premul) return ringTreeRun(comm, t, forced);
+
+  // ---- small all-reduce: flagged lines, no registration needed
+  int64_t llEnv = paramLLThreshold();
+  size_t llMax = llEnv >= 0 ? (size_t)llEnv : dp->tune.arLLMax[n];
+  llMax = std::min(llMax, kLLDataBytes);
+  if (t.func == FUNC_ALLREDUCE && !op.premul && (forced == ALGO_LL_ONESHOT ? bytes <= kLLDataBytes : (forced == ALGO_AUTO && bytes <= llMax))) {
+    CollArgs a;
+    baseArgs(comm, &a, t.func);
+    a.count = t.count;
+    a.lsend[me] = t.send;
+    a.lrecv[me] = t.recv;
+    a.scaleMode = op.scaleMode; a.scaleF = op.scaleF; a.scaleD = op.scaleD; a.intDiv = op.intDiv;
+    size_t lines = (bytes + 7) / 8;
+    int ctas = (int)std::min<size_t>((lines + kCtaThreads - 1) / kCtaThreads, 64);
+    return launchColl(comm, reduceKernelFn(KERNEL_ALLREDUCE_LL, t.type, op.red), &a, std::max(ctas, 1), t.stream);
+  }
+
+  // ---- large: every rank reduces one slice, inputs must be peer-visible
+  Aliases sendAl = op.premul ? Aliases{} : aliasesOf(comm, t.send, bytes);
+  const bool needRecvAll = t.func == FUNC_ALLREDUCE;
+  Aliases recvAl = needRecvAll ? aliasesOf(comm, t.recv, bytes) : Aliases{};
+  const bool direct = sendAl.ok && (!needRecvAll || recvAl.ok);
+
+  // work is cut in pieces that fit the staging area when staging is needed
+  const size_t stageElems = dp->stageBytes / es / (16 / es > 0 ? 1 : 1);
+  size_t pieceTotal = total;        // elements (over all slices) handled per launch
+  if (!direct) {
+    size_t cap = stageElems / n * n;  // keep reduce-scatter pieces divisible by n
+    cap = cap / (16 * n) * (16 * n);
+    if (pieceTotal > cap) pieceTotal = cap;
+  }
+  for (size_t done = 0; done < total;) {
+    size_t cur = std::min(pieceTotal, total - done);   // all-reduce / reduce: elements; reduce-scatter: n * piece
+    CollArgs a;
+    baseArgs(comm, &a, t.func);
+    a.scaleMode = op.scaleMode; a.scaleF = op.scaleF; a.scaleD = op.scaleD; a.intDiv = op.intDiv;
+    a.root = t.root;
+    Aliases in, out;
+    size_t rsPiece = 0, rsDone = 0;
+    if (t.func == FUNC_REDUCESCATTER) { rsPiece = cur / n; rsDone = done / n; if (!direct && rsPiece == 0) rsPiece = t.count; }
+    if (direct) {
+      in = sendAl;
+      out = recvAl;
+      cur = total;
+    } else {
+      // copy-in (fused with the pre-multiplication when there is one)
+      in = stageAliases(comm, 0);
+      out = in;
+      char* st = (char*)dp->resBase + dp->offStage;
+      if (t.func == FUNC_REDUCESCATTER) {
+        // rows of rsPiece elements, one per destination rank, gathered from a pitch of t.count
+        if (op.premul) {
+          for (int r = 0; r < n; ++r)
+            NCCLCHECK(scaleCopy(comm, t.type, (const char*)t.send + ((size_t)r * t.count + rsDone) * es, st + (size_t)r * rsPiece * es, rsPiece, op, t.stream));
+        } else {
+          CUDACHECK(cudaMemcpy2DAsync(st, rsPiece * es, (const char*)t.send + rsDone * es, t.count * es, rsPiece * es, n, cudaMemcpyDeviceToDevice, t.stream));
+        }
+      } else if (op.premul) {
+        NCCLCHECK(scaleCopy(comm, t.type, (const char*)t.send + done * es, st, cur, op, t.stream));
+      } else {
+        CUDACHECK(cudaMemcpyAsync(st, (const char*)t.send + done * es, cur * es, cudaMemcpyDeviceToDevice, t.stream));
+      }
+    }
+    // slices
+    if (t.func == FUNC_ALLREDUCE) {
+      sliceEven(cur, es, n, a.sliceBegin, a.sliceCount);
+      for (int r = 0; r < n; ++r) a.dstOff[r] = a.sliceBegin[r];
+      a.dstAll = 1;
+    } else if (t.func == FUNC_REDUCESCATTER) {
+      size_t per = direct ? t.count : rsPiece;
+      for (int r = 0; r < n; ++r) { a.sliceBegin[r] = (size_t)r * per; a.sliceCount[r] = per; a.dstOff[r] = 0; }
+      a.dstAll = 0;
+    } else {  // reduce: the root does all the work
+      for (int r = 0; r < n; ++r) { a.sliceBegin[r] = 0; a.sliceCount[r] = r == t.root ? cur : 0; a.dstOff[r] = 0; }
+      a.dstAll = 0;
+    }
+    for (int p = 0; p < n; ++p) { a.send[p] = in.peer[p]; a.recv[p] = out.peer[p]; }
+    a.sendMc = in.mc;
+    a.recvMc = out.mc;
+    // local result pointer for reduce-scatter / reduce
+    if (t.func == FUNC_REDUCESCATTER) a.lrecv[me] = (char*)t.recv + (direct ? 0 : rsDone * es);
+    else if (t.func == FUNC_REDUCE) a.lrecv[me] = me == t.root ? (char*)t.recv + (direct ? 0 : done * es) : nullptr;
+    const size_t curBytes = cur * es;
+    bool v16 = aligned16(in, n) && (!a.dstAll || aligned16(out, n));
+    if (!a.dstAll && a.lrecv[me] && ((uintptr_t)a.lrecv[me] & 15)) v16 = false;
+    if (t.func == FUNC_REDUCESCATTER && (a.sliceCount[0] * es) % 16) v16 = false;
+    a.vec16 = v16;
+    // multimem needs whole 16-byte packs in every slice
+    bool nvlsOk = in.mc && (!a.dstAll || out.mc) && v16 && nvlsReduceSupported(t.type, op.red) && (curBytes % 16 == 0) &&
+                  (t.func != FUNC_REDUCESCATTER || (a.sliceCount[0] * es) % 16 == 0);
+    int64_t nvEnv = paramNvlsThreshold();
+    size_t nvMin = nvEnv >= 0 ? (size_t)nvEnv : (t.func == FUNC_ALLREDUCE ? dp->tune.arNvlsMin[n] : dp->tune.rsNvlsMin[n]);
+    bool useNvls = nvlsOk && (forced == ALGO_NVLS || (forced == ALGO_AUTO && curBytes >= nvMin));
+    if (forced == ALGO_P2P) useNvls = false;
+    const size_t perRankBytes = t.func == FUNC_REDUCE ? curBytes : curBytes / n;
+    int ctas = clampCtas(comm, perRankBytes, useNvls ? dp->tune.nvlsCtas : dp->tune.p2pCtas);
+    NCCLCHECK(launchColl(comm, reduceKernelFn(useNvls ? KERNEL_REDUCE_NVLS : KERNEL_REDUCE_P2P, t.type, op.red), &a, ctas, t.stream));
+    if (direct) break;
+    // copy-out of the staged all-reduce
+    if (t.func == FUNC_ALLREDUCE)
+      CUDACHECK(cudaMemcpyAsync((char*)t.recv + done * es, (char*)dp->resBase + dp->offStage, cur * es, cudaMemcpyDeviceToDevice, t.stream));
+    done += cur;
+  }
+  return ncclSuccess;
+}
+
+static ncclResult_t runCopyColl(ncclComm* comm, const Task& t) {
+  DevicePlane* dp = comm->devPlane;
+  const int n = comm->nRanks, me = comm->rank;
+  const size_t es = typeSize(t.type);
+  const size_t B = t.count * es;   // bytes per segment
+  if (B == 0) return ncclSuccess;
+  const int forced = forcedAlgo();
+  if (forced == ALGO_RING && (t.func == FUNC_ALLGATHER || t.func == FUNC_BROADCAST)) return ringTreeRun(comm, t, forced);
+  if (forced == ALGO_CE || (forced == ALGO_AUTO && dp->tune.ceMin && B >= dp->tune.ceMin)) {
+    bool handled = false;
+    NCCLCHECK(ceCollRun(comm, t, &handled));
+    if (handled) return ncclSuccess;
+  }
+  size_t sendBytes = B, recvBytes = B;
+  if (t.func == FUNC_ALLGATHER || t.func == FUNC_GATHER) recvBytes = B * n;
+  if (t.func == FUNC_ALLTOALL) { sendBytes = B * n; recvBytes = B * n; }
+  if (t.func == FUNC_SCATTER) sendBytes = B * n;
+  // which side is significant on this rank
+  const bool recvEverywhere = t.func != FUNC_GATHER;
+  const bool sendEverywhere = t.func != FUNC_BROADCAST && t.func != FUNC_SCATTER;
+  Aliases recvAl = recvEverywhere ? aliasesOf(comm, t.recv, recvBytes) : Aliases{};
+  Aliases sendAl = sendEverywhere ? aliasesOf(comm, t.send, sendBytes) : Aliases{};
+  // registration must be agreed upon: a buffer counts as symmetric only if its window is (collective property)
+  int mode;
+  bool staged = false;
+  if (recvAl.ok) mode = MODE_PUSH;
+  else if (sendAl.ok) mode = MODE_PULL;
+  else { mode = MODE_PULL; staged = true; }
+
+  // pieces that fit the staging area
+  const size_t segsStaged = (t.func == FUNC_ALLTOALL || t.func == FUNC_SCATTER) ? n : 1;
+  size_t piece = B;
+  if (staged) {
+    size_t cap = dp->stageBytes / segsStaged / 16 * 16;
+    piece = std::min(B, cap);
+  }
+  for (size_t done = 0; done < B; done += piece) {
+    const size_t cur = std::min(piece, B - done);
+    CollArgs a;
+    baseArgs(comm, &a, t.func);
+    a.root = t.root;
+    a.count = cur;
+    a.sendStride = staged ? cur : B;
+    a.recvStride = B;
+    a.mode = mode;
+    Aliases in = sendAl, out = recvAl;
+    a.lsend[me] = (const char*)t.send + done;
+    a.lrecv[me] = (char*)t.recv + done;
+    if (staged) {
+      in = stageAliases(comm, 0);
+      char* st = (char*)dp->resBase + dp->offStage;
+      const bool iSend = sendEverywhere || me == t.root;
+      if (iSend) {
+        if (segsStaged > 1) {
+          CUDACHECK(cudaMemcpy2DAsync(st, cur, (const char*)t.send + done, B, cur, n, cudaMemcpyDeviceToDevice, t.stream));
+        } else {
+          CUDACHECK(cudaMemcpyAsync(st, (const char*)t.send + done, cur, cudaMemcpyDeviceToDevice, t.stream));
+        }
+      }
+      a.lsend[me] = st;
+    } else if (cur != B) {
+      return ncclInternalError;
+    }
+    for (int p = 0; p < n; ++p) { a.send[p] = in.peer[p]; a.recv[p] = out.peer[p]; }
+    bool v16 = (cur % 16 == 0) && (((uintptr_t)a.lsend[me] | (uintptr_t)a.lrecv[me]) & 15) == 0;
+    if (mode == MODE_PUSH) v16 = v16 && aligned16(out, n); else v16 = v16 && aligned16(in, n);
+    if (B % 16) v16 = false;
+    a.vec16 = v16;
+    if (mode == MODE_PUSH && out.mc && v16 && (t.func == FUNC_ALLGATHER || t.func == FUNC_BROADCAST) &&
+        (forced == ALGO_NVLS || (forced == ALGO_AUTO && cur >= dp->tune.agMcMin[n]))) {
+      a.mode = MODE_MC;
+      a.recvMc = out.mc;
+    }
+    // offsets of this piece inside peer buffers
+    if (done) {
+      for (int p = 0; p < n; ++p) {
+        if (a.send[p] && !staged) a.send[p] = (const char*)a.send[p] + done;
+        if (a.recv[p]) a.recv[p] = (char*)a.recv[p] + done;
+      }
+      if (a.recvMc) a.recvMc = (char*)a.recvMc + done;
+    }
+    size_t moved = cur * ((t.func == FUNC_BROADCAST && mode != MODE_PUSH) ? 1 : (a.mode == MODE_MC ? 1 : n));
+    int ctas = clampCtas(comm, moved, dp->tune.copyCtas);
+    NCCLCHECK(launchColl(comm, copyKernelFn(), &a, ctas, t.stream));
+  }
+  return ncclSuccess;
+}
+
+static ncclResult_t runOneRank(ncclComm* comm, const Task& t) {
+  const size_t es = typeSize(t.type);
+  size_t bytes = t.count * es;
+  const void* src = t.send;
+  void* dst = t.recv;
+  switch (t.func) {
+    case FUNC_SEND: case FUNC_RECV:
+      WARN("send/recv to self must be grouped");
+      return ncclInvalidUsage;
+    default: break;
+  }
+  if (bytes == 0) return ncclSuccess;
+  bool reduces = t.func == FUNC_ALLREDUCE || t.func == FUNC_REDUCE || t.func == FUNC_REDUCESCATTER;
+  if (reduces && t.op >= ncclNumOps) {
+    DevOp op;
+    NCCLCHECK(lowerOp(comm, t, &op));
+    return scaleCopy(comm, t.type, src, dst, t.count, op, t.stream);
+  }
+  if (src != dst) CUDACHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, t.stream));
+  return ncclSuccess;
+}
+
+// GPU buffers, ranks that cannot map each other: stage through pinned host memory and sockets.
+static ncclResult_t runViaHost(ncclComm* comm, const Task& t) {
+  const int n = comm->nRanks;
+  const size_t es = typeSize(t.type);
+  size_t sendBytes = t.count * es, recvBytes = t.count * es;
+  switch (t.func) {
+    case FUNC_ALLGATHER: recvBytes *= n; break;
+    case FUNC_REDUCESCATTER: sendBytes *= n; break;
+    case FUNC_ALLTOALL: sendBytes *= n; recvBytes *= n; break;
+    case FUNC_GATHER: recvBytes *= n; break;
+    case FUNC_SCATTER: sendBytes *= n; break;
+    default: break;
+  }
+  std::vector<char> hs(t.send ? sendBytes : 0), hr(t.recv ? recvBytes : 0);
+  CUDACHECK(cudaStreamSynchronize(t.stream));
+  if (t.send && t.func != FUNC_RECV) CUDACHECK(cudaMemcpy(hs.data(), t.send, sendBytes, cudaMemcpyDeviceToHost));
+  Task ht = t;
+  ht.send = hs.data();
+  ht.recv = hr.data();
+  NCCLCHECK(hostPlaneRun(comm, ht));
+  bool wroteRecv = t.recv && !(t.func == FUNC_SEND) && !((t.func == FUNC_REDUCE || t.func == FUNC_GATHER) && comm->rank != t.root);
+  if (wroteRecv) CUDACHECK(cudaMemcpy(t.recv, hr.data(), recvBytes, cudaMemcpyHostToDevice));
+  return ncclSuccess;
+}
+
+ncclResult_t signalRun(ncclComm* comm, const Task& t);  // sched/rma.cc
+
+ncclResult_t devPlaneRun(ncclComm* comm, const Task& t, ncclSimInfo_t* sim) {
+  (void)sim;
+  DevicePlane* dp = comm->devPlane;
+  if (!dp) return ncclInternalError;
+  NCCLCHECK(devPlaneCheckStatus(comm));
+  int cur = -1;
+  CUDACHECK(cudaGetDevice(&cur));
+  if (cur != comm->cudaDev) CUDACHECK(cudaSetDevice(comm->cudaDev));
+  ncclResult_t r = ncclSuccess;
+  if (t.func == FUNC_PUTSIGNAL || t.func == FUNC_SIGNAL || t.func == FUNC_WAITSIGNAL) {
+    r = orderStreams(comm, t.stream);
+    if (r == ncclSuccess) r = signalRun(comm, t);
+  } else if (comm->nRanks == 1) {
+    r = runOneRank(comm, t);
+  } else if (!comm->lsaAll) {
+    r = runViaHost(comm, t);
+  } else {
+    r = orderStreams(comm, t.stream);
+    if (r == ncclSuccess) {
+      switch (t.func) {
+        case FUNC_ALLREDUCE: case FUNC_REDUCESCATTER: case FUNC_REDUCE: r = runReduction(comm, t); break;
+        case FUNC_ALLGATHER: case FUNC_BROADCAST: case FUNC_ALLTOALL: case FUNC_GATHER: case FUNC_SCATTER: r = runCopyColl(comm, t); break;
+        default: WARN("unexpected function %d", t.func); r = ncclInternalError;
+      }
+    }
+  }
+  if (cur != comm->cudaDev && cur >= 0) cudaSetDevice(cur);
+  return r;
+}
+
+ncclResult_t devPlaneRunP2pGroup(ncclComm* comm, const std::vector<Task>& tasks) {
+  DevicePlane* dp = comm->devPlane;
+  if (!dp) return ncclInternalError;
+  if (tasks.empty()) return ncclSuccess;
+  NCCLCHECK(devPlaneCheckStatus(comm));
+  cudaStream_t stream = tasks[0].stream;
+  int cur = -1;
+  CUDACHECK(cudaGetDevice(&cur));
+  if (cur != comm->cudaDev) CUDACHECK(cudaSetDevice(comm->cudaDev));
+  ncclResult_t res = ncclSuccess;
+  // sends and receives addressed to myself pair up in posting order and become local copies
+  std::vector<const Task*> selfS, selfR;
+  std::vector<const Task*> remote;
+  for (auto& t : tasks) {
+    if (t.root == comm->rank) (t.func == FUNC_SEND ? selfS : selfR).push_back(&t);
+    else remote.push_back(&t);
+  }
+  if (selfS.size() != selfR.size()) { WARN("send/recv to self: %zu sends but %zu receives in the group", selfS.size(), selfR.size()); return ncclInvalidUsage; }
+  for (size_t i = 0; i < selfS.size(); ++i) {
+    size_t sb = selfS[i]->count * typeSize(selfS[i]->type), rb = selfR[i]->count * typeSize(selfR[i]->type);
+    if (sb > rb) { WARN("send to self is larger than the matching receive"); return ncclInvalidArgument; }
+    if (sb && selfS[i]->send != selfR[i]->recv) CUDACHECK(cudaMemcpyAsync(selfR[i]->recv, selfS[i]->send, sb, cudaMemcpyDeviceToDevice, stream));
+  }
+  if (remote.empty()) goto out;
+  if (!comm->lsaAll) {
+    CUDACHECK(cudaStreamSynchronize(stream));
+    std::vector<Task> ht;
+    std::vector<std::vector<char>> bufs(remote.size());
+    for (size_t i = 0; i < remote.size(); ++i) {
+      const Task& t = *remote[i];
+      size_t b = t.count * typeSize(t.type);
+      bufs[i].resize(b);
+      Task h = t;
+      if (t.func == FUNC_SEND) { CUDACHECK(cudaMemcpy(bufs[i].data(), t.send, b, cudaMemcpyDeviceToHost)); h.send = bufs[i].data(); }
+      else h.recv = bufs[i].data();
+      ht.push_back(h);
+    }
+    res = hostPlaneRunP2pGroup(comm, ht);
+    if (res == ncclSuccess)
+      for (size_t i = 0; i < remote.size(); ++i)
+        if (remote[i]->func == FUNC_RECV) CUDACHECK(cudaMemcpy(remote[i]->recv, bufs[i].data(), bufs[i].size(), cudaMemcpyHostToDevice));
+    goto out;
+  }
+  res = orderStreams(comm, stream);
+  for (size_t first = 0; first < remote.size() && res == ncclSuccess; first += kMaxP2pOps) {
+    size_t nOps = std::min<size_t>(kMaxP2pOps, remote.size() - first);
+    P2pArgs a;
+    memset(&a, 0, sizeof(a));
+    a.rank = comm->rank;
+    a.nRanks = comm->nRanks;
+    fillSync(comm, &a.sync);
+    for (int p = 0; p < comm->nRanks; ++p) {
+      char* base = (char*)dp->resWin->host.peerPtr[p];
+      a.mailbox[p] = base + dp->offMailbox;
+      a.ready[p] = (uint32_t*)(base + kOffP2pReady);
+      a.ack[p] = (uint32_t*)(base + kOffP2pAck);
+    }
+    a.seq[comm->rank] = dp->p2pSeq;
+    a.nOps[comm->rank] = (int)nOps;
+    a.opBase[comm->rank] = 0;
+    int cta = 0;
+    int perOpCap = std::max(1, std::min(dp->tune.sendrecvCtas, (int)(std::min(kMaxCtas, dp->smCount) / (int)nOps)));
+    for (size_t i = 0; i < nOps; ++i) {
+      const Task& t = *remote[first + i];
+      P2pOp& o = a.ops[i];
+      o.peer = t.root;
+      o.isSend = t.func == FUNC_SEND;
+      o.buf = o.isSend ? (void*)t.send : t.recv;
+      o.bytes = t.count * typeSize(t.type);
+      size_t chunks = (o.bytes + kP2pChunkBytes - 1) / kP2pChunkBytes;
+      o.ctaCount = (int)std::max<size_t>(1, std::min<size_t>(chunks, (size_t)perOpCap));
+      o.ctaBegin = cta;
+      cta += o.ctaCount;
+    }
+    dp->launches++;
+    res = launchKernel(p2pKernelFn(), dim3(cta), dim3(kCtaThreads), 0, &a, stream, false);
+  }
+out:
+  if (cur != comm->cudaDev && cur >= 0) cudaSetDevice(cur);
+  return res;
+}
+
+// Latency/bandwidth model used only for ncclGroupSimulateEnd (microseconds).
+float devPlaneEstimateUs(ncclComm* comm, const Task& t) {
+  const int n = comm->nRanks;
+  const double bytes = (double)t.count * typeSize(t.type);
+  if (n == 1) return (float)(2.0 + bytes / 3.0e6);
+  const double linkGBs = comm->lsaAll ? 700.0 : 5.0;   // NVLink 5 through NVSwitch vs host sockets
+  double lat = comm->lsaAll ? 6.0 : 60.0, moved = bytes;
+  switch (t.func) {
+    case FUNC_ALLREDUCE: moved = 2.0 * bytes * (n - 1) / n; lat = bytes <= 32768 ? 4.0 : 9.0; break;
+    case FUNC_ALLGATHER: case FUNC_ALLTOALL: case FUNC_GATHER: moved = bytes * (n - 1); break;
+    case FUNC_REDUCESCATTER: moved = bytes * (n - 1); break;
+    default: break;
+  }
+  return (float)(lat + moved / (linkGBs * 1e3));
+}
+
+}  // namespace b200

@@ -1,0 +1,62 @@
+// GPU data plane of a communicator: the resource window (flags, flagged-line buffers, mailboxes,
+// staging area), algorithm selection and kernel launches.
+// Reference parity: the roles of src/enqueue.cc (plan + launch), src/sym_kernels.cc (kernel choice)
+// and src/scheduler/symmetric_sched.cc in the reference, reduced to one launch per collective.
+#pragma once
+#include "../kernels/launch.h"
+#include "../mem/symmetric.h"
+#include "comm.h"
+
+namespace b200 {
+
+struct TuningTable {
+  // Crossover sizes in bytes (per-rank message size of the call); measured defaults, overridable
+  // with NCCL_TUNING_FILE or the NCCL_B200_* parameters.
+  size_t arLLMax[kMaxRanks + 1];       // all-reduce: flagged-line one-shot up to this size
+  size_t arNvlsMin[kMaxRanks + 1];     // all-reduce: multimem from this size (below: P2P two-shot)
+  size_t agMcMin[kMaxRanks + 1];       // all-gather / broadcast: multimem.st from this size
+  size_t rsNvlsMin[kMaxRanks + 1];     // reduce-scatter: multimem.ld_reduce from this size
+  size_t ceMin;                        // copy-engine all-gather / all-to-all from this size (0 = never)
+  int nvlsCtas, p2pCtas, copyCtas, sendrecvCtas;
+  size_t bytesPerCta;                  // grow the grid by one CTA per this many bytes
+};
+
+struct DevicePlane {
+  void* resBase = nullptr;
+  size_t resSize = 0;
+  SymWindow* resWin = nullptr;
+  size_t offLL = 0, offMailbox = 0, offStage = 0, stageBytes = 0;
+  uint32_t* priv = nullptr;           // private device words: epochs, ll epoch, p2p sequence numbers
+  uint32_t* epochs = nullptr;
+  uint32_t* llEpoch = nullptr;
+  uint32_t* p2pSeq = nullptr;
+  uint64_t* sigSeen = nullptr;
+  cudaEvent_t lastEvent = nullptr;
+  cudaStream_t lastStream = nullptr;
+  bool hasLast = false;
+  int smCount = 0;
+  uint64_t timeoutNs = 0;
+  TuningTable tune;
+  void* hostStage = nullptr;          // pinned staging for the host-socket fallback
+  size_t hostStageBytes = 0;
+  uint64_t ceEpoch = 0;
+  uint64_t launches = 0;              // kernels launched by this communicator
+};
+
+ncclResult_t devPlaneCreate(ncclComm* comm);
+void devPlaneDestroy(ncclComm* comm);
+ncclResult_t devPlaneRun(ncclComm* comm, const Task& t, ncclSimInfo_t* sim = nullptr);
+ncclResult_t devPlaneRunP2pGroup(ncclComm* comm, const std::vector<Task>& tasks);
+ncclResult_t devPlaneCheckStatus(ncclComm* comm);   // turns a kernel-side time-out into an async error
+void tuningDefaults(TuningTable* t);
+ncclResult_t tuningLoadFile(TuningTable* t, const char* path);
+// Predicted duration (microseconds) of a task, used by ncclGroupSimulateEnd.
+float devPlaneEstimateUs(ncclComm* comm, const Task& t);
+
+// memory manager (mem/memmgr.cc)
+ncclResult_t memSuspend(ncclComm* comm);
+ncclResult_t memResume(ncclComm* comm);
+ncclResult_t memStats(ncclComm* comm, int stat, uint64_t* value);
+void memMgrDestroy(ncclComm* comm);
+
+}  // namespace b200

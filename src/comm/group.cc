@@ -1,0 +1,162 @@
+// Group semantics and the enqueue path.
+// ncclGroupStart/End nest per thread; calls made inside a group are queued and issued when the
+// outermost group ends: deferred communicator jobs first, then, per communicator in order of
+// first appearance, the collectives in program order with every run of consecutive send/recv
+// tasks fused into one launch. Outside a group a call is a group of one.
+// Reference parity: src/group.cc (:97-124 API, :309-384 launch loop, :598-760 groupLaunch,
+// :766-887 group end), src/enqueue.cc:3014-3172 (taskAppend / ncclEnqueueCheck).
+#include <algorithm>
+
+#include "device_plane.h"
+
+namespace b200 {
+
+struct GroupState {
+  int depth = 0;
+  std::vector<Task> tasks;
+  std::vector<std::function<ncclResult_t()>> jobs;
+  ncclResult_t error = ncclSuccess;
+};
+static thread_local GroupState tGroup;
+
+int groupDepth() { return tGroup.depth; }
+
+ncclResult_t groupStart() {
+  tGroup.depth++;
+  return ncclSuccess;
+}
+
+ncclResult_t groupRunOrDefer(std::function<ncclResult_t()> fn) {
+  if (tGroup.depth == 0) return fn();
+  tGroup.jobs.push_back(std::move(fn));
+  return ncclSuccess;
+}
+
+static ncclResult_t runTask(ncclComm* comm, const Task& t) {
+  comm->opCount++;
+  INFO(SUB_COLL, "%s: opCount %llx sendbuff %p recvbuff %p count %zu datatype %d op %d root %d comm %p [nranks=%d] stream %p",
+       funcName(t.func), (unsigned long long)comm->opCount, t.send, t.recv, t.count, (int)t.type, t.op, t.root, (void*)comm,
+       comm->nRanks, (void*)t.stream);
+  if (comm->hostOnly) {
+    if (comm->nRanks == 1) {
+      Task one = t;
+      // single host rank: copy (and scale for pre-multiplied sums) in place
+      size_t bytes = t.count * typeSize(t.type);
+      if (t.func == FUNC_ALLGATHER || t.func == FUNC_GATHER || t.func == FUNC_ALLTOALL || t.func == FUNC_SCATTER ||
+          t.func == FUNC_BROADCAST || t.op < ncclNumOps) {
+        if (t.send != t.recv && t.send && t.recv) memcpy(t.recv, t.send, bytes);
+        return ncclSuccess;
+      }
+    }
+    return hostPlaneRun(comm, t);
+  }
+  return devPlaneRun(comm, t);
+}
+
+static ncclResult_t runP2p(ncclComm* comm, const std::vector<Task>& p2p) {
+  if (p2p.empty()) return ncclSuccess;
+  comm->opCount++;
+  if (comm->hostOnly) {
+    if (comm->nRanks == 1) {
+      std::vector<const Task*> s, r;
+      for (auto& t : p2p) (t.func == FUNC_SEND ? s : r).push_back(&t);
+      if (s.size() != r.size()) return ncclInvalidUsage;
+      for (size_t i = 0; i < s.size(); ++i) memcpy(r[i]->recv, s[i]->send, s[i]->count * typeSize(s[i]->type));
+      return ncclSuccess;
+    }
+    return hostPlaneRunP2pGroup(comm, p2p);
+  }
+  return devPlaneRunP2pGroup(comm, p2p);
+}
+
+static ncclResult_t launchAll(std::vector<Task>& tasks, ncclSimInfo_t* sim) {
+  // communicators in order of first appearance
+  std::vector<ncclComm*> comms;
+  for (auto& t : tasks) if (std::find(comms.begin(), comms.end(), t.comm) == comms.end()) comms.push_back(t.comm);
+  float simUs = 0;
+  for (ncclComm* comm : comms) {
+    std::vector<Task> p2p;
+    float commUs = 0;
+    for (auto& t : tasks) {
+      if (t.comm != comm) continue;
+      if (sim) { commUs += comm->hostOnly ? 0.f : devPlaneEstimateUs(comm, t); continue; }
+      if (t.func == FUNC_SEND || t.func == FUNC_RECV) { p2p.push_back(t); continue; }
+      NCCLCHECK(runP2p(comm, p2p));
+      p2p.clear();
+      NCCLCHECK(runTask(comm, t));
+    }
+    if (!sim) NCCLCHECK(runP2p(comm, p2p));
+    simUs = std::max(simUs, commUs);  // communicators of one group run concurrently
+  }
+  if (sim) sim->estimatedTime = simUs;
+  return ncclSuccess;
+}
+
+ncclResult_t groupEnd(ncclSimInfo_t* sim) {
+  if (tGroup.depth == 0) { WARN("ncclGroupEnd: not in a group call."); return ncclInvalidUsage; }
+  if (--tGroup.depth > 0) return ncclSuccess;
+  ncclResult_t res = tGroup.error;
+  std::vector<Task> tasks;
+  std::vector<std::function<ncclResult_t()>> jobs;
+  tasks.swap(tGroup.tasks);
+  jobs.swap(tGroup.jobs);
+  tGroup.error = ncclSuccess;
+  if (res != ncclSuccess) return res;
+  bool inProgress = false;
+  if (jobs.size() > 1) {
+    // communicator jobs of one group (e.g. one ncclCommInitRank per device) rendezvous with each
+    // other, so they must run concurrently
+    std::vector<std::thread> th;
+    std::vector<ncclResult_t> rs(jobs.size(), ncclSuccess);
+    int dev = -1;
+    cudaGetDevice(&dev);
+    (void)cudaGetLastError();
+    for (size_t i = 0; i < jobs.size(); ++i) th.emplace_back([&, i] { rs[i] = jobs[i](); });
+    for (auto& t : th) t.join();
+    for (auto r : rs) { if (r == ncclInProgress) inProgress = true; else if (r != ncclSuccess) return r; }
+  } else if (jobs.size() == 1) {
+    ncclResult_t r = jobs[0]();
+    if (r == ncclInProgress) inProgress = true; else if (r != ncclSuccess) return r;
+  }
+  NCCLCHECK(launchAll(tasks, sim));
+  return inProgress ? ncclInProgress : ncclSuccess;
+}
+
+ncclResult_t enqueueTask(const Task& t) {
+  ncclResult_t ready = commEnsureReady(t.comm);
+  if (ready != ncclSuccess) {
+    if (tGroup.depth > 0 && ready != ncclInProgress) tGroup.error = ready;
+    return ready;
+  }
+  ncclResult_t chk = argCheck(t, funcName(t.func));
+  if (chk != ncclSuccess) {
+    if (tGroup.depth > 0) tGroup.error = chk;
+    return chk;
+  }
+  if (tGroup.depth > 0) {
+    tGroup.tasks.push_back(t);
+    return ncclSuccess;
+  }
+  std::vector<Task> one{t};
+  if ((t.func == FUNC_SEND || t.func == FUNC_RECV) && t.root == t.comm->rank) {
+    WARN("%s to self outside of a group would never complete", funcName(t.func));
+    return ncclInvalidUsage;
+  }
+  return launchAll(one, nullptr);
+}
+
+}  // namespace b200
+
+extern "C" {
+ncclResult_t ncclGroupStart(void) { return b200::groupStart(); }
+ncclResult_t ncclGroupEnd(void) { return b200::groupEnd(nullptr); }
+ncclResult_t ncclGroupSimulateEnd(ncclSimInfo_t* simInfo) {
+  if (simInfo && simInfo->magic != 0x74685283) { WARN("ncclSimInfo_t was not initialised with NCCL_SIM_INFO_INITIALIZER"); return ncclInvalidArgument; }
+  ncclSimInfo_t local = NCCL_SIM_INFO_INITIALIZER;
+  ncclResult_t r = b200::groupEnd(simInfo ? simInfo : &local);
+  return r;
+}
+ncclResult_t pncclGroupStart(void) { return ncclGroupStart(); }
+ncclResult_t pncclGroupEnd(void) { return ncclGroupEnd(); }
+ncclResult_t pncclGroupSimulateEnd(ncclSimInfo_t* s) { return ncclGroupSimulateEnd(s); }
+}

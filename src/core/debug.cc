@@ -1,0 +1,130 @@
+// Logging: NCCL_DEBUG level, NCCL_DEBUG_SUBSYS mask, NCCL_DEBUG_FILE (%h host, %p pid),
+// optional timestamps. Reference parity: src/debug.cc:45-110,197-220 (same env names,
+// same "host:pid:tid [dev] NCCL LEVEL msg" line shape).
+#include <errno.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <sys/syscall.h>
+#include <sys/time.h>
+#include <unistd.h>
+
+#include <mutex>
+
+#include "core.h"
+
+namespace b200 {
+
+static std::once_flag gOnce;
+static int gLevel = -1;
+static uint64_t gMask = SUB_INIT | SUB_BOOTSTRAP | SUB_ENV;
+static FILE* gFile = nullptr;
+static char gHost[256];
+static int gPid;
+static bool gTimestamps = false;
+static std::mutex gLock;
+static char gLastError[1024] = "";
+static thread_local char tName[32] = "";
+
+struct SubName { const char* name; uint64_t bit; };
+static const SubName kSubs[] = {
+    {"INIT", SUB_INIT}, {"COLL", SUB_COLL}, {"P2P", SUB_P2P}, {"SHM", SUB_SHM}, {"NET", SUB_NET},
+    {"GRAPH", SUB_GRAPH}, {"TUNING", SUB_TUNING}, {"ENV", SUB_ENV}, {"ALLOC", SUB_ALLOC}, {"CALL", SUB_CALL},
+    {"PROXY", SUB_PROXY}, {"NVLS", SUB_NVLS}, {"BOOTSTRAP", SUB_BOOTSTRAP}, {"REG", SUB_REG},
+    {"PROFILE", SUB_PROFILE}, {"RAS", SUB_RAS}, {"ALL", SUB_ALL}};
+
+static void initOnce() {
+  const char* lv = getenv("NCCL_DEBUG");
+  gLevel = LOG_NONE;
+  if (lv) {
+    if (!strcasecmp(lv, "VERSION")) gLevel = LOG_VERSION;
+    else if (!strcasecmp(lv, "WARN")) gLevel = LOG_WARN;
+    else if (!strcasecmp(lv, "INFO")) gLevel = LOG_INFO;
+    else if (!strcasecmp(lv, "ABORT")) gLevel = LOG_ABORT;
+    else if (!strcasecmp(lv, "TRACE")) gLevel = LOG_TRACE;
+  }
+  const char* subs = getenv("NCCL_DEBUG_SUBSYS");
+  if (subs) {
+    bool invert = subs[0] == '^';
+    if (invert) subs++;
+    uint64_t m = 0;
+    std::string s(subs);
+    size_t pos = 0;
+    while (pos <= s.size()) {
+      size_t c = s.find(',', pos);
+      std::string tok = s.substr(pos, c == std::string::npos ? std::string::npos : c - pos);
+      for (auto& k : kSubs) if (!strcasecmp(tok.c_str(), k.name)) m |= k.bit;
+      if (c == std::string::npos) break;
+      pos = c + 1;
+    }
+    gMask = invert ? ~m : m;
+  }
+  gethostname(gHost, sizeof(gHost) - 1);
+  for (char* p = gHost; *p; ++p) if (*p == '.') { *p = 0; break; }
+  gPid = getpid();
+  gFile = stdout;
+  const char* f = getenv("NCCL_DEBUG_FILE");
+  if (f && gLevel > LOG_VERSION) {
+    std::string out;
+    for (const char* p = f; *p; ++p) {
+      if (*p == '%' && p[1] == 'h') { out += gHost; ++p; }
+      else if (*p == '%' && p[1] == 'p') { out += std::to_string(gPid); ++p; }
+      else if (*p == '%' && p[1] == '%') { out += '%'; ++p; }
+      else out += *p;
+    }
+    FILE* fp = fopen(out.c_str(), "w");
+    if (fp) { setvbuf(fp, nullptr, _IOLBF, 0); gFile = fp; }
+  }
+  const char* ts = getenv("NCCL_DEBUG_TIMESTAMP_LEVELS");
+  gTimestamps = ts && *ts && strcasecmp(ts, "NONE") != 0;
+}
+
+int debugLevel() {
+  std::call_once(gOnce, initOnce);
+  return gLevel;
+}
+
+const char* lastErrorString() { return gLastError; }
+
+void setThreadName(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tName, sizeof(tName), fmt, ap);
+  va_end(ap);
+}
+
+void debugLog(LogLevel level, uint64_t subsys, const char* file, int line, const char* fmt, ...) {
+  std::call_once(gOnce, initOnce);
+  char msg[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(msg, sizeof(msg), fmt, ap);
+  va_end(ap);
+  if (level == LOG_WARN) {
+    std::lock_guard<std::mutex> g(gLock);
+    snprintf(gLastError, sizeof(gLastError), "%s", msg);
+  }
+  if (gLevel < (int)level) return;
+  if (level != LOG_WARN && !(subsys & gMask)) return;
+  int dev = -1;
+  // cudaGetDevice is cheap and never initialises a context; ignore errors on GPU-less hosts.
+  if (cudaGetDevice(&dev) != cudaSuccess) { (void)cudaGetLastError(); dev = -1; }
+  long tid = syscall(SYS_gettid);
+  char stamp[48] = "";
+  if (gTimestamps) {
+    struct timeval tv;
+    gettimeofday(&tv, nullptr);
+    snprintf(stamp, sizeof(stamp), "[%ld.%06ld] ", (long)tv.tv_sec, (long)tv.tv_usec);
+  }
+  const char* base = strrchr(file, '/');
+  base = base ? base + 1 : file;
+  std::lock_guard<std::mutex> g(gLock);
+  if (level == LOG_WARN)
+    fprintf(gFile, "\n%s%s:%d:%ld [%d] %s:%d NCCL WARN %s\n", stamp, gHost, gPid, tid, dev, base, line, msg);
+  else if (level == LOG_INFO)
+    fprintf(gFile, "%s%s:%d:%ld [%d] NCCL INFO %s\n", stamp, gHost, gPid, tid, dev, msg);
+  else
+    fprintf(gFile, "%s%s:%d:%ld [%d] %s:%d NCCL TRACE %s\n", stamp, gHost, gPid, tid, dev, base, line, msg);
+  fflush(gFile);
+}
+
+}  // namespace b200

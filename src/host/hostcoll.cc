@@ -1,0 +1,297 @@
+// Host-memory data plane: every collective executed by the calling thread over a full mesh of
+// persistent TCP connections between the ranks. It serves communicators created on machines
+// without a GPU (buffers are host pointers) and is the fallback that GPU communicators stage
+// through when ranks are not load/store reachable (different hosts, P2P disabled).
+// Schedules: ring reduce-scatter + ring all-gather for all-reduce (the classic 2(n-1)-step
+// schedule, reference: src/device/all_reduce.h:14-83 runs the same steps on the GPU), rings for
+// all-gather / reduce-scatter, chains for broadcast / reduce, pairwise exchange for all-to-all.
+#include <algorithm>
+#include <functional>
+
+#include "../comm/comm.h"
+#include "hosttypes.h"
+
+namespace b200 {
+
+struct HostPlane {
+  std::vector<Socket> peer;   // peer[r] connected to rank r (unused for r == rank)
+  std::vector<char> tmp;
+};
+
+static constexpr int kTagHostMesh = BS_TAG_USER + 1;
+
+ncclResult_t hostPlaneCreate(ncclComm* comm) {
+  HostPlane* hp = new HostPlane;
+  int n = comm->nRanks, me = comm->rank;
+  hp->peer.resize(n);
+  // Higher ranks listen, lower ranks dial: connects land in the listen backlog, so dialling
+  // everything first and accepting afterwards cannot deadlock.
+  for (int r = me + 1; r < n; ++r) {
+    ncclResult_t res = bootstrapConnect(comm->bootstrap, r, kTagHostMesh, &hp->peer[r]);
+    if (res != ncclSuccess) { delete hp; return res; }
+  }
+  for (int r = 0; r < me; ++r) {
+    ncclResult_t res = bootstrapAccept(comm->bootstrap, r, kTagHostMesh, &hp->peer[r]);
+    if (res != ncclSuccess) { delete hp; return res; }
+  }
+  comm->hostPlane = hp;
+  return ncclSuccess;
+}
+
+void hostPlaneDestroy(ncclComm* comm) {
+  if (!comm->hostPlane) return;
+  for (auto& s : comm->hostPlane->peer) sockClose(&s);
+  delete comm->hostPlane;
+  comm->hostPlane = nullptr;
+}
+
+static ncclResult_t exchange(HostPlane* hp, int to, const void* sbuf, size_t sbytes, int from, void* rbuf, size_t rbytes) {
+  // messages larger than INT_MAX are cut in pieces; both sides cut identically
+  const size_t piece = 1u << 30;
+  size_t so = 0, ro = 0;
+  while (so < sbytes || ro < rbytes) {
+    int sn = (int)std::min(piece, sbytes - so), rn = (int)std::min(piece, rbytes - ro);
+    SockOp ops[2];
+    int k = 0;
+    if (sn > 0) ops[k++] = SockOp{SOCK_OP_SEND, &hp->peer[to], (char*)sbuf + so, sn, 0};
+    if (rn > 0) ops[k++] = SockOp{SOCK_OP_RECV, &hp->peer[from], (char*)rbuf + ro, rn, 0};
+    NCCLCHECK(sockMultiOp(ops, k));
+    so += sn;
+    ro += rn;
+  }
+  return ncclSuccess;
+}
+
+struct Chunks {
+  size_t count;
+  int n;
+  size_t off(int i) const { size_t base = count / n, rem = count % n; return (size_t)i * base + std::min<size_t>(i, rem); }
+  size_t len(int i) const { return count / n + ((size_t)i < count % n ? 1 : 0); }
+};
+
+struct OpDesc {
+  int hop;            // HostOp
+  bool premul = false, postscale = false;
+  double scale = 1.0;
+  int64_t intDiv = 1;
+};
+
+static ncclResult_t resolveOp(ncclComm* comm, const Task& t, OpDesc* d) {
+  if (t.op == ncclSum || t.op == ncclProd || t.op == ncclMax || t.op == ncclMin) {
+    d->hop = t.op == ncclSum ? HOP_SUM : t.op == ncclProd ? HOP_PROD : t.op == ncclMax ? HOP_MAX : HOP_MIN;
+    return ncclSuccess;
+  }
+  if (t.op == ncclAvg) {
+    d->hop = HOP_SUM;
+    d->postscale = true;
+    d->scale = 1.0 / comm->nRanks;
+    d->intDiv = comm->nRanks;
+    return ncclSuccess;
+  }
+  int idx = t.op - ncclNumOps;
+  if (idx < 0 || idx >= (int)comm->userOps.size() || !comm->userOps[idx].used) {
+    WARN("invalid reduction operator %d", t.op);
+    return ncclInvalidArgument;
+  }
+  const UserRedOp& u = comm->userOps[idx];
+  uint64_t bits = u.scalarBits;
+  if (u.residence == ncclScalarDevice) memcpy(&bits, u.devScalar, typeSize(u.type));  // host plane: plain memory
+  d->hop = HOP_SUM;
+  d->premul = true;
+  switch (u.type) {
+    case ncclFloat32: { float f; memcpy(&f, &bits, 4); d->scale = f; } break;
+    case ncclFloat64: { double f; memcpy(&f, &bits, 8); d->scale = f; } break;
+    case ncclFloat16: d->scale = halfToFloat((uint16_t)bits); break;
+    case ncclBfloat16: d->scale = bf16ToFloat((uint16_t)bits); break;
+    case ncclFloat8e4m3: d->scale = e4m3ToFloat((uint8_t)bits); break;
+    case ncclFloat8e5m2: d->scale = e5m2ToFloat((uint8_t)bits); break;
+    default: {
+      // integer pre-multiply
+      int64_t v = 0;
+      memcpy(&v, &bits, typeSize(u.type));
+      d->scale = (double)v;
+    }
+  }
+  return ncclSuccess;
+}
+
+static void premulInto(void* dst, size_t n, ncclDataType_t type, const OpDesc& d) {
+  if (!d.premul) return;
+  switch (type) {
+    case ncclInt8: case ncclUint8: case ncclInt32: case ncclUint32: case ncclInt64: case ncclUint64: {
+      int64_t m = (int64_t)d.scale;
+      size_t es = typeSize(type);
+      for (size_t i = 0; i < n; ++i) {
+        int64_t v = 0;
+        memcpy(&v, (char*)dst + i * es, es);
+        if (type == ncclInt8) v = (int8_t)v; else if (type == ncclInt32) v = (int32_t)v;
+        v *= m;
+        memcpy((char*)dst + i * es, &v, es);
+      }
+    } break;
+    default: hostScale(dst, n, type, d.scale, 1);
+  }
+}
+
+static ncclResult_t ringReduceScatterInPlace(ncclComm* comm, char* buf, const Chunks& ch, size_t es, ncclDataType_t type, int hop,
+                                             int shift) {
+  // After n-1 steps rank r holds the fully reduced chunk (r + shift) mod n.
+  HostPlane* hp = comm->hostPlane;
+  int n = comm->nRanks, r = comm->rank, next = (r + 1) % n, prev = (r - 1 + n) % n;
+  hp->tmp.resize((ch.count / n + 1) * es);
+  for (int s = 0; s < n - 1; ++s) {
+    int sc = ((r + shift - 1 - s) % n + 2 * n) % n, rc = ((r + shift - 2 - s) % n + 2 * n) % n;
+    NCCLCHECK(exchange(hp, next, buf + ch.off(sc) * es, ch.len(sc) * es, prev, hp->tmp.data(), ch.len(rc) * es));
+    hostReduceInto(buf + ch.off(rc) * es, hp->tmp.data(), ch.len(rc), type, hop);
+  }
+  return ncclSuccess;
+}
+
+static ncclResult_t ringAllGatherInPlace(ncclComm* comm, char* buf, const Chunks& ch, size_t es, int shift) {
+  // Rank r starts owning chunk (r + shift) mod n.
+  HostPlane* hp = comm->hostPlane;
+  int n = comm->nRanks, r = comm->rank, next = (r + 1) % n, prev = (r - 1 + n) % n;
+  for (int s = 0; s < n - 1; ++s) {
+    int sc = ((r + shift - s) % n + 2 * n) % n, rc = ((r + shift - 1 - s) % n + 2 * n) % n;
+    NCCLCHECK(exchange(hp, next, buf + ch.off(sc) * es, ch.len(sc) * es, prev, buf + ch.off(rc) * es, ch.len(rc) * es));
+  }
+  return ncclSuccess;
+}
+
+ncclResult_t hostPlaneRun(ncclComm* comm, const Task& t) {
+  HostPlane* hp = comm->hostPlane;
+  if (!hp) return ncclInternalError;
+  const int n = comm->nRanks, r = comm->rank;
+  const size_t es = typeSize(t.type);
+  OpDesc od{};
+  switch (t.func) {
+    case FUNC_ALLREDUCE: {
+      NCCLCHECK(resolveOp(comm, t, &od));
+      if (t.recv != t.send) memcpy(t.recv, t.send, t.count * es);
+      premulInto(t.recv, t.count, t.type, od);
+      if (n > 1) {
+        Chunks ch{t.count, n};
+        NCCLCHECK(ringReduceScatterInPlace(comm, (char*)t.recv, ch, es, t.type, od.hop, 1));
+        NCCLCHECK(ringAllGatherInPlace(comm, (char*)t.recv, ch, es, 1));
+      }
+      if (od.postscale) hostScale(t.recv, t.count, t.type, od.scale, od.intDiv);
+    } break;
+    case FUNC_REDUCESCATTER: {
+      NCCLCHECK(resolveOp(comm, t, &od));
+      size_t total = t.count * n;
+      std::vector<char> work(total * es);
+      memcpy(work.data(), t.send, total * es);
+      premulInto(work.data(), total, t.type, od);
+      Chunks ch{total, n};  // equal chunks of t.count
+      if (n > 1) NCCLCHECK(ringReduceScatterInPlace(comm, work.data(), ch, es, t.type, od.hop, 0));
+      memcpy(t.recv, work.data() + (size_t)r * t.count * es, t.count * es);
+      if (od.postscale) hostScale(t.recv, t.count, t.type, od.scale, od.intDiv);
+    } break;
+    case FUNC_ALLGATHER: {
+      char* out = (char*)t.recv;
+      if (out + (size_t)r * t.count * es != t.send) memcpy(out + (size_t)r * t.count * es, t.send, t.count * es);
+      Chunks ch{t.count * n, n};
+      if (n > 1) NCCLCHECK(ringAllGatherInPlace(comm, out, ch, es, 0));
+    } break;
+    case FUNC_BROADCAST: {
+      if (r == t.root) {
+        if (t.recv != t.send) memcpy(t.recv, t.send, t.count * es);
+        for (int p = 0; p < n; ++p) if (p != r) NCCLCHECK(exchange(hp, p, t.send, t.count * es, p, nullptr, 0));
+      } else {
+        NCCLCHECK(exchange(hp, t.root, nullptr, 0, t.root, t.recv, t.count * es));
+      }
+    } break;
+    case FUNC_REDUCE: {
+      NCCLCHECK(resolveOp(comm, t, &od));
+      // chain root+1 -> root+2 -> ... -> root, each hop adds its own contribution
+      std::vector<char> acc(t.count * es);
+      memcpy(acc.data(), t.send, t.count * es);
+      premulInto(acc.data(), t.count, t.type, od);
+      int pos = (r - t.root - 1 + n) % n;  // 0 = first in chain, n-1 = root
+      int prev = (r - 1 + n) % n, next = (r + 1) % n;
+      if (n > 1 && pos > 0) {
+        hp->tmp.resize(t.count * es);
+        NCCLCHECK(exchange(hp, prev, nullptr, 0, prev, hp->tmp.data(), t.count * es));
+        hostReduceInto(acc.data(), hp->tmp.data(), t.count, t.type, od.hop);
+      }
+      if (n > 1 && pos < n - 1) NCCLCHECK(exchange(hp, next, acc.data(), t.count * es, next, nullptr, 0));
+      if (r == t.root) {
+        memcpy(t.recv, acc.data(), t.count * es);
+        if (od.postscale) hostScale(t.recv, t.count, t.type, od.scale, od.intDiv);
+      }
+    } break;
+    case FUNC_ALLTOALL: {
+      size_t b = t.count * es;
+      memcpy((char*)t.recv + (size_t)r * b, (const char*)t.send + (size_t)r * b, b);
+      for (int s = 1; s < n; ++s) {
+        int to = (r + s) % n, from = (r - s + n) % n;
+        NCCLCHECK(exchange(hp, to, (const char*)t.send + (size_t)to * b, b, from, (char*)t.recv + (size_t)from * b, b));
+      }
+    } break;
+    case FUNC_GATHER: {
+      size_t b = t.count * es;
+      if (r == t.root) {
+        memcpy((char*)t.recv + (size_t)r * b, t.send, b);
+        for (int p = 0; p < n; ++p) if (p != r) NCCLCHECK(exchange(hp, p, nullptr, 0, p, (char*)t.recv + (size_t)p * b, b));
+      } else {
+        NCCLCHECK(exchange(hp, t.root, t.send, b, t.root, nullptr, 0));
+      }
+    } break;
+    case FUNC_SCATTER: {
+      size_t b = t.count * es;
+      if (r == t.root) {
+        memcpy(t.recv, (const char*)t.send + (size_t)r * b, b);
+        for (int p = 0; p < n; ++p) if (p != r) NCCLCHECK(exchange(hp, p, (const char*)t.send + (size_t)p * b, b, p, nullptr, 0));
+      } else {
+        NCCLCHECK(exchange(hp, t.root, nullptr, 0, t.root, t.recv, b));
+      }
+    } break;
+    case FUNC_SEND: NCCLCHECK(exchange(hp, t.root, t.send, t.count * es, t.root, nullptr, 0)); break;
+    case FUNC_RECV: NCCLCHECK(exchange(hp, t.root, nullptr, 0, t.root, t.recv, t.count * es)); break;
+    default:
+      WARN("host plane: %s is not available on host-memory communicators", funcName(t.func));
+      return ncclInvalidUsage;
+  }
+  return ncclSuccess;
+}
+
+// A group of sends and receives progresses all at once so that any matching order works.
+ncclResult_t hostPlaneRunP2pGroup(ncclComm* comm, const std::vector<Task>& tasks) {
+  HostPlane* hp = comm->hostPlane;
+  std::vector<SockOp> ops;
+  for (auto& t : tasks) {
+    size_t bytes = t.count * typeSize(t.type);
+    if (bytes > (size_t)INT32_MAX) { WARN("host plane: grouped p2p larger than 2 GiB"); return ncclInvalidArgument; }
+    if (t.root == comm->rank) continue;  // self send/recv pairs are matched below
+    if (t.func == FUNC_SEND) ops.push_back(SockOp{SOCK_OP_SEND, &hp->peer[t.root], (void*)t.send, (int)bytes, 0});
+    else if (t.func == FUNC_RECV) ops.push_back(SockOp{SOCK_OP_RECV, &hp->peer[t.root], t.recv, (int)bytes, 0});
+  }
+  std::vector<const Task*> selfSend, selfRecv;
+  for (auto& t : tasks) if (t.root == comm->rank) (t.func == FUNC_SEND ? selfSend : selfRecv).push_back(&t);
+  if (selfSend.size() != selfRecv.size()) { WARN("unmatched send/recv to self"); return ncclInvalidUsage; }
+  for (size_t i = 0; i < selfSend.size(); ++i)
+    memcpy(selfRecv[i]->recv, selfSend[i]->send, selfSend[i]->count * typeSize(selfSend[i]->type));
+  // Per-socket byte streams keep the order in which the ops were posted; progress them together.
+  // sockMultiOp advances every op, but two ops on the same socket+direction must run in order.
+  std::vector<SockOp> wave;
+  std::vector<char> done(ops.size(), 0);
+  size_t left = ops.size();
+  while (left) {
+    wave.clear();
+    std::vector<size_t> idx;
+    for (size_t i = 0; i < ops.size(); ++i) {
+      if (done[i]) continue;
+      bool clash = false;
+      for (auto& w : wave) if (w.sock == ops[i].sock && w.kind == ops[i].kind) clash = true;
+      if (clash) continue;
+      wave.push_back(ops[i]);
+      idx.push_back(i);
+    }
+    NCCLCHECK(sockMultiOp(wave.data(), (int)wave.size()));
+    for (size_t i : idx) done[i] = 1;
+    left -= idx.size();
+  }
+  return ncclSuccess;
+}
+
+}  // namespace b200

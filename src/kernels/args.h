@@ -1,0 +1,115 @@
+// Kernel argument blocks shared by host and device code.
+// One block (< 4 KiB, passed by value) describes a whole collective for one rank. Pointer tables
+// are indexed by rank: table[p] is where rank p's buffer is mapped in the address space of the
+// GPU that runs the kernel (symmetric windows), so the same block layout serves real multi-GPU
+// launches and the single-GPU emulation used by unit tests, where one cooperative grid plays
+// every rank (rank = blockIdx.y) over buffers that all live on one device.
+// Reference parity: ncclSymkDevWorkArgs / ncclDevKernelArgs (src/include/sym_kernels.h:75-114,
+// src/include/device.h:419-496) play this role in the reference.
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+namespace b200 {
+
+constexpr int kMaxRanks = 8;            // ranks of one load/store domain served by the kernels
+constexpr int kBarrierSlots = 256;      // one slot per CTA index
+constexpr int kMaxCtas = 148;           // never more CTAs than SMs: CTAs of one grid wait on peers' CTAs
+constexpr int kCtaThreads = 512;
+
+// Layout of the per-rank synchronisation page (first bytes of the resource window).
+constexpr size_t kInboxBytes = kBarrierSlots * kMaxRanks * sizeof(uint32_t);   // 8 KiB
+constexpr int kP2pSlots = 4;                       // mailbox chunks in flight per ordered pair
+constexpr size_t kP2pChunkBytes = 1 << 20;
+constexpr size_t kOffP2pReady = kInboxBytes;                                        // [src][slot] u32, written by sender
+constexpr size_t kOffP2pAck = kOffP2pReady + kMaxRanks * kP2pSlots * 4;             // [dst][slot] u32, written by receiver
+constexpr size_t kOffSignals = kOffP2pAck + kMaxRanks * kP2pSlots * 4;              // [src][kSignalsPerPeer] u64
+constexpr int kSignalsPerPeer = 64;
+constexpr size_t kOffSyncEnd = kOffSignals + kMaxRanks * kSignalsPerPeer * 8;
+constexpr size_t kSyncPageBytes = 64 << 10;
+static_assert(kOffSyncEnd <= kSyncPageBytes, "sync page overflow");
+
+constexpr size_t kLLDataBytes = 256 << 10;                   // largest payload of the flagged-line protocol
+constexpr size_t kLLLines = kLLDataBytes / 8;                // 8 payload bytes per 16-byte line
+constexpr size_t kLLRegionBytes = 2 * kMaxRanks * kLLLines * 16;   // [parity][src][line]
+constexpr size_t kMailboxBytes = (size_t)kMaxRanks * kP2pSlots * kP2pChunkBytes;  // [src][slot][chunk]
+
+enum DevStatus : uint32_t { DEV_OK = 0, DEV_TIMEOUT = 1, DEV_ABORTED = 2 };
+enum DevWaitKind : uint32_t { WAIT_BARRIER = 1, WAIT_LL = 2, WAIT_P2P_READY = 3, WAIT_P2P_ACK = 4, WAIT_SIGNAL = 5, WAIT_TILE = 6 };
+
+struct SyncArgs {
+  uint32_t* inbox[kMaxRanks];     // inbox[p]: rank p's barrier inbox [slot][src]
+  uint32_t* epoch[kMaxRanks];     // epoch[r]: rank r's private epoch counters [slot]
+  uint32_t* status[kMaxRanks];    // status[r]: {code, kind, peer, expected} written on a failed wait
+  const uint32_t* abortFlag;      // set by the host to make every wait give up
+  unsigned long long timeoutNs;   // budget of one wait
+};
+
+enum RedOp : int { RED_SUM = 0, RED_PROD = 1, RED_MAX = 2, RED_MIN = 3 };
+enum ScaleMode : int { SCALE_NONE = 0, SCALE_MUL = 1, SCALE_INTDIV = 2 };
+
+enum CollMode : int {
+  MODE_PUSH = 0,     // writer stores into peers' buffers
+  MODE_PULL = 1,     // reader loads from peers' buffers
+  MODE_MC = 2,       // one multimem.st stream reaches every peer
+};
+
+struct CollArgs {
+  int rank, nRanks;
+  int emu;                              // 1: blockIdx.y selects the rank
+  int func;                             // Func
+  int root;
+  int mode;                             // CollMode (copy collectives)
+  int vec16;                            // every pointer and slice is 16-byte aligned
+  int dstAll;                           // reductions: store the result to every rank (all-reduce) or locally
+  const void* send[kMaxRanks];          // peer-visible inputs
+  void* recv[kMaxRanks];                // peer-visible outputs
+  const void* lsend[kMaxRanks];         // rank-private input pointers (lsend[r] is only touched by rank r)
+  void* lrecv[kMaxRanks];               // rank-private output pointers
+  const void* sendMc;                   // multicast alias of send (NVLS) or null
+  void* recvMc;                         // multicast alias of recv
+  size_t count;                         // elements: all-reduce/broadcast/reduce total; per-rank block otherwise
+  size_t sendStride, recvStride;        // copy collectives: bytes between consecutive blocks of the input / output
+  size_t sliceBegin[kMaxRanks];         // reductions: first element reduced by rank r
+  size_t sliceCount[kMaxRanks];         // reductions: number of elements reduced by rank r
+  size_t dstOff[kMaxRanks];             // reductions: element offset of rank r's result inside the output
+  int scaleMode;
+  float scaleF;
+  double scaleD;
+  long long intDiv;
+  SyncArgs sync;
+  // flagged-line (LL) resources
+  void* ll[kMaxRanks];                  // ll[p]: rank p's LL region
+  uint32_t* llEpoch[kMaxRanks];         // llEpoch[r]: {epoch, finished CTAs} private to rank r
+};
+
+struct P2pOp {
+  int peer;
+  int isSend;
+  void* buf;             // rank-private user buffer
+  size_t bytes;
+  int ctaBegin, ctaCount;   // CTAs [ctaBegin, ctaBegin+ctaCount) of the grid serve this op
+};
+constexpr int kMaxP2pOps = 32;
+
+struct P2pArgs {
+  int rank, nRanks;
+  int emu;
+  int nOps[kMaxRanks];                   // ops of rank r (only [rank] outside emulation)
+  P2pOp ops[kMaxP2pOps];                 // emulation packs every rank's ops back to back: opBase[r]
+  int opBase[kMaxRanks];
+  char* mailbox[kMaxRanks];              // mailbox[p]: rank p's mailbox region [src][slot][chunk]
+  uint32_t* ready[kMaxRanks];            // ready[p]: rank p's [src][slot] flags
+  uint32_t* ack[kMaxRanks];              // ack[p]: rank p's [dst][slot] flags
+  uint32_t* seq[kMaxRanks];              // seq[r]: private counters {send[kMaxRanks], recv[kMaxRanks]}
+  SyncArgs sync;
+};
+
+struct SignalArgs {
+  int rank, nRanks;
+  uint64_t* signals[kMaxRanks];          // signals[p]: rank p's [src][kSignalsPerPeer] counters
+  uint64_t* seen;                        // private [src][kSignalsPerPeer]: how many were consumed
+  SyncArgs sync;
+};
+
+}  // namespace b200

@@ -1,0 +1,330 @@
+// Data-movement kernels without arithmetic.
+//   copyCollKernel   all-gather, broadcast, all-to-all, gather and scatter as direct peer stores
+//                    (push), peer loads (pull) or one multimem.st stream (mc). Every transfer is a
+//                    list of equal segments; CTAs interleave over segments so that all peers are
+//                    in flight at once, and segment order is rotated by rank so that no two ranks
+//                    target the same peer first.
+//   p2pKernel        grouped send/recv through per-pair mailboxes in the receiver's resource
+//                    window: chunked, kP2pSlots chunks in flight, ready/ack flags per slot.
+//   scaleKernel      dst = src * scalar (pre-multiplied sums, single-rank communicators).
+//   signal kernels   one-sided signal / wait-signal counters.
+// Reference parity: src/device/symmetric/all_gather.cuh:13-303 (ST / STMC), src/device/sendrecv.h,
+// contrib/custom_algos/alltoall/lsa_simple_alltoall_kernel.cuh, src/device/onerank.cu, src/rma/rma_ce.cc.
+#include "common.cuh"
+#include "launch.h"
+#include "../comm/comm.h"
+
+namespace b200 {
+
+struct Seg {
+  const char* src;
+  char* dst;
+  int mc;
+};
+
+__device__ __forceinline__ int buildSegs(const CollArgs& a, int rank, Seg* segs) {
+  const int n = a.nRanks;
+  const size_t SS = a.sendStride, RS = a.recvStride;  // block pitch of inputs / outputs (>= a.count)
+  int k = 0;
+  const char* ls = (const char*)a.lsend[rank];
+  char* lr = (char*)a.lrecv[rank];
+  switch (a.func) {
+    case FUNC_ALLGATHER:
+      if (a.mode == MODE_MC) {
+        segs[k++] = Seg{ls, (char*)a.recvMc + rank * RS, 1};
+      } else if (a.mode == MODE_PUSH) {
+        for (int j = 0; j < n; ++j) {
+          int p = (rank + j) % n;
+          char* d = (char*)a.recv[p] + rank * RS;
+          if (d != ls) segs[k++] = Seg{ls, d, 0};
+        }
+      } else {
+        for (int j = 0; j < n; ++j) {
+          int p = (rank + j) % n;
+          const char* s = p == rank ? ls : (const char*)a.send[p];
+          if (s != lr + p * RS) segs[k++] = Seg{s, lr + p * RS, 0};
+        }
+      }
+      break;
+    case FUNC_BROADCAST:
+      if (a.mode == MODE_MC) {
+        if (rank == a.root) segs[k++] = Seg{ls, (char*)a.recvMc, 1};
+      } else if (a.mode == MODE_PUSH) {
+        if (rank == a.root)
+          for (int j = 0; j < n; ++j) {
+            int p = (rank + j) % n;
+            char* d = (char*)a.recv[p];
+            if (d != ls) segs[k++] = Seg{ls, d, 0};
+          }
+      } else {
+        const char* s = rank == a.root ? ls : (const char*)a.send[a.root];
+        if (s != lr) segs[k++] = Seg{s, lr, 0};
+      }
+      break;
+    case FUNC_ALLTOALL:
+      for (int j = 0; j < n; ++j) {
+        int p = (rank + j) % n;
+        if (a.mode == MODE_PUSH) segs[k++] = Seg{ls + p * SS, (char*)a.recv[p] + rank * RS, 0};
+        else segs[k++] = Seg{(p == rank ? ls : (const char*)a.send[p]) + rank * SS, lr + p * RS, 0};
+      }
+      break;
+    case FUNC_GATHER:
+      if (a.mode == MODE_PUSH) {
+        segs[k++] = Seg{ls, (char*)a.recv[a.root] + rank * RS, 0};
+      } else if (rank == a.root) {
+        for (int j = 0; j < n; ++j) {
+          int p = (rank + j) % n;
+          segs[k++] = Seg{p == rank ? ls : (const char*)a.send[p], lr + p * RS, 0};
+        }
+      }
+      break;
+    case FUNC_SCATTER:
+      if (a.mode == MODE_PUSH) {
+        if (rank == a.root)
+          for (int j = 0; j < n; ++j) {
+            int p = (rank + j) % n;
+            segs[k++] = Seg{ls + p * SS, (char*)a.recv[p], 0};
+          }
+      } else {
+        segs[k++] = Seg{(rank == a.root ? ls : (const char*)a.send[a.root]) + rank * SS, lr, 0};
+      }
+      break;
+    default: break;
+  }
+  return k;
+}
+
+constexpr int kTilePacks = kCtaThreads * 4;  // 32 KiB per CTA tile
+
+__global__ void __launch_bounds__(kCtaThreads, 1) copyCollKernel(const __grid_constant__ CollArgs a) {
+  const int rank = ctaRank(a.emu, a.rank);
+  CtaBarrier bar;
+  bar.init(a.sync, rank, a.nRanks, blockIdx.x);
+  bool ok = bar.sync();
+  __shared__ Seg segs[kMaxRanks];
+  __shared__ int nSeg;
+  if (threadIdx.x == 0) nSeg = buildSegs(a, rank, segs);
+  __syncthreads();
+  const size_t B = a.count;
+  if (ok && nSeg > 0 && B > 0) {
+    if (a.vec16) {
+      const size_t packs = B / 16;
+      const size_t tilesPerSeg = (packs + kTilePacks - 1) / kTilePacks;
+      const size_t tiles = tilesPerSeg * nSeg;
+      for (size_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const Seg s = segs[t % nSeg];
+        const size_t base = (t / nSeg) * kTilePacks;
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          size_t i = base + u * kCtaThreads + threadIdx.x;
+          if (i < packs) v[u] = ldStream16(s.src + i * 16);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          size_t i = base + u * kCtaThreads + threadIdx.x;
+          if (i < packs) { if (s.mc) mcSt16(s.dst + i * 16, v[u]); else st16(s.dst + i * 16, v[u]); }
+        }
+      }
+      // bytes past the last whole pack (multicast stores need 16-byte units: the host only picks
+      // MODE_MC when B is a multiple of 16)
+      const size_t rem = B - packs * 16;
+      if (rem && blockIdx.x == 0)
+        for (size_t j = threadIdx.x; j < rem * nSeg; j += blockDim.x) {
+          const Seg s = segs[j / rem];
+          s.dst[packs * 16 + j % rem] = s.src[packs * 16 + j % rem];
+        }
+    } else {
+      const size_t stride = (size_t)gridDim.x * blockDim.x;
+      for (int si = 0; si < nSeg; ++si) {
+        const Seg s = segs[si];
+        for (size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x; j < B; j += stride) s.dst[j] = s.src[j];
+      }
+    }
+  }
+  bar.sync();
+  bar.finish();
+}
+
+// ------------------------------------------------------------------------- send / recv
+__device__ __forceinline__ void copyChunk(char* dst, const char* src, size_t bytes) {
+  if ((((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {
+    const size_t packs = bytes / 16;
+    size_t i = threadIdx.x;
+    for (; i + 3 * blockDim.x < packs; i += 4 * blockDim.x) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = ldStream16(src + (i + u * blockDim.x) * 16);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) st16(dst + (i + u * blockDim.x) * 16, v[u]);
+    }
+    for (; i < packs; i += blockDim.x) st16(dst + i * 16, ldStream16(src + i * 16));
+    for (size_t j = packs * 16 + threadIdx.x; j < bytes; j += blockDim.x) dst[j] = src[j];
+  } else {
+    for (size_t j = threadIdx.x; j < bytes; j += blockDim.x) dst[j] = src[j];
+  }
+}
+
+__global__ void __launch_bounds__(kCtaThreads, 1) p2pKernel(const __grid_constant__ P2pArgs a) {
+  const int rank = ctaRank(a.emu, a.rank);
+  const int nOps = a.nOps[rank];
+  const P2pOp* ops = a.ops + a.opBase[rank];
+  WaitCtx w{&a.sync, a.sync.status[rank]};
+  uint32_t* seq = a.seq[rank];  // [0,kMaxRanks) send counters, [kMaxRanks,2*kMaxRanks) recv counters, [2*kMaxRanks] finished CTAs
+  int mine = -1;
+  for (int i = 0; i < nOps; ++i)
+    if ((int)blockIdx.x >= ops[i].ctaBegin && (int)blockIdx.x < ops[i].ctaBegin + ops[i].ctaCount) mine = i;
+  if (mine >= 0) {
+    const P2pOp op = ops[mine];
+    const int local = blockIdx.x - op.ctaBegin;
+    const size_t nChunks = (op.bytes + kP2pChunkBytes - 1) / kP2pChunkBytes;
+    const uint32_t base = op.isSend ? seq[op.peer] : seq[kMaxRanks + op.peer];
+    bool ok = true;
+    for (size_t c = local; c < nChunks && ok; c += op.ctaCount) {
+      const uint32_t q = base + (uint32_t)c;
+      const int slot = q % kP2pSlots;
+      const size_t off = c * kP2pChunkBytes;
+      const size_t len = op.bytes - off < kP2pChunkBytes ? op.bytes - off : kP2pChunkBytes;
+      if (op.isSend) {
+        // the slot is free once the receiver has consumed the chunk that used it last (q - slots)
+        // (sequence numbers run across calls, so this also covers slots used by the previous call)
+        if (threadIdx.x == 0 && q >= (uint32_t)kP2pSlots) {
+          const uint32_t* ackp = a.ack[rank] + op.peer * kP2pSlots + slot;
+          const uint32_t want = q - kP2pSlots + 1;
+          ok = boundedWait(w, WAIT_P2P_ACK, (uint32_t)op.peer, want, [&] { return (int32_t)(ldAcquireSys(ackp) - want) >= 0; });
+        }
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+        char* dst = a.mailbox[op.peer] + ((size_t)rank * kP2pSlots + slot) * kP2pChunkBytes;
+        copyChunk(dst, (const char*)op.buf + off, len);
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          fenceSys();
+          stReleaseSys(a.ready[op.peer] + rank * kP2pSlots + slot, q + 1);
+        }
+      } else {
+        if (threadIdx.x == 0) {
+          const uint32_t* rdy = a.ready[rank] + op.peer * kP2pSlots + slot;
+          const uint32_t want = q + 1;
+          ok = boundedWait(w, WAIT_P2P_READY, (uint32_t)op.peer, want, [&] { return (int32_t)(ldAcquireSys(rdy) - want) >= 0; });
+        }
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+        const char* src = a.mailbox[rank] + ((size_t)op.peer * kP2pSlots + slot) * kP2pChunkBytes;
+        copyChunk((char*)op.buf + off, src, len);
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          fenceSys();
+          stReleaseSys(a.ack[op.peer] + rank * kP2pSlots + slot, q + 1);
+        }
+      }
+    }
+  }
+  // The last CTA of the grid advances the per-peer sequence numbers for the next launch.
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    uint32_t done = atomicAdd(&seq[2 * kMaxRanks], 1u);
+    if (done == gridDim.x - 1) {
+      seq[2 * kMaxRanks] = 0;
+      for (int i = 0; i < nOps; ++i) {
+        uint32_t chunks = (uint32_t)((ops[i].bytes + kP2pChunkBytes - 1) / kP2pChunkBytes);
+        if (ops[i].isSend) seq[ops[i].peer] += chunks; else seq[kMaxRanks + ops[i].peer] += chunks;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------- local scale
+template <typename T>
+__global__ void scaleKernel(ScaleArgs a) {
+  using A = typename Elem<T>::Acc;
+  T s;
+  if (a.scalarPtr) s = *(const T*)a.scalarPtr;
+  else memcpy(&s, &a.scalarBits, sizeof(T));
+  const A sa = Elem<T>::ld(s);
+  const T* src = (const T*)a.src;
+  T* dst = (T*)a.dst;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.count; i += (size_t)gridDim.x * blockDim.x)
+    dst[i] = Elem<T>::st(Elem<T>::ld(src[i]) * sa);
+}
+
+const void* scaleKernelFn(ncclDataType_t type) {
+  switch (type) {
+    case ncclInt8: return (const void*)scaleKernel<int8_t>;
+    case ncclUint8: return (const void*)scaleKernel<uint8_t>;
+    case ncclInt32: return (const void*)scaleKernel<int32_t>;
+    case ncclUint32: return (const void*)scaleKernel<uint32_t>;
+    case ncclInt64: return (const void*)scaleKernel<int64_t>;
+    case ncclUint64: return (const void*)scaleKernel<uint64_t>;
+    case ncclFloat16: return (const void*)scaleKernel<__half>;
+    case ncclFloat32: return (const void*)scaleKernel<float>;
+    case ncclFloat64: return (const void*)scaleKernel<double>;
+    case ncclBfloat16: return (const void*)scaleKernel<__nv_bfloat16>;
+    case ncclFloat8e4m3: return (const void*)scaleKernel<F8E4>;
+    case ncclFloat8e5m2: return (const void*)scaleKernel<F8E5>;
+    default: return nullptr;
+  }
+}
+
+// ------------------------------------------------------------------------- signals
+__global__ void signalKernel(OneSignalArgs a) {
+  if (threadIdx.x == 0) {
+    fenceSys();
+    redReleaseSysAdd64(a.target, 1);
+  }
+}
+
+__global__ void waitSignalKernel(const __grid_constant__ WaitSignalArgs a) {
+  int t = threadIdx.x;
+  if (t < a.nDesc) {
+    WaitCtx w{&a.sync, a.sync.status[a.rank]};
+    const uint64_t want = *a.seen[t] + a.opCnt[t];
+    const uint64_t* c = a.counter[t];
+    bool ok = boundedWait(w, WAIT_SIGNAL, (uint32_t)t, (uint32_t)want, [&] { return ldAcquireSys64(c) >= want; });
+    if (ok) *a.seen[t] = want;
+  }
+}
+
+const void* copyKernelFn() { return (const void*)copyCollKernel; }
+const void* p2pKernelFn() { return (const void*)p2pKernel; }
+const void* signalKernelFn() { return (const void*)signalKernel; }
+const void* waitSignalKernelFn() { return (const void*)waitSignalKernel; }
+
+ncclResult_t launchKernel(const void* fn, dim3 grid, dim3 block, size_t smem, void* argStruct, cudaStream_t stream,
+                          bool cooperative, bool pdl) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[3];
+  int na = 0;
+  if (cooperative) {
+    attrs[na].id = cudaLaunchAttributeCooperative;
+    attrs[na].val.cooperative = 1;
+    ++na;
+  }
+  if (pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  // stores to peers are ordered in the "remote" memory-synchronisation domain so that fences of
+  // this kernel do not wait for unrelated local traffic of concurrent compute kernels
+  attrs[na].id = cudaLaunchAttributeMemSyncDomain;
+  attrs[na].val.memSyncDomain = cudaLaunchMemSyncDomainRemote;
+  ++na;
+  cfg.attrs = attrs;
+  cfg.numAttrs = na;
+  void* args[1] = {argStruct};
+  cudaError_t e = cudaLaunchKernelExC(&cfg, fn, args);
+  if (e != cudaSuccess) {
+    WARN("kernel launch failed: %s", cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    return ncclUnhandledCudaError;
+  }
+  return ncclSuccess;
+}
+
+}  // namespace b200

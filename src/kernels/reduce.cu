@@ -1,0 +1,299 @@
+// Reduction kernels over peer-mapped buffers.
+//   reduceP2pKernel    every rank loads its slice from all ranks, reduces in registers (fp32
+//                      accumulation for 8/16-bit floats, fixed rank order) and stores the result
+//                      locally (reduce-scatter, reduce) or to every rank (two-shot all-reduce).
+//   allReduceLLKernel  one-shot all-reduce for small payloads: every rank pushes flagged 16-byte
+//                      lines {data, flag, data, flag} to all peers and reduces what it receives;
+//                      the flag is the call's epoch, so no barrier is needed.
+//   reduceNvlsKernel   the same three collectives with multimem.ld_reduce (the NVSwitch reduces)
+//                      and multimem.st (the switch replicates).
+// Reference parity: src/device/symmetric/all_reduce.cuh:14-262 (RSxLD_AGxST), :431-504
+// (RSxLDMC_AGxSTMC), :506-584 (AGxLL_R), reduce_scatter.cuh:13-242,396-469.
+#include "common.cuh"
+#include "launch.h"
+
+namespace b200 {
+
+// ------------------------------------------------------------------------- P2P
+template <typename T, int OP>
+__global__ void __launch_bounds__(kCtaThreads, 1) reduceP2pKernel(const __grid_constant__ CollArgs a) {
+  const int rank = ctaRank(a.emu, a.rank);
+  const int n = a.nRanks;
+  CtaBarrier bar;
+  bar.init(a.sync, rank, n, blockIdx.x);
+  bool ok = bar.sync();  // inputs of every rank are final; outputs may be overwritten
+  const size_t begin = a.sliceBegin[rank], cnt = a.sliceCount[rank];
+  if (ok && cnt) {
+    constexpr int N = 16 / sizeof(T);
+    const char* src[kMaxRanks];
+    char* dst[kMaxRanks];
+#pragma unroll
+    for (int p = 0; p < kMaxRanks; ++p) {
+      src[p] = p < n ? (const char*)a.send[p] + begin * sizeof(T) : nullptr;
+      dst[p] = p < n ? (a.dstAll ? (char*)a.recv[p] : (char*)a.lrecv[rank]) + a.dstOff[rank] * sizeof(T) : nullptr;
+    }
+    const int nDst = a.dstAll ? n : 1;
+    if (!a.dstAll) dst[0] = (char*)a.lrecv[rank] + a.dstOff[rank] * sizeof(T);
+    const size_t nPacks = a.vec16 ? cnt / N : 0;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    // two packs per iteration: 2 * nRanks independent 16-byte loads in flight per thread
+    for (; i + stride < nPacks; i += 2 * stride) {
+      uint4 v0[kMaxRanks], v1[kMaxRanks];
+#pragma unroll
+      for (int p = 0; p < kMaxRanks; ++p) {
+        if (p < n) {
+          v0[p] = ldStream16(src[p] + i * 16);
+          v1[p] = ldStream16(src[p] + (i + stride) * 16);
+        }
+      }
+      PackAcc<T, OP> a0, a1;
+      a0.set(v0[0]);
+      a1.set(v1[0]);
+#pragma unroll
+      for (int p = 1; p < kMaxRanks; ++p) {
+        if (p < n) { a0.add(v0[p]); a1.add(v1[p]); }
+      }
+      uint4 r0 = a0.get(a.scaleMode, a.scaleF, a.scaleD, a.intDiv);
+      uint4 r1 = a1.get(a.scaleMode, a.scaleF, a.scaleD, a.intDiv);
+#pragma unroll
+      for (int q = 0; q < kMaxRanks; ++q) {
+        if (q < nDst) { st16(dst[q] + i * 16, r0); st16(dst[q] + (i + stride) * 16, r1); }
+      }
+    }
+    for (; i < nPacks; i += stride) {
+      PackAcc<T, OP> acc;
+      acc.set(ldStream16(src[0] + i * 16));
+#pragma unroll
+      for (int p = 1; p < kMaxRanks; ++p) if (p < n) acc.add(ldStream16(src[p] + i * 16));
+      uint4 r = acc.get(a.scaleMode, a.scaleF, a.scaleD, a.intDiv);
+#pragma unroll
+      for (int q = 0; q < kMaxRanks; ++q) if (q < nDst) st16(dst[q] + i * 16, r);
+    }
+    // ragged tail (and the whole slice when a pointer is not 16-byte aligned): one element at a time
+    for (size_t e = nPacks * N + (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < cnt; e += stride) {
+      typename Elem<T>::Acc acc = Elem<T>::ld(((const T*)src[0])[e]);
+      for (int p = 1; p < n; ++p) acc = redApply<OP>(acc, Elem<T>::ld(((const T*)src[p])[e]));
+      T r = scalarPost<T, OP>(acc, a);
+      for (int q = 0; q < nDst; ++q) ((T*)dst[q])[e] = r;
+    }
+  }
+  bar.sync();  // results have landed everywhere; nobody reads this rank's input any more
+  bar.finish();
+}
+
+// ------------------------------------------------------------------------- LL one-shot
+__device__ __forceinline__ uint64_t load8Partial(const char* p, size_t valid) {
+  if (valid >= 8 && ((uintptr_t)p & 7) == 0) return *(const uint64_t*)p;
+  uint64_t v = 0;
+  for (size_t b = 0; b < 8 && b < valid; ++b) v |= (uint64_t)(uint8_t)p[b] << (8 * b);
+  return v;
+}
+__device__ __forceinline__ void store8Partial(char* p, uint64_t v, size_t valid) {
+  if (valid >= 8 && ((uintptr_t)p & 7) == 0) { *(uint64_t*)p = v; return; }
+  for (size_t b = 0; b < 8 && b < valid; ++b) p[b] = (char)(v >> (8 * b));
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(kCtaThreads, 1) allReduceLLKernel(const __grid_constant__ CollArgs a) {
+  const int rank = ctaRank(a.emu, a.rank);
+  const int n = a.nRanks;
+  constexpr int N = 8 / sizeof(T);
+  uint32_t* ep = a.llEpoch[rank];
+  uint32_t epoch = ep[0] + 1;
+  if (epoch == 0) epoch = 1;
+  const int parity = epoch & 1;
+  WaitCtx w{&a.sync, a.sync.status[rank]};
+  const size_t bytes = a.count * sizeof(T);
+  const size_t nLines = (bytes + 7) / 8;
+  const char* in = (const char*)a.lsend[rank];
+  char* out = (char*)a.lrecv[rank];
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  // region of source `s` inside rank p's LL buffer for this parity
+  auto region = [&](int p, int s) { return (char*)a.ll[p] + ((size_t)(parity * kMaxRanks + s) * kLLLines) * 16; };
+  // phase 1: publish my lines everywhere
+  for (size_t l = (size_t)blockIdx.x * blockDim.x + threadIdx.x; l < nLines; l += stride) {
+    uint64_t d = load8Partial(in + l * 8, bytes - l * 8);
+    uint4 line = make_uint4((uint32_t)d, epoch, (uint32_t)(d >> 32), epoch);
+    for (int p = 0; p < n; ++p)
+      if (p != rank) stVolatile16(region(p, rank) + l * 16, line);
+  }
+  // phase 2: collect every rank's line, reduce in rank order, write the result
+  bool ok = true;
+  for (size_t l = (size_t)blockIdx.x * blockDim.x + threadIdx.x; l < nLines && ok; l += stride) {
+    typename Elem<T>::Acc acc[N];
+    for (int s = 0; s < n; ++s) {
+      uint64_t d;
+      if (s == rank) {
+        d = load8Partial(in + l * 8, bytes - l * 8);
+      } else {
+        const char* slot = region(rank, s) + l * 16;
+        uint4 v = ldVolatile16(slot);
+        if (v.y != epoch || v.w != epoch)
+          ok = boundedWait(w, WAIT_LL, (uint32_t)s, epoch, [&] { v = ldVolatile16(slot); return v.y == epoch && v.w == epoch; });
+        if (!ok) break;
+        d = (uint64_t)v.x | ((uint64_t)v.z << 32);
+      }
+      union { uint64_t u; T e[N]; } cv;
+      cv.u = d;
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        typename Elem<T>::Acc x = Elem<T>::ld(cv.e[k]);
+        acc[k] = s == 0 ? x : redApply<OP>(acc[k], x);
+      }
+    }
+    if (!ok) break;
+    union { uint64_t u; T e[N]; } res;
+#pragma unroll
+    for (int k = 0; k < N; ++k) res.e[k] = scalarPost<T, OP>(acc[k], a);
+    store8Partial(out + l * 8, res.u, bytes - l * 8);
+  }
+  // the last CTA to finish publishes the epoch for the next call
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    uint32_t done = atomicAdd(&ep[1], 1u);
+    if (done == gridDim.x - 1) {
+      ep[1] = 0;
+      ep[0] = epoch;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------- NVLS
+template <typename T, int OP> struct McRed { static constexpr bool kSupported = false; };
+
+#define MC_V4(T, OP, INSTR)                                                                                  \
+  template <> struct McRed<T, OP> {                                                                          \
+    static constexpr bool kSupported = true;                                                                 \
+    static __device__ __forceinline__ uint4 ld(const void* mc) {                                             \
+      uint4 v;                                                                                               \
+      asm volatile("multimem.ld_reduce.relaxed.sys.global." INSTR " {%0,%1,%2,%3}, [%4];"                    \
+                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");                       \
+      return v;                                                                                              \
+    }                                                                                                        \
+  };
+#define MC_S32(T, OP, INSTR)                                                                                 \
+  template <> struct McRed<T, OP> {                                                                          \
+    static constexpr bool kSupported = true;                                                                 \
+    static __device__ __forceinline__ uint4 ld(const void* mc) {                                             \
+      uint4 v;                                                                                               \
+      const char* p = (const char*)mc;                                                                       \
+      asm volatile("multimem.ld_reduce.relaxed.sys.global." INSTR " %0, [%1];" : "=r"(v.x) : "l"(p) : "memory");      \
+      asm volatile("multimem.ld_reduce.relaxed.sys.global." INSTR " %0, [%1];" : "=r"(v.y) : "l"(p + 4) : "memory");  \
+      asm volatile("multimem.ld_reduce.relaxed.sys.global." INSTR " %0, [%1];" : "=r"(v.z) : "l"(p + 8) : "memory");  \
+      asm volatile("multimem.ld_reduce.relaxed.sys.global." INSTR " %0, [%1];" : "=r"(v.w) : "l"(p + 12) : "memory"); \
+      return v;                                                                                              \
+    }                                                                                                        \
+  };
+#define MC_S64(T, OP, INSTR, CONSTRAINT)                                                                     \
+  template <> struct McRed<T, OP> {                                                                          \
+    static constexpr bool kSupported = true;                                                                 \
+    static __device__ __forceinline__ uint4 ld(const void* mc) {                                             \
+      union { uint4 v; unsigned long long q[2]; double d[2]; } u;                                            \
+      const char* p = (const char*)mc;                                                                       \
+      asm volatile("multimem.ld_reduce.relaxed.sys.global." INSTR " %0, [%1];" : CONSTRAINT(u.q[0]) : "l"(p) : "memory");     \
+      asm volatile("multimem.ld_reduce.relaxed.sys.global." INSTR " %0, [%1];" : CONSTRAINT(u.q[1]) : "l"(p + 8) : "memory"); \
+      return u.v;                                                                                            \
+    }                                                                                                        \
+  };
+MC_V4(float, RED_SUM, "add.v4.f32")
+MC_V4(__half, RED_SUM, "add.acc::f32.v4.f16x2")
+MC_V4(__half, RED_MAX, "max.v4.f16x2")
+MC_V4(__half, RED_MIN, "min.v4.f16x2")
+MC_V4(__nv_bfloat16, RED_SUM, "add.acc::f32.v4.bf16x2")
+MC_V4(__nv_bfloat16, RED_MAX, "max.v4.bf16x2")
+MC_V4(__nv_bfloat16, RED_MIN, "min.v4.bf16x2")
+MC_V4(F8E4, RED_SUM, "add.acc::f16.v4.e4m3x4")
+MC_V4(F8E5, RED_SUM, "add.acc::f16.v4.e5m2x4")
+MC_S32(int32_t, RED_SUM, "add.s32")
+MC_S32(int32_t, RED_MAX, "max.s32")
+MC_S32(int32_t, RED_MIN, "min.s32")
+MC_S32(uint32_t, RED_SUM, "add.u32")
+MC_S32(uint32_t, RED_MAX, "max.u32")
+MC_S32(uint32_t, RED_MIN, "min.u32")
+MC_S64(int64_t, RED_SUM, "add.u64", "=l")
+MC_S64(int64_t, RED_MAX, "max.s64", "=l")
+MC_S64(int64_t, RED_MIN, "min.s64", "=l")
+MC_S64(uint64_t, RED_SUM, "add.u64", "=l")
+MC_S64(uint64_t, RED_MAX, "max.u64", "=l")
+MC_S64(uint64_t, RED_MIN, "min.u64", "=l")
+MC_S64(double, RED_SUM, "add.f64", "=l")
+
+// Slices, offsets and counts must be multiples of 16 bytes (the host falls back to P2P otherwise).
+template <typename T, int OP>
+__global__ void __launch_bounds__(kCtaThreads, 1) reduceNvlsKernel(const __grid_constant__ CollArgs a) {
+  const int rank = a.rank;
+  CtaBarrier bar;
+  bar.init(a.sync, rank, a.nRanks, blockIdx.x);
+  bool ok = bar.sync();
+  if constexpr (McRed<T, OP>::kSupported) {
+    const size_t cnt = a.sliceCount[rank];
+    if (ok && cnt) {
+      constexpr int N = 16 / sizeof(T);
+      const char* src = (const char*)a.sendMc + a.sliceBegin[rank] * sizeof(T);
+      char* dst = (a.dstAll ? (char*)a.recvMc : (char*)a.lrecv[rank]) + a.dstOff[rank] * sizeof(T);
+      const size_t nPacks = cnt / N;
+      const size_t stride = (size_t)gridDim.x * blockDim.x;
+      const bool scale = a.scaleMode != SCALE_NONE;
+      size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+      for (; i + 3 * stride < nPacks; i += 4 * stride) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = McRed<T, OP>::ld(src + (i + u * stride) * 16);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (scale) { PackAcc<T, OP> acc; acc.set(v[u]); v[u] = acc.get(a.scaleMode, a.scaleF, a.scaleD, a.intDiv); }
+          if (a.dstAll) mcSt16(dst + (i + u * stride) * 16, v[u]); else st16(dst + (i + u * stride) * 16, v[u]);
+        }
+      }
+      for (; i < nPacks; i += stride) {
+        uint4 v = McRed<T, OP>::ld(src + i * 16);
+        if (scale) { PackAcc<T, OP> acc; acc.set(v); v = acc.get(a.scaleMode, a.scaleF, a.scaleD, a.intDiv); }
+        if (a.dstAll) mcSt16(dst + i * 16, v); else st16(dst + i * 16, v);
+      }
+    }
+  }
+  bar.sync();
+  bar.finish();
+}
+
+// ------------------------------------------------------------------------- dispatch
+template <template <typename, int> class K> struct KernelOf;
+
+template <typename T, int OP> static const void* p2pFn() { return (const void*)reduceP2pKernel<T, OP>; }
+template <typename T, int OP> static const void* llFn() { return (const void*)allReduceLLKernel<T, OP>; }
+template <typename T, int OP> static const void* nvlsFn() {
+  if constexpr (McRed<T, OP>::kSupported) return (const void*)reduceNvlsKernel<T, OP>;
+  else return nullptr;
+}
+
+#define BY_OP(FN, T, op)                                   \
+  ((op) == RED_SUM ? FN<T, RED_SUM>() : (op) == RED_PROD ? FN<T, RED_PROD>() : (op) == RED_MAX ? FN<T, RED_MAX>() : FN<T, RED_MIN>())
+#define BY_TYPE(FN, type, op)                                               \
+  switch (type) {                                                           \
+    case ncclInt8: return BY_OP(FN, int8_t, op);                            \
+    case ncclUint8: return BY_OP(FN, uint8_t, op);                          \
+    case ncclInt32: return BY_OP(FN, int32_t, op);                          \
+    case ncclUint32: return BY_OP(FN, uint32_t, op);                        \
+    case ncclInt64: return BY_OP(FN, int64_t, op);                          \
+    case ncclUint64: return BY_OP(FN, uint64_t, op);                        \
+    case ncclFloat16: return BY_OP(FN, __half, op);                         \
+    case ncclFloat32: return BY_OP(FN, float, op);                          \
+    case ncclFloat64: return BY_OP(FN, double, op);                         \
+    case ncclBfloat16: return BY_OP(FN, __nv_bfloat16, op);                 \
+    case ncclFloat8e4m3: return BY_OP(FN, F8E4, op);                        \
+    case ncclFloat8e5m2: return BY_OP(FN, F8E5, op);                        \
+    default: return nullptr;                                                \
+  }
+
+const void* reduceKernelFn(int algo, ncclDataType_t type, int op) {
+  if (algo == KERNEL_REDUCE_P2P) { BY_TYPE(p2pFn, type, op) }
+  if (algo == KERNEL_ALLREDUCE_LL) { BY_TYPE(llFn, type, op) }
+  if (algo == KERNEL_REDUCE_NVLS) { BY_TYPE(nvlsFn, type, op) }
+  return nullptr;
+}
+
+bool nvlsReduceSupported(ncclDataType_t type, int op) { return reduceKernelFn(KERNEL_REDUCE_NVLS, type, op) != nullptr; }
+
+}  // namespace b200

@@ -1,0 +1,76 @@
+// Symmetric-memory runtime: registered windows whose memory every rank of the load/store domain
+// can address (peer mappings) and, when the fabric supports it, a multicast alias that reaches
+// all ranks with one multimem instruction.
+// Reference parity: src/dev_runtime.cc (symMemoryObtain :545-656, symMemoryMapLsaTeam :294-340,
+// multicast team :342-479, symWindowCreate :712-789), src/register/register.cc.
+#pragma once
+#include "../comm/comm.h"
+#include "../core/ipcsocket.h"
+#include "../kernels/args.h"
+#include "allocator.h"
+
+// Device-visible description of a window (also what ncclWindow_t points to on the host).
+struct ncclWindow_vidmem {
+  void* peerPtr[b200::kMaxRanks];   // peerPtr[p]: start of rank p's part of the window, mapped here
+  void* mcPtr;                      // multicast alias of the window, or null
+  size_t size;
+  int rank, nRanks;
+  void* userPtr;
+  struct ncclWindow_vidmem* devSelf;   // address of the device copy
+  void* hostState;                     // b200::SymWindow*
+  unsigned long long magic;
+};
+
+namespace b200 {
+
+constexpr unsigned long long kWindowMagic = 0x57494e42323030ull;
+
+enum SegKind : int { SEG_NONE = 0, SEG_VMM = 1, SEG_IPC = 2 };
+
+struct SymSegment {
+  int kind = SEG_NONE;
+  uintptr_t base = 0;
+  size_t size = 0;
+  CUmemGenericAllocationHandle ownHandle = 0;
+  bool ownHandleRetained = false;
+  uintptr_t peerBaseId[kMaxRanks] = {};         // peers' own base addresses (cache key)
+  void* peerBase[kMaxRanks] = {};               // local mapping of peer p's allocation
+  size_t peerSize[kMaxRanks] = {};
+  CUmemGenericAllocationHandle peerHandle[kMaxRanks] = {};
+  bool peerIpcOpened[kMaxRanks] = {};
+  void* mcBase = nullptr;
+  size_t mcSize = 0;
+  CUmemGenericAllocationHandle mcHandle = 0;
+  bool mcBound = false;
+  int refs = 0;
+};
+
+struct SymWindow {
+  ncclWindow_vidmem host;          // host mirror (host.devSelf = device copy)
+  SymSegment* seg = nullptr;
+  size_t offset = 0;               // offset of the window inside my allocation
+  int flags = 0;
+  bool symmetric = false;          // peers are mapped; false = local-only registration
+};
+
+struct SymRuntime {
+  ncclComm* comm = nullptr;
+  IpcSocket ipc;
+  bool mcUsable = false;           // every rank supports multicast
+  bool vmmUsable = false;
+  int regSeq = 0;
+  std::vector<SymSegment*> segments;
+  std::vector<SymWindow*> windows;
+  std::vector<std::pair<IpcMsg, int>> stash;   // early datagrams of a later stage
+  std::mutex lock;
+};
+
+ncclResult_t symInit(ncclComm* comm);
+void symDestroy(ncclComm* comm);
+// Collective over the communicator.
+ncclResult_t symWindowRegister(ncclComm* comm, void* buff, size_t size, SymWindow** out, int flags);
+ncclResult_t symWindowDeregister(ncclComm* comm, SymWindow* win);
+// Window of `comm` that contains [ptr, ptr+bytes), or null.
+SymWindow* symFindWindow(ncclComm* comm, const void* ptr, size_t bytes);
+
+}  // namespace b200

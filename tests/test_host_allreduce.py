@@ -1,0 +1,90 @@
+"""Host-memory communicators: TCP bootstrap + ring reduce-scatter/all-gather executed on the CPU."""
+import numpy as np
+import pytest
+
+from mp_util import run_ranks
+
+
+def _allreduce_rank(rank, nranks, uid, count):
+    import numpy as np
+    from nccl_b200 import Communicator
+    comm = Communicator(nranks, rank, uid)
+    rng = np.random.default_rng(1000 + rank)
+    x = rng.standard_normal(count).astype(np.float32)
+    y = np.empty_like(x)
+    comm.all_reduce(x, y, op="sum")
+    comm.destroy()
+    return y
+
+
+def test_allreduce_sum_two_ranks_1mi_fp32():
+    # 2 processes, 1,048,576 fp32 values from N(0,1) with seed 1000+rank, exact check against the host sum
+    count = 1 << 20
+    res = run_ranks(_allreduce_rank, 2, args=(count,))
+    a = np.random.default_rng(1000).standard_normal(count).astype(np.float32)
+    b = np.random.default_rng(1001).standard_normal(count).astype(np.float32)
+    expect = a + b
+    assert np.array_equal(res[0], expect)
+    assert np.array_equal(res[1], expect)
+
+
+def _all_colls_rank(rank, nranks, uid):
+    import numpy as np
+    from nccl_b200 import Communicator, group
+    comm = Communicator(nranks, rank, uid)
+    n = nranks
+    out = {}
+    x = (np.arange(1000, dtype=np.float64) + rank)
+    y = np.empty_like(x)
+    comm.all_reduce(x, y, op="max")
+    out["ar_max"] = y.copy()
+    comm.all_reduce(x, y, op="avg")
+    out["ar_avg"] = y.copy()
+    g = np.empty(n * 10, dtype=np.int32)
+    comm.all_gather(np.full(10, rank, dtype=np.int32), g)
+    out["ag"] = g
+    rs = np.empty(7, dtype=np.int64)
+    comm.reduce_scatter(np.arange(7 * n, dtype=np.int64) * (rank + 1), rs)
+    out["rs"] = rs
+    b = np.arange(33, dtype=np.float32) if rank == 1 else np.zeros(33, dtype=np.float32)
+    comm.broadcast(b, b, root=1)
+    out["bc"] = b
+    r = np.zeros(5, dtype=np.float32)
+    comm.reduce(np.full(5, rank + 1, dtype=np.float32), r, root=0, op="prod")
+    out["red"] = r
+    a2a = np.empty(n * 3, dtype=np.int32)
+    comm.all_to_all(np.repeat(np.arange(n, dtype=np.int32) + 100 * rank, 3), a2a)
+    out["a2a"] = a2a
+    # ring send/recv in a group
+    nxt, prv = (rank + 1) % n, (rank - 1) % n
+    rb = np.empty(4, dtype=np.float32)
+    with group():
+        comm.send(np.full(4, rank, dtype=np.float32), nxt)
+        comm.recv(rb, prv)
+    out["ring"] = rb
+    half = np.full(6, np.float16(1.5) * (rank + 1), dtype=np.float16)
+    hout = np.empty_like(half)
+    comm.all_reduce(half, hout)
+    out["half"] = hout
+    comm.destroy()
+    return out
+
+
+@pytest.mark.parametrize("nranks", [2, 3, 4])
+def test_every_collective_on_host(nranks):
+    res = run_ranks(_all_colls_rank, nranks)
+    n = nranks
+    base = np.arange(1000, dtype=np.float64)
+    for r in range(n):
+        o = res[r]
+        assert np.array_equal(o["ar_max"], base + n - 1)
+        assert np.allclose(o["ar_avg"], base + (n - 1) / 2)
+        assert np.array_equal(o["ag"], np.repeat(np.arange(n, dtype=np.int32), 10))
+        tot = sum(range(1, n + 1))
+        assert np.array_equal(o["rs"], np.arange(7 * n, dtype=np.int64)[7 * r:7 * r + 7] * tot)
+        assert np.array_equal(o["bc"], np.arange(33, dtype=np.float32))
+        if r == 0:
+            assert np.array_equal(o["red"], np.full(5, float(np.prod(np.arange(1, n + 1))), dtype=np.float32))
+        assert np.array_equal(o["a2a"], np.repeat(np.arange(n, dtype=np.int32) * 100 + r, 3))
+        assert np.array_equal(o["ring"], np.full(4, (r - 1) % n, dtype=np.float32))
+        assert np.array_equal(o["half"], np.full(6, 1.5 * tot, dtype=np.float16))
