@@ -42,7 +42,7 @@ $(BUILD)/%.cu.o: %.cu $(wildcard include/*.h include/nccl_device/*.h src/*/*.h s
 
 $(LIB): $(HOST_OBJS) $(CU_OBJS)
 	@mkdir -p $(LIBDIR)
-	$(NVCC) -shared $(GENCODE) -o $@ $^ -cudart static -Xcompiler -pthread -ldl -lrt $(if $(SAN),-Xcompiler $(LDSAN))
+	$(NVCC) -shared $(GENCODE) -o $@ $^ -cudart static -Xcompiler -pthread -Xlinker -Bsymbolic -ldl -lrt $(if $(SAN),-Xcompiler $(LDSAN))
 
 $(BINDIR)/%: tools/%.cc $(LIB)
 	@mkdir -p $(BINDIR)

@@ -1,0 +1,214 @@
+#!/usr/bin/env python
+"""Headline benchmark: bus bandwidth of a large all-reduce, plus a short sweep of the other collectives.
+
+    python bench.py --gpus N --steps K --warmup W [--impl ours|reference]
+
+A step is one ncclAllReduce(sum, bf16) of 1 GiB per rank on registered (symmetric) buffers, the
+large-message end of the collective sweep; inputs are synthetic uniform[-1,1] values (seed 7+rank).
+N > 1 is launched with one process per GPU (torchrun); rank 0 prints one JSON line.
+
+  value       nccl-tests bus bandwidth, GB/s: bytes/time * 2(n-1)/n. With one GPU that factor is
+              zero, so the n=1 line reports the algorithm bandwidth of the one-rank path instead.
+  e2e         the same step through nccl_b200.Communicator.all_reduce including, every step, the
+              host->device copy of the input from pinned memory and the device->host copy of the result.
+  sweep       bus bandwidth of all-reduce / all-gather / reduce-scatter / all-to-all at a few sizes.
+
+--impl reference runs the same driver against the library built from the reference sources
+(baseline/_ref/build/lib/libnccl.so.2) through its public C API.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+REF_LIB = os.path.join(ROOT, "baseline", "_ref", "build", "lib", "libnccl.so.2")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.lines = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--bytes", type=int, default=1 << 30)
+    ap.add_argument("--no-sweep", action="store_true")
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3)
+
+    if a.impl == "reference" and not os.path.exists(REF_LIB):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/build/lib/libnccl.so.2 is missing (reference was not built in this checkout)"}))
+        return 0
+
+    import torch
+    from nccl_b200 import _lib
+    from nccl_b200.core import BF16
+    from nccl_b200.utils import perf
+
+    d = perf.Dist()
+    n = d.world
+    if n != a.gpus and d.rank == 0:
+        print("warning: --gpus %d but WORLD_SIZE %d" % (a.gpus, n), file=sys.stderr)
+    torch.cuda.set_device(d.local_rank)
+    lib = _lib.load(REF_LIB) if a.impl == "reference" else _lib.load()
+    nbytes = a.bytes
+    h = perf.Harness(d, lib, max_bytes=nbytes, symmetric=True)
+    h.fill(BF16)
+
+    # ---------------- device-timed headline: K all-reduces back to back
+    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else
+                           os.environ["CUDA_VISIBLE_DEVICES"].split(",")[torch.cuda.current_device()])
+    launches0 = 0
+    count_launches = a.impl == "ours" and hasattr(lib, "b200CommLaunchCount")
+    if count_launches:
+        lib.b200CommLaunchCount.restype = ctypes.c_ulonglong
+        lib.b200CommLaunchCount.argtypes = [ctypes.c_void_p]
+    sp = h.stream.cuda_stream
+    with torch.cuda.stream(h.stream):
+        for _ in range(a.warmup):
+            _lib.check(h.call("all_reduce", nbytes, BF16, sp), "ncclAllReduce", lib)
+    d.barrier()
+    torch.cuda.synchronize()
+    if count_launches:
+        launches0 = lib.b200CommLaunchCount(h.comm)
+    if d.rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(h.stream):
+        e0.record(h.stream)
+        for _ in range(a.steps):
+            _lib.check(h.call("all_reduce", nbytes, BF16, sp), "ncclAllReduce", lib)
+        e1.record(h.stream)
+    torch.cuda.synchronize()
+    d.barrier()
+    clocks = sampler.stop() if d.rank == 0 else None
+    ms = d.max(e0.elapsed_time(e1) / a.steps)
+    launches = (lib.b200CommLaunchCount(h.comm) - launches0) if count_launches else None
+    factor = perf.bus_factor("all_reduce", n)
+    value = nbytes / (ms * 1e-3) / 1e9 * factor
+
+    # ---------------- end to end: pinned host -> device, all-reduce through the public API, device -> host
+    e2e = None
+    try:
+        host_in = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+        host_out = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+        host_in.view(torch.bfloat16).copy_(h.send_t.view(torch.bfloat16).cpu())
+        if a.impl == "ours":
+            from nccl_b200.core import Communicator
+            api = Communicator(n, d.rank, None, lib=lib, _handle=h.comm)
+            send_bf, recv_bf = h.send_t.view(torch.bfloat16), h.recv_t.view(torch.bfloat16)
+
+            def step():
+                h.send_t.copy_(host_in, non_blocking=True)
+                api.all_reduce(send_bf, recv_bf, op="sum", stream=h.stream)
+                host_out.copy_(h.recv_t, non_blocking=True)
+        else:
+            def step():
+                h.send_t.copy_(host_in, non_blocking=True)
+                _lib.check(h.call("all_reduce", nbytes, BF16, sp), "ncclAllReduce", lib)
+                host_out.copy_(h.recv_t, non_blocking=True)
+        k2 = max(3, min(a.steps, 10))
+        with torch.cuda.stream(h.stream):
+            for _ in range(3):
+                step()
+        torch.cuda.synchronize()
+        d.barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(h.stream):
+            f0.record(h.stream)
+            for _ in range(k2):
+                step()
+            f1.record(h.stream)
+        torch.cuda.synchronize()
+        ms2 = d.max(f0.elapsed_time(f1) / k2)
+        e2e = {"value": round(nbytes / (ms2 * 1e-3) / 1e9 * factor, 3), "unit": "GB/s", "ms_per_step": round(ms2, 4), "steps": k2,
+               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
+    except Exception as ex:  # noqa: BLE001
+        e2e = {"error": str(ex)[:200]}
+
+    # ---------------- short sweep (bus bandwidth at a few sizes, registered buffers)
+    sweep = None
+    if not a.no_sweep and n > 1:
+        sweep = {}
+        sizes = [s for s in (8, 1 << 10, 32 << 10, 1 << 20, 16 << 20, 256 << 20) if s <= nbytes]
+        for coll in ("all_reduce", "all_gather", "reduce_scatter", "all_to_all"):
+            try:
+                rows = perf.sweep(h, coll, BF16, sizes, warmup=5, iters=20)
+                sweep[coll] = {str(r["bytes"]): [r["time_us"], r["busbw_GBps"]] for r in rows}
+            except Exception as ex:  # noqa: BLE001
+                sweep[coll] = {"error": str(ex)[:200]}
+    h.close()
+    if d.rank == 0:
+        out = {
+            "metric": "allreduce_busbw_GBps", "value": round(value, 3), "unit": "GB/s", "n_gpus": n, "steps": a.steps, "warmup": a.warmup,
+            "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic uniform[-1,1], seed 7+rank", "impl": a.impl,
+            "config": {"model": "collective sweep, large-message point", "collective": "AllReduce", "op": "sum",
+                       "bytes_per_rank": nbytes, "global_batch": n, "seq_len": nbytes // 2, "parallelism": "dp%d" % n,
+                       "buffers": "ncclMemAlloc + ncclCommWindowRegister(NCCL_WIN_COLL_SYMMETRIC)",
+                       "l2": "1 GiB per rank per step: inputs larger than the 126 MB L2, no flush needed",
+                       "busbw": "algBW*2(n-1)/n" if n > 1 else "n=1: algBW of the one-rank copy path (the bus factor is 0)"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "sweep_time_us_busbw": sweep,
+        }
+        print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -302,7 +302,7 @@ static ncclResult_t scaleCopy(ncclComm* comm, ncclDataType_t type, const void* s
   return launchKernel(scaleKernelFn(type), dim3(std::max(ctas, 1)), dim3(256), 0, &sa, stream, false);
 }
 
-static void sliceEven(size_t count, size_t es, int n, size_t* begin, size_t* cnt) {
+void sliceEven(size_t count, size_t es, int n, size_t* begin, size_t* cnt) {
   const size_t unit = 16 / es;  // elements per 16 bytes
   size_t per = (count + n - 1) / n;
   per = (per + unit - 1) / unit * unit;
@@ -554,7 +554,13 @@ static ncclResult_t runOneRank(ncclComm* comm, const Task& t) {
     NCCLCHECK(lowerOp(comm, t, &op));
     return scaleCopy(comm, t.type, src, dst, t.count, op, t.stream);
   }
-  if (src != dst) CUDACHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, t.stream));
+  if (src != dst) {
+    ScaleArgs ca{src, dst, bytes, 0, nullptr};
+    size_t perCta = 256 * 4 * 16;
+    int ctas = (int)std::min<size_t>((bytes + perCta - 1) / perCta, (size_t)comm->devPlane->smCount * 16);
+    comm->devPlane->launches++;
+    NCCLCHECK(launchKernel(localCopyKernelFn(), dim3(std::max(ctas, 1)), dim3(256), 0, &ca, t.stream, false));
+  }
   return ncclSuccess;
 }
 

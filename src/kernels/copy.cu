@@ -267,6 +267,32 @@ const void* scaleKernelFn(ncclDataType_t type) {
   }
 }
 
+// Local copy of `count` bytes: the data movement of a single-rank communicator (out-of-place
+// collectives reduce to dst = src) and of staged transfers. Four independent 16-byte loads per
+// thread per iteration keep enough bytes in flight to run at HBM copy speed.
+__global__ void __launch_bounds__(256) localCopyKernel(ScaleArgs a) {
+  const char* src = (const char*)a.src;
+  char* dst = (char*)a.dst;
+  const size_t bytes = a.count;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if ((((uintptr_t)src | (uintptr_t)dst) & 15) == 0) {
+    const size_t packs = bytes / 16;
+    for (; i + 3 * stride < packs; i += 4 * stride) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = ldStream16(src + (i + u * stride) * 16);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) st16(dst + (i + u * stride) * 16, v[u]);
+    }
+    for (; i < packs; i += stride) st16(dst + i * 16, ldStream16(src + i * 16));
+    for (size_t j = packs * 16 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; j < bytes; j += stride) dst[j] = src[j];
+  } else {
+    for (; i < bytes; i += stride) dst[i] = src[i];
+  }
+}
+const void* localCopyKernelFn() { return (const void*)localCopyKernel; }
+
 // ------------------------------------------------------------------------- signals
 __global__ void signalKernel(OneSignalArgs a) {
   if (threadIdx.x == 0) {

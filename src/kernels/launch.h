@@ -29,6 +29,7 @@ const void* treeKernelFn(ncclDataType_t type, int op);
 const void* copyKernelFn();
 const void* p2pKernelFn();
 const void* scaleKernelFn(ncclDataType_t type);
+const void* localCopyKernelFn();   // takes ScaleArgs{src, dst, count = bytes}
 const void* signalKernelFn();
 const void* waitSignalKernelFn();
 
