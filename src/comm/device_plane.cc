@@ -21,6 +21,9 @@ B200_PARAM(MinCtas, "MIN_CTAS", 0, "Lower bound on CTAs per collective kernel")
 B200_PARAM(LLThreshold, "B200_LL_THRESHOLD", -1, "All-reduce payloads up to this many bytes use the one-shot flagged-line kernel")
 B200_PARAM(NvlsThreshold, "B200_NVLS_THRESHOLD", -1, "All-reduce payloads from this many bytes use multimem")
 B200_PARAM(P2pDisable, "P2P_DISABLE", 0, "Never map peer memory; GPU buffers are staged through host sockets")
+B200_PARAM(CopyThreads, "B200_COPY_THREADS", 512, "Threads per CTA of the local copy kernel")
+B200_PARAM(CopyUnroll, "B200_COPY_UNROLL", 4, "16-byte loads in flight per thread of the local copy kernel (4 or 8)")
+B200_PARAM(CopyCtasPerSm, "B200_COPY_CTAS_PER_SM", 16, "Grid size of the local copy kernel in CTAs per SM")
 B200_PARAM(LaunchPdl, "B200_PDL", 0, "Launch collectives with programmatic stream serialisation")
 
 // ------------------------------------------------------------------------------------ tuning
@@ -30,6 +33,8 @@ void tuningDefaults(TuningTable* t) {
     t->arNvlsMin[n] = 64 << 10;
     t->agMcMin[n] = 64 << 10;
     t->rsNvlsMin[n] = 64 << 10;
+    t->rsLLMax[n] = 16 << 10;
+    t->llCopyMax[n] = 16 << 10;
   }
   t->ceMin = 0;
   t->nvlsCtas = 32;
@@ -48,6 +53,11 @@ ncclResult_t tuningLoadFile(TuningTable* t, const char* path) {
   size_t r;
   while ((r = fread(buf, 1, sizeof(buf), f)) > 0) s.append(buf, r);
   fclose(f);
+  if (s.find("\"all_reduce\"") != std::string::npos || s.find("\"all_gather\"") != std::string::npos) {
+    if (!tuneParse(t, s)) { WARN("tuning file %s: malformed selection table", path); return ncclInvalidArgument; }
+    INFO(SUB_TUNING, "selection table loaded from %s", path);
+    return ncclSuccess;
+  }
   auto scalar = [&](const char* key, long long* out) {
     size_t p = s.find(std::string("\"") + key + "\"");
     if (p == std::string::npos) return false;
@@ -73,6 +83,8 @@ ncclResult_t tuningLoadFile(TuningTable* t, const char* path) {
   table("arNvlsMin", t->arNvlsMin);
   table("agMcMin", t->agMcMin);
   table("rsNvlsMin", t->rsNvlsMin);
+  table("rsLLMax", t->rsLLMax);
+  table("llCopyMax", t->llCopyMax);
   long long v;
   if (scalar("ceMin", &v)) t->ceMin = (size_t)v;
   if (scalar("nvlsCtas", &v)) t->nvlsCtas = (int)v;
@@ -89,6 +101,7 @@ ncclResult_t devPlaneCreate(ncclComm* comm) {
   DevicePlane* dp = new DevicePlane;
   comm->devPlane = dp;
   tuningDefaults(&dp->tune);
+  tuneLoadDefaults(&dp->tune);
   const char* tf = getEnv("NCCL_TUNING_FILE");
   if (tf && *tf) tuningLoadFile(&dp->tune, tf);
   cudaDeviceProp prop;
@@ -96,13 +109,13 @@ ncclResult_t devPlaneCreate(ncclComm* comm) {
   dp->smCount = prop.multiProcessorCount;
   dp->timeoutNs = (uint64_t)paramWaitTimeoutMs() * 1000000ull;
   CUDACHECK(cudaEventCreateWithFlags(&dp->lastEvent, cudaEventDisableTiming));
-  const size_t privWords = kBarrierSlots + 4 + (2 * kMaxRanks + 4) + 2 * kMaxRanks * kSignalsPerPeer;
+  const size_t privWords = kPrivWords + 2 * kMaxRanks * kSignalsPerPeer;
   CUDACHECK(cudaMalloc(&dp->priv, privWords * sizeof(uint32_t)));
   CUDACHECK(cudaMemset(dp->priv, 0, privWords * sizeof(uint32_t)));
   dp->epochs = dp->priv;
   dp->llEpoch = dp->priv + kBarrierSlots;
   dp->p2pSeq = dp->llEpoch + 4;
-  dp->sigSeen = (uint64_t*)(dp->p2pSeq + 2 * kMaxRanks + 4);
+  dp->sigSeen = (uint64_t*)(dp->priv + kPrivWords);
   if (comm->nRanks == 1) return ncclSuccess;
 
   int usable = comm->lsaAll ? 1 : 0;
@@ -256,13 +269,16 @@ static bool aligned16(const Aliases& al, int n) {
   return true;
 }
 
+static thread_local int tPickCtas = 0;   // CTA count of the measured row that chose this launch (0 = none)
+
 static int clampCtas(ncclComm* comm, size_t bytes, int cap) {
   DevicePlane* dp = comm->devPlane;
+  if (tPickCtas > 0) cap = tPickCtas;
   int64_t envMax = paramMaxCtas(), envMin = paramMinCtas();
   if (comm->config.maxCTAs != NCCL_CONFIG_UNDEF_INT && comm->config.maxCTAs > 0) cap = std::min(cap, comm->config.maxCTAs);
   if (envMax > 0) cap = (int)std::min<int64_t>(cap, envMax);
   cap = std::min(cap, std::min(kMaxCtas, dp->smCount));
-  int want = (int)std::min<size_t>((bytes + dp->tune.bytesPerCta - 1) / dp->tune.bytesPerCta, (size_t)cap);
+  int want = tPickCtas > 0 ? cap : (int)std::min<size_t>((bytes + dp->tune.bytesPerCta - 1) / dp->tune.bytesPerCta, (size_t)cap);
   int lo = 1;
   if (comm->config.minCTAs != NCCL_CONFIG_UNDEF_INT && comm->config.minCTAs > 0) lo = comm->config.minCTAs;
   if (envMin > 0) lo = (int)envMin;
@@ -314,8 +330,12 @@ void sliceEven(size_t count, size_t es, int n, size_t* begin, size_t* cnt) {
 }
 
 // ------------------------------------------------------------------------------------ collectives
+static thread_local int tForceAlgo = ALGO_AUTO, tForceMode = -1;
+void devPlaneForce(int algo, int mode) { tForceAlgo = algo; tForceMode = mode; }
+
 static int forcedAlgo() {
-  const char* e = getEnv("NCCL_ALGO");
+  if (tForceAlgo != ALGO_AUTO) return tForceAlgo;
+  static const char* e = getEnv("NCCL_ALGO");
   if (!e || !*e) return ALGO_AUTO;
   if (!strcasecmp(e, "NVLS")) return ALGO_NVLS;
   if (!strcasecmp(e, "P2P") || !strcasecmp(e, "TwoShot") || !strcasecmp(e, "Direct")) return ALGO_P2P;
@@ -339,24 +359,34 @@ static ncclResult_t runReduction(ncclComm* comm, const Task& t) {
   const size_t total = t.func == FUNC_REDUCESCATTER ? t.count * n : t.count;
   const size_t bytes = total * es;
   if (total == 0) return ncclSuccess;
-  const int forced = forcedAlgo();
+  int forced = forcedAlgo();
+  tPickCtas = 0;
+  if (forced == ALGO_AUTO && paramLLThreshold() < 0 && paramNvlsThreshold() < 0) {
+    TunePick pk = tunePick(dp->tune, t.func, n, bytes);
+    if (pk.valid) { forced = pk.algo; tPickCtas = pk.ctas; }
+  }
 
-  if ((forced == ALGO_RING || forced == ALGO_TREE) && !op.premul) return ringTreeRun(comm, t, forced);
+  if ((forced == ALGO_RING || forced == ALGO_TREE) && !op.premul && t.func != FUNC_REDUCE) return ringTreeRun(comm, t, forced);
 
-  // ---- small all-reduce: flagged lines, no registration needed
-  int64_t llEnv = paramLLThreshold();
-  size_t llMax = llEnv >= 0 ? (size_t)llEnv : dp->tune.arLLMax[n];
-  llMax = std::min(llMax, kLLDataBytes);
-  if (t.func == FUNC_ALLREDUCE && !op.premul && (forced == ALGO_LL_ONESHOT ? bytes <= kLLDataBytes : (forced == ALGO_AUTO && bytes <= llMax))) {
-    CollArgs a;
-    baseArgs(comm, &a, t.func);
-    a.count = t.count;
-    a.lsend[me] = t.send;
-    a.lrecv[me] = t.recv;
-    a.scaleMode = op.scaleMode; a.scaleF = op.scaleF; a.scaleD = op.scaleD; a.intDiv = op.intDiv;
-    size_t lines = (bytes + 7) / 8;
-    int ctas = (int)std::min<size_t>((lines + kCtaThreads - 1) / kCtaThreads, 64);
-    return launchColl(comm, reduceKernelFn(KERNEL_ALLREDUCE_LL, t.type, op.red), &a, std::max(ctas, 1), t.stream);
+  // ---- small payloads: flagged lines, one NVLink crossing, no registration needed
+  {
+    int64_t llEnv = paramLLThreshold();
+    const size_t recvBytes = t.count * es;   // what one receiver ends up with
+    size_t llMax = llEnv >= 0 ? (size_t)llEnv : (t.func == FUNC_ALLREDUCE ? dp->tune.arLLMax[n] : dp->tune.rsLLMax[n]);
+    llMax = std::min(llMax, kLLDataBytes);
+    const bool llFits = recvBytes <= kLLDataBytes - 8;   // the last line of a region carries acknowledgements
+    if (!op.premul && llFits && (forced == ALGO_LL_ONESHOT || (forced == ALGO_AUTO && recvBytes <= llMax))) {
+      CollArgs a;
+      baseArgs(comm, &a, t.func);
+      a.count = t.count;
+      a.root = t.root;
+      a.lsend[me] = t.send;
+      a.lrecv[me] = t.recv;
+      a.scaleMode = op.scaleMode; a.scaleF = op.scaleF; a.scaleD = op.scaleD; a.intDiv = op.intDiv;
+      size_t lines = (recvBytes + 7) / 8;
+      int ctas = (int)std::min<size_t>((lines + kCtaThreads - 1) / kCtaThreads, 64);
+      return launchColl(comm, llReduceKernelFn(t.type, op.red), &a, std::max(ctas, 1), t.stream);
+    }
   }
 
   // ---- large: every rank reduces one slice, inputs must be peer-visible
@@ -454,12 +484,33 @@ static ncclResult_t runCopyColl(ncclComm* comm, const Task& t) {
   const size_t es = typeSize(t.type);
   const size_t B = t.count * es;   // bytes per segment
   if (B == 0) return ncclSuccess;
-  const int forced = forcedAlgo();
-  if (forced == ALGO_RING && (t.func == FUNC_ALLGATHER || t.func == FUNC_BROADCAST)) return ringTreeRun(comm, t, forced);
+  int forced = forcedAlgo();
+  int modeForce = tForceMode;
+  tPickCtas = 0;
+  if (forced == ALGO_AUTO && modeForce < 0) {
+    size_t key = (t.func == FUNC_ALLGATHER || t.func == FUNC_ALLTOALL) ? B * n : B;
+    TunePick pk = tunePick(dp->tune, t.func, n, key);
+    if (pk.valid) { forced = pk.algo; modeForce = pk.mode; tPickCtas = pk.ctas; }
+  }
+  if (forced == ALGO_RING && t.func == FUNC_ALLGATHER) return ringTreeRun(comm, t, forced);
   if (forced == ALGO_CE || (forced == ALGO_AUTO && dp->tune.ceMin && B >= dp->tune.ceMin)) {
     bool handled = false;
     NCCLCHECK(ceCollRun(comm, t, &handled));
     if (handled) return ncclSuccess;
+  }
+  // ---- small blocks: flagged lines
+  if (B <= kLLDataBytes - 8 && (forced == ALGO_LL_ONESHOT || (forced == ALGO_AUTO && B <= dp->tune.llCopyMax[n]))) {
+    CollArgs a;
+    baseArgs(comm, &a, t.func);
+    a.root = t.root;
+    a.count = B;
+    a.sendStride = B;
+    a.recvStride = B;
+    a.lsend[me] = t.send;
+    a.lrecv[me] = t.recv;
+    size_t items = ((B + 7) / 8) * (size_t)(n - 1);
+    int ctas = (int)std::min<size_t>((items + kCtaThreads - 1) / kCtaThreads, 64);
+    return launchColl(comm, llCopyKernelFn(), &a, std::max(ctas, 1), t.stream);
   }
   size_t sendBytes = B, recvBytes = B;
   if (t.func == FUNC_ALLGATHER || t.func == FUNC_GATHER) recvBytes = B * n;
@@ -473,7 +524,7 @@ static ncclResult_t runCopyColl(ncclComm* comm, const Task& t) {
   // registration must be agreed upon: a buffer counts as symmetric only if its window is (collective property)
   int mode;
   bool staged = false;
-  if (recvAl.ok) mode = MODE_PUSH;
+  if (recvAl.ok && !(modeForce == MODE_PULL && sendAl.ok)) mode = MODE_PUSH;
   else if (sendAl.ok) mode = MODE_PULL;
   else { mode = MODE_PULL; staged = true; }
 
@@ -517,7 +568,7 @@ static ncclResult_t runCopyColl(ncclComm* comm, const Task& t) {
     if (B % 16) v16 = false;
     a.vec16 = v16;
     if (mode == MODE_PUSH && out.mc && v16 && (t.func == FUNC_ALLGATHER || t.func == FUNC_BROADCAST) &&
-        (forced == ALGO_NVLS || (forced == ALGO_AUTO && cur >= dp->tune.agMcMin[n]))) {
+        modeForce != MODE_PUSH && (forced == ALGO_NVLS || modeForce == MODE_MC || (forced == ALGO_AUTO && cur >= dp->tune.agMcMin[n]))) {
       a.mode = MODE_MC;
       a.recvMc = out.mc;
     }
@@ -556,10 +607,11 @@ static ncclResult_t runOneRank(ncclComm* comm, const Task& t) {
   }
   if (src != dst) {
     ScaleArgs ca{src, dst, bytes, 0, nullptr};
-    size_t perCta = 256 * 4 * 16;
-    int ctas = (int)std::min<size_t>((bytes + perCta - 1) / perCta, (size_t)comm->devPlane->smCount * 16);
+    const int threads = (int)paramCopyThreads(), unroll = (int)paramCopyUnroll();
+    size_t perCta = (size_t)threads * unroll * 16;
+    int ctas = (int)std::min<size_t>((bytes + perCta - 1) / perCta, (size_t)comm->devPlane->smCount * paramCopyCtasPerSm());
     comm->devPlane->launches++;
-    NCCLCHECK(launchKernel(localCopyKernelFn(), dim3(std::max(ctas, 1)), dim3(256), 0, &ca, t.stream, false));
+    NCCLCHECK(launchKernel(localCopyKernelFn(unroll), dim3(std::max(ctas, 1)), dim3(threads), 0, &ca, t.stream, false));
   }
   return ncclSuccess;
 }
@@ -701,6 +753,50 @@ ncclResult_t devPlaneRunP2pGroup(ncclComm* comm, const std::vector<Task>& tasks)
 out:
   if (cur != comm->cudaDev && cur >= 0) cudaSetDevice(cur);
   return res;
+}
+
+// Ring / tree schedules (NCCL_ALGO=Ring|Tree): always run in place on the staging area, which is
+// symmetric, so any user buffer works; the copies in and out ride on the same stream.
+ncclResult_t ringTreeRun(ncclComm* comm, const Task& t, int algo) {
+  DevicePlane* dp = comm->devPlane;
+  const int n = comm->nRanks, me = comm->rank;
+  const size_t es = typeSize(t.type);
+  DevOp op;
+  NCCLCHECK(lowerOp(comm, t, &op));
+  if (op.premul) return ncclInvalidUsage;
+  if (algo == ALGO_TREE && t.func != FUNC_ALLREDUCE) algo = ALGO_RING;
+  char* st = (char*)dp->resBase + dp->offStage;
+  const bool blocks = t.func != FUNC_ALLREDUCE;          // stage holds n blocks of `piece` elements
+  size_t cap = dp->stageBytes / es / (blocks ? n : 1);
+  cap = cap / 64 * 64;
+  for (size_t done = 0; done < t.count; done += cap) {
+    const size_t cur = std::min(cap, t.count - done);
+    if (t.func == FUNC_ALLREDUCE) {
+      CUDACHECK(cudaMemcpyAsync(st, (const char*)t.send + done * es, cur * es, cudaMemcpyDeviceToDevice, t.stream));
+    } else if (t.func == FUNC_REDUCESCATTER) {
+      CUDACHECK(cudaMemcpy2DAsync(st, cur * es, (const char*)t.send + done * es, t.count * es, cur * es, n, cudaMemcpyDeviceToDevice, t.stream));
+    } else {
+      CUDACHECK(cudaMemcpyAsync(st + (size_t)me * cur * es, (const char*)t.send + done * es, cur * es, cudaMemcpyDeviceToDevice, t.stream));
+    }
+    CollArgs a;
+    baseArgs(comm, &a, t.func);
+    a.count = cur;
+    a.scaleMode = op.scaleMode; a.scaleF = op.scaleF; a.scaleD = op.scaleD; a.intDiv = op.intDiv;
+    Aliases W = stageAliases(comm, 0);
+    for (int p = 0; p < n; ++p) a.recv[p] = W.peer[p];
+    a.vec16 = !blocks || (cur * es) % 16 == 0;
+    int ctas = clampCtas(comm, cur * es, dp->tune.p2pCtas);
+    const void* fn = algo == ALGO_TREE ? treeKernelFn(t.type, op.red) : ringKernelFn(t.type, op.red);
+    NCCLCHECK(launchColl(comm, fn, &a, ctas, t.stream));
+    if (t.func == FUNC_ALLREDUCE) {
+      CUDACHECK(cudaMemcpyAsync((char*)t.recv + done * es, st, cur * es, cudaMemcpyDeviceToDevice, t.stream));
+    } else if (t.func == FUNC_REDUCESCATTER) {
+      CUDACHECK(cudaMemcpyAsync((char*)t.recv + done * es, st + (size_t)me * cur * es, cur * es, cudaMemcpyDeviceToDevice, t.stream));
+    } else {
+      CUDACHECK(cudaMemcpy2DAsync((char*)t.recv + done * es, t.count * es, st, cur * es, cur * es, n, cudaMemcpyDeviceToDevice, t.stream));
+    }
+  }
+  return ncclSuccess;
 }
 
 // Latency/bandwidth model used only for ncclGroupSimulateEnd (microseconds).

@@ -9,6 +9,9 @@
 
 namespace b200 {
 
+struct TuneEntry { size_t upto; int algo; int mode; int ctas; };
+struct TunePick { bool valid; int algo, mode, ctas; };
+
 struct TuningTable {
   // Crossover sizes in bytes (per-rank message size of the call); measured defaults, overridable
   // with NCCL_TUNING_FILE or the NCCL_B200_* parameters.
@@ -16,9 +19,12 @@ struct TuningTable {
   size_t arNvlsMin[kMaxRanks + 1];     // all-reduce: multimem from this size (below: P2P two-shot)
   size_t agMcMin[kMaxRanks + 1];       // all-gather / broadcast: multimem.st from this size
   size_t rsNvlsMin[kMaxRanks + 1];     // reduce-scatter: multimem.ld_reduce from this size
+  size_t rsLLMax[kMaxRanks + 1];       // reduce-scatter / reduce: flagged lines up to this many bytes per receiver
+  size_t llCopyMax[kMaxRanks + 1];     // copy collectives: flagged lines up to this block size
   size_t ceMin;                        // copy-engine all-gather / all-to-all from this size (0 = never)
   int nvlsCtas, p2pCtas, copyCtas, sendrecvCtas;
   size_t bytesPerCta;                  // grow the grid by one CTA per this many bytes
+  std::vector<TuneEntry> entries[5][kMaxRanks + 1];   // measured rows per collective and rank count (sched/tuning.cc)
 };
 
 struct DevicePlane {
@@ -52,6 +58,13 @@ void tuningDefaults(TuningTable* t);
 ncclResult_t tuningLoadFile(TuningTable* t, const char* path);
 // Predicted duration (microseconds) of a task, used by ncclGroupSimulateEnd.
 float devPlaneEstimateUs(ncclComm* comm, const Task& t);
+// Forces the algorithm / copy mode of the calling thread's next launches (tuning sweeps, tests); ALGO_AUTO, -1 = automatic.
+void devPlaneForce(int algo, int mode);
+
+// measured selection table (sched/tuning.cc)
+bool tuneParse(TuningTable* t, const std::string& json);
+void tuneLoadDefaults(TuningTable* t);
+TunePick tunePick(const TuningTable& t, int func, int n, size_t bytes);
 
 // memory manager (mem/memmgr.cc)
 ncclResult_t memSuspend(ncclComm* comm);

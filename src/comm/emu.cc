@@ -57,7 +57,7 @@ void* b200EmuCreate(int nRanks, unsigned long long timeoutMs) {
   EmuCtx* e = new EmuCtx;
   e->n = nRanks;
   if (timeoutMs) e->timeoutNs = timeoutMs * 1000000ull;
-  const size_t privWords = kBarrierSlots + 4 + 2 * kMaxRanks + 4;
+  const size_t privWords = kPrivWords;
   for (int p = 0; p < nRanks; ++p) {
     bool ok = cudaMalloc(&e->sync[p], kSyncPageBytes) == cudaSuccess && cudaMalloc(&e->ll[p], kLLRegionBytes) == cudaSuccess &&
               cudaMalloc(&e->mailbox[p], kMailboxBytes) == cudaSuccess && cudaMalloc(&e->priv[p], privWords * 4) == cudaSuccess &&
@@ -157,6 +157,10 @@ int b200EmuCopy(void* ctx, int func, int mode, size_t bytes, const void** send, 
     if (((uintptr_t)send[p] & 15) || ((uintptr_t)recv[p] & 15)) v16 = false;
   }
   a.vec16 = v16;
+  if (mode == 3) {  // flagged lines
+    for (int p = 0; p < n; ++p) { a.ll[p] = e->ll[p]; a.llEpoch[p] = e->priv[p] + kBarrierSlots; }
+    return coopLaunch(llCopyKernelFn(), ctas, n, &a);
+  }
   return coopLaunch(copyKernelFn(), ctas, n, &a);
 }
 
@@ -199,3 +203,25 @@ extern "C" unsigned long long b200CommLaunchCount(ncclComm_t comm) {
 }
 extern "C" int b200CommIsSymmetric(ncclComm_t comm) { return commValid(comm) && comm->lsaAll ? 1 : 0; }
 extern "C" int b200CommHasMulticast(ncclComm_t comm) { return commValid(comm) && comm->sym && comm->sym->mcUsable ? 1 : 0; }
+
+// Live tuning (sweeps): name is a TuningTable field; n selects the rank-count column of tables.
+extern "C" int b200CommSetTuning(ncclComm_t comm, const char* name, int n, long long value) {
+  if (!commValid(comm) || !comm->devPlane || n < 0 || n > kMaxRanks) return 1;
+  TuningTable& t = comm->devPlane->tune;
+  std::string k(name);
+  if (k == "arLLMax") t.arLLMax[n] = (size_t)value;
+  else if (k == "arNvlsMin") t.arNvlsMin[n] = (size_t)value;
+  else if (k == "agMcMin") t.agMcMin[n] = (size_t)value;
+  else if (k == "rsNvlsMin") t.rsNvlsMin[n] = (size_t)value;
+  else if (k == "rsLLMax") t.rsLLMax[n] = (size_t)value;
+  else if (k == "llCopyMax") t.llCopyMax[n] = (size_t)value;
+  else if (k == "ceMin") t.ceMin = (size_t)value;
+  else if (k == "nvlsCtas") t.nvlsCtas = (int)value;
+  else if (k == "p2pCtas") t.p2pCtas = (int)value;
+  else if (k == "copyCtas") t.copyCtas = (int)value;
+  else if (k == "sendrecvCtas") t.sendrecvCtas = (int)value;
+  else if (k == "bytesPerCta") t.bytesPerCta = (size_t)value;
+  else return 2;
+  return 0;
+}
+extern "C" void b200ForceAlgo(int algo, int mode) { devPlaneForce(algo, mode); }

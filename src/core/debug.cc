@@ -94,6 +94,7 @@ void setThreadName(const char* fmt, ...) {
 
 void debugLog(LogLevel level, uint64_t subsys, const char* file, int line, const char* fmt, ...) {
   std::call_once(gOnce, initOnce);
+  if (level != LOG_WARN && (gLevel < (int)level || !(subsys & gMask))) return;   // nothing to format
   char msg[1024];
   va_list ap;
   va_start(ap, fmt);

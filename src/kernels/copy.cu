@@ -268,30 +268,37 @@ const void* scaleKernelFn(ncclDataType_t type) {
 }
 
 // Local copy of `count` bytes: the data movement of a single-rank communicator (out-of-place
-// collectives reduce to dst = src) and of staged transfers. Four independent 16-byte loads per
-// thread per iteration keep enough bytes in flight to run at HBM copy speed.
-__global__ void __launch_bounds__(256) localCopyKernel(ScaleArgs a) {
+// collectives reduce to dst = src) and of staged transfers. A CTA moves contiguous tiles of
+// U x blockDim x 16 bytes (all loads of a tile issued before its stores), and CTAs stride over
+// tiles, so that each DRAM page is opened once and enough bytes are in flight for HBM speed.
+template <int U>
+__global__ void __launch_bounds__(512) localCopyKernel(ScaleArgs a) {
   const char* src = (const char*)a.src;
   char* dst = (char*)a.dst;
   const size_t bytes = a.count;
-  const size_t stride = (size_t)gridDim.x * blockDim.x;
-  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if ((((uintptr_t)src | (uintptr_t)dst) & 15) == 0) {
     const size_t packs = bytes / 16;
-    for (; i + 3 * stride < packs; i += 4 * stride) {
-      uint4 v[4];
+    const size_t tilePacks = (size_t)U * blockDim.x;
+    const size_t fullTiles = packs / tilePacks;
+    for (size_t t = blockIdx.x; t < fullTiles; t += gridDim.x) {
+      const size_t base = t * tilePacks + threadIdx.x;
+      uint4 v[U];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) v[u] = ldStream16(src + (i + u * stride) * 16);
+      for (int u = 0; u < U; ++u) v[u] = ldStream16(src + (base + (size_t)u * blockDim.x) * 16);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) st16(dst + (i + u * stride) * 16, v[u]);
+      for (int u = 0; u < U; ++u) st16(dst + (base + (size_t)u * blockDim.x) * 16, v[u]);
     }
-    for (; i < packs; i += stride) st16(dst + i * 16, ldStream16(src + i * 16));
-    for (size_t j = packs * 16 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; j < bytes; j += stride) dst[j] = src[j];
+    // remainder: packs past the last full tile, then loose bytes
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (size_t i = fullTiles * tilePacks + tid; i < packs; i += stride) st16(dst + i * 16, ldStream16(src + i * 16));
+    for (size_t j = packs * 16 + tid; j < bytes; j += stride) dst[j] = src[j];
   } else {
-    for (; i < bytes; i += stride) dst[i] = src[i];
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < bytes; i += stride) dst[i] = src[i];
   }
 }
-const void* localCopyKernelFn() { return (const void*)localCopyKernel; }
+const void* localCopyKernelFn(int unroll) { return unroll >= 8 ? (const void*)localCopyKernel<8> : (const void*)localCopyKernel<4>; }
 
 // ------------------------------------------------------------------------- signals
 __global__ void signalKernel(OneSignalArgs a) {

@@ -26,10 +26,12 @@ const void* reduceKernelFn(int kernelId, ncclDataType_t type, int op);
 bool nvlsReduceSupported(ncclDataType_t type, int op);
 const void* ringKernelFn(ncclDataType_t type, int op);
 const void* treeKernelFn(ncclDataType_t type, int op);
+const void* llReduceKernelFn(ncclDataType_t type, int op);   // all-reduce, reduce-scatter, reduce (a.func)
+const void* llCopyKernelFn();
 const void* copyKernelFn();
 const void* p2pKernelFn();
 const void* scaleKernelFn(ncclDataType_t type);
-const void* localCopyKernelFn();   // takes ScaleArgs{src, dst, count = bytes}
+const void* localCopyKernelFn(int unroll);   // takes ScaleArgs{src, dst, count = bytes}; unroll 4 or 8
 const void* signalKernelFn();
 const void* waitSignalKernelFn();
 

@@ -2,9 +2,7 @@
 //   reduceP2pKernel    every rank loads its slice from all ranks, reduces in registers (fp32
 //                      accumulation for 8/16-bit floats, fixed rank order) and stores the result
 //                      locally (reduce-scatter, reduce) or to every rank (two-shot all-reduce).
-//   allReduceLLKernel  one-shot all-reduce for small payloads: every rank pushes flagged 16-byte
-//                      lines {data, flag, data, flag} to all peers and reduces what it receives;
-//                      the flag is the call's epoch, so no barrier is needed.
+//   (the flagged-line kernels for small payloads are in ll.cu)
 //   reduceNvlsKernel   the same three collectives with multimem.ld_reduce (the NVSwitch reduces)
 //                      and multimem.st (the switch replicates).
 // Reference parity: src/device/symmetric/all_reduce.cuh:14-262 (RSxLD_AGxST), :431-504
@@ -80,84 +78,6 @@ __global__ void __launch_bounds__(kCtaThreads, 1) reduceP2pKernel(const __grid_c
   }
   bar.sync();  // results have landed everywhere; nobody reads this rank's input any more
   bar.finish();
-}
-
-// ------------------------------------------------------------------------- LL one-shot
-__device__ __forceinline__ uint64_t load8Partial(const char* p, size_t valid) {
-  if (valid >= 8 && ((uintptr_t)p & 7) == 0) return *(const uint64_t*)p;
-  uint64_t v = 0;
-  for (size_t b = 0; b < 8 && b < valid; ++b) v |= (uint64_t)(uint8_t)p[b] << (8 * b);
-  return v;
-}
-__device__ __forceinline__ void store8Partial(char* p, uint64_t v, size_t valid) {
-  if (valid >= 8 && ((uintptr_t)p & 7) == 0) { *(uint64_t*)p = v; return; }
-  for (size_t b = 0; b < 8 && b < valid; ++b) p[b] = (char)(v >> (8 * b));
-}
-
-template <typename T, int OP>
-__global__ void __launch_bounds__(kCtaThreads, 1) allReduceLLKernel(const __grid_constant__ CollArgs a) {
-  const int rank = ctaRank(a.emu, a.rank);
-  const int n = a.nRanks;
-  constexpr int N = 8 / sizeof(T);
-  uint32_t* ep = a.llEpoch[rank];
-  uint32_t epoch = ep[0] + 1;
-  if (epoch == 0) epoch = 1;
-  const int parity = epoch & 1;
-  WaitCtx w{&a.sync, a.sync.status[rank]};
-  const size_t bytes = a.count * sizeof(T);
-  const size_t nLines = (bytes + 7) / 8;
-  const char* in = (const char*)a.lsend[rank];
-  char* out = (char*)a.lrecv[rank];
-  const size_t stride = (size_t)gridDim.x * blockDim.x;
-  // region of source `s` inside rank p's LL buffer for this parity
-  auto region = [&](int p, int s) { return (char*)a.ll[p] + ((size_t)(parity * kMaxRanks + s) * kLLLines) * 16; };
-  // phase 1: publish my lines everywhere
-  for (size_t l = (size_t)blockIdx.x * blockDim.x + threadIdx.x; l < nLines; l += stride) {
-    uint64_t d = load8Partial(in + l * 8, bytes - l * 8);
-    uint4 line = make_uint4((uint32_t)d, epoch, (uint32_t)(d >> 32), epoch);
-    for (int p = 0; p < n; ++p)
-      if (p != rank) stVolatile16(region(p, rank) + l * 16, line);
-  }
-  // phase 2: collect every rank's line, reduce in rank order, write the result
-  bool ok = true;
-  for (size_t l = (size_t)blockIdx.x * blockDim.x + threadIdx.x; l < nLines && ok; l += stride) {
-    typename Elem<T>::Acc acc[N];
-    for (int s = 0; s < n; ++s) {
-      uint64_t d;
-      if (s == rank) {
-        d = load8Partial(in + l * 8, bytes - l * 8);
-      } else {
-        const char* slot = region(rank, s) + l * 16;
-        uint4 v = ldVolatile16(slot);
-        if (v.y != epoch || v.w != epoch)
-          ok = boundedWait(w, WAIT_LL, (uint32_t)s, epoch, [&] { v = ldVolatile16(slot); return v.y == epoch && v.w == epoch; });
-        if (!ok) break;
-        d = (uint64_t)v.x | ((uint64_t)v.z << 32);
-      }
-      union { uint64_t u; T e[N]; } cv;
-      cv.u = d;
-#pragma unroll
-      for (int k = 0; k < N; ++k) {
-        typename Elem<T>::Acc x = Elem<T>::ld(cv.e[k]);
-        acc[k] = s == 0 ? x : redApply<OP>(acc[k], x);
-      }
-    }
-    if (!ok) break;
-    union { uint64_t u; T e[N]; } res;
-#pragma unroll
-    for (int k = 0; k < N; ++k) res.e[k] = scalarPost<T, OP>(acc[k], a);
-    store8Partial(out + l * 8, res.u, bytes - l * 8);
-  }
-  // the last CTA to finish publishes the epoch for the next call
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    uint32_t done = atomicAdd(&ep[1], 1u);
-    if (done == gridDim.x - 1) {
-      ep[1] = 0;
-      ep[0] = epoch;
-    }
-  }
 }
 
 // ------------------------------------------------------------------------- NVLS
@@ -262,7 +182,6 @@ __global__ void __launch_bounds__(kCtaThreads, 1) reduceNvlsKernel(const __grid_
 template <template <typename, int> class K> struct KernelOf;
 
 template <typename T, int OP> static const void* p2pFn() { return (const void*)reduceP2pKernel<T, OP>; }
-template <typename T, int OP> static const void* llFn() { return (const void*)allReduceLLKernel<T, OP>; }
 template <typename T, int OP> static const void* nvlsFn() {
   if constexpr (McRed<T, OP>::kSupported) return (const void*)reduceNvlsKernel<T, OP>;
   else return nullptr;
@@ -289,7 +208,7 @@ template <typename T, int OP> static const void* nvlsFn() {
 
 const void* reduceKernelFn(int algo, ncclDataType_t type, int op) {
   if (algo == KERNEL_REDUCE_P2P) { BY_TYPE(p2pFn, type, op) }
-  if (algo == KERNEL_ALLREDUCE_LL) { BY_TYPE(llFn, type, op) }
+  if (algo == KERNEL_ALLREDUCE_LL) return llReduceKernelFn(type, op);
   if (algo == KERNEL_REDUCE_NVLS) { BY_TYPE(nvlsFn, type, op) }
   return nullptr;
 }

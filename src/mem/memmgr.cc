@@ -50,7 +50,7 @@ ncclResult_t memResume(ncclComm* comm) {
   NCCLCHECK(memAlloc(&dp->resBase, dp->resSize, comm->cudaDev));
   CUDACHECK(cudaMemset(dp->resBase, 0, dp->offMailbox));
   // epochs restart together with the flags they are compared against
-  const size_t privWords = kBarrierSlots + 4 + (2 * kMaxRanks + 4);
+  const size_t privWords = kPrivWords;
   CUDACHECK(cudaMemset(dp->priv, 0, privWords * sizeof(uint32_t)));
   CUDACHECK(cudaDeviceSynchronize());
   NCCLCHECK(symWindowRegister(comm, dp->resBase, dp->resSize, &dp->resWin, NCCL_WIN_COLL_SYMMETRIC));

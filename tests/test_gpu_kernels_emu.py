@@ -288,3 +288,60 @@ def test_wait_runs_out_and_reports(emu_lib):
         assert int((torch.ones(8, device="cuda") * 2).sum().item()) == 16
     finally:
         emu_lib.b200EmuDestroy(ctx)
+
+
+@pytest.mark.parametrize("n,dtype,count", [(8, torch.bfloat16, 1024), (4, torch.float32, 1001), (3, torch.float16, 5), (2, torch.int32, 4099)])
+def test_flagged_line_reduce_scatter_and_reduce(emu_lib, n, dtype, count):
+    ctx = emu_lib.b200EmuCreate(n, 5000)
+    try:
+        for rep in range(3):
+            ins = _make_inputs(n, count * n, dtype, 21 + rep, "sum")
+            want = _reference(ins, "sum", dtype)
+            outs = [torch.zeros(count, dtype=dtype, device="cuda") for _ in range(n)]
+            assert emu_lib.b200EmuReduce(ctx, KERNEL_ALLREDUCE_LL, FUNC_REDUCESCATTER, _types()[dtype], 0, count, _ptrs(ins), _ptrs(outs), 0, 2) == 0
+            for r in range(n):
+                assert _close(outs[r], want[r * count:(r + 1) * count], dtype), (rep, r)
+            root = rep % n
+            full = [torch.zeros(count * n, dtype=dtype, device="cuda") for _ in range(n)]
+            assert emu_lib.b200EmuReduce(ctx, KERNEL_ALLREDUCE_LL, FUNC_REDUCE, _types()[dtype], 0, count * n, _ptrs(ins), _ptrs(full), root, 2) == 0
+            assert _close(full[root], want, dtype)
+    finally:
+        emu_lib.b200EmuDestroy(ctx)
+
+
+@pytest.mark.parametrize("n", [2, 5, 8])
+@pytest.mark.parametrize("nbytes", [8, 13, 4096, 100003])
+def test_flagged_line_copy_collectives(emu_lib, n, nbytes):
+    MODE_LL = 3
+    ctx = emu_lib.b200EmuCreate(n, 5000)
+    try:
+        g = torch.Generator().manual_seed(nbytes * 3 + n)
+
+        def rnd(k):
+            return torch.randint(0, 256, (k,), generator=g, dtype=torch.uint8).cuda()
+        for rep in range(2):
+            send = [rnd(nbytes) for _ in range(n)]
+            recv = [torch.zeros(nbytes * n, dtype=torch.uint8, device="cuda") for _ in range(n)]
+            assert emu_lib.b200EmuCopy(ctx, FUNC_ALLGATHER, MODE_LL, nbytes, _ptrs(send), _ptrs(recv), 0, 2) == 0
+            assert all(torch.equal(r, torch.cat(send)) for r in recv)
+            send = [rnd(nbytes * n) for _ in range(n)]
+            recv = [torch.zeros(nbytes * n, dtype=torch.uint8, device="cuda") for _ in range(n)]
+            assert emu_lib.b200EmuCopy(ctx, FUNC_ALLTOALL, MODE_LL, nbytes, _ptrs(send), _ptrs(recv), 0, 2) == 0
+            for r in range(n):
+                assert torch.equal(recv[r], torch.cat([send[p][r * nbytes:(r + 1) * nbytes] for p in range(n)]))
+            root = (rep + 1) % n
+            send = [rnd(nbytes) for _ in range(n)]
+            recv = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(n)]
+            assert emu_lib.b200EmuCopy(ctx, FUNC_BROADCAST, MODE_LL, nbytes, _ptrs(send), _ptrs(recv), root, 1) == 0
+            assert all(torch.equal(r, send[root]) for r in recv)
+            send = [rnd(nbytes * n) for _ in range(n)]
+            recv = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(n)]
+            assert emu_lib.b200EmuCopy(ctx, FUNC_SCATTER, MODE_LL, nbytes, _ptrs(send), _ptrs(recv), root, 1) == 0
+            for r in range(n):
+                assert torch.equal(recv[r], send[root][r * nbytes:(r + 1) * nbytes])
+            send = [rnd(nbytes) for _ in range(n)]
+            recv = [torch.zeros(nbytes * n, dtype=torch.uint8, device="cuda") for _ in range(n)]
+            assert emu_lib.b200EmuCopy(ctx, FUNC_GATHER, MODE_LL, nbytes, _ptrs(send), _ptrs(recv), root, 1) == 0
+            assert torch.equal(recv[root], torch.cat(send))
+    finally:
+        emu_lib.b200EmuDestroy(ctx)

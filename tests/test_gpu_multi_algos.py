@@ -1,0 +1,104 @@
+"""Multi-GPU runs of the alternative schedules and of communicator management.
+
+Ring / tree / flagged-line / copy-engine variants are forced with NCCL_ALGO and checked with the
+same collective battery as the default selection; then split, one-sided signals, suspend/resume
+and pre-multiplied sums.
+"""
+import pytest
+
+torch = pytest.importorskip("torch")
+
+from mp_util import run_ranks  # noqa: E402
+from test_gpu_multi import _check, _colls_rank, _ngpus, _sym_tensor  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("algo", ["Ring", "Tree", "LL", "CE"])
+@pytest.mark.parametrize("registered", [True, False])
+def test_forced_schedules(algo, registered):
+    n = min(_ngpus(), 8)
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    res = run_ranks(_colls_rank, n, args=(registered, algo), timeout=300)
+    _check(res, n)
+
+
+def _mgmt_rank(rank, nranks, uid):
+    import ctypes
+    import torch
+    torch.cuda.set_device(rank)
+    from nccl_b200 import Communicator, _lib
+    from nccl_b200.core import FP32
+    comm = Communicator(nranks, rank, uid)
+    lib = comm.lib
+    out = {}
+    # split in two halves (odd / even ranks), all-reduce inside each
+    sub = comm.split(rank % 2, key=rank)
+    x = torch.full((1000,), float(rank + 1), device="cuda")
+    sub.all_reduce(x)
+    torch.cuda.synchronize()
+    out["split_sum"] = float(x[0])
+    out["split_size"] = sub.nranks
+    sub.destroy()
+    # pre-multiplied sum: sum_r (0.5 * x_r)
+    op = comm.premul_sum(0.5, FP32)
+    y = torch.full((4096,), float(rank + 1), device="cuda")
+    z = torch.empty_like(y)
+    comm.all_reduce(y, z, op=op)
+    torch.cuda.synchronize()
+    out["premul"] = float(z[7])
+    comm.destroy_op(op)
+    # one-sided put + signal around a ring: every rank writes into its successor's window
+    win_t = _sym_tensor(comm, 1024, torch.float32)
+    win_t.zero_()
+    torch.cuda.synchronize()
+    win = comm._windows[next(iter(comm._windows))]
+    src = torch.full((1024,), 100.0 + rank, device="cuda")
+    nxt, prv = (rank + 1) % nranks, (rank - 1) % nranks
+    lib.ncclPutSignal.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t,
+                                  ctypes.c_int, ctypes.c_int, ctypes.c_uint, ctypes.c_void_p, ctypes.c_void_p]
+
+    class Desc(ctypes.Structure):
+        _fields_ = [("opCnt", ctypes.c_int), ("peer", ctypes.c_int), ("sigIdx", ctypes.c_int), ("ctx", ctypes.c_int)]
+    lib.ncclWaitSignal.argtypes = [ctypes.c_int, ctypes.POINTER(Desc), ctypes.c_void_p, ctypes.c_void_p]
+    st = torch.cuda.current_stream().cuda_stream
+    # a barrier first: the target must have zeroed its window before anybody writes into it
+    b = torch.zeros(1, device="cuda")
+    comm.all_reduce(b)
+    for _ in range(2):
+        _lib.check(lib.ncclPutSignal(src.data_ptr(), 1024, FP32, nxt, win, 0, 3, 0, 0, comm.handle, st), "ncclPutSignal", lib)
+        d = Desc(1, prv, 3, 0)
+        _lib.check(lib.ncclWaitSignal(1, ctypes.byref(d), comm.handle, st), "ncclWaitSignal", lib)
+    torch.cuda.synchronize()
+    out["put"] = float(win_t[5])
+    # suspend / resume: the resource window goes away and comes back, collectives still work
+    before = comm.mem_stats(0)
+    comm.suspend()
+    out["suspended_flag"] = comm.mem_stats(1)
+    out["suspendable_after"] = comm.mem_stats(0)
+    comm.resume()
+    w = torch.full((1 << 16,), 1.0, device="cuda")
+    comm.all_reduce(w)
+    torch.cuda.synchronize()
+    out["after_resume"] = float(w[0])
+    out["suspendable_before"] = before
+    assert comm.async_error() == 0
+    comm.destroy()
+    return out
+
+
+def test_split_premul_signals_suspend():
+    n = min(_ngpus(), 8)
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    res = run_ranks(_mgmt_rank, n, timeout=300)
+    for r in range(n):
+        o = res[r]
+        members = [q for q in range(n) if q % 2 == r % 2]
+        assert o["split_size"] == len(members)
+        assert o["split_sum"] == sum(q + 1 for q in members)
+        assert o["premul"] == 0.5 * sum(q + 1 for q in range(n))
+        assert o["put"] == 100.0 + (r - 1) % n
+        assert o["suspended_flag"] == 1 and o["suspendable_after"] == 0 and o["suspendable_before"] > 0
+        assert o["after_resume"] == float(n)
