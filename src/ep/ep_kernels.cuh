@@ -1,0 +1,42 @@
+// Argument block of the expert-parallel dispatch / combine kernels (shared by host and device).
+#pragma once
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "../kernels/args.h"
+
+namespace b200 {
+
+struct EpArgs {
+  int rank, nRanks, emu;
+  int numExperts, expertsPerRank, topk, hidden;
+  int maxTokens;                               // capacity: tokens a rank may dispatch per call
+  int fp8;                                     // dispatch payload: 1 = e4m3 + one fp32 scale per 128 channels, 0 = bf16
+  int numTokens[kMaxRanks];                    // tokens of rank r in this call
+  // rank-private inputs
+  const __nv_bfloat16* x[kMaxRanks];           // dispatch: [numTokens, hidden]; combine: expert outputs [E_local, cap, hidden]
+  const int64_t* topkIdx[kMaxRanks];           // [numTokens, topk], -1 = unused entry
+  const float* topkW[kMaxRanks];               // [numTokens, topk]
+  // peer-visible windows
+  char* recvBuf[kMaxRanks];                    // dispatch landing zone [E_local][nRanks][maxTokens] slots
+  unsigned long long* recvCount[kMaxRanks];    // [E_local][nRanks]: epoch << 32 | count
+  char* combBuf[kMaxRanks];                    // combine landing zone [maxTokens][topk][hidden] bf16
+  unsigned long long* combFlag[kMaxRanks];     // [nRanks]: epoch of the last completed combine per source
+  // rank-private state and outputs
+  uint32_t* state[kMaxRanks];                  // [0] epoch, [1] CTAs past the send phase, [2] CTAs finished, [8 ..] per-expert send counters
+  void* outTokens[kMaxRanks];                  // dispatch: [E_local, cap, hidden] fp8 or bf16 ; combine: [numTokens, hidden] bf16
+  float* outScales[kMaxRanks];                 // dispatch fp8: [E_local, cap, hidden/128]
+  int* expertCount[kMaxRanks];                 // [E_local] tokens received per local expert
+  int2* srcInfo[kMaxRanks];                    // [E_local, cap] {source rank, token * topk + k}; written by dispatch, read by combine
+  SyncArgs sync;
+};
+
+__host__ __device__ inline size_t epSlotBytes(int hidden, int fp8) {
+  size_t b = fp8 ? (size_t)hidden + (size_t)(hidden / 128) * 4 : (size_t)hidden * 2;
+  return (b + 16 + 15) / 16 * 16;              // payload + 16-byte header, 16-byte aligned
+}
+
+const void* epDispatchKernelFn();
+const void* epCombineKernelFn();
+
+}  // namespace b200

@@ -1,0 +1,440 @@
+// Host side of expert-parallel dispatch / combine: groups (symmetric landing zones), handles
+// (routing of one batch), launches, and a single-GPU emulation used by the unit tests.
+// Reference parity: contrib/nccl_ep/nccl_ep.cc (ncclEpCreateGroup :1223, handles :1904-2408,
+// ncclEpDispatch :2410, ncclEpCombine :2984, ncclEpComplete :3413, error API :3430-3545).
+#include "nccl_ep.h"
+
+#include <algorithm>
+
+#include "../comm/device_plane.h"
+#include "ep_kernels.cuh"
+
+using namespace b200;
+
+struct ncclEpGroup {
+  ncclComm* comm = nullptr;
+  ncclEpGroupConfig_t cfg;
+  int n = 1, E = 0, El = 0, H = 0, maxTokens = 0, K = 0;
+  size_t slotBytes = 0, zoneBytes = 0, combZoneBytes = 0;
+  char* recvZone = nullptr;           // 2 zones (epoch parity)
+  SymWindow* recvWin = nullptr;
+  char* ctl = nullptr;                // counts [2][El][n] u64, combine flags [n] u64
+  SymWindow* ctlWin = nullptr;
+  char* combZone = nullptr;           // 2 zones, allocated with the first handle (needs top-k)
+  SymWindow* combWin = nullptr;
+  uint32_t* state = nullptr;
+  int smCount = 0;
+  int lastError = 0;
+};
+
+struct ncclEpHandle {
+  ncclEpGroup* g = nullptr;
+  ncclEpLayout_t layout;
+  int K = 0, T = 0;
+  const int64_t* topkIdx = nullptr;
+  const float* topkW = nullptr;
+  int2* srcInfo = nullptr;
+  int* expertCount = nullptr;
+};
+
+static bool cfgOk(const void* p) {
+  const unsigned int* u = (const unsigned int*)p;
+  return p && u[1] == NCCL_EP_MAGIC;
+}
+static bool tensorOk(const ncclEpTensor_t* t, unsigned ndim) {
+  return t && t->magic == NCCL_EP_TENSOR_MAGIC && t->ndim == ndim && t->data && t->sizes;
+}
+
+static size_t ctlBytes(int El, int n) { return ((size_t)2 * El * n + n) * sizeof(unsigned long long); }
+
+static void fillEpArgs(ncclEpGroup* g, EpArgs* a) {
+  memset(a, 0, sizeof(*a));
+  ncclComm* comm = g->comm;
+  a->rank = comm->rank;
+  a->nRanks = g->n;
+  a->numExperts = g->E;
+  a->expertsPerRank = g->El;
+  a->hidden = g->H;
+  a->maxTokens = g->maxTokens;
+  for (int p = 0; p < g->n; ++p) {
+    char* rz = g->n > 1 ? (char*)g->recvWin->host.peerPtr[p] : g->recvZone;
+    char* cz = g->n > 1 ? (char*)g->ctlWin->host.peerPtr[p] : g->ctl;
+    a->recvBuf[p] = rz;
+    a->recvCount[p] = (unsigned long long*)cz;
+    a->combFlag[p] = (unsigned long long*)cz + (size_t)2 * g->El * g->n;
+    if (g->combZone) a->combBuf[p] = g->n > 1 ? (char*)g->combWin->host.peerPtr[p] : g->combZone;
+  }
+  a->state[comm->rank] = g->state;
+  a->sync.status[comm->rank] = comm->devStatusDev;
+  a->sync.abortFlag = comm->abortFlagDev;
+  a->sync.timeoutNs = g->cfg.timeout_ns ? g->cfg.timeout_ns : (comm->devPlane ? comm->devPlane->timeoutNs : 5000000000ull);
+}
+
+static ncclResult_t launchEp(const void* fn, EpArgs* a, int ctas, int ranksY, size_t smem, cudaStream_t stream, bool coop) {
+  static bool attr[2] = {false, false};
+  int which = fn == epDispatchKernelFn() ? 0 : 1;
+  if (!attr[which] && smem > 40000) {
+    CUDACHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr[which] = true;
+  }
+  return launchKernel(fn, dim3(ctas, ranksY), dim3(512), smem, a, stream, coop);
+}
+
+static size_t dispatchSmem(int H, int fp8) { return fp8 ? (size_t)H + (size_t)(H / 128) * 4 + 16 : (size_t)H * 2; }
+
+extern "C" {
+
+ncclResult_t ncclEpGetVersion(int* version) {
+  if (!version) return ncclInvalidArgument;
+  *version = NCCL_EP_VERSION_CODE;
+  return ncclSuccess;
+}
+
+ncclResult_t ncclEpTensorAlloc(ncclEpTensor_t** tensor, unsigned int ndim, ncclDataType_t datatype, const size_t* sizes, const ncclEpTensorAllocConfig_t* config) {
+  if (!tensor || !sizes || ndim == 0 || ndim > 8) return ncclInvalidArgument;
+  if (config && !cfgOk(config)) return ncclInvalidArgument;
+  ncclEpTensor_t* t = new ncclEpTensor_t;
+  t->size = sizeof(*t);
+  t->magic = NCCL_EP_TENSOR_MAGIC;
+  t->ndim = ndim;
+  t->datatype = datatype;
+  t->win_hdl = nullptr;
+  t->win_offset = 0;
+  t->sizes = new size_t[ndim];
+  size_t bytes = typeSize(datatype);
+  for (unsigned i = 0; i < ndim; ++i) { t->sizes[i] = sizes[i]; bytes *= sizes[i]; }
+  t->data = nullptr;
+  if (cudaMalloc(&t->data, std::max<size_t>(bytes, 16)) != cudaSuccess) { (void)cudaGetLastError(); delete[] t->sizes; delete t; return ncclUnhandledCudaError; }
+  *tensor = t;
+  return ncclSuccess;
+}
+
+ncclResult_t ncclEpTensorDestroy(ncclEpTensor_t* t) {
+  if (!t) return ncclSuccess;
+  if (t->magic != NCCL_EP_TENSOR_MAGIC) return ncclInvalidArgument;
+  if (t->data) cudaFree(t->data);
+  delete[] t->sizes;
+  delete t;
+  return ncclSuccess;
+}
+
+ncclResult_t ncclEpCreateGroup(ncclEpGroup_t* out, ncclComm_t comm, const ncclEpGroupConfig_t* cfg) {
+  if (!out) return ncclInvalidArgument;
+  *out = nullptr;
+  if (!commValid(comm) || comm->hostOnly) { WARN("ncclEpCreateGroup needs a GPU communicator"); return ncclInvalidArgument; }
+  if (!cfgOk(cfg)) { WARN("ncclEpCreateGroup: configuration was not initialised"); return ncclInvalidArgument; }
+  NCCLCHECK(commEnsureReady(comm));
+  const int n = comm->nRanks;
+  if (n > 1 && !comm->lsaAll) { WARN("ncclEpCreateGroup: ranks must be able to map each other's memory"); return ncclInvalidUsage; }
+  if (cfg->num_experts == 0 || cfg->num_experts % n) { WARN("ncclEpCreateGroup: %u experts do not divide over %d ranks", cfg->num_experts, n); return ncclInvalidArgument; }
+  if (cfg->max_token_bytes == 0 || (cfg->max_token_bytes / 2) % 128) { WARN("ncclEpCreateGroup: hidden size must be a multiple of 128"); return ncclInvalidArgument; }
+  if (cfg->max_dispatch_tokens_per_rank == 0) return ncclInvalidArgument;
+  ncclEpGroup* g = new ncclEpGroup;
+  g->comm = comm;
+  g->cfg = *cfg;
+  g->n = n;
+  g->E = (int)cfg->num_experts;
+  g->El = g->E / n;
+  g->H = (int)cfg->max_token_bytes / 2;
+  g->maxTokens = (int)cfg->max_dispatch_tokens_per_rank;
+  g->slotBytes = epSlotBytes(g->H, 0);   // sized for the larger (bf16) payload
+  g->zoneBytes = (size_t)g->El * n * g->maxTokens * g->slotBytes;
+  int cur = -1;
+  CUDACHECK(cudaGetDevice(&cur));
+  if (cur != comm->cudaDev) CUDACHECK(cudaSetDevice(comm->cudaDev));
+  CUDACHECK(cudaDeviceGetAttribute(&g->smCount, cudaDevAttrMultiProcessorCount, comm->cudaDev));
+  NCCLCHECK(memAlloc((void**)&g->recvZone, 2 * g->zoneBytes, comm->cudaDev));
+  NCCLCHECK(memAlloc((void**)&g->ctl, ctlBytes(g->El, n), comm->cudaDev));
+  CUDACHECK(cudaMemset(g->ctl, 0, ctlBytes(g->El, n)));
+  CUDACHECK(cudaMalloc(&g->state, (8 + g->E) * sizeof(uint32_t)));
+  CUDACHECK(cudaMemset(g->state, 0, (8 + g->E) * sizeof(uint32_t)));
+  CUDACHECK(cudaDeviceSynchronize());
+  if (n > 1) {
+    NCCLCHECK(symWindowRegister(comm, g->recvZone, 2 * g->zoneBytes, &g->recvWin, NCCL_WIN_COLL_SYMMETRIC));
+    NCCLCHECK(symWindowRegister(comm, g->ctl, ctlBytes(g->El, n), &g->ctlWin, NCCL_WIN_COLL_SYMMETRIC));
+    if (!g->recvWin->symmetric || !g->ctlWin->symmetric) { WARN("ncclEpCreateGroup: windows could not be mapped by the peers"); return ncclInternalError; }
+    NCCLCHECK(bootstrapBarrier(comm->bootstrap));
+  }
+  if (cur != comm->cudaDev) cudaSetDevice(cur);
+  *out = g;
+  return ncclSuccess;
+}
+
+ncclResult_t ncclEpGroupDestroy(ncclEpGroup_t g) {
+  if (!g) return ncclSuccess;
+  cudaDeviceSynchronize();
+  if (g->recvWin) symWindowDeregister(g->comm, g->recvWin);
+  if (g->ctlWin) symWindowDeregister(g->comm, g->ctlWin);
+  if (g->combWin) symWindowDeregister(g->comm, g->combWin);
+  if (g->recvZone) memFree(g->recvZone);
+  if (g->ctl) memFree(g->ctl);
+  if (g->combZone) memFree(g->combZone);
+  if (g->state) cudaFree(g->state);
+  delete g;
+  return ncclSuccess;
+}
+
+ncclResult_t ncclEpHandleMemSize(ncclEpGroup_t g, ncclEpLayout_t, const ncclEpHandleConfig_t*, size_t* size_out, int) {
+  if (!g || !size_out) return ncclInvalidArgument;
+  *size_out = (size_t)g->El * g->n * g->maxTokens * sizeof(int2) + (size_t)g->El * sizeof(int);
+  return ncclSuccess;
+}
+
+ncclResult_t ncclEpInitHandle(ncclEpHandle_t* out, ncclEpGroup_t g, ncclEpLayout_t layout, const ncclEpHandleConfig_t* config, int num_topk, const ncclEpTensor_t*) {
+  if (!out || !g || num_topk <= 0 || num_topk > 16) return ncclInvalidArgument;
+  if (config && !cfgOk(config)) return ncclInvalidArgument;
+  if (layout != NCCL_EP_LAYOUT_UNSET && layout != NCCL_EP_LAYOUT_EXPERT_MAJOR) { WARN("ncclEp: only the expert-major layout is implemented"); return ncclInvalidUsage; }
+  if (g->K == 0) {
+    // first handle: the combine landing zones depend on top-k (collective, like every handle creation)
+    g->K = num_topk;
+    g->combZoneBytes = (size_t)g->maxTokens * num_topk * g->H * 2;
+    NCCLCHECK(memAlloc((void**)&g->combZone, 2 * g->combZoneBytes, g->comm->cudaDev));
+    if (g->n > 1) {
+      NCCLCHECK(symWindowRegister(g->comm, g->combZone, 2 * g->combZoneBytes, &g->combWin, NCCL_WIN_COLL_SYMMETRIC));
+      if (!g->combWin->symmetric) return ncclInternalError;
+    }
+  } else if (g->K != num_topk) {
+    WARN("ncclEp: all handles of a group must use the same top-k (%d, got %d)", g->K, num_topk);
+    return ncclInvalidUsage;
+  }
+  ncclEpHandle* h = new ncclEpHandle;
+  h->g = g;
+  h->layout = NCCL_EP_LAYOUT_EXPERT_MAJOR;
+  h->K = num_topk;
+  const size_t cap = (size_t)g->n * g->maxTokens;
+  CUDACHECK(cudaMalloc(&h->srcInfo, (size_t)g->El * cap * sizeof(int2)));
+  CUDACHECK(cudaMalloc(&h->expertCount, (size_t)g->El * sizeof(int)));
+  CUDACHECK(cudaMemset(h->expertCount, 0, (size_t)g->El * sizeof(int)));
+  *out = h;
+  return ncclSuccess;
+}
+
+ncclResult_t ncclEpUpdateHandle(ncclEpHandle_t h, const ncclEpTensor_t* topk_idx, const ncclEpLayoutInfo_t*, cudaStream_t) {
+  if (!h || !tensorOk(topk_idx, 2)) return ncclInvalidArgument;
+  if (topk_idx->datatype != ncclInt64) { WARN("ncclEp: topk_idx must be int64"); return ncclInvalidArgument; }
+  if ((int)topk_idx->sizes[1] != h->K) { WARN("ncclEp: topk_idx has %zu columns, the handle was made for top-%d", topk_idx->sizes[1], h->K); return ncclInvalidArgument; }
+  if ((int)topk_idx->sizes[0] > h->g->maxTokens) { WARN("ncclEp: %zu tokens exceed max_dispatch_tokens_per_rank", topk_idx->sizes[0]); return ncclInvalidArgument; }
+  h->T = (int)topk_idx->sizes[0];
+  h->topkIdx = (const int64_t*)topk_idx->data;
+  return ncclSuccess;
+}
+
+ncclResult_t ncclEpCreateHandle(ncclEpHandle_t* out, ncclEpGroup_t g, ncclEpLayout_t layout, const ncclEpTensor_t* topk_idx, const ncclEpLayoutInfo_t* li,
+                                const ncclEpHandleConfig_t* config, cudaStream_t stream) {
+  if (!tensorOk(topk_idx, 2)) return ncclInvalidArgument;
+  NCCLCHECK(ncclEpInitHandle(out, g, layout, config, (int)topk_idx->sizes[1], nullptr));
+  return ncclEpUpdateHandle(*out, topk_idx, li, stream);
+}
+
+ncclResult_t ncclEpHandleDestroy(ncclEpHandle_t h) {
+  if (!h) return ncclSuccess;
+  cudaDeviceSynchronize();
+  if (h->srcInfo) cudaFree(h->srcInfo);
+  if (h->expertCount) cudaFree(h->expertCount);
+  delete h;
+  return ncclSuccess;
+}
+
+ncclResult_t ncclEpDispatch(ncclEpHandle_t h, const ncclEpDispatchInputs_t* in, const ncclEpDispatchOutputs_t* out, const ncclEpLayoutInfo_t* li,
+                            const ncclEpDispatchConfig_t* config, cudaStream_t stream) {
+  if (!h || !cfgOk(in) || !cfgOk(out)) return ncclInvalidArgument;
+  if (config && !cfgOk(config)) return ncclInvalidArgument;
+  ncclEpGroup* g = h->g;
+  NCCLCHECK(devPlaneCheckStatus(g->comm));
+  if (!h->topkIdx) { WARN("ncclEpDispatch: the handle has no routing (ncclEpUpdateHandle)"); return ncclInvalidUsage; }
+  if (!tensorOk(in->tokens, 2) || in->tokens->datatype != ncclBfloat16 || (int)in->tokens->sizes[1] != g->H || (int)in->tokens->sizes[0] != h->T) {
+    WARN("ncclEpDispatch: input tokens must be bf16 [%d, %d]", h->T, g->H);
+    return ncclInvalidArgument;
+  }
+  if (!tensorOk(out->tokens, 3)) { WARN("ncclEpDispatch: output tokens must be [local experts, capacity, hidden]"); return ncclInvalidArgument; }
+  const bool fp8 = out->scales != nullptr;
+  const size_t cap = (size_t)g->n * g->maxTokens;
+  if ((int)out->tokens->sizes[0] != g->El || out->tokens->sizes[1] != cap || (int)out->tokens->sizes[2] != g->H ||
+      out->tokens->datatype != (fp8 ? ncclFloat8e4m3 : ncclBfloat16)) {
+    WARN("ncclEpDispatch: output tokens must be %s [%d, %zu, %d]", fp8 ? "fp8 e4m3" : "bf16", g->El, cap, g->H);
+    return ncclInvalidArgument;
+  }
+  if (fp8 && (!tensorOk(out->scales, 3) || out->scales->datatype != ncclFloat32)) return ncclInvalidArgument;
+  if (in->topk_weights) {
+    if (!tensorOk(in->topk_weights, 2) || in->topk_weights->datatype != ncclFloat32) return ncclInvalidArgument;
+    h->topkW = (const float*)in->topk_weights->data;
+  }
+  EpArgs a;
+  fillEpArgs(g, &a);
+  const int me = g->comm->rank;
+  a.topk = h->K;
+  a.fp8 = fp8;
+  a.numTokens[me] = h->T;
+  a.x[me] = (const __nv_bfloat16*)in->tokens->data;
+  a.topkIdx[me] = h->topkIdx;
+  a.topkW[me] = h->topkW;
+  a.outTokens[me] = out->tokens->data;
+  a.outScales[me] = fp8 ? (float*)out->scales->data : nullptr;
+  a.expertCount[me] = h->expertCount;
+  a.srcInfo[me] = h->srcInfo;
+  int ctas = g->cfg.max_num_sms ? (int)std::min<unsigned>(g->cfg.max_num_sms, (unsigned)g->smCount) : g->smCount;
+  NCCLCHECK(launchEp(epDispatchKernelFn(), &a, ctas, 1, dispatchSmem(g->H, fp8), stream, false));
+  if (g->comm->devPlane) g->comm->devPlane->launches++;
+  if (li && li->expert_counters && li->expert_counters->data)
+    CUDACHECK(cudaMemcpyAsync(li->expert_counters->data, h->expertCount, (size_t)g->El * sizeof(int), cudaMemcpyDeviceToDevice, stream));
+  return ncclSuccess;
+}
+
+ncclResult_t ncclEpCombine(ncclEpHandle_t h, const ncclEpCombineInputs_t* in, const ncclEpCombineOutputs_t* out, const ncclEpCombineConfig_t* config, cudaStream_t stream) {
+  if (!h || !cfgOk(in) || !cfgOk(out)) return ncclInvalidArgument;
+  if (config && !cfgOk(config)) return ncclInvalidArgument;
+  ncclEpGroup* g = h->g;
+  NCCLCHECK(devPlaneCheckStatus(g->comm));
+  const size_t cap = (size_t)g->n * g->maxTokens;
+  if (!tensorOk(in->tokens, 3) || in->tokens->datatype != ncclBfloat16 || (int)in->tokens->sizes[0] != g->El || in->tokens->sizes[1] != cap || (int)in->tokens->sizes[2] != g->H) {
+    WARN("ncclEpCombine: input tokens must be bf16 [%d, %zu, %d]", g->El, cap, g->H);
+    return ncclInvalidArgument;
+  }
+  if (!tensorOk(out->tokens, 2) || out->tokens->datatype != ncclBfloat16 || (int)out->tokens->sizes[0] != h->T || (int)out->tokens->sizes[1] != g->H) {
+    WARN("ncclEpCombine: output tokens must be bf16 [%d, %d]", h->T, g->H);
+    return ncclInvalidArgument;
+  }
+  const float* weights = h->topkW;
+  if (in->topk_weights && in->topk_weights->data) weights = (const float*)in->topk_weights->data;
+  if (!weights) { WARN("ncclEpCombine: no top-k weights were given (dispatch inputs or combine inputs)"); return ncclInvalidUsage; }
+  EpArgs a;
+  fillEpArgs(g, &a);
+  const int me = g->comm->rank;
+  a.topk = h->K;
+  a.numTokens[me] = h->T;
+  a.x[me] = (const __nv_bfloat16*)in->tokens->data;
+  a.topkIdx[me] = h->topkIdx;
+  a.topkW[me] = weights;
+  a.outTokens[me] = out->tokens->data;
+  a.expertCount[me] = h->expertCount;
+  a.srcInfo[me] = h->srcInfo;
+  int ctas = g->cfg.max_num_sms ? (int)std::min<unsigned>(g->cfg.max_num_sms, (unsigned)g->smCount) : g->smCount;
+  NCCLCHECK(launchEp(epCombineKernelFn(), &a, ctas, 1, 0, stream, false));
+  if (g->comm->devPlane) g->comm->devPlane->launches++;
+  return ncclSuccess;
+}
+
+ncclResult_t ncclEpComplete(ncclEpHandle_t h, const ncclEpCompleteConfig_t*, cudaStream_t) {
+  // dispatch and combine always run both phases in one kernel; nothing is left pending
+  return h ? ncclSuccess : ncclInvalidArgument;
+}
+
+ncclResult_t ncclEpMaskQuery(ncclEpGroup_t g, int* mask_status, cudaStream_t) {
+  if (!g || !mask_status) return ncclInvalidArgument;
+  for (int r = 0; r < g->n; ++r) mask_status[r] = 0;   // no rank is masked out
+  return ncclSuccess;
+}
+ncclResult_t ncclEpMaskUpdate(ncclEpGroup_t g, const int* mask, cudaStream_t) {
+  if (!g || !mask) return ncclInvalidArgument;
+  for (int r = 0; r < g->n; ++r) if (mask[r]) { WARN("ncclEpMaskUpdate: masking ranks out is not implemented"); return ncclInvalidUsage; }
+  return ncclSuccess;
+}
+ncclResult_t ncclEpMaskClean(ncclEpGroup_t g, cudaStream_t) { return g ? ncclSuccess : ncclInvalidArgument; }
+
+ncclResult_t ncclEpGetAsyncError(ncclEpGroup_t g, int* error_out) {
+  if (!g || !error_out) return ncclInvalidArgument;
+  ncclResult_t r = devPlaneCheckStatus(g->comm);
+  if (r != ncclSuccess) g->lastError = (int)r;
+  *error_out = g->lastError;
+  return ncclSuccess;
+}
+ncclResult_t ncclEpErrorClear(ncclEpGroup_t g) {
+  if (!g) return ncclInvalidArgument;
+  g->lastError = 0;
+  if (g->comm->devStatus) for (int i = 0; i < 4; ++i) g->comm->devStatus[i] = 0;
+  return ncclSuccess;
+}
+
+// --------------------------------------------------------------------------- single-GPU emulation
+struct EpEmu {
+  int n, E, El, K, H, maxTokens;
+  char* recv[kMaxRanks];
+  char* ctl[kMaxRanks];
+  char* comb[kMaxRanks];
+  uint32_t* state[kMaxRanks];
+  uint32_t* status[kMaxRanks];
+  int2* srcInfo[kMaxRanks];
+  int* counts[kMaxRanks];
+};
+
+void* b200EpEmuCreate(int n, int E, int K, int H, int maxTokens) {
+  if (n < 1 || n > kMaxRanks || E % n || H % 128) return nullptr;
+  EpEmu* e = new EpEmu;
+  memset(e, 0, sizeof(*e));
+  e->n = n; e->E = E; e->El = E / n; e->K = K; e->H = H; e->maxTokens = maxTokens;
+  size_t zone = (size_t)e->El * n * maxTokens * epSlotBytes(H, 0);
+  size_t comb = (size_t)maxTokens * K * H * 2;
+  for (int r = 0; r < n; ++r) {
+    bool ok = cudaMalloc(&e->recv[r], 2 * zone) == cudaSuccess && cudaMalloc(&e->ctl[r], ctlBytes(e->El, n)) == cudaSuccess &&
+              cudaMalloc(&e->comb[r], 2 * comb) == cudaSuccess && cudaMalloc(&e->state[r], (8 + E) * 4) == cudaSuccess &&
+              cudaMalloc(&e->status[r], 16) == cudaSuccess && cudaMalloc(&e->srcInfo[r], (size_t)e->El * n * maxTokens * sizeof(int2)) == cudaSuccess &&
+              cudaMalloc(&e->counts[r], e->El * sizeof(int)) == cudaSuccess;
+    if (!ok) return nullptr;
+    cudaMemset(e->ctl[r], 0, ctlBytes(e->El, n));
+    cudaMemset(e->state[r], 0, (8 + E) * 4);
+    cudaMemset(e->status[r], 0, 16);
+  }
+  cudaDeviceSynchronize();
+  return e;
+}
+void b200EpEmuDestroy(void* ctx) {
+  EpEmu* e = (EpEmu*)ctx;
+  if (!e) return;
+  for (int r = 0; r < e->n; ++r) { cudaFree(e->recv[r]); cudaFree(e->ctl[r]); cudaFree(e->comb[r]); cudaFree(e->state[r]); cudaFree(e->status[r]); cudaFree(e->srcInfo[r]); cudaFree(e->counts[r]); }
+  delete e;
+}
+static void emuArgs(EpEmu* e, EpArgs* a) {
+  memset(a, 0, sizeof(*a));
+  a->nRanks = e->n; a->emu = 1; a->numExperts = e->E; a->expertsPerRank = e->El; a->topk = e->K; a->hidden = e->H; a->maxTokens = e->maxTokens;
+  for (int r = 0; r < e->n; ++r) {
+    a->recvBuf[r] = e->recv[r];
+    a->recvCount[r] = (unsigned long long*)e->ctl[r];
+    a->combFlag[r] = (unsigned long long*)e->ctl[r] + (size_t)2 * e->El * e->n;
+    a->combBuf[r] = e->comb[r];
+    a->state[r] = e->state[r];
+    a->sync.status[r] = e->status[r];
+    a->srcInfo[r] = e->srcInfo[r];
+    a->expertCount[r] = e->counts[r];
+  }
+  a->sync.timeoutNs = 3000000000ull;
+}
+int b200EpEmuDispatch(void* ctx, int fp8, const int* numTokens, void** x, void** idx, void** outTokens, void** outScales, int** countsOut, int ctas) {
+  EpEmu* e = (EpEmu*)ctx;
+  EpArgs a;
+  emuArgs(e, &a);
+  a.fp8 = fp8;
+  for (int r = 0; r < e->n; ++r) {
+    a.numTokens[r] = numTokens[r];
+    a.x[r] = (const __nv_bfloat16*)x[r];
+    a.topkIdx[r] = (const int64_t*)idx[r];
+    a.outTokens[r] = outTokens[r];
+    a.outScales[r] = outScales ? (float*)outScales[r] : nullptr;
+  }
+  ncclResult_t res = launchEp(epDispatchKernelFn(), &a, ctas, e->n, dispatchSmem(e->H, fp8), 0, true);
+  if (res != ncclSuccess) return res;
+  if (cudaDeviceSynchronize() != cudaSuccess) return ncclUnhandledCudaError;
+  for (int r = 0; r < e->n; ++r) cudaMemcpy(countsOut[r], e->counts[r], e->El * sizeof(int), cudaMemcpyDeviceToHost);
+  uint32_t st = 0;
+  for (int r = 0; r < e->n; ++r) { cudaMemcpy(&st, e->status[r], 4, cudaMemcpyDeviceToHost); if (st) return ncclTimeout; }
+  return 0;
+}
+int b200EpEmuCombine(void* ctx, const int* numTokens, void** y, void** idx, void** weights, void** out, int ctas) {
+  EpEmu* e = (EpEmu*)ctx;
+  EpArgs a;
+  emuArgs(e, &a);
+  for (int r = 0; r < e->n; ++r) {
+    a.numTokens[r] = numTokens[r];
+    a.x[r] = (const __nv_bfloat16*)y[r];
+    a.topkIdx[r] = (const int64_t*)idx[r];
+    a.topkW[r] = (const float*)weights[r];
+    a.outTokens[r] = out[r];
+  }
+  ncclResult_t res = launchEp(epCombineKernelFn(), &a, ctas, e->n, 0, 0, true);
+  if (res != ncclSuccess) return res;
+  if (cudaDeviceSynchronize() != cudaSuccess) return ncclUnhandledCudaError;
+  uint32_t st = 0;
+  for (int r = 0; r < e->n; ++r) { cudaMemcpy(&st, e->status[r], 4, cudaMemcpyDeviceToHost); if (st) return ncclTimeout; }
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,297 @@
+// Tensor-parallel GEMM kernels for sm_100a: C[M,N] = A[M,K] * W[N,K]^T in bf16 with fp32
+// accumulation in tensor memory, fused with the collective that follows or precedes it.
+//
+// One persistent CTA per SM, 192 threads in three roles:
+//   warp 0      TMA producer: streams 128x64 A tiles and 256x64 W tiles (128-byte swizzle) through
+//               a 4-stage shared-memory ring, one elected thread, mbarrier transaction counts.
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma (128x256x16, cta_group::1) into
+//               one of two 256-column TMEM accumulators; tcgen05.commit releases ring stages and
+//               publishes finished accumulators.
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (each warp owns 32 TMEM lanes = 32 rows),
+//               then, depending on the mode,
+//                 STORE      convert to bf16 and store C;
+//                 REDUCE     GEMM -> reduce-scatter: add the fp32 partial tile straight into the
+//                            accumulation buffer of the rank that owns those rows, over NVLink,
+//                            with 16-byte red.add; tiles are visited owner by owner, starting with
+//                            the next rank, so every step each GPU receives from exactly one peer.
+//   GATHER mode all-gather -> GEMM: extra "comm" CTAs pull the other ranks' A rows from their
+//               windows into the local A buffer, 128-row block by block, and publish a flag per
+//               block; the TMA producer waits for the flag of the block it needs. Blocks are
+//               fetched in the order the GEMM consumes them (own rows first, then rank+1, ...).
+// No TMA load uses cluster multicast and no TMA load touches peer memory: remote data reaches this
+// GPU through plain peer loads / red.add issued by SM threads.
+// Every wait (mbarrier, flag, cross-GPU barrier) is bounded; on expiry the kernel records a status,
+// drains its outstanding TMA copies, frees its tensor memory and returns.
+// The reference has no GEMM kernels; the comparison point is its reduce-scatter / all-gather plus a
+// separate GEMM.
+#include "gemm_sm100.cuh"
+
+#include "../kernels/common.cuh"
+#include "tp.h"
+
+namespace b200 {
+
+using namespace sm100;
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int kTpThreads = 192;
+constexpr uint32_t kStageABytes = BM * BK * 2, kStageBBytes = BN * BK * 2;
+constexpr uint32_t kStageBytes = kStageABytes + kStageBBytes;
+constexpr uint32_t kTmemCols = 512;
+constexpr size_t kTpSmemBytes = 1024 + (size_t)STAGES * kStageBytes + 256;
+
+struct TileCoord { int mBlk, nBlk, owner; };
+
+__device__ __forceinline__ TileCoord tileOf(const TpGemmArgs& a, int t) {
+  const int tilesN = a.N / BN;
+  TileCoord c;
+  if (a.mode == TP_MODE_STORE || a.nRanks == 1) {
+    c.mBlk = t / tilesN;
+    c.nBlk = t % tilesN;
+    c.owner = a.rank;
+    if (a.mode == TP_MODE_REDUCE) c.owner = 0;
+    return c;
+  }
+  const int tilesMPerRank = a.M / a.nRanks / BM;
+  const int per = tilesMPerRank * tilesN;
+  const int step = t / per, j = t % per;
+  const int who = a.mode == TP_MODE_REDUCE ? (a.rank + 1 + step) % a.nRanks : (a.rank + step) % a.nRanks;
+  c.owner = who;
+  c.mBlk = who * tilesMPerRank + j / tilesN;
+  c.nBlk = j % tilesN;
+  return c;
+}
+
+__global__ void __launch_bounds__(kTpThreads, 1)
+tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ TpGemmArgs a) {
+  extern __shared__ uint8_t smemRaw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);
+  uint8_t* ctrl = smem + (size_t)STAGES * kStageBytes;
+  uint64_t* fullBar = (uint64_t*)ctrl;            // [STAGES]
+  uint64_t* emptyBar = fullBar + STAGES;          // [STAGES]
+  uint64_t* accFull = emptyBar + STAGES;          // [2]
+  uint64_t* accEmpty = accFull + 2;               // [2]
+  uint32_t* tmemSlot = (uint32_t*)(accEmpty + 2);
+  volatile uint32_t* abortFlag = tmemSlot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = a.rank, n = a.nRanks;
+  const bool multi = n > 1 && a.mode != TP_MODE_STORE;
+  const bool commCta = a.mode == TP_MODE_GATHER && n > 1 && (int)blockIdx.x >= a.gemmCtas;
+
+  CtaBarrier bar;
+  bool ok = true;
+  if (multi) {
+    bar.init(a.sync, rank, n, blockIdx.x);
+    ok = bar.sync();   // REDUCE: every accumulation buffer is zeroed; GATHER: every rank's rows are in place
+  }
+
+  if (commCta) {
+    // ---- all-gather role: pull the other ranks' row blocks in consumption order
+    const int blocksPerRank = a.M / n / BM;
+    const size_t blockBytes = (size_t)BM * a.K * 2;
+    const int commIdx = blockIdx.x - a.gemmCtas, commN = gridDim.x - a.gemmCtas;
+    for (int step = 1; step < n && ok; ++step) {
+      const int src = (rank + step) % n;
+      for (int b = commIdx; b < blocksPerRank; b += commN) {
+        const int mb = src * blocksPerRank + b;
+        const char* from = (const char*)a.peerA[src] + (size_t)mb * blockBytes;
+        char* to = (char*)a.peerA[rank] + (size_t)mb * blockBytes;
+        const size_t packs = blockBytes / 16;
+        size_t i = threadIdx.x;
+        for (; i + 3 * kTpThreads < packs; i += 4 * kTpThreads) {
+          uint4 v[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) v[u] = ldStream16(from + (i + u * kTpThreads) * 16);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) st16(to + (i + u * kTpThreads) * 16, v[u]);
+        }
+        for (; i < packs; i += kTpThreads) st16(to + i * 16, ldStream16(from + i * 16));
+        // the rows were written through the generic proxy and will be read by TMA (async proxy)
+        fenceProxyAsync();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          __threadfence();
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.blockFlags + mb), "r"(a.flagEpoch) : "memory");
+        }
+      }
+    }
+    bar.sync();        // nobody reads my rows any more
+    bar.finish();
+    return;
+  }
+
+  // ---- GEMM CTA set-up
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbarInit(smemAddr(&fullBar[s]), 1); mbarInit(smemAddr(&emptyBar[s]), 1); }
+    for (int b = 0; b < 2; ++b) { mbarInit(smemAddr(&accFull[b]), 1); mbarInit(smemAddr(&accEmpty[b]), 4); }
+    *abortFlag = ok ? 0u : 1u;
+    mbarInitFence();
+    prefetchTensorMap(&tmA);
+    prefetchTensorMap(&tmB);
+  }
+  if (warp == 1) {
+    tmemAlloc(smemAddr(tmemSlot), kTmemCols);
+    tmemRelinquish();
+  }
+  tcFenceBefore();
+  __syncthreads();
+  tcFenceAfter();
+  const uint32_t tmemBase = *tmemSlot;
+
+  const int tilesN = a.N / BN;
+  const int nTiles = (a.M / BM) * tilesN;
+  const int kBlocks = a.K / BK;
+  const int gemmCtas = (a.mode == TP_MODE_GATHER && n > 1) ? a.gemmCtas : gridDim.x;
+  const uint32_t smemA0 = smemAddr(smem), smemB0 = smemA0 + STAGES * kStageABytes;
+  auto fail = [&](uint32_t kind, uint32_t what) {
+    *abortFlag = 1;
+    if (a.sync.status[rank] && ldRelaxedSys(a.sync.status[rank]) == DEV_OK) {
+      a.sync.status[rank][1] = kind;
+      a.sync.status[rank][2] = what;
+      a.sync.status[rank][3] = blockIdx.x;
+      __threadfence_system();
+      stRelaxedSys(a.sync.status[rank], DEV_TIMEOUT);
+    }
+  };
+
+  if (warp == 0) {
+    if (electOne()) {
+      uint32_t kc = 0;
+      int armedStage[STAGES];
+      for (int s = 0; s < STAGES; ++s) armedStage[s] = -1;
+      for (int t = blockIdx.x; t < nTiles && !*abortFlag; t += gemmCtas) {
+        const TileCoord tc = tileOf(a, t);
+        if (a.mode == TP_MODE_GATHER && n > 1 && tc.owner != rank) {
+          // wait until the comm CTAs have landed this block of rows
+          const uint32_t* f = a.blockFlags + tc.mBlk;
+          bool got = false;
+          for (uint32_t spin = 0; spin < (1u << 26); ++spin) {
+            uint32_t v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if ((int32_t)(v - a.flagEpoch) >= 0) { got = true; break; }
+            if (*abortFlag) break;
+          }
+          if (!got) { fail(WAIT_TILE, (uint32_t)tc.mBlk); break; }
+          fenceProxyAsync();
+        }
+        for (int kb = 0; kb < kBlocks; ++kb, ++kc) {
+          const int s = kc % STAGES;
+          const uint32_t ph = (kc / STAGES) & 1;
+          if (!mbarWait(smemAddr(&emptyBar[s]), ph ^ 1)) { fail(WAIT_TILE, 1000 + s); break; }
+          const uint32_t fb = smemAddr(&fullBar[s]);
+          mbarExpectTx(fb, kStageBytes);
+          tmaLoad2d(smemA0 + s * kStageABytes, &tmA, kb * BK, tc.mBlk * BM, fb);
+          tmaLoad2d(smemB0 + s * kStageBBytes, &tmB, kb * BK, tc.nBlk * BN, fb);
+          armedStage[s] = (int)ph;
+        }
+      }
+      if (*abortFlag) {
+        // copies already issued still write into this CTA's shared memory: wait for them (bounded)
+        for (int s = 0; s < STAGES; ++s)
+          if (armedStage[s] >= 0) mbarWait(smemAddr(&fullBar[s]), (uint32_t)armedStage[s], 1u << 20);
+      }
+    }
+  } else if (warp == 1) {
+    if (electOne()) {
+      const uint32_t idesc = umInstrBf16(BM, BN);
+      uint32_t kc = 0;
+      int it = 0;
+      for (int t = blockIdx.x; t < nTiles && !*abortFlag; t += gemmCtas, ++it) {
+        const int buf = it & 1;
+        const uint32_t aph = (it >> 1) & 1;
+        if (!mbarWait(smemAddr(&accEmpty[buf]), aph ^ 1)) { fail(WAIT_TILE, 2000 + buf); break; }
+        tcFenceAfter();
+        const uint32_t dT = tmemBase + buf * BN;
+        bool bad = false;
+        for (int kb = 0; kb < kBlocks; ++kb, ++kc) {
+          const int s = kc % STAGES;
+          const uint32_t ph = (kc / STAGES) & 1;
+          if (!mbarWait(smemAddr(&fullBar[s]), ph)) { fail(WAIT_TILE, 3000 + s); bad = true; break; }
+          tcFenceAfter();
+          const uint32_t aAddr = smemA0 + s * kStageABytes, bAddr = smemB0 + s * kStageBBytes;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            ummaBf16(dT, umDescK128(aAddr + k * UMMA_K * 2), umDescK128(bAddr + k * UMMA_K * 2), idesc, (kb | k) != 0);
+          ummaCommit(smemAddr(&emptyBar[s]));   // the stage is free once these MMAs have read it
+        }
+        if (bad) break;
+        ummaCommit(smemAddr(&accFull[buf]));    // accumulator complete
+      }
+    }
+  } else {
+    // ---- epilogue warps: TMEM lanes [32q, 32q+32) belong to the warp with warp % 4 == q
+    const int q = warp & 3;
+    int it = 0;
+    for (int t = blockIdx.x; t < nTiles && !*abortFlag; t += gemmCtas, ++it) {
+      const TileCoord tc = tileOf(a, t);
+      const int buf = it & 1;
+      const uint32_t aph = (it >> 1) & 1;
+      if (!mbarWait(smemAddr(&accFull[buf]), aph)) { if (lane == 0) fail(WAIT_TILE, 4000 + buf); break; }
+      tcFenceAfter();
+      const int row = tc.mBlk * BM + q * 32 + lane;
+      const uint32_t tBase = tmemBase + ((uint32_t)(q * 32) << 16) + buf * BN;
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmemLd32(tBase + c * 32, r);
+        tmemLdWait();
+        const int col = tc.nBlk * BN + c * 32;
+        if (a.mode == TP_MODE_REDUCE) {
+          const int rowsPerRank = a.M / n;
+          float* dst = a.accum[tc.owner] + (size_t)(row - tc.owner * rowsPerRank) * a.N + col;
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            redAddF32x4(dst + v * 4, __uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+        } else {
+          __nv_bfloat16* dst = (__nv_bfloat16*)a.C + (size_t)row * a.ldc + col;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[8 * v]), __uint_as_float(r[8 * v + 1]));
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+            o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1; o.z = *(uint32_t*)&p2; o.w = *(uint32_t*)&p3;
+            *(uint4*)(dst + v * 8) = o;
+          }
+        }
+      }
+      tcFenceBefore();
+      __syncwarp();
+      if (lane == 0) mbarArrive(smemAddr(&accEmpty[buf]));
+    }
+  }
+
+  // ---- teardown: everybody meets, tensor memory goes back, then the cross-GPU barrier
+  tcFenceBefore();
+  __syncthreads();
+  if (warp == 1) {
+    tcFenceAfter();
+    tmemDealloc(tmemBase, kTmemCols);
+  }
+  if (multi) {
+    bar.sync();      // REDUCE: every partial sum has landed in its owner's buffer
+    bar.finish();
+  }
+}
+
+// out[i] = bf16(acc[i]): the fp32 accumulation buffer of GEMM -> reduce-scatter becomes the output.
+__global__ void tpConvertKernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ out, size_t count) {
+  size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  const size_t stride = (size_t)gridDim.x * blockDim.x * 8;
+  for (; i + 7 < count; i += stride) {
+    float4 a = *(const float4*)(acc + i), b = *(const float4*)(acc + i + 4);
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
+    uint4 o;
+    o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1; o.z = *(uint32_t*)&p2; o.w = *(uint32_t*)&p3;
+    *(uint4*)(out + i) = o;
+  }
+}
+
+const void* tpGemmKernelFn() { return (const void*)tpGemmKernel; }
+const void* tpConvertKernelFn() { return (const void*)tpConvertKernel; }
+size_t tpGemmSmemBytes() { return kTpSmemBytes; }
+int tpGemmThreads() { return kTpThreads; }
+
+}  // namespace b200
