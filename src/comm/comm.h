@@ -87,7 +87,7 @@ struct HostPlane;     // host/hostcoll.cc
 struct DevicePlane;   // comm/device_plane.h
 struct Proxy;         // transport/proxy.h
 struct RasState;
-struct TopoSystem;
+struct TopoState;
 struct TunerState;
 struct ProfilerState;
 struct MemManager;
@@ -124,7 +124,7 @@ struct ncclComm {
   b200::DevicePlane* devPlane = nullptr;
   b200::SymRuntime* sym = nullptr;
   b200::Proxy* proxy = nullptr;
-  b200::TopoSystem* topo = nullptr;
+  b200::TopoState* topo = nullptr;
   b200::TunerState* tuner = nullptr;
   b200::MemManager* memMgr = nullptr;
 

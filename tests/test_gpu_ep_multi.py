@@ -1,0 +1,59 @@
+"""Expert-parallel dispatch / combine across real GPUs through the ncclEp* API."""
+import pytest
+
+torch = pytest.importorskip("torch")
+
+from mp_util import run_ranks  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+def _ep_rank(rank, nranks, uid, E, K, H, T):
+    import torch
+    torch.cuda.set_device(rank)
+    from nccl_b200 import Communicator
+    from nccl_b200.ops.ep import ExpertParallel
+    comm = Communicator(nranks, rank, uid)
+    ep = ExpertParallel(comm, E, T, H)
+    res = {}
+    for rep in range(3):
+        g = torch.Generator().manual_seed(100 * rep + rank)
+        x = torch.randn(T, H, generator=g).bfloat16().cuda()
+        idx = torch.rand(T, E, generator=g).topk(K, dim=1).indices.to(torch.int64).cuda()
+        w = torch.softmax(torch.randn(T, K, generator=g), dim=1).cuda()
+        toks, scales, counts = ep.dispatch(x, idx, w, fp8=bool(rep % 2))
+        torch.cuda.synchronize()
+        if rep % 2:
+            y = (toks.view(torch.float8_e4m3fn).float().view(ep.El, ep.cap, H // 128, 128) * scales.unsqueeze(-1)).view(ep.El, ep.cap, H).bfloat16()
+        else:
+            y = toks
+        # expert e multiplies by (e + 1)
+        for el in range(ep.El):
+            y[el] *= float(rank * ep.El + el + 1)
+        out = ep.combine(y.contiguous())
+        torch.cuda.synchronize()
+        scale = torch.zeros(T, 1, device="cuda")
+        for k in range(K):
+            scale[:, 0] += w[:, k] * (idx[:, k] + 1).float()
+        ref = x.float() * scale
+        res["err%d" % rep] = float(((out.float() - ref).abs() / (ref.abs() + 1.0)).max())
+        res["count%d" % rep] = int(counts.sum())
+    assert comm.async_error() == 0
+    ep.destroy()
+    comm.destroy()
+    return res
+
+
+@pytest.mark.parametrize("E,K,H,T", [(16, 2, 256, 32), (64, 8, 1024, 128)])
+def test_ep_roundtrip(E, K, H, T):
+    n = min(torch.cuda.device_count() if torch.cuda.is_available() else 0, 8)
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    if E % n:
+        pytest.skip("experts do not divide over the ranks")
+    res = run_ranks(_ep_rank, n, args=(E, K, H, T), timeout=300)
+    for rep in range(3):
+        assert sum(res[r]["count%d" % rep] for r in range(n)) == n * T * K
+        tol = 0.12 if rep % 2 else 0.03
+        for r in range(n):
+            assert res[r]["err%d" % rep] < tol, (rep, r, res[r])
