@@ -1,0 +1,154 @@
+/*
+ * Device API, core types: device communicator, windows, teams and pointer getters.
+ * A kernel that includes <nccl_device.h> can address the memory of every rank of its load/store
+ * team (the ranks whose memory is mapped here, NVLink domain) through registered windows, use the
+ * NVLink-multicast alias of a window, and synchronise with the other ranks.
+ * Reference parity: src/include/nccl_device/core.h (:78-142 requirements, :175-192 properties,
+ * :210-255 teams, :267-275 pointer getters), impl/core__types.h.
+ */
+#ifndef NCCL_DEVICE_CORE_H_
+#define NCCL_DEVICE_CORE_H_
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "nccl.h"
+
+#define NCCL_DEVICE_MAX_LSA 8
+
+/* Device-visible description of a registered window (ncclWindow_t points to one of these). */
+struct ncclWindow_vidmem {
+  void* peerPtr[NCCL_DEVICE_MAX_LSA]; /* peerPtr[p]: rank p's part of the window as mapped on this GPU */
+  void* mcPtr;                        /* multicast alias of the window, or NULL */
+  size_t size;
+  int rank, nRanks;
+  void* userPtr;
+  struct ncclWindow_vidmem* devSelf;  /* device copy of this struct: what kernels receive */
+  void* hostState;
+  unsigned long long magic;
+};
+
+typedef struct {
+  int nRanks;
+  int rank;
+  int stride;
+} ncclTeam_t;
+
+/* Resources a kernel asks for when the device communicator is created. */
+typedef struct ncclDevResourceRequirements {
+  struct ncclDevResourceRequirements* next;
+  size_t bufferSize;
+  size_t bufferAlign;
+  uint32_t* outBufferHandle;   /* receives the byte offset of the buffer inside the resource window */
+  int ginSignalCount;
+  int ginCounterCount;
+  uint32_t* outGinSignalStart;
+  uint32_t* outGinCounterStart;
+} ncclDevResourceRequirements_t;
+
+typedef struct ncclTeamRequirements {
+  struct ncclTeamRequirements* next;
+  ncclTeam_t team;
+  int multimem;
+  uint32_t* outMultimemHandle;
+} ncclTeamRequirements_t;
+
+typedef struct {
+  size_t size;
+  unsigned int magic;
+  unsigned int version;
+  ncclDevResourceRequirements_t* resourceRequirementsList;
+  ncclTeamRequirements_t* teamRequirementsList;
+  int lsaMultimem;             /* want the multicast alias of the resource window */
+  int barrierCount;            /* hybrid (LSA + rail) barriers */
+  int lsaBarrierCount;         /* barriers among the load/store team, one per CTA that synchronises */
+  int railGinBarrierCount;
+  int lsaLLA2ABlockCount;      /* CTAs that run low-latency all-to-all sessions */
+  int lsaLLA2ASlotCount;       /* 16-byte slots per CTA and peer */
+  int ginForceEnable;
+  int ginContextCount;
+  int ginSignalCount;
+  int ginCounterCount;
+  int ginConnectionType;
+  int ginExclusiveContexts;
+  int ginQueueDepth;
+  int ginTrafficClass;
+  int worldGinBarrierCount;
+  int ginStrongSignalsRequired;
+  int ginVaSignalsRequired;
+} ncclDevCommRequirements_t;
+
+#define NCCL_DEV_COMM_REQUIREMENTS_MAGIC 0xdec0de01u
+#define NCCL_DEV_COMM_REQUIREMENTS_INITIALIZER \
+  { sizeof(ncclDevCommRequirements_t), NCCL_DEV_COMM_REQUIREMENTS_MAGIC, NCCL_VERSION_CODE, NULL, NULL, 0, 0, 0, 0, 0, 0, 0, 4, 0, 0, 0, 0, 0, 0, 0, 0, 0 }
+
+typedef struct {
+  size_t size;
+  unsigned int magic;
+  unsigned int version;
+  int rank;
+  int nRanks;
+  int cudaDev;
+  int nvmlDev;
+  int deviceApiSupport;
+  int multimemSupport;
+  int ginType;
+  int nLsaTeams;
+  int hostRmaSupport;
+  int railedGinType;
+} ncclCommProperties_t;
+
+#define NCCL_COMM_PROPERTIES_INITIALIZER \
+  { sizeof(ncclCommProperties_t), 0xdec0de02u, NCCL_VERSION_CODE, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0 }
+
+/* Passed by value to kernels. */
+typedef struct ncclDevComm {
+  int rank, nRanks;
+  int lsaRank, lsaSize;
+  struct ncclWindow_vidmem resource;   /* the communicator's resource window (barriers, LL slots, user buffers) */
+  uint32_t lsaBarrierOffset;           /* byte offsets inside the resource window */
+  int lsaBarrierCount;
+  uint32_t llA2AOffset;
+  int llA2ABlockCount, llA2ASlotCount;
+  uint32_t* barrierEpochs;             /* private device words: one epoch per LSA barrier */
+  uint32_t* llA2AEpochs;               /* private device words: one epoch per LLA2A block */
+  const uint32_t* abortFlag;           /* host-mapped: non-zero once the communicator is aborted */
+  unsigned long long timeoutCycles;    /* default budget of device-side waits */
+} ncclDevComm_t;
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+ncclResult_t ncclCommQueryProperties(ncclComm_t comm, ncclCommProperties_t* props);
+ncclResult_t ncclDevCommCreate(ncclComm_t comm, const ncclDevCommRequirements_t* reqs, ncclDevComm_t* devComm);
+ncclResult_t ncclDevCommDestroy(ncclComm_t comm, const ncclDevComm_t* devComm);
+/* Host-side pointer getters: where rank `peer`'s part of the window is mapped in this process. */
+ncclResult_t ncclGetLsaDevicePointer(ncclWindow_t win, size_t offset, int peer, void** out);
+ncclResult_t ncclGetLsaMultimemDevicePointer(ncclWindow_t win, size_t offset, void** out);
+/* The device copy of a window handle, to pass to kernels. */
+ncclResult_t ncclWinGetDeviceHandle(ncclWindow_t win, ncclWindow_t* devHandle);
+#ifdef __cplusplus
+}
+#endif
+
+#if defined(__CUDACC__)
+__host__ __device__ inline ncclTeam_t ncclTeamWorld(const ncclDevComm_t& c) { ncclTeam_t t = {c.nRanks, c.rank, 1}; return t; }
+__host__ __device__ inline ncclTeam_t ncclTeamLsa(const ncclDevComm_t& c) { ncclTeam_t t = {c.lsaSize, c.lsaRank, 1}; return t; }
+__host__ __device__ inline ncclTeam_t ncclTeamRail(const ncclDevComm_t& c) { ncclTeam_t t = {c.nRanks / c.lsaSize, c.rank / c.lsaSize, c.lsaSize}; return t; }
+__host__ __device__ inline int ncclTeamRankToWorld(const ncclDevComm_t& c, ncclTeam_t t, int r) { return c.rank + (r - t.rank) * t.stride; }
+
+__device__ inline void* ncclGetLocalPointer(ncclWindow_t w, size_t offset) { return (char*)w->peerPtr[w->rank] + offset; }
+__device__ inline void* ncclGetLsaPointer(ncclWindow_t w, size_t offset, int lsaPeer) { return (char*)w->peerPtr[lsaPeer] + offset; }
+__device__ inline void* ncclGetPeerPointer(ncclWindow_t w, size_t offset, ncclTeam_t team, int peer) {
+  return (char*)w->peerPtr[w->rank + (peer - team.rank) * team.stride] + offset;
+}
+__device__ inline void* ncclGetMultimemPointer(ncclWindow_t w, size_t offset) { return w->mcPtr ? (char*)w->mcPtr + offset : (void*)0; }
+__device__ inline void* ncclGetLsaMultimemPointer(ncclWindow_t w, size_t offset, const ncclDevComm_t&) { return ncclGetMultimemPointer(w, offset); }
+/* Pointers into the communicator's own resource window. */
+__device__ inline void* ncclGetResourceBufferLocalPointer(const ncclDevComm_t& c, uint32_t handle) { return (char*)c.resource.peerPtr[c.lsaRank] + handle; }
+__device__ inline void* ncclGetResourceBufferLsaPointer(const ncclDevComm_t& c, uint32_t handle, int peer) { return (char*)c.resource.peerPtr[peer] + handle; }
+__device__ inline void* ncclGetResourceBufferMultimemPointer(const ncclDevComm_t& c, uint32_t handle) { return c.resource.mcPtr ? (char*)c.resource.mcPtr + handle : (void*)0; }
+#endif
+
+#endif

@@ -1,0 +1,55 @@
+/*
+ * Barrier among the ranks of the load/store team, executed by one cooperative group per rank.
+ * Each barrier index owns one inbox word per peer in every rank's resource window and a private
+ * epoch; arrive() release-stores the new epoch into every peer's inbox, wait() polls the local
+ * inbox. Waits are bounded: after timeoutCycles (or when the communicator is aborted) they give
+ * up and return ncclTimeout, leaving the kernel free to finish.
+ * Reference parity: src/include/nccl_device/lsa_barrier.h, impl/lsa_barrier__funcs.h:55-175.
+ */
+#ifndef NCCL_DEVICE_LSA_BARRIER_H_
+#define NCCL_DEVICE_LSA_BARRIER_H_
+#include "coop.h"
+#include "utility.h"
+#if defined(__CUDACC__)
+template <typename Coop>
+struct ncclLsaBarrierSession {
+  Coop coop;
+  const ncclDevComm_t& comm;
+  int index;
+  uint32_t epoch;
+  __device__ ncclLsaBarrierSession(Coop coop_, const ncclDevComm_t& c, ncclTeam_t /*lsa team*/, int barrierIndex)
+      : coop(coop_), comm(c), index(barrierIndex), epoch(c.barrierEpochs[barrierIndex]) {}
+  __device__ uint32_t* inbox(int owner, int src) const {
+    return (uint32_t*)((char*)comm.resource.peerPtr[owner] + comm.lsaBarrierOffset) + (size_t)index * NCCL_DEVICE_MAX_LSA + src;
+  }
+  /* Everything the group wrote before arrive() is visible to a peer after its matching wait(). */
+  __device__ void arrive() {
+    coop.sync();
+    ++epoch;
+    for (int p = coop.thread_rank(); p < comm.lsaSize; p += coop.size()) {
+      if (p == comm.lsaRank) continue;
+      nccl_device::fenceAcqRelSys();
+      nccl_device::stReleaseSys(inbox(p, comm.lsaRank), epoch);
+    }
+  }
+  __device__ ncclResult_t wait(unsigned long long timeoutCycles = 0) {
+    const unsigned long long budget = timeoutCycles ? timeoutCycles : comm.timeoutCycles;
+    ncclResult_t res = ncclSuccess;
+    for (int p = coop.thread_rank(); p < comm.lsaSize; p += coop.size()) {
+      if (p == comm.lsaRank) continue;
+      const uint32_t* w = inbox(comm.lsaRank, p);
+      const long long start = clock64();
+      unsigned spins = 0;
+      while (nccl_device::rollingDiff(nccl_device::ldAcquireSys(w), epoch) < 0) {
+        if ((++spins & 0xff) == 0 && ((unsigned long long)(clock64() - start) >= budget || ncclTestAbort(comm))) { res = ncclTimeout; break; }
+      }
+    }
+    coop.sync();
+    return res;
+  }
+  __device__ ncclResult_t sync(unsigned long long timeoutCycles = 0) { arrive(); return wait(timeoutCycles); }
+  /* Stores the epoch for the next kernel; call once, by the last user of this index in the kernel. */
+  __device__ void finish() { if (coop.thread_rank() == 0) comm.barrierEpochs[index] = epoch; }
+};
+#endif
+#endif
