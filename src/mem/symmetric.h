@@ -9,17 +9,9 @@
 #include "../kernels/args.h"
 #include "allocator.h"
 
-// Device-visible description of a window (also what ncclWindow_t points to on the host).
-struct ncclWindow_vidmem {
-  void* peerPtr[b200::kMaxRanks];   // peerPtr[p]: start of rank p's part of the window, mapped here
-  void* mcPtr;                      // multicast alias of the window, or null
-  size_t size;
-  int rank, nRanks;
-  void* userPtr;
-  struct ncclWindow_vidmem* devSelf;   // address of the device copy
-  void* hostState;                     // b200::SymWindow*
-  unsigned long long magic;
-};
+// ncclWindow_vidmem (what ncclWindow_t points to, on the host and on the device) is part of the public device API.
+#include "nccl_device/core.h"
+static_assert(NCCL_DEVICE_MAX_LSA == b200::kMaxRanks, "window peer table and kernel rank limit must agree");
 
 namespace b200 {
 
