@@ -239,6 +239,8 @@ static ncclResult_t progressOnce(SockOpKind kind, Socket* s, void* p, int n, int
   return ncclSuccess;
 }
 
+ncclResult_t sockProgress(SockOpKind kind, Socket* s, void* p, int n, int* off) { return progressOnce(kind, s, p, n, off, nullptr); }
+
 static ncclResult_t waitAll(SockOp* ops, int n) {
   uint64_t lastProgress = nowNs();
   int64_t timeoutMs = paramSocketTimeoutMs();

@@ -59,6 +59,8 @@ ncclResult_t sockSend(Socket* s, const void* p, int n);
 ncclResult_t sockRecv(Socket* s, void* p, int n);
 ncclResult_t sockTryRecv(Socket* s, void* p, int n, int* closed, bool blocking);
 ncclResult_t sockSendRecv(Socket* sendSock, const void* sp, int sn, Socket* recvSock, void* rp, int rn);
+// One non-blocking attempt: moves what the kernel accepts right now and advances *off (never waits).
+ncclResult_t sockProgress(SockOpKind kind, Socket* s, void* p, int n, int* off);
 ncclResult_t sockMultiOp(SockOp* ops, int n);  // progresses all ops concurrently until all complete
 ncclResult_t sockClose(Socket* s, bool waitPeer = false);
 ncclResult_t sockShutdown(Socket* s);

@@ -1,0 +1,65 @@
+// Plugin loading and the glue between the core and each plugin kind.
+// Reference parity: src/plugin/plugin_open.cc (library names and search), src/plugin/net.cc,
+// tuner.cc, profiler.cc, env.cc.
+#pragma once
+#include <string>
+
+#include "../comm/comm.h"
+#include "plugin/nccl_env.h"
+#include "plugin/nccl_net.h"
+#include "plugin/nccl_profiler.h"
+#include "plugin/nccl_tuner.h"
+
+namespace b200 {
+
+enum PluginKind { PLUGIN_NET = 0, PLUGIN_TUNER = 1, PLUGIN_PROFILER = 2, PLUGIN_ENV = 3, PLUGIN_KINDS = 4 };
+
+// dlopen()s the library chosen by the kind's environment variable (NCCL_NET_PLUGIN,
+// NCCL_TUNER_PLUGIN, NCCL_PROFILER_PLUGIN, NCCL_ENV_PLUGIN):
+//   unset        -> "libnccl-<kind>.so" if the dynamic loader finds it, else no plugin
+//   "none"       -> no plugin
+//   has '/' or ".so" -> that file
+//   NAME         -> "libnccl-<kind>-NAME.so"
+// Returns nullptr when there is nothing to load. `resolved` receives the name that was opened.
+void* pluginOpen(PluginKind kind, std::string* resolved);
+void* pluginSymbol(void* lib, const char* name);
+const char* pluginKindName(PluginKind kind);
+
+void pluginLogger(ncclDebugLogLevel level, unsigned long flags, const char* file, int line, const char* fmt, ...);
+
+// ---- env plugin: consulted by every parameter read (core/param.cc)
+void envPluginInit();                       // idempotent; called before the first parameter is read
+const char* envPluginGet(const char* name); // value from the plugin, or from getenv() when none is loaded
+void envPluginFinalize();
+
+// ---- tuner plugin: per communicator
+struct TunerState {
+  void* lib = nullptr;
+  ncclTuner_v6_t* v6 = nullptr;
+  ncclTuner_v5_t* v5 = nullptr;
+  void* ctx = nullptr;
+  std::string name;
+};
+ncclResult_t tunerLoad(ncclComm* comm);     // no-op when no tuner plugin is configured
+void tunerUnload(ncclComm* comm);
+// Lets the plugin choose for one collective. Returns true and fills algo (comm.h Algo) / ctas when
+// the plugin expressed a choice that this data plane can run.
+bool tunerPick(ncclComm* comm, int func, size_t bytes, int numPipeOps, bool registered, int* algo, int* ctas);
+
+// ---- profiler plugin: per communicator
+struct ProfilerState {
+  void* lib = nullptr;
+  ncclProfiler_v6_t* prof = nullptr;
+  void* ctx = nullptr;
+  int mask = 0;
+  std::string name;
+  uint64_t seq[FUNC_COUNT] = {};
+};
+ncclResult_t profilerLoad(ncclComm* comm);
+void profilerUnload(ncclComm* comm);
+void* profStart(ncclComm* comm, ncclProfilerEventDescr_t* d);   // nullptr when the type is not enabled
+void profStop(ncclComm* comm, void* handle);
+void profState(ncclComm* comm, void* handle, ncclProfilerEventState_t st, ncclProfilerEventStateArgs_t* a);
+inline bool profWants(ncclComm* comm, int type);
+
+}  // namespace b200

@@ -1,0 +1,63 @@
+// Network transport of the host data plane: the ncclNet_t table in use (an external plugin or
+// the built-in TCP backend), per-peer send/receive connections, and the proxy thread that
+// progresses posted operations.
+// Reference parity: src/transport/net.cc (proxy progress :1304-1765), src/proxy.cc (progress
+// thread :954), src/plugin/net.cc (plugin choice), src/transport/net_socket.cc (TCP backend).
+#pragma once
+#include <atomic>
+#include <condition_variable>
+#include <deque>
+#include <mutex>
+#include <thread>
+#include <vector>
+
+#include "../comm/comm.h"
+#include "plugin/nccl_net.h"
+
+namespace b200 {
+
+extern ncclNet_t netSocketBackend;                 // transport/net_socket.cc
+
+// Resolves the network backend once per process: NCCL_NET_PLUGIN (library), NCCL_NET (name).
+ncclResult_t netSelect(ncclNet_t** net, bool* external);
+void pluginLogger(ncclDebugLogLevel level, unsigned long flags, const char* file, int line, const char* fmt, ...);
+
+struct ProxyOp {
+  bool isSend;
+  int peer;
+  char* data;
+  size_t bytes;
+  size_t posted = 0;        // bytes handed to the network so far
+  size_t completed = 0;
+  void* requests[NCCL_NET_MAX_REQUESTS] = {};
+  size_t reqBytes[NCCL_NET_MAX_REQUESTS] = {};
+  int head = 0, tail = 0;   // ring of requests in flight
+  std::atomic<int> state{0};   // 0 running, 1 done, <0 failed (ncclResult_t negated)
+  void* profHandle = nullptr;
+};
+
+struct Proxy {
+  ncclComm* comm = nullptr;
+  ncclNet_t* net = nullptr;
+  bool external = false;
+  void* netCtx = nullptr;
+  int dev = 0;
+  void* listenComm = nullptr;
+  std::vector<void*> sendComm, recvComm;   // per peer
+  size_t sliceBytes = 0;
+  int maxInflight = 0;
+  std::thread thread;
+  std::mutex lock;
+  std::condition_variable wake;
+  std::deque<ProxyOp*> ops;
+  bool stop = false;
+  uint64_t opsDone = 0, bytesMoved = 0, steps = 0;
+};
+
+ncclResult_t proxyCreate(ncclComm* comm);      // collective: listen, exchange handles, connect the full mesh, start the thread
+void proxyDestroy(ncclComm* comm);
+// Posts an operation; the proxy thread progresses it. proxyWait blocks until every op given is done.
+ProxyOp* proxyPost(Proxy* p, bool isSend, int peer, void* data, size_t bytes);
+ncclResult_t proxyWait(Proxy* p, ProxyOp** ops, int n);
+
+}  // namespace b200

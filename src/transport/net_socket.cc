@@ -1,0 +1,210 @@
+// Built-in network backend "Socket": the ncclNet_t table over TCP.
+// One TCP connection per send/receive pair. A message travels as an 8-byte length followed by
+// the payload; isend / irecv only record the request and test() moves whatever the kernel
+// accepts without blocking, so one proxy thread can keep many transfers in flight.
+// Reference parity: src/transport/net_socket.cc (devices/properties :50-346, listen/connect/
+// accept :408-540, test :608-720, isend/irecv :728-757); the reference adds helper threads and
+// multi-socket striping, which a loopback / single-NIC host path does not need.
+#include <string.h>
+
+#include "../core/socket.h"
+#include "net.h"
+
+namespace b200 {
+namespace {
+
+constexpr int kMaxIfs = 16;
+constexpr uint64_t kNetSocketMagic = 0x4e45545342323030ull;   // "NETSB200"
+
+struct Devices {
+  int n = -1;
+  char names[kMaxIfs][64];
+  SockAddr addrs[kMaxIfs];
+};
+Devices gDevs;
+std::mutex gDevLock;
+
+void loadDevices() {
+  std::lock_guard<std::mutex> g(gDevLock);
+  if (gDevs.n >= 0) return;
+  gDevs.n = findInterfaces(gDevs.names, gDevs.addrs, kMaxIfs);
+  if (gDevs.n < 0) gDevs.n = 0;
+}
+
+struct Handle {            // what listen() hands to the sender; fits NCCL_NET_HANDLE_MAXSIZE
+  SockAddr addr;
+  uint64_t magic;
+};
+static_assert(sizeof(Handle) <= NCCL_NET_HANDLE_MAXSIZE, "handle too large");
+
+struct ListenComm { Socket sock; };
+struct Comm {
+  Socket sock;
+  bool isSend;
+};
+struct Request {
+  Comm* comm;
+  bool isSend;
+  char* data;
+  uint64_t size;        // send: bytes to send; recv: capacity, then bytes received
+  uint64_t header;
+  int headerOff = 0;
+  uint64_t off = 0;
+  bool headerDone = false;
+};
+
+ncclResult_t sInit(void** ctx, uint64_t, ncclNetCommConfig_t*, ncclDebugLogger_t, ncclProfilerCallback_t) {
+  loadDevices();
+  if (ctx) *ctx = nullptr;
+  return ncclSuccess;
+}
+ncclResult_t sDevices(int* ndev) { loadDevices(); *ndev = gDevs.n; return ncclSuccess; }
+
+ncclResult_t sGetProperties(int dev, ncclNetProperties_t* p) {
+  loadDevices();
+  if (dev < 0 || dev >= gDevs.n) return ncclInvalidArgument;
+  memset(p, 0, sizeof(*p));
+  p->name = gDevs.names[dev];
+  p->pciPath = nullptr;
+  p->guid = dev;
+  p->ptrSupport = NCCL_PTR_HOST;
+  p->regIsGlobal = 0;
+  p->speed = strcmp(gDevs.names[dev], "lo") == 0 ? 100000 : 10000;
+  p->port = 0;
+  p->latency = 0;
+  p->maxComms = 65536;
+  p->maxRecvs = 1;
+  p->netDeviceType = NCCL_NET_DEVICE_HOST;
+  p->netDeviceVersion = 0;
+  p->vProps.ndevs = 1;
+  p->vProps.devs[0] = dev;
+  p->maxP2pBytes = (size_t)1 << 40;
+  p->maxCollBytes = (size_t)1 << 30;
+  p->maxMultiRequestSize = 1;
+  p->railId = -1;
+  p->planeId = -1;
+  return ncclSuccess;
+}
+
+ncclResult_t sListen(void*, int dev, void* handle, void** listenComm) {
+  loadDevices();
+  if (dev < 0 || dev >= gDevs.n) return ncclInvalidArgument;
+  ListenComm* l = new ListenComm;
+  NCCLCHECK(sockInit(&l->sock, &gDevs.addrs[dev], kNetSocketMagic, SOCK_NET));
+  ncclResult_t r = sockListen(&l->sock);
+  if (r != ncclSuccess) { delete l; return r; }
+  Handle h;
+  memset(&h, 0, sizeof(h));
+  h.addr = l->sock.addr;
+  h.magic = kNetSocketMagic;
+  memset(handle, 0, NCCL_NET_HANDLE_MAXSIZE);
+  memcpy(handle, &h, sizeof(h));
+  *listenComm = l;
+  return ncclSuccess;
+}
+
+ncclResult_t sConnect(void*, int, void* handle, void** sendComm, ncclNetDeviceHandle_t** devComm) {
+  Handle h;
+  memcpy(&h, handle, sizeof(h));
+  Comm* c = new Comm;
+  c->isSend = true;
+  NCCLCHECK(sockInit(&c->sock, &h.addr, h.magic, SOCK_NET));
+  ncclResult_t r = sockConnect(&c->sock);
+  if (r != ncclSuccess) { delete c; return r; }
+  *sendComm = c;
+  if (devComm) *devComm = nullptr;
+  return ncclSuccess;
+}
+
+ncclResult_t sAccept(void* listenComm, void** recvComm, ncclNetDeviceHandle_t** devComm) {
+  ListenComm* l = (ListenComm*)listenComm;
+  Comm* c = new Comm;
+  c->isSend = false;
+  ncclResult_t r = sockAccept(&c->sock, &l->sock);
+  if (r != ncclSuccess) { delete c; return r; }
+  *recvComm = c;
+  if (devComm) *devComm = nullptr;
+  return ncclSuccess;
+}
+
+ncclResult_t sRegMr(void*, void*, size_t, int type, void** mhandle) {
+  if (type != NCCL_PTR_HOST) return ncclInvalidArgument;   // TCP reads and writes host memory only
+  *mhandle = nullptr;
+  return ncclSuccess;
+}
+ncclResult_t sRegMrDmaBuf(void*, void*, size_t, int, uint64_t, int, void**) { return ncclInvalidUsage; }
+ncclResult_t sDeregMr(void*, void*) { return ncclSuccess; }
+
+ncclResult_t sIsend(void* sendComm, void* data, size_t size, int, void*, void*, void** request) {
+  Request* r = new Request;
+  r->comm = (Comm*)sendComm;
+  r->isSend = true;
+  r->data = (char*)data;
+  r->size = size;
+  r->header = size;
+  *request = r;
+  return ncclSuccess;
+}
+
+ncclResult_t sIrecv(void* recvComm, int n, void** data, size_t* sizes, int*, void**, void**, void** request) {
+  if (n != 1) return ncclInvalidArgument;
+  Request* r = new Request;
+  r->comm = (Comm*)recvComm;
+  r->isSend = false;
+  r->data = (char*)data[0];
+  r->size = sizes[0];
+  r->header = 0;
+  *request = r;
+  return ncclSuccess;
+}
+
+ncclResult_t sIflush(void*, int, void**, int*, void**, void** request) { *request = nullptr; return ncclSuccess; }
+
+ncclResult_t sTest(void* request, int* done, int* sizes) {
+  Request* r = (Request*)request;
+  *done = 0;
+  if (!r) { *done = 1; return ncclSuccess; }
+  const SockOpKind kind = r->isSend ? SOCK_OP_SEND : SOCK_OP_RECV;
+  if (!r->headerDone) {
+    NCCLCHECK(sockProgress(kind, &r->comm->sock, &r->header, 8, &r->headerOff));
+    if (r->headerOff < 8) return ncclSuccess;
+    r->headerDone = true;
+    if (!r->isSend) {
+      if (r->header > r->size) { WARN("net socket: message of %llu bytes does not fit the posted %llu", (unsigned long long)r->header, (unsigned long long)r->size); return ncclInternalError; }
+      r->size = r->header;
+    }
+  }
+  while (r->off < r->size) {
+    int chunk = (int)std::min<uint64_t>(r->size - r->off, 1u << 30), moved = 0;
+    NCCLCHECK(sockProgress(kind, &r->comm->sock, r->data + r->off, chunk, &moved));
+    r->off += moved;
+    if (moved < chunk) return ncclSuccess;
+  }
+  *done = 1;
+  if (sizes) sizes[0] = (int)std::min<uint64_t>(r->size, 0x7fffffff);
+  delete r;
+  return ncclSuccess;
+}
+
+ncclResult_t sCloseComm(void* comm) {
+  Comm* c = (Comm*)comm;
+  if (c) { sockClose(&c->sock); delete c; }
+  return ncclSuccess;
+}
+ncclResult_t sCloseListen(void* listenComm) {
+  ListenComm* l = (ListenComm*)listenComm;
+  if (l) { sockClose(&l->sock); delete l; }
+  return ncclSuccess;
+}
+ncclResult_t sGetDeviceMr(void*, void*, void**) { return ncclInvalidUsage; }
+ncclResult_t sIrecvConsumed(void*, int, void*) { return ncclSuccess; }
+ncclResult_t sMakeVDevice(int*, ncclNetVDeviceProps_t*) { return ncclInvalidUsage; }
+ncclResult_t sFinalize(void*) { return ncclSuccess; }
+ncclResult_t sSetNetAttr(void*, ncclNetAttr_t*) { return ncclSuccess; }
+
+}  // namespace
+
+ncclNet_t netSocketBackend = {"Socket", sInit, sDevices, sGetProperties, sListen, sConnect, sAccept, sRegMr, sRegMrDmaBuf, sDeregMr, sIsend, sIrecv,
+                              sIflush, sTest, sCloseComm, sCloseComm, sCloseListen, sGetDeviceMr, sIrecvConsumed, sMakeVDevice, sFinalize, sSetNetAttr};
+
+}  // namespace b200
