@@ -1,0 +1,186 @@
+// Example network plugin: ncclNet_v12 over UNIX-domain stream sockets (abstract namespace), for
+// ranks of one host. It shows the contract a backend must meet: listen() fills an opaque handle,
+// connect()/accept() may return a NULL comm ("call again"), isend()/irecv() only queue work and
+// test() makes progress without blocking. Messages are an 8-byte length plus payload.
+// Reference parity: plugins/net/example/plugin.c (table layout and call contract).
+#include <errno.h>
+#include <fcntl.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <sys/socket.h>
+#include <sys/un.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <deque>
+
+#include "plugin/nccl_net.h"
+
+namespace {
+
+std::atomic<int> gSeq{0};
+ncclDebugLogger_t gLog = nullptr;
+
+struct Handle { char name[64]; };
+struct Listen { int fd; };
+struct Req;
+struct Comm { int fd; std::deque<Req*> q; };
+struct Req {
+  Comm* c;
+  bool send;
+  char* data;
+  uint64_t size, header, off = 0;
+  int hoff = 0;
+};
+
+void nonblock(int fd) { fcntl(fd, F_SETFL, fcntl(fd, F_GETFL, 0) | O_NONBLOCK); }
+
+socklen_t fill(sockaddr_un* sa, const char* name) {
+  memset(sa, 0, sizeof(*sa));
+  sa->sun_family = AF_UNIX;
+  size_t n = strlen(name);
+  memcpy(sa->sun_path + 1, name, n);   // leading NUL: abstract namespace, nothing to unlink
+  return (socklen_t)(offsetof(sockaddr_un, sun_path) + 1 + n);
+}
+
+ncclResult_t nInit(void** ctx, uint64_t, ncclNetCommConfig_t*, ncclDebugLogger_t log, ncclProfilerCallback_t) {
+  gLog = log;
+  if (ctx) *ctx = nullptr;
+  return ncclSuccess;
+}
+ncclResult_t nDevices(int* n) { *n = 1; return ncclSuccess; }
+ncclResult_t nProps(int dev, ncclNetProperties_t* p) {
+  if (dev != 0) return ncclInvalidArgument;
+  memset(p, 0, sizeof(*p));
+  static char name[] = "unix0";
+  p->name = name;
+  p->ptrSupport = NCCL_PTR_HOST;
+  p->speed = 100000;
+  p->maxComms = 65536;
+  p->maxRecvs = 1;
+  p->netDeviceType = NCCL_NET_DEVICE_HOST;
+  p->vProps.ndevs = 1;
+  p->maxP2pBytes = (size_t)1 << 40;
+  p->maxCollBytes = (size_t)1 << 30;
+  p->maxMultiRequestSize = 1;
+  p->railId = p->planeId = -1;
+  return ncclSuccess;
+}
+ncclResult_t nListen(void*, int, void* handle, void** lc) {
+  Handle h;
+  memset(&h, 0, sizeof(h));
+  snprintf(h.name, sizeof(h.name), "nccl-unix-net-%d-%d", (int)getpid(), gSeq++);
+  int fd = socket(AF_UNIX, SOCK_STREAM, 0);
+  if (fd < 0) return ncclSystemError;
+  sockaddr_un sa;
+  socklen_t len = fill(&sa, h.name);
+  if (bind(fd, (sockaddr*)&sa, len) != 0 || listen(fd, 1024) != 0) { close(fd); return ncclSystemError; }
+  nonblock(fd);
+  memset(handle, 0, NCCL_NET_HANDLE_MAXSIZE);
+  memcpy(handle, &h, sizeof(h));
+  *lc = new Listen{fd};
+  return ncclSuccess;
+}
+ncclResult_t nConnect(void*, int, void* handle, void** sc, ncclNetDeviceHandle_t** dh) {
+  Handle h;
+  memcpy(&h, handle, sizeof(h));
+  *sc = nullptr;
+  if (dh) *dh = nullptr;
+  int fd = socket(AF_UNIX, SOCK_STREAM, 0);
+  if (fd < 0) return ncclSystemError;
+  sockaddr_un sa;
+  socklen_t len = fill(&sa, h.name);
+  if (connect(fd, (sockaddr*)&sa, len) != 0) {
+    int e = errno;
+    close(fd);
+    return (e == ECONNREFUSED || e == EAGAIN || e == ENOENT) ? ncclSuccess : ncclSystemError;   // not yet: the caller retries
+  }
+  nonblock(fd);
+  *sc = new Comm{fd, {}};
+  return ncclSuccess;
+}
+ncclResult_t nAccept(void* lc, void** rc, ncclNetDeviceHandle_t** dh) {
+  *rc = nullptr;
+  if (dh) *dh = nullptr;
+  int fd = accept(((Listen*)lc)->fd, nullptr, nullptr);
+  if (fd < 0) return (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR) ? ncclSuccess : ncclSystemError;
+  nonblock(fd);
+  *rc = new Comm{fd, {}};
+  return ncclSuccess;
+}
+ncclResult_t nRegMr(void*, void*, size_t, int type, void** mh) { *mh = nullptr; return type == NCCL_PTR_HOST ? ncclSuccess : ncclInvalidArgument; }
+ncclResult_t nRegMrDmaBuf(void*, void*, size_t, int, uint64_t, int, void**) { return ncclInvalidUsage; }
+ncclResult_t nDeregMr(void*, void*) { return ncclSuccess; }
+ncclResult_t nIsend(void* sc, void* data, size_t size, int, void*, void*, void** req) {
+  Req* r = new Req{(Comm*)sc, true, (char*)data, size, size};
+  r->c->q.push_back(r);
+  *req = r;
+  return ncclSuccess;
+}
+ncclResult_t nIrecv(void* rc, int n, void** data, size_t* sizes, int*, void**, void**, void** req) {
+  if (n != 1) return ncclInvalidArgument;
+  Req* r = new Req{(Comm*)rc, false, (char*)data[0], sizes[0], 0};
+  r->c->q.push_back(r);
+  *req = r;
+  return ncclSuccess;
+}
+ncclResult_t nIflush(void*, int, void**, int*, void**, void** req) { *req = nullptr; return ncclSuccess; }
+
+// moves bytes without blocking; returns false on a broken connection
+bool move(Req* r, char* p, uint64_t want, uint64_t* off) {
+  while (*off < want) {
+    ssize_t k = r->send ? send(r->c->fd, p + *off, want - *off, MSG_NOSIGNAL | MSG_DONTWAIT) : recv(r->c->fd, p + *off, want - *off, MSG_DONTWAIT);
+    if (k > 0) { *off += (uint64_t)k; continue; }
+    if (k < 0 && (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR)) return true;
+    return false;
+  }
+  return true;
+}
+ncclResult_t nTest(void* req, int* done, int* sizes) {
+  *done = 0;
+  Req* r = (Req*)req;
+  if (!r) { *done = 1; return ncclSuccess; }
+  if (r->c->q.front() != r) return ncclSuccess;
+  if (r->hoff < 8) {
+    uint64_t ho = (uint64_t)r->hoff;
+    if (!move(r, (char*)&r->header, 8, &ho)) return ncclRemoteError;
+    r->hoff = (int)ho;
+    if (r->hoff < 8) return ncclSuccess;
+    if (!r->send) {
+      if (r->header > r->size) return ncclInternalError;
+      r->size = r->header;
+    }
+  }
+  if (!move(r, r->data, r->size, &r->off)) return ncclRemoteError;
+  if (r->off < r->size) return ncclSuccess;
+  *done = 1;
+  if (sizes) sizes[0] = (int)r->size;
+  r->c->q.pop_front();
+  delete r;
+  return ncclSuccess;
+}
+ncclResult_t nCloseComm(void* c) {
+  Comm* k = (Comm*)c;
+  if (k) {
+    for (Req* r : k->q) delete r;
+    close(k->fd);
+    delete k;
+  }
+  return ncclSuccess;
+}
+ncclResult_t nCloseListen(void* l) {
+  if (l) { close(((Listen*)l)->fd); delete (Listen*)l; }
+  return ncclSuccess;
+}
+ncclResult_t nGetDeviceMr(void*, void*, void**) { return ncclInvalidUsage; }
+ncclResult_t nIrecvConsumed(void*, int, void*) { return ncclSuccess; }
+ncclResult_t nMakeVDevice(int*, ncclNetVDeviceProps_t*) { return ncclInvalidUsage; }
+ncclResult_t nFinalize(void*) { return ncclSuccess; }
+ncclResult_t nSetNetAttr(void*, ncclNetAttr_t*) { return ncclSuccess; }
+
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) const ncclNet_v12_t ncclNetPlugin_v12 = {
+    "UnixExample", nInit, nDevices, nProps, nListen, nConnect, nAccept, nRegMr, nRegMrDmaBuf, nDeregMr, nIsend, nIrecv, nIflush, nTest,
+    nCloseComm, nCloseComm, nCloseListen, nGetDeviceMr, nIrecvConsumed, nMakeVDevice, nFinalize, nSetNetAttr};

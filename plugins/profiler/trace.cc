@@ -1,0 +1,130 @@
+// Example profiler plugin: records every event it is offered and writes them at finalize as a
+// Chrome trace (chrome://tracing, Perfetto) to $NCCL_PROFILE_DUMP_FILE-<commId>-<rank>.json
+// (default ./nccl_trace). NCCL_PROFILE_EVENT_MASK selects event kinds (default: everything).
+// Reference parity: plugins/profiler/example (plugin.cc event pools, print_event.cc trace output).
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <time.h>
+
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "plugin/nccl_profiler.h"
+
+namespace {
+
+double nowUs() {
+  timespec ts;
+  clock_gettime(CLOCK_MONOTONIC, &ts);
+  return ts.tv_sec * 1e6 + ts.tv_nsec / 1e3;
+}
+
+struct Ctx;
+struct Event {
+  Ctx* ctx;
+  uint64_t type;
+  std::string name, args;
+  double t0, t1 = 0;
+};
+struct Ctx {
+  uint64_t commId;
+  int rank;
+  std::mutex lock;
+  std::vector<Event*> done;
+};
+
+const char* kindName(uint64_t t) {
+  switch (t) {
+    case ncclProfileGroup: return "Group";
+    case ncclProfileColl: return "Coll";
+    case ncclProfileP2p: return "P2p";
+    case ncclProfileProxyOp: return "ProxyOp";
+    case ncclProfileProxyStep: return "ProxyStep";
+    case ncclProfileProxyCtrl: return "ProxyCtrl";
+    case ncclProfileKernelCh: return "KernelCh";
+    case ncclProfileNetPlugin: return "NetPlugin";
+    case ncclProfileGroupApi: return "GroupApi";
+    case ncclProfileCollApi: return "CollApi";
+    case ncclProfileP2pApi: return "P2pApi";
+    case ncclProfileKernelLaunch: return "KernelLaunch";
+    case ncclProfileCeColl: return "CeColl";
+    default: return "Event";
+  }
+}
+
+ncclResult_t pInit(void** context, uint64_t commId, int* mask, const char*, int, int, int rank, ncclDebugLogger_t) {
+  Ctx* c = new Ctx;
+  c->commId = commId;
+  c->rank = rank;
+  if (*mask == 0) *mask = 0x7fff;
+  *context = c;
+  return ncclSuccess;
+}
+
+ncclResult_t pStart(void* context, void** handle, ncclProfilerEventDescr_t* d) {
+  Event* e = new Event;
+  e->ctx = (Ctx*)context;
+  e->type = d->type;
+  e->t0 = nowUs();
+  char buf[256] = "";
+  if (d->type == ncclProfileColl) {
+    e->name = d->coll.func ? d->coll.func : "coll";
+    snprintf(buf, sizeof(buf), "\"count\":%zu,\"algo\":\"%s\",\"proto\":\"%s\",\"channels\":%d,\"seq\":%llu", d->coll.count, d->coll.algo ? d->coll.algo : "",
+             d->coll.proto ? d->coll.proto : "", d->coll.nChannels, (unsigned long long)d->coll.seqNumber);
+  } else if (d->type == ncclProfileCollApi) {
+    e->name = std::string(d->collApi.func ? d->collApi.func : "coll") + " (API)";
+    snprintf(buf, sizeof(buf), "\"count\":%zu,\"datatype\":\"%s\"", d->collApi.count, d->collApi.datatype ? d->collApi.datatype : "");
+  } else if (d->type == ncclProfileP2p) {
+    e->name = d->p2p.func ? d->p2p.func : "p2p";
+    snprintf(buf, sizeof(buf), "\"count\":%zu,\"peer\":%d", d->p2p.count, d->p2p.peer);
+  } else if (d->type == ncclProfileP2pApi) {
+    e->name = std::string(d->p2pApi.func ? d->p2pApi.func : "p2p") + " (API)";
+  } else if (d->type == ncclProfileProxyOp) {
+    e->name = d->proxyOp.isSend ? "ProxySend" : "ProxyRecv";
+    snprintf(buf, sizeof(buf), "\"peer\":%d,\"steps\":%d,\"chunk\":%d", d->proxyOp.peer, d->proxyOp.nSteps, d->proxyOp.chunkSize);
+  } else {
+    e->name = kindName(d->type);
+  }
+  e->args = buf;
+  *handle = e;
+  return ncclSuccess;
+}
+
+ncclResult_t pStop(void* handle) {
+  Event* e = (Event*)handle;
+  if (!e) return ncclSuccess;
+  e->t1 = nowUs();
+  std::lock_guard<std::mutex> g(e->ctx->lock);
+  e->ctx->done.push_back(e);
+  return ncclSuccess;
+}
+
+ncclResult_t pState(void*, ncclProfilerEventState_t, ncclProfilerEventStateArgs_t*) { return ncclSuccess; }
+
+ncclResult_t pFinalize(void* context) {
+  Ctx* c = (Ctx*)context;
+  const char* base = getenv("NCCL_PROFILE_DUMP_FILE");
+  char path[512];
+  snprintf(path, sizeof(path), "%s-%llx-%d.json", base && *base ? base : "nccl_trace", (unsigned long long)c->commId, c->rank);
+  FILE* f = fopen(path, "w");
+  if (f) {
+    fprintf(f, "[\n");
+    bool first = true;
+    for (Event* e : c->done) {
+      fprintf(f, "%s{\"name\":\"%s\",\"cat\":\"%s\",\"ph\":\"X\",\"ts\":%.3f,\"dur\":%.3f,\"pid\":%d,\"tid\":\"%s\",\"args\":{%s}}", first ? "" : ",\n", e->name.c_str(),
+              kindName(e->type), e->t0, e->t1 - e->t0, c->rank, kindName(e->type), e->args.c_str());
+      first = false;
+    }
+    fprintf(f, "\n]\n");
+    fclose(f);
+  }
+  for (Event* e : c->done) delete e;
+  delete c;
+  return ncclSuccess;
+}
+
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) const ncclProfiler_v6_t ncclProfiler_v6 = {"trace", pInit, pStart, pStop, pState, pFinalize};

@@ -126,6 +126,7 @@ struct ncclComm {
   b200::Proxy* proxy = nullptr;
   b200::TopoState* topo = nullptr;
   b200::TunerState* tuner = nullptr;
+  b200::ProfilerState* profiler = nullptr;
   b200::MemManager* memMgr = nullptr;
 
   std::vector<b200::UserRedOp> userOps;

@@ -4,6 +4,7 @@
 // Reference parity: src/enqueue.cc:1989-2180 (algorithm choice), :2479-2583 (reduction operator
 // lowering), src/sym_kernels.cc:599-641 (kernel pick), src/scheduler/symmetric_sched.cc.
 #include "device_plane.h"
+#include "../plugin/plugin.h"
 
 #include <math.h>
 #include <stdio.h>
@@ -304,9 +305,18 @@ static ncclResult_t orderStreams(ncclComm* comm, cudaStream_t stream) {
   return ncclSuccess;
 }
 
-static ncclResult_t launchColl(ncclComm* comm, const void* fn, CollArgs* a, int ctas, cudaStream_t stream) {
+// what the most recent launch of this thread ran (reported to profiler plugins)
+static thread_local const char* tLastAlgo = "NONE";
+static thread_local const char* tLastProto = "SIMPLE";
+static thread_local int tLastCtas = 0;
+
+static ncclResult_t launchColl(ncclComm* comm, const void* fn, CollArgs* a, int ctas, cudaStream_t stream, const char* algo = "P2P",
+                               const char* proto = "SIMPLE") {
   if (!fn) { WARN("no kernel for this data type / operator"); return ncclInvalidUsage; }
   comm->devPlane->launches++;
+  tLastAlgo = algo;
+  tLastProto = proto;
+  tLastCtas = ctas;
   return launchKernel(fn, dim3(ctas), dim3(kCtaThreads), 0, a, stream, false, paramLaunchPdl() != 0);
 }
 
@@ -361,6 +371,10 @@ static ncclResult_t runReduction(ncclComm* comm, const Task& t) {
   if (total == 0) return ncclSuccess;
   int forced = forcedAlgo();
   tPickCtas = 0;
+  if (forced == ALGO_AUTO && comm->tuner) {
+    int a = ALGO_AUTO, c = 0;
+    if (tunerPick(comm, t.func, bytes, 1, symFindWindow(comm, t.recv, 1) != nullptr, &a, &c)) { forced = a; tPickCtas = c; }
+  }
   if (forced == ALGO_AUTO && paramLLThreshold() < 0 && paramNvlsThreshold() < 0) {
     TunePick pk = tunePick(dp->tune, t.func, n, bytes);
     if (pk.valid) { forced = pk.algo; tPickCtas = pk.ctas; }
@@ -385,7 +399,7 @@ static ncclResult_t runReduction(ncclComm* comm, const Task& t) {
       a.scaleMode = op.scaleMode; a.scaleF = op.scaleF; a.scaleD = op.scaleD; a.intDiv = op.intDiv;
       size_t lines = (recvBytes + 7) / 8;
       int ctas = (int)std::min<size_t>((lines + kCtaThreads - 1) / kCtaThreads, 64);
-      return launchColl(comm, llReduceKernelFn(t.type, op.red), &a, std::max(ctas, 1), t.stream);
+      return launchColl(comm, llReduceKernelFn(t.type, op.red), &a, std::max(ctas, 1), t.stream, "ONESHOT", "LL");
     }
   }
 
@@ -468,7 +482,7 @@ static ncclResult_t runReduction(ncclComm* comm, const Task& t) {
     if (forced == ALGO_P2P) useNvls = false;
     const size_t perRankBytes = t.func == FUNC_REDUCE ? curBytes : curBytes / n;
     int ctas = clampCtas(comm, perRankBytes, useNvls ? dp->tune.nvlsCtas : dp->tune.p2pCtas);
-    NCCLCHECK(launchColl(comm, reduceKernelFn(useNvls ? KERNEL_REDUCE_NVLS : KERNEL_REDUCE_P2P, t.type, op.red), &a, ctas, t.stream));
+    NCCLCHECK(launchColl(comm, reduceKernelFn(useNvls ? KERNEL_REDUCE_NVLS : KERNEL_REDUCE_P2P, t.type, op.red), &a, ctas, t.stream, useNvls ? "NVLS" : "P2P"));
     if (direct) break;
     // copy-out of the staged all-reduce
     if (t.func == FUNC_ALLREDUCE)
@@ -487,6 +501,13 @@ static ncclResult_t runCopyColl(ncclComm* comm, const Task& t) {
   int forced = forcedAlgo();
   int modeForce = tForceMode;
   tPickCtas = 0;
+  if (forced == ALGO_AUTO && modeForce < 0 && comm->tuner) {
+    int a = ALGO_AUTO, c = 0;
+    if (tunerPick(comm, t.func, B * (t.func == FUNC_ALLGATHER ? n : 1), 1, symFindWindow(comm, t.recv, 1) != nullptr, &a, &c)) {
+      forced = a == ALGO_TREE ? ALGO_AUTO : a;   // copy collectives have no tree form
+      tPickCtas = c;
+    }
+  }
   if (forced == ALGO_AUTO && modeForce < 0) {
     size_t key = (t.func == FUNC_ALLGATHER || t.func == FUNC_ALLTOALL) ? B * n : B;
     TunePick pk = tunePick(dp->tune, t.func, n, key);
@@ -510,7 +531,7 @@ static ncclResult_t runCopyColl(ncclComm* comm, const Task& t) {
     a.lrecv[me] = t.recv;
     size_t items = ((B + 7) / 8) * (size_t)(n - 1);
     int ctas = (int)std::min<size_t>((items + kCtaThreads - 1) / kCtaThreads, 64);
-    return launchColl(comm, llCopyKernelFn(), &a, std::max(ctas, 1), t.stream);
+    return launchColl(comm, llCopyKernelFn(), &a, std::max(ctas, 1), t.stream, "ONESHOT", "LL");
   }
   size_t sendBytes = B, recvBytes = B;
   if (t.func == FUNC_ALLGATHER || t.func == FUNC_GATHER) recvBytes = B * n;
@@ -582,7 +603,7 @@ static ncclResult_t runCopyColl(ncclComm* comm, const Task& t) {
     }
     size_t moved = cur * ((t.func == FUNC_BROADCAST && mode != MODE_PUSH) ? 1 : (a.mode == MODE_MC ? 1 : n));
     int ctas = clampCtas(comm, moved, dp->tune.copyCtas);
-    NCCLCHECK(launchColl(comm, copyKernelFn(), &a, ctas, t.stream));
+    NCCLCHECK(launchColl(comm, copyKernelFn(), &a, ctas, t.stream, a.mode == MODE_MC ? "NVLS" : a.mode == MODE_PULL ? "P2P_PULL" : "P2P_PUSH"));
   }
   return ncclSuccess;
 }
@@ -652,6 +673,10 @@ ncclResult_t devPlaneRun(ncclComm* comm, const Task& t, ncclSimInfo_t* sim) {
   CUDACHECK(cudaGetDevice(&cur));
   if (cur != comm->cudaDev) CUDACHECK(cudaSetDevice(comm->cudaDev));
   ncclResult_t r = ncclSuccess;
+  void* prof = comm->profiler ? profilerTaskStart(comm, t) : nullptr;
+  tLastAlgo = comm->nRanks == 1 ? "ONERANK" : comm->lsaAll ? "P2P" : "HOST";
+  tLastProto = "SIMPLE";
+  tLastCtas = 0;
   if (t.func == FUNC_PUTSIGNAL || t.func == FUNC_SIGNAL || t.func == FUNC_WAITSIGNAL) {
     r = orderStreams(comm, t.stream);
     if (r == ncclSuccess) r = signalRun(comm, t);
@@ -669,6 +694,7 @@ ncclResult_t devPlaneRun(ncclComm* comm, const Task& t, ncclSimInfo_t* sim) {
       }
     }
   }
+  if (prof) profilerTaskStop(comm, t, prof, tLastAlgo, tLastProto, tLastCtas);
   if (cur != comm->cudaDev && cur >= 0) cudaSetDevice(cur);
   return r;
 }
@@ -787,7 +813,7 @@ ncclResult_t ringTreeRun(ncclComm* comm, const Task& t, int algo) {
     a.vec16 = !blocks || (cur * es) % 16 == 0;
     int ctas = clampCtas(comm, cur * es, dp->tune.p2pCtas);
     const void* fn = algo == ALGO_TREE ? treeKernelFn(t.type, op.red) : ringKernelFn(t.type, op.red);
-    NCCLCHECK(launchColl(comm, fn, &a, ctas, t.stream));
+    NCCLCHECK(launchColl(comm, fn, &a, ctas, t.stream, algo == ALGO_TREE ? "TREE" : "RING"));
     if (t.func == FUNC_ALLREDUCE) {
       CUDACHECK(cudaMemcpyAsync((char*)t.recv + done * es, st, cur * es, cudaMemcpyDeviceToDevice, t.stream));
     } else if (t.func == FUNC_REDUCESCATTER) {

@@ -7,6 +7,7 @@
 // :766-887 group end), src/enqueue.cc:3014-3172 (taskAppend / ncclEnqueueCheck).
 #include <algorithm>
 
+#include "../plugin/plugin.h"
 #include "device_plane.h"
 
 namespace b200 {
@@ -48,7 +49,10 @@ static ncclResult_t runTask(ncclComm* comm, const Task& t) {
         return ncclSuccess;
       }
     }
-    return hostPlaneRun(comm, t);
+    void* prof = comm->profiler ? profilerTaskStart(comm, t) : nullptr;
+    ncclResult_t r = hostPlaneRun(comm, t);
+    if (prof) profilerTaskStop(comm, t, prof, "RING", "SIMPLE", 1);
+    return r;
   }
   return devPlaneRun(comm, t);
 }
@@ -64,9 +68,17 @@ static ncclResult_t runP2p(ncclComm* comm, const std::vector<Task>& p2p) {
       for (size_t i = 0; i < s.size(); ++i) memcpy(r[i]->recv, s[i]->send, s[i]->count * typeSize(s[i]->type));
       return ncclSuccess;
     }
-    return hostPlaneRunP2pGroup(comm, p2p);
+    std::vector<void*> prof;
+    if (comm->profiler) for (auto& t : p2p) prof.push_back(profilerTaskStart(comm, t));
+    ncclResult_t r = hostPlaneRunP2pGroup(comm, p2p);
+    for (size_t i = 0; i < prof.size(); ++i) profilerTaskStop(comm, p2p[i], prof[i], "P2P", "SIMPLE", 1);
+    return r;
   }
-  return devPlaneRunP2pGroup(comm, p2p);
+  std::vector<void*> prof;
+  if (comm->profiler) for (auto& t : p2p) prof.push_back(profilerTaskStart(comm, t));
+  ncclResult_t r = devPlaneRunP2pGroup(comm, p2p);
+  for (size_t i = 0; i < prof.size(); ++i) profilerTaskStop(comm, p2p[i], prof[i], "P2P", "SIMPLE", 1);
+  return r;
 }
 
 static ncclResult_t launchAll(std::vector<Task>& tasks, ncclSimInfo_t* sim) {

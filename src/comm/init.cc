@@ -9,6 +9,8 @@
 #include <set>
 
 #include "../core/cudawrap.h"
+#include "../plugin/plugin.h"
+#include "../plugin/profiler.h"
 #include "../ras/ras.h"
 #include "../topo/topo.h"
 #include "device_plane.h"
@@ -148,6 +150,8 @@ static ncclResult_t commSetup(ncclComm* comm) {
   } else {
     NCCLCHECK(devPlaneCreate(comm));
   }
+  NCCLCHECK(tunerLoad(comm));
+  profilerCommInit(comm);
   if (paramRasEnable()) rasCommAdd(comm);
   INFO(SUB_INIT, "comm %p rank %d nranks %d cudaDev %d nodes %d localRanks %d %s - Init COMPLETE", (void*)comm, comm->rank, n, comm->cudaDev,
        comm->nNodes, comm->localRanks, comm->hostOnly ? "(host memory)" : (comm->lsaAll ? "(symmetric data plane)" : "(socket fallback)"));
@@ -176,6 +180,8 @@ static void freeComm(ncclComm* comm) {
   if (!comm) return;
   if (comm->initThread) { if (comm->initThread->joinable()) comm->initThread->join(); delete comm->initThread; }
   rasCommRemove(comm);
+  profilerCommFini(comm);
+  tunerUnload(comm);
   if (comm->devPlane) {
     int cur = -1;
     cudaGetDevice(&cur);

@@ -16,6 +16,7 @@
 namespace b200 {
 
 static const char* (*gEnvProvider)(const char*) = nullptr;
+void envPluginInit();   // plugin/env.cc
 static std::once_flag gConfOnce;
 static std::mutex gRegLock;
 
@@ -58,6 +59,7 @@ void loadConfFiles() {
 
 const char* getEnv(const char* name) {
   loadConfFiles();
+  envPluginInit();
   if (gEnvProvider) {
     const char* v = gEnvProvider(name);
     if (v) return v;

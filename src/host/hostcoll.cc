@@ -11,12 +11,17 @@
 #include "../comm/comm.h"
 #include "hosttypes.h"
 
+#include "../transport/net.h"
+
 namespace b200 {
 
 struct HostPlane {
   std::vector<Socket> peer;   // peer[r] connected to rank r (unused for r == rank)
   std::vector<char> tmp;
+  Proxy* proxy = nullptr;     // set when messages travel through the network backend instead
 };
+
+B200_PARAM(HostNet, "NCCL_B200_HOST_NET", 0, "1: host-memory messages go through the network backend (plugin or built-in Socket) and the proxy thread; 0: direct TCP mesh");
 
 static constexpr int kTagHostMesh = BS_TAG_USER + 1;
 
@@ -24,6 +29,15 @@ ncclResult_t hostPlaneCreate(ncclComm* comm) {
   HostPlane* hp = new HostPlane;
   int n = comm->nRanks, me = comm->rank;
   hp->peer.resize(n);
+  bool ext = false;
+  ncclNet_t* net = nullptr;
+  if (netSelect(&net, &ext) == ncclSuccess && (ext || paramHostNet())) {
+    ncclResult_t res = proxyCreate(comm);
+    if (res != ncclSuccess) { delete hp; return res; }
+    hp->proxy = comm->proxy;
+    comm->hostPlane = hp;
+    return ncclSuccess;
+  }
   // Higher ranks listen, lower ranks dial: connects land in the listen backlog, so dialling
   // everything first and accepting afterwards cannot deadlock.
   for (int r = me + 1; r < n; ++r) {
@@ -40,12 +54,20 @@ ncclResult_t hostPlaneCreate(ncclComm* comm) {
 
 void hostPlaneDestroy(ncclComm* comm) {
   if (!comm->hostPlane) return;
+  proxyDestroy(comm);
   for (auto& s : comm->hostPlane->peer) sockClose(&s);
   delete comm->hostPlane;
   comm->hostPlane = nullptr;
 }
 
 static ncclResult_t exchange(HostPlane* hp, int to, const void* sbuf, size_t sbytes, int from, void* rbuf, size_t rbytes) {
+  if (hp->proxy) {
+    ProxyOp* ops[2];
+    int k = 0;
+    if (sbytes > 0) ops[k++] = proxyPost(hp->proxy, true, to, (void*)sbuf, sbytes);
+    if (rbytes > 0) ops[k++] = proxyPost(hp->proxy, false, from, rbuf, rbytes);
+    return proxyWait(hp->proxy, ops, k);
+  }
   // messages larger than INT_MAX are cut in pieces; both sides cut identically
   const size_t piece = 1u << 30;
   size_t so = 0, ro = 0;
@@ -258,6 +280,19 @@ ncclResult_t hostPlaneRun(ncclComm* comm, const Task& t) {
 // A group of sends and receives progresses all at once so that any matching order works.
 ncclResult_t hostPlaneRunP2pGroup(ncclComm* comm, const std::vector<Task>& tasks) {
   HostPlane* hp = comm->hostPlane;
+  if (hp->proxy) {
+    std::vector<ProxyOp*> posted;
+    std::vector<const Task*> sSelf, rSelf;
+    for (auto& t : tasks) {
+      size_t bytes = t.count * typeSize(t.type);
+      if (t.root == comm->rank) { (t.func == FUNC_SEND ? sSelf : rSelf).push_back(&t); continue; }
+      if (t.func == FUNC_SEND) posted.push_back(proxyPost(hp->proxy, true, t.root, (void*)t.send, bytes));
+      else if (t.func == FUNC_RECV) posted.push_back(proxyPost(hp->proxy, false, t.root, t.recv, bytes));
+    }
+    if (sSelf.size() != rSelf.size()) { WARN("unmatched send/recv to self"); return ncclInvalidUsage; }
+    for (size_t i = 0; i < sSelf.size(); ++i) memcpy(rSelf[i]->recv, sSelf[i]->send, sSelf[i]->count * typeSize(sSelf[i]->type));
+    return proxyWait(hp->proxy, posted.data(), (int)posted.size());
+  }
   std::vector<SockOp> ops;
   for (auto& t : tasks) {
     size_t bytes = t.count * typeSize(t.type);

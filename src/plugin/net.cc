@@ -1,0 +1,47 @@
+// Network backend choice: an external plugin (NCCL_NET_PLUGIN) exporting ncclNetPlugin_v12, or
+// the built-in TCP backend. NCCL_NET=<name> insists on one backend by name.
+// Reference parity: src/plugin/net.cc:60-495 (external first, then internal backends; name match
+// against NCCL_NET), src/plugin/net/net_v12.cc.
+#include <mutex>
+
+#include "../transport/net.h"
+#include "plugin.h"
+
+namespace b200 {
+
+static std::once_flag gNetOnce;
+static ncclNet_t* gNet = nullptr;
+static bool gNetExternal = false;
+
+ncclResult_t netSelect(ncclNet_t** net, bool* external) {
+  std::call_once(gNetOnce, [] {
+    const char* wantName = getEnv("NCCL_NET");
+    std::string resolved;
+    void* lib = pluginOpen(PLUGIN_NET, &resolved);
+    ncclNet_t* ext = lib ? (ncclNet_t*)pluginSymbol(lib, NCCL_NET_PLUGIN_SYMBOL) : nullptr;
+    if (lib && !ext) WARN("net plugin %s does not export %s (older interfaces are not supported); using the built-in backend", resolved.c_str(), NCCL_NET_PLUGIN_SYMBOL);
+    if (ext && wantName && *wantName && strcasecmp(wantName, ext->name) != 0 && strcasecmp(wantName, netSocketBackend.name) == 0) ext = nullptr;
+    if (ext) {
+      int ndev = 0;
+      void* ctx = nullptr;
+      ncclNetCommConfig_t cfg = {NCCL_NET_TRAFFIC_CLASS_UNDEF};
+      if (ext->init(&ctx, 0, &cfg, pluginLogger, nullptr) == ncclSuccess && ext->devices(&ndev) == ncclSuccess && ndev > 0) {
+        if (ext->finalize) ext->finalize(ctx);
+        gNet = ext;
+        gNetExternal = true;
+        INFO(SUB_NET | SUB_INIT, "network backend: plugin %s (%s), %d device(s)", ext->name, resolved.c_str(), ndev);
+        return;
+      }
+      WARN("net plugin %s found no usable device; using the built-in backend", ext->name);
+    }
+    if (wantName && *wantName && strcasecmp(wantName, netSocketBackend.name) != 0)
+      WARN("NCCL_NET=%s does not match any available backend; using %s", wantName, netSocketBackend.name);
+    gNet = &netSocketBackend;
+    INFO(SUB_NET | SUB_INIT, "network backend: built-in %s", gNet->name);
+  });
+  *net = gNet;
+  if (external) *external = gNetExternal;
+  return gNet ? ncclSuccess : ncclInternalError;
+}
+
+}  // namespace b200

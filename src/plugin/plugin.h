@@ -60,6 +60,9 @@ void profilerUnload(ncclComm* comm);
 void* profStart(ncclComm* comm, ncclProfilerEventDescr_t* d);   // nullptr when the type is not enabled
 void profStop(ncclComm* comm, void* handle);
 void profState(ncclComm* comm, void* handle, ncclProfilerEventState_t st, ncclProfilerEventStateArgs_t* a);
-inline bool profWants(ncclComm* comm, int type);
+// Task events of the data plane (profiler_plugin.cc).
+void* profilerTaskStart(ncclComm* comm, const Task& t);
+void profilerTaskStop(ncclComm* comm, const Task& t, void* handle, const char* algo, const char* proto, int nCtas);
+void profilerPoll(ncclComm* comm, bool drain);
 
 }  // namespace b200

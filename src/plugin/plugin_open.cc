@@ -43,14 +43,14 @@ void* pluginOpen(PluginKind kind, std::string* resolved) {
 void* pluginSymbol(void* lib, const char* name) { return lib ? dlsym(lib, name) : nullptr; }
 
 void pluginLogger(ncclDebugLogLevel level, unsigned long flags, const char* file, int line, const char* fmt, ...) {
-  int lvl = level == NCCL_LOG_WARN ? LOG_WARN : level == NCCL_LOG_INFO ? LOG_INFO : level == NCCL_LOG_TRACE ? LOG_TRACE : -1;
-  if (lvl < 0 || !debugEnabled(lvl, flags)) return;
+  const LogLevel lvl = level == NCCL_LOG_WARN ? LOG_WARN : level == NCCL_LOG_INFO ? LOG_INFO : level == NCCL_LOG_TRACE ? LOG_TRACE : LOG_NONE;
+  if (lvl == LOG_NONE || (lvl != LOG_WARN && debugLevel() < (int)lvl)) return;
   char buf[1024];
   va_list ap;
   va_start(ap, fmt);
   vsnprintf(buf, sizeof(buf), fmt, ap);
   va_end(ap);
-  debugLog(lvl, flags, file, line, "%s", buf);
+  debugLog(lvl, (uint64_t)flags, file, line, "%s", buf);
 }
 
 }  // namespace b200

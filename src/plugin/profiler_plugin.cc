@@ -1,9 +1,280 @@
-// External profiler plugin glue (filled in by plugin loading; no plugin = no events).
+// External profiler plugin glue. Events sent to a plugin exporting ncclProfiler_v6:
+//   GroupApi / CollApi / P2pApi   around each public call (and its group)
+//   KernelLaunch                  around each kernel launch of the data plane
+//   Group -> Coll / P2p           one per task that reaches the data plane, with algorithm names
+//   KernelCh                      device-side execution window of the task's kernels: a pair of
+//                                 CUDA events around the launches, polled at later API calls;
+//                                 pTimer values are nanoseconds on the host clock of the start
+//                                 event plus the measured device duration
+// Reference parity: src/plugin/profiler.cc (load :46-113, init/finalize :245-263, API events
+// :275-386, kernel launch :388-430, group/task :432-565, kernel channel :679-705).
+#include <cuda_runtime.h>
+
+#include <deque>
+#include <mutex>
+
+#include "plugin.h"
 #include "profiler.h"
 
 namespace b200 {
-__attribute__((weak)) void* profilerPluginStart(ncclComm*, const Task&) { return nullptr; }
-__attribute__((weak)) void profilerPluginStop(void*) {}
-void profilerCommInit(ncclComm*) {}
-void profilerCommFini(ncclComm*) {}
+
+static const char* kTypeNames[] = {"ncclInt8", "ncclUint8", "ncclInt32", "ncclUint32", "ncclInt64", "ncclUint64", "ncclFloat16", "ncclFloat32",
+                                   "ncclFloat64", "ncclBfloat16", "ncclFloat8e4m3", "ncclFloat8e5m2"};
+static const char* typeName(int t) { return t >= 0 && t < 12 ? kTypeNames[t] : "unknown"; }
+
+struct PendingKernel {
+  cudaEvent_t start, stop;
+  void* collHandle;
+  void* groupHandle;
+  uint64_t hostStartNs;
+};
+
+struct ProfilerExtra {
+  std::mutex lock;
+  std::deque<PendingKernel> pending;
+  std::vector<cudaEvent_t> pool;
+};
+static std::mutex gExtraLock;
+static std::map<ncclComm*, ProfilerExtra*> gExtra;
+
+static ProfilerExtra* extraOf(ncclComm* comm, bool create) {
+  std::lock_guard<std::mutex> g(gExtraLock);
+  auto it = gExtra.find(comm);
+  if (it != gExtra.end()) return it->second;
+  if (!create) return nullptr;
+  return gExtra[comm] = new ProfilerExtra;
+}
+
+ncclResult_t profilerLoad(ncclComm* comm) {
+  std::string resolved;
+  void* lib = pluginOpen(PLUGIN_PROFILER, &resolved);
+  if (!lib) return ncclSuccess;
+  ncclProfiler_v6_t* p = (ncclProfiler_v6_t*)pluginSymbol(lib, NCCL_PROFILER_PLUGIN_SYMBOL);
+  if (!p) { WARN("profiler plugin %s does not export %s (older interfaces are not supported)", resolved.c_str(), NCCL_PROFILER_PLUGIN_SYMBOL); return ncclSuccess; }
+  ProfilerState* ps = new ProfilerState;
+  ps->lib = lib;
+  ps->prof = p;
+  ps->name = p->name ? p->name : resolved;
+  int mask = 0;
+  const char* m = getEnv("NCCL_PROFILE_EVENT_MASK");
+  if (m && *m) mask = (int)strtol(m, nullptr, 0);
+  ncclResult_t r = p->init(&ps->ctx, comm->commHash, &mask, comm->name.c_str(), comm->nNodes, comm->nRanks, comm->rank, pluginLogger);
+  if (r != ncclSuccess) { WARN("profiler plugin %s failed to initialise (%d)", ps->name.c_str(), (int)r); delete ps; return ncclSuccess; }
+  ps->mask = mask;
+  comm->profiler = ps;
+  INFO(SUB_PROFILE, "profiler plugin %s (%s) attached, event mask 0x%x", ps->name.c_str(), resolved.c_str(), mask);
+  return ncclSuccess;
+}
+
+void profilerPoll(ncclComm* comm, bool drain);
+
+void profilerUnload(ncclComm* comm) {
+  ProfilerState* ps = comm->profiler;
+  if (!ps) return;
+  profilerPoll(comm, true);
+  if (ps->prof->finalize) ps->prof->finalize(ps->ctx);
+  ProfilerExtra* ex = extraOf(comm, false);
+  if (ex) {
+    for (cudaEvent_t e : ex->pool) cudaEventDestroy(e);
+    {
+      std::lock_guard<std::mutex> g(gExtraLock);
+      gExtra.erase(comm);
+    }
+    delete ex;
+  }
+  delete ps;
+  comm->profiler = nullptr;
+}
+
+void* profStart(ncclComm* comm, ncclProfilerEventDescr_t* d) {
+  ProfilerState* ps = comm->profiler;
+  if (!ps || !(ps->mask & (int)d->type)) return nullptr;
+  d->rank = comm->rank;
+  void* h = nullptr;
+  if (ps->prof->startEvent(ps->ctx, &h, d) != ncclSuccess) return nullptr;
+  return h;
+}
+void profStop(ncclComm* comm, void* h) {
+  if (h && comm->profiler) comm->profiler->prof->stopEvent(h);
+}
+void profState(ncclComm* comm, void* h, ncclProfilerEventState_t st, ncclProfilerEventStateArgs_t* a) {
+  if (h && comm->profiler && comm->profiler->prof->recordEventState) comm->profiler->prof->recordEventState(h, st, a);
+}
+
+// ---- public-call events (called through ProfilerApiScope)
+struct ApiPluginHandle {
+  ncclComm* comm;
+  void* group;
+  void* api;
+};
+
+void* profilerPluginStart(ncclComm* comm, const Task& t) {
+  if (!comm->profiler) return nullptr;
+  profilerPoll(comm, false);
+  ApiPluginHandle* h = new ApiPluginHandle{comm, nullptr, nullptr};
+  ncclProfilerEventDescr_t d;
+  memset(&d, 0, sizeof(d));
+  d.type = ncclProfileGroupApi;
+  d.groupApi.groupDepth = groupDepth();
+  h->group = profStart(comm, &d);
+  memset(&d, 0, sizeof(d));
+  const bool p2p = t.func == FUNC_SEND || t.func == FUNC_RECV;
+  d.parentObj = h->group;
+  if (p2p) {
+    d.type = ncclProfileP2pApi;
+    d.p2pApi.func = funcName(t.func);
+    d.p2pApi.count = t.count;
+    d.p2pApi.datatype = typeName(t.type);
+    d.p2pApi.stream = (void*)t.stream;
+  } else {
+    d.type = ncclProfileCollApi;
+    d.collApi.func = funcName(t.func);
+    d.collApi.count = t.count;
+    d.collApi.datatype = typeName(t.type);
+    d.collApi.root = t.root;
+    d.collApi.stream = (void*)t.stream;
+  }
+  h->api = profStart(comm, &d);
+  return h;
+}
+
+void profilerPluginStop(void* hv) {
+  ApiPluginHandle* h = (ApiPluginHandle*)hv;
+  profStop(h->comm, h->api);
+  profStop(h->comm, h->group);
+  delete h;
+}
+
+// ---- task events (data plane)
+struct TaskProfile {
+  void* group = nullptr;
+  void* coll = nullptr;
+  void* launch = nullptr;
+  cudaEvent_t start = nullptr, stop = nullptr;
+  uint64_t hostStartNs = 0;
+};
+
+static cudaEvent_t takeEvent(ProfilerExtra* ex) {
+  {
+    std::lock_guard<std::mutex> g(ex->lock);
+    if (!ex->pool.empty()) { cudaEvent_t e = ex->pool.back(); ex->pool.pop_back(); return e; }
+  }
+  cudaEvent_t e = nullptr;
+  if (cudaEventCreate(&e) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+  return e;
+}
+
+// Called before the data plane chooses and launches: records the device-side start marker.
+void* profilerTaskStart(ncclComm* comm, const Task& t) {
+  ProfilerState* ps = comm->profiler;
+  if (!ps) return nullptr;
+  TaskProfile* tp = new TaskProfile;
+  tp->hostStartNs = nowNs();
+  // device window: only outside stream capture (captured events cannot be queried)
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  if ((ps->mask & ncclProfileKernelCh) && !comm->hostOnly && cudaStreamIsCapturing(t.stream, &cs) == cudaSuccess && cs == cudaStreamCaptureStatusNone) {
+    ProfilerExtra* ex = extraOf(comm, true);
+    tp->start = takeEvent(ex);
+    tp->stop = takeEvent(ex);
+    if (tp->start && tp->stop) cudaEventRecord(tp->start, t.stream);
+  }
+  (void)cudaGetLastError();
+  return tp;
+}
+
+// Called after the launches: by now the algorithm is known, so the task events carry its name.
+void profilerTaskStop(ncclComm* comm, const Task& t, void* hv, const char* algo, const char* proto, int nCtas) {
+  TaskProfile* tp = (TaskProfile*)hv;
+  ProfilerState* ps = comm->profiler;
+  if (!tp) return;
+  if (!ps) { delete tp; return; }
+  ncclProfilerEventDescr_t d;
+  memset(&d, 0, sizeof(d));
+  d.type = ncclProfileGroup;
+  tp->group = profStart(comm, &d);
+  memset(&d, 0, sizeof(d));
+  d.parentObj = tp->group;
+  if (t.func == FUNC_SEND || t.func == FUNC_RECV) {
+    d.type = ncclProfileP2p;
+    d.p2p.func = funcName(t.func);
+    d.p2p.buff = t.func == FUNC_SEND ? (void*)t.send : t.recv;
+    d.p2p.datatype = typeName(t.type);
+    d.p2p.count = t.count;
+    d.p2p.peer = t.root;
+    d.p2p.nChannels = (uint8_t)std::min(nCtas, 255);
+    d.p2p.parentGroup = tp->group;
+  } else {
+    d.type = ncclProfileColl;
+    d.coll.seqNumber = t.func < FUNC_COUNT ? ps->seq[t.func]++ : 0;
+    d.coll.func = funcName(t.func);
+    d.coll.sendBuff = t.send;
+    d.coll.recvBuff = t.recv;
+    d.coll.count = t.count;
+    d.coll.root = t.root;
+    d.coll.datatype = typeName(t.type);
+    d.coll.nChannels = (uint8_t)std::min(nCtas, 255);
+    d.coll.nWarps = 16;
+    d.coll.algo = algo;
+    d.coll.proto = proto;
+    d.coll.parentGroup = tp->group;
+  }
+  tp->coll = profStart(comm, &d);
+  memset(&d, 0, sizeof(d));
+  d.type = ncclProfileKernelLaunch;
+  d.parentObj = tp->coll;
+  d.kernelLaunch.stream = (void*)t.stream;
+  tp->launch = profStart(comm, &d);
+  profStop(comm, tp->launch);
+  if (tp->start && tp->stop) {
+    cudaEventRecord(tp->stop, t.stream);
+    ProfilerExtra* ex = extraOf(comm, true);
+    std::lock_guard<std::mutex> g(ex->lock);
+    ex->pending.push_back(PendingKernel{tp->start, tp->stop, tp->coll, tp->group, tp->hostStartNs});
+  } else {
+    profStop(comm, tp->coll);
+    profStop(comm, tp->group);
+  }
+  (void)cudaGetLastError();
+  delete tp;
+}
+
+// Closes the task events whose kernels have finished (all of them, waiting, when drain is set).
+void profilerPoll(ncclComm* comm, bool drain) {
+  ProfilerExtra* ex = extraOf(comm, false);
+  if (!ex) return;
+  for (;;) {
+    PendingKernel pk;
+    {
+      std::lock_guard<std::mutex> g(ex->lock);
+      if (ex->pending.empty()) return;
+      pk = ex->pending.front();
+      cudaError_t q = drain ? cudaEventSynchronize(pk.stop) : cudaEventQuery(pk.stop);
+      if (q == cudaErrorNotReady) { (void)cudaGetLastError(); return; }
+      ex->pending.pop_front();
+    }
+    float ms = 0;
+    if (cudaEventElapsedTime(&ms, pk.start, pk.stop) != cudaSuccess) { (void)cudaGetLastError(); ms = 0; }
+    ncclProfilerEventDescr_t d;
+    memset(&d, 0, sizeof(d));
+    d.type = ncclProfileKernelCh;
+    d.parentObj = pk.collHandle;
+    d.kernelCh.channelId = 0;
+    d.kernelCh.pTimer = pk.hostStartNs;
+    void* h = profStart(comm, &d);
+    ncclProfilerEventStateArgs_t a;
+    memset(&a, 0, sizeof(a));
+    a.kernelCh.pTimer = pk.hostStartNs + (uint64_t)(ms * 1e6);
+    profState(comm, h, ncclProfilerKernelChStop, &a);
+    profStop(comm, h);
+    profStop(comm, pk.collHandle);
+    profStop(comm, pk.groupHandle);
+    std::lock_guard<std::mutex> g(ex->lock);
+    ex->pool.push_back(pk.start);
+    ex->pool.push_back(pk.stop);
+  }
+}
+
+void profilerCommInit(ncclComm* comm) { profilerLoad(comm); }
+void profilerCommFini(ncclComm* comm) { profilerUnload(comm); }
+
 }  // namespace b200

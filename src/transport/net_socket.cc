@@ -7,6 +7,8 @@
 // multi-socket striping, which a loopback / single-NIC host path does not need.
 #include <string.h>
 
+#include <deque>
+
 #include "../core/socket.h"
 #include "net.h"
 
@@ -38,9 +40,11 @@ struct Handle {            // what listen() hands to the sender; fits NCCL_NET_H
 static_assert(sizeof(Handle) <= NCCL_NET_HANDLE_MAXSIZE, "handle too large");
 
 struct ListenComm { Socket sock; };
+struct Request;
 struct Comm {
   Socket sock;
   bool isSend;
+  std::deque<Request*> queue;   // requests share one byte stream: only the oldest may move bytes
 };
 struct Request {
   Comm* comm;
@@ -142,6 +146,7 @@ ncclResult_t sIsend(void* sendComm, void* data, size_t size, int, void*, void*, 
   r->data = (char*)data;
   r->size = size;
   r->header = size;
+  r->comm->queue.push_back(r);
   *request = r;
   return ncclSuccess;
 }
@@ -154,6 +159,7 @@ ncclResult_t sIrecv(void* recvComm, int n, void** data, size_t* sizes, int*, voi
   r->data = (char*)data[0];
   r->size = sizes[0];
   r->header = 0;
+  r->comm->queue.push_back(r);
   *request = r;
   return ncclSuccess;
 }
@@ -164,6 +170,7 @@ ncclResult_t sTest(void* request, int* done, int* sizes) {
   Request* r = (Request*)request;
   *done = 0;
   if (!r) { *done = 1; return ncclSuccess; }
+  if (r->comm->queue.front() != r) return ncclSuccess;
   const SockOpKind kind = r->isSend ? SOCK_OP_SEND : SOCK_OP_RECV;
   if (!r->headerDone) {
     NCCLCHECK(sockProgress(kind, &r->comm->sock, &r->header, 8, &r->headerOff));
@@ -182,13 +189,18 @@ ncclResult_t sTest(void* request, int* done, int* sizes) {
   }
   *done = 1;
   if (sizes) sizes[0] = (int)std::min<uint64_t>(r->size, 0x7fffffff);
+  r->comm->queue.pop_front();
   delete r;
   return ncclSuccess;
 }
 
 ncclResult_t sCloseComm(void* comm) {
   Comm* c = (Comm*)comm;
-  if (c) { sockClose(&c->sock); delete c; }
+  if (c) {
+    for (Request* r : c->queue) delete r;
+    sockClose(&c->sock);
+    delete c;
+  }
   return ncclSuccess;
 }
 ncclResult_t sCloseListen(void* listenComm) {

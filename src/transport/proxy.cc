@@ -1,0 +1,263 @@
+// Proxy: the service thread of a communicator that moves host-memory messages through the
+// network backend. Callers post send / receive operations; the thread cuts each into slices,
+// keeps several slices per operation in flight (isend / irecv), polls test(), and marks the
+// operation done. proxyCreate wires a full mesh: every rank listens, handles are all-gathered
+// through the bootstrap ring, lower ranks connect first to higher ones and accept afterwards.
+// Reference parity: src/proxy.cc (ncclProxySaveOp :602, progress loop :954, service thread
+// :1713), src/transport/net.cc (sendProxyProgress :1304-1468, recvProxyProgress :1470-1765).
+#include "net.h"
+
+#include <sched.h>
+#include <unistd.h>
+
+#include "../plugin/plugin.h"
+
+namespace b200 {
+
+B200_PARAM(NetSliceKb, "NCCL_B200_NET_SLICE_KB", 512, "slice size of proxy network operations, KiB");
+B200_PARAM(NetInflight, "NCCL_B200_NET_INFLIGHT", 8, "slices of one proxy operation kept in flight");
+
+static constexpr int kTagNetMesh = BS_TAG_USER + 7;
+
+static void profProxyOp(Proxy* p, ProxyOp* op, bool start) {
+  ncclComm* comm = p->comm;
+  if (!comm->profiler) return;
+  if (start) {
+    ncclProfilerEventDescr_t d;
+    memset(&d, 0, sizeof(d));
+    d.type = ncclProfileProxyOp;
+    d.proxyOp.pid = getpid();
+    d.proxyOp.peer = op->peer;
+    d.proxyOp.nSteps = (int)((op->bytes + p->sliceBytes - 1) / p->sliceBytes);
+    d.proxyOp.chunkSize = (int)std::min<size_t>(p->sliceBytes, op->bytes);
+    d.proxyOp.isSend = op->isSend ? 1 : 0;
+    op->profHandle = profStart(comm, &d);
+  } else if (op->profHandle) {
+    profStop(comm, op->profHandle);
+    op->profHandle = nullptr;
+  }
+}
+
+static ncclResult_t progressOp(Proxy* p, ProxyOp* op) {
+  ncclNet_t* net = p->net;
+  // post new slices
+  while (op->posted < op->bytes && op->tail - op->head < p->maxInflight) {
+    size_t n = std::min(p->sliceBytes, op->bytes - op->posted);
+    void* req = nullptr;
+    char* ptr = op->data + op->posted;
+    if (op->isSend) {
+      NCCLCHECK(net->isend(p->sendComm[op->peer], ptr, n, 0, nullptr, nullptr, &req));
+    } else {
+      void* ptrs[1] = {ptr};
+      size_t sizes[1] = {n};
+      int tags[1] = {0};
+      void* mh[1] = {nullptr};
+      void* ph[1] = {nullptr};
+      NCCLCHECK(net->irecv(p->recvComm[op->peer], 1, ptrs, sizes, tags, mh, ph, &req));
+    }
+    if (!req) break;   // the backend is out of request slots: try again later
+    int slot = op->tail % NCCL_NET_MAX_REQUESTS;
+    op->requests[slot] = req;
+    op->reqBytes[slot] = n;
+    op->tail++;
+    op->posted += n;
+    p->steps++;
+  }
+  // complete in order
+  while (op->head < op->tail) {
+    int slot = op->head % NCCL_NET_MAX_REQUESTS;
+    int done = 0, size = 0;
+    NCCLCHECK(net->test(op->requests[slot], &done, &size));
+    if (!done) break;
+    op->completed += op->reqBytes[slot];
+    p->bytesMoved += op->reqBytes[slot];
+    op->head++;
+  }
+  // zero-byte operations still exchange one empty message so that both sides match
+  if (op->bytes == 0 && op->posted == 0 && op->tail == 0) {
+    void* req = nullptr;
+    static char dummy;
+    if (op->isSend) NCCLCHECK(net->isend(p->sendComm[op->peer], &dummy, 0, 0, nullptr, nullptr, &req));
+    else {
+      void* ptrs[1] = {&dummy};
+      size_t sizes[1] = {0};
+      int tags[1] = {0};
+      void* mh[1] = {nullptr};
+      void* ph[1] = {nullptr};
+      NCCLCHECK(net->irecv(p->recvComm[op->peer], 1, ptrs, sizes, tags, mh, ph, &req));
+    }
+    if (req) { op->requests[0] = req; op->reqBytes[0] = 0; op->tail = 1; }
+  }
+  return ncclSuccess;
+}
+
+static bool opFinished(const ProxyOp* op) { return op->head == op->tail && op->posted >= op->bytes && (op->bytes > 0 || op->tail > 0); }
+
+static void proxyMain(Proxy* p) {
+  setThreadName("NCCL Proxy %d", p->comm->rank);
+  std::vector<ProxyOp*> active;
+  uint64_t idle = 0;
+  for (;;) {
+    {
+      std::unique_lock<std::mutex> lk(p->lock);
+      if (active.empty()) p->wake.wait(lk, [&] { return p->stop || !p->ops.empty(); });
+      while (!p->ops.empty()) {
+        active.push_back(p->ops.front());
+        p->ops.pop_front();
+        profProxyOp(p, active.back(), true);
+      }
+      if (p->stop && active.empty()) return;
+    }
+    const bool aborted = p->comm->abortFlag && __atomic_load_n(p->comm->abortFlag, __ATOMIC_RELAXED);
+    bool progressed = false;
+    // Two operations of one direction towards one peer share a byte stream: only the oldest may run.
+    for (size_t i = 0; i < active.size();) {
+      ProxyOp* op = active[i];
+      bool blocked = false;
+      for (size_t j = 0; j < i; ++j) if (active[j]->peer == op->peer && active[j]->isSend == op->isSend) blocked = true;
+      ncclResult_t r = ncclSuccess;
+      size_t before = op->completed + op->posted;
+      if (aborted) r = ncclInternalError;
+      else if (!blocked) r = progressOp(p, op);
+      if (op->completed + op->posted != before) progressed = true;
+      if (r != ncclSuccess) {
+        profProxyOp(p, op, false);
+        op->state.store(-(int)r, std::memory_order_release);
+        active.erase(active.begin() + i);
+        p->wake.notify_all();
+        continue;
+      }
+      if (!blocked && opFinished(op)) {
+        profProxyOp(p, op, false);
+        p->opsDone++;
+        op->state.store(1, std::memory_order_release);
+        active.erase(active.begin() + i);
+        p->wake.notify_all();
+        progressed = true;
+        continue;
+      }
+      ++i;
+    }
+    if (progressed) idle = 0;
+    else if (++idle > 200) usleep(20);   // nothing moved for a while: stop burning the core
+  }
+}
+
+ncclResult_t proxyCreate(ncclComm* comm) {
+  Proxy* p = new Proxy;
+  p->comm = comm;
+  ncclResult_t res = netSelect(&p->net, &p->external);
+  if (res != ncclSuccess) { delete p; return res; }
+  const int n = comm->nRanks, me = comm->rank;
+  ncclNetCommConfig_t cfg = {NCCL_NET_TRAFFIC_CLASS_UNDEF};
+  if (comm->config.trafficClass != NCCL_CONFIG_UNDEF_INT) cfg.trafficClass = comm->config.trafficClass;
+  NCCLCHECKGOTO(p->net->init(&p->netCtx, comm->commHash, &cfg, pluginLogger, nullptr), res, fail);
+  {
+    int ndev = 0;
+    NCCLCHECKGOTO(p->net->devices(&ndev), res, fail);
+    if (ndev <= 0) { WARN("network backend %s has no device", p->net->name); res = ncclSystemError; goto fail; }
+    p->dev = 0;
+    p->sliceBytes = (size_t)std::max<int64_t>(paramNetSliceKb(), 4) << 10;
+    p->maxInflight = (int)std::min<int64_t>(std::max<int64_t>(paramNetInflight(), 1), NCCL_NET_MAX_REQUESTS);
+    std::vector<char> handles((size_t)n * NCCL_NET_HANDLE_MAXSIZE, 0);
+    NCCLCHECKGOTO(p->net->listen(p->netCtx, p->dev, handles.data() + (size_t)me * NCCL_NET_HANDLE_MAXSIZE, &p->listenComm), res, fail);
+    NCCLCHECKGOTO(bootstrapAllGather(comm->bootstrap, handles.data(), NCCL_NET_HANDLE_MAXSIZE), res, fail);
+    p->sendComm.assign(n, nullptr);
+    p->recvComm.assign(n, nullptr);
+    // Connects land in the peer's listen queue, so dialling everyone before accepting cannot
+    // deadlock. Each accepted connection says who dialled with a first 4-byte message.
+    for (int r = 0; r < n; ++r) {
+      if (r == me) continue;
+      void* sc = nullptr;
+      while (!sc) {
+        NCCLCHECKGOTO(p->net->connect(p->netCtx, p->dev, handles.data() + (size_t)r * NCCL_NET_HANDLE_MAXSIZE, &sc, nullptr), res, fail);
+        if (comm->abortFlag && *comm->abortFlag) { res = ncclInternalError; goto fail; }
+      }
+      p->sendComm[r] = sc;
+      int hello = me, done = 0;
+      void* req = nullptr;
+      while (!req) NCCLCHECKGOTO(p->net->isend(sc, &hello, sizeof(hello), 0, nullptr, nullptr, &req), res, fail);
+      while (!done) NCCLCHECKGOTO(p->net->test(req, &done, nullptr), res, fail);
+    }
+    for (int k = 0; k < n - 1; ++k) {
+      void* rc = nullptr;
+      while (!rc) {
+        NCCLCHECKGOTO(p->net->accept(p->listenComm, &rc, nullptr), res, fail);
+        if (comm->abortFlag && *comm->abortFlag) { res = ncclInternalError; goto fail; }
+      }
+      int hello = -1, done = 0;
+      void* req = nullptr;
+      void* ptrs[1] = {&hello};
+      size_t sizes[1] = {sizeof(hello)};
+      int tags[1] = {0};
+      void* mh[1] = {nullptr};
+      void* ph[1] = {nullptr};
+      while (!req) NCCLCHECKGOTO(p->net->irecv(rc, 1, ptrs, sizes, tags, mh, ph, &req), res, fail);
+      while (!done) NCCLCHECKGOTO(p->net->test(req, &done, nullptr), res, fail);
+      if (hello < 0 || hello >= n || hello == me || p->recvComm[hello]) { WARN("proxy: unexpected peer %d on the network mesh", hello); res = ncclInternalError; goto fail; }
+      p->recvComm[hello] = rc;
+    }
+  }
+  p->thread = std::thread(proxyMain, p);
+  comm->proxy = p;
+  INFO(SUB_PROXY | SUB_NET, "proxy of rank %d: %s mesh to %d peers, %zu KiB slices, %d in flight", me, p->net->name, n - 1, p->sliceBytes >> 10, p->maxInflight);
+  return ncclSuccess;
+fail:
+  comm->proxy = p;
+  proxyDestroy(comm);
+  return res;
+}
+
+void proxyDestroy(ncclComm* comm) {
+  Proxy* p = comm->proxy;
+  if (!p) return;
+  if (p->thread.joinable()) {
+    {
+      std::lock_guard<std::mutex> g(p->lock);
+      p->stop = true;
+    }
+    p->wake.notify_all();
+    p->thread.join();
+  }
+  if (p->net) {
+    for (void* c : p->sendComm) if (c) p->net->closeSend(c);
+    for (void* c : p->recvComm) if (c) p->net->closeRecv(c);
+    if (p->listenComm) p->net->closeListen(p->listenComm);
+    if (p->net->finalize) p->net->finalize(p->netCtx);
+  }
+  delete p;
+  comm->proxy = nullptr;
+}
+
+ProxyOp* proxyPost(Proxy* p, bool isSend, int peer, void* data, size_t bytes) {
+  ProxyOp* op = new ProxyOp;
+  op->isSend = isSend;
+  op->peer = peer;
+  op->data = (char*)data;
+  op->bytes = bytes;
+  {
+    std::lock_guard<std::mutex> g(p->lock);
+    p->ops.push_back(op);
+  }
+  p->wake.notify_all();
+  return op;
+}
+
+ncclResult_t proxyWait(Proxy* p, ProxyOp** ops, int n) {
+  ncclResult_t res = ncclSuccess;
+  for (int i = 0; i < n; ++i) {
+    ProxyOp* op = ops[i];
+    int spins = 0;
+    while (op->state.load(std::memory_order_acquire) == 0) {
+      if (++spins < 2000) { sched_yield(); continue; }
+      std::unique_lock<std::mutex> lk(p->lock);
+      p->wake.wait_for(lk, std::chrono::milliseconds(1), [&] { return op->state.load(std::memory_order_acquire) != 0; });
+    }
+    int st = op->state.load(std::memory_order_acquire);
+    if (st < 0 && res == ncclSuccess) res = (ncclResult_t)(-st);
+    delete op;
+  }
+  return res;
+}
+
+}  // namespace b200

@@ -1,0 +1,94 @@
+"""Plugin system on CPU ranks: environment, tuner, profiler (inspector and trace) and network
+plugins are loaded from the in-tree example libraries and observed through their side effects."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from mp_util import run_ranks
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PLUG = os.path.join(ROOT, "nccl_b200", "lib", "plugins")
+BASE = {"NCCL_B200_HOST_ONLY": "1", "NCCL_SOCKET_IFNAME": "lo"}
+
+
+def _rank(rank, nranks, uid, n_iter):
+    from nccl_b200 import Communicator, group
+    comm = Communicator(nranks, rank, uid)
+    x = np.full(1 << 16, rank + 1, dtype=np.float32)
+    y = np.zeros_like(x)
+    for _ in range(n_iter):
+        comm.all_reduce(x, y)
+    g = np.zeros(nranks * 128, dtype=np.float32)
+    comm.all_gather(x[:128], g)
+    peer = (rank + 1) % nranks
+    r = np.zeros(256, dtype=np.float32)
+    with group():
+        comm.send(x[:256], peer)
+        comm.recv(r, (rank - 1) % nranks)
+    comm.destroy()
+    return float(y[0]), float(g[-1]), float(r[0])
+
+
+def _check(res, n):
+    for r in range(n):
+        assert res[r][0] == n * (n + 1) / 2
+        assert res[r][1] == n
+        assert res[r][2] == (r - 1) % n + 1
+
+
+def test_inspector_plugin_writes_records(tmp_path):
+    env = dict(BASE, NCCL_PROFILER_PLUGIN=os.path.join(PLUG, "profiler", "inspector.so"), NCCL_INSPECTOR_DUMP_DIR=str(tmp_path),
+               NCCL_INSPECTOR_PROM_DUMP="1", NCCL_INSPECTOR_DUMP_THREAD_INTERVAL_MICROSECONDS="50000")
+    _check(run_ranks(_rank, 2, args=(3,), env=env), 2)
+    files = sorted(p for p in os.listdir(tmp_path) if p.endswith(".jsonl"))
+    assert len(files) == 2
+    recs = [json.loads(line) for line in open(os.path.join(tmp_path, files[0]))]
+    ar = [r for r in recs if r["func"] == "AllReduce"]
+    assert len(ar) == 3 and [r["seq"] for r in ar] == [0, 1, 2]
+    assert ar[0]["bytes"] == (1 << 16) * 4 and ar[0]["bus_bw_gbs"] > 0 and ar[0]["nranks"] == 2
+    assert any(r["kind"] == "p2p" and r["func"] == "Send" for r in recs)
+    prom = [p for p in os.listdir(tmp_path) if p.endswith(".prom")]
+    text = open(os.path.join(tmp_path, prom[0])).read()
+    assert "nccl_bus_bandwidth_gbs{" in text and 'collective="AllReduce"' in text and "nccl_p2p_count{" in text
+
+
+def test_trace_plugin_writes_chrome_trace(tmp_path):
+    env = dict(BASE, NCCL_PROFILER_PLUGIN=os.path.join(PLUG, "profiler", "trace.so"), NCCL_PROFILE_DUMP_FILE=str(tmp_path / "trace"))
+    _check(run_ranks(_rank, 2, args=(1,), env=env), 2)
+    files = [p for p in os.listdir(tmp_path) if p.endswith(".json")]
+    assert len(files) == 2
+    ev = json.load(open(os.path.join(tmp_path, files[0])))
+    cats = {e["cat"] for e in ev}
+    assert {"CollApi", "Coll", "P2pApi", "P2p", "GroupApi"} <= cats
+    assert all(e["dur"] >= 0 for e in ev)
+
+
+def test_env_plugin_supplies_settings(tmp_path):
+    conf = tmp_path / "settings"
+    dump = tmp_path / "insp"
+    dump.mkdir()
+    # the profiler plugin is configured only inside the file: it loads only if the env plugin is consulted
+    conf.write_text("NCCL_PROFILER_PLUGIN=%s\n" % os.path.join(PLUG, "profiler", "inspector.so"))
+    env = dict(BASE, NCCL_ENV_PLUGIN=os.path.join(PLUG, "env", "file_env.so"), NCCL_ENV_PLUGIN_FILE=str(conf), NCCL_INSPECTOR_DUMP_DIR=str(dump))
+    _check(run_ranks(_rank, 2, args=(1,), env=env), 2)
+    assert len([p for p in os.listdir(dump) if p.endswith(".jsonl")]) == 2
+
+
+def test_net_plugin_carries_host_traffic(tmp_path):
+    env = dict(BASE, NCCL_NET_PLUGIN=os.path.join(PLUG, "net", "unix_net.so"), NCCL_DEBUG="INFO", NCCL_DEBUG_SUBSYS="NET,INIT",
+               NCCL_DEBUG_FILE=str(tmp_path / "log.%p"))
+    _check(run_ranks(_rank, 3, args=(2,), env=env), 3)
+    logs = "".join(open(os.path.join(tmp_path, p)).read() for p in os.listdir(tmp_path))
+    assert "network backend: plugin UnixExample" in logs
+
+
+def test_builtin_socket_backend_through_proxy():
+    env = dict(BASE, NCCL_B200_HOST_NET="1")
+    _check(run_ranks(_rank, 3, args=(2,), env=env), 3)
+
+
+def test_missing_plugin_falls_back(tmp_path):
+    env = dict(BASE, NCCL_TUNER_PLUGIN="does-not-exist", NCCL_NET_PLUGIN="none")
+    _check(run_ranks(_rank, 2, args=(1,), env=env), 2)
