@@ -22,6 +22,9 @@
 
 namespace b200 {
 
+bool rasListenAddr(SockAddr* out);   // ras/ras.cc
+
+
 B200_PARAM(StaggerRate, "UID_STAGGER_RATE", 7000, "Rank check-ins per second above the stagger threshold")
 B200_PARAM(StaggerThreshold, "UID_STAGGER_THRESHOLD", 256, "Ranks per root above which check-ins are staggered")
 B200_PARAM(RasEnable, "RAS_ENABLE", 1, "Start the reliability/availability/serviceability thread")
@@ -297,6 +300,10 @@ ncclResult_t bootstrapInit(int nHandles, const void* handles, int rank, int nran
   NCCLCHECKGOTO(listenOn(&b->peerListen, b->magic, SOCK_BOOTSTRAP, b->abortFlag, nullptr), ret, fail);
   memset(&ras, 0, sizeof(ras));
   ras.addr = gIfAddr;
+  if (paramRasEnable()) {
+    SockAddr ra;
+    if (rasListenAddr(&ra)) ras.addr = ra;   // port 0 (the bare interface address) tells peers that this rank runs without RAS
+  }
   ras.pid = (int)getpid();
   ras.cudaDev = args.cudaDev;
   ras.nvmlDev = args.nvmlDev;

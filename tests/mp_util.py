@@ -21,8 +21,9 @@ def _entry(fn, rank, nranks, uid_conn, result_q, env, args):
         result_q.put((rank, "error", "%s\n%s" % (e, traceback.format_exc())))
 
 
-def run_ranks(fn, nranks, args=(), env=None, timeout=120, make_uid=None, expect_fail=()):
-    """fn(rank, nranks, uid_bytes, *args) runs in nranks processes; returns {rank: result}."""
+def run_ranks(fn, nranks, args=(), env=None, timeout=120, make_uid=None, expect_fail=(), may_exit=()):
+    """fn(rank, nranks, uid_bytes, *args) runs in nranks processes; returns {rank: result}.
+    Ranks listed in may_exit are allowed to leave (os._exit) without reporting a result."""
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     env = dict(env or {})
@@ -39,7 +40,7 @@ def run_ranks(fn, nranks, args=(), env=None, timeout=120, make_uid=None, expect_
         pipes[r][1].send(uid)
     results = {}
     try:
-        for _ in range(nranks):
+        for _ in range(nranks - len(may_exit)):
             rank, status, out = q.get(timeout=timeout)
             if status != "ok" and rank not in expect_fail:
                 raise AssertionError("rank %d failed: %s" % (rank, out))

@@ -1,0 +1,95 @@
+"""RAS thread: status reports through the client socket, operation-count mismatch detection, and
+dead-process detection after a rank's process has gone away (host-side failure, no GPU)."""
+import json
+import os
+import socket
+import subprocess
+import time
+
+import numpy as np
+
+from mp_util import run_ranks
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+NCCLRAS = os.path.join(ROOT, "nccl_b200", "bin", "ncclras")
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _query(port, fmt="json", verbose=False):
+    cmd = [NCCLRAS, "-h", "127.0.0.1", "-p", str(port), "-t", "2", "-f", fmt] + (["-v"] if verbose else [])
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=60).stdout
+
+
+def _status_rank(rank, nranks, uid, port):
+    from nccl_b200 import Communicator
+    comm = Communicator(nranks, rank, uid)
+    x = np.ones(1024, dtype=np.float32)
+    for _ in range(3):
+        comm.all_reduce(x.copy(), x)
+    out = None
+    if rank == 0:
+        time.sleep(0.3)
+        out = (_query(port, "json"), _query(port, "text", verbose=True))
+    # everyone stays until rank 0 has its report
+    comm.all_reduce(np.ones(4, dtype=np.float32))
+    comm.destroy()
+    return out
+
+
+def test_status_report():
+    port = _free_port()
+    env = {"NCCL_B200_HOST_ONLY": "1", "NCCL_SOCKET_IFNAME": "lo", "NCCL_RAS_ADDR": "127.0.0.1:%d" % port}
+    res = run_ranks(_status_rank, 3, args=(port,), env=env)
+    js, text = res[0]
+    rep = json.loads(js)
+    assert rep["job"]["processes"] == 3 and rep["job"]["dead_processes"] == 0
+    assert len(rep["communicators"]) == 1
+    c = rep["communicators"][0]
+    assert c["nranks"] == 3 and c["status"] == "RUNNING" and c["missing_ranks"] == 0 and c["op_count"] >= 3
+    assert "Job summary" in text and "Communicators" in text and "rank 2: pid" in text
+
+
+def _dead_rank(rank, nranks, uid, port, done_file):
+    from nccl_b200 import Communicator
+    comm = Communicator(nranks, rank, uid)
+    comm.all_reduce(np.ones(16, dtype=np.float32))
+    if rank == 2:
+        os._exit(0)     # leaves between steps, nothing in flight; its RAS thread dies with it
+    out = None
+    if rank == 0:
+        deadline = time.time() + 30
+        while time.time() < deadline:
+            raw = _query(port, "json")
+            if not raw:      # the process that served the client port has just gone; another one takes it over
+                time.sleep(0.3)
+                continue
+            rep = json.loads(raw)
+            if rep["job"]["dead_processes"] >= 1:
+                out = rep
+                break
+            time.sleep(0.3)
+        open(done_file, "w").close()
+    else:
+        deadline = time.time() + 40
+        while not os.path.exists(done_file) and time.time() < deadline:   # stay alive until rank 0 has its report
+            time.sleep(0.1)
+    return out
+
+
+def test_dead_process_is_reported(tmp_path):
+    port = _free_port()
+    env = {"NCCL_B200_HOST_ONLY": "1", "NCCL_SOCKET_IFNAME": "lo", "NCCL_RAS_ADDR": "127.0.0.1:%d" % port,
+           "NCCL_B200_RAS_KEEPALIVE_MS": "100", "NCCL_B200_RAS_DEAD_AFTER": "3"}
+    res = run_ranks(_dead_rank, 3, args=(port, str(tmp_path / "done")), env=env, timeout=120, may_exit=(2,))
+    rep = res[0]
+    assert rep is not None, "the dead process was never reported"
+    assert rep["job"]["dead_processes"] == 1 and rep["job"]["processes"] == 2
+    assert rep["communicators"][0]["status"] == "INCOMPLETE" and rep["communicators"][0]["missing_ranks"] == 1
+    assert any("DEAD" in e for e in rep["errors"])
