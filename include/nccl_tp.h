@@ -36,6 +36,22 @@ ncclResult_t ncclTpGemm(ncclTp_t tp, const void* A, const void* W, void* C, int 
 ncclResult_t ncclTpGemmReduceScatter(ncclTp_t tp, const void* A, const void* W, void* out, int M, int N, int K, cudaStream_t stream);
 ncclResult_t ncclTpAllGatherGemm(ncclTp_t tp, void* gatheredA, const void* W, void* C, int M, int N, int K, cudaStream_t stream);
 
+/* ---- block-scaled fp8 (e4m3) variants, fp32 accumulation, bf16 output --------------------------
+ * Activations carry one fp32 scale per row and 128 columns, stored K-block-major: scaleA[K/128][M].
+ * Weights carry one scale per 128 x 128 block: scaleW[K/128][N/128]. x ~= q * scale.
+ * M multiple of 128 * nRanks, N of 256, K of 128. */
+/* Quantises a row-major bf16 matrix [rows, K]: blockRows 1 (activations) or 128 (weights). */
+ncclResult_t ncclTpQuantizeFp8(ncclTp_t tp, const void* x, void* q, float* scales, int rows, int K, int blockRows, cudaStream_t stream);
+ncclResult_t ncclTpGemmFp8(ncclTp_t tp, const void* A, const float* scaleA, const void* W, const float* scaleW, void* C, int M, int N, int K,
+                           cudaStream_t stream);
+ncclResult_t ncclTpGemmReduceScatterFp8(ncclTp_t tp, const void* A, const float* scaleA, const void* W, const float* scaleW, void* out, int M, int N,
+                                        int K, cudaStream_t stream);
+/* Symmetric activation window for ncclTpAllGatherGemmFp8: rows x cols e4m3 followed by its scales
+ * [cols/128][rows]; every rank fills its own rows and their scales before the call. Collective.
+ * Free with ncclTpFreeGathered(tp, *q). */
+ncclResult_t ncclTpAllocGatheredFp8(ncclTp_t tp, size_t rows, size_t cols, void** q, float** scales);
+ncclResult_t ncclTpAllGatherGemmFp8(ncclTp_t tp, void* gatheredA, const void* W, const float* scaleW, void* C, int M, int N, int K, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -40,28 +40,6 @@ constexpr uint32_t kStageBytes = kStageABytes + kStageBBytes;
 constexpr uint32_t kTmemCols = 512;
 constexpr size_t kTpSmemBytes = 1024 + (size_t)STAGES * kStageBytes + 256;
 
-struct TileCoord { int mBlk, nBlk, owner; };
-
-__device__ __forceinline__ TileCoord tileOf(const TpGemmArgs& a, int t) {
-  const int tilesN = a.N / BN;
-  TileCoord c;
-  if (a.mode == TP_MODE_STORE || a.nRanks == 1) {
-    c.mBlk = t / tilesN;
-    c.nBlk = t % tilesN;
-    c.owner = a.rank;
-    if (a.mode == TP_MODE_REDUCE) c.owner = 0;
-    return c;
-  }
-  const int tilesMPerRank = a.M / a.nRanks / BM;
-  const int per = tilesMPerRank * tilesN;
-  const int step = t / per, j = t % per;
-  const int who = a.mode == TP_MODE_REDUCE ? (a.rank + 1 + step) % a.nRanks : (a.rank + step) % a.nRanks;
-  c.owner = who;
-  c.mBlk = who * tilesMPerRank + j / tilesN;
-  c.nBlk = j % tilesN;
-  return c;
-}
-
 __global__ void __launch_bounds__(kTpThreads, 1)
 tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ TpGemmArgs a) {
   extern __shared__ uint8_t smemRaw[];

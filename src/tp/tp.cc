@@ -42,16 +42,16 @@ static EncodeTiledFn encodeFn() {
   return fn;
 }
 
-// Row-major [rows, K] bf16 tensor, tiles of boxRows x 64 elements with 128-byte swizzle.
-static ncclResult_t makeMap(CUtensorMap* map, const void* base, int rows, int K, int boxRows) {
+// Row-major [rows, K] tensor of bf16 (elemBytes 2) or fp8 (1), tiles of boxRows x 128 bytes with 128-byte swizzle.
+static ncclResult_t makeMap(CUtensorMap* map, const void* base, int rows, int K, int boxRows, int elemBytes = 2) {
   EncodeTiledFn enc = encodeFn();
   if (!enc) { WARN("cuTensorMapEncodeTiled is not available"); return ncclUnhandledCudaError; }
   if ((uintptr_t)base & 15) { WARN("tensor-parallel GEMM operands must be 16-byte aligned"); return ncclInvalidArgument; }
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)boxRows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * elemBytes};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / elemBytes), (cuuint32_t)boxRows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  CUresult r = enc(map, elemBytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { WARN("cuTensorMapEncodeTiled failed (%d)", (int)r); return ncclUnhandledCudaError; }
   return ncclSuccess;
@@ -98,7 +98,142 @@ static ncclResult_t launchGemm(ncclTpContext* tp, const void* A, const void* W, 
   return ncclSuccess;
 }
 
+static ncclResult_t launchGemmFp8(ncclTpContext* tp, const void* A, const void* W, TpGemmArgs* a, int grid, cudaStream_t stream) {
+  static bool attrSet = false;
+  if (!attrSet) {
+    CUDACHECK(cudaFuncSetAttribute(tpGemmFp8KernelFn(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tpGemmFp8SmemBytes()));
+    attrSet = true;
+  }
+  CUtensorMap tmA, tmB;
+  NCCLCHECK(makeMap(&tmA, A, a->M, a->K, 128, 1));
+  NCCLCHECK(makeMap(&tmB, W, a->N, a->K, 256, 1));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(tpGemmFp8Threads());
+  cfg.dynamicSmemBytes = tpGemmFp8SmemBytes();
+  cfg.stream = stream;
+  void* args[3] = {&tmA, &tmB, a};
+  cudaError_t e = cudaLaunchKernelExC(&cfg, tpGemmFp8KernelFn(), args);
+  if (e != cudaSuccess) { WARN("fp8 tensor-parallel GEMM launch failed: %s", cudaGetErrorString(e)); (void)cudaGetLastError(); return ncclUnhandledCudaError; }
+  if (tp->comm->devPlane) tp->comm->devPlane->launches++;
+  return ncclSuccess;
+}
+
+static ncclResult_t checkShapeFp8(int M, int N, int K, int n) {
+  if (M <= 0 || N <= 0 || K <= 0 || M % (128 * n) || N % 256 || K % 128) {
+    WARN("fp8 tensor-parallel GEMM: M=%d must be a multiple of %d, N=%d of 256, K=%d of 128", M, 128 * n, N, K);
+    return ncclInvalidArgument;
+  }
+  return ncclSuccess;
+}
+
 extern "C" {
+
+ncclResult_t ncclTpQuantizeFp8(ncclTp_t tp, const void* x, void* q, float* scales, int rows, int K, int blockRows, cudaStream_t stream) {
+  if (!tp || !x || !q || !scales || rows <= 0 || K <= 0 || K % 128 || (blockRows != 1 && blockRows != 128)) return ncclInvalidArgument;
+  if (blockRows == 128 && rows % 128) return ncclInvalidArgument;
+  if (((uintptr_t)x & 7) || ((uintptr_t)q & 3)) return ncclInvalidArgument;
+  void* args[5] = {(void*)&x, &q, &scales, &rows, &K};
+  if (blockRows == 1) {
+    size_t warps = (size_t)rows * (K / 128);
+    int ctas = (int)std::min<size_t>((warps + 7) / 8, (size_t)tp->smCount * 16);
+    CUDACHECK(cudaLaunchKernel(tpQuantRowsKernelFn(), dim3(std::max(ctas, 1)), dim3(256), args, 0, stream));
+  } else {
+    int blocks = (rows / 128) * (K / 128);
+    CUDACHECK(cudaLaunchKernel(tpQuantBlocksKernelFn(), dim3(std::min(blocks, tp->smCount * 8)), dim3(256), args, 0, stream));
+  }
+  if (tp->comm->devPlane) tp->comm->devPlane->launches++;
+  return ncclSuccess;
+}
+
+ncclResult_t ncclTpGemmFp8(ncclTp_t tp, const void* A, const float* scaleA, const void* W, const float* scaleW, void* C, int M, int N, int K, cudaStream_t stream) {
+  if (!tp || !A || !W || !C || !scaleA || !scaleW) return ncclInvalidArgument;
+  NCCLCHECK(checkShapeFp8(M, N, K, 1));
+  TpGemmArgs a;
+  memset(&a, 0, sizeof(a));
+  a.C = C; a.ldc = N; a.M = M; a.N = N; a.K = K;
+  a.mode = TP_MODE_STORE;
+  a.rank = tp->comm->rank; a.nRanks = tp->comm->nRanks;
+  a.scaleA = scaleA; a.scaleW = scaleW;
+  fillSyncTp(tp->comm, &a.sync);
+  int tiles = (M / 128) * (N / 256);
+  return launchGemmFp8(tp, A, W, &a, std::min(tp->smCount, tiles), stream);
+}
+
+ncclResult_t ncclTpGemmReduceScatterFp8(ncclTp_t tp, const void* A, const float* scaleA, const void* W, const float* scaleW, void* out, int M, int N, int K,
+                                        cudaStream_t stream) {
+  if (!tp || !A || !W || !out || !scaleA || !scaleW) return ncclInvalidArgument;
+  ncclComm* comm = tp->comm;
+  const int n = comm->nRanks;
+  NCCLCHECK(checkShapeFp8(M, N, K, n));
+  NCCLCHECK(devPlaneCheckStatus(comm));
+  if (n == 1) return ncclTpGemmFp8(tp, A, scaleA, W, scaleW, out, M, N, K, stream);
+  const size_t need = (size_t)(M / n) * N * sizeof(float);
+  if (need > tp->accumBytes) { WARN("ncclTpGemmReduceScatterFp8: %d x %d exceeds the context's accumulation window", M, N); return ncclInvalidArgument; }
+  CUDACHECK(cudaMemsetAsync(tp->accum, 0, need, stream));
+  TpGemmArgs a;
+  memset(&a, 0, sizeof(a));
+  a.M = M; a.N = N; a.K = K;
+  a.mode = TP_MODE_REDUCE;
+  a.rank = comm->rank; a.nRanks = n;
+  a.scaleA = scaleA; a.scaleW = scaleW;
+  for (int p = 0; p < n; ++p) a.accum[p] = (float*)tp->accumWin->host.peerPtr[p];
+  fillSyncTp(comm, &a.sync);
+  int tiles = (M / 128) * (N / 256);
+  NCCLCHECK(launchGemmFp8(tp, A, W, &a, std::min(tp->smCount, tiles), stream));
+  size_t count = (size_t)(M / n) * N;
+  int ctas = (int)std::min<size_t>((count / 8 + 255) / 256, (size_t)tp->smCount * 8);
+  const float* acc = tp->accum;
+  void* args[3] = {(void*)&acc, &out, &count};
+  CUDACHECK(cudaLaunchKernel(tpConvertKernelFn(), dim3(ctas), dim3(256), args, 0, stream));
+  if (comm->devPlane) comm->devPlane->launches++;
+  return ncclSuccess;
+}
+
+ncclResult_t ncclTpAllocGatheredFp8(ncclTp_t tp, size_t rows, size_t cols, void** q, float** scales) {
+  if (!tp || !q || !scales || cols % 128) return ncclInvalidArgument;
+  // one window: rows x cols bytes of e4m3, then cols/128 x rows fp32 scales
+  const size_t qBytes = (rows * cols + 255) / 256 * 256;
+  const size_t bytes = qBytes + (cols / 128) * rows * sizeof(float);
+  void* p = nullptr;
+  NCCLCHECK(memAlloc(&p, bytes, tp->comm->cudaDev));
+  SymWindow* w = nullptr;
+  if (tp->comm->nRanks > 1) {
+    NCCLCHECK(symWindowRegister(tp->comm, p, bytes, &w, NCCL_WIN_COLL_SYMMETRIC));
+    if (!w->symmetric) { WARN("ncclTpAllocGatheredFp8: window could not be mapped by the peers"); return ncclInternalError; }
+  }
+  tp->gathered[p] = w;
+  *q = p;
+  *scales = (float*)((char*)p + qBytes);
+  return ncclSuccess;
+}
+
+ncclResult_t ncclTpAllGatherGemmFp8(ncclTp_t tp, void* gatheredA, const void* W, const float* scaleW, void* C, int M, int N, int K, cudaStream_t stream) {
+  if (!tp || !gatheredA || !W || !scaleW || !C) return ncclInvalidArgument;
+  ncclComm* comm = tp->comm;
+  const int n = comm->nRanks;
+  NCCLCHECK(checkShapeFp8(M, N, K, n));
+  NCCLCHECK(devPlaneCheckStatus(comm));
+  const size_t scaleOffset = ((size_t)M * K + 255) / 256 * 256;
+  if (n == 1) return ncclTpGemmFp8(tp, gatheredA, (const float*)((char*)gatheredA + scaleOffset), W, scaleW, C, M, N, K, stream);
+  auto it = tp->gathered.find(gatheredA);
+  if (it == tp->gathered.end() || !it->second) { WARN("ncclTpAllGatherGemmFp8: the activation buffer must come from ncclTpAllocGatheredFp8"); return ncclInvalidArgument; }
+  if ((size_t)(M / 128) > tp->maxBlocks) { WARN("ncclTpAllGatherGemmFp8: M=%d exceeds the context's row limit", M); return ncclInvalidArgument; }
+  TpGemmArgs a;
+  memset(&a, 0, sizeof(a));
+  a.C = C; a.ldc = N; a.M = M; a.N = N; a.K = K;
+  a.mode = TP_MODE_GATHER;
+  a.rank = comm->rank; a.nRanks = n;
+  for (int p = 0; p < n; ++p) a.peerA[p] = it->second->host.peerPtr[p];
+  a.scaleOffset = scaleOffset;
+  a.scaleW = scaleW;
+  a.blockFlags = tp->blockFlags;
+  a.flagEpoch = ++tp->epoch;
+  int commCtas = (int)std::max<int64_t>(1, std::min<int64_t>(paramTpCommCtas(), tp->smCount / 4));
+  a.gemmCtas = tp->smCount - commCtas;
+  fillSyncTp(comm, &a.sync);
+  return launchGemmFp8(tp, gatheredA, W, &a, tp->smCount, stream);
+}
 
 ncclResult_t ncclTpCreate(ncclComm_t comm, size_t maxRows, size_t maxCols, ncclTp_t* out) {
   if (!out) return ncclInvalidArgument;

@@ -22,9 +22,45 @@ struct TpGemmArgs {
   int rank, nRanks;
   int gemmCtas;                   // GATHER: CTAs [0, gemmCtas) compute, the rest gather
   SyncArgs sync;
+  // block-scaled fp8 (e4m3) operands: A scaled per row and 128 columns, W per 128 x 128 block
+  const float* scaleA;            // [K/128][M]   (for GATHER: inside the gathered window, see scaleOffset)
+  const float* scaleW;            // [K/128][N/128]
+  size_t scaleOffset;             // GATHER, fp8: byte offset of the scales inside every rank's activation window
 };
 
+#if defined(__CUDACC__)
+constexpr int kTpBM = 128, kTpBN = 256;
+struct TileCoord { int mBlk, nBlk, owner; };
+// Tile t of this CTA's walk: row-major over the output for plain GEMMs; owner by owner for the
+// fused modes (REDUCE starts with the next rank so that every step each GPU receives from one
+// peer; GATHER starts with the rows that are already local).
+__device__ __forceinline__ TileCoord tileOf(const TpGemmArgs& a, int t) {
+  const int tilesN = a.N / kTpBN;
+  TileCoord c;
+  if (a.mode == TP_MODE_STORE || a.nRanks == 1) {
+    c.mBlk = t / tilesN;
+    c.nBlk = t % tilesN;
+    c.owner = a.rank;
+    if (a.mode == TP_MODE_REDUCE) c.owner = 0;
+    return c;
+  }
+  const int tilesMPerRank = a.M / a.nRanks / kTpBM;
+  const int per = tilesMPerRank * tilesN;
+  const int step = t / per, j = t % per;
+  const int who = a.mode == TP_MODE_REDUCE ? (a.rank + 1 + step) % a.nRanks : (a.rank + step) % a.nRanks;
+  c.owner = who;
+  c.mBlk = who * tilesMPerRank + j / tilesN;
+  c.nBlk = j % tilesN;
+  return c;
+}
+#endif
+
 const void* tpGemmKernelFn();
+const void* tpGemmFp8KernelFn();
+const void* tpQuantRowsKernelFn();     // (const bf16* x, uint8_t* q, float* scales, int rows, int K): 1 x 128 blocks, scales [K/128][rows]
+const void* tpQuantBlocksKernelFn();   // same arguments: 128 x 128 blocks, scales [K/128][rows/128]
+size_t tpGemmFp8SmemBytes();
+int tpGemmFp8Threads();
 const void* tpConvertKernelFn();
 size_t tpGemmSmemBytes();
 int tpGemmThreads();
