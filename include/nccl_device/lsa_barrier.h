@@ -22,17 +22,19 @@ struct ncclLsaBarrierSession {
   __device__ uint32_t* inbox(int owner, int src) const {
     return (uint32_t*)((char*)comm.resource.peerPtr[owner] + comm.lsaBarrierOffset) + (size_t)index * NCCL_DEVICE_MAX_LSA + src;
   }
-  /* Everything the group wrote before arrive() is visible to a peer after its matching wait(). */
-  __device__ void arrive() {
+  /* With release, everything the group wrote before arrive() is visible to a peer after its matching
+   * wait(acquire). A barrier that only announces "this kernel has started" needs neither (data
+   * written by earlier kernels is already visible), and system-scope fences cost microseconds. */
+  __device__ void arrive(bool release = true) {
     coop.sync();
     ++epoch;
     for (int p = coop.thread_rank(); p < comm.lsaSize; p += coop.size()) {
       if (p == comm.lsaRank) continue;
-      nccl_device::fenceAcqRelSys();
-      nccl_device::stReleaseSys(inbox(p, comm.lsaRank), epoch);
+      if (release) nccl_device::fenceAcqRelSys();
+      nccl_device::stRelaxedSys(inbox(p, comm.lsaRank), epoch);
     }
   }
-  __device__ ncclResult_t wait(unsigned long long timeoutCycles = 0) {
+  __device__ ncclResult_t wait(unsigned long long timeoutCycles = 0, bool acquire = true) {
     const unsigned long long budget = timeoutCycles ? timeoutCycles : comm.timeoutCycles;
     ncclResult_t res = ncclSuccess;
     for (int p = coop.thread_rank(); p < comm.lsaSize; p += coop.size()) {
@@ -40,14 +42,15 @@ struct ncclLsaBarrierSession {
       const uint32_t* w = inbox(comm.lsaRank, p);
       const long long start = clock64();
       unsigned spins = 0;
-      while (nccl_device::rollingDiff(nccl_device::ldAcquireSys(w), epoch) < 0) {
+      while (nccl_device::rollingDiff(nccl_device::ldRelaxedSys(w), epoch) < 0) {
         if ((++spins & 0xff) == 0 && ((unsigned long long)(clock64() - start) >= budget || ncclTestAbort(comm))) { res = ncclTimeout; break; }
       }
+      if (acquire) nccl_device::fenceAcqRelSys();
     }
     coop.sync();
     return res;
   }
-  __device__ ncclResult_t sync(unsigned long long timeoutCycles = 0) { arrive(); return wait(timeoutCycles); }
+  __device__ ncclResult_t sync(unsigned long long timeoutCycles = 0, bool release = true, bool acquire = true) { arrive(release); return wait(timeoutCycles, acquire); }
   /* Stores the epoch for the next kernel; call once, by the last user of this index in the kernel. */
   __device__ void finish() { if (coop.thread_rank() == 0) comm.barrierEpochs[index] = epoch; }
 };

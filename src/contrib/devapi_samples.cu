@@ -24,7 +24,7 @@ __global__ void __launch_bounds__(kThreads) devApiAllReduceKernel(ncclDevComm_t 
   using V = nccl_device::Vec16<T>;
   ncclCoopCta cta;
   ncclLsaBarrierSession<ncclCoopCta> bar(cta, dc, ncclTeamLsa(dc), blockIdx.x);
-  if (bar.sync() != ncclSuccess) {
+  if (bar.sync(0, false, false) != ncclSuccess) {
     if (threadIdx.x == 0) atomicExch(status, 1);
     bar.finish();
     return;
@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(kThreads) devApiAllReduceKernel(ncclDevComm_t 
       for (int p = 0; p < n; ++p) *(uint4*)((char*)ncclGetLsaPointer(recvWin, recvOff, (dc.lsaRank + p) % n) + i * 16) = r;
     }
   }
-  if (bar.sync() != ncclSuccess && threadIdx.x == 0) atomicExch(status, 2);
+  if (bar.sync(0, true, false) != ncclSuccess && threadIdx.x == 0) atomicExch(status, 2);
   bar.finish();
 }
 
@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(kThreads) devApiArRmsNormKernel(ncclDevComm_t 
   __shared__ float red[40];
   ncclCoopCta cta;
   ncclLsaBarrierSession<ncclCoopCta> bar(cta, dc, ncclTeamLsa(dc), blockIdx.x);
-  if (bar.sync() != ncclSuccess) {
+  if (bar.sync(0, false, false) != ncclSuccess) {
     if (threadIdx.x == 0) atomicExch(status, 1);
     bar.finish();
     return;
@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(kThreads) devApiArRmsNormKernel(ncclDevComm_t 
       }
     }
   }
-  if (bar.sync() != ncclSuccess && threadIdx.x == 0) atomicExch(status, 2);
+  if (bar.sync(0, true, false) != ncclSuccess && threadIdx.x == 0) atomicExch(status, 2);
   bar.finish();
 }
 

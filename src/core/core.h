@@ -28,6 +28,9 @@ void debugLog(LogLevel level, uint64_t subsys, const char* file, int line, const
 int debugLevel();
 const char* lastErrorString();       // thread-independent last WARN text (ncclGetLastError)
 void setThreadName(const char* fmt, ...);
+// NVTX range around a public call (core/nvtx.cc); a no-op unless a profiling tool is attached.
+void nvtxRangeBegin(const char* func, size_t bytes, uint64_t commHash, int rank);
+void nvtxRangeEnd();
 
 #define WARN(...) ::b200::debugLog(::b200::LOG_WARN, ::b200::SUB_ALL, __FILE__, __LINE__, __VA_ARGS__)
 #define INFO(sub, ...) ::b200::debugLog(::b200::LOG_INFO, (sub), __FILE__, __LINE__, __VA_ARGS__)

@@ -113,7 +113,8 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
     if (threadIdx.x < n) {
       const unsigned long long* c = a.recvCount[rank] + cntOff + (size_t)el * n + threadIdx.x;
       unsigned long long v = 0;
-      bool got = boundedWait(w, WAIT_TILE, threadIdx.x, epoch, [&] { v = ldAcquireSys64((const uint64_t*)c); return (uint32_t)(v >> 32) == epoch; });
+      bool got = boundedWait(w, WAIT_TILE, threadIdx.x, epoch, [&] { v = ldRelaxedSys64((const uint64_t*)c); return (uint32_t)(v >> 32) == epoch; });
+      fenceSys();
       sCnt[threadIdx.x] = got ? (int)(uint32_t)v : -1;
     }
     __syncthreads();
@@ -196,7 +197,8 @@ __global__ void __launch_bounds__(kEpThreads, 1) epCombineKernel(const __grid_co
   __syncthreads();
   if (threadIdx.x < n) {
     const unsigned long long* f = a.combFlag[rank] + threadIdx.x;
-    bool got = boundedWait(w, WAIT_TILE, threadIdx.x, epoch, [&] { return (int32_t)((uint32_t)ldAcquireSys64((const uint64_t*)f) - epoch) >= 0; });
+    bool got = boundedWait(w, WAIT_TILE, threadIdx.x, epoch, [&] { return (int32_t)((uint32_t)ldRelaxedSys64((const uint64_t*)f) - epoch) >= 0; });
+    fenceSys();
     if (!got) sOk = 0;
   }
   __syncthreads();

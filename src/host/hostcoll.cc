@@ -11,7 +11,10 @@
 #include "../comm/comm.h"
 #include "hosttypes.h"
 
+#include <sched.h>
+
 #include "../transport/net.h"
+#include "../transport/shm.h"
 
 namespace b200 {
 
@@ -19,7 +22,40 @@ struct HostPlane {
   std::vector<Socket> peer;   // peer[r] connected to rank r (unused for r == rank)
   std::vector<char> tmp;
   Proxy* proxy = nullptr;     // set when messages travel through the network backend instead
+  std::vector<ShmLink> shmOut, shmIn;   // set when every rank is on this host and NCCL_B200_HOST_SHM=1
+  bool shm = false;
+  volatile uint32_t* abortFlag = nullptr;
 };
+
+B200_PARAM(HostShm, "NCCL_B200_HOST_SHM", 0, "1: ranks of one host exchange host-memory messages through shared-memory rings instead of TCP");
+B200_PARAM(HostShmKb, "NCCL_B200_HOST_SHM_KB", 4096, "capacity of one shared-memory ring, KiB");
+
+struct ShmOp { ShmLink* link; char* p; size_t n, off; bool send; };
+
+// Progresses all operations together; two operations on one link and direction run in posting order.
+static ncclResult_t shmRun(HostPlane* hp, std::vector<ShmOp>& ops) {
+  uint64_t last = nowNs();
+  const uint64_t budget = 120ull * 1000000000ull;
+  size_t left = 0;
+  for (auto& o : ops) if (o.off < o.n) ++left;
+  while (left) {
+    bool moved = false;
+    for (size_t i = 0; i < ops.size(); ++i) {
+      ShmOp& o = ops[i];
+      if (o.off >= o.n) continue;
+      bool blocked = false;
+      for (size_t j = 0; j < i; ++j) if (ops[j].off < ops[j].n && ops[j].link == o.link && ops[j].send == o.send) blocked = true;
+      if (blocked) continue;
+      size_t m = o.send ? shmLinkSend(o.link, o.p + o.off, o.n - o.off) : shmLinkRecv(o.link, o.p + o.off, o.n - o.off);
+      if (m) { o.off += m; moved = true; if (o.off >= o.n) --left; }
+    }
+    if (moved) { last = nowNs(); continue; }
+    if (hp->abortFlag && __atomic_load_n(hp->abortFlag, __ATOMIC_RELAXED)) return ncclInternalError;
+    if (nowNs() - last > budget) { WARN("shared-memory link made no progress for 120 s"); return ncclSystemError; }
+    sched_yield();
+  }
+  return ncclSuccess;
+}
 
 B200_PARAM(HostNet, "NCCL_B200_HOST_NET", 0, "1: host-memory messages go through the network backend (plugin or built-in Socket) and the proxy thread; 0: direct TCP mesh");
 
@@ -29,6 +65,26 @@ ncclResult_t hostPlaneCreate(ncclComm* comm) {
   HostPlane* hp = new HostPlane;
   int n = comm->nRanks, me = comm->rank;
   hp->peer.resize(n);
+  hp->abortFlag = comm->abortFlag;
+  if (paramHostShm() && comm->nNodes == 1) {
+    hp->shmIn.resize(n);
+    hp->shmOut.resize(n);
+    char base[96];
+    snprintf(base, sizeof(base), "/nccl-b200-%llx", (unsigned long long)comm->commHash);
+    ncclResult_t res = ncclSuccess;
+    for (int r = 0; r < n && res == ncclSuccess; ++r)
+      if (r != me) res = shmLinkCreate(std::string(base) + "-" + std::to_string(r) + "-" + std::to_string(me), (size_t)paramHostShmKb() << 10, &hp->shmIn[r]);
+    if (res == ncclSuccess) res = bootstrapBarrier(comm->bootstrap);
+    for (int r = 0; r < n && res == ncclSuccess; ++r)
+      if (r != me) res = shmLinkOpen(std::string(base) + "-" + std::to_string(me) + "-" + std::to_string(r), &hp->shmOut[r]);
+    if (res == ncclSuccess) res = bootstrapBarrier(comm->bootstrap);
+    for (auto& l : hp->shmIn) shmLinkUnlink(&l);   // everybody has attached: the names can go
+    if (res != ncclSuccess) { delete hp; return res; }
+    hp->shm = true;
+    comm->hostPlane = hp;
+    INFO(SUB_SHM | SUB_INIT, "host plane of rank %d: shared-memory rings to %d local peers (%lld KiB each)", me, n - 1, (long long)paramHostShmKb());
+    return ncclSuccess;
+  }
   bool ext = false;
   ncclNet_t* net = nullptr;
   if (netSelect(&net, &ext) == ncclSuccess && (ext || paramHostNet())) {
@@ -55,12 +111,20 @@ ncclResult_t hostPlaneCreate(ncclComm* comm) {
 void hostPlaneDestroy(ncclComm* comm) {
   if (!comm->hostPlane) return;
   proxyDestroy(comm);
+  for (auto& l : comm->hostPlane->shmIn) shmLinkClose(&l);
+  for (auto& l : comm->hostPlane->shmOut) shmLinkClose(&l);
   for (auto& s : comm->hostPlane->peer) sockClose(&s);
   delete comm->hostPlane;
   comm->hostPlane = nullptr;
 }
 
 static ncclResult_t exchange(HostPlane* hp, int to, const void* sbuf, size_t sbytes, int from, void* rbuf, size_t rbytes) {
+  if (hp->shm) {
+    std::vector<ShmOp> ops;
+    if (sbytes > 0) ops.push_back(ShmOp{&hp->shmOut[to], (char*)sbuf, sbytes, 0, true});
+    if (rbytes > 0) ops.push_back(ShmOp{&hp->shmIn[from], (char*)rbuf, rbytes, 0, false});
+    return shmRun(hp, ops);
+  }
   if (hp->proxy) {
     ProxyOp* ops[2];
     int k = 0;
@@ -280,6 +344,19 @@ ncclResult_t hostPlaneRun(ncclComm* comm, const Task& t) {
 // A group of sends and receives progresses all at once so that any matching order works.
 ncclResult_t hostPlaneRunP2pGroup(ncclComm* comm, const std::vector<Task>& tasks) {
   HostPlane* hp = comm->hostPlane;
+  if (hp->shm) {
+    std::vector<ShmOp> ops;
+    std::vector<const Task*> sSelf, rSelf;
+    for (auto& t : tasks) {
+      size_t bytes = t.count * typeSize(t.type);
+      if (t.root == comm->rank) { (t.func == FUNC_SEND ? sSelf : rSelf).push_back(&t); continue; }
+      if (t.func == FUNC_SEND) ops.push_back(ShmOp{&hp->shmOut[t.root], (char*)t.send, bytes, 0, true});
+      else if (t.func == FUNC_RECV) ops.push_back(ShmOp{&hp->shmIn[t.root], (char*)t.recv, bytes, 0, false});
+    }
+    if (sSelf.size() != rSelf.size()) { WARN("unmatched send/recv to self"); return ncclInvalidUsage; }
+    for (size_t i = 0; i < sSelf.size(); ++i) memcpy(rSelf[i]->recv, sSelf[i]->send, sSelf[i]->count * typeSize(sSelf[i]->type));
+    return shmRun(hp, ops);
+  }
   if (hp->proxy) {
     std::vector<ProxyOp*> posted;
     std::vector<const Task*> sSelf, rSelf;

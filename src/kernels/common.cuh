@@ -29,6 +29,14 @@ __device__ __forceinline__ uint32_t ldRelaxedSys(const uint32_t* p) {
   asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ uint64_t ldRelaxedSys64(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+// A system-scope fence costs microseconds on this part, and st.release / ld.acquire each carry
+// one. Flags are therefore published as "one fence, then a relaxed store" and awaited as
+// "relaxed polls, then one fence": the same ordering with one fence per hand-off side.
 __device__ __forceinline__ void stReleaseSys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -129,19 +137,27 @@ struct CtaBarrier {
     epochPtr = s.epoch[rank_] + slot_;
     epoch = *epochPtr;  // every thread reads the same value; written back by finish()
   }
-  // All threads of the CTA must call. Data written before the call by any thread of the CTA is
-  // visible to every peer CTA after its matching call returns.
-  __device__ __forceinline__ bool sync() {
+  // All threads of the CTA must call.
+  //   release: data written before the call by any thread of the CTA is visible to every peer CTA
+  //            after its matching call returns (one system-scope fence by the signalling thread,
+  //            cumulative over the CTA through the __syncthreads before it);
+  //   acquire: data the peers released before their call may be read after this call returns.
+  // A barrier that only says "my kernel has started" (inputs were written by earlier kernels, which
+  // a kernel boundary already made visible) needs neither, and a closing barrier after which this
+  // kernel reads nothing needs no acquire: system-scope fences cost microseconds each, so callers
+  // ask only for what they need. Polling uses relaxed loads; the acquire fence comes once, after.
+  __device__ __forceinline__ bool sync(bool release = true, bool acquire = true) {
     ++epoch;
     __syncthreads();
     bool ok = true;
     int t = threadIdx.x;
     if (t < nRanks && t != rank) {
-      fenceSys();
-      stReleaseSys(inbox[t] + (size_t)slot * kMaxRanks + rank, epoch);
+      if (release) fenceSys();
+      stRelaxedSys(inbox[t] + (size_t)slot * kMaxRanks + rank, epoch);
       const uint32_t* mine = inbox[rank] + (size_t)slot * kMaxRanks + t;
       uint32_t want = epoch;
-      ok = boundedWait(w, WAIT_BARRIER, (uint32_t)t, want, [&] { return (int32_t)(ldAcquireSys(mine) - want) >= 0; });
+      ok = boundedWait(w, WAIT_BARRIER, (uint32_t)t, want, [&] { return (int32_t)(ldRelaxedSys(mine) - want) >= 0; });
+      if (acquire) fenceSys();
     }
     ok = __syncthreads_and(ok);
     return ok;

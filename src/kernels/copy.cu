@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) copyCollKernel(const __grid_co
   const int rank = ctaRank(a.emu, a.rank);
   CtaBarrier bar;
   bar.init(a.sync, rank, a.nRanks, blockIdx.x);
-  bool ok = bar.sync();
+  bool ok = bar.sync(false, false);   // every rank's kernel has started: inputs final, outputs free
   __shared__ Seg segs[kMaxRanks];
   __shared__ int nSeg;
   if (threadIdx.x == 0) nSeg = buildSegs(a, rank, segs);
@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) copyCollKernel(const __grid_co
       }
     }
   }
-  bar.sync();
+  bar.sync(true, false);
   bar.finish();
 }
 
@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) p2pKernel(const __grid_constan
         if (threadIdx.x == 0 && q >= (uint32_t)kP2pSlots) {
           const uint32_t* ackp = a.ack[rank] + op.peer * kP2pSlots + slot;
           const uint32_t want = q - kP2pSlots + 1;
-          ok = boundedWait(w, WAIT_P2P_ACK, (uint32_t)op.peer, want, [&] { return (int32_t)(ldAcquireSys(ackp) - want) >= 0; });
+          ok = boundedWait(w, WAIT_P2P_ACK, (uint32_t)op.peer, want, [&] { return (int32_t)(ldRelaxedSys(ackp) - want) >= 0; });   // permission only: no data to acquire
         }
         ok = __syncthreads_and(ok);
         if (!ok) break;
@@ -200,13 +200,14 @@ __global__ void __launch_bounds__(kCtaThreads, 1) p2pKernel(const __grid_constan
         __syncthreads();
         if (threadIdx.x == 0) {
           fenceSys();
-          stReleaseSys(a.ready[op.peer] + rank * kP2pSlots + slot, q + 1);
+          stRelaxedSys(a.ready[op.peer] + rank * kP2pSlots + slot, q + 1);
         }
       } else {
         if (threadIdx.x == 0) {
           const uint32_t* rdy = a.ready[rank] + op.peer * kP2pSlots + slot;
           const uint32_t want = q + 1;
-          ok = boundedWait(w, WAIT_P2P_READY, (uint32_t)op.peer, want, [&] { return (int32_t)(ldAcquireSys(rdy) - want) >= 0; });
+          ok = boundedWait(w, WAIT_P2P_READY, (uint32_t)op.peer, want, [&] { return (int32_t)(ldRelaxedSys(rdy) - want) >= 0; });
+          fenceSys();   // acquire: the chunk behind the flag
         }
         ok = __syncthreads_and(ok);
         if (!ok) break;
@@ -214,8 +215,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) p2pKernel(const __grid_constan
         copyChunk((char*)op.buf + off, src, len);
         __syncthreads();
         if (threadIdx.x == 0) {
-          fenceSys();
-          stReleaseSys(a.ack[op.peer] + rank * kP2pSlots + slot, q + 1);
+          stRelaxedSys(a.ack[op.peer] + rank * kP2pSlots + slot, q + 1);   // the reads above completed before the barrier
         }
       }
     }
@@ -303,7 +303,6 @@ const void* localCopyKernelFn(int unroll) { return unroll >= 8 ? (const void*)lo
 // ------------------------------------------------------------------------- signals
 __global__ void signalKernel(OneSignalArgs a) {
   if (threadIdx.x == 0) {
-    fenceSys();
     redReleaseSysAdd64(a.target, 1);
   }
 }
@@ -314,7 +313,8 @@ __global__ void waitSignalKernel(const __grid_constant__ WaitSignalArgs a) {
     WaitCtx w{&a.sync, a.sync.status[a.rank]};
     const uint64_t want = *a.seen[t] + a.opCnt[t];
     const uint64_t* c = a.counter[t];
-    bool ok = boundedWait(w, WAIT_SIGNAL, (uint32_t)t, (uint32_t)want, [&] { return ldAcquireSys64(c) >= want; });
+    bool ok = boundedWait(w, WAIT_SIGNAL, (uint32_t)t, (uint32_t)want, [&] { return ldRelaxedSys64(c) >= want; });
+    fenceSys();
     if (ok) *a.seen[t] = want;
   }
 }

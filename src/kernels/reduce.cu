@@ -19,7 +19,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) reduceP2pKernel(const __grid_c
   const int n = a.nRanks;
   CtaBarrier bar;
   bar.init(a.sync, rank, n, blockIdx.x);
-  bool ok = bar.sync();  // inputs of every rank are final; outputs may be overwritten
+  bool ok = bar.sync(false, false);  // inputs of every rank are final (written by earlier kernels); outputs may be overwritten
   const size_t begin = a.sliceBegin[rank], cnt = a.sliceCount[rank];
   if (ok && cnt) {
     constexpr int N = 16 / sizeof(T);
@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) reduceP2pKernel(const __grid_c
       for (int q = 0; q < nDst; ++q) ((T*)dst[q])[e] = r;
     }
   }
-  bar.sync();  // results have landed everywhere; nobody reads this rank's input any more
+  bar.sync(true, false);  // results have landed everywhere; nobody reads this rank's input any more
   bar.finish();
 }
 
@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) reduceNvlsKernel(const __grid_
   const int rank = a.rank;
   CtaBarrier bar;
   bar.init(a.sync, rank, a.nRanks, blockIdx.x);
-  bool ok = bar.sync();
+  bool ok = bar.sync(false, false);
   if constexpr (McRed<T, OP>::kSupported) {
     const size_t cnt = a.sliceCount[rank];
     if (ok && cnt) {
@@ -174,7 +174,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) reduceNvlsKernel(const __grid_
       }
     }
   }
-  bar.sync();
+  bar.sync(true, false);
   bar.finish();
 }
 

@@ -53,14 +53,15 @@ struct StepFlags {
     __syncthreads();
     if (threadIdx.x == 0) {
       fenceSys();
-      stReleaseSys(peerWords + me, value);
+      stRelaxedSys(peerWords + me, value);
     }
   }
   __device__ __forceinline__ bool wait(int src, uint32_t value) {
     bool ok = true;
     if (threadIdx.x == 0) {
       const uint32_t* p = mine + src;
-      ok = boundedWait(w, WAIT_TILE, (uint32_t)src, value, [&] { return (int32_t)(ldAcquireSys(p) - value) >= 0; });
+      ok = boundedWait(w, WAIT_TILE, (uint32_t)src, value, [&] { return (int32_t)(ldRelaxedSys(p) - value) >= 0; });
+      fenceSys();
     }
     return __syncthreads_and(ok);
   }
@@ -92,7 +93,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) ringKernel(const __grid_consta
   uint32_t* nextWords = (uint32_t*)((char*)a.sync.inbox[next] + kOffRingFlags) + (size_t)slot * kMaxRanks;
   char* W = (char*)a.recv[rank];
   const char* Wprev = (const char*)a.recv[prev];
-  bool ok = bar.sync();   // every rank's work buffer holds its input
+  bool ok = bar.sync(false, false);   // every rank's work buffer holds its input (copied in by an earlier stream operation)
   // this CTA's range, cut in n chunks
   size_t rb, re;
   const bool gatherOnly = a.func == FUNC_ALLGATHER;
@@ -152,7 +153,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) ringKernel(const __grid_consta
   }
   // steps that were not run (failed wait) still advance the base identically on every rank
   const uint32_t planned = (gatherOnly ? 0 : n - 1) + (a.func != FUNC_REDUCESCATTER ? n - 1 : 0);
-  bar.sync();             // nobody still reads my work buffer
+  bar.sync(true, false);  // nobody still reads my work buffer
   if (threadIdx.x == 0) *basePtr = f.base + planned;
   bar.finish();
 }
@@ -172,7 +173,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) treeKernel(const __grid_consta
   uint32_t* basePtr = a.sync.epoch[rank] + kPrivTreeBase + slot;
   const uint32_t base = *basePtr;
   char* W = (char*)a.recv[rank];
-  bool ok = bar.sync();
+  bool ok = bar.sync(false, false);
   size_t rb, re;
   ctaRange(a.count, unit, slot, gridDim.x, &rb, &re);
   const size_t half = ((re - rb) / 2 + unit - 1) / unit * unit;
@@ -212,7 +213,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) treeKernel(const __grid_consta
       f.post(words(treeReal(cv, tree, n)), rank, base + 2);
     }
   }
-  bar.sync();
+  bar.sync(true, false);
   if (threadIdx.x == 0) *basePtr = base + 2;
   bar.finish();
 }

@@ -22,12 +22,14 @@ void* profilerApiStart(ncclComm* comm, const Task& t) {
   ApiHandle* h = new ApiHandle;
   h->ev = ApiEvent{nowNs(), 0, comm->commHash, comm->rank, t.func, t.root, t.count, (int)t.type, t.op, (void*)t.stream};
   h->plugin = profilerPluginStart(comm, t);
+  nvtxRangeBegin(funcName(t.func), t.count * typeSize(t.type), comm->commHash, comm->rank);
   return h;
 }
 
 void profilerApiStop(void* hv) {
   ApiHandle* h = (ApiHandle*)hv;
   h->ev.tEndNs = nowNs();
+  nvtxRangeEnd();
   if (h->plugin) profilerPluginStop(h->plugin);
   {
     std::lock_guard<std::mutex> g(gLock);

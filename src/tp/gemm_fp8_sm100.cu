@@ -60,7 +60,7 @@ tpGemmFp8Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   bool ok = true;
   if (multi) {
     bar.init(a.sync, rank, n, blockIdx.x);
-    ok = bar.sync();
+    ok = bar.sync(false, false);
   }
 
   if (commCta) {
@@ -99,7 +99,7 @@ tpGemmFp8Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
       }
     }
-    bar.sync();
+    bar.sync(true, false);
     bar.finish();
     return;
   }
@@ -296,7 +296,7 @@ tpGemmFp8Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     tmemDealloc(tmemBase, kTmemCols);
   }
   if (multi) {
-    bar.sync();
+    bar.sync(true, false);
     bar.finish();
   }
 }

@@ -61,7 +61,7 @@ tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   bool ok = true;
   if (multi) {
     bar.init(a.sync, rank, n, blockIdx.x);
-    ok = bar.sync();   // REDUCE: every accumulation buffer is zeroed; GATHER: every rank's rows are in place
+    ok = bar.sync(false, false);   // REDUCE: every accumulation buffer is zeroed; GATHER: every rank's rows are in place
   }
 
   if (commCta) {
@@ -94,7 +94,7 @@ tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         }
       }
     }
-    bar.sync();        // nobody reads my rows any more
+    bar.sync(true, false);   // nobody reads my rows any more
     bar.finish();
     return;
   }
@@ -248,7 +248,7 @@ tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     tmemDealloc(tmemBase, kTmemCols);
   }
   if (multi) {
-    bar.sync();      // REDUCE: every partial sum has landed in its owner's buffer
+    bar.sync(true, false);   // REDUCE: every partial sum has landed in its owner's buffer
     bar.finish();
   }
 }

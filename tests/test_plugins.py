@@ -92,3 +92,9 @@ def test_builtin_socket_backend_through_proxy():
 def test_missing_plugin_falls_back(tmp_path):
     env = dict(BASE, NCCL_TUNER_PLUGIN="does-not-exist", NCCL_NET_PLUGIN="none")
     _check(run_ranks(_rank, 2, args=(1,), env=env), 2)
+
+
+def test_shm_links():
+    """Ranks of one host exchange host-memory messages through shared-memory rings."""
+    env = dict(BASE, NCCL_B200_HOST_SHM="1", NCCL_B200_HOST_SHM_KB="64")   # small rings: messages wrap many times
+    _check(run_ranks(_rank, 3, args=(2,), env=env), 3)
