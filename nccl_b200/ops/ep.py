@@ -107,7 +107,7 @@ class ExpertParallel:
     def _stream(self):
         return self.torch.cuda.current_stream().cuda_stream
 
-    def dispatch(self, x, topk_idx, topk_weights, fp8=True):
+    def dispatch(self, x, topk_idx, topk_weights, fp8=True, toks=None, scales=None, counts=None):
         torch, L = self.torch, self.lib
         idx_t = _tensor(topk_idx, INT64)
         if self.handle is None:
@@ -116,9 +116,12 @@ class ExpertParallel:
             self.handle = h
         else:
             _lib.check(L.ncclEpUpdateHandle(self.handle, ctypes.byref(idx_t), None, self._stream()), "ncclEpUpdateHandle", L)
-        toks = torch.empty(self.El, self.cap, self.H, dtype=torch.uint8 if fp8 else torch.bfloat16, device=x.device)
-        scales = torch.empty(self.El, self.cap, self.H // 128, dtype=torch.float32, device=x.device) if fp8 else None
-        counts = torch.zeros(self.El, dtype=torch.int32, device=x.device)
+        if toks is None:
+            toks = torch.empty(self.El, self.cap, self.H, dtype=torch.uint8 if fp8 else torch.bfloat16, device=x.device)
+        if scales is None and fp8:
+            scales = torch.empty(self.El, self.cap, self.H // 128, dtype=torch.float32, device=x.device)
+        if counts is None:
+            counts = torch.zeros(self.El, dtype=torch.int32, device=x.device)
         xin, win = _tensor(x, BF16), _tensor(topk_weights, FP32)
         tout, cnt_t = _tensor(toks, FP8_E4M3 if fp8 else BF16), _tensor(counts, INT32)
         sout = _tensor(scales, FP32) if fp8 else None
