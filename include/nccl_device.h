@@ -17,6 +17,7 @@
 #include "nccl_device/coop.h"
 #include "nccl_device/utility.h"
 #include "nccl_device/lsa_barrier.h"
+#include "nccl_device/barrier.h"
 #include "nccl_device/ll_a2a.h"
 #include "nccl_device/multimem.h"
 #include "nccl_device/reduce_copy.h"

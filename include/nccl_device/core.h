@@ -113,6 +113,10 @@ typedef struct ncclDevComm {
   int llA2ABlockCount, llA2ASlotCount;
   uint32_t* barrierEpochs;             /* private device words: one epoch per LSA barrier */
   uint32_t* llA2AEpochs;               /* private device words: one epoch per LLA2A block */
+  uint32_t ginSignalOffset;            /* u64 signal words [ginSignalCount], in the resource window */
+  int ginSignalCount;
+  uint32_t ginCounterOffset;           /* u64 local completion counters [ginCounterCount] */
+  int ginCounterCount;
   const uint32_t* abortFlag;           /* host-mapped: non-zero once the communicator is aborted */
   unsigned long long timeoutCycles;    /* default budget of device-side waits */
 } ncclDevComm_t;

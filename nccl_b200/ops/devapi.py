@@ -30,7 +30,9 @@ class _DevComm(ctypes.Structure):
     _fields_ = [("rank", ctypes.c_int), ("nRanks", ctypes.c_int), ("lsaRank", ctypes.c_int), ("lsaSize", ctypes.c_int), ("resource", _Window),
                 ("lsaBarrierOffset", ctypes.c_uint32), ("lsaBarrierCount", ctypes.c_int), ("llA2AOffset", ctypes.c_uint32),
                 ("llA2ABlockCount", ctypes.c_int), ("llA2ASlotCount", ctypes.c_int), ("barrierEpochs", ctypes.c_void_p),
-                ("llA2AEpochs", ctypes.c_void_p), ("abortFlag", ctypes.c_void_p), ("timeoutCycles", ctypes.c_ulonglong)]
+                ("llA2AEpochs", ctypes.c_void_p), ("ginSignalOffset", ctypes.c_uint32), ("ginSignalCount", ctypes.c_int),
+                ("ginCounterOffset", ctypes.c_uint32), ("ginCounterCount", ctypes.c_int), ("abortFlag", ctypes.c_void_p),
+                ("timeoutCycles", ctypes.c_ulonglong)]
 
 
 class _Requirements(ctypes.Structure):
@@ -55,7 +57,7 @@ def query_properties(comm):
 
 
 class DeviceComm:
-    def __init__(self, comm, barriers=64, ll_blocks=0, ll_slots=0, multimem=False):
+    def __init__(self, comm, barriers=64, ll_blocks=0, ll_slots=0, multimem=False, gin_signals=0, gin_counters=0):
         self.comm = comm
         self.lib = L = comm.lib
         L.ncclDevCommCreate.argtypes = [ctypes.c_void_p, ctypes.POINTER(_Requirements), ctypes.POINTER(_DevComm)]
@@ -65,6 +67,7 @@ class DeviceComm:
         L.b200DevApiArRmsNorm.argtypes = [ctypes.POINTER(_DevComm), W, S, W, S, W, S, P, ctypes.c_float, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, P]
         L.b200DevApiLLSum.argtypes = [ctypes.POINTER(_DevComm), P, P, ctypes.c_int, ctypes.c_int, P]
         L.b200DevApiStatus.restype = ctypes.c_int
+        L.b200DevApiGinRing.argtypes = [ctypes.POINTER(_DevComm), W, S, S, S, ctypes.c_ulonglong, P]
         req = _Requirements()
         req.size = ctypes.sizeof(_Requirements)
         req.magic = 0xdec0de01
@@ -74,6 +77,9 @@ class DeviceComm:
         req.lsaLLA2ABlockCount = ll_blocks
         req.lsaLLA2ASlotCount = ll_slots
         req.ginContextCount = 4
+        req.ginSignalCount = gin_signals
+        req.ginCounterCount = gin_counters
+        self._gin_seq = 0
         self.dc = _DevComm()
         _lib.check(L.ncclDevCommCreate(comm.handle, ctypes.byref(req), ctypes.byref(self.dc)), "ncclDevCommCreate", L)
         self.barriers = barriers
@@ -134,6 +140,16 @@ class DeviceComm:
         slots = values.shape[1]
         _lib.check(self.lib.b200DevApiLLSum(ctypes.byref(self.dc), values.data_ptr(), out.data_ptr(), slots, ctas, self._stream(stream)),
                    "b200DevApiLLSum", self.lib)
+
+    def gin_ring(self, send, recv, stream=None):
+        """Every rank puts `send` into the next rank's `recv` (same symmetric buffer) and waits for its own to arrive."""
+        sw, so = self._locate(send)
+        rw, ro = self._locate(recv)
+        if ctypes.addressof(sw.contents) != ctypes.addressof(rw.contents):
+            raise ValueError("send and recv must live in the same symmetric buffer")
+        self._gin_seq += 1
+        _lib.check(self.lib.b200DevApiGinRing(ctypes.byref(self.dc), sw, so, ro, send.numel() * send.element_size(), self._gin_seq,
+                                              self._stream(stream)), "b200DevApiGinRing", self.lib)
 
     def status(self):
         return self.lib.b200DevApiStatus()

@@ -58,8 +58,8 @@ ncclResult_t ncclDevCommCreate(ncclComm_t comm, const ncclDevCommRequirements_t*
   ncclCommProperties_t props = NCCL_COMM_PROPERTIES_INITIALIZER;
   NCCLCHECK(ncclCommQueryProperties(comm, &props));
   if (!props.deviceApiSupport) { WARN("ncclDevCommCreate : the ranks of this communicator do not share one load/store domain"); return ncclInvalidUsage; }
-  if (reqs->ginForceEnable || reqs->ginSignalCount || reqs->ginCounterCount || reqs->railGinBarrierCount || reqs->worldGinBarrierCount) {
-    WARN("ncclDevCommCreate : GPU-initiated networking was requested but no such backend exists in this build");
+  if (reqs->railGinBarrierCount || reqs->worldGinBarrierCount || reqs->ginConnectionType > 0) {
+    WARN("ncclDevCommCreate : network (rail / world) resources were requested but this build serves one NVLink domain without a GPU-initiated network backend");
     return ncclInvalidUsage;
   }
   if (reqs->lsaMultimem && !props.multimemSupport) { WARN("ncclDevCommCreate : multimem requested but NVLink multicast is not available"); return ncclInvalidUsage; }
@@ -75,6 +75,18 @@ ncclResult_t ncclDevCommCreate(ncclComm_t comm, const ncclDevCommRequirements_t*
   off = alignUp(off + (size_t)nBar * NCCL_DEVICE_MAX_LSA * sizeof(uint32_t), 256);
   const size_t llOff = off;
   off = alignUp(off + (size_t)llBlocks * 2 * NCCL_DEVICE_MAX_LSA * llSlots * 16, 256);
+  // signals and counters of the GPU-initiated put / signal surface: served over NVLink inside the team
+  int nSignals = reqs->ginSignalCount, nCounters = reqs->ginCounterCount;
+  for (ncclDevResourceRequirements_t* r = reqs->resourceRequirementsList; r; r = r->next) {
+    if (r->outGinSignalStart) *r->outGinSignalStart = (uint32_t)nSignals;
+    if (r->outGinCounterStart) *r->outGinCounterStart = (uint32_t)nCounters;
+    nSignals += r->ginSignalCount;
+    nCounters += r->ginCounterCount;
+  }
+  const size_t sigOff = off;
+  off = alignUp(off + (size_t)nSignals * 8, 256);
+  const size_t cntOff = off;
+  off = alignUp(off + (size_t)nCounters * 8, 256);
   for (ncclDevResourceRequirements_t* r = reqs->resourceRequirementsList; r; r = r->next) {
     size_t a = std::max<size_t>(r->bufferAlign, 16);
     if (a & (a - 1)) { WARN("ncclDevCommCreate : buffer alignment %zu is not a power of two", a); return ncclInvalidArgument; }
@@ -82,8 +94,6 @@ ncclResult_t ncclDevCommCreate(ncclComm_t comm, const ncclDevCommRequirements_t*
     if (off + r->bufferSize > 0xffffffffull) { WARN("ncclDevCommCreate : resource buffers exceed 4 GiB"); return ncclInvalidArgument; }
     if (r->outBufferHandle) *r->outBufferHandle = (uint32_t)off;
     off += r->bufferSize;
-    if (r->outGinSignalStart) *r->outGinSignalStart = 0;
-    if (r->outGinCounterStart) *r->outGinCounterStart = 0;
   }
   for (ncclTeamRequirements_t* t = reqs->teamRequirementsList; t; t = t->next)
     if (t->outMultimemHandle) *t->outMultimemHandle = 0;   // the one multicast alias covers the whole team
@@ -119,6 +129,10 @@ ncclResult_t ncclDevCommCreate(ncclComm_t comm, const ncclDevCommRequirements_t*
   out->llA2AOffset = (uint32_t)llOff;
   out->llA2ABlockCount = llBlocks;
   out->llA2ASlotCount = llSlots;
+  out->ginSignalOffset = (uint32_t)sigOff;
+  out->ginSignalCount = nSignals;
+  out->ginCounterOffset = (uint32_t)cntOff;
+  out->ginCounterCount = nCounters;
   out->barrierEpochs = st.priv;
   out->llA2AEpochs = st.priv + nBar;
   out->abortFlag = comm->abortFlagDev;

@@ -158,6 +158,21 @@ __global__ void __launch_bounds__(256) devApiLLSumKernel(ncclDevComm_t dc, const
   ll.endEpoch();
 }
 
+// Exercises ncclGin: every rank puts `bytes` from its send region into the next rank's receive region,
+// bumps signal 0 there, and waits until its own signal 0 has reached the call's sequence number.
+__global__ void __launch_bounds__(256) devApiGinRingKernel(ncclDevComm_t dc, ncclWindow_t win, size_t sendOff, size_t recvOff, size_t bytes,
+                                                           unsigned long long seq, int* status) {
+  ncclCoopCta cta;
+  ncclGin gin(dc);
+  const ncclTeam_t team = ncclTeamLsa(dc);
+  const int next = (dc.lsaRank + 1) % dc.lsaSize;
+  if (gin.put(cta, team, next, win, recvOff, win, sendOff, bytes, /*signal*/ 0, /*counter*/ 0) != ncclSuccess) {
+    if (threadIdx.x == 0) atomicExch(status, 4);
+    return;
+  }
+  if (threadIdx.x == 0 && gin.waitSignal(0, seq) != ncclSuccess) atomicExch(status, 5);
+}
+
 int* statusWord() {
   static thread_local int* w[64] = {};
   int dev = 0;
@@ -210,6 +225,16 @@ ncclResult_t b200DevApiLLSum(const ncclDevComm_t* dc, const void* in, void* out,
   int* st = statusWord();
   if (!st) return ncclUnhandledCudaError;
   devApiLLSumKernel<<<nCtas, 256, 0, stream>>>(*dc, (const float2*)in, (float2*)out, slots, st);
+  return cudaGetLastError() == cudaSuccess ? ncclSuccess : ncclUnhandledCudaError;
+}
+
+// One CTA; needs a device communicator created with at least one GIN signal and counter.
+ncclResult_t b200DevApiGinRing(const ncclDevComm_t* dc, ncclWindow_t win, size_t sendOff, size_t recvOff, size_t bytes, unsigned long long seq,
+                               cudaStream_t stream) {
+  if (!dc || !win || dc->ginSignalCount < 1 || dc->ginCounterCount < 1) return ncclInvalidArgument;
+  int* st = statusWord();
+  if (!st) return ncclUnhandledCudaError;
+  devApiGinRingKernel<<<1, 256, 0, stream>>>(*dc, win->devSelf, sendOff, recvOff, bytes, seq, st);
   return cudaGetLastError() == cudaSuccess ? ncclSuccess : ncclUnhandledCudaError;
 }
 

@@ -22,7 +22,7 @@ def _rank(rank, nranks, uid):
     comm = Communicator(nranks, rank, uid)
     props = query_properties(comm)
     assert props["deviceApiSupport"] == 1 and props["nRanks"] == nranks
-    dc = DeviceComm(comm, barriers=64, ll_blocks=2, ll_slots=128)
+    dc = DeviceComm(comm, barriers=64, ll_blocks=2, ll_slots=128, gin_signals=2, gin_counters=1)
     res = {"multimem": props["multimemSupport"]}
     # all-reduce written with the device headers
     for dtype, numel in ((torch.float32, 1 << 18), (torch.bfloat16, (1 << 16) + 8)):
@@ -62,6 +62,17 @@ def _rank(rank, nranks, uid):
         dc.ll_sum(vals, o, ctas=2)
     assert dc.status() == 0
     res["ll"] = o.cpu().numpy()
+    # one-sided put + signal around the ring
+    both = dc.symmetric(2 * 1000, torch.float32)
+    snd, rcv = both[:1000], both[1000:]
+    for it in range(3):
+        snd.fill_(100.0 * it + rank)
+        torch.cuda.synchronize()
+        comm.all_reduce(torch.zeros(8, device="cuda"))   # nobody overwrites a receive region that is still being read
+        torch.cuda.synchronize()
+        dc.gin_ring(snd, rcv)
+        assert dc.status() == 0
+        assert float(rcv[0]) == 100.0 * it + (rank - 1) % nranks and float(rcv[-1]) == float(rcv[0])
     dc.destroy()
     comm.destroy()
     return res
