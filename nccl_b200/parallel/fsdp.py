@@ -35,7 +35,7 @@ class _Unit:
 
 
 class FSDPEngine:
-    def __init__(self, comm, cfg, device="cuda", seed=0, lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, symmetric=True):
+    def __init__(self, comm, cfg, device="cuda", seed=0, lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, symmetric=True, init_on_device=False):
         self.comm, self.cfg, self.device = comm, cfg, torch.device(device)
         self.cuda = self.device.type == "cuda"
         self.n, self.rank = comm.nranks, comm.rank
@@ -56,8 +56,23 @@ class FSDPEngine:
             u.name, u.shapes, u.numel = name, shapes, M.numel(shapes)
             u.padded = _align(u.numel, self.n * 128)
             u.shard = u.padded // self.n
-            full = torch.zeros(u.padded, dtype=torch.bfloat16)
-            full[:u.numel] = M.init_flat(shapes, gen)      # every rank draws the same stream, keeps its slice
+            if init_on_device and self.cuda:
+                # large models: draw the unit on the GPU (same seed on every rank), keep this rank's slice
+                dgen = torch.Generator(device=self.device).manual_seed(seed * 1000003 + len(self.units))
+                full = torch.zeros(u.padded, dtype=torch.bfloat16, device=self.device)
+                off = 0
+                for _, shape in shapes:
+                    cnt = 1
+                    for sdim in shape:
+                        cnt *= sdim
+                    if len(shape) == 1:
+                        full[off:off + cnt] = 1.0
+                    else:
+                        full[off:off + cnt] = (torch.randn(cnt, generator=dgen, device=self.device) * 0.02).to(torch.bfloat16)
+                    off += cnt
+            else:
+                full = torch.zeros(u.padded, dtype=torch.bfloat16)
+                full[:u.numel] = M.init_flat(shapes, gen)      # every rank draws the same stream, keeps its slice
             mine = full[self.rank * u.shard:(self.rank + 1) * u.shard]
             u.param = self._buffer(u.shard, torch.bfloat16)
             u.param.copy_(mine)

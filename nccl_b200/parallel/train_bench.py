@@ -53,7 +53,7 @@ def main(argv=None):
 
     if a.what == "fsdp":
         from nccl_b200.parallel.fsdp import FSDPEngine
-        eng = FSDPEngine(comm, cfg, device="cuda", seed=0)
+        eng = FSDPEngine(comm, cfg, device="cuda", seed=0, init_on_device=True)
         tok = torch.randint(0, cfg.vocab, (a.batch, a.seq), generator=g).pin_memory()
         tgt = torch.randint(0, cfg.vocab, (a.batch, a.seq), generator=g).pin_memory()
         loss = None

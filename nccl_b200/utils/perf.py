@@ -154,14 +154,20 @@ class Harness:
             return L.ncclGroupEnd()
         raise ValueError(coll)
 
-    def time(self, coll, nbytes, dtype_code=FP32, warmup=20, iters=100):
-        """Mean device time per call in microseconds (max over ranks)."""
+    def time(self, coll, nbytes, dtype_code=FP32, warmup=20, iters=100, min_warm_ms=3.0):
+        """Mean device time per call in microseconds (max over ranks). The warm-up covers at least
+        `warmup` calls and roughly `min_warm_ms` of device time: after the host-side barrier between
+        two measurements the GPU has been idle and its clocks have dropped, and a window of a few
+        short kernels would otherwise be timed at idle clocks. The number of warm-up calls is a
+        function of the message size only, so every rank issues the same sequence of collectives."""
         sp = self.stream.cuda_stream
+        est_us = 10.0 + nbytes / 3.0e5                       # rough per-call time: 10 us + bytes at 300 GB/s
+        warm = max(warmup, min(2000, int(min_warm_ms * 1e3 / est_us) + 1))
         with torch.cuda.stream(self.stream):
-            for _ in range(warmup):
+            self.d.barrier()
+            for _ in range(warm):
                 _lib.check(self.call(coll, nbytes, dtype_code, sp), coll, self.lib)
             self.stream.synchronize()
-            self.d.barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(self.stream)
             for _ in range(iters):

@@ -11,18 +11,18 @@ static const char kDefaultTuningJson[] = R"JSON({
  "broadcast": [[1048576,"LL",0],[4194304,"MC",16],[16777216,"PULL",64],[67108864,"MC",16],[268435456,"PULL",64],[1099511627776,"PUSH",128]]
 },
 "3": {
- "all_reduce": [[1048576,"LL",0],[67108864,"NVLS",16],[268435456,"NVLS",32],[1099511627776,"NVLS",64]],
- "all_gather": [[4194304,"LL",0],[67108864,"PUSH",64],[1099511627776,"PUSH",128]],
- "reduce_scatter": [[4194304,"LL",0],[16777216,"P2P",64],[67108864,"P2P",128],[1099511627776,"P2P",64]],
+ "all_reduce": [[524288,"LL",0],[4194304,"NVLS",64],[268435456,"NVLS",16],[1099511627776,"NVLS",64]],
+ "all_gather": [[1048576,"LL",0],[4194304,"MC",128],[16777216,"PUSH",64],[1099511627776,"PUSH",128]],
+ "reduce_scatter": [[4194304,"LL",0],[16777216,"NVLS",16],[1099511627776,"P2P",128]],
  "all_to_all": [[4194304,"LL",0],[16777216,"PUSH",64],[1099511627776,"PUSH",128]],
- "broadcast": [[1048576,"LL",0],[4194304,"MC",128],[16777216,"MC",32],[268435456,"MC",16],[1099511627776,"MC",64]]
+ "broadcast": [[262144,"LL",0],[1048576,"MC",16],[16777216,"MC",128],[268435456,"MC",16],[1099511627776,"MC",64]]
 },
 "4": {
- "all_reduce": [[1048576,"LL",0],[67108864,"NVLS",16],[268435456,"NVLS",32],[1099511627776,"NVLS",64]],
- "all_gather": [[4194304,"LL",0],[67108864,"PUSH",64],[1099511627776,"PUSH",128]],
- "reduce_scatter": [[4194304,"LL",0],[16777216,"P2P",64],[67108864,"P2P",128],[1099511627776,"P2P",64]],
+ "all_reduce": [[524288,"LL",0],[4194304,"NVLS",64],[268435456,"NVLS",16],[1099511627776,"NVLS",64]],
+ "all_gather": [[1048576,"LL",0],[4194304,"MC",128],[16777216,"PUSH",64],[1099511627776,"PUSH",128]],
+ "reduce_scatter": [[4194304,"LL",0],[16777216,"NVLS",16],[1099511627776,"P2P",128]],
  "all_to_all": [[4194304,"LL",0],[16777216,"PUSH",64],[1099511627776,"PUSH",128]],
- "broadcast": [[1048576,"LL",0],[4194304,"MC",128],[16777216,"MC",32],[268435456,"MC",16],[1099511627776,"MC",64]]
+ "broadcast": [[262144,"LL",0],[1048576,"MC",16],[16777216,"MC",128],[268435456,"MC",16],[1099511627776,"MC",64]]
 }
 })JSON";
 }  // namespace b200
