@@ -22,8 +22,8 @@ extern "C" {
 
 typedef struct ncclTpContext* ncclTp_t;
 
-/* Collective over comm. maxRows x maxCols bounds the outputs of ncclTpGemmReduceScatter
- * (fp32 accumulation window of maxRows/nRanks x maxCols per rank). */
+/* Collective over comm. maxRows x maxCols bounds the products of ncclTpGemmReduceScatter
+ * (a symmetric bf16 staging window of maxRows x maxCols per rank). */
 ncclResult_t ncclTpCreate(ncclComm_t comm, size_t maxRows, size_t maxCols, ncclTp_t* tp);
 ncclResult_t ncclTpDestroy(ncclTp_t tp);
 

@@ -136,7 +136,19 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
         const size_t o = (size_t)el * cap + pos;
         if (lane == 0) a.srcInfo[rank][o] = make_int2(s, ((const int*)slot)[0]);
         char* dstTok = (char*)a.outTokens[rank] + o * rowBytes;
-        for (size_t i = lane; i < rowBytes / 16; i += 32) st16(dstTok + i * 16, ldLocal16(slot + 16 + i * 16));
+        {
+          const size_t packs = rowBytes / 16;
+          size_t i = lane;
+          for (; i + 96 < packs; i += 128) {
+            uint4 v0 = ldLocal16(slot + 16 + i * 16), v1 = ldLocal16(slot + 16 + (i + 32) * 16);
+            uint4 v2 = ldLocal16(slot + 16 + (i + 64) * 16), v3 = ldLocal16(slot + 16 + (i + 96) * 16);
+            st16(dstTok + i * 16, v0);
+            st16(dstTok + (i + 32) * 16, v1);
+            st16(dstTok + (i + 64) * 16, v2);
+            st16(dstTok + (i + 96) * 16, v3);
+          }
+          for (; i < packs; i += 32) st16(dstTok + i * 16, ldLocal16(slot + 16 + i * 16));
+        }
         if (a.fp8) {
           const float* sc = (const float*)(slot + 16 + H);
           float* dsc = a.outScales[rank] + o * (H / 128);
@@ -178,7 +190,18 @@ __global__ void __launch_bounds__(kEpThreads, 1) epCombineKernel(const __grid_co
       const int2 info = a.srcInfo[rank][o];
       const char* src = (const char*)(y + o * H);
       char* dst = a.combBuf[info.x] + combOff + (size_t)info.y * H * 2;
-      for (int i = lane; i < H / 8; i += 32) st16(dst + (size_t)i * 16, ldLocal16(src + (size_t)i * 16));
+      // four independent 16-byte loads in flight per lane before the stores that depend on them
+      const int packs = H / 8;
+      int i = lane;
+      for (; i + 96 < packs; i += 128) {
+        uint4 v0 = ldLocal16(src + (size_t)i * 16), v1 = ldLocal16(src + (size_t)(i + 32) * 16);
+        uint4 v2 = ldLocal16(src + (size_t)(i + 64) * 16), v3 = ldLocal16(src + (size_t)(i + 96) * 16);
+        st16(dst + (size_t)i * 16, v0);
+        st16(dst + (size_t)(i + 32) * 16, v1);
+        st16(dst + (size_t)(i + 64) * 16, v2);
+        st16(dst + (size_t)(i + 96) * 16, v3);
+      }
+      for (; i < packs; i += 32) st16(dst + (size_t)i * 16, ldLocal16(src + (size_t)i * 16));
     }
   }
   __syncthreads();
@@ -208,16 +231,31 @@ __global__ void __launch_bounds__(kEpThreads, 1) epCombineKernel(const __grid_co
     for (int t = blockIdx.x; t < T; t += gridDim.x) {
       for (int c = threadIdx.x; c < H / 8; c += kEpThreads) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int k = 0; k < K; ++k) {
-          const long long e = a.topkIdx[rank][(size_t)t * K + k];
-          if (e < 0 || e >= a.numExperts) continue;
-          const float wk = a.topkW[rank][(size_t)t * K + k];
-          uint4 v = ldLocal16(a.combBuf[rank] + combOff + ((size_t)(t * K + k) * H + (size_t)c * 8) * 2);
-          const __nv_bfloat162* p = (const __nv_bfloat162*)&v;
+        // the rows of up to eight selected experts are fetched together, then accumulated in slot order
+        for (int k0 = 0; k0 < K; k0 += 8) {
+          uint4 v[8];
+          float wk[8];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            acc[2 * i] += wk * __bfloat162float(p[i].x);
-            acc[2 * i + 1] += wk * __bfloat162float(p[i].y);
+          for (int u = 0; u < 8; ++u) {
+            const int k = k0 + u;
+            wk[u] = 0.0f;
+            v[u] = make_uint4(0, 0, 0, 0);
+            if (k < K) {
+              const long long e = a.topkIdx[rank][(size_t)t * K + k];
+              if (e >= 0 && e < a.numExperts) {
+                wk[u] = a.topkW[rank][(size_t)t * K + k];
+                v[u] = ldLocal16(a.combBuf[rank] + combOff + ((size_t)(t * K + k) * H + (size_t)c * 8) * 2);
+              }
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const __nv_bfloat162* p = (const __nv_bfloat162*)&v[u];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              acc[2 * i] += wk[u] * __bfloat162float(p[i].x);
+              acc[2 * i + 1] += wk[u] * __bfloat162float(p[i].y);
+            }
           }
         }
         uint4 o;

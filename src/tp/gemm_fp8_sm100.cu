@@ -11,9 +11,10 @@
 // Persistent CTAs of 320 threads: warp 0 TMA producer (128x128-byte A tiles, 256x128-byte W tiles,
 // 128-byte swizzle, 4-stage ring), warp 1 MMA issuer, warps 2-9 epilogue (each warp owns 32 TMEM
 // lanes and one 128-column half of the tile: 128 fp32 accumulators per thread).
-// The fused modes work as in the bf16 kernel (gemm_sm100.cu): REDUCE adds the scaled fp32 tile
-// into the owning rank's buffer over NVLink with red.add; GATHER has comm CTAs pull remote row
-// blocks and their scales with plain peer loads. No TMA load uses cluster multicast or peer memory.
+// The fused modes work as in the bf16 kernel (gemm_sm100.cu): REDUCE stores the scaled tile as bf16
+// into this rank's slot of the owning rank's staging buffer over NVLink (summed afterwards);
+// GATHER has comm CTAs pull remote row blocks with bulk copies and their scales with plain peer
+// loads. No load uses cluster multicast; tensor-map TMA loads read local memory only.
 // Quantisation kernels for both operand kinds are at the end of the file.
 // Every wait is bounded; on expiry the kernel records a status, drains its TMA copies, frees its
 // tensor memory and returns.
@@ -68,35 +69,46 @@ tpGemmFp8Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int blocksPerRank = a.M / n / BM;
     const size_t blockBytes = (size_t)BM * a.K;
     const int commIdx = blockIdx.x - a.gemmCtas, commN = gridDim.x - a.gemmCtas;
+    constexpr int kPipeStages = 6;
+    constexpr uint32_t kPipeChunk = 32768;
+    static_assert((size_t)kPipeStages * kPipeChunk <= (size_t)STAGES * kStageBytes, "copy ring must fit the operand ring");
+    uint64_t* pipeBars = fullBar;
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < kPipeStages; ++s) mbarInit(smemAddr(&pipeBars[s]), 1);
+      mbarInitFence();
+    }
+    __syncthreads();
+    uint32_t phaseBits = 0;
     for (int step = 1; step < n && ok; ++step) {
       const int src = (rank + step) % n;
-      for (int b = commIdx; b < blocksPerRank; b += commN) {
+      for (int b = commIdx; b < blocksPerRank && ok; b += commN) {
         const int mb = src * blocksPerRank + b;
-        const char* from = (const char*)a.peerA[src] + (size_t)mb * blockBytes;
-        char* to = (char*)a.peerA[rank] + (size_t)mb * blockBytes;
-        const size_t packs = blockBytes / 16;
-        size_t i = threadIdx.x;
-        for (; i + 3 * kThreads < packs; i += 4 * kThreads) {
-          uint4 v[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) v[u] = ldStream16(from + (i + u * kThreads) * 16);
-#pragma unroll
-          for (int u = 0; u < 4; ++u) st16(to + (i + u * kThreads) * 16, v[u]);
-        }
-        for (; i < packs; i += kThreads) st16(to + i * 16, ldStream16(from + i * 16));
-        // scales of these 128 rows: one 512-byte run per K block
+        // scales of these 128 rows: one 512-byte run per K block, plain peer loads by all threads
         const float* sFrom = (const float*)((const char*)a.peerA[src] + a.scaleOffset);
         float* sTo = (float*)((char*)a.peerA[rank] + a.scaleOffset);
         for (int e = threadIdx.x; e < kBlocks * (BM / 4); e += kThreads) {
           const size_t off = (size_t)(e / (BM / 4)) * a.M + (size_t)mb * BM + (size_t)(e % (BM / 4)) * 4;
           st16(sTo + off, ldStream16(sFrom + off));
         }
-        fenceProxyAsync();
         __syncthreads();
         if (threadIdx.x == 0) {
-          __threadfence();
-          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.blockFlags + mb), "r"(a.flagEpoch) : "memory");
+          // the rows: bulk copies peer -> shared memory -> local, driven by this one thread
+          const char* from = (const char*)a.peerA[src] + (size_t)mb * blockBytes;
+          char* to = (char*)a.peerA[rank] + (size_t)mb * blockBytes;
+          ok = bulkPipe<kPipeStages, kPipeChunk>(to, from, blockBytes, smemAddr(smem), pipeBars, phaseBits);
+          if (ok) {
+            fenceProxyAsync();
+            __threadfence();
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.blockFlags + mb), "r"(a.flagEpoch) : "memory");
+          } else if (a.sync.status[rank] && ldRelaxedSys(a.sync.status[rank]) == DEV_OK) {
+            a.sync.status[rank][1] = WAIT_TILE;
+            a.sync.status[rank][2] = 5000 + mb;
+            a.sync.status[rank][3] = blockIdx.x;
+            __threadfence_system();
+            stRelaxedSys(a.sync.status[rank], DEV_TIMEOUT);
+          }
         }
+        ok = __syncthreads_and(ok);
       }
     }
     bar.sync(true, false);
@@ -268,13 +280,14 @@ tpGemmFp8Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
       if (bad) break;
       const int col = tc.nBlk * BN + h * 128;
-      if (a.mode == TP_MODE_REDUCE && n > 1) {
-        const int rowsPerRank = a.M / n;
-        float* dst = a.accum[tc.owner] + (size_t)(row - tc.owner * rowsPerRank) * a.N + col;
-#pragma unroll
-        for (int v = 0; v < 32; ++v) redAddF32x4(dst + v * 4, acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
-      } else {
-        __nv_bfloat16* dst = (__nv_bfloat16*)a.C + (size_t)row * a.ldc + col;
+      {
+        __nv_bfloat16* dst;
+        if (a.mode == TP_MODE_REDUCE && n > 1) {
+          const int rowsPerRank = a.M / n;
+          dst = (__nv_bfloat16*)a.partial[tc.owner] + ((size_t)rank * rowsPerRank + (row - tc.owner * rowsPerRank)) * a.N + col;
+        } else {
+          dst = (__nv_bfloat16*)a.C + (size_t)row * a.ldc + col;
+        }
 #pragma unroll
         for (int v = 0; v < 16; ++v) {
           uint4 o;

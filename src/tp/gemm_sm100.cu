@@ -10,16 +10,17 @@
 //   warps 2-5   epilogue: tcgen05.ld the accumulator (each warp owns 32 TMEM lanes = 32 rows),
 //               then, depending on the mode,
 //                 STORE      convert to bf16 and store C;
-//                 REDUCE     GEMM -> reduce-scatter: add the fp32 partial tile straight into the
-//                            accumulation buffer of the rank that owns those rows, over NVLink,
-//                            with 16-byte red.add; tiles are visited owner by owner, starting with
-//                            the next rank, so every step each GPU receives from exactly one peer.
+//                 REDUCE     GEMM -> reduce-scatter: store the tile, rounded to bf16 (what a separate
+//                            GEMM would hand to a reduce-scatter), straight into this rank's slot of
+//                            the staging buffer of the rank that owns those rows, over NVLink; tiles
+//                            are visited owner by owner, starting with the next rank, so every step
+//                            each GPU receives from exactly one peer. A small kernel sums the slots.
 //   GATHER mode all-gather -> GEMM: extra "comm" CTAs pull the other ranks' A rows from their
-//               windows into the local A buffer, 128-row block by block, and publish a flag per
-//               block; the TMA producer waits for the flag of the block it needs. Blocks are
-//               fetched in the order the GEMM consumes them (own rows first, then rank+1, ...).
-// No TMA load uses cluster multicast and no TMA load touches peer memory: remote data reaches this
-// GPU through plain peer loads / red.add issued by SM threads.
+//               windows into the local A buffer, 128-row block by block, with bulk copies
+//               (cp.async.bulk peer -> shared memory -> local, one issuing thread, several copies
+//               in flight) and publish a flag per block; the TMA producer waits for the flag of
+//               the block it needs. Blocks are fetched in the order the GEMM consumes them.
+// No load uses cluster multicast; tensor-map (tiled) TMA loads read local memory only.
 // Every wait (mbarrier, flag, cross-GPU barrier) is bounded; on expiry the kernel records a status,
 // drains its outstanding TMA copies, frees its tensor memory and returns.
 // The reference has no GEMM kernels; the comparison point is its reduce-scatter / all-gather plus a
@@ -69,31 +70,44 @@ tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     const int blocksPerRank = a.M / n / BM;
     const size_t blockBytes = (size_t)BM * a.K * 2;
     const int commIdx = blockIdx.x - a.gemmCtas, commN = gridDim.x - a.gemmCtas;
-    for (int step = 1; step < n && ok; ++step) {
-      const int src = (rank + step) % n;
-      for (int b = commIdx; b < blocksPerRank; b += commN) {
-        const int mb = src * blocksPerRank + b;
-        const char* from = (const char*)a.peerA[src] + (size_t)mb * blockBytes;
-        char* to = (char*)a.peerA[rank] + (size_t)mb * blockBytes;
-        const size_t packs = blockBytes / 16;
-        size_t i = threadIdx.x;
-        for (; i + 3 * kTpThreads < packs; i += 4 * kTpThreads) {
-          uint4 v[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) v[u] = ldStream16(from + (i + u * kTpThreads) * 16);
-#pragma unroll
-          for (int u = 0; u < 4; ++u) st16(to + (i + u * kTpThreads) * 16, v[u]);
-        }
-        for (; i < packs; i += kTpThreads) st16(to + i * 16, ldStream16(from + i * 16));
-        // the rows were written through the generic proxy and will be read by TMA (async proxy)
-        fenceProxyAsync();
-        __syncthreads();
-        if (threadIdx.x == 0) {
+    constexpr int kPipeStages = 6;
+    constexpr uint32_t kPipeChunk = 32768;
+    static_assert((size_t)kPipeStages * kPipeChunk <= (size_t)STAGES * kStageBytes, "copy ring must fit the operand ring");
+    uint64_t* pipeBars = fullBar;   // the first kPipeStages of the 2 * STAGES operand barriers (unused by a comm CTA)
+    static_assert(kPipeStages <= 2 * STAGES, "not enough barriers");
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < kPipeStages; ++s) mbarInit(smemAddr(&pipeBars[s]), 1);
+      mbarInitFence();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      // one thread drives bulk copies peer -> shared memory -> local rows; the copy engines of this SM do the work
+      uint32_t phaseBits = 0;
+      for (int step = 1; step < n && ok; ++step) {
+        const int src = (rank + step) % n;
+        for (int b = commIdx; b < blocksPerRank && ok; b += commN) {
+          const int mb = src * blocksPerRank + b;
+          const char* from = (const char*)a.peerA[src] + (size_t)mb * blockBytes;
+          char* to = (char*)a.peerA[rank] + (size_t)mb * blockBytes;
+          ok = bulkPipe<kPipeStages, kPipeChunk>(to, from, blockBytes, smemAddr(smem), pipeBars, phaseBits);
+          if (!ok) {
+            if (a.sync.status[rank] && ldRelaxedSys(a.sync.status[rank]) == DEV_OK) {
+              a.sync.status[rank][1] = WAIT_TILE;
+              a.sync.status[rank][2] = 5000 + mb;
+              a.sync.status[rank][3] = blockIdx.x;
+              __threadfence_system();
+              stRelaxedSys(a.sync.status[rank], DEV_TIMEOUT);
+            }
+            break;
+          }
+          // the rows were written through the async proxy and will be read by TMA loads of other CTAs
+          fenceProxyAsync();
           __threadfence();
           asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.blockFlags + mb), "r"(a.flagEpoch) : "memory");
         }
       }
     }
+    __syncthreads();
     bar.sync(true, false);   // nobody reads my rows any more
     bar.finish();
     return;
@@ -214,14 +228,15 @@ tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         tmemLd32(tBase + c * 32, r);
         tmemLdWait();
         const int col = tc.nBlk * BN + c * 32;
-        if (a.mode == TP_MODE_REDUCE) {
-          const int rowsPerRank = a.M / n;
-          float* dst = a.accum[tc.owner] + (size_t)(row - tc.owner * rowsPerRank) * a.N + col;
-#pragma unroll
-          for (int v = 0; v < 8; ++v)
-            redAddF32x4(dst + v * 4, __uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-        } else {
-          __nv_bfloat16* dst = (__nv_bfloat16*)a.C + (size_t)row * a.ldc + col;
+        {
+          // STORE / GATHER: C; REDUCE: slot `rank` of the owner's staging buffer (over NVLink when the owner is a peer)
+          __nv_bfloat16* dst;
+          if (a.mode == TP_MODE_REDUCE && n > 1) {
+            const int rowsPerRank = a.M / n;
+            dst = (__nv_bfloat16*)a.partial[tc.owner] + ((size_t)rank * rowsPerRank + (row - tc.owner * rowsPerRank)) * a.N + col;
+          } else {
+            dst = (__nv_bfloat16*)a.C + (size_t)row * a.ldc + col;
+          }
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             uint4 o;
@@ -253,22 +268,29 @@ tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   }
 }
 
-// out[i] = bf16(acc[i]): the fp32 accumulation buffer of GEMM -> reduce-scatter becomes the output.
-__global__ void tpConvertKernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ out, size_t count) {
+// out[i] = sum over sources of staged[src][i]: the partial products of GEMM -> reduce-scatter become the
+// output; bf16 inputs, fp32 accumulation in source order, bf16 result. count is a multiple of 8.
+__global__ void tpReduceKernel(const __nv_bfloat16* __restrict__ staged, __nv_bfloat16* __restrict__ out, size_t count, int nSources) {
   size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   const size_t stride = (size_t)gridDim.x * blockDim.x * 8;
   for (; i + 7 < count; i += stride) {
-    float4 a = *(const float4*)(acc + i), b = *(const float4*)(acc + i + 4);
-    __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
-    __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s = 0; s < nSources; ++s) {
+      const uint4 v = *(const uint4*)(staged + (size_t)s * count + i);
+      const __nv_bfloat162* p = (const __nv_bfloat162*)&v;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) { acc[2 * k] += __bfloat162float(p[k].x); acc[2 * k + 1] += __bfloat162float(p[k].y); }
+    }
     uint4 o;
-    o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1; o.z = *(uint32_t*)&p2; o.w = *(uint32_t*)&p3;
+    __nv_bfloat162* q = (__nv_bfloat162*)&o;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) q[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
     *(uint4*)(out + i) = o;
   }
 }
 
 const void* tpGemmKernelFn() { return (const void*)tpGemmKernel; }
-const void* tpConvertKernelFn() { return (const void*)tpConvertKernel; }
+const void* tpReduceKernelFn() { return (const void*)tpReduceKernel; }
 size_t tpGemmSmemBytes() { return kTpSmemBytes; }
 int tpGemmThreads() { return kTpThreads; }
 

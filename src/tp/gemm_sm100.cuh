@@ -46,6 +46,59 @@ __device__ __forceinline__ void tmaLoad2d(uint32_t dstSmem, const CUtensorMap* m
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dstSmem), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
+// ---------------------------------------------------------------- bulk copies (no tensor map, no multicast)
+// global -> shared, completion counted on an mbarrier; the source may be a peer GPU's memory
+__device__ __forceinline__ void bulkLoad(uint32_t dstSmem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dstSmem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// shared -> global, tracked by bulk groups
+__device__ __forceinline__ void bulkStore(void* dst, uint32_t srcSmem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(srcSmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulkCommit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulkWaitRead() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulkWaitAll() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// Moves `bytes` (a multiple of 16) from `from` (possibly peer memory) to `to` (local memory) through a
+// ring of shared-memory stages with bulk copies issued by ONE thread: several loads stay in flight
+// over NVLink while earlier chunks are written out, without occupying the other threads of the CTA.
+// `bars` are kStages initialised mbarriers (count 1); `phase` carries their parity across calls.
+// Returns false when a load did not arrive within the wait limit (nothing is left in flight then).
+template <int kStages, uint32_t kChunk>
+__device__ __forceinline__ bool bulkPipe(char* to, const char* from, size_t bytes, uint32_t smemBase, uint64_t* bars, uint32_t& phaseBits) {
+  const int total = (int)((bytes + kChunk - 1) / kChunk);
+  constexpr int kAhead = kStages - 2;    // loads in flight ahead of the store being issued
+  bool ok = true;
+  int stored = 0;
+  for (int i = 0; i < total + kAhead && ok; ++i) {
+    if (i < total) {
+      const int s = i % kStages;
+      // the store that last used this stage was committed two stores ago: at most one newer group may still be reading
+      if (i >= kStages) bulkWaitRead<1>();
+      const uint32_t n = (uint32_t)(bytes - (size_t)i * kChunk < kChunk ? bytes - (size_t)i * kChunk : kChunk);
+      const uint32_t b = smemAddr(&bars[s]);
+      mbarExpectTx(b, n);
+      bulkLoad(smemBase + s * kChunk, from + (size_t)i * kChunk, n, b);
+    }
+    if (i >= kAhead) {
+      const int j = i - kAhead, s = j % kStages;
+      const uint32_t n = (uint32_t)(bytes - (size_t)j * kChunk < kChunk ? bytes - (size_t)j * kChunk : kChunk);
+      if (!mbarWait(smemAddr(&bars[s]), (phaseBits >> s) & 1u)) { ok = false; break; }
+      phaseBits ^= 1u << s;
+      bulkStore(to + (size_t)j * kChunk, smemBase + s * kChunk, n);
+      bulkCommit();
+      ++stored;
+    }
+  }
+  if (!ok) {
+    // loads already issued still write into shared memory: give them a bounded chance to land
+    for (int j = stored; j < total && j < stored + kStages; ++j) mbarWait(smemAddr(&bars[j % kStages]), (phaseBits >> (j % kStages)) & 1u, 1u << 20);
+  }
+  bulkWaitAll();
+  return ok;
+}
+
 __device__ __forceinline__ void prefetchTensorMap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }

@@ -12,13 +12,13 @@
 using namespace b200;
 
 namespace b200 {
-B200_PARAM(TpCommCtas, "B200_TP_COMM_CTAS", 16, "CTAs that gather remote rows in all-gather -> GEMM")
+B200_PARAM(TpCommCtas, "B200_TP_COMM_CTAS", 12, "CTAs that gather remote rows in all-gather -> GEMM")
 }
 
 struct ncclTpContext {
   ncclComm* comm = nullptr;
   int smCount = 0;
-  float* accum = nullptr;          // symmetric fp32 window [maxRows / n, maxCols]
+  void* accum = nullptr;           // symmetric staging window: bf16 [n sources][maxRows / n][maxCols]
   size_t accumBytes = 0;
   SymWindow* accumWin = nullptr;
   uint32_t* blockFlags = nullptr;  // one word per 128-row block (all-gather -> GEMM)
@@ -168,24 +168,24 @@ ncclResult_t ncclTpGemmReduceScatterFp8(ncclTp_t tp, const void* A, const float*
   NCCLCHECK(checkShapeFp8(M, N, K, n));
   NCCLCHECK(devPlaneCheckStatus(comm));
   if (n == 1) return ncclTpGemmFp8(tp, A, scaleA, W, scaleW, out, M, N, K, stream);
-  const size_t need = (size_t)(M / n) * N * sizeof(float);
-  if (need > tp->accumBytes) { WARN("ncclTpGemmReduceScatterFp8: %d x %d exceeds the context's accumulation window", M, N); return ncclInvalidArgument; }
-  CUDACHECK(cudaMemsetAsync(tp->accum, 0, need, stream));
+  const size_t need = (size_t)M * N * 2;
+  if (need > tp->accumBytes) { WARN("ncclTpGemmReduceScatterFp8: %d x %d exceeds the context's staging window", M, N); return ncclInvalidArgument; }
   TpGemmArgs a;
   memset(&a, 0, sizeof(a));
   a.M = M; a.N = N; a.K = K;
   a.mode = TP_MODE_REDUCE;
   a.rank = comm->rank; a.nRanks = n;
   a.scaleA = scaleA; a.scaleW = scaleW;
-  for (int p = 0; p < n; ++p) a.accum[p] = (float*)tp->accumWin->host.peerPtr[p];
+  for (int p = 0; p < n; ++p) a.partial[p] = tp->accumWin->host.peerPtr[p];
   fillSyncTp(comm, &a.sync);
   int tiles = (M / 128) * (N / 256);
   NCCLCHECK(launchGemmFp8(tp, A, W, &a, std::min(tp->smCount, tiles), stream));
   size_t count = (size_t)(M / n) * N;
   int ctas = (int)std::min<size_t>((count / 8 + 255) / 256, (size_t)tp->smCount * 8);
-  const float* acc = tp->accum;
-  void* args[3] = {(void*)&acc, &out, &count};
-  CUDACHECK(cudaLaunchKernel(tpConvertKernelFn(), dim3(ctas), dim3(256), args, 0, stream));
+  const void* staged = tp->accum;
+  int nSources = n;
+  void* args[4] = {(void*)&staged, &out, &count, &nSources};
+  CUDACHECK(cudaLaunchKernel(tpReduceKernelFn(), dim3(ctas), dim3(256), args, 0, stream));
   if (comm->devPlane) comm->devPlane->launches++;
   return ncclSuccess;
 }
@@ -249,7 +249,7 @@ ncclResult_t ncclTpCreate(ncclComm_t comm, size_t maxRows, size_t maxCols, ncclT
   if (cur != comm->cudaDev) CUDACHECK(cudaSetDevice(comm->cudaDev));
   CUDACHECK(cudaDeviceGetAttribute(&tp->smCount, cudaDevAttrMultiProcessorCount, comm->cudaDev));
   const int n = comm->nRanks;
-  tp->accumBytes = (maxRows / n) * maxCols * sizeof(float);
+  tp->accumBytes = n > 1 ? maxRows * maxCols * 2 : 0;   // bf16 staging: one [maxRows / n, maxCols] slot per source rank
   if (tp->accumBytes) {
     NCCLCHECK(memAlloc((void**)&tp->accum, tp->accumBytes, comm->cudaDev));
     if (n > 1) {
@@ -324,24 +324,24 @@ ncclResult_t ncclTpGemmReduceScatter(ncclTp_t tp, const void* A, const void* W, 
   NCCLCHECK(checkShape(M, N, K, n));
   NCCLCHECK(devPlaneCheckStatus(comm));
   if (n == 1) return ncclTpGemm(tp, A, W, out, M, N, K, stream);
-  const size_t need = (size_t)(M / n) * N * sizeof(float);
-  if (need > tp->accumBytes) { WARN("ncclTpGemmReduceScatter: %d x %d exceeds the context's accumulation window", M, N); return ncclInvalidArgument; }
-  CUDACHECK(cudaMemsetAsync(tp->accum, 0, need, stream));
+  const size_t need = (size_t)M * N * 2;
+  if (need > tp->accumBytes) { WARN("ncclTpGemmReduceScatter: %d x %d exceeds the context's staging window", M, N); return ncclInvalidArgument; }
   TpGemmArgs a;
   memset(&a, 0, sizeof(a));
   a.M = M; a.N = N; a.K = K;
   a.mode = TP_MODE_REDUCE;
   a.rank = comm->rank; a.nRanks = n;
-  for (int p = 0; p < n; ++p) a.accum[p] = (float*)tp->accumWin->host.peerPtr[p];
+  for (int p = 0; p < n; ++p) a.partial[p] = tp->accumWin->host.peerPtr[p];
   fillSyncTp(comm, &a.sync);
   int tiles = (M / 128) * (N / 256);
   NCCLCHECK(launchGemm(tp, A, W, &a, std::min(tp->smCount, tiles), stream));
-  // kernel completion implies that every rank's partial sums have landed here
+  // kernel completion implies that every rank's partial tiles have landed in this rank's staging slots
   size_t count = (size_t)(M / n) * N;
   int ctas = (int)std::min<size_t>((count / 8 + 255) / 256, (size_t)tp->smCount * 8);
-  const float* acc = tp->accum;
-  void* args[3] = {(void*)&acc, &out, &count};
-  CUDACHECK(cudaLaunchKernel(tpConvertKernelFn(), dim3(ctas), dim3(256), args, 0, stream));
+  const void* staged = tp->accum;
+  int nSources = n;
+  void* args[4] = {(void*)&staged, &out, &count, &nSources};
+  CUDACHECK(cudaLaunchKernel(tpReduceKernelFn(), dim3(ctas), dim3(256), args, 0, stream));
   if (comm->devPlane) comm->devPlane->launches++;
   return ncclSuccess;
 }

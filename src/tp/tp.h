@@ -6,14 +6,14 @@ namespace b200 {
 
 enum TpMode : int {
   TP_MODE_STORE = 0,    // C = A * W^T, stored locally
-  TP_MODE_REDUCE = 1,   // GEMM -> reduce-scatter: partial tiles are added into the owner's fp32 buffer
+  TP_MODE_REDUCE = 1,   // GEMM -> reduce-scatter: bf16 partial tiles are stored into the owner's staging buffer, summed there afterwards
   TP_MODE_GATHER = 2,   // all-gather -> GEMM: comm CTAs pull remote row blocks while the GEMM runs
 };
 
 struct TpGemmArgs {
   void* C;                        // bf16 output [M, ldc] (STORE / GATHER)
   int ldc;
-  float* accum[kMaxRanks];        // REDUCE: accum[p] = rank p's fp32 buffer [M / nRanks, N], mapped here
+  void* partial[kMaxRanks];       // REDUCE: partial[p] = rank p's staging buffer, bf16 [nRanks sources][M / nRanks][N], mapped here
   const void* peerA[kMaxRanks];   // GATHER: peerA[p] = rank p's A buffer [M, K] bf16, mapped here
   uint32_t* blockFlags;           // GATHER: one word per 128-row block of A, set to flagEpoch when landed
   uint32_t flagEpoch;
@@ -61,7 +61,7 @@ const void* tpQuantRowsKernelFn();     // (const bf16* x, uint8_t* q, float* sca
 const void* tpQuantBlocksKernelFn();   // same arguments: 128 x 128 blocks, scales [K/128][rows/128]
 size_t tpGemmFp8SmemBytes();
 int tpGemmFp8Threads();
-const void* tpConvertKernelFn();
+const void* tpReduceKernelFn();        // (const bf16* staged, bf16* out, size_t count, int nSources): out = sum over sources, fp32 accumulation
 size_t tpGemmSmemBytes();
 int tpGemmThreads();
 
