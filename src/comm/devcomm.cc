@@ -12,7 +12,7 @@
 
 namespace b200 {
 
-B200_PARAM(DevCommTimeoutMs, "NCCL_B200_DEVCOMM_TIMEOUT_MS", 10000, "default budget of device-API waits (barriers, low-latency receives), milliseconds");
+B200_PARAM(DevCommTimeoutMs, "B200_DEVCOMM_TIMEOUT_MS", 10000, "default budget of device-API waits (barriers, low-latency receives), milliseconds");
 
 struct DevCommState {
   void* buf = nullptr;

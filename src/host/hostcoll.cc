@@ -27,8 +27,8 @@ struct HostPlane {
   volatile uint32_t* abortFlag = nullptr;
 };
 
-B200_PARAM(HostShm, "NCCL_B200_HOST_SHM", 0, "1: ranks of one host exchange host-memory messages through shared-memory rings instead of TCP");
-B200_PARAM(HostShmKb, "NCCL_B200_HOST_SHM_KB", 4096, "capacity of one shared-memory ring, KiB");
+B200_PARAM(HostShm, "B200_HOST_SHM", 0, "1: ranks of one host exchange host-memory messages through shared-memory rings instead of TCP");
+B200_PARAM(HostShmKb, "B200_HOST_SHM_KB", 4096, "capacity of one shared-memory ring, KiB");
 
 struct ShmOp { ShmLink* link; char* p; size_t n, off; bool send; };
 
@@ -57,7 +57,7 @@ static ncclResult_t shmRun(HostPlane* hp, std::vector<ShmOp>& ops) {
   return ncclSuccess;
 }
 
-B200_PARAM(HostNet, "NCCL_B200_HOST_NET", 0, "1: host-memory messages go through the network backend (plugin or built-in Socket) and the proxy thread; 0: direct TCP mesh");
+B200_PARAM(HostNet, "B200_HOST_NET", 0, "1: host-memory messages go through the network backend (plugin or built-in Socket) and the proxy thread; 0: direct TCP mesh");
 
 static constexpr int kTagHostMesh = BS_TAG_USER + 1;
 

@@ -32,9 +32,9 @@
 
 namespace b200 {
 
-B200_PARAM(RasKeepAliveMs, "NCCL_B200_RAS_KEEPALIVE_MS", 1000, "interval of RAS keep-alive pings, milliseconds");
+B200_PARAM(RasKeepAliveMs, "B200_RAS_KEEPALIVE_MS", 1000, "interval of RAS keep-alive pings, milliseconds");
 B200_PARAM(RasTimeoutFactor, "RAS_TIMEOUT_FACTOR", 1, "multiplier applied to every RAS time-out");
-B200_PARAM(RasDeadAfter, "NCCL_B200_RAS_DEAD_AFTER", 5, "missed keep-alives after which a process is declared dead");
+B200_PARAM(RasDeadAfter, "B200_RAS_DEAD_AFTER", 5, "missed keep-alives after which a process is declared dead");
 
 namespace {
 

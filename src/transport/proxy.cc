@@ -14,8 +14,8 @@
 
 namespace b200 {
 
-B200_PARAM(NetSliceKb, "NCCL_B200_NET_SLICE_KB", 512, "slice size of proxy network operations, KiB");
-B200_PARAM(NetInflight, "NCCL_B200_NET_INFLIGHT", 8, "slices of one proxy operation kept in flight");
+B200_PARAM(NetSliceKb, "B200_NET_SLICE_KB", 512, "slice size of proxy network operations, KiB");
+B200_PARAM(NetInflight, "B200_NET_INFLIGHT", 8, "slices of one proxy operation kept in flight");
 
 static constexpr int kTagNetMesh = BS_TAG_USER + 7;
 
