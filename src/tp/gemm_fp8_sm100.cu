@@ -35,7 +35,8 @@ constexpr int kThreads = 320, kEpiWarps = 8;
 constexpr uint32_t kStageABytes = BM * BK, kStageBBytes = BN * BK;
 constexpr uint32_t kStageBytes = kStageABytes + kStageBBytes;
 constexpr uint32_t kTmemCols = 512;
-constexpr size_t kSmemBytes = 1024 + (size_t)STAGES * kStageBytes + 256;
+constexpr size_t kEpiBufBytes = kEpiWarps * 4096;   // one 32 x 128-byte transpose buffer per epilogue warp
+constexpr size_t kSmemBytes = 1024 + (size_t)STAGES * kStageBytes + 256 + kEpiBufBytes;
 constexpr int kPrefetch = 4;   // K blocks of scale look-ahead
 }  // namespace
 
@@ -50,6 +51,7 @@ tpGemmFp8Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   uint64_t* accEmpty = accFull + 2;
   uint32_t* tmemSlot = (uint32_t*)(accEmpty + 2);
   volatile uint32_t* abortFlag = tmemSlot + 1;
+  uint8_t* epiBuf = ctrl + 256;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = a.rank, n = a.nRanks;
@@ -279,24 +281,42 @@ tpGemmFp8Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
       }
       if (bad) break;
-      const int col = tc.nBlk * BN + h * 128;
+      // final tile: bf16, transposed through shared memory so that every store instruction writes
+      // whole 128-byte row segments (see the bf16 kernel); REDUCE targets the owner's staging slot
       {
-        __nv_bfloat16* dst;
+        const int row0 = tc.mBlk * BM + q * 32;
+        __nv_bfloat16* dstBase;
+        size_t ld;
         if (a.mode == TP_MODE_REDUCE && n > 1) {
           const int rowsPerRank = a.M / n;
-          dst = (__nv_bfloat16*)a.partial[tc.owner] + ((size_t)rank * rowsPerRank + (row - tc.owner * rowsPerRank)) * a.N + col;
+          dstBase = (__nv_bfloat16*)a.partial[tc.owner] + ((size_t)rank * rowsPerRank + (row0 - tc.owner * rowsPerRank)) * a.N + (size_t)tc.nBlk * BN + h * 128;
+          ld = (size_t)a.N;
         } else {
-          dst = (__nv_bfloat16*)a.C + (size_t)row * a.ldc + col;
+          dstBase = (__nv_bfloat16*)a.C + (size_t)row0 * a.ldc + (size_t)tc.nBlk * BN + h * 128;
+          ld = (size_t)a.ldc;
         }
+        uint8_t* wbuf = epiBuf + (size_t)(warp - 2) * 4096;
 #pragma unroll
-        for (int v = 0; v < 16; ++v) {
-          uint4 o;
-          __nv_bfloat162 p0 = __floats2bfloat162_rn(acc[8 * v], acc[8 * v + 1]);
-          __nv_bfloat162 p1 = __floats2bfloat162_rn(acc[8 * v + 2], acc[8 * v + 3]);
-          __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[8 * v + 4], acc[8 * v + 5]);
-          __nv_bfloat162 p3 = __floats2bfloat162_rn(acc[8 * v + 6], acc[8 * v + 7]);
-          o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1; o.z = *(uint32_t*)&p2; o.w = *(uint32_t*)&p3;
-          *(uint4*)(dst + v * 8) = o;
+        for (int cc = 0; cc < 2; ++cc) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 o;
+            const int b0 = cc * 64 + j * 8;
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(acc[b0], acc[b0 + 1]);
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(acc[b0 + 2], acc[b0 + 3]);
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[b0 + 4], acc[b0 + 5]);
+            __nv_bfloat162 p3 = __floats2bfloat162_rn(acc[b0 + 6], acc[b0 + 7]);
+            o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1; o.z = *(uint32_t*)&p2; o.w = *(uint32_t*)&p3;
+            *(uint4*)(wbuf + lane * 128 + ((j ^ (lane & 7)) * 16)) = o;
+          }
+          __syncwarp();
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int rr = k * 4 + (lane >> 3), j = lane & 7;
+            const uint4 o = *(const uint4*)(wbuf + rr * 128 + ((j ^ (rr & 7)) * 16));
+            *(uint4*)((char*)(dstBase + (size_t)rr * ld) + cc * 128 + j * 16) = o;
+          }
+          __syncwarp();
         }
       }
     }

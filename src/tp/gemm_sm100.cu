@@ -39,7 +39,8 @@ constexpr int kTpThreads = 192;
 constexpr uint32_t kStageABytes = BM * BK * 2, kStageBBytes = BN * BK * 2;
 constexpr uint32_t kStageBytes = kStageABytes + kStageBBytes;
 constexpr uint32_t kTmemCols = 512;
-constexpr size_t kTpSmemBytes = 1024 + (size_t)STAGES * kStageBytes + 256;
+constexpr size_t kEpiBufBytes = 4 * 4096;   // one 32 x 128-byte transpose buffer per epilogue warp
+constexpr size_t kTpSmemBytes = 1024 + (size_t)STAGES * kStageBytes + 256 + kEpiBufBytes;
 
 __global__ void __launch_bounds__(kTpThreads, 1)
 tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ TpGemmArgs a) {
@@ -52,6 +53,7 @@ tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   uint64_t* accEmpty = accFull + 2;               // [2]
   uint32_t* tmemSlot = (uint32_t*)(accEmpty + 2);
   volatile uint32_t* abortFlag = tmemSlot + 1;
+  uint8_t* epiBuf = ctrl + 256;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = a.rank, n = a.nRanks;
@@ -221,22 +223,30 @@ tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       const uint32_t aph = (it >> 1) & 1;
       if (!mbarWait(smemAddr(&accFull[buf]), aph)) { if (lane == 0) fail(WAIT_TILE, 4000 + buf); break; }
       tcFenceAfter();
-      const int row = tc.mBlk * BM + q * 32 + lane;
+      const int row0 = tc.mBlk * BM + q * 32;   // first of this warp's 32 rows
       const uint32_t tBase = tmemBase + ((uint32_t)(q * 32) << 16) + buf * BN;
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmemLd32(tBase + c * 32, r);
-        tmemLdWait();
-        const int col = tc.nBlk * BN + c * 32;
-        {
-          // STORE / GATHER: C; REDUCE: slot `rank` of the owner's staging buffer (over NVLink when the owner is a peer)
-          __nv_bfloat16* dst;
-          if (a.mode == TP_MODE_REDUCE && n > 1) {
-            const int rowsPerRank = a.M / n;
-            dst = (__nv_bfloat16*)a.partial[tc.owner] + ((size_t)rank * rowsPerRank + (row - tc.owner * rowsPerRank)) * a.N + col;
-          } else {
-            dst = (__nv_bfloat16*)a.C + (size_t)row * a.ldc + col;
-          }
+      // STORE / GATHER: C; REDUCE: slot `rank` of the owner's staging buffer (over NVLink when the owner is a peer)
+      __nv_bfloat16* dstBase;
+      size_t ld;
+      if (a.mode == TP_MODE_REDUCE && n > 1) {
+        const int rowsPerRank = a.M / n;
+        dstBase = (__nv_bfloat16*)a.partial[tc.owner] + ((size_t)rank * rowsPerRank + (row0 - tc.owner * rowsPerRank)) * a.N + (size_t)tc.nBlk * BN;
+        ld = (size_t)a.N;
+      } else {
+        dstBase = (__nv_bfloat16*)a.C + (size_t)row0 * a.ldc + (size_t)tc.nBlk * BN;
+        ld = (size_t)a.ldc;
+      }
+      // Each lane owns one row of the accumulator, so storing straight from registers would write 16
+      // scattered bytes per lane and instruction. The warp instead transposes 64 columns at a time
+      // through 4 KiB of shared memory (16-byte chunks XOR-swizzled by row against bank conflicts) and
+      // writes 128 contiguous bytes per row, four rows per instruction: whole lines for HBM and NVLink.
+      uint8_t* wbuf = epiBuf + (size_t)(warp - 2) * 4096;
+      for (int cc = 0; cc < BN / 64; ++cc) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tmemLd32(tBase + (cc * 2 + half) * 32, r);
+          tmemLdWait();
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             uint4 o;
@@ -245,9 +255,18 @@ tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
             __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
             o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1; o.z = *(uint32_t*)&p2; o.w = *(uint32_t*)&p3;
-            *(uint4*)(dst + v * 8) = o;
+            const int j = half * 4 + v;   // 16-byte chunk of the 128-byte row segment
+            *(uint4*)(wbuf + lane * 128 + ((j ^ (lane & 7)) * 16)) = o;
           }
         }
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int rr = k * 4 + (lane >> 3), j = lane & 7;
+          const uint4 o = *(const uint4*)(wbuf + rr * 128 + ((j ^ (rr & 7)) * 16));
+          *(uint4*)((char*)(dstBase + (size_t)rr * ld) + cc * 128 + j * 16) = o;
+        }
+        __syncwarp();
       }
       tcFenceBefore();
       __syncwarp();
