@@ -25,6 +25,7 @@ B200_PARAM(P2pDisable, "P2P_DISABLE", 0, "Never map peer memory; GPU buffers are
 B200_PARAM(CopyThreads, "B200_COPY_THREADS", 512, "Threads per CTA of the local copy kernel")
 B200_PARAM(CopyUnroll, "B200_COPY_UNROLL", 4, "16-byte loads in flight per thread of the local copy kernel (4 or 8)")
 B200_PARAM(CopyCtasPerSm, "B200_COPY_CTAS_PER_SM", 16, "Grid size of the local copy kernel in CTAs per SM")
+B200_PARAM(LLMulticast, "B200_LL_MC_MIN_RANKS", 0, "Flagged-line all-reduce / all-gather publish each line with one multimem.st instead of one store per peer from this many ranks on (0 = never)")
 B200_PARAM(LaunchPdl, "B200_PDL", 0, "Launch collectives with programmatic stream serialisation")
 
 // ------------------------------------------------------------------------------------ tuning
@@ -237,6 +238,7 @@ static void baseArgs(ncclComm* comm, CollArgs* a, int func) {
   fillSync(comm, &a->sync);
   for (int p = 0; p < comm->nRanks; ++p) a->ll[p] = (char*)dp->resWin->host.peerPtr[p] + dp->offLL;
   a->llEpoch[comm->rank] = dp->llEpoch;
+  if (dp->resWin->host.mcPtr && paramLLMulticast() && comm->nRanks >= paramLLMulticast()) a->llMc = (char*)dp->resWin->host.mcPtr + dp->offLL;
 }
 
 // Peer-visible aliases of `ptr` when it lies in a symmetric window (same offset on every rank).

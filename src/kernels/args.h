@@ -90,6 +90,7 @@ struct CollArgs {
   // flagged-line (LL) resources
   void* ll[kMaxRanks];                  // ll[p]: rank p's LL region
   uint32_t* llEpoch[kMaxRanks];         // llEpoch[r]: {epoch, finished CTAs} private to rank r
+  char* llMc;                           // multicast alias of the flagged-line region (null: unicast stores only)
 };
 
 struct P2pOp {

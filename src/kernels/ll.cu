@@ -92,9 +92,18 @@ __global__ void __launch_bounds__(kCtaThreads, 1) llReduceKernel(const __grid_co
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   // phase 1: publish
+  // all-reduce sends the same line to every peer: with a multicast alias of the region one
+  // multimem.st does it (the switch replicates; the copy that lands in this rank's own region is unused)
+  const bool mcast = a.llMc != nullptr && !scatter && !rooted;
   for (size_t l = tid; l < nLines; l += stride) {
     const size_t valid = bytes - l * 8;
     uint64_t d = scatter ? 0 : llLoad8(in + l * 8, valid);
+    if (mcast) {
+      char* slot = a.llMc + ((size_t)(ll.parity * kMaxRanks + rank) * kLLLines) * 16 + l * 16;
+      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(slot), "r"((uint32_t)d), "r"(ll.epoch), "r"((uint32_t)(d >> 32)),
+                   "r"(ll.epoch) : "memory");
+      continue;
+    }
     for (int j = 1; j < n; ++j) {
       const int p = (rank + j) % n;
       if (rooted && p != a.root) continue;

@@ -24,6 +24,15 @@ def test_forced_schedules(algo, registered):
     _check(res, n)
 
 
+def test_flagged_lines_with_multicast_stores():
+    """The flagged-line all-reduce publishes each line with one multimem.st when asked to."""
+    n = min(_ngpus(), 8)
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    res = run_ranks(_colls_rank, n, args=(True, "LL"), env={"NCCL_B200_LL_MC_MIN_RANKS": "2"}, timeout=300)
+    _check(res, n)
+
+
 def _mgmt_rank(rank, nranks, uid):
     import ctypes
     import torch
