@@ -81,9 +81,11 @@ tpGemmFp8Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
     __syncthreads();
     uint32_t phaseBits = 0;
-    for (int step = 1; step < n && ok; ++step) {
-      const int src = (rank + step) % n;
-      for (int b = commIdx; b < blocksPerRank && ok; b += commN) {
+    // remote blocks in the order the GEMM consumes them (rank+1 first), dealt round-robin to the comm CTAs
+    for (int idx = commIdx; idx < (n - 1) * blocksPerRank && ok; idx += commN) {
+      const int src = (rank + 1 + idx / blocksPerRank) % n;
+      {
+        const int b = idx % blocksPerRank;
         const int mb = src * blocksPerRank + b;
         // scales of these 128 rows: one 512-byte run per K block, plain peer loads by all threads
         const float* sFrom = (const float*)((const char*)a.peerA[src] + a.scaleOffset);

@@ -85,9 +85,11 @@ tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     if (threadIdx.x == 0) {
       // one thread drives bulk copies peer -> shared memory -> local rows; the copy engines of this SM do the work
       uint32_t phaseBits = 0;
-      for (int step = 1; step < n && ok; ++step) {
-        const int src = (rank + step) % n;
-        for (int b = commIdx; b < blocksPerRank && ok; b += commN) {
+      // remote blocks in the order the GEMM consumes them (rank+1 first), dealt round-robin to the comm CTAs
+      for (int idx = commIdx; idx < (n - 1) * blocksPerRank && ok; idx += commN) {
+        const int src = (rank + 1 + idx / blocksPerRank) % n;
+        {
+          const int b = idx % blocksPerRank;
           const int mb = src * blocksPerRank + b;
           const char* from = (const char*)a.peerA[src] + (size_t)mb * blockBytes;
           char* to = (char*)a.peerA[rank] + (size_t)mb * blockBytes;
