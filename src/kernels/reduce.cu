@@ -23,15 +23,12 @@ __global__ void __launch_bounds__(kCtaThreads, 1) reduceP2pKernel(const __grid_c
   const size_t begin = a.sliceBegin[rank], cnt = a.sliceCount[rank];
   if (ok && cnt) {
     constexpr int N = 16 / sizeof(T);
-    const char* src[kMaxRanks];
-    char* dst[kMaxRanks];
-#pragma unroll
-    for (int p = 0; p < kMaxRanks; ++p) {
-      src[p] = p < n ? (const char*)a.send[p] + begin * sizeof(T) : nullptr;
-      dst[p] = p < n ? (a.dstAll ? (char*)a.recv[p] : (char*)a.lrecv[rank]) + a.dstOff[rank] * sizeof(T) : nullptr;
-    }
+    // Peer pointers stay in the kernel-parameter bank (a.send / a.recv) and are re-read per access:
+    // keeping sixteen 64-bit pointers in registers next to 2 * nRanks 16-byte packs spilled.
+    const size_t inOff = begin * sizeof(T), outOff = a.dstOff[rank] * sizeof(T);
     const int nDst = a.dstAll ? n : 1;
-    if (!a.dstAll) dst[0] = (char*)a.lrecv[rank] + a.dstOff[rank] * sizeof(T);
+    auto srcOf = [&](int p) { return (const char*)a.send[p] + inOff; };
+    auto dstOf = [&](int q) { return (a.dstAll ? (char*)a.recv[q] : (char*)a.lrecv[rank]) + outOff; };
     const size_t nPacks = a.vec16 ? cnt / N : 0;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -41,8 +38,9 @@ __global__ void __launch_bounds__(kCtaThreads, 1) reduceP2pKernel(const __grid_c
 #pragma unroll
       for (int p = 0; p < kMaxRanks; ++p) {
         if (p < n) {
-          v0[p] = ldStream16(src[p] + i * 16);
-          v1[p] = ldStream16(src[p] + (i + stride) * 16);
+          const char* s = srcOf(p);
+          v0[p] = ldStream16(s + i * 16);
+          v1[p] = ldStream16(s + (i + stride) * 16);
         }
       }
       PackAcc<T, OP> a0, a1;
@@ -56,24 +54,24 @@ __global__ void __launch_bounds__(kCtaThreads, 1) reduceP2pKernel(const __grid_c
       uint4 r1 = a1.get(a.scaleMode, a.scaleF, a.scaleD, a.intDiv);
 #pragma unroll
       for (int q = 0; q < kMaxRanks; ++q) {
-        if (q < nDst) { st16(dst[q] + i * 16, r0); st16(dst[q] + (i + stride) * 16, r1); }
+        if (q < nDst) { char* d = dstOf(q); st16(d + i * 16, r0); st16(d + (i + stride) * 16, r1); }
       }
     }
     for (; i < nPacks; i += stride) {
       PackAcc<T, OP> acc;
-      acc.set(ldStream16(src[0] + i * 16));
+      acc.set(ldStream16(srcOf(0) + i * 16));
 #pragma unroll
-      for (int p = 1; p < kMaxRanks; ++p) if (p < n) acc.add(ldStream16(src[p] + i * 16));
+      for (int p = 1; p < kMaxRanks; ++p) if (p < n) acc.add(ldStream16(srcOf(p) + i * 16));
       uint4 r = acc.get(a.scaleMode, a.scaleF, a.scaleD, a.intDiv);
 #pragma unroll
-      for (int q = 0; q < kMaxRanks; ++q) if (q < nDst) st16(dst[q] + i * 16, r);
+      for (int q = 0; q < kMaxRanks; ++q) if (q < nDst) st16(dstOf(q) + i * 16, r);
     }
     // ragged tail (and the whole slice when a pointer is not 16-byte aligned): one element at a time
     for (size_t e = nPacks * N + (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < cnt; e += stride) {
-      typename Elem<T>::Acc acc = Elem<T>::ld(((const T*)src[0])[e]);
-      for (int p = 1; p < n; ++p) acc = redApply<OP>(acc, Elem<T>::ld(((const T*)src[p])[e]));
+      typename Elem<T>::Acc acc = Elem<T>::ld(((const T*)srcOf(0))[e]);
+      for (int p = 1; p < n; ++p) acc = redApply<OP>(acc, Elem<T>::ld(((const T*)srcOf(p))[e]));
       T r = scalarPost<T, OP>(acc, a);
-      for (int q = 0; q < nDst; ++q) ((T*)dst[q])[e] = r;
+      for (int q = 0; q < nDst; ++q) ((T*)dstOf(q))[e] = r;
     }
   }
   bar.sync(true, false);  // results have landed everywhere; nobody reads this rank's input any more
