@@ -232,16 +232,12 @@ tpGemmFp8KernelV2(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const bool must = ctl.loadKc <= kc;   // the block the epilogue waits for next has to be on its way
       if (!tryLoad(must)) break;
     }
-    // MMAs: block kc must be issued now; block kc+1 is issued early when its accumulator and stage are ready
+    // MMAs: block kc must be issued now, and block kc+1 right behind it so that the tensor cores work
+    // on it while block kc is being accumulated. Its accumulator is free once every warp has finished
+    // block kc-1, which they do within a few hundred cycles of this warp: a (bounded) wait, not a test.
     while (ctl.mmaKc < totalKc && ctl.mmaKc <= kc + 1 && !*abortFlag) {
-      const bool must = ctl.mmaKc <= kc;
-      if (ctl.loadKc <= ctl.mmaKc) { if (!tryLoad(must)) break; }
-      bool done = tryMma(must);
-      if (!done && !must) {
-        // the other warps finish their part of the previous block within a few hundred cycles: look again briefly
-        for (int spin = 0; spin < 64 && !done; ++spin) done = tryMma(false);
-      }
-      if (!done) break;
+      if (ctl.loadKc <= ctl.mmaKc) { if (!tryLoad(true)) break; }
+      if (!tryMma(true)) break;
     }
     while (ctl.loadKc < totalKc && ctl.loadKc < ctl.mmaKc + STAGES && !*abortFlag) {
       if (!tryLoad(false)) break;
