@@ -12,7 +12,6 @@
 using namespace b200;
 
 namespace b200 {
-B200_PARAM(TpFp8Kernel, "B200_TP_FP8_KERNEL", 2, "Block-scaled fp8 GEMM kernel: 2 = 8-warp CTA with the pipeline control inside an epilogue warp, 1 = 10-warp CTA with producer and MMA warps")
 B200_PARAM(TpCommCtas, "B200_TP_COMM_CTAS", 12, "CTAs that gather remote rows in all-gather -> GEMM")
 }
 
@@ -100,24 +99,21 @@ static ncclResult_t launchGemm(ncclTpContext* tp, const void* A, const void* W, 
 }
 
 static ncclResult_t launchGemmFp8(ncclTpContext* tp, const void* A, const void* W, TpGemmArgs* a, int grid, cudaStream_t stream) {
-  const bool v2 = paramTpFp8Kernel() != 1;
-  const void* fn = v2 ? tpGemmFp8V2KernelFn() : tpGemmFp8KernelFn();
-  const size_t smem = v2 ? tpGemmFp8V2SmemBytes() : tpGemmFp8SmemBytes();
-  static bool attrSet[2] = {false, false};
-  if (!attrSet[v2]) {
-    CUDACHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attrSet[v2] = true;
+  static bool attrSet = false;
+  if (!attrSet) {
+    CUDACHECK(cudaFuncSetAttribute(tpGemmFp8KernelFn(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tpGemmFp8SmemBytes()));
+    attrSet = true;
   }
   CUtensorMap tmA, tmB;
   NCCLCHECK(makeMap(&tmA, A, a->M, a->K, 128, 1));
   NCCLCHECK(makeMap(&tmB, W, a->N, a->K, 256, 1));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(v2 ? tpGemmFp8V2Threads() : tpGemmFp8Threads());
-  cfg.dynamicSmemBytes = smem;
+  cfg.blockDim = dim3(tpGemmFp8Threads());
+  cfg.dynamicSmemBytes = tpGemmFp8SmemBytes();
   cfg.stream = stream;
   void* args[3] = {&tmA, &tmB, a};
-  cudaError_t e = cudaLaunchKernelExC(&cfg, fn, args);
+  cudaError_t e = cudaLaunchKernelExC(&cfg, tpGemmFp8KernelFn(), args);
   if (e != cudaSuccess) { WARN("fp8 tensor-parallel GEMM launch failed: %s", cudaGetErrorString(e)); (void)cudaGetLastError(); return ncclUnhandledCudaError; }
   if (tp->comm->devPlane) tp->comm->devPlane->launches++;
   return ncclSuccess;

@@ -60,9 +60,6 @@ const void* tpGemmFp8KernelFn();
 const void* tpQuantRowsKernelFn();     // (const bf16* x, uint8_t* q, float* scales, int rows, int K): 1 x 128 blocks, scales [K/128][rows]
 const void* tpQuantBlocksKernelFn();   // same arguments: 128 x 128 blocks, scales [K/128][rows/128]
 size_t tpGemmFp8SmemBytes();
-const void* tpGemmFp8V2KernelFn();     // 8-warp variant (control thread inside an epilogue warp), same arguments
-size_t tpGemmFp8V2SmemBytes();
-int tpGemmFp8V2Threads();
 int tpGemmFp8Threads();
 const void* tpReduceKernelFn();        // (const bf16* staged, bf16* out, size_t count, int nSources): out = sum over sources, fp32 accumulation
 size_t tpGemmSmemBytes();

@@ -56,36 +56,6 @@ def test_fp8_gemm_single_gpu(M, N, K):
     comm.destroy()
 
 
-def _single(rank, nranks, uid, M, N, K):
-    import torch
-    torch.cuda.set_device(0)
-    from nccl_b200 import Communicator
-    from nccl_b200.ops.tp import TensorParallel
-    comm = Communicator(1, 0, uid)
-    tp = TensorParallel(comm, 4096, 4096)
-    g = torch.Generator(device="cuda").manual_seed(1)
-    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
-    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).bfloat16()
-    xq, xs = tp.quantize_fp8(x, 1)
-    wq, ws = tp.quantize_fp8(w, 128)
-    y = tp.gemm_fp8(xq, xs, wq, ws)
-    torch.cuda.synchronize()
-    ref = _dequant(xq, xs, 1) @ _dequant(wq, ws, 128).t()
-    err = (y.float() - ref).abs().max().item() / ref.abs().max().item()
-    assert comm.async_error() == 0
-    tp.destroy()
-    comm.destroy()
-    return err
-
-
-@pytest.mark.parametrize("kernel", ["1", "2"])
-def test_fp8_gemm_both_kernels(kernel):
-    """The 10-warp and the 8-warp kernel are selected with NCCL_B200_TP_FP8_KERNEL."""
-    _needs_sm100()
-    res = run_ranks(_single, 1, args=(1024, 1024, 2048), env={"NCCL_B200_TP_FP8_KERNEL": kernel}, timeout=200)
-    assert res[0] < 1.5e-2, res[0]
-
-
 def _rank(rank, nranks, uid, M, N, K):
     import torch
     torch.cuda.set_device(rank)
