@@ -26,6 +26,7 @@ B200_PARAM(CopyThreads, "B200_COPY_THREADS", 512, "Threads per CTA of the local 
 B200_PARAM(CopyUnroll, "B200_COPY_UNROLL", 4, "16-byte loads in flight per thread of the local copy kernel (4 or 8)")
 B200_PARAM(CopyCtasPerSm, "B200_COPY_CTAS_PER_SM", 16, "Grid size of the local copy kernel in CTAs per SM")
 B200_PARAM(LLMulticast, "B200_LL_MC_MIN_RANKS", 0, "Flagged-line all-reduce / all-gather publish each line with one multimem.st instead of one store per peer from this many ranks on (0 = never)")
+B200_PARAM(CopyKernel, "B200_COPY_KERNEL", 0, "One-rank copy path: 0 = vector loads and stores, 1 = bulk-copy engines through shared memory (messages of 1 MiB and more)")
 B200_PARAM(LaunchPdl, "B200_PDL", 0, "Launch collectives with programmatic stream serialisation")
 
 // ------------------------------------------------------------------------------------ tuning
@@ -630,6 +631,15 @@ static ncclResult_t runOneRank(ncclComm* comm, const Task& t) {
   }
   if (src != dst) {
     ScaleArgs ca{src, dst, bytes, 0, nullptr};
+    if (paramCopyKernel() == 1 && bytes >= (1u << 20) && (((uintptr_t)src | (uintptr_t)dst) & 15) == 0) {
+      static bool attrSet = false;
+      if (!attrSet) {
+        CUDACHECK(cudaFuncSetAttribute(localBulkCopyKernelFn(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)localBulkCopySmemBytes()));
+        attrSet = true;
+      }
+      comm->devPlane->launches++;
+      return launchKernel(localBulkCopyKernelFn(), dim3(comm->devPlane->smCount), dim3(32), localBulkCopySmemBytes(), &ca, t.stream, false);
+    }
     const int threads = (int)paramCopyThreads(), unroll = (int)paramCopyUnroll();
     size_t perCta = (size_t)threads * unroll * 16;
     int ctas = (int)std::min<size_t>((bytes + perCta - 1) / perCta, (size_t)comm->devPlane->smCount * paramCopyCtasPerSm());

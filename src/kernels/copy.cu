@@ -11,6 +11,7 @@
 // Reference parity: src/device/symmetric/all_gather.cuh:13-303 (ST / STMC), src/device/sendrecv.h,
 // contrib/custom_algos/alltoall/lsa_simple_alltoall_kernel.cuh, src/device/onerank.cu, src/rma/rma_ce.cc.
 #include "common.cuh"
+#include "../tp/gemm_sm100.cuh"
 #include "launch.h"
 #include "../comm/comm.h"
 
@@ -298,6 +299,36 @@ __global__ void __launch_bounds__(512) localCopyKernel(ScaleArgs a) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < bytes; i += stride) dst[i] = src[i];
   }
 }
+// The same copy driven by the bulk-copy engines of each SM: one thread per CTA moves its contiguous
+// share through a ring of shared-memory stages (cp.async.bulk global -> shared -> global), several
+// 32 KiB chunks in flight per SM. Needs 16-byte aligned pointers; bytes past the last multiple of 16
+// are copied by thread 0 of CTA 0.
+constexpr int kBulkStages = 6;
+constexpr uint32_t kBulkChunk = 32768;
+__global__ void __launch_bounds__(32) localBulkCopyKernel(ScaleArgs a) {
+  extern __shared__ uint8_t bulkSmemRaw[];
+  uint8_t* sm = (uint8_t*)(((uintptr_t)bulkSmemRaw + 127) & ~(uintptr_t)127);
+  uint64_t* bars = (uint64_t*)(sm + (size_t)kBulkStages * kBulkChunk);
+  const size_t bytes16 = a.count & ~(size_t)15;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kBulkStages; ++s) sm100::mbarInit(sm100::smemAddr(&bars[s]), 1);
+    sm100::mbarInitFence();
+    // contiguous share per CTA, in whole chunks
+    const size_t chunks = (bytes16 + kBulkChunk - 1) / kBulkChunk;
+    const size_t per = (chunks + gridDim.x - 1) / gridDim.x;
+    const size_t lo = (size_t)blockIdx.x * per * kBulkChunk;
+    if (lo < bytes16) {
+      const size_t n = bytes16 - lo < per * kBulkChunk ? bytes16 - lo : per * kBulkChunk;
+      uint32_t phaseBits = 0;
+      sm100::bulkPipe<kBulkStages, kBulkChunk>((char*)a.dst + lo, (const char*)a.src + lo, n, sm100::smemAddr(sm), bars, phaseBits);
+    }
+    if (blockIdx.x == 0)
+      for (size_t j = bytes16; j < a.count; ++j) ((char*)a.dst)[j] = ((const char*)a.src)[j];
+  }
+}
+const void* localBulkCopyKernelFn() { return (const void*)localBulkCopyKernel; }
+size_t localBulkCopySmemBytes() { return 128 + (size_t)kBulkStages * kBulkChunk + kBulkStages * 8; }
+
 const void* localCopyKernelFn(int unroll) { return unroll >= 8 ? (const void*)localCopyKernel<8> : (const void*)localCopyKernel<4>; }
 
 // ------------------------------------------------------------------------- signals

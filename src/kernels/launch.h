@@ -32,6 +32,8 @@ const void* copyKernelFn();
 const void* p2pKernelFn();
 const void* scaleKernelFn(ncclDataType_t type);
 const void* localCopyKernelFn(int unroll);   // takes ScaleArgs{src, dst, count = bytes}; unroll 4 or 8
+const void* localBulkCopyKernelFn();         // same arguments: one thread per CTA drives cp.async.bulk copies through shared memory
+size_t localBulkCopySmemBytes();
 const void* signalKernelFn();
 const void* waitSignalKernelFn();
 
