@@ -773,6 +773,7 @@ ncclResult_t devPlaneRunP2pGroup(ncclComm* comm, const std::vector<Task>& tasks)
     a.opBase[comm->rank] = 0;
     int cta = 0;
     int perOpCap = std::max(1, std::min(dp->tune.sendrecvCtas, (int)(std::min(kMaxCtas, dp->smCount) / (int)nOps)));
+    uint32_t posted[2][kMaxRanks] = {};   // chunks of earlier ops of this launch per direction and peer
     for (size_t i = 0; i < nOps; ++i) {
       const Task& t = *remote[first + i];
       P2pOp& o = a.ops[i];
@@ -784,6 +785,8 @@ ncclResult_t devPlaneRunP2pGroup(ncclComm* comm, const std::vector<Task>& tasks)
       o.ctaCount = (int)std::max<size_t>(1, std::min<size_t>(chunks, (size_t)perOpCap));
       o.ctaBegin = cta;
       cta += o.ctaCount;
+      o.seqOffset = posted[o.isSend ? 0 : 1][o.peer];
+      posted[o.isSend ? 0 : 1][o.peer] += (uint32_t)chunks;
     }
     dp->launches++;
     res = launchKernel(p2pKernelFn(), dim3(cta), dim3(kCtaThreads), 0, &a, stream, false);

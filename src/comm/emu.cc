@@ -183,11 +183,14 @@ int b200EmuP2p(void* ctx, int nOps, const int* opRank, const int* peer, const in
   }
   int maxCtas = 1;
   std::vector<int> nextCta(n, 0);
+  std::vector<uint32_t> posted((size_t)n * 2 * kMaxRanks, 0);   // [rank][direction][peer] chunks so far
   for (int i = 0; i < nOps; ++i) {
     int r = opRank[i];
     if (a.opBase[r] < 0) a.opBase[r] = i;
     a.nOps[r]++;
-    a.ops[i] = P2pOp{peer[i], isSend[i], buf[i], bytes[i], nextCta[r], ctasPerOp};
+    uint32_t& before = posted[((size_t)r * 2 + (isSend[i] ? 0 : 1)) * kMaxRanks + peer[i]];
+    a.ops[i] = P2pOp{peer[i], isSend[i], buf[i], bytes[i], nextCta[r], ctasPerOp, before};
+    before += (uint32_t)((bytes[i] + kP2pChunkBytes - 1) / kP2pChunkBytes);
     nextCta[r] += ctasPerOp;
     maxCtas = std::max(maxCtas, nextCta[r]);
   }

@@ -40,7 +40,6 @@ static ncclResult_t runTask(ncclComm* comm, const Task& t) {
        comm->nRanks, (void*)t.stream);
   if (comm->hostOnly) {
     if (comm->nRanks == 1) {
-      Task one = t;
       // single host rank: copy (and scale for pre-multiplied sums) in place
       size_t bytes = t.count * typeSize(t.type);
       if (t.func == FUNC_ALLGATHER || t.func == FUNC_GATHER || t.func == FUNC_ALLTOALL || t.func == FUNC_SCATTER ||

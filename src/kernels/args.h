@@ -99,6 +99,7 @@ struct P2pOp {
   void* buf;             // rank-private user buffer
   size_t bytes;
   int ctaBegin, ctaCount;   // CTAs [ctaBegin, ctaBegin+ctaCount) of the grid serve this op
+  uint32_t seqOffset;       // mailbox chunks of earlier ops of this launch with the same peer and direction
 };
 constexpr int kMaxP2pOps = 32;
 

@@ -179,7 +179,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) p2pKernel(const __grid_constan
     const P2pOp op = ops[mine];
     const int local = blockIdx.x - op.ctaBegin;
     const size_t nChunks = (op.bytes + kP2pChunkBytes - 1) / kP2pChunkBytes;
-    const uint32_t base = op.isSend ? seq[op.peer] : seq[kMaxRanks + op.peer];
+    const uint32_t base = (op.isSend ? seq[op.peer] : seq[kMaxRanks + op.peer]) + op.seqOffset;
     bool ok = true;
     for (size_t c = local; c < nChunks && ok; c += op.ctaCount) {
       const uint32_t q = base + (uint32_t)c;

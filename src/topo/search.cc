@@ -176,15 +176,10 @@ ncclResult_t buildRing(int nRanks, const std::vector<int>& order, std::vector<in
   return ncclSuccess;
 }
 
-// In-order binary tree: the lowest set bit of (rank) decides the level. Rank 0 is the root; the
-// tree over ranks 1..n-1 hangs below it.
-//        0---------------8
-//                 ______/ \______
-//                4               12
-//              /   \            /  \
-//            2       6       10     \
-//           / \     / \     /  \     \
-//          1   3   5   7   9   11    13
+// In-order binary tree: the lowest set bit of a rank decides its level (odd ranks are leaves, ranks
+// with lowest bit 2 sit one level up, and so on). Rank 0 is the root and has a single child, the
+// largest power of two below nRanks; a rank whose computed parent or child falls outside
+// [0, nRanks) is re-attached to the nearest existing rank on the same side.
 void getBtree(int nRanks, int rank, int* u, int* d0, int* d1, int* parentChildType) {
   int up, down0, down1;
   int bit;

@@ -22,7 +22,7 @@ static const float kNetLat[MODEL_PROTOS] = {5.0f, 8.5f, 14.0f};
 void topoTuneModel(const TopoSystem* sys, const TopoGraph* ring, const TopoGraph* tree, const TopoGraph* nvls, int nRanks, int nNodes,
                    int compCap, TuneModel* m) {
   (void)sys;
-  memset(m, 0, sizeof(*m));
+  *m = TuneModel();
   m->nRanks = nRanks;
   m->nNodes = nNodes;
   if (nRanks <= 1) return;

@@ -270,6 +270,38 @@ def test_send_recv_ring(emu_lib, n, nbytes):
         emu_lib.b200EmuDestroy(ctx)
 
 
+def test_send_recv_several_per_peer(emu_lib):
+    """Several sends to the same peer in one group arrive in posting order (sizes of less than one,
+    exactly one and several mailbox chunks), and the next group continues the sequence."""
+    n = 2
+    ctx = emu_lib.b200EmuCreate(n, 5000)
+    try:
+        g = torch.Generator().manual_seed(7)
+        sizes_each = [100, 1 << 20, (3 << 20) + 5, 16, 2 << 20]
+        for rep in range(2):
+            send = [[torch.randint(0, 256, (s,), generator=g, dtype=torch.uint8).cuda() for s in sizes_each] for _ in range(n)]
+            recv = [[torch.zeros(s, dtype=torch.uint8, device="cuda") for s in sizes_each] for _ in range(n)]
+            ranks, peers, sends, bufs, sizes = [], [], [], [], []
+            for r in range(n):
+                for i, s in enumerate(sizes_each):
+                    ranks += [r, r]
+                    peers += [1 - r, 1 - r]
+                    sends += [1, 0]
+                    bufs += [send[r][i], recv[r][i]]
+                    sizes += [s, s]
+            k = len(ranks)
+            rc = emu_lib.b200EmuP2p(ctx, k, (ctypes.c_int * k)(*ranks), (ctypes.c_int * k)(*peers), (ctypes.c_int * k)(*sends),
+                                    _ptrs(bufs), (ctypes.c_size_t * k)(*sizes), 1)
+            assert rc == 0
+            st = (ctypes.c_uint * 4)()
+            assert emu_lib.b200EmuStatus(ctx, 0, st) == 0 and st[0] == 0
+            for r in range(n):
+                for i in range(len(sizes_each)):
+                    assert torch.equal(recv[r][i], send[1 - r][i]), "rank %d op %d rep %d" % (r, i, rep)
+    finally:
+        emu_lib.b200EmuDestroy(ctx)
+
+
 def test_wait_runs_out_and_reports(emu_lib):
     """A receive whose sender never posts: the wait gives up after its budget, the kernel returns
     and the status words say what it was waiting for. Nothing faults and the context stays usable."""
