@@ -1,5 +1,5 @@
 # Builds the library and its command-line tools for sm_100a.
-#   make -j8            -> nccl_b200/lib/libnccl_b200.so + bin/ncclparam + bin/ncclras + plugins
+#   make -j8            -> nccl_b200/lib/libnccl_b200.so + bin/ncclparam + bin/ncclras + plugins + bin/examples/*
 #   make SAN=address    -> host code instrumented (CPU-only tests)
 CUDA_HOME ?= /usr/local/cuda
 NVCC      ?= $(CUDA_HOME)/bin/nvcc
@@ -30,7 +30,9 @@ TOOLS := $(patsubst tools/%.cc,$(BINDIR)/%,$(wildcard tools/*.cc))
 PLUGIN_SRCS := $(wildcard plugins/*/*.cc)
 PLUGINS := $(patsubst plugins/%.cc,$(LIBDIR)/plugins/%.so,$(PLUGIN_SRCS))
 
-all: $(LIB) $(TOOLS) plugins
+EXAMPLES := $(patsubst examples/%.cu,$(BINDIR)/examples/%,$(wildcard examples/*.cu))
+
+all: $(LIB) $(TOOLS) plugins examples
 
 $(BUILD)/%.o: %.cc $(wildcard include/*.h src/*/*.h)
 	@mkdir -p $(dir $@)
@@ -48,6 +50,11 @@ $(BINDIR)/%: tools/%.cc $(LIB)
 	@mkdir -p $(BINDIR)
 	$(CXX) $(CXXFLAGS) $< -o $@ -L$(LIBDIR) -lnccl_b200 -Wl,-rpath,'$$ORIGIN/../lib' -ldl $(LDSAN)
 
+examples: $(EXAMPLES)
+$(BINDIR)/examples/%: examples/%.cu examples/common.h $(LIB) $(wildcard include/*.h include/nccl_device/*.h)
+	@mkdir -p $(dir $@)
+	$(NVCC) -std=c++17 -O2 -lineinfo $(GENCODE) -Iinclude $< -o $@ -L$(LIBDIR) -lnccl_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../../lib' -Xcompiler -pthread
+
 plugins: $(PLUGINS)
 $(LIBDIR)/plugins/%.so: plugins/%.cc $(wildcard include/*.h include/plugin/*.h)
 	@mkdir -p $(dir $@)
@@ -56,4 +63,4 @@ $(LIBDIR)/plugins/%.so: plugins/%.cc $(wildcard include/*.h include/plugin/*.h)
 clean:
 	rm -rf $(BUILD) $(LIBDIR) $(BINDIR)
 
-.PHONY: all clean plugins
+.PHONY: all clean plugins examples

@@ -188,6 +188,9 @@ NCCL_API_DECL(ncclResult_t, ncclCommGrow, ncclComm_t comm, int nRanks, const ncc
               ncclComm_t* newcomm, ncclConfig_t* config);
 NCCL_API_DECL(const char*, ncclGetErrorString, ncclResult_t result);
 NCCL_API_DECL(const char*, ncclGetLastError, ncclComm_t comm);
+/* Reads the logging environment variables again (kept for source compatibility; deprecated upstream). */
+void ncclResetDebugInit(void);
+void pncclResetDebugInit(void);
 NCCL_API_DECL(ncclResult_t, ncclCommGetAsyncError, ncclComm_t comm, ncclResult_t* asyncError);
 NCCL_API_DECL(ncclResult_t, ncclCommCount, const ncclComm_t comm, int* count);
 NCCL_API_DECL(ncclResult_t, ncclCommCuDevice, const ncclComm_t comm, int* device);

@@ -83,6 +83,15 @@ int debugLevel() {
   return gLevel;
 }
 
+// Reads NCCL_DEBUG, NCCL_DEBUG_SUBSYS, NCCL_DEBUG_FILE and NCCL_DEBUG_TIMESTAMP_LEVELS again.
+void debugReload() {
+  std::call_once(gOnce, [] {});   // a later first use must not undo this reload
+  std::lock_guard<std::mutex> g(gLock);
+  if (gFile && gFile != stdout) fclose(gFile);
+  gMask = SUB_INIT | SUB_BOOTSTRAP | SUB_ENV;
+  initOnce();
+}
+
 const char* lastErrorString() { return gLastError; }
 
 void setThreadName(const char* fmt, ...) {
@@ -129,3 +138,7 @@ void debugLog(LogLevel level, uint64_t subsys, const char* file, int line, const
 }
 
 }  // namespace b200
+
+// Deprecated entry point of the reference's header (src/nccl.h.in:277): reload the logging settings.
+extern "C" __attribute__((visibility("default"))) void ncclResetDebugInit() { b200::debugReload(); }
+extern "C" __attribute__((visibility("default"))) void pncclResetDebugInit() { b200::debugReload(); }
