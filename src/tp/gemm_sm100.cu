@@ -25,16 +25,13 @@
 // drains its outstanding TMA copies, frees its tensor memory and returns.
 // The reference has no GEMM kernels; the comparison point is its reduce-scatter / all-gather plus a
 // separate GEMM.
-#include "gemm_sm100.cuh"
-
-#include "../kernels/common.cuh"
-#include "tp.h"
+#include "gemm_roles.cuh"
 
 namespace b200 {
 
 using namespace sm100;
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int BM = kTpBM, BN = kTpBN, BK = kTpBK, STAGES = 4, UMMA_K = 16;
 constexpr int kTpThreads = 192;
 constexpr uint32_t kStageABytes = BM * BK * 2, kStageBBytes = BN * BK * 2;
 constexpr uint32_t kStageBytes = kStageABytes + kStageBBytes;
@@ -69,49 +66,9 @@ tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 
   if (commCta) {
     // ---- all-gather role: pull the other ranks' row blocks in consumption order
-    const int blocksPerRank = a.M / n / BM;
-    const size_t blockBytes = (size_t)BM * a.K * 2;
-    const int commIdx = blockIdx.x - a.gemmCtas, commN = gridDim.x - a.gemmCtas;
-    constexpr int kPipeStages = 6;
-    constexpr uint32_t kPipeChunk = 32768;
-    static_assert((size_t)kPipeStages * kPipeChunk <= (size_t)STAGES * kStageBytes, "copy ring must fit the operand ring");
-    uint64_t* pipeBars = fullBar;   // the first kPipeStages of the 2 * STAGES operand barriers (unused by a comm CTA)
-    static_assert(kPipeStages <= 2 * STAGES, "not enough barriers");
-    if (threadIdx.x == 0) {
-      for (int s = 0; s < kPipeStages; ++s) mbarInit(smemAddr(&pipeBars[s]), 1);
-      mbarInitFence();
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      // one thread drives bulk copies peer -> shared memory -> local rows; the copy engines of this SM do the work
-      uint32_t phaseBits = 0;
-      // remote blocks in the order the GEMM consumes them (rank+1 first), dealt round-robin to the comm CTAs
-      for (int idx = commIdx; idx < (n - 1) * blocksPerRank && ok; idx += commN) {
-        const int src = (rank + 1 + idx / blocksPerRank) % n;
-        {
-          const int b = idx % blocksPerRank;
-          const int mb = src * blocksPerRank + b;
-          const char* from = (const char*)a.peerA[src] + (size_t)mb * blockBytes;
-          char* to = (char*)a.peerA[rank] + (size_t)mb * blockBytes;
-          ok = bulkPipe<kPipeStages, kPipeChunk>(to, from, blockBytes, smemAddr(smem), pipeBars, phaseBits);
-          if (!ok) {
-            if (a.sync.status[rank] && ldRelaxedSys(a.sync.status[rank]) == DEV_OK) {
-              a.sync.status[rank][1] = WAIT_TILE;
-              a.sync.status[rank][2] = 5000 + mb;
-              a.sync.status[rank][3] = blockIdx.x;
-              __threadfence_system();
-              stRelaxedSys(a.sync.status[rank], DEV_TIMEOUT);
-            }
-            break;
-          }
-          // the rows were written through the async proxy and will be read by TMA loads of other CTAs
-          fenceProxyAsync();
-          __threadfence();
-          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.blockFlags + mb), "r"(a.flagEpoch) : "memory");
-        }
-      }
-    }
-    __syncthreads();
+    static_assert(kTpPipeBytes <= (size_t)STAGES * kStageBytes, "copy ring must fit the operand ring");
+    static_assert(kTpPipeStages <= 2 * STAGES, "not enough barriers");   // the operand barriers are unused by a comm CTA
+    tpCommRole(a, blockIdx.x - a.gemmCtas, gridDim.x - a.gemmCtas, smem, fullBar, ok);
     bar.sync(true, false);   // nobody reads my rows any more
     bar.finish();
     return;
@@ -142,13 +99,7 @@ tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   const uint32_t smemA0 = smemAddr(smem), smemB0 = smemA0 + STAGES * kStageABytes;
   auto fail = [&](uint32_t kind, uint32_t what) {
     *abortFlag = 1;
-    if (a.sync.status[rank] && ldRelaxedSys(a.sync.status[rank]) == DEV_OK) {
-      a.sync.status[rank][1] = kind;
-      a.sync.status[rank][2] = what;
-      a.sync.status[rank][3] = blockIdx.x;
-      __threadfence_system();
-      stRelaxedSys(a.sync.status[rank], DEV_TIMEOUT);
-    }
+    tpReportTimeout(a, kind, what);
   };
 
   if (warp == 0) {
@@ -160,16 +111,7 @@ tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         const TileCoord tc = tileOf(a, t);
         if (a.mode == TP_MODE_GATHER && n > 1 && tc.owner != rank) {
           // wait until the comm CTAs have landed this block of rows
-          const uint32_t* f = a.blockFlags + tc.mBlk;
-          bool got = false;
-          for (uint32_t spin = 0; spin < (1u << 26); ++spin) {
-            uint32_t v;
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-            if ((int32_t)(v - a.flagEpoch) >= 0) { got = true; break; }
-            if (*abortFlag) break;
-          }
-          if (!got) { fail(WAIT_TILE, (uint32_t)tc.mBlk); break; }
-          fenceProxyAsync();
+          if (!tpWaitBlock(a, tc.mBlk, abortFlag)) { fail(WAIT_TILE, (uint32_t)tc.mBlk); break; }
         }
         for (int kb = 0; kb < kBlocks; ++kb, ++kc) {
           const int s = kc % STAGES;
@@ -227,49 +169,7 @@ tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       tcFenceAfter();
       const int row0 = tc.mBlk * BM + q * 32;   // first of this warp's 32 rows
       const uint32_t tBase = tmemBase + ((uint32_t)(q * 32) << 16) + buf * BN;
-      // STORE / GATHER: C; REDUCE: slot `rank` of the owner's staging buffer (over NVLink when the owner is a peer)
-      __nv_bfloat16* dstBase;
-      size_t ld;
-      if (a.mode == TP_MODE_REDUCE && n > 1) {
-        const int rowsPerRank = a.M / n;
-        dstBase = (__nv_bfloat16*)a.partial[tc.owner] + ((size_t)rank * rowsPerRank + (row0 - tc.owner * rowsPerRank)) * a.N + (size_t)tc.nBlk * BN;
-        ld = (size_t)a.N;
-      } else {
-        dstBase = (__nv_bfloat16*)a.C + (size_t)row0 * a.ldc + (size_t)tc.nBlk * BN;
-        ld = (size_t)a.ldc;
-      }
-      // Each lane owns one row of the accumulator, so storing straight from registers would write 16
-      // scattered bytes per lane and instruction. The warp instead transposes 64 columns at a time
-      // through 4 KiB of shared memory (16-byte chunks XOR-swizzled by row against bank conflicts) and
-      // writes 128 contiguous bytes per row, four rows per instruction: whole lines for HBM and NVLink.
-      uint8_t* wbuf = epiBuf + (size_t)(warp - 2) * 4096;
-      for (int cc = 0; cc < BN / 64; ++cc) {
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t r[32];
-          tmemLd32(tBase + (cc * 2 + half) * 32, r);
-          tmemLdWait();
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 o;
-            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[8 * v]), __uint_as_float(r[8 * v + 1]));
-            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-            o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1; o.z = *(uint32_t*)&p2; o.w = *(uint32_t*)&p3;
-            const int j = half * 4 + v;   // 16-byte chunk of the 128-byte row segment
-            *(uint4*)(wbuf + lane * 128 + ((j ^ (lane & 7)) * 16)) = o;
-          }
-        }
-        __syncwarp();
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const int rr = k * 4 + (lane >> 3), j = lane & 7;
-          const uint4 o = *(const uint4*)(wbuf + rr * 128 + ((j ^ (rr & 7)) * 16));
-          *(uint4*)((char*)(dstBase + (size_t)rr * ld) + cc * 128 + j * 16) = o;
-        }
-        __syncwarp();
-      }
+      tpStoreAccum(a, tBase, row0, tc.nBlk, tc.owner, epiBuf + (size_t)(warp - 2) * 4096, lane);
       tcFenceBefore();
       __syncwarp();
       if (lane == 0) mbarArrive(smemAddr(&accEmpty[buf]));

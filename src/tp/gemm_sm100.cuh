@@ -99,6 +99,37 @@ __device__ __forceinline__ bool bulkPipe(char* to, const char* from, size_t byte
   return ok;
 }
 
+// ---------------------------------------------------------------- CTA pairs (cluster of two, cta_group::2)
+__device__ __forceinline__ uint32_t clusterCtaRank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// All threads of every CTA of the cluster meet; shared-memory writes before it are visible after it.
+__device__ __forceinline__ void clusterSync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of this CTA's shared-memory location `addr` as seen in CTA `ctaRank` of the cluster.
+__device__ __forceinline__ uint32_t mapaShared(uint32_t addr, uint32_t ctaRank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(ctaRank));
+  return r;
+}
+__device__ __forceinline__ void mbarArriveCluster(uint32_t clusterAddr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterAddr) : "memory");
+}
+__device__ __forceinline__ void stSharedCluster(uint32_t clusterAddr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(clusterAddr), "r"(v) : "memory");
+}
+// Tile load into this CTA's shared memory whose completion bytes are counted on an mbarrier of
+// either CTA of the pair (cluster address). No multicast.
+__device__ __forceinline__ void tmaLoad2dPair(uint32_t dstSmem, const CUtensorMap* map, int c0, int c1, uint32_t barCluster) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dstSmem), "l"(map), "r"(c0), "r"(c1), "r"(barCluster) : "memory");
+}
+
 __device__ __forceinline__ void prefetchTensorMap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -112,6 +143,14 @@ __device__ __forceinline__ void tmemAlloc(uint32_t dstSmem, uint32_t cols) {
 __device__ __forceinline__ void tmemRelinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmemDealloc(uint32_t taddr, uint32_t cols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// Pair allocation: one warp in EACH CTA of the pair issues these collectively.
+__device__ __forceinline__ void tmemAllocPair(uint32_t dstSmem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dstSmem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmemRelinquishPair() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmemDeallocPair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
 __device__ __forceinline__ void tcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -155,6 +194,21 @@ __device__ __forceinline__ void ummaF8(uint32_t dTmem, uint64_t aDesc, uint64_t 
 // Arrives on `bar` once every tcgen05.mma issued so far by this thread has completed.
 __device__ __forceinline__ void ummaCommit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// CTA pair: one thread of the leader CTA issues a 256 x N x 16 MMA over both CTAs' shared memory (each
+// holds 128 rows of A and N/2 rows of B at the same offsets) into both CTAs' tensor memory.
+__device__ __forceinline__ void ummaBf16Pair(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives on the mbarrier at the same shared-memory offset in every CTA of `ctaMask` once the MMAs
+// issued so far have completed (this multicast is an mbarrier signal, not a load).
+__device__ __forceinline__ void ummaCommitPair(uint32_t bar, uint16_t ctaMask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(ctaMask) : "memory");
 }
 
 // ---------------------------------------------------------------- epilogue loads

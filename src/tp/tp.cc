@@ -13,11 +13,13 @@ using namespace b200;
 
 namespace b200 {
 B200_PARAM(TpCommCtas, "B200_TP_COMM_CTAS", 12, "CTAs that gather remote rows in all-gather -> GEMM")
+B200_PARAM(TpPair, "B200_TP_PAIR", 0, "bf16 GEMM on CTA pairs (256 x 256 tiles, tcgen05 cta_group::2) when the row count allows")
 }
 
 struct ncclTpContext {
   ncclComm* comm = nullptr;
   int smCount = 0;
+  int pairClusters = 0;   // clusters of the CTA-pair GEMM kernel that can be resident at once (0: unavailable)
   void* accum = nullptr;           // symmetric staging window: bf16 [n sources][maxRows / n][maxCols]
   size_t accumBytes = 0;
   SymWindow* accumWin = nullptr;
@@ -77,22 +79,42 @@ static void fillSyncTp(ncclComm* comm, SyncArgs* s) {
   s->timeoutNs = dp ? dp->timeoutNs : 5000000000ull;
 }
 
-static ncclResult_t launchGemm(ncclTpContext* tp, const void* A, const void* W, TpGemmArgs* a, int grid, cudaStream_t stream) {
+// Launches the bf16 GEMM kernel in the mode of `a`. Grid: one CTA per SM (fewer when there are fewer
+// tiles); in all-gather mode the last CTAs are the comm CTAs. The CTA-pair kernel runs when enabled,
+// when its clusters fit and when every rank's rows split into 256-row tiles.
+static ncclResult_t launchGemm(ncclTpContext* tp, const void* A, const void* W, TpGemmArgs* a, cudaStream_t stream) {
   static bool attrSet = false;
   if (!attrSet) {
     CUDACHECK(cudaFuncSetAttribute(tpGemmKernelFn(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tpGemmSmemBytes()));
     attrSet = true;
   }
+  const int n = a->nRanks;
+  const bool fused = n > 1 && a->mode != TP_MODE_STORE;
+  const bool gather = fused && a->mode == TP_MODE_GATHER;
+  const bool pair = paramTpPair() != 0 && tp->pairClusters > 0 && a->M % (256 * (fused ? n : 1)) == 0;
+  int commCtas = gather ? (int)std::max<int64_t>(1, std::min<int64_t>(paramTpCommCtas(), tp->smCount / 4)) : 0;
+  int grid;
+  if (pair) {
+    commCtas = (commCtas + 1) & ~1;   // both CTAs of a cluster have the same role
+    const int tiles = (a->M / 256) * (a->N / 256);
+    const int pairs = std::max(1, std::min(tp->pairClusters - commCtas / 2, tiles));
+    a->gemmCtas = 2 * pairs;
+    grid = 2 * pairs + commCtas;
+  } else {
+    const int tiles = (a->M / 128) * (a->N / 256);
+    grid = gather ? tp->smCount : std::min(tp->smCount, tiles);
+    a->gemmCtas = grid - commCtas;
+  }
   CUtensorMap tmA, tmB;
   NCCLCHECK(makeMap(&tmA, A, a->M, a->K, 128));
-  NCCLCHECK(makeMap(&tmB, W, a->N, a->K, 256));
+  NCCLCHECK(makeMap(&tmB, W, a->N, a->K, pair ? 128 : 256));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(tpGemmThreads());
-  cfg.dynamicSmemBytes = tpGemmSmemBytes();
+  cfg.blockDim = dim3(pair ? tpGemmPairThreads() : tpGemmThreads());
+  cfg.dynamicSmemBytes = pair ? tpGemmPairSmemBytes() : tpGemmSmemBytes();
   cfg.stream = stream;
   void* args[3] = {&tmA, &tmB, a};
-  cudaError_t e = cudaLaunchKernelExC(&cfg, tpGemmKernelFn(), args);
+  cudaError_t e = cudaLaunchKernelExC(&cfg, pair ? tpGemmPairKernelFn() : tpGemmKernelFn(), args);
   if (e != cudaSuccess) { WARN("tensor-parallel GEMM launch failed: %s", cudaGetErrorString(e)); (void)cudaGetLastError(); return ncclUnhandledCudaError; }
   if (tp->comm->devPlane) tp->comm->devPlane->launches++;
   return ncclSuccess;
@@ -248,6 +270,21 @@ ncclResult_t ncclTpCreate(ncclComm_t comm, size_t maxRows, size_t maxCols, ncclT
   CUDACHECK(cudaGetDevice(&cur));
   if (cur != comm->cudaDev) CUDACHECK(cudaSetDevice(comm->cudaDev));
   CUDACHECK(cudaDeviceGetAttribute(&tp->smCount, cudaDevAttrMultiProcessorCount, comm->cudaDev));
+  {
+    // how many clusters of two CTAs of the pair kernel the device can hold at once: the grid never exceeds it,
+    // because its CTAs wait for one another (comm CTAs, cross-GPU barriers)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tp->smCount & ~1);
+    cfg.blockDim = dim3(tpGemmPairThreads());
+    cfg.dynamicSmemBytes = tpGemmPairSmemBytes();
+    int clusters = 0;
+    if (cudaFuncSetAttribute(tpGemmPairKernelFn(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tpGemmPairSmemBytes()) == cudaSuccess &&
+        cudaOccupancyMaxActiveClusters(&clusters, tpGemmPairKernelFn(), &cfg) == cudaSuccess)
+      tp->pairClusters = std::min(clusters, tp->smCount / 2);
+    else
+      (void)cudaGetLastError();
+    INFO(SUB_INIT, "tensor-parallel GEMM: %d SMs, %d resident CTA pairs", tp->smCount, tp->pairClusters);
+  }
   const int n = comm->nRanks;
   tp->accumBytes = n > 1 ? maxRows * maxCols * 2 : 0;   // bf16 staging: one [maxRows / n, maxCols] slot per source rank
   if (tp->accumBytes) {
@@ -313,8 +350,7 @@ ncclResult_t ncclTpGemm(ncclTp_t tp, const void* A, const void* W, void* C, int 
   a.mode = TP_MODE_STORE;
   a.rank = tp->comm->rank; a.nRanks = tp->comm->nRanks;
   fillSyncTp(tp->comm, &a.sync);
-  int tiles = (M / 128) * (N / 256);
-  return launchGemm(tp, A, W, &a, std::min(tp->smCount, tiles), stream);
+  return launchGemm(tp, A, W, &a, stream);
 }
 
 ncclResult_t ncclTpGemmReduceScatter(ncclTp_t tp, const void* A, const void* W, void* out, int M, int N, int K, cudaStream_t stream) {
@@ -333,8 +369,7 @@ ncclResult_t ncclTpGemmReduceScatter(ncclTp_t tp, const void* A, const void* W, 
   a.rank = comm->rank; a.nRanks = n;
   for (int p = 0; p < n; ++p) a.partial[p] = tp->accumWin->host.peerPtr[p];
   fillSyncTp(comm, &a.sync);
-  int tiles = (M / 128) * (N / 256);
-  NCCLCHECK(launchGemm(tp, A, W, &a, std::min(tp->smCount, tiles), stream));
+  NCCLCHECK(launchGemm(tp, A, W, &a, stream));
   // kernel completion implies that every rank's partial tiles have landed in this rank's staging slots
   size_t count = (size_t)(M / n) * N;
   int ctas = (int)std::min<size_t>((count / 8 + 255) / 256, (size_t)tp->smCount * 8);
@@ -364,10 +399,8 @@ ncclResult_t ncclTpAllGatherGemm(ncclTp_t tp, void* gatheredA, const void* W, vo
   for (int p = 0; p < n; ++p) a.peerA[p] = it->second->host.peerPtr[p];
   a.blockFlags = tp->blockFlags;
   a.flagEpoch = ++tp->epoch;
-  int commCtas = (int)std::max<int64_t>(1, std::min<int64_t>(paramTpCommCtas(), tp->smCount / 4));
-  a.gemmCtas = tp->smCount - commCtas;
   fillSyncTp(comm, &a.sync);
-  return launchGemm(tp, gatheredA, W, &a, tp->smCount, stream);
+  return launchGemm(tp, gatheredA, W, &a, stream);
 }
 
 }  // extern "C"

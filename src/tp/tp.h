@@ -34,7 +34,8 @@ struct TileCoord { int mBlk, nBlk, owner; };
 // Tile t of this CTA's walk: row-major over the output for plain GEMMs; owner by owner for the
 // fused modes (REDUCE starts with the next rank so that every step each GPU receives from one
 // peer; GATHER starts with the rows that are already local).
-__device__ __forceinline__ TileCoord tileOf(const TpGemmArgs& a, int t) {
+// `bm` is the tile height in rows (128 for one CTA, 256 for a CTA pair); mBlk counts tiles of that height.
+__device__ __forceinline__ TileCoord tileOf(const TpGemmArgs& a, int t, int bm = kTpBM) {
   const int tilesN = a.N / kTpBN;
   TileCoord c;
   if (a.mode == TP_MODE_STORE || a.nRanks == 1) {
@@ -44,7 +45,7 @@ __device__ __forceinline__ TileCoord tileOf(const TpGemmArgs& a, int t) {
     if (a.mode == TP_MODE_REDUCE) c.owner = 0;
     return c;
   }
-  const int tilesMPerRank = a.M / a.nRanks / kTpBM;
+  const int tilesMPerRank = a.M / a.nRanks / bm;
   const int per = tilesMPerRank * tilesN;
   const int step = t / per, j = t % per;
   const int who = a.mode == TP_MODE_REDUCE ? (a.rank + 1 + step) % a.nRanks : (a.rank + step) % a.nRanks;
@@ -56,6 +57,7 @@ __device__ __forceinline__ TileCoord tileOf(const TpGemmArgs& a, int t) {
 #endif
 
 const void* tpGemmKernelFn();
+const void* tpGemmPairKernelFn();      // CTA-pair variant (cluster of two, 256 x 256 tiles): same arguments, W map with 128-row boxes
 const void* tpGemmFp8KernelFn();
 const void* tpQuantRowsKernelFn();     // (const bf16* x, uint8_t* q, float* scales, int rows, int K): 1 x 128 blocks, scales [K/128][rows]
 const void* tpQuantBlocksKernelFn();   // same arguments: 128 x 128 blocks, scales [K/128][rows/128]
@@ -63,6 +65,8 @@ size_t tpGemmFp8SmemBytes();
 int tpGemmFp8Threads();
 const void* tpReduceKernelFn();        // (const bf16* staged, bf16* out, size_t count, int nSources): out = sum over sources, fp32 accumulation
 size_t tpGemmSmemBytes();
+size_t tpGemmPairSmemBytes();
+int tpGemmPairThreads();
 int tpGemmThreads();
 
 }  // namespace b200
