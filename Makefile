@@ -12,7 +12,7 @@ GENCODE   := -gencode arch=compute_100a,code=sm_100a
 CXXFLAGS  := -std=c++17 -O2 -g -fPIC -Wall -Wno-unused-function -Wno-sign-compare \
              -Iinclude -Isrc -I$(CUDA_HOME)/include -pthread
 NVCCFLAGS := -std=c++17 -O3 -lineinfo $(GENCODE) -Xcompiler -fPIC -Iinclude -Isrc \
-             --expt-relaxed-constexpr -Xptxas -v
+             --expt-relaxed-constexpr -Xptxas -v $(EXTRA_NVCCFLAGS)
 ifdef SAN
 CXXFLAGS  += -fsanitize=$(SAN) -fno-omit-frame-pointer
 LDSAN     := -fsanitize=$(SAN)

@@ -23,6 +23,8 @@
 // No load uses cluster multicast; tensor-map (tiled) TMA loads read local memory only.
 // Every wait (mbarrier, flag, cross-GPU barrier) is bounded; on expiry the kernel records a status,
 // drains its outstanding TMA copies, frees its tensor memory and returns.
+// gemm_pair_sm100.cu is the variant on CTA pairs (256 x 256 tiles, tcgen05 cta_group::2), which the host
+// prefers when every rank's rows split into 256-row tiles; this kernel covers the remaining shapes.
 // The reference has no GEMM kernels; the comparison point is its reduce-scatter / all-gather plus a
 // separate GEMM.
 #include "gemm_roles.cuh"

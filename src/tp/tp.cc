@@ -12,8 +12,8 @@
 using namespace b200;
 
 namespace b200 {
-B200_PARAM(TpCommCtas, "B200_TP_COMM_CTAS", 12, "CTAs that gather remote rows in all-gather -> GEMM")
-B200_PARAM(TpPair, "B200_TP_PAIR", 0, "bf16 GEMM on CTA pairs (256 x 256 tiles, tcgen05 cta_group::2) when the row count allows")
+B200_PARAM(TpCommCtas, "B200_TP_COMM_CTAS", 0, "CTAs that gather remote rows in all-gather -> GEMM (0: 4 for two ranks, 8 up to four, 16 beyond)")
+B200_PARAM(TpPair, "B200_TP_PAIR", 1, "bf16 GEMM on CTA pairs (256 x 256 tiles, tcgen05 cta_group::2) when the row count allows")
 }
 
 struct ncclTpContext {
@@ -45,6 +45,10 @@ static EncodeTiledFn encodeFn() {
 }
 
 // Row-major [rows, K] tensor of bf16 (elemBytes 2) or fp8 (1), tiles of boxRows x 128 bytes with 128-byte swizzle.
+// Comm CTAs of all-gather -> GEMM: each moves about 33 GB/s (128 KiB of loads in flight over NVLink, measured at two
+// ranks); the remote share of the rows and how early the first remote chunk is needed both grow with the number of ranks.
+static int tpCommCtas(const ncclTpContext* tp, int nRanks);
+
 static ncclResult_t makeMap(CUtensorMap* map, const void* base, int rows, int K, int boxRows, int elemBytes = 2) {
   EncodeTiledFn enc = encodeFn();
   if (!enc) { WARN("cuTensorMapEncodeTiled is not available"); return ncclUnhandledCudaError; }
@@ -57,6 +61,12 @@ static ncclResult_t makeMap(CUtensorMap* map, const void* base, int rows, int K,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { WARN("cuTensorMapEncodeTiled failed (%d)", (int)r); return ncclUnhandledCudaError; }
   return ncclSuccess;
+}
+
+static int tpCommCtas(const ncclTpContext* tp, int nRanks) {
+  int64_t want = paramTpCommCtas();
+  if (want <= 0) want = nRanks <= 2 ? 4 : nRanks <= 4 ? 8 : 16;
+  return (int)std::max<int64_t>(1, std::min<int64_t>(want, tp->smCount / 4));
 }
 
 static ncclResult_t checkShape(int M, int N, int K, int n) {
@@ -92,7 +102,7 @@ static ncclResult_t launchGemm(ncclTpContext* tp, const void* A, const void* W, 
   const bool fused = n > 1 && a->mode != TP_MODE_STORE;
   const bool gather = fused && a->mode == TP_MODE_GATHER;
   const bool pair = paramTpPair() != 0 && tp->pairClusters > 0 && a->M % (256 * (fused ? n : 1)) == 0;
-  int commCtas = gather ? (int)std::max<int64_t>(1, std::min<int64_t>(paramTpCommCtas(), tp->smCount / 4)) : 0;
+  int commCtas = gather ? tpCommCtas(tp, n) : 0;
   int grid;
   if (pair) {
     commCtas = (commCtas + 1) & ~1;   // both CTAs of a cluster have the same role
@@ -251,7 +261,7 @@ ncclResult_t ncclTpAllGatherGemmFp8(ncclTp_t tp, void* gatheredA, const void* W,
   a.scaleW = scaleW;
   a.blockFlags = tp->blockFlags;
   a.flagEpoch = ++tp->epoch;
-  int commCtas = (int)std::max<int64_t>(1, std::min<int64_t>(paramTpCommCtas(), tp->smCount / 4));
+  int commCtas = tpCommCtas(tp, n);
   a.gemmCtas = tp->smCount - commCtas;
   fillSyncTp(comm, &a.sync);
   return launchGemmFp8(tp, gatheredA, W, &a, tp->smCount, stream);

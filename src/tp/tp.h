@@ -31,16 +31,29 @@ struct TpGemmArgs {
 #if defined(__CUDACC__)
 constexpr int kTpBM = 128, kTpBN = 256;
 struct TileCoord { int mBlk, nBlk, owner; };
-// Tile t of this CTA's walk: row-major over the output for plain GEMMs; owner by owner for the
-// fused modes (REDUCE starts with the next rank so that every step each GPU receives from one
-// peer; GATHER starts with the rows that are already local).
+// Tile j of a block of `rows` x `tilesN` tiles, visited in panels of kTpPanel tile columns, row by row
+// inside a panel: the tiles in flight at any time (one per CTA or CTA pair) then cover a roughly square
+// region, so every operand tile fetched into L2 is reused by several CTAs before it is evicted, instead
+// of streaming the whole of W once per tile row.
+constexpr int kTpPanel = 8;
+constexpr int kTpChunkRows = 2048;   // rows of one owner walked together in the fused modes
+__device__ __forceinline__ void panelOrder(int j, int rows, int tilesN, int* r, int* c) {
+  const int perPanel = kTpPanel * rows;
+  const int p = j / perPanel;
+  const int width = tilesN - p * kTpPanel < kTpPanel ? tilesN - p * kTpPanel : kTpPanel;
+  const int k = j - p * perPanel;
+  *r = k / width;
+  *c = p * kTpPanel + k % width;
+}
+// Tile t of this CTA's walk: the whole output for plain GEMMs; owner by owner for the fused modes
+// (REDUCE starts with the next rank so that every step each GPU receives from one peer; GATHER
+// starts with the rows that are already local), panel order inside each block of rows.
 // `bm` is the tile height in rows (128 for one CTA, 256 for a CTA pair); mBlk counts tiles of that height.
 __device__ __forceinline__ TileCoord tileOf(const TpGemmArgs& a, int t, int bm = kTpBM) {
   const int tilesN = a.N / kTpBN;
   TileCoord c;
   if (a.mode == TP_MODE_STORE || a.nRanks == 1) {
-    c.mBlk = t / tilesN;
-    c.nBlk = t % tilesN;
+    panelOrder(t, a.M / bm, tilesN, &c.mBlk, &c.nBlk);
     c.owner = a.rank;
     if (a.mode == TP_MODE_REDUCE) c.owner = 0;
     return c;
@@ -49,9 +62,16 @@ __device__ __forceinline__ TileCoord tileOf(const TpGemmArgs& a, int t, int bm =
   const int per = tilesMPerRank * tilesN;
   const int step = t / per, j = t % per;
   const int who = a.mode == TP_MODE_REDUCE ? (a.rank + 1 + step) % a.nRanks : (a.rank + step) % a.nRanks;
+  // an owner's rows are walked in chunks of kTpChunkRows rows, panel order inside a chunk: all-gather -> GEMM then
+  // needs a peer's rows chunk by chunk instead of all of them for the first panel
+  const int chunkTiles = kTpChunkRows / bm;
+  const int chunk = j / (chunkTiles * tilesN);
+  const int rowsHere = tilesMPerRank - chunk * chunkTiles < chunkTiles ? tilesMPerRank - chunk * chunkTiles : chunkTiles;
+  int r;
+  panelOrder(j - chunk * chunkTiles * tilesN, rowsHere, tilesN, &r, &c.nBlk);
+  r += chunk * chunkTiles;
   c.owner = who;
-  c.mBlk = who * tilesMPerRank + j / tilesN;
-  c.nBlk = j % tilesN;
+  c.mBlk = who * tilesMPerRank + r;
   return c;
 }
 #endif

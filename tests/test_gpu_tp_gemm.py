@@ -12,16 +12,12 @@ def _ref(x, w):
     return (x.float() @ w.float().t())
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (1024, 768, 4096), (2048, 3584, 1024)])
-def test_gemm_single_gpu(M, N, K):
-    if not torch.cuda.is_available():
-        pytest.skip("needs a GPU")
-    if torch.cuda.get_device_capability()[0] < 10:
-        pytest.skip("needs sm_100")
-    from nccl_b200 import Communicator, get_unique_id
+def _gemm_rank(rank, nranks, uid, M, N, K):
+    import torch
+    from nccl_b200 import Communicator
     from nccl_b200.ops.tp import TensorParallel
     torch.cuda.set_device(0)
-    comm = Communicator(1, 0, get_unique_id())
+    comm = Communicator(1, 0, uid)
     tp = TensorParallel(comm, 4096, 4096)
     g = torch.Generator(device="cuda").manual_seed(M + N + K)
     x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
@@ -36,6 +32,20 @@ def test_gemm_single_gpu(M, N, K):
     assert comm.async_error() == 0
     tp.destroy()
     comm.destroy()
+    return True
+
+
+# pair = 1: two CTAs per 256 x 256 tile (tcgen05 cta_group::2) where the row count allows; 0: one CTA per 128 x 256 tile
+@pytest.mark.parametrize("pair", [1, 0])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (1024, 768, 4096), (2048, 3584, 1024), (4096, 4096, 512)])
+def test_gemm_single_gpu(M, N, K, pair):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    if torch.cuda.get_device_capability()[0] < 10:
+        pytest.skip("needs sm_100")
+    if pair == 0 and (M, N, K) not in ((256, 512, 256), (2048, 3584, 1024)):
+        pytest.skip("shape covered with the default kernel choice")
+    assert run_ranks(_gemm_rank, 1, args=(M, N, K), env={"NCCL_B200_TP_PAIR": str(pair)}, timeout=200)[0] is True
 
 
 def _tp_rank(rank, nranks, uid, M, N, K):
@@ -75,14 +85,15 @@ def _tp_rank(rank, nranks, uid, M, N, K):
     return out
 
 
+@pytest.mark.parametrize("pair", [1, 0])
 @pytest.mark.parametrize("M,N,K", [(1024, 512, 1024), (2048, 1024, 2048)])
-def test_fused_tp_multi_gpu(M, N, K):
+def test_fused_tp_multi_gpu(M, N, K, pair):
     n = min(torch.cuda.device_count() if torch.cuda.is_available() else 0, 8)
     if n < 2:
         pytest.skip("needs at least two GPUs")
     if torch.cuda.get_device_capability()[0] < 10:
         pytest.skip("needs sm_100")
-    res = run_ranks(_tp_rank, n, args=(M, N, K), timeout=300)
+    res = run_ranks(_tp_rank, n, args=(M, N, K), env={"NCCL_B200_TP_PAIR": str(pair)}, timeout=300)
     gx = torch.Generator().manual_seed(5)
     x_full = torch.randn(M, K, generator=gx).bfloat16()
     w_full = (torch.randn(N, K, generator=gx) * 0.05).bfloat16()
