@@ -4,7 +4,8 @@
     python -m nccl_b200.ops.tp_bench --dtype fp8  --shapes 8192x8192x8192 --iters 20
 
 Shapes are MxNxK with C[M,N] = A[M,K] * W[N,K]^T. Inputs are larger than L2 for the default
-shapes; timing is CUDA events around `iters` launches after 3 warm-ups. Prints one line per shape.
+shapes; timing is CUDA events around at least `iters` launches after a warm-up long enough to reach sustained
+clocks (--warm-ms, --time-ms). Prints one line per shape.
 
 Fused tensor-parallel layers (one process per GPU, torchrun), Llama-3-70B MLP shapes by default:
 
@@ -23,11 +24,42 @@ import sys
 import torch
 
 
+def timed_sustained(fn, a, reduce_max, barrier):
+    """Milliseconds per call of fn, CUDA events, max over ranks. A short burst runs at boost clocks and a long
+    run at the power cap, 15-25 % apart on a dense GEMM, so every variant is first run for --warm-ms and then
+    timed for at least --time-ms; the counts come from a 3-call estimate that all ranks agree on."""
+    import torch
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    est = max(reduce_max(e0.elapsed_time(e1) / 3), 1e-3)
+    for _ in range(int(min(5000, a.warm_ms / est))):
+        fn()
+    torch.cuda.synchronize()
+    barrier()
+    iters = int(max(a.iters, min(5000, a.time_ms / est)))
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return reduce_max(e0.elapsed_time(e1) / iters)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--dtype", default="bf16", choices=("bf16", "fp8"))
     ap.add_argument("--shapes", default="8192x3584x8192,8192x8192x3584,8192x8192x8192")
-    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--iters", type=int, default=20, help="least number of timed launches")
+    ap.add_argument("--warm-ms", type=float, default=400.0, help="warm every variant up for this long, so that all are timed at sustained (power-capped) clocks")
+    ap.add_argument("--time-ms", type=float, default=300.0, help="time every variant for at least this long")
     ap.add_argument("--no-cublas", action="store_true")
     ap.add_argument("--fused", action="store_true")
     ap.add_argument("--tokens", type=int, default=8192)
@@ -45,16 +77,7 @@ def main(argv=None):
     tp = TensorParallel(comm, max(s[0] for s in shapes), max(s[1] for s in shapes))
 
     def timed(fn):
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(a.iters):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / a.iters
+        return timed_sustained(fn, a, lambda v: v, lambda: None)
 
     for M, N, K in shapes:
         x = torch.randn(M, K, device="cuda").bfloat16()
@@ -126,17 +149,7 @@ def fused(a):
     d.barrier()
 
     def timed(fn):
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        d.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(a.iters):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return d.max(e0.elapsed_time(e1) / a.iters)
+        return timed_sustained(fn, a, d.max, d.barrier)
 
     def unfused_up():
         base.all_gather(x_rows, x_full)
