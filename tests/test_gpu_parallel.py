@@ -131,3 +131,69 @@ def test_pipeline_matches_autograd(n):
     assert abs(res[n - 1][0] - res[n - 1][1]) < 3e-2 * max(1.0, abs(res[n - 1][1]))
     for r in range(n):
         assert max(res[r][2].values()) < 0.1, res[r][2]
+
+
+def _ddp_ctx_rank(rank, nranks, uid):
+    import torch
+    torch.cuda.set_device(rank)
+    from nccl_b200 import Communicator
+    from nccl_b200.parallel.context import ring_attention, ulysses_attention
+    from nccl_b200.parallel.ddp import GradientBuckets
+    comm = Communicator(nranks, rank, uid)
+    torch.manual_seed(3)
+    model = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.GELU(), torch.nn.Linear(512, 128)).cuda()
+    buckets = GradientBuckets(comm, list(model.parameters()), bucket_bytes=256 << 10)
+    g = torch.Generator().manual_seed(100 + rank)
+    x, y = torch.randn(32, 256, generator=g).cuda(), torch.randn(32, 128, generator=g).cuda()
+    for _ in range(2):
+        buckets.zero_grad()
+        ((model(x) - y) ** 2).mean().backward()
+        buckets.finish()
+    torch.cuda.synchronize()
+    grads = [p.grad.float().cpu().numpy().copy() for p in model.parameters()]
+    nb = len(buckets.buckets)
+    buckets.close()
+    # sequence-parallel attention on the same communicator
+    B, H, S_all, D = 2, 8, 64 * nranks, 32
+    gq = torch.Generator().manual_seed(11)
+    q, k, v = [torch.randn(B, H, S_all, D, generator=gq) for _ in range(3)]
+    S = S_all // nranks
+    sl = slice(rank * S, (rank + 1) * S)
+    loc = [t[:, :, sl].contiguous().cuda() for t in (q, k, v)]
+    ring = ring_attention(comm, *loc, causal=True)
+    uly = ulysses_attention(comm, *[t.transpose(1, 2).contiguous() for t in loc], causal=True).transpose(1, 2)
+    torch.cuda.synchronize()
+    assert comm.async_error() == 0
+    out = grads, nb, ring.cpu().numpy(), uly.cpu().numpy()
+    comm.destroy()
+    return out
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_gradient_buckets_and_context_parallel(n):
+    import numpy as np
+    if _ngpus() < n:
+        pytest.skip("needs %d GPUs" % n)
+    res = run_ranks(_ddp_ctx_rank, n, timeout=300)
+    torch.manual_seed(3)
+    model = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.GELU(), torch.nn.Linear(512, 128))
+    ref = [torch.zeros_like(p) for p in model.parameters()]
+    for r in range(n):
+        model.zero_grad()
+        g = torch.Generator().manual_seed(100 + r)
+        x, y = torch.randn(32, 256, generator=g), torch.randn(32, 128, generator=g)
+        ((model(x) - y) ** 2).mean().backward()
+        for a, p in zip(ref, model.parameters()):
+            a += p.grad / n
+    B, H, S_all, D = 2, 8, 64 * n, 32
+    gq = torch.Generator().manual_seed(11)
+    q, k, v = [torch.randn(B, H, S_all, D, generator=gq) for _ in range(3)]
+    att = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True).numpy()
+    S = S_all // n
+    for r in range(n):
+        grads, nb, ring, uly = res[r]
+        assert nb >= 2
+        for gg, a in zip(grads, ref):
+            np.testing.assert_allclose(gg, a.numpy(), rtol=2e-3, atol=2e-5)
+        np.testing.assert_allclose(ring, att[:, :, r * S:(r + 1) * S], rtol=2e-3, atol=2e-4)
+        np.testing.assert_allclose(uly, att[:, :, r * S:(r + 1) * S], rtol=2e-3, atol=2e-4)
