@@ -244,6 +244,48 @@ static ncclResult_t ringAllGatherInPlace(ncclComm* comm, char* buf, const Chunks
   return ncclSuccess;
 }
 
+// ---- log-step schedules (what the reference calls PAT, parallel aggregated trees: include/collectives.h:411-923).
+// ceil(log2 n) exchanges instead of n - 1: step k moves up to 2^k aggregated blocks between ranks 2^k apart.
+// `work` holds n blocks of `blk` bytes in rotated order: work[i] belongs to rank (r + i) mod n.
+static ncclResult_t logStepAllGather(ncclComm* comm, char* work, size_t blk) {
+  HostPlane* hp = comm->hostPlane;
+  const int n = comm->nRanks, r = comm->rank;
+  for (int dist = 1; dist < n; dist <<= 1) {
+    const int cnt = std::min(dist, n - dist);
+    const int to = (r - dist + n) % n, from = (r + dist) % n;
+    NCCLCHECK(exchange(hp, to, work, (size_t)cnt * blk, from, work + (size_t)dist * blk, (size_t)cnt * blk));
+  }
+  return ncclSuccess;
+}
+
+// The same exchanges backwards: blocks travel towards their owners and are summed on the way; work[0] ends
+// as the reduction of this rank's block over all ranks.
+static ncclResult_t logStepReduceScatter(ncclComm* comm, char* work, size_t blkElems, size_t es, ncclDataType_t type, int hop) {
+  HostPlane* hp = comm->hostPlane;
+  const int n = comm->nRanks, r = comm->rank;
+  const size_t blk = blkElems * es;
+  int top = 1;
+  while (top * 2 < n) top <<= 1;
+  for (int dist = top; dist >= 1; dist >>= 1) {
+    const int cnt = std::min(dist, n - dist);
+    const int to = (r + dist) % n, from = (r - dist + n) % n;
+    hp->tmp.resize((size_t)cnt * blk);
+    NCCLCHECK(exchange(hp, to, work + (size_t)dist * blk, (size_t)cnt * blk, from, hp->tmp.data(), (size_t)cnt * blk));
+    hostReduceInto(work, hp->tmp.data(), (size_t)cnt * blkElems, type, hop);
+  }
+  return ncclSuccess;
+}
+
+B200_PARAM(HostLogStepBytes, "B200_HOST_LOGSTEP_BYTES", 65536,
+           "host-memory all-gather / reduce-scatter of at most this many bytes per rank use the log-step (PAT) schedule when there are more than two ranks");
+
+static bool useLogStep(ncclComm* comm, size_t bytesPerRank) {
+  static const char* e = getEnv("NCCL_ALGO");
+  if (comm->nRanks < 3) return false;
+  if (e && *e) return !strcasecmp(e, "PAT");
+  return bytesPerRank <= (size_t)paramHostLogStepBytes();
+}
+
 ncclResult_t hostPlaneRun(ncclComm* comm, const Task& t) {
   HostPlane* hp = comm->hostPlane;
   if (!hp) return ncclInternalError;
@@ -266,6 +308,16 @@ ncclResult_t hostPlaneRun(ncclComm* comm, const Task& t) {
       NCCLCHECK(resolveOp(comm, t, &od));
       size_t total = t.count * n;
       std::vector<char> work(total * es);
+      if (useLogStep(comm, t.count * es)) {
+        // rotate so that work[i] is the block of rank (r + i) mod n
+        const size_t blk = t.count * es;
+        for (int i = 0; i < n; ++i) memcpy(work.data() + (size_t)i * blk, (const char*)t.send + (size_t)((r + i) % n) * blk, blk);
+        premulInto(work.data(), total, t.type, od);
+        NCCLCHECK(logStepReduceScatter(comm, work.data(), t.count, es, t.type, od.hop));
+        memcpy(t.recv, work.data(), blk);
+        if (od.postscale) hostScale(t.recv, t.count, t.type, od.scale, od.intDiv);
+        break;
+      }
       memcpy(work.data(), t.send, total * es);
       premulInto(work.data(), total, t.type, od);
       Chunks ch{total, n};  // equal chunks of t.count
@@ -275,6 +327,14 @@ ncclResult_t hostPlaneRun(ncclComm* comm, const Task& t) {
     } break;
     case FUNC_ALLGATHER: {
       char* out = (char*)t.recv;
+      if (useLogStep(comm, t.count * es)) {
+        const size_t blk = t.count * es;
+        std::vector<char> work((size_t)n * blk);
+        memcpy(work.data(), t.send, blk);
+        NCCLCHECK(logStepAllGather(comm, work.data(), blk));
+        for (int i = 0; i < n; ++i) memcpy(out + (size_t)((r + i) % n) * blk, work.data() + (size_t)i * blk, blk);
+        break;
+      }
       if (out + (size_t)r * t.count * es != t.send) memcpy(out + (size_t)r * t.count * es, t.send, t.count * es);
       Chunks ch{t.count * n, n};
       if (n > 1) NCCLCHECK(ringAllGatherInPlace(comm, out, ch, es, 0));

@@ -88,3 +88,43 @@ def test_every_collective_on_host(nranks):
         assert np.array_equal(o["a2a"], np.repeat(np.arange(n, dtype=np.int32) * 100 + r, 3))
         assert np.array_equal(o["ring"], np.full(4, (r - 1) % n, dtype=np.float32))
         assert np.array_equal(o["half"], np.full(6, 1.5 * tot, dtype=np.float16))
+
+
+def _logstep_rank(rank, nranks, uid, count):
+    import numpy as np
+    from nccl_b200 import Communicator
+    comm = Communicator(nranks, rank, uid)
+    n = nranks
+    rng = np.random.default_rng(7 + rank)
+    mine = rng.integers(-1000, 1000, size=count).astype(np.int64)
+    gathered = np.empty(count * n, dtype=np.int64)
+    comm.all_gather(mine, gathered)
+    full = rng.integers(-1000, 1000, size=count * n).astype(np.int64)
+    part = np.empty(count, dtype=np.int64)
+    comm.reduce_scatter(full, part, op="sum")
+    favg = np.full(count * n, float(rank + 1), dtype=np.float32)
+    pavg = np.empty(count, dtype=np.float32)
+    comm.reduce_scatter(favg, pavg, op="avg")
+    comm.destroy()
+    return gathered, part, pavg
+
+
+@pytest.mark.parametrize("algo", ["PAT", "Ring", None])
+@pytest.mark.parametrize("nranks", [3, 5, 8])
+def test_log_step_all_gather_and_reduce_scatter(nranks, algo):
+    """The log-step (PAT-style) schedule gives the results of the ring schedule for every rank count, power of two or not."""
+    count = 3001
+    env = {"NCCL_ALGO": algo} if algo else {}
+    res = run_ranks(_logstep_rank, nranks, args=(count,), env=env, timeout=200)
+    n = nranks
+    mines, fulls = [], []
+    for r in range(n):
+        rng = np.random.default_rng(7 + r)
+        mines.append(rng.integers(-1000, 1000, size=count).astype(np.int64))
+        fulls.append(rng.integers(-1000, 1000, size=count * n).astype(np.int64))
+    total = sum(fulls)
+    for r in range(n):
+        g, p, a = res[r]
+        assert np.array_equal(g, np.concatenate(mines))
+        assert np.array_equal(p, total[r * count:(r + 1) * count])
+        assert np.allclose(a, (n + 1) / 2.0)
