@@ -108,7 +108,7 @@ static ParamRegistrar kStrParams[] = {
     {{"NCCL_SOCKET_IFNAME", PT_STR, "", "Interface name filter for bootstrap sockets (^ excludes, = exact)", true}},
     {{"NCCL_COMM_ID", PT_STR, "", "ip:port of the bootstrap root instead of a broadcast unique id", true}},
     {{"NCCL_HOSTID", PT_STR, "", "String hashed into the host identity instead of hostname+boot id", true}},
-    {{"NCCL_ALGO", PT_STR, "", "Restrict algorithms: Ring,Tree,NVLS,OneShot,TwoShot,Direct (^ excludes)", true}},
+    {{"NCCL_ALGO", PT_STR, "", "Force one algorithm: Ring, Tree, NVLS, OneShot (LL), TwoShot (P2P, Direct), CE on GPU communicators; PAT or Ring on host-memory communicators", true}},
     {{"NCCL_PROTO", PT_STR, "", "Restrict protocols: LL,Simple (^ excludes)", true}},
     {{"NCCL_TOPO_FILE", PT_STR, "", "XML topology to load instead of probing the machine", true}},
     {{"NCCL_TOPO_DUMP_FILE", PT_STR, "", "Write the detected topology XML here", true}},
