@@ -60,7 +60,20 @@ $(LIBDIR)/plugins/%.so: plugins/%.cc $(wildcard include/*.h include/plugin/*.h)
 	@mkdir -p $(dir $@)
 	$(CXX) $(CXXFLAGS) -shared $< -o $@
 
+# make install PREFIX=/opt/nccl_b200 : library, headers, tools, plugins and a pkg-config file
+PREFIX ?= /usr/local
+install: all
+	install -d $(DESTDIR)$(PREFIX)/lib/pkgconfig $(DESTDIR)$(PREFIX)/lib/nccl_b200/plugins $(DESTDIR)$(PREFIX)/bin \
+	           $(DESTDIR)$(PREFIX)/include/nccl_device $(DESTDIR)$(PREFIX)/include/plugin
+	install -m 755 $(LIB) $(DESTDIR)$(PREFIX)/lib/
+	install -m 755 $(TOOLS) $(DESTDIR)$(PREFIX)/bin/
+	install -m 644 include/*.h $(DESTDIR)$(PREFIX)/include/
+	install -m 644 include/nccl_device/*.h $(DESTDIR)$(PREFIX)/include/nccl_device/
+	install -m 644 include/plugin/*.h $(DESTDIR)$(PREFIX)/include/plugin/
+	cp -r $(LIBDIR)/plugins/. $(DESTDIR)$(PREFIX)/lib/nccl_b200/plugins/
+	printf 'prefix=%s\nlibdir=$${prefix}/lib\nincludedir=$${prefix}/include\n\nName: nccl_b200\nDescription: collective communication library for B200 with the NCCL host API\nVersion: 2.30.7\nLibs: -L$${libdir} -lnccl_b200\nCflags: -I$${includedir}\n' '$(PREFIX)' > $(DESTDIR)$(PREFIX)/lib/pkgconfig/nccl_b200.pc
+
 clean:
 	rm -rf $(BUILD) $(LIBDIR) $(BINDIR)
 
-.PHONY: all clean plugins examples
+.PHONY: all clean plugins examples install
