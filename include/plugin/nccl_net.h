@@ -90,4 +90,43 @@ typedef struct {
 typedef ncclNet_v12_t ncclNet_t;
 #define NCCL_NET_PLUGIN_SYMBOL "ncclNetPlugin_v12"
 
+/* ---- collective network: a fabric that reduces / gathers on its own (in-network reduction).
+ * A net plugin may export this second table; all ranks of a communicator then form one group
+ * (listen on every rank, handles exchanged by the library, connect) and hand whole collectives to it. */
+typedef struct {
+  void* mhandle;
+  void* address;
+  size_t size;
+} ncclNetSGE_v12_t;
+typedef ncclNetSGE_v12_t ncclNetSGE_t;
+
+typedef struct {
+  const char* name;
+  ncclResult_t (*init)(void** ctx, uint64_t commId, ncclDebugLogger_t logFunction);
+  ncclResult_t (*devices)(int* ndev);                                   /* 0 devices: nothing else needs to be set */
+  ncclResult_t (*getProperties)(int dev, ncclNetProperties_t* props);
+  ncclResult_t (*listen)(void* ctx, int dev, void* handle, void** listenComm);
+  ncclResult_t (*connect)(void* handles[], int nranks, int rank, void* listenComm, void** collComm);
+  ncclResult_t (*reduceSupport)(ncclDataType_t dataType, ncclRedOp_t redOp, int* supported);
+  ncclResult_t (*regMr)(void* collComm, void* data, size_t size, int type, void** mhandle);
+  ncclResult_t (*regMrDmaBuf)(void* collComm, void* data, size_t size, int type, uint64_t offset, int fd, void** mhandle);
+  ncclResult_t (*deregMr)(void* collComm, void* mhandle);
+  ncclResult_t (*iallreduce)(void* collComm, void* sendData, void* recvData, size_t count, ncclDataType_t dataType,
+                             ncclRedOp_t redOp, void* sendMhandle, void* recvMhandle, void** request);
+  ncclResult_t (*iallgather)(void* collComm, void* sendData, int nRecvParts, ncclNetSGE_v12_t* recvParts, size_t bytesPerRank,
+                             size_t windowOffset, size_t windowBytes, void* sendMhandle, void** request);
+  ncclResult_t (*ireducescatter)(void* collComm, int nSendParts, ncclNetSGE_v12_t* sendParts, void* recvData, size_t bytesPerRank,
+                                 size_t windowOffset, size_t windowBytes, ncclDataType_t dataType, ncclRedOp_t redOp,
+                                 void* recvMhandle, void** request);
+  ncclResult_t (*iflush)(void* collComm, void* data, int size, void* mhandle, void** request);
+  ncclResult_t (*test)(void* request, int* done, int* size);
+  ncclResult_t (*closeColl)(void* collComm);
+  ncclResult_t (*closeListen)(void* listenComm);
+  ncclResult_t (*makeVDevice)(int* d, ncclNetVDeviceProps_t* props);
+  ncclResult_t (*finalize)(void* ctx);
+} ncclCollNet_v12_t;
+
+typedef ncclCollNet_v12_t ncclCollNet_t;
+#define NCCL_COLLNET_PLUGIN_SYMBOL "ncclCollNetPlugin_v12"
+
 #endif

@@ -24,6 +24,7 @@ struct HostPlane {
   Proxy* proxy = nullptr;     // set when messages travel through the network backend instead
   std::vector<ShmLink> shmOut, shmIn;   // set when every rank is on this host and NCCL_B200_HOST_SHM=1
   bool shm = false;
+  CollNet* collnet = nullptr;   // in-network collectives of the net plugin, when every rank joined (NCCL_COLLNET_ENABLE=1)
   volatile uint32_t* abortFlag = nullptr;
 };
 
@@ -61,7 +62,7 @@ B200_PARAM(HostNet, "B200_HOST_NET", 0, "1: host-memory messages go through the 
 
 static constexpr int kTagHostMesh = BS_TAG_USER + 1;
 
-ncclResult_t hostPlaneCreate(ncclComm* comm) {
+static ncclResult_t hostPlaneCreateLinks(ncclComm* comm) {
   HostPlane* hp = new HostPlane;
   int n = comm->nRanks, me = comm->rank;
   hp->peer.resize(n);
@@ -108,8 +109,14 @@ ncclResult_t hostPlaneCreate(ncclComm* comm) {
   return ncclSuccess;
 }
 
+ncclResult_t hostPlaneCreate(ncclComm* comm) {
+  NCCLCHECK(hostPlaneCreateLinks(comm));
+  return collNetCreate(comm, &comm->hostPlane->collnet);
+}
+
 void hostPlaneDestroy(ncclComm* comm) {
   if (!comm->hostPlane) return;
+  collNetDestroy(comm->hostPlane->collnet);
   proxyDestroy(comm);
   for (auto& l : comm->hostPlane->shmIn) shmLinkClose(&l);
   for (auto& l : comm->hostPlane->shmOut) shmLinkClose(&l);
@@ -200,6 +207,8 @@ static ncclResult_t resolveOp(ncclComm* comm, const Task& t, OpDesc* d) {
   }
   return ncclSuccess;
 }
+
+static ncclRedOp_t hopToRedOp(int hop) { return hop == HOP_SUM ? ncclSum : hop == HOP_PROD ? ncclProd : hop == HOP_MAX ? ncclMax : ncclMin; }
 
 static void premulInto(void* dst, size_t n, ncclDataType_t type, const OpDesc& d) {
   if (!d.premul) return;
@@ -295,6 +304,11 @@ ncclResult_t hostPlaneRun(ncclComm* comm, const Task& t) {
   switch (t.func) {
     case FUNC_ALLREDUCE: {
       NCCLCHECK(resolveOp(comm, t, &od));
+      if (hp->collnet && n > 1 && !od.premul && collNetSupports(hp->collnet, t.type, hopToRedOp(od.hop))) {
+        NCCLCHECK(collNetAllReduce(comm, hp->collnet, t.send, t.recv, t.count, t.type, hopToRedOp(od.hop)));
+        if (od.postscale) hostScale(t.recv, t.count, t.type, od.scale, od.intDiv);
+        break;
+      }
       if (t.recv != t.send) memcpy(t.recv, t.send, t.count * es);
       premulInto(t.recv, t.count, t.type, od);
       if (n > 1) {
@@ -307,6 +321,11 @@ ncclResult_t hostPlaneRun(ncclComm* comm, const Task& t) {
     case FUNC_REDUCESCATTER: {
       NCCLCHECK(resolveOp(comm, t, &od));
       size_t total = t.count * n;
+      if (hp->collnet && n > 1 && !od.premul && collNetSupports(hp->collnet, t.type, hopToRedOp(od.hop)) &&
+          collNetReduceScatter(comm, hp->collnet, t.send, t.recv, t.count, t.type, hopToRedOp(od.hop)) == ncclSuccess) {
+        if (od.postscale) hostScale(t.recv, t.count, t.type, od.scale, od.intDiv);
+        break;
+      }
       std::vector<char> work(total * es);
       if (useLogStep(comm, t.count * es)) {
         // rotate so that work[i] is the block of rank (r + i) mod n
@@ -327,6 +346,7 @@ ncclResult_t hostPlaneRun(ncclComm* comm, const Task& t) {
     } break;
     case FUNC_ALLGATHER: {
       char* out = (char*)t.recv;
+      if (hp->collnet && n > 1 && out + (size_t)r * t.count * es != t.send && collNetAllGather(comm, hp->collnet, t.send, out, t.count * es) == ncclSuccess) break;
       if (useLogStep(comm, t.count * es)) {
         const size_t blk = t.count * es;
         std::vector<char> work((size_t)n * blk);

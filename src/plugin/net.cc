@@ -12,6 +12,7 @@ namespace b200 {
 static std::once_flag gNetOnce;
 static ncclNet_t* gNet = nullptr;
 static bool gNetExternal = false;
+static ncclCollNet_t* gCollNet = nullptr;
 
 ncclResult_t netSelect(ncclNet_t** net, bool* external) {
   std::call_once(gNetOnce, [] {
@@ -19,7 +20,10 @@ ncclResult_t netSelect(ncclNet_t** net, bool* external) {
     std::string resolved;
     void* lib = pluginOpen(PLUGIN_NET, &resolved);
     ncclNet_t* ext = lib ? (ncclNet_t*)pluginSymbol(lib, NCCL_NET_PLUGIN_SYMBOL) : nullptr;
-    if (lib && !ext) WARN("net plugin %s does not export %s (older interfaces are not supported); using the built-in backend", resolved.c_str(), NCCL_NET_PLUGIN_SYMBOL);
+    gCollNet = lib ? (ncclCollNet_t*)pluginSymbol(lib, NCCL_COLLNET_PLUGIN_SYMBOL) : nullptr;
+    if (gCollNet) INFO(SUB_NET | SUB_INIT, "net plugin %s offers the collective network %s", resolved.c_str(), gCollNet->name ? gCollNet->name : "?");
+    if (lib && !ext && gCollNet) INFO(SUB_NET | SUB_INIT, "net plugin %s has no point-to-point table (%s): point-to-point traffic stays on the built-in backend", resolved.c_str(), NCCL_NET_PLUGIN_SYMBOL);
+    else if (lib && !ext) WARN("net plugin %s does not export %s (older interfaces are not supported); using the built-in backend", resolved.c_str(), NCCL_NET_PLUGIN_SYMBOL);
     if (ext && wantName && *wantName && strcasecmp(wantName, ext->name) != 0 && strcasecmp(wantName, netSocketBackend.name) == 0) ext = nullptr;
     if (ext) {
       int ndev = 0;
@@ -42,6 +46,12 @@ ncclResult_t netSelect(ncclNet_t** net, bool* external) {
   *net = gNet;
   if (external) *external = gNetExternal;
   return gNet ? ncclSuccess : ncclInternalError;
+}
+
+ncclCollNet_t* netCollNetTable() {
+  ncclNet_t* net;
+  if (netSelect(&net, nullptr) != ncclSuccess) return nullptr;
+  return gCollNet;
 }
 
 }  // namespace b200

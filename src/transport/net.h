@@ -20,6 +20,16 @@ extern ncclNet_t netSocketBackend;                 // transport/net_socket.cc
 
 // Resolves the network backend once per process: NCCL_NET_PLUGIN (library), NCCL_NET (name).
 ncclResult_t netSelect(ncclNet_t** net, bool* external);
+ncclCollNet_t* netCollNetTable();                  // collective-network table of the loaded plugin, or nullptr
+
+// Collective network (in-network reduction) of a communicator: transport/collnet.cc
+struct CollNet;
+ncclResult_t collNetCreate(ncclComm* comm, CollNet** out);   // collective over the bootstrap; *out stays nullptr unless every rank can join
+void collNetDestroy(CollNet* c);
+bool collNetSupports(CollNet* c, ncclDataType_t type, ncclRedOp_t op);
+ncclResult_t collNetAllReduce(ncclComm* comm, CollNet* c, const void* send, void* recv, size_t count, ncclDataType_t type, ncclRedOp_t op);
+ncclResult_t collNetAllGather(ncclComm* comm, CollNet* c, const void* send, void* recv, size_t bytesPerRank);
+ncclResult_t collNetReduceScatter(ncclComm* comm, CollNet* c, const void* send, void* recv, size_t countPerRank, ncclDataType_t type, ncclRedOp_t op);
 void pluginLogger(ncclDebugLogLevel level, unsigned long flags, const char* file, int line, const char* fmt, ...);
 
 struct ProxyOp {

@@ -98,3 +98,50 @@ def test_shm_links():
     """Ranks of one host exchange host-memory messages through shared-memory rings."""
     env = dict(BASE, NCCL_B200_HOST_SHM="1", NCCL_B200_HOST_SHM_KB="64")   # small rings: messages wrap many times
     _check(run_ranks(_rank, 3, args=(2,), env=env), 3)
+
+
+def _collnet_rank(rank, nranks, uid):
+    from nccl_b200 import Communicator
+    comm = Communicator(nranks, rank, uid)
+    n = nranks
+    x = np.arange(5000, dtype=np.float64) * (rank + 1)
+    y = np.zeros_like(x)
+    comm.all_reduce(x, y, op="sum")
+    z = np.zeros_like(x)
+    comm.all_reduce(x, z, op="avg")
+    g = np.zeros(n * 300, dtype=np.int32)
+    comm.all_gather(np.full(300, rank, dtype=np.int32), g)
+    full = np.arange(n * 77, dtype=np.int64) + rank
+    part = np.zeros(77, dtype=np.int64)
+    comm.reduce_scatter(full, part, op="max")
+    half = np.full(64, np.float16(rank + 1), dtype=np.float16)   # a type the fabric does not reduce: falls back to the ring
+    hout = np.zeros_like(half)
+    comm.all_reduce(half, hout)
+    comm.destroy()
+    return y, z, g, part, hout
+
+
+@pytest.mark.parametrize("enable", ["1", "0"])
+def test_collective_network_plugin(tmp_path, enable):
+    """With NCCL_COLLNET_ENABLE=1 all-reduce / all-gather / reduce-scatter of supported types go through the plugin's
+    collective network (its log shows them); unsupported types and NCCL_COLLNET_ENABLE=0 stay on the ring."""
+    n = 3
+    env = dict(BASE, NCCL_NET_PLUGIN=os.path.join(PLUG, "net", "star_collnet.so"), NCCL_COLLNET_ENABLE=enable,
+               STAR_COLLNET_LOG=str(tmp_path / "star"))
+    res = run_ranks(_collnet_rank, n, env=env, timeout=200)
+    tot = n * (n + 1) / 2
+    base = np.arange(5000, dtype=np.float64)
+    for r in range(n):
+        y, z, g, part, hout = res[r]
+        assert np.array_equal(y, base * tot)
+        assert np.allclose(z, base * tot / n)
+        assert np.array_equal(g, np.repeat(np.arange(n, dtype=np.int32), 300))
+        assert np.array_equal(part, np.arange(n * 77, dtype=np.int64)[r * 77:(r + 1) * 77] + n - 1)
+        assert np.array_equal(hout, np.full(64, tot, dtype=np.float16))
+    logs = [open(os.path.join(tmp_path, p)).read().split() for p in os.listdir(tmp_path)]
+    if enable == "1":
+        assert len(logs) == n
+        for words in logs:
+            assert words.count("allreduce") == 2 and words.count("allgather") == 1 and words.count("reducescatter") == 1
+    else:
+        assert logs == []
