@@ -53,6 +53,10 @@ int main() {
     CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), s));
     sumKernel<<<kCtas, kThreads, 0, s>>>(dc, devWin, count, status);
     CUDA_OK(cudaGetLastError());
+    // The handle from ncclCommWindowRegister is itself readable from kernels (pinned, mapped host memory);
+    // the device copy above is only the faster of the two. Run once more with it.
+    sumKernel<<<kCtas, kThreads, 0, s>>>(dc, win, count, status);
+    CUDA_OK(cudaGetLastError());
     int st = -1;
     CUDA_OK(cudaMemcpyAsync(&st, status, sizeof(int), cudaMemcpyDeviceToHost, s));
     CUDA_OK(cudaMemcpyAsync(h.data(), buf + count, count * sizeof(float), cudaMemcpyDeviceToHost, s));

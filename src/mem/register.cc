@@ -43,6 +43,7 @@ ncclResult_t ncclCommWindowRegister(ncclComm_t comm, void* buff, size_t size, nc
     CUDACHECK(cudaMalloc(&dev, sizeof(*dev)));
     w->host.devSelf = dev;
     CUDACHECK(cudaMemcpy(dev, &w->host, sizeof(*dev), cudaMemcpyHostToDevice));
+    symWindowPublishHandle(w);
     *win = &w->host;
     return ncclSuccess;
   }
@@ -63,6 +64,7 @@ ncclResult_t ncclCommWindowDeregister(ncclComm_t comm, ncclWindow_t win) {
   if (win->magic != kWindowMagic) { WARN("ncclCommWindowDeregister : not a window handle"); return ncclInvalidArgument; }
   SymWindow* w = (SymWindow*)win->hostState;
   if (comm->nRanks == 1 || !comm->sym) {
+    symWindowUnpublishHandle(w);
     if (w->host.devSelf) cudaFree(w->host.devSelf);
     delete w;
     return ncclSuccess;

@@ -73,6 +73,7 @@ void symDestroy(ncclComm* comm) {
   SymRuntime* s = comm->sym;
   if (!s) return;
   for (auto* w : s->windows) {
+    symWindowUnpublishHandle(w);
     if (w->host.devSelf) cudaFree(w->host.devSelf);
     delete w;
   }
@@ -383,11 +384,28 @@ ncclResult_t symWindowRegister(ncclComm* comm, void* buff, size_t size, SymWindo
   if (cudaMalloc(&dev, sizeof(ncclWindow_vidmem)) != cudaSuccess) { (void)cudaGetLastError(); delete w; return ncclUnhandledCudaError; }
   w->host.devSelf = dev;
   cudaMemcpy(dev, &w->host, sizeof(ncclWindow_vidmem), cudaMemcpyHostToDevice);
+  symWindowPublishHandle(w);
   s->windows.push_back(w);
   INFO(SUB_REG, "window %p size %zu: %s%s", buff, size, w->symmetric ? (kind == SEG_VMM ? "symmetric (vmm)" : "symmetric (ipc)") : "local only",
        w->host.mcPtr ? " + multicast" : "");
   *out = w;
   return ncclSuccess;
+}
+
+void symWindowPublishHandle(SymWindow* w) {
+  int dev = 0, same = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&same, cudaDevAttrCanUseHostPointerForRegisteredMem, dev) != cudaSuccess || !same) {
+    (void)cudaGetLastError();
+    return;
+  }
+  if (cudaHostRegister(&w->host, sizeof(w->host), cudaHostRegisterPortable | cudaHostRegisterMapped) == cudaSuccess) w->hostMapped = true;
+  else (void)cudaGetLastError();   // the host handle then works on the host only; kernels use devSelf
+}
+
+void symWindowUnpublishHandle(SymWindow* w) {
+  if (!w->hostMapped) return;
+  if (cudaHostUnregister(&w->host) != cudaSuccess) (void)cudaGetLastError();
+  w->hostMapped = false;
 }
 
 ncclResult_t symWindowDeregister(ncclComm* comm, SymWindow* win) {
@@ -404,6 +422,7 @@ ncclResult_t symWindowDeregister(ncclComm* comm, SymWindow* win) {
     cudaDeviceSynchronize();
     releaseSegment(comm, win->seg);
   }
+  symWindowUnpublishHandle(win);
   if (win->host.devSelf) cudaFree(win->host.devSelf);
   delete win;
   return ncclSuccess;

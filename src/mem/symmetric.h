@@ -37,13 +37,20 @@ struct SymSegment {
   int refs = 0;
 };
 
-struct SymWindow {
+// Page-aligned and page-sized so that `host` can be pinned and mapped for device access on its own:
+// the handle ncclCommWindowRegister returns (&host) is then valid inside kernels too, as the
+// reference's window handles are; host.devSelf is the copy in device memory that kernels read faster.
+struct alignas(4096) SymWindow {
   ncclWindow_vidmem host;          // host mirror (host.devSelf = device copy)
+  bool hostMapped = false;         // `host` is registered with the CUDA driver (cudaHostRegister)
   SymSegment* seg = nullptr;
   size_t offset = 0;               // offset of the window inside my allocation
   int flags = 0;
   bool symmetric = false;          // peers are mapped; false = local-only registration
 };
+
+void symWindowPublishHandle(SymWindow* w);     // after `host` is complete: make &w->host readable from kernels
+void symWindowUnpublishHandle(SymWindow* w);   // before the object is freed
 
 struct SymRuntime {
   ncclComm* comm = nullptr;
