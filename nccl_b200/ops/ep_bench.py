@@ -75,6 +75,12 @@ def main(argv=None):
            "dispatch_us": disp_ms * 1e3, "combine_us": comb_ms * 1e3, "dispatch_plus_combine_us": both_ms * 1e3,
            "recv_tokens_max": int(recv_max),
            "dispatch_GBps": recv_max * (H + H // 128 * 4) / disp_ms / 1e6, "combine_GBps": recv_max * H * 2 / comb_ms / 1e6}
+    # Roofline: the bytes the busiest rank must receive (dispatch) or return (combine), of which (n - 1) / n cross NVLink,
+    # over the measured peer-copy bandwidth per direction per GPU.
+    link = 770.0
+    res["roofline_fraction"] = {"dispatch": round(res["dispatch_GBps"] * (n - 1) / n / link, 3) if n > 1 else None,
+                                "combine": round(res["combine_GBps"] * (n - 1) / n / link, 3) if n > 1 else None}
+    res["peaks"] = {"nvlink_gbs": link}
     assert comm.async_error() == 0
     ep.destroy()
 
