@@ -146,6 +146,10 @@ namespace b200 {
 inline bool commValid(const ncclComm* c) { return c && c->startMagic == kCommMagic && c->endMagic == kCommMagic; }
 ncclResult_t commEnsureReady(ncclComm* c);  // waits for / reports the state of a non-blocking init
 
+// process-wide checkpoint calls walk the live communicators: contrib/checkpoint.cc
+void checkpointCommAdd(ncclComm* comm);
+void checkpointCommRemove(ncclComm* comm);
+
 // host data plane ---------------------------------------------------------------------------
 ncclResult_t hostPlaneCreate(ncclComm* comm);
 void hostPlaneDestroy(ncclComm* comm);

@@ -153,6 +153,7 @@ static ncclResult_t commSetup(ncclComm* comm) {
   NCCLCHECK(tunerLoad(comm));
   profilerCommInit(comm);
   if (paramRasEnable()) rasCommAdd(comm);
+  checkpointCommAdd(comm);
   INFO(SUB_INIT, "comm %p rank %d nranks %d cudaDev %d nodes %d localRanks %d %s - Init COMPLETE", (void*)comm, comm->rank, n, comm->cudaDev,
        comm->nNodes, comm->localRanks, comm->hostOnly ? "(host memory)" : (comm->lsaAll ? "(symmetric data plane)" : "(socket fallback)"));
   return ncclSuccess;
@@ -180,6 +181,7 @@ static void freeComm(ncclComm* comm) {
   if (!comm) return;
   if (comm->initThread) { if (comm->initThread->joinable()) comm->initThread->join(); delete comm->initThread; }
   rasCommRemove(comm);
+  checkpointCommRemove(comm);
   profilerCommFini(comm);
   tunerUnload(comm);
   if (comm->devPlane) {

@@ -1,6 +1,9 @@
 // Checkpoint support: see include/nccl_checkpoint.h.
 #include "nccl_checkpoint.h"
 
+#include <algorithm>
+#include <mutex>
+
 #include "../comm/comm.h"
 #include "../comm/device_plane.h"
 #include "../mem/symmetric.h"
@@ -17,14 +20,31 @@ struct ncclCheckpointState {
   std::vector<Win> windows;
 };
 
+// Live communicators of this process in creation order (init.cc adds and removes them), and the ones the
+// process-wide prepare call suspended.
+static std::mutex gCommsLock;
+static std::vector<ncclComm*> gComms, gSuspended;
+
+namespace b200 {
+void checkpointCommAdd(ncclComm* comm) {
+  std::lock_guard<std::mutex> g(gCommsLock);
+  gComms.push_back(comm);
+}
+void checkpointCommRemove(ncclComm* comm) {
+  std::lock_guard<std::mutex> g(gCommsLock);
+  gComms.erase(std::remove(gComms.begin(), gComms.end(), comm), gComms.end());
+  gSuspended.erase(std::remove(gSuspended.begin(), gSuspended.end(), comm), gSuspended.end());
+}
+}  // namespace b200
+
 static constexpr uint64_t kCkptMagic = 0x434b50544232303ull;
 
 extern "C" {
 
-ncclResult_t ncclCheckpointPrepare(ncclComm_t comm, ncclCheckpoint_t* out) {
+ncclResult_t ncclCommCheckpointPrepare(ncclComm_t comm, ncclCheckpoint_t* out) {
   if (!commValid(comm) || !out) return ncclInvalidArgument;
   NCCLCHECK(commEnsureReady(comm));
-  if (comm->parent || comm->childCount) INFO(SUB_INIT, "ncclCheckpointPrepare: split relations are not recorded; re-split after the restore");
+  if (comm->parent || comm->childCount) INFO(SUB_INIT, "ncclCommCheckpointPrepare: split relations are not recorded; re-split after the restore");
   ncclCheckpointState* st = new ncclCheckpointState;
   st->nRanks = comm->nRanks;
   st->rank = comm->rank;
@@ -55,7 +75,7 @@ ncclResult_t ncclCheckpointPrepare(ncclComm_t comm, ncclCheckpoint_t* out) {
   return ncclSuccess;
 }
 
-ncclResult_t ncclCheckpointSave(ncclCheckpoint_t st, void* buf, size_t* bytes) {
+ncclResult_t ncclCommCheckpointSave(ncclCheckpoint_t st, void* buf, size_t* bytes) {
   if (!st || !bytes) return ncclInvalidArgument;
   const size_t need = 8 + 4 + 4 * 3 + sizeof(ncclConfig_t) + sizeof(st->name) + 4 + st->windows.size() * sizeof(ncclCheckpointState::Win);
   if (!buf || *bytes < need) { bool query = !buf; *bytes = need; return query ? ncclSuccess : ncclInvalidArgument; }
@@ -75,13 +95,13 @@ ncclResult_t ncclCheckpointSave(ncclCheckpoint_t st, void* buf, size_t* bytes) {
   return ncclSuccess;
 }
 
-ncclResult_t ncclCheckpointLoad(const void* buf, size_t bytes, ncclCheckpoint_t* out) {
+ncclResult_t ncclCommCheckpointLoad(const void* buf, size_t bytes, ncclCheckpoint_t* out) {
   if (!buf || !out || bytes < 8 + 4 + 12 + sizeof(ncclConfig_t) + 128 + 4) return ncclInvalidArgument;
   const char* p = (const char*)buf;
   auto get = [&](void* dst, size_t n) { memcpy(dst, p, n); p += n; };
   uint64_t magic;
   get(&magic, 8);
-  if (magic != kCkptMagic) { WARN("ncclCheckpointLoad: not a checkpoint record"); return ncclInvalidArgument; }
+  if (magic != kCkptMagic) { WARN("ncclCommCheckpointLoad: not a checkpoint record"); return ncclInvalidArgument; }
   ncclCheckpointState* st = new ncclCheckpointState;
   get(&st->version, 4);
   get(&st->nRanks, 4);
@@ -100,7 +120,7 @@ ncclResult_t ncclCheckpointLoad(const void* buf, size_t bytes, ncclCheckpoint_t*
   return ncclSuccess;
 }
 
-ncclResult_t ncclCheckpointRestore(ncclCheckpoint_t st, ncclUniqueId uid, ncclComm_t* comm, ncclWindow_t* windows, int maxWindows) {
+ncclResult_t ncclCommCheckpointRestore(ncclCheckpoint_t st, ncclUniqueId uid, ncclComm_t* comm, ncclWindow_t* windows, int maxWindows) {
   if (!st || !comm) return ncclInvalidArgument;
   ncclConfig_t cfg = st->config;
   cfg.commName = st->name[0] ? st->name : nullptr;
@@ -113,8 +133,59 @@ ncclResult_t ncclCheckpointRestore(ncclCheckpoint_t st, ncclUniqueId uid, ncclCo
   return ncclSuccess;
 }
 
-ncclResult_t ncclCheckpointFree(ncclCheckpoint_t st) {
+ncclResult_t ncclCommCheckpointFree(ncclCheckpoint_t st) {
   delete st;
+  return ncclSuccess;
+}
+
+// ---- process-wide calls with the reference's signatures (contrib/nccl_checkpoint/nccl_checkpoint.h:22-24).
+// Every communicator keeps its handle. Prepare drains each GPU communicator and releases the device memory and
+// peer mappings the library owns (the collective suspend of ncclCommSuspend), in creation order, which is the same
+// on every rank; Restore maps everything again. Communicators the application suspended itself are left alone.
+ncclResult_t ncclCheckpointPrepare(void) {
+  std::vector<ncclComm*> comms;
+  {
+    std::lock_guard<std::mutex> g(gCommsLock);
+    if (!gSuspended.empty()) { WARN("ncclCheckpointPrepare: already prepared; call ncclCheckpointRestore first"); return ncclInvalidUsage; }
+    comms = gComms;
+  }
+  std::vector<ncclComm*> done;
+  for (ncclComm* c : comms) {
+    if (!commValid(c) || c->hostOnly || c->revoked || c->finalized) continue;
+    NCCLCHECK(commEnsureReady(c));
+    uint64_t already = 0;
+    if (memStats(c, ncclStatGpuMemSuspended, &already) == ncclSuccess && already) continue;
+    ncclResult_t r = memSuspend(c);
+    if (r != ncclSuccess) {
+      for (ncclComm* d : done) memResume(d);
+      return r;
+    }
+    done.push_back(c);
+  }
+  std::lock_guard<std::mutex> g(gCommsLock);
+  gSuspended = done;
+  INFO(SUB_INIT, "ncclCheckpointPrepare: %zu communicator(s) suspended", done.size());
+  return ncclSuccess;
+}
+
+ncclResult_t ncclCheckpointRestore(void) {
+  std::vector<ncclComm*> comms;
+  {
+    std::lock_guard<std::mutex> g(gCommsLock);
+    comms.swap(gSuspended);
+  }
+  ncclResult_t res = ncclSuccess;
+  for (ncclComm* c : comms) {
+    ncclResult_t r = commValid(c) ? memResume(c) : ncclSuccess;
+    if (r != ncclSuccess && res == ncclSuccess) res = r;
+  }
+  INFO(SUB_INIT, "ncclCheckpointRestore: %zu communicator(s) resumed", comms.size());
+  return res;
+}
+
+ncclResult_t ncclCheckpointGetVersion(int* checkpointVersion, int* ncclVersion) {
+  if (checkpointVersion) *checkpointVersion = NCCL_CHECKPOINT_VERSION;
+  if (ncclVersion) *ncclVersion = NCCL_VERSION_CODE;
   return ncclSuccess;
 }
 
