@@ -29,7 +29,7 @@ struct ncclWindow_vidmem {
   unsigned long long magic;
 };
 
-typedef struct {
+typedef struct ncclTeam {
   int nRanks;
   int rank;
   int stride;
@@ -54,7 +54,7 @@ typedef struct ncclTeamRequirements {
   uint32_t* outMultimemHandle;
 } ncclTeamRequirements_t;
 
-typedef struct {
+typedef struct ncclDevCommRequirements {
   size_t size;
   unsigned int magic;
   unsigned int version;
@@ -83,7 +83,7 @@ typedef struct {
 #define NCCL_DEV_COMM_REQUIREMENTS_INITIALIZER \
   { sizeof(ncclDevCommRequirements_t), NCCL_DEV_COMM_REQUIREMENTS_MAGIC, NCCL_VERSION_CODE, NULL, NULL, 0, 0, 0, 0, 0, 0, 0, 4, 0, 0, 0, 0, 0, 0, 0, 0, 0 }
 
-typedef struct {
+typedef struct ncclCommProperties {
   size_t size;
   unsigned int magic;
   unsigned int version;
@@ -141,6 +141,39 @@ __host__ __device__ inline ncclTeam_t ncclTeamWorld(const ncclDevComm_t& c) { nc
 __host__ __device__ inline ncclTeam_t ncclTeamLsa(const ncclDevComm_t& c) { ncclTeam_t t = {c.lsaSize, c.lsaRank, 1}; return t; }
 __host__ __device__ inline ncclTeam_t ncclTeamRail(const ncclDevComm_t& c) { ncclTeam_t t = {c.nRanks / c.lsaSize, c.rank / c.lsaSize, c.lsaSize}; return t; }
 __host__ __device__ inline int ncclTeamRankToWorld(const ncclDevComm_t& c, ncclTeam_t t, int r) { return c.rank + (r - t.rank) * t.stride; }
+/* Tags that select one of the three built-in teams in constructors. */
+struct ncclTeamTagWorld {};
+struct ncclTeamTagLsa {};
+struct ncclTeamTagRail {};
+/* Rank of team member r inside the load/store team (the team's ranks must lie in this rank's load/store team). */
+__host__ __device__ inline int ncclTeamRankToLsa(const ncclDevComm_t& c, ncclTeam_t t, int r) { return c.lsaRank + (r - t.rank) * t.stride; }
+/* Teams are arithmetic progressions of world ranks around the caller: member i of team t is world rank
+ * self + (i - t.rank) * t.stride. The helpers below translate between two such teams. */
+__host__ __device__ inline bool ncclTeamRankIsMember(ncclTeam_t a, ncclTeam_t b, int bPeer) {
+  const int delta = (bPeer - b.rank) * b.stride;
+  if (delta % a.stride) return false;
+  const int i = a.rank + delta / a.stride;
+  return i >= 0 && i < a.nRanks;
+}
+__host__ __device__ inline int ncclTeamRankToTeam(ncclTeam_t a, ncclTeam_t b, int bPeer) { return a.rank + (bPeer - b.rank) * b.stride / a.stride; }
+/* Split a team of n ranks into blocks of innerSize consecutive members: the block this rank is in, and the team
+ * of the ranks that hold the same position in every block. */
+__host__ __device__ inline ncclTeam_t ncclTeamInnerFactor(ncclTeam_t parent, int innerSize) {
+  ncclTeam_t t = {innerSize, parent.rank % innerSize, parent.stride};
+  return t;
+}
+__host__ __device__ inline ncclTeam_t ncclTeamOuterFactor(ncclTeam_t parent, int innerSize) {
+  ncclTeam_t t = {parent.nRanks / innerSize, parent.rank / innerSize, parent.stride * innerSize};
+  return t;
+}
+/* The index-th member (as a rank of `parent`) of parent minus subset; subset must be a subset of parent. */
+__host__ __device__ inline int ncclTeamRankInDifference(ncclTeam_t parent, ncclTeam_t subset, int index) {
+  for (int i = 0; i < parent.nRanks; ++i) {
+    if (ncclTeamRankIsMember(subset, parent, i)) continue;
+    if (index-- == 0) return i;
+  }
+  return -1;
+}
 
 __device__ inline void* ncclGetLocalPointer(ncclWindow_t w, size_t offset) { return (char*)w->peerPtr[w->rank] + offset; }
 __device__ inline void* ncclGetLsaPointer(ncclWindow_t w, size_t offset, int lsaPeer) { return (char*)w->peerPtr[lsaPeer] + offset; }

@@ -14,8 +14,55 @@
 #ifndef NCCL_DEVICE_GIN_H_
 #define NCCL_DEVICE_GIN_H_
 #include "core.h"
+#include "coop.h"
 #include "utility.h"
 #if defined(__CUDACC__)
+#include <cuda/atomic>
+/* ---- the reference's spellings of "what else to do with a put": a signal on the peer (by id, or a 64-bit word
+ * at an offset of a window: "VA" signals), a completion counter on this rank. Strong and weak variants differ in
+ * what a network must settle first; with peer stores both are a release-ordered add after the data. */
+typedef uint32_t ncclGinSignal_t;
+typedef uint32_t ncclGinCounter_t;
+struct ncclGin_None {};
+struct ncclGin_SignalInc { ncclGinSignal_t signal; };
+struct ncclGin_StrongSignalInc { ncclGinSignal_t signal; };
+struct ncclGin_WeakSignalInc { ncclGinSignal_t signal; };
+struct ncclGin_SignalAdd { ncclGinSignal_t signal; uint64_t value; };
+struct ncclGin_StrongSignalAdd { ncclGinSignal_t signal; uint64_t value; };
+struct ncclGin_WeakSignalAdd { ncclGinSignal_t signal; uint64_t value; };
+struct ncclGin_VASignalInc { ncclWindow_t signalWindow; size_t signalOffset; };
+struct ncclGin_StrongVASignalInc { ncclWindow_t signalWindow; size_t signalOffset; };
+struct ncclGin_WeakVASignalInc { ncclWindow_t signalWindow; size_t signalOffset; };
+struct ncclGin_VASignalAdd { ncclWindow_t signalWindow; size_t signalOffset; uint64_t value; };
+struct ncclGin_StrongVASignalAdd { ncclWindow_t signalWindow; size_t signalOffset; uint64_t value; };
+struct ncclGin_WeakVASignalAdd { ncclWindow_t signalWindow; size_t signalOffset; uint64_t value; };
+struct ncclGin_CounterInc { ncclGinCounter_t counter; };
+struct ncclGin_WeakCounterInc { ncclGinCounter_t counter; };
+namespace nccl_device {
+struct GinAction {   /* normal form of the action types above */
+  int signal;                 /* signal id, or -1 */
+  ncclWindow_t window;        /* VA signal: window and byte offset of the 64-bit word, else NULL */
+  size_t offset;
+  unsigned long long add;
+  int counter;                /* counter id, or -1 */
+};
+__device__ inline GinAction ginAction(ncclGin_None) { GinAction a = {-1, nullptr, 0, 0, -1}; return a; }
+#define NCCL_GIN_ACTION_ID_INC(T) __device__ inline GinAction ginAction(T x) { GinAction a = {(int)x.signal, nullptr, 0, 1, -1}; return a; }
+#define NCCL_GIN_ACTION_ID_ADD(T) __device__ inline GinAction ginAction(T x) { GinAction a = {(int)x.signal, nullptr, 0, x.value, -1}; return a; }
+#define NCCL_GIN_ACTION_VA_INC(T) __device__ inline GinAction ginAction(T x) { GinAction a = {-1, x.signalWindow, x.signalOffset, 1, -1}; return a; }
+#define NCCL_GIN_ACTION_VA_ADD(T) __device__ inline GinAction ginAction(T x) { GinAction a = {-1, x.signalWindow, x.signalOffset, x.value, -1}; return a; }
+#define NCCL_GIN_ACTION_COUNTER(T) __device__ inline GinAction ginAction(T x) { GinAction a = {-1, nullptr, 0, 0, (int)x.counter}; return a; }
+NCCL_GIN_ACTION_ID_INC(ncclGin_SignalInc) NCCL_GIN_ACTION_ID_INC(ncclGin_StrongSignalInc) NCCL_GIN_ACTION_ID_INC(ncclGin_WeakSignalInc)
+NCCL_GIN_ACTION_ID_ADD(ncclGin_SignalAdd) NCCL_GIN_ACTION_ID_ADD(ncclGin_StrongSignalAdd) NCCL_GIN_ACTION_ID_ADD(ncclGin_WeakSignalAdd)
+NCCL_GIN_ACTION_VA_INC(ncclGin_VASignalInc) NCCL_GIN_ACTION_VA_INC(ncclGin_StrongVASignalInc) NCCL_GIN_ACTION_VA_INC(ncclGin_WeakVASignalInc)
+NCCL_GIN_ACTION_VA_ADD(ncclGin_VASignalAdd) NCCL_GIN_ACTION_VA_ADD(ncclGin_StrongVASignalAdd) NCCL_GIN_ACTION_VA_ADD(ncclGin_WeakVASignalAdd)
+NCCL_GIN_ACTION_COUNTER(ncclGin_CounterInc) NCCL_GIN_ACTION_COUNTER(ncclGin_WeakCounterInc)
+#undef NCCL_GIN_ACTION_ID_INC
+#undef NCCL_GIN_ACTION_ID_ADD
+#undef NCCL_GIN_ACTION_VA_INC
+#undef NCCL_GIN_ACTION_VA_ADD
+#undef NCCL_GIN_ACTION_COUNTER
+}  // namespace nccl_device
 struct ncclGin {
   const ncclDevComm_t& comm;
   __device__ explicit ncclGin(const ncclDevComm_t& c, int /*context*/ = 0) : comm(c) {}
@@ -79,6 +126,61 @@ struct ncclGin {
   __device__ void resetSignal(int id) { *(volatile unsigned long long*)signalWord(comm.lsaRank, id) = 0; }
   __device__ void resetCounter(int id) { *(volatile unsigned long long*)counterWord(id) = 0; }
   __device__ void flush() { nccl_device::fenceAcqRelSys(); }
+
+  /* ---- the reference's call shapes (team first, actions as typed values, cooperative group last) */
+  __device__ void applyRemote(int world, const nccl_device::GinAction& a) const {
+    if (a.signal >= 0 && a.signal < comm.ginSignalCount)
+      asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(signalWord(world, a.signal)), "l"(a.add) : "memory");
+    else if (a.window)
+      asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(ncclGetLsaPointer(a.window, a.offset, world)), "l"(a.add) : "memory");
+  }
+  template <typename RemoteAction = ncclGin_None, typename LocalAction = ncclGin_None, typename Coop = ncclCoopThread>
+  __device__ void put(ncclTeam_t team, int peer, ncclWindow_t dstWin, size_t dstOffset, ncclWindow_t srcWin, size_t srcOffset, size_t bytes,
+                      RemoteAction remoteAction = ncclGin_None{}, LocalAction localAction = ncclGin_None{}, Coop coop = ncclCoopThread{}) {
+    const nccl_device::GinAction ra = nccl_device::ginAction(remoteAction), la = nccl_device::ginAction(localAction);
+    if (put(coop, team, peer, dstWin, dstOffset, srcWin, srcOffset, bytes, -1, la.counter) != ncclSuccess) return;
+    if (coop.thread_rank() == 0) applyRemote(ncclTeamRankToWorld(comm, team, peer), ra);
+  }
+  template <typename T, typename RemoteAction = ncclGin_None, typename Coop = ncclCoopThread>
+  __device__ void putValue(ncclTeam_t team, int peer, ncclWindow_t dstWin, size_t dstOffset, T value, RemoteAction remoteAction = ncclGin_None{},
+                           Coop coop = ncclCoopThread{}) {
+    static_assert(sizeof(T) <= 8, "putValue moves at most eight bytes");
+    const int world = ncclTeamRankToWorld(comm, team, peer);
+    if (world < 0 || world >= comm.lsaSize) return;
+    if (coop.thread_rank() == 0) {
+      *(volatile T*)ncclGetLsaPointer(dstWin, dstOffset, world) = value;
+      applyRemote(world, nccl_device::ginAction(remoteAction));
+    }
+  }
+  template <typename RemoteAction, typename Coop = ncclCoopThread>
+  __device__ void signal(ncclTeam_t team, int peer, RemoteAction remoteAction, Coop coop = ncclCoopThread{}) {
+    const int world = ncclTeamRankToWorld(comm, team, peer);
+    if (world < 0 || world >= comm.lsaSize) return;
+    coop.sync();
+    if (coop.thread_rank() == 0) applyRemote(world, nccl_device::ginAction(remoteAction));
+  }
+  template <typename Coop>
+  __device__ void waitSignal(Coop coop, ncclGinSignal_t id, uint64_t least, int /*bits*/ = 64, cuda::memory_order = cuda::memory_order_acquire) const {
+    if (coop.thread_rank() == 0) (void)waitSignal((int)id, (unsigned long long)least, 0ull);
+    coop.sync();
+  }
+  template <typename Coop>
+  __device__ void waitCounter(Coop coop, ncclGinCounter_t id, uint64_t least, int /*bits*/ = 64, cuda::memory_order = cuda::memory_order_acquire) const {
+    if (coop.thread_rank() == 0 && (int)id < comm.ginCounterCount) {
+      const long long start = clock64();
+      unsigned spins = 0;
+      while (readCounter((int)id) < least)
+        if ((++spins & 0xff) == 0 && ((unsigned long long)(clock64() - start) >= comm.timeoutCycles || ncclTestAbort(comm))) break;
+    }
+    coop.sync();
+  }
+  __device__ uint64_t readSignal(ncclGinSignal_t id, int /*bits*/, cuda::memory_order = cuda::memory_order_acquire) const { return readSignal((int)id); }
+  __device__ uint64_t readCounter(ncclGinCounter_t id, int /*bits*/, cuda::memory_order = cuda::memory_order_acquire) const { return readCounter((int)id); }
+  template <typename Coop>
+  __device__ void flush(Coop coop, cuda::memory_order = cuda::memory_order_acquire) const {
+    nccl_device::fenceAcqRelSys();
+    coop.sync();
+  }
 };
 #endif
 #endif

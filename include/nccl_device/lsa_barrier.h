@@ -11,14 +11,35 @@
 #include "coop.h"
 #include "utility.h"
 #if defined(__CUDACC__)
+#include <cuda/atomic>
+namespace nccl_device {
+__host__ __device__ inline bool orderReleases(cuda::memory_order o) {
+  return o == cuda::memory_order_release || o == cuda::memory_order_acq_rel || o == cuda::memory_order_seq_cst;
+}
+__host__ __device__ inline bool orderAcquires(cuda::memory_order o) {
+  return o == cuda::memory_order_acquire || o == cuda::memory_order_consume || o == cuda::memory_order_acq_rel || o == cuda::memory_order_seq_cst;
+}
+}  // namespace nccl_device
 template <typename Coop>
 struct ncclLsaBarrierSession {
   Coop coop;
   const ncclDevComm_t& comm;
   int index;
   uint32_t epoch;
+  bool autoFinish;   /* the tag constructor stores the epoch back when the session goes out of scope */
   __device__ ncclLsaBarrierSession(Coop coop_, const ncclDevComm_t& c, ncclTeam_t /*lsa team*/, int barrierIndex)
-      : coop(coop_), comm(c), index(barrierIndex), epoch(c.barrierEpochs[barrierIndex]) {}
+      : coop(coop_), comm(c), index(barrierIndex), epoch(c.barrierEpochs[barrierIndex]), autoFinish(false) {}
+  /* The reference's spelling: team chosen by tag, scoped session (no finish() call), memory orders instead of flags. */
+  __device__ ncclLsaBarrierSession(Coop coop_, const ncclDevComm_t& c, ncclTeamTagLsa, uint32_t barrierIndex, bool /*multimem*/ = false)
+      : coop(coop_), comm(c), index((int)barrierIndex), epoch(c.barrierEpochs[barrierIndex]), autoFinish(true) {}
+  __device__ ~ncclLsaBarrierSession() { if (autoFinish) finish(); }
+  __device__ void arrive(Coop, cuda::memory_order order) { arrive(nccl_device::orderReleases(order)); }
+  __device__ void wait(Coop, cuda::memory_order order) { (void)wait(0ull, nccl_device::orderAcquires(order)); }
+  __device__ ncclResult_t wait(Coop, cuda::memory_order order, uint64_t timeoutCycles) { return wait((unsigned long long)timeoutCycles, nccl_device::orderAcquires(order)); }
+  __device__ void sync(Coop, cuda::memory_order order) { (void)sync(0ull, nccl_device::orderReleases(order), nccl_device::orderAcquires(order)); }
+  __device__ ncclResult_t sync(Coop, cuda::memory_order order, uint64_t timeoutCycles) {
+    return sync((unsigned long long)timeoutCycles, nccl_device::orderReleases(order), nccl_device::orderAcquires(order));
+  }
   __device__ uint32_t* inbox(int owner, int src) const {
     return (uint32_t*)((char*)comm.resource.peerPtr[owner] + comm.lsaBarrierOffset) + (size_t)index * NCCL_DEVICE_MAX_LSA + src;
   }
