@@ -21,8 +21,6 @@
 // the one-CTA kernel (gemm_sm100.cu); rows per rank must be a multiple of 256 in the fused modes.
 #include "gemm_roles.cuh"
 
-#include <cstdio>
-
 namespace b200 {
 
 using namespace sm100;
@@ -34,10 +32,7 @@ constexpr int P_STAGES = 6;
 constexpr int kThreads = 192;
 constexpr uint32_t kHalfBytes = 128 * BK * 2;   // 128 rows x 64 bf16: A half and W half are the same size
 constexpr uint32_t kStageBytes = 2 * kHalfBytes;
-#ifndef TP_PAIR_ACC_BUFS
-#define TP_PAIR_ACC_BUFS 2
-#endif
-constexpr int kAccBufs = TP_PAIR_ACC_BUFS;     // accumulators of 256 columns in tensor memory (2: the epilogue overlaps the next tile)
+constexpr int kAccBufs = 2;                     // accumulators of 256 columns in tensor memory: the epilogue of one tile overlaps the MMAs of the next
 constexpr uint32_t kTmemCols = kAccBufs * 256;
 constexpr size_t kEpiBufBytes = 4 * 4096;
 constexpr size_t kSmemBytes = 1024 + (size_t)P_STAGES * kStageBytes + 256 + kEpiBufBytes;
@@ -100,9 +95,6 @@ tpGemmPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   clusterSync();   // both CTAs' barriers are initialised before either signals the other's
   tcFenceAfter();
   const uint32_t tmemBase = *tmemSlot;
-#ifdef TP_PAIR_PROBE
-  if (threadIdx.x == 0 && blockIdx.x < 4) printf("pair kernel: block %d cluster rank %u tensor memory base %u\n", (int)blockIdx.x, cr, tmemBase);
-#endif
   if (!ok && threadIdx.x == 0) stSharedCluster(mapaShared(smemAddr((const void*)abortFlag), cr ^ 1), 1u);
 
   const int tilesN = a.N / BN;
