@@ -65,3 +65,55 @@ def test_key_table_and_tool():
     tool = subprocess.run([TOOL], capture_output=True, text=True, timeout=60, env=dict(os.environ, NCCL_B200_NET_INFLIGHT="5"))
     assert tool.returncode == 0
     assert "NCCL_B200_NET_INFLIGHT" in tool.stdout and "5" in tool.stdout
+
+
+TYPED = """
+import ctypes
+from nccl_b200 import _lib
+lib = _lib.load()
+h = ctypes.c_void_p()
+lib.ncclParamBind.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p]
+assert lib.ncclParamBind(ctypes.byref(h), b"NCCL_B200_NET_INFLIGHT") == 0
+for name, ct in (("I8", ctypes.c_int8), ("I16", ctypes.c_int16), ("I32", ctypes.c_int32), ("I64", ctypes.c_int64),
+                 ("U8", ctypes.c_uint8), ("U16", ctypes.c_uint16), ("U32", ctypes.c_uint32), ("U64", ctypes.c_uint64)):
+    fn = getattr(lib, "ncclParamGet" + name)
+    fn.argtypes = [ctypes.c_void_p, ctypes.POINTER(ct)]
+    v = ct()
+    assert fn(h, ctypes.byref(v)) == 0, name
+    assert v.value == 5, (name, v.value)
+assert lib.ncclParamBind(ctypes.byref(h), b"NCCL_SOCKET_IFNAME") == 0
+lib.ncclParamGetStr.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_char_p)]
+s = ctypes.c_char_p()
+assert lib.ncclParamGetStr(h, ctypes.byref(s)) == 0 and s.value == b"lo"
+buf = ctypes.create_string_buffer(16)
+n = ctypes.c_int()
+lib.ncclParamGet.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
+assert lib.ncclParamGet(h, buf, 16, ctypes.byref(n)) == 0
+print("raw", n.value, buf.raw[:max(n.value, 0)])
+"""
+
+
+def test_typed_getters():
+    out = _child(TYPED, {"NCCL_B200_NET_INFLIGHT": "5", "NCCL_SOCKET_IFNAME": "lo"})
+    assert out.startswith("raw")
+
+
+RELOAD = """
+import os, sys
+from nccl_b200 import _lib, Communicator, get_unique_id
+lib = _lib.load()
+path = sys.argv[1] if len(sys.argv) > 1 else os.environ["LOG_PATH"]
+c = Communicator(1, 0, get_unique_id())      # logging is off: nothing is written
+c.destroy()
+os.environ["NCCL_DEBUG"] = "INFO"
+os.environ["NCCL_DEBUG_FILE"] = path
+lib.ncclResetDebugInit()                      # re-reads the logging variables
+c = Communicator(1, 0, get_unique_id())
+c.destroy()
+print(os.path.exists(path) and "Init COMPLETE" in open(path).read())
+"""
+
+
+def test_reset_debug_init_rereads_the_environment(tmp_path):
+    out = _child(RELOAD, {"LOG_PATH": str(tmp_path / "log.txt"), "NCCL_B200_HOST_ONLY": "1", "NCCL_DEBUG": ""})
+    assert out.strip().endswith("True"), out
