@@ -133,6 +133,7 @@ struct ncclComm {
   std::mutex lock;
   int childCount = 0;
   uint64_t opCount = 0;
+  std::atomic<uintptr_t> launchOwner{0};   // thread that is issuing work on this communicator right now (0: none)
   ncclComm* parent = nullptr;
 
   // ncclCommInitAll: communicators created together in one process share a launch group

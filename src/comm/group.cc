@@ -80,12 +80,34 @@ static ncclResult_t runP2p(ncclComm* comm, const std::vector<Task>& p2p) {
   return r;
 }
 
+B200_PARAM(LaunchRaceFatal, "LAUNCH_RACE_FATAL", 1, "Two threads issuing work on one communicator at the same time: 1 = fail the later call, 0 = warn only");
+
+// One thread at a time may issue work on a communicator (reference: NCCL_LAUNCH_RACE_FATAL, src/misc/strongstream.cc).
+// The guard marks the communicator for the duration of the issue and notices a second thread.
+struct LaunchGuard {
+  ncclComm* comm;
+  bool owner = false, raced = false;
+  explicit LaunchGuard(ncclComm* c) : comm(c) {
+    static thread_local char token;
+    const uintptr_t me = (uintptr_t)&token;
+    uintptr_t expected = 0;
+    if (comm->launchOwner.compare_exchange_strong(expected, me, std::memory_order_acquire)) owner = true;
+    else if (expected != me) raced = true;
+  }
+  ~LaunchGuard() { if (owner) comm->launchOwner.store(0, std::memory_order_release); }
+};
+
 static ncclResult_t launchAll(std::vector<Task>& tasks, ncclSimInfo_t* sim) {
   // communicators in order of first appearance
   std::vector<ncclComm*> comms;
   for (auto& t : tasks) if (std::find(comms.begin(), comms.end(), t.comm) == comms.end()) comms.push_back(t.comm);
   float simUs = 0;
   for (ncclComm* comm : comms) {
+    LaunchGuard guard(comm);
+    if (guard.raced && !sim) {
+      WARN("communicator %p (rank %d) is being used by two threads at the same time; calls on one communicator must be serialised", (void*)comm, comm->rank);
+      if (paramLaunchRaceFatal()) return ncclInvalidUsage;
+    }
     std::vector<Task> p2p;
     float commUs = 0;
     for (auto& t : tasks) {

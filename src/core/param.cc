@@ -120,6 +120,8 @@ static ParamRegistrar kStrParams[] = {
     {{"NCCL_ENV_PLUGIN", PT_STR, "", "Environment plugin library name", true}},
     {{"NCCL_TUNING_FILE", PT_STR, "", "JSON table of measured algorithm crossover sizes", false}},
     {{"NCCL_SYM_KERNEL", PT_STR, "", "Force one symmetric kernel by name", true}},
+    {{"NCCL_PROXY_DUMP_SIGNAL", PT_STR, "", "Signal number on which proxy threads log their operations in flight", true}},
+    {{"NCCL_NET", PT_STR, "", "Insist on one network backend by name (a plugin's name, or Socket)", true}},
     {{"NCCL_PARAM_DUMP_ALL", PT_BOOL, "0", "Include undocumented parameters in ncclParamDumpAll", true}},
 };
 

@@ -5,6 +5,8 @@
 // through the bootstrap ring, lower ranks connect first to higher ones and accept afterwards.
 // Reference parity: src/proxy.cc (ncclProxySaveOp :602, progress loop :954, service thread
 // :1713), src/transport/net.cc (sendProxyProgress :1304-1468, recvProxyProgress :1470-1765).
+#include <signal.h>
+
 #include "net.h"
 
 #include <sched.h>
@@ -93,10 +95,37 @@ static ncclResult_t progressOp(Proxy* p, ProxyOp* op) {
 
 static bool opFinished(const ProxyOp* op) { return op->head == op->tail && op->posted >= op->bytes && (op->bytes > 0 || op->tail > 0); }
 
+// NCCL_PROXY_DUMP_SIGNAL=<signal number>: on that signal every proxy thread logs its operations in flight
+// (reference: ncclDumpProxyState, src/proxy.cc:920-965, installed for the same variable). The handler only
+// bumps a counter; the threads print from their own loop.
+static std::atomic<unsigned> gDumpRequests{0};
+static void proxyDumpHandler(int) { gDumpRequests.fetch_add(1, std::memory_order_relaxed); }
+static void proxyInstallDumpSignal() {
+  static std::once_flag once;
+  std::call_once(once, [] {
+    const char* e = getEnv("NCCL_PROXY_DUMP_SIGNAL");
+    const int sig = e && *e ? atoi(e) : -1;
+    if (sig <= 0) return;
+    struct sigaction sa;
+    memset(&sa, 0, sizeof(sa));
+    sa.sa_handler = proxyDumpHandler;
+    sa.sa_flags = SA_RESTART;
+    if (sigaction(sig, &sa, nullptr) == 0) INFO(SUB_PROXY | SUB_INIT, "proxy state dump on signal %d", sig);
+  });
+}
+static void proxyDump(Proxy* p, const std::vector<ProxyOp*>& active) {
+  WARN("proxy state of rank %d: %zu operation(s) in flight, %llu completed", p->comm->rank, active.size(), (unsigned long long)p->opsDone);
+  for (const ProxyOp* op : active)
+    WARN("  %s peer %d: %zu of %zu bytes posted, %zu completed, %d request(s) outstanding", op->isSend ? "send to" : "recv from", op->peer, op->posted,
+         op->bytes, op->completed, op->tail - op->head);
+}
+
 static void proxyMain(Proxy* p) {
   setThreadName("NCCL Proxy %d", p->comm->rank);
+  proxyInstallDumpSignal();
   std::vector<ProxyOp*> active;
   uint64_t idle = 0;
+  unsigned dumpsSeen = gDumpRequests.load(std::memory_order_relaxed);
   for (;;) {
     {
       std::unique_lock<std::mutex> lk(p->lock);
@@ -109,6 +138,8 @@ static void proxyMain(Proxy* p) {
       if (p->stop && active.empty()) return;
     }
     const bool aborted = p->comm->abortFlag && __atomic_load_n(p->comm->abortFlag, __ATOMIC_RELAXED);
+    const unsigned dumps = gDumpRequests.load(std::memory_order_relaxed);
+    if (dumps != dumpsSeen) { dumpsSeen = dumps; proxyDump(p, active); }
     bool progressed = false;
     // Two operations of one direction towards one peer share a byte stream: only the oldest may run.
     for (size_t i = 0; i < active.size();) {

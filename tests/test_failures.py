@@ -113,3 +113,40 @@ def test_abort_from_another_thread_unblocks_a_collective():
     status, code, dt = res[0]
     assert status == "error", res[0]
     assert dt < 2.5, "the blocked collective returned only after %.1f s" % dt
+
+
+def _two_threads_rank(rank, nranks, uid, fatal):
+    import threading
+    import time
+    import numpy as np
+    from nccl_b200 import Communicator
+    comm = Communicator(nranks, rank, uid)
+    x = np.full(1 << 16, rank + 1.0, dtype=np.float32)
+    second = {}
+    if rank == 1:
+        time.sleep(1.0)                      # keeps rank 0 inside its all-reduce for a second
+        comm.all_reduce(x)
+    else:
+        def late():
+            y = np.ones(16, dtype=np.float32)
+            try:
+                time.sleep(0.3)
+                if fatal:
+                    comm.all_reduce(y)       # refused: another thread is inside a call on this communicator
+                second["rc"] = "ok"
+            except Exception as e:           # noqa: BLE001
+                second["rc"] = str(e)
+        t = threading.Thread(target=late)
+        t.start()
+        comm.all_reduce(x)
+        t.join()
+    comm.destroy()
+    return float(x[0]), second.get("rc")
+
+
+def test_two_threads_on_one_communicator_are_detected():
+    """Calls on one communicator must be serialised: the later of two concurrent calls fails with ncclInvalidUsage
+    (NCCL_LAUNCH_RACE_FATAL=1, the default) and the first one completes normally."""
+    res = run_ranks(_two_threads_rank, 2, args=(True,), env=ENV, timeout=120)
+    assert res[0][0] == 3.0 and res[1][0] == 3.0
+    assert "ncclInvalidUsage" in res[0][1] and "two threads" in res[0][1], res[0][1]

@@ -145,3 +145,31 @@ def test_collective_network_plugin(tmp_path, enable):
             assert words.count("allreduce") == 2 and words.count("allgather") == 1 and words.count("reducescatter") == 1
     else:
         assert logs == []
+
+
+def _slow_peer_rank(rank, nranks, uid):
+    import os
+    import signal
+    import time
+    from nccl_b200 import Communicator
+    comm = Communicator(nranks, rank, uid)
+    x = np.full(1 << 20, rank + 1, dtype=np.float32)
+    if rank == 1:
+        time.sleep(1.5)                       # rank 0 sits in its all-reduce meanwhile
+    else:
+        import threading
+        threading.Timer(0.6, lambda: os.kill(os.getpid(), signal.SIGUSR1)).start()
+    comm.all_reduce(x)
+    comm.destroy()
+    return float(x[0])
+
+
+def test_proxy_state_dump_on_signal(tmp_path):
+    """NCCL_PROXY_DUMP_SIGNAL: a signal makes the proxy thread log the operations it has in flight."""
+    import signal
+    env = dict(BASE, NCCL_B200_HOST_NET="1", NCCL_PROXY_DUMP_SIGNAL=str(int(signal.SIGUSR1)), NCCL_DEBUG="WARN",
+               NCCL_DEBUG_FILE=str(tmp_path / "log.%p"))
+    res = run_ranks(_slow_peer_rank, 2, env=env, timeout=120)
+    assert res[0] == 3.0 and res[1] == 3.0
+    logs = "".join(open(os.path.join(tmp_path, p)).read() for p in os.listdir(tmp_path))
+    assert "proxy state of rank 0" in logs and "recv from peer 1" in logs
