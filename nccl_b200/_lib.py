@@ -10,7 +10,8 @@ import threading
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_HERE)
-LIB_PATH = os.path.join(_HERE, "lib", "libnccl_b200.so")
+# NCCL_B200_LIBRARY points the package at another build of the library (e.g. one made with `make SAN=address`).
+LIB_PATH = os.environ.get("NCCL_B200_LIBRARY") or os.path.join(_HERE, "lib", "libnccl_b200.so")
 
 _lock = threading.Lock()
 _lib = None

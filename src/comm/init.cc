@@ -388,6 +388,9 @@ ncclResult_t ncclCommAbort(ncclComm_t comm) {
   if (!commValid(comm)) return ncclInvalidArgument;
   if (comm->abortFlag) __atomic_store_n((uint32_t*)comm->abortFlag, 1u, __ATOMIC_SEQ_CST);
   if (comm->initThread && comm->initThread->joinable()) comm->initThread->join();
+  // A thread blocked inside a call on this communicator leaves it once it sees the flag; its objects must outlive it.
+  for (int ms = 0; comm->launchOwner.load(std::memory_order_acquire) != 0 && ms < 30000; ++ms) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+  if (comm->launchOwner.load(std::memory_order_acquire) != 0) WARN("ncclCommAbort: another thread is still inside a call on communicator %p after 30 s", (void*)comm);
   if (!comm->hostOnly && comm->devPlane) {
     int cur = -1;
     cudaGetDevice(&cur);
