@@ -35,6 +35,10 @@ typedef struct ncclTeam {
   int stride;
 } ncclTeam_t;
 
+/* Byte offset of a requested buffer inside the communicator's resource window. */
+typedef uint32_t ncclDevResourceHandle;
+typedef ncclDevResourceHandle ncclDevResourceHandle_t;
+
 /* Resources a kernel asks for when the device communicator is created. */
 typedef struct ncclDevResourceRequirements {
   struct ncclDevResourceRequirements* next;
@@ -130,6 +134,7 @@ ncclResult_t ncclDevCommDestroy(ncclComm_t comm, const ncclDevComm_t* devComm);
 /* Host-side pointer getters: where rank `peer`'s part of the window is mapped in this process. */
 ncclResult_t ncclGetLsaDevicePointer(ncclWindow_t win, size_t offset, int peer, void** out);
 ncclResult_t ncclGetLsaMultimemDevicePointer(ncclWindow_t win, size_t offset, void** out);
+ncclResult_t ncclGetPeerDevicePointer(ncclWindow_t win, size_t offset, int peer, void** out);
 /* The device copy of a window handle, to pass to kernels. */
 ncclResult_t ncclWinGetDeviceHandle(ncclWindow_t win, ncclWindow_t* devHandle);
 #ifdef __cplusplus
@@ -186,6 +191,12 @@ __device__ inline void* ncclGetLsaMultimemPointer(ncclWindow_t w, size_t offset,
 __device__ inline void* ncclGetResourceBufferLocalPointer(const ncclDevComm_t& c, uint32_t handle) { return (char*)c.resource.peerPtr[c.lsaRank] + handle; }
 __device__ inline void* ncclGetResourceBufferLsaPointer(const ncclDevComm_t& c, uint32_t handle, int peer) { return (char*)c.resource.peerPtr[peer] + handle; }
 __device__ inline void* ncclGetResourceBufferMultimemPointer(const ncclDevComm_t& c, uint32_t handle) { return c.resource.mcPtr ? (char*)c.resource.mcPtr + handle : (void*)0; }
+__device__ inline void* ncclGetResourceBufferLsaMultimemPointer(const ncclDevComm_t& c, ncclDevResourceHandle handle) { return ncclGetResourceBufferMultimemPointer(c, handle); }
+__device__ inline void* ncclGetResourceBufferPeerPointer(const ncclDevComm_t& c, ncclDevResourceHandle handle, ncclTeam_t team, int peer) {
+  return (char*)c.resource.peerPtr[c.lsaRank + (peer - team.rank) * team.stride] + handle;
+}
+__host__ __device__ inline size_t ncclGetResourceBufferOffset(ncclDevResourceHandle_t handle) { return handle; }
+__device__ inline void* ncclGetPeerPointer(ncclWindow_t w, size_t offset, int worldPeer) { return (char*)w->peerPtr[worldPeer] + offset; }
 #endif
 
 #endif

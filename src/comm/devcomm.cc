@@ -179,6 +179,9 @@ ncclResult_t ncclGetLsaMultimemDevicePointer(ncclWindow_t win, size_t offset, vo
   return ncclSuccess;
 }
 
+// World ranks and load/store ranks coincide: every rank of a device communicator is in one load/store team.
+ncclResult_t ncclGetPeerDevicePointer(ncclWindow_t win, size_t offset, int peer, void** outPtr) { return ncclGetLsaDevicePointer(win, offset, peer, outPtr); }
+
 ncclResult_t ncclWinGetDeviceHandle(ncclWindow_t win, ncclWindow_t* devHandle) {
   if (!win || !devHandle || win->magic != kWindowMagic) return ncclInvalidArgument;
   *devHandle = win->devSelf;

@@ -37,6 +37,9 @@ __global__ void teams(ncclDevComm devComm, int* out) {
   ncclTeam world = ncclTeamWorld(devComm), lsa = ncclTeamLsa(devComm), rail = ncclTeamRail(devComm);
   ncclTeam inner = ncclTeamInnerFactor(world, 2), outer = ncclTeamOuterFactor(world, 2);
   out[0] = ncclTeamRankToWorld(devComm, lsa, 0) + ncclTeamRankToLsa(devComm, world, world.rank) + ncclTeamRankToTeam(lsa, world, 0);
+  ncclDevResourceHandle_t h = 256;
+  out[2] = (int)ncclGetResourceBufferOffset(h) + (ncclGetResourceBufferPeerPointer(devComm, h, world, 0) != ncclGetResourceBufferLsaPointer(devComm, h, 0)) +
+           (ncclGetResourceBufferLsaMultimemPointer(devComm, h) != nullptr);
   out[1] = ncclTeamRankIsMember(inner, world, 1) + ncclTeamRankInDifference(world, inner, 0) + outer.nRanks + rail.nRanks;
 }
 
