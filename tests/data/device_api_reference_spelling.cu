@@ -43,6 +43,22 @@ __global__ void teams(ncclDevComm devComm, int* out) {
   out[1] = ncclTeamRankIsMember(inner, world, 1) + ncclTeamRankInDifference(world, inner, 0) + outer.nRanks + rail.nRanks;
 }
 
+__global__ void reduceCopy(ncclDevComm devComm, ncclWindow_t in, ncclWindow_t out, float* local, __nv_bfloat16* localH, size_t count) {
+  ncclCoopCta cta;
+  ncclTeam lsa = ncclTeamLsa(devComm);
+  ncclLsaReduceSumCopy<float>(cta, in, 0, out, 0, count, lsa);
+  ncclLsaReduceSumCopy<float>(cta, in, 0, out, 0, count, devComm);
+  ncclLsaReduceSum<float>(cta, in, 0, local, count, lsa);
+  ncclLsaCopy<float>(cta, local, out, 0, count, devComm);
+  ncclLsaReduceSumLsaCopy<__nv_bfloat16>(cta, [=](int i) { return (__nv_bfloat16*)ncclGetLsaPointer(in, 0, i); }, lsa.nRanks,
+                                         [=](int j) { return (__nv_bfloat16*)ncclGetLsaPointer(out, 0, j); }, lsa.nRanks, count);
+  ncclLocalReduceSum<__nv_bfloat16>(cta, [=](int i) { return localH + i * count; }, 2, localH, count);
+  ncclLocalCopy<float>(cta, local, [=](int j) { return local + (j + 1) * count; }, 2, count);
+  ncclSymPtr<float> src(in, 0), dst(out, 0);
+  ncclLsaReduceSumCopy<float>(cta, src, dst, count, lsa);
+  ncclMultimemReduceSumMultimemCopy<float>(cta, (float*)ncclGetMultimemPointer(in, 0), (float*)ncclGetMultimemPointer(out, 0), count);
+}
+
 int main() {
   ncclDevCommRequirements reqs = NCCL_DEV_COMM_REQUIREMENTS_INITIALIZER;
   reqs.lsaBarrierCount = 4;
