@@ -2,7 +2,7 @@
 
 ``nccl_b200.core`` wraps the C API (communicators, collectives, windows); ``nccl_b200.ops`` has
 symmetric tensors and the fused tensor-parallel / expert-parallel operators; ``nccl_b200.parallel``
-has the FSDP and pipeline drivers; ``nccl_b200.models`` the Llama-shaped model used by the benches.
+has the data-parallel, FSDP, pipeline and context-parallel drivers; ``nccl_b200.models`` the Llama-shaped model used by the benches.
 """
 from . import _lib  # noqa: F401
 from .core import (AVG, MAX, MIN, PROD, SUM, Communicator, get_unique_id, group, mem_alloc, mem_free,  # noqa: F401
