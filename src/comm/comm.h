@@ -132,7 +132,7 @@ struct ncclComm {
   std::vector<b200::UserRedOp> userOps;
   std::mutex lock;
   int childCount = 0;
-  uint64_t opCount = 0;
+  std::atomic<uint64_t> opCount{0};        // read by the RAS thread while the application issues work
   std::atomic<uintptr_t> launchOwner{0};   // thread that is issuing work on this communicator right now (0: none)
   ncclComm* parent = nullptr;
 
@@ -144,6 +144,7 @@ struct ncclComm {
 
 namespace b200 {
 
+inline bool flagSet(const volatile uint32_t* f) { return f && __atomic_load_n((const uint32_t*)f, __ATOMIC_ACQUIRE) != 0; }   // abort flags are written by other threads
 inline bool commValid(const ncclComm* c) { return c && c->startMagic == kCommMagic && c->endMagic == kCommMagic; }
 ncclResult_t commEnsureReady(ncclComm* c);  // waits for / reports the state of a non-blocking init
 

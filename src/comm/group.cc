@@ -36,7 +36,7 @@ ncclResult_t groupRunOrDefer(std::function<ncclResult_t()> fn) {
 static ncclResult_t runTask(ncclComm* comm, const Task& t) {
   comm->opCount++;
   INFO(SUB_COLL, "%s: opCount %llx sendbuff %p recvbuff %p count %zu datatype %d op %d root %d comm %p [nranks=%d] stream %p",
-       funcName(t.func), (unsigned long long)comm->opCount, t.send, t.recv, t.count, (int)t.type, t.op, t.root, (void*)comm,
+       funcName(t.func), (unsigned long long)comm->opCount.load(), t.send, t.recv, t.count, (int)t.type, t.op, t.root, (void*)comm,
        comm->nRanks, (void*)t.stream);
   if (comm->hostOnly) {
     if (comm->nRanks == 1) {

@@ -265,7 +265,7 @@ ncclResult_t commEnsureReady(ncclComm* c) {
   if (r == ncclInProgress) return ncclInProgress;
   if (r != ncclSuccess) return (ncclResult_t)r;
   if (c->revoked) { WARN("communicator was revoked"); return ncclInvalidUsage; }
-  if (c->abortFlag && *c->abortFlag) return ncclInternalError;
+  if (flagSet(c->abortFlag)) return ncclInternalError;
   return ncclSuccess;
 }
 

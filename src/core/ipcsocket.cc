@@ -78,7 +78,7 @@ ncclResult_t ipcRecvFd(IpcSocket* s, int* recvFd, IpcMsg* msg, volatile uint32_t
     struct pollfd p{s->fd, POLLIN, 0};
     int rc = poll(&p, 1, 50);
     if (rc > 0) break;
-    if (abortFlag && *abortFlag) return ncclInternalError;
+    if (abortFlag && __atomic_load_n((const uint32_t*)abortFlag, __ATOMIC_ACQUIRE)) return ncclInternalError;
     waited += 50;
     if (timeoutMs > 0 && waited >= timeoutMs) { WARN("UDS: timed out waiting for a descriptor"); return ncclTimeout; }
   }

@@ -154,7 +154,7 @@ std::string localCommsText() {
   for (auto& c : gRas.comms) {
     ncclComm* k = c.comm;
     const bool aborted = k->abortFlag && *k->abortFlag;
-    o << std::hex << c.hash << std::dec << ' ' << c.rank << ' ' << c.nRanks << ' ' << k->opCount << ' ' << k->asyncResult.load() << ' ' << (aborted ? 1 : 0)
+    o << std::hex << c.hash << std::dec << ' ' << c.rank << ' ' << c.nRanks << ' ' << k->opCount.load() << ' ' << k->asyncResult.load() << ' ' << (aborted ? 1 : 0)
       << ' ' << c.cudaDev << ' ' << (int)getpid() << ' ' << k->nNodes << '\n';
   }
   return o.str();

@@ -103,7 +103,7 @@ static ncclResult_t waitRequest(ncclComm* comm, CollNet* c, void* request) {
   while (!done) {
     NCCLCHECK(c->api->test(request, &done, nullptr));
     if (done) break;
-    if (comm->abortFlag && *comm->abortFlag) return ncclInternalError;
+    if (flagSet(comm->abortFlag)) return ncclInternalError;
     if (++spins > 1000) std::this_thread::sleep_for(std::chrono::microseconds(50));
   }
   return ncclSuccess;
@@ -115,7 +115,7 @@ static ncclResult_t postAndWait(ncclComm* comm, CollNet* c, Post post) {
   for (int tries = 0; !request; ++tries) {
     NCCLCHECK(post(&request));
     if (request) break;
-    if (comm->abortFlag && *comm->abortFlag) return ncclInternalError;
+    if (flagSet(comm->abortFlag)) return ncclInternalError;
     if (tries > 1000) std::this_thread::sleep_for(std::chrono::microseconds(50));
   }
   c->calls++;

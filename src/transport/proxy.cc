@@ -202,7 +202,7 @@ ncclResult_t proxyCreate(ncclComm* comm) {
       void* sc = nullptr;
       while (!sc) {
         NCCLCHECKGOTO(p->net->connect(p->netCtx, p->dev, handles.data() + (size_t)r * NCCL_NET_HANDLE_MAXSIZE, &sc, nullptr), res, fail);
-        if (comm->abortFlag && *comm->abortFlag) { res = ncclInternalError; goto fail; }
+        if (flagSet(comm->abortFlag)) { res = ncclInternalError; goto fail; }
       }
       p->sendComm[r] = sc;
       int hello = me, done = 0;
@@ -214,7 +214,7 @@ ncclResult_t proxyCreate(ncclComm* comm) {
       void* rc = nullptr;
       while (!rc) {
         NCCLCHECKGOTO(p->net->accept(p->listenComm, &rc, nullptr), res, fail);
-        if (comm->abortFlag && *comm->abortFlag) { res = ncclInternalError; goto fail; }
+        if (flagSet(comm->abortFlag)) { res = ncclInternalError; goto fail; }
       }
       int hello = -1, done = 0;
       void* req = nullptr;
