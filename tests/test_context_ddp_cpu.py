@@ -95,3 +95,17 @@ def test_ring_and_ulysses_attention(n, causal):
     for r in range(n):
         np.testing.assert_allclose(res[r][0], ref[:, :, r * S:(r + 1) * S], rtol=2e-4, atol=2e-5)
         np.testing.assert_allclose(res[r][1], ref[:, :, r * S:(r + 1) * S], rtol=2e-4, atol=2e-5)
+
+
+def test_example_script_runs_on_cpu_ranks():
+    """examples/train_ddp_ring_attention.py under torch.distributed.run with two CPU ranks."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NCCL_B200_HOST_ONLY="1", NCCL_SOCKET_IFNAME="lo", OMP_NUM_THREADS="2")
+    p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29631", os.path.join(root, "examples", "train_ddp_ring_attention.py")],
+                       env=env, capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    assert p.stdout.count("ring attention max error") == 2
