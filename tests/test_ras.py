@@ -70,7 +70,11 @@ def _dead_rank(rank, nranks, uid, port, done_file):
             if not raw:      # the process that served the client port has just gone; another one takes it over
                 time.sleep(0.3)
                 continue
-            rep = json.loads(raw)
+            try:
+                rep = json.loads(raw)
+            except ValueError:   # the serving process went away in the middle of a reply
+                time.sleep(0.3)
+                continue
             if rep["job"]["dead_processes"] >= 1:
                 out = rep
                 break
