@@ -113,3 +113,22 @@ TunePick tunePick(const TuningTable& t, int func, int n, size_t bytes) {
 }
 
 }  // namespace b200
+
+// Parses the built-in table and returns the number of (collective, rank count) cells it fills, or -1 when it does
+// not parse: lets a test without a GPU check the table that every GPU communicator loads.
+extern "C" __attribute__((visibility("default"))) int b200TuningDefaultsCheck() {
+  b200::TuningTable t;
+  if (!b200::tuneParse(&t, b200::kDefaultTuningJson)) return -1;
+  int cells = 0;
+  for (auto& coll : t.entries)
+    for (auto& rows : coll) {
+      if (rows.empty()) continue;
+      ++cells;
+      size_t last = 0;
+      for (auto& r : rows) {
+        if (r.upto <= last || r.ctas < 0 || r.ctas > 148) return -2;   // thresholds ascend, CTA counts fit the device
+        last = r.upto;
+      }
+    }
+  return cells;
+}

@@ -98,3 +98,8 @@ def test_binary_trees(lib):
                 if o[4] >= 0 or o[5] >= 0:
                     interior1.add(r)
             assert len(interior0 & interior1) <= 1, (n, interior0 & interior1)
+
+
+def test_builtin_selection_table_parses(lib):
+    """The measured selection table compiled into the library: five collectives for each of 2 to 8 ranks."""
+    assert lib.b200TuningDefaultsCheck() == 5 * 7
