@@ -360,12 +360,25 @@ ncclResult_t hostPlaneRun(ncclComm* comm, const Task& t) {
       if (n > 1) NCCLCHECK(ringAllGatherInPlace(comm, out, ch, es, 0));
     } break;
     case FUNC_BROADCAST: {
-      if (r == t.root) {
-        if (t.recv != t.send) memcpy(t.recv, t.send, t.count * es);
-        for (int p = 0; p < n; ++p) if (p != r) NCCLCHECK(exchange(hp, p, t.send, t.count * es, p, nullptr, 0));
-      } else {
-        NCCLCHECK(exchange(hp, t.root, nullptr, 0, t.root, t.recv, t.count * es));
+      // binomial tree rooted at t.root: in round k every rank that already has the data sends it 2^k positions on
+      const size_t bytes = t.count * es;
+      const int rel = (r - t.root + n) % n;
+      if (r == t.root && t.recv != t.send) memcpy(t.recv, t.send, bytes);
+      const void* have = r == t.root ? t.send : t.recv;
+      int mask = 1;
+      while (mask < n) {                      // receive from the parent: the lowest set bit of rel names it
+        if (rel & mask) {
+          const int parent = (r - mask + n) % n;
+          NCCLCHECK(exchange(hp, parent, nullptr, 0, parent, t.recv, bytes));
+          break;
+        }
+        mask <<= 1;
       }
+      for (mask >>= 1; mask > 0; mask >>= 1)   // then serve the children, farthest first
+        if (rel + mask < n) {
+          const int child = (r + mask) % n;
+          NCCLCHECK(exchange(hp, child, have, bytes, child, nullptr, 0));
+        }
     } break;
     case FUNC_REDUCE: {
       NCCLCHECK(resolveOp(comm, t, &od));

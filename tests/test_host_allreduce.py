@@ -128,3 +128,26 @@ def test_log_step_all_gather_and_reduce_scatter(nranks, algo):
         assert np.array_equal(g, np.concatenate(mines))
         assert np.array_equal(p, total[r * count:(r + 1) * count])
         assert np.allclose(a, (n + 1) / 2.0)
+
+
+def _bcast_rank(rank, nranks, uid):
+    import numpy as np
+    from nccl_b200 import Communicator
+    comm = Communicator(nranks, rank, uid)
+    out = []
+    for root in range(nranks):
+        buf = np.arange(5000, dtype=np.float32) + 100 * root if rank == root else np.zeros(5000, dtype=np.float32)
+        res = np.empty_like(buf)
+        comm.broadcast(buf, res, root)
+        out.append(res.copy())
+    comm.destroy()
+    return out
+
+
+@pytest.mark.parametrize("nranks", [2, 5, 8])
+def test_broadcast_from_every_root(nranks):
+    """The binomial-tree broadcast of the host plane delivers the root's data for every root and rank count."""
+    res = run_ranks(_bcast_rank, nranks, timeout=200)
+    for r in range(nranks):
+        for root in range(nranks):
+            assert np.array_equal(res[r][root], np.arange(5000, dtype=np.float32) + 100 * root)
