@@ -177,6 +177,49 @@ class Harness:
         us = e0.elapsed_time(e1) * 1000.0 / iters
         return self.d.max(us)
 
+    def time_host(self, coll, nbytes, dtype_code=FP32, iters=200):
+        """Host time per call in microseconds (max over ranks): how long the calling thread spends
+        inside the library per collective while the device queue is not full."""
+        import time as _time
+        sp = self.stream.cuda_stream
+        with torch.cuda.stream(self.stream):
+            self.d.barrier()
+            for _ in range(20):
+                _lib.check(self.call(coll, nbytes, dtype_code, sp), coll, self.lib)
+            self.stream.synchronize()
+            t0 = _time.perf_counter()
+            for _ in range(iters):
+                self.call(coll, nbytes, dtype_code, sp)
+            t1 = _time.perf_counter()
+            self.stream.synchronize()
+        return self.d.max((t1 - t0) * 1e6 / iters)
+
+    def time_graph(self, coll, nbytes, dtype_code=FP32, calls=50, replays=5):
+        """Mean device time per call when `calls` collectives are captured into one CUDA graph and
+        the graph is replayed: launch cost on the host no longer limits the rate."""
+        sp = self.stream.cuda_stream
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(self.stream):
+            self.d.barrier()
+            for _ in range(5):
+                _lib.check(self.call(coll, nbytes, dtype_code, sp), coll, self.lib)
+            self.stream.synchronize()
+        with torch.cuda.graph(g, stream=self.stream):
+            for _ in range(calls):
+                _lib.check(self.call(coll, nbytes, dtype_code, self.stream.cuda_stream), coll, self.lib)
+        with torch.cuda.stream(self.stream):
+            self.d.barrier()
+            g.replay()
+            self.stream.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(self.stream)
+            for _ in range(replays):
+                g.replay()
+            e1.record(self.stream)
+            self.stream.synchronize()
+        us = e0.elapsed_time(e1) * 1000.0 / (replays * calls)
+        return self.d.max(us)
+
     def close(self):
         torch.cuda.synchronize()
         for w in self.wins:
@@ -208,13 +251,15 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--coll", default="all_reduce", choices=COLLS)
     ap.add_argument("--dtype", default="fp32", choices=("fp32", "bf16"))
-    ap.add_argument("--min", type=int, default=8)
-    ap.add_argument("--max", type=int, default=1 << 30)
+    # (--min / --max also work when the module is not started through torchrun, whose own parser claims "--max")
+    ap.add_argument("--minbytes", "--min", dest="min", type=int, default=8)
+    ap.add_argument("--maxbytes", "--max", dest="max", type=int, default=1 << 30)
     ap.add_argument("--lib", default=None, help="path of another libnccl.so to measure instead of this package's library")
     ap.add_argument("--plain", action="store_true", help="cudaMalloc buffers instead of registered symmetric windows")
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--iters", type=int, default=100)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--latency", action="store_true", help="per size: host time per call, device time per call issued eagerly, and replayed from a CUDA graph")
     a = ap.parse_args(argv)
     d = Dist()
     lib = _lib.load(a.lib) if a.lib else _lib.load()
@@ -226,7 +271,20 @@ def main(argv=None):
     while s <= a.max:
         sizes.append(s)
         s *= 2
-    rows = sweep(h, a.coll, dt, sizes, a.warmup, a.iters)
+    if a.latency:
+        rows = []
+        es = TYPE_SIZE[dt]
+        unit = es * (h.n if a.coll in ("all_gather", "reduce_scatter", "all_to_all") else 1)
+        for nbytes in sizes:
+            nb = max(unit, nbytes // unit * unit)
+            row = {"bytes": nb, "eager_us": round(h.time(a.coll, nb, dt, a.warmup, a.iters), 2), "host_us": round(h.time_host(a.coll, nb, dt), 2)}
+            try:
+                row["graph_us"] = round(h.time_graph(a.coll, nb, dt), 2)
+            except Exception as ex:  # noqa: BLE001
+                row["graph_error"] = str(ex)[:120]
+            rows.append(row)
+    else:
+        rows = sweep(h, a.coll, dt, sizes, a.warmup, a.iters)
     h.close()
     if d.rank == 0:
         out = {"coll": a.coll, "dtype": a.dtype, "n_gpus": d.world, "lib": a.lib or "nccl_b200", "symmetric": not a.plain, "rows": rows}

@@ -9,6 +9,9 @@ using namespace b200;
 namespace b200 {
 
 extern int64_t paramCheckMode();
+// Pointer validation asks the driver about both buffers on every call (about a microsecond each):
+// off by default like the reference's NCCL_CHECK_POINTERS (src/init.cc, src/misc/argcheck.cc).
+B200_PARAM(CheckPointers, "CHECK_POINTERS", 0, "Validate send / receive pointers with the CUDA driver on every call")
 
 ncclResult_t argCheck(const Task& t, const char* opName) {
   ncclComm* comm = t.comm;
@@ -31,7 +34,7 @@ ncclResult_t argCheck(const Task& t, const char* opName) {
   const bool needRecv = !(t.func == FUNC_SEND || t.func == FUNC_PUTSIGNAL) && !((t.func == FUNC_REDUCE || t.func == FUNC_GATHER) && comm->rank != t.root);
   if (needSend && !t.send) { WARN("%s : sendbuff is NULL", opName); return ncclInvalidArgument; }
   if (needRecv && !t.recv) { WARN("%s : recvbuff is NULL", opName); return ncclInvalidArgument; }
-  if (!comm->hostOnly) {
+  if (!comm->hostOnly && paramCheckPointers()) {
     // pointers must be device-accessible memory of this communicator's device
     auto check = [&](const void* p, const char* what) -> ncclResult_t {
       cudaPointerAttributes attr;

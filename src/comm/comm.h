@@ -39,7 +39,8 @@ enum Algo : int {
   ALGO_TREE = 5,          // double binary tree over peer windows
   ALGO_CE = 6,            // copy engines (cudaMemcpyAsync + stream memory operations)
   ALGO_HOST = 7,          // staged through host memory and sockets
-  ALGO_COUNT = 8
+  ALGO_NVLS_ONESHOT = 8,  // all-reduce: every rank reads the whole vector with multimem.ld_reduce (small registered inputs)
+  ALGO_COUNT = 9
 };
 const char* algoName(int a);
 

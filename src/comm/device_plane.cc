@@ -25,9 +25,10 @@ B200_PARAM(P2pDisable, "P2P_DISABLE", 0, "Never map peer memory; GPU buffers are
 B200_PARAM(CopyThreads, "B200_COPY_THREADS", 512, "Threads per CTA of the local copy kernel")
 B200_PARAM(CopyUnroll, "B200_COPY_UNROLL", 4, "16-byte loads in flight per thread of the local copy kernel (4 or 8)")
 B200_PARAM(CopyCtasPerSm, "B200_COPY_CTAS_PER_SM", 16, "Grid size of the local copy kernel in CTAs per SM")
-B200_PARAM(LLMulticast, "B200_LL_MC_MIN_RANKS", 0, "Flagged-line all-reduce / all-gather publish each line with one multimem.st instead of one store per peer from this many ranks on (0 = never)")
+B200_PARAM(LLMulticast, "B200_LL_MC_MIN_RANKS", -1, "Flagged-line all-reduce / all-gather publish each line with one multimem.st instead of one store per peer from this many ranks on (0 = never, -1 = from the selection table)")
 B200_PARAM(CopyKernel, "B200_COPY_KERNEL", 0, "One-rank copy path: 0 = vector loads and stores, 1 = bulk-copy engines through shared memory (messages of 1 MiB and more)")
-B200_PARAM(LaunchPdl, "B200_PDL", 0, "Launch collectives with programmatic stream serialisation")
+B200_PARAM(LaunchPdl, "B200_PDL", 1, "Launch collectives with programmatic stream serialisation (the next kernel of the stream is scheduled while the previous one drains)")
+B200_PARAM(BarrierMulticast, "B200_BARRIER_MC_MIN_RANKS", -1, "Cross-GPU barriers arrive with one multimem.red on a multicast alias of the flag page from this many ranks on (0 = never, -1 = from the selection table)")
 
 // ------------------------------------------------------------------------------------ tuning
 void tuningDefaults(TuningTable* t) {
@@ -111,7 +112,11 @@ ncclResult_t devPlaneCreate(ncclComm* comm) {
   CUDACHECK(cudaGetDeviceProperties(&prop, comm->cudaDev));
   dp->smCount = prop.multiProcessorCount;
   dp->timeoutNs = (uint64_t)paramWaitTimeoutMs() * 1000000ull;
+  dp->barrierMcMin = paramBarrierMulticast() >= 0 ? (int)paramBarrierMulticast() : dp->tune.barrierMcMin;
+  dp->llMcMin = paramLLMulticast() >= 0 ? (int)paramLLMulticast() : dp->tune.llMcMin;
   CUDACHECK(cudaEventCreateWithFlags(&dp->lastEvent, cudaEventDisableTiming));
+  // function attributes are per device: set with this communicator's device current
+  CUDACHECK(cudaFuncSetAttribute(localBulkCopyKernelFn(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)localBulkCopySmemBytes()));
   const size_t privWords = kPrivWords + 2 * kMaxRanks * kSignalsPerPeer;
   CUDACHECK(cudaMalloc(&dp->priv, privWords * sizeof(uint32_t)));
   CUDACHECK(cudaMemset(dp->priv, 0, privWords * sizeof(uint32_t)));
@@ -228,6 +233,9 @@ static void fillSync(ncclComm* comm, SyncArgs* s) {
   s->status[comm->rank] = comm->devStatusDev;
   s->abortFlag = comm->abortFlagDev;
   s->timeoutNs = dp->timeoutNs;
+  // every rank takes the same decision: the multicast alias exists on all ranks or on none
+  if (dp->resWin->host.mcPtr && dp->barrierMcMin > 0 && comm->nRanks >= dp->barrierMcMin)
+    s->mcArrive = (uint32_t*)((char*)dp->resWin->host.mcPtr + kOffMcBarrier);
 }
 
 static void baseArgs(ncclComm* comm, CollArgs* a, int func) {
@@ -239,7 +247,7 @@ static void baseArgs(ncclComm* comm, CollArgs* a, int func) {
   fillSync(comm, &a->sync);
   for (int p = 0; p < comm->nRanks; ++p) a->ll[p] = (char*)dp->resWin->host.peerPtr[p] + dp->offLL;
   a->llEpoch[comm->rank] = dp->llEpoch;
-  if (dp->resWin->host.mcPtr && paramLLMulticast() && comm->nRanks >= paramLLMulticast()) a->llMc = (char*)dp->resWin->host.mcPtr + dp->offLL;
+  if (dp->resWin->host.mcPtr && dp->llMcMin > 0 && comm->nRanks >= dp->llMcMin) a->llMc = (char*)dp->resWin->host.mcPtr + dp->offLL;
 }
 
 // Peer-visible aliases of `ptr` when it lies in a symmetric window (same offset on every rank).
@@ -297,7 +305,7 @@ static bool capturing(cudaStream_t s) {
 }
 
 // Collectives of one communicator run one after the other even when issued on different streams.
-static ncclResult_t orderStreams(ncclComm* comm, cudaStream_t stream) {
+ncclResult_t devPlaneOrderStreams(ncclComm* comm, cudaStream_t stream) {
   DevicePlane* dp = comm->devPlane;
   if (dp->hasLast && dp->lastStream != stream && !capturing(stream) && !capturing(dp->lastStream)) {
     CUDACHECK(cudaEventRecord(dp->lastEvent, dp->lastStream));
@@ -351,6 +359,7 @@ static int forcedAlgo() {
   static const char* e = getEnv("NCCL_ALGO");
   if (!e || !*e) return ALGO_AUTO;
   if (!strcasecmp(e, "NVLS")) return ALGO_NVLS;
+  if (!strcasecmp(e, "NVLS1") || !strcasecmp(e, "NVLSOneShot")) return ALGO_NVLS_ONESHOT;
   if (!strcasecmp(e, "P2P") || !strcasecmp(e, "TwoShot") || !strcasecmp(e, "Direct")) return ALGO_P2P;
   if (!strcasecmp(e, "LL") || !strcasecmp(e, "OneShot")) return ALGO_LL_ONESHOT;
   if (!strcasecmp(e, "Ring")) return ALGO_RING;
@@ -405,6 +414,29 @@ static ncclResult_t runReduction(ncclComm* comm, const Task& t) {
       return launchColl(comm, llReduceKernelFn(t.type, op.red), &a, std::max(ctas, 1), t.stream, "ONESHOT", "LL");
     }
   }
+
+  // ---- one-shot through the switch: every rank reads the whole reduced vector with multimem.ld_reduce
+  // and stores it locally. No second phase and no remote store, so the closing barrier carries no
+  // release fence. The input must have a multicast alias; the output may be any local buffer, but not
+  // the input itself (a rank would overwrite what its peers are still reading).
+  // Reference parity: contrib/custom_algos/allreduce/oneshot_mc_allreduce_kernel.cuh.
+  if (forced == ALGO_NVLS_ONESHOT && t.func == FUNC_ALLREDUCE && !op.premul && nvlsReduceSupported(t.type, op.red) && bytes % 16 == 0) {
+    Aliases in = aliasesOf(comm, t.send, bytes);
+    const bool disjoint = (const char*)t.recv + bytes <= (const char*)t.send || (const char*)t.send + bytes <= (const char*)t.recv;
+    if (in.ok && in.mc && disjoint && aligned16(in, n) && ((uintptr_t)t.recv & 15) == 0) {
+      CollArgs a;
+      baseArgs(comm, &a, t.func);
+      a.scaleMode = op.scaleMode; a.scaleF = op.scaleF; a.scaleD = op.scaleD; a.intDiv = op.intDiv;
+      for (int r = 0; r < n; ++r) { a.sliceBegin[r] = 0; a.sliceCount[r] = total; a.dstOff[r] = 0; }
+      a.dstAll = 0;
+      a.sendMc = in.mc;
+      a.lrecv[me] = t.recv;
+      a.vec16 = 1;
+      int ctas = clampCtas(comm, bytes, dp->tune.nvlsCtas);
+      return launchColl(comm, reduceKernelFn(KERNEL_REDUCE_NVLS, t.type, op.red), &a, ctas, t.stream, "NVLS_ONESHOT");
+    }
+  }
+  if (forced == ALGO_NVLS_ONESHOT) forced = ALGO_NVLS;
 
   // ---- large: every rank reduces one slice, inputs must be peer-visible
   Aliases sendAl = op.premul ? Aliases{} : aliasesOf(comm, t.send, bytes);
@@ -632,11 +664,6 @@ static ncclResult_t runOneRank(ncclComm* comm, const Task& t) {
   if (src != dst) {
     ScaleArgs ca{src, dst, bytes, 0, nullptr};
     if (paramCopyKernel() == 1 && bytes >= (1u << 20) && (((uintptr_t)src | (uintptr_t)dst) & 15) == 0) {
-      static bool attrSet = false;
-      if (!attrSet) {
-        CUDACHECK(cudaFuncSetAttribute(localBulkCopyKernelFn(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)localBulkCopySmemBytes()));
-        attrSet = true;
-      }
       comm->devPlane->launches++;
       return launchKernel(localBulkCopyKernelFn(), dim3(comm->devPlane->smCount), dim3(32), localBulkCopySmemBytes(), &ca, t.stream, false);
     }
@@ -690,14 +717,14 @@ ncclResult_t devPlaneRun(ncclComm* comm, const Task& t, ncclSimInfo_t* sim) {
   tLastProto = "SIMPLE";
   tLastCtas = 0;
   if (t.func == FUNC_PUTSIGNAL || t.func == FUNC_SIGNAL || t.func == FUNC_WAITSIGNAL) {
-    r = orderStreams(comm, t.stream);
+    r = devPlaneOrderStreams(comm, t.stream);
     if (r == ncclSuccess) r = signalRun(comm, t);
   } else if (comm->nRanks == 1) {
     r = runOneRank(comm, t);
   } else if (!comm->lsaAll) {
     r = runViaHost(comm, t);
   } else {
-    r = orderStreams(comm, t.stream);
+    r = devPlaneOrderStreams(comm, t.stream);
     if (r == ncclSuccess) {
       switch (t.func) {
         case FUNC_ALLREDUCE: case FUNC_REDUCESCATTER: case FUNC_REDUCE: r = runReduction(comm, t); break;
@@ -754,7 +781,7 @@ ncclResult_t devPlaneRunP2pGroup(ncclComm* comm, const std::vector<Task>& tasks)
         if (remote[i]->func == FUNC_RECV) CUDACHECK(cudaMemcpy(remote[i]->recv, bufs[i].data(), bufs[i].size(), cudaMemcpyHostToDevice));
     goto out;
   }
-  res = orderStreams(comm, stream);
+  res = devPlaneOrderStreams(comm, stream);
   for (size_t first = 0; first < remote.size() && res == ncclSuccess; first += kMaxP2pOps) {
     size_t nOps = std::min<size_t>(kMaxP2pOps, remote.size() - first);
     P2pArgs a;
@@ -789,7 +816,7 @@ ncclResult_t devPlaneRunP2pGroup(ncclComm* comm, const std::vector<Task>& tasks)
       posted[o.isSend ? 0 : 1][o.peer] += (uint32_t)chunks;
     }
     dp->launches++;
-    res = launchKernel(p2pKernelFn(), dim3(cta), dim3(kCtaThreads), 0, &a, stream, false);
+    res = launchKernel(p2pKernelFn(), dim3(cta), dim3(kCtaThreads), 0, &a, stream, false, paramLaunchPdl() != 0);
   }
 out:
   if (cur != comm->cudaDev && cur >= 0) cudaSetDevice(cur);

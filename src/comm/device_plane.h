@@ -22,6 +22,8 @@ struct TuningTable {
   size_t rsLLMax[kMaxRanks + 1];       // reduce-scatter / reduce: flagged lines up to this many bytes per receiver
   size_t llCopyMax[kMaxRanks + 1];     // copy collectives: flagged lines up to this block size
   size_t ceMin;                        // copy-engine all-gather / all-to-all from this size (0 = never)
+  int llMcMin = 0;                     // flagged lines published by multimem.st from this many ranks on (0 = never)
+  int barrierMcMin = 0;                // barriers arrive by multimem.red from this many ranks on (0 = never)
   int nvlsCtas, p2pCtas, copyCtas, sendrecvCtas;
   size_t bytesPerCta;                  // grow the grid by one CTA per this many bytes
   std::vector<TuneEntry> entries[5][kMaxRanks + 1];   // measured rows per collective and rank count (sched/tuning.cc)
@@ -47,12 +49,17 @@ struct DevicePlane {
   size_t hostStageBytes = 0;
   uint64_t ceEpoch = 0;
   uint64_t launches = 0;              // kernels launched by this communicator
+  int barrierMcMin = 0;               // barriers arrive by multimem.red from this many ranks on (0 = never)
+  int llMcMin = 0;                    // flagged lines are published by multimem.st from this many ranks on (0 = never)
 };
 
 ncclResult_t devPlaneCreate(ncclComm* comm);
 void devPlaneDestroy(ncclComm* comm);
 ncclResult_t devPlaneRun(ncclComm* comm, const Task& t, ncclSimInfo_t* sim = nullptr);
 ncclResult_t devPlaneRunP2pGroup(ncclComm* comm, const std::vector<Task>& tasks);
+// Kernels of one communicator share its barrier slots and epochs, so they run one after the other even
+// when issued on different streams: makes `stream` wait for the communicator's previous launch.
+ncclResult_t devPlaneOrderStreams(ncclComm* comm, cudaStream_t stream);
 ncclResult_t devPlaneCheckStatus(ncclComm* comm);   // turns a kernel-side time-out into an async error
 void tuningDefaults(TuningTable* t);
 ncclResult_t tuningLoadFile(TuningTable* t, const char* path);

@@ -224,6 +224,8 @@ extern "C" int b200CommSetTuning(ncclComm_t comm, const char* name, int n, long 
   else if (k == "copyCtas") t.copyCtas = (int)value;
   else if (k == "sendrecvCtas") t.sendrecvCtas = (int)value;
   else if (k == "bytesPerCta") t.bytesPerCta = (size_t)value;
+  else if (k == "barrierMcMin") comm->devPlane->barrierMcMin = (int)value;
+  else if (k == "llMcMin") comm->devPlane->llMcMin = (int)value;
   else return 2;
   return 0;
 }

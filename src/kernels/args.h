@@ -26,17 +26,19 @@ constexpr size_t kOffP2pAck = kOffP2pReady + kMaxRanks * kP2pSlots * 4;         
 constexpr size_t kOffSignals = kOffP2pAck + kMaxRanks * kP2pSlots * 4;              // [src][kSignalsPerPeer] u64
 constexpr int kSignalsPerPeer = 64;
 constexpr size_t kOffSyncEnd = kOffSignals + kMaxRanks * kSignalsPerPeer * 8;
+constexpr size_t kOffMcBarrier = 13 << 10;                                          // [slot] u32: arrival counters of the multicast barrier
 constexpr size_t kOffRingFlags = 16 << 10;                                          // [slot][src] u32: ring step counters
 constexpr size_t kOffTreeFlags = 24 << 10;                                          // [slot][tree 2][src] u32: tree phase counters
 constexpr size_t kSyncPageBytes = 64 << 10;
-static_assert(kOffSyncEnd <= kOffRingFlags, "sync page overflow");
+static_assert(kOffSyncEnd <= kOffMcBarrier && kOffMcBarrier + kBarrierSlots * 4 <= kOffRingFlags, "sync page overflow");
 static_assert(kOffTreeFlags + kBarrierSlots * 2 * kMaxRanks * 4 <= kSyncPageBytes, "sync page overflow");
 // private per-rank words: barrier epochs | flagged-line epoch (4) | p2p sequence numbers | ring / tree step bases
 constexpr size_t kPrivLLEpoch = kBarrierSlots;
 constexpr size_t kPrivP2pSeq = kPrivLLEpoch + 4;
 constexpr size_t kPrivRingBase = kPrivP2pSeq + 2 * kMaxRanks + 4;
 constexpr size_t kPrivTreeBase = kPrivRingBase + kBarrierSlots;
-constexpr size_t kPrivWords = kPrivTreeBase + kBarrierSlots;
+constexpr size_t kPrivMcEpoch = kPrivTreeBase + kBarrierSlots;       // epochs of the multicast barrier, per slot
+constexpr size_t kPrivWords = kPrivMcEpoch + kBarrierSlots;
 
 constexpr size_t kLLDataBytes = 1 << 20;                     // largest payload of the flagged-line protocol
 constexpr size_t kLLLines = kLLDataBytes / 8;                // 8 payload bytes per 16-byte line
@@ -50,6 +52,7 @@ struct SyncArgs {
   uint32_t* inbox[kMaxRanks];     // inbox[p]: rank p's barrier inbox [slot][src]
   uint32_t* epoch[kMaxRanks];     // epoch[r]: rank r's private epoch counters [slot]
   uint32_t* status[kMaxRanks];    // status[r]: {code, kind, peer, expected} written on a failed wait
+  uint32_t* mcArrive;             // multicast alias of the barrier arrival counters [slot] (null: unicast barrier)
   const uint32_t* abortFlag;      // set by the host to make every wait give up
   unsigned long long timeoutNs;   // budget of one wait
 };

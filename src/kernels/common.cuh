@@ -76,6 +76,23 @@ __device__ __forceinline__ void mcSt16(void* mc, uint4 v) {
 __device__ __forceinline__ void mcRedAdd32(uint32_t* mc, uint32_t v) {
   asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
 }
+__device__ __forceinline__ void mcRedAdd32Relaxed(uint32_t* mc, uint32_t v) {
+  asm volatile("multimem.red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+}
+
+// ------------------------------------------------------------------ programmatic dependent launch
+// Collective kernels are launched with programmatic stream serialisation: the grid may be scheduled
+// while the previous kernel of the stream is still draining, which hides the launch latency between
+// back-to-back collectives. pdlWait() returns once every earlier grid of the stream has completed
+// and its writes are visible; nothing that an earlier kernel may have written (epoch words, user
+// buffers) is read before it. pdlLaunchDependents() lets the next grid be scheduled from then on
+// (it still waits for this grid's completion in its own pdlWait()). Both are no-ops for a grid
+// launched without the attribute.
+// Reference parity: cudaGridDependencySynchronize at the top of every symmetric kernel
+// (src/device/symmetric/generate.py:171-222), launch attribute in src/enqueue.cc:1753-1851.
+__device__ __forceinline__ void pdlWait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdlLaunchDependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdlEnter() { pdlWait(); pdlLaunchDependents(); }
 
 // ------------------------------------------------------------------ bounded waits
 // A wait polls until `done()` holds, the host raises the abort flag, or the time budget runs
@@ -116,14 +133,21 @@ __device__ __forceinline__ bool boundedWait(const WaitCtx& w, uint32_t kind, uin
 }
 
 // ------------------------------------------------------------------ cross-GPU CTA barrier
-// CTA `slot` of every rank meets CTA `slot` of every other rank. Thread t (< nRanks) of the
-// CTA signals peer t with a release store of the new epoch into the peer's inbox and then
-// polls its own inbox for that peer's epoch. Epoch counters are private per rank and per
-// slot and persist across launches, so a CUDA-graph replay needs no host-side state.
+// CTA `slot` of every rank meets CTA `slot` of every other rank. Two forms:
+//   unicast    thread t (< nRanks) of the CTA signals peer t with a store of the new epoch into
+//              the peer's inbox and then polls its own inbox for that peer's epoch;
+//   multicast  (when the sync page has a multicast alias) one thread adds 1 to the slot's arrival
+//              counter on every rank with a single multimem.red and polls its own copy until it
+//              shows nRanks arrivals per barrier so far (reference:
+//              nccl_device/impl/lsa_barrier__funcs.h:58-66, 100-115).
+// Epoch counters are private per rank, per slot and per form and persist across launches, so a
+// CUDA-graph replay needs no host-side state.
 struct CtaBarrier {
   WaitCtx w;
   uint32_t* const* inbox;
   uint32_t* epochPtr;
+  uint32_t* mcArrive;     // multicast address of this slot's arrival counter, or null
+  const uint32_t* mcMine; // this rank's copy of that counter
   int rank, nRanks, slot;
   uint32_t epoch;
 
@@ -134,7 +158,9 @@ struct CtaBarrier {
     rank = rank_;
     nRanks = nRanks_;
     slot = slot_;
-    epochPtr = s.epoch[rank_] + slot_;
+    mcArrive = s.mcArrive ? s.mcArrive + slot_ : nullptr;
+    mcMine = s.mcArrive ? (const uint32_t*)((const char*)s.inbox[rank_] + kOffMcBarrier) + slot_ : nullptr;
+    epochPtr = s.epoch[rank_] + (s.mcArrive ? kPrivMcEpoch : 0) + slot_;
     epoch = *epochPtr;  // every thread reads the same value; written back by finish()
   }
   // All threads of the CTA must call.
@@ -151,7 +177,15 @@ struct CtaBarrier {
     __syncthreads();
     bool ok = true;
     int t = threadIdx.x;
-    if (t < nRanks && t != rank) {
+    if (mcArrive) {
+      if (t == 0) {
+        if (release) mcRedAdd32(mcArrive, 1u); else mcRedAdd32Relaxed(mcArrive, 1u);
+        const uint32_t want = epoch * (uint32_t)nRanks;   // arrivals of all barriers so far on this slot, modulo 2^32
+        const uint32_t* mine = mcMine;
+        ok = boundedWait(w, WAIT_BARRIER, (uint32_t)rank, want, [&] { return (int32_t)(ldRelaxedSys(mine) - want) >= 0; });
+        if (acquire) fenceSys();
+      }
+    } else if (t < nRanks && t != rank) {
       if (release) fenceSys();
       stRelaxedSys(inbox[t] + (size_t)slot * kMaxRanks + rank, epoch);
       const uint32_t* mine = inbox[rank] + (size_t)slot * kMaxRanks + t;

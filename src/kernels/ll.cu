@@ -48,8 +48,12 @@ struct LLCtx {
   __device__ __forceinline__ void end(const CollArgs& a, const WaitCtx& w, int rank, unsigned ackTo, unsigned ackFrom) {
     __syncthreads();
     if (threadIdx.x == 0) {
-      __threadfence();
-      uint32_t done = atomicAdd(&ep[1], 1u);
+      // a grid of one CTA (the smallest messages) has nobody to count
+      uint32_t done = 0;
+      if (gridDim.x > 1) {
+        __threadfence();
+        done = atomicAdd(&ep[1], 1u);
+      }
       if (done == gridDim.x - 1) {
         const uint32_t e = epoch;
         for (int p = 0; p < a.nRanks; ++p)
@@ -63,6 +67,34 @@ struct LLCtx {
         ep[0] = epoch;
       }
     }
+  }
+  // Lines of all sources for one position, loaded together: the loads are independent, so a
+  // receiver pays one trip to memory instead of one per source; only lines that have not landed
+  // yet are polled again.
+  template <typename F>
+  __device__ __forceinline__ bool recvLines(const CollArgs& a, const WaitCtx& w, int rank, size_t l, uint64_t own, F&& consume) const {
+    const uint32_t e = epoch;
+    uint4 v[kMaxRanks];
+#pragma unroll
+    for (int s = 0; s < kMaxRanks; ++s)
+      if (s < a.nRanks && s != rank) v[s] = ldVolatile16(region(a, rank, s) + l * 16);
+    bool ok = true;
+#pragma unroll
+    for (int s = 0; s < kMaxRanks; ++s) {
+      if (s >= a.nRanks) break;
+      uint64_t d = own;
+      if (s != rank) {
+        if (v[s].y != e || v[s].w != e) {
+          const char* slot = region(a, rank, s) + l * 16;
+          uint4 r = v[s];
+          ok = ok && boundedWait(w, WAIT_LL, (uint32_t)s, e, [&] { r = ldVolatile16(slot); return r.y == e && r.w == e; });
+          v[s] = r;
+        }
+        d = (uint64_t)v[s].x | ((uint64_t)v[s].z << 32);
+      }
+      if (ok) consume(s, d);
+    }
+    return ok;
   }
   __device__ __forceinline__ bool recvLine(const WaitCtx& w, const char* slot, int src, uint64_t* d) const {
     uint4 v = ldVolatile16(slot);
@@ -80,6 +112,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) llReduceKernel(const __grid_co
   const int rank = ctaRank(a.emu, a.rank);
   const int n = a.nRanks;
   constexpr int N = 8 / sizeof(T);
+  pdlEnter();
   LLCtx ll;
   ll.begin(a, rank);
   WaitCtx w{&a.sync, a.sync.status[rank]};
@@ -118,11 +151,8 @@ __global__ void __launch_bounds__(kCtaThreads, 1) llReduceKernel(const __grid_co
     for (size_t l = tid; l < nLines && ok; l += stride) {
       const size_t valid = bytes - l * 8;
       typename Elem<T>::Acc acc[N];
-      for (int s = 0; s < n && ok; ++s) {
-        uint64_t d;
-        if (s == rank) d = llLoad8(own + l * 8, valid);
-        else ok = ll.recvLine(w, ll.region(a, rank, s) + l * 16, s, &d);
-        if (!ok) break;
+      // sources are folded in rank order whatever order their lines arrived in
+      ok = ll.recvLines(a, w, rank, l, llLoad8(own + l * 8, valid), [&](int s, uint64_t d) {
         union { uint64_t u; T e[N]; } cv;
         cv.u = d;
 #pragma unroll
@@ -130,7 +160,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) llReduceKernel(const __grid_co
           typename Elem<T>::Acc x = Elem<T>::ld(cv.e[k]);
           acc[k] = s == 0 ? x : redApply<OP>(acc[k], x);
         }
-      }
+      });
       if (!ok) break;
       union { uint64_t u; T e[N]; } res;
 #pragma unroll
@@ -150,6 +180,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) llReduceKernel(const __grid_co
 __global__ void __launch_bounds__(kCtaThreads, 1) llCopyKernel(const __grid_constant__ CollArgs a) {
   const int rank = ctaRank(a.emu, a.rank);
   const int n = a.nRanks;
+  pdlEnter();
   LLCtx ll;
   ll.begin(a, rank);
   WaitCtx w{&a.sync, a.sync.status[rank]};

@@ -37,12 +37,16 @@ __global__ void __launch_bounds__(kCtaThreads, 1) noAllocAllReduceKernel(const _
   const int n = a.nRanks;
   constexpr int N = 8 / sizeof(T);
   unsigned char* mine = a.scratch + (size_t)rank * kNaRankBytes;
-  uint32_t* ctrl = (uint32_t*)(mine + kNaRegionBytes);   // [0] epoch, [1] finished CTAs, [16..19] status
+  uint32_t* ctrl = (uint32_t*)(mine + kNaRegionBytes);   // [16..19] status record of this rank
+  // One epoch for the whole call, kept in the control block of rank 0 whatever nRanks is: every
+  // CTA of the grid reads it here and the last CTA of the grid to finish publishes the next value.
+  // (An epoch per rank would let ranks that sat out a call with fewer ranks fall behind.)
+  uint32_t* call = (uint32_t*)(a.scratch + kNaRegionBytes);   // [0] epoch, [1] finished CTAs
   SyncArgs sync;
   sync.abortFlag = nullptr;
   sync.timeoutNs = a.timeoutNs;
   WaitCtx w{&sync, ctrl + 16};
-  uint32_t epoch = ctrl[0] + 1;
+  uint32_t epoch = call[0] + 1;
   if (epoch == 0) epoch = 1;
   const int parity = epoch & 1;
   const size_t bytes = a.count * sizeof(T);
@@ -100,10 +104,10 @@ __global__ void __launch_bounds__(kCtaThreads, 1) noAllocAllReduceKernel(const _
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
-    uint32_t done = atomicAdd(&ctrl[1], 1u);
-    if (done == gridDim.x - 1) {
-      ctrl[1] = 0;
-      ctrl[0] = epoch;
+    uint32_t done = atomicAdd(&call[1], 1u);
+    if (done == gridDim.x * gridDim.y - 1) {
+      call[1] = 0;
+      call[0] = epoch;
     }
   }
 }
@@ -120,8 +124,8 @@ extern "C" ncclResult_t b200NoAllocAllReduce(int nRanks, ncclDataType_t type, si
   if (nRanks < 1 || nRanks > B200_NOALLOC_MAX_RANKS) { WARN("b200NoAllocAllReduce: nRanks %d is outside [1, %d]", nRanks, B200_NOALLOC_MAX_RANKS); return ncclInvalidArgument; }
   if (type != ncclFloat32 && type != ncclFloat16 && type != ncclBfloat16) { WARN("b200NoAllocAllReduce: only fp32, fp16 and bf16 are supported"); return ncclInvalidArgument; }
   const size_t es = type == ncclFloat32 ? 4 : 2;
-  if (count * es > B200_NOALLOC_MAX_BYTES) {
-    WARN("b200NoAllocAllReduce: %zu bytes per buffer exceed the fixed scratch (limit %d bytes)", count * es, B200_NOALLOC_MAX_BYTES);
+  if (count > B200_NOALLOC_MAX_BYTES / es) {   // compared in elements: count * es could wrap
+    WARN("b200NoAllocAllReduce: %zu elements of %zu bytes per buffer exceed the fixed scratch (limit %d bytes)", count, es, B200_NOALLOC_MAX_BYTES);
     return ncclInvalidArgument;
   }
   if (!send || !recv) return ncclInvalidArgument;

@@ -19,13 +19,16 @@
 //     library image, so every GPU on which a process has loaded this library holds it until the
 //     process exits, whether or not this function is ever called.
 //   * First call on a device: looks up the device address of the array (cudaGetSymbolAddress, with
-//     that device current) and caches it per device. Make that first call outside any stream
-//     capture.
+//     that device current) and caches it per device; that first call should come before any
+//     stream capture. Every call, the first included, also synchronises `stream` and reads the
+//     status words back with a blocking copy before it returns (see below).
 //   * Every call uses the same array, which still holds whatever the previous call left there.
 //     The words that must start at zero (the status record) are cleared on `stream` before the
 //     launch; the flagged lines are never cleared because each call tags its lines with a new
-//     epoch kept in the array. Two calls that overlap on the GPU (different streams, or two host
-//     threads) race on the array: callers must serialise calls per device.
+//     epoch kept in the array (one epoch word for the whole call, shared by all ranks, so calls
+//     with different nRanks can follow each other in any order). Two calls that overlap on the
+//     GPU (different streams, or two host threads) race on the array: callers must serialise
+//     calls per device.
 //   * The call returns after the kernel has finished (it synchronises `stream`) so that a wait
 //     that ran out of time is reported by this call: ncclTimeout, with the context still usable.
 //   * It calls no cudaMalloc, cudaFree, or any library routine that allocates.

@@ -17,6 +17,7 @@ template <typename T, int OP>
 __global__ void __launch_bounds__(kCtaThreads, 1) reduceP2pKernel(const __grid_constant__ CollArgs a) {
   const int rank = ctaRank(a.emu, a.rank);
   const int n = a.nRanks;
+  pdlEnter();
   CtaBarrier bar;
   bar.init(a.sync, rank, n, blockIdx.x);
   bool ok = bar.sync(false, false);  // inputs of every rank are final (written by earlier kernels); outputs may be overwritten
@@ -74,7 +75,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) reduceP2pKernel(const __grid_c
       for (int q = 0; q < nDst; ++q) ((T*)dstOf(q))[e] = r;
     }
   }
-  bar.sync(true, false);  // results have landed everywhere; nobody reads this rank's input any more
+  bar.sync(a.dstAll != 0, false);  // results have landed everywhere (release only when peers were written); nobody reads this rank's input any more
   bar.finish();
 }
 
@@ -142,6 +143,7 @@ MC_S64(double, RED_SUM, "add.f64", "=l")
 template <typename T, int OP>
 __global__ void __launch_bounds__(kCtaThreads, 1) reduceNvlsKernel(const __grid_constant__ CollArgs a) {
   const int rank = a.rank;
+  pdlEnter();
   CtaBarrier bar;
   bar.init(a.sync, rank, a.nRanks, blockIdx.x);
   bool ok = bar.sync(false, false);
@@ -154,25 +156,29 @@ __global__ void __launch_bounds__(kCtaThreads, 1) reduceNvlsKernel(const __grid_
       const size_t nPacks = cnt / N;
       const size_t stride = (size_t)gridDim.x * blockDim.x;
       const bool scale = a.scaleMode != SCALE_NONE;
-      size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-      for (; i + 3 * stride < nPacks; i += 4 * stride) {
-        uint4 v[4];
+      // Eight independent multimem loads per thread and round (tails predicated, not peeled): the
+      // switch round trip is long, and a few CTAs with deep queues keep the links as busy as many
+      // CTAs with shallow ones while their barriers cost less.
+      constexpr int U = 8;
+      for (size_t base = (size_t)blockIdx.x * blockDim.x + threadIdx.x; base < nPacks; base += (size_t)U * stride) {
+        uint4 v[U];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) v[u] = McRed<T, OP>::ld(src + (i + u * stride) * 16);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (scale) { PackAcc<T, OP> acc; acc.set(v[u]); v[u] = acc.get(a.scaleMode, a.scaleF, a.scaleD, a.intDiv); }
-          if (a.dstAll) mcSt16(dst + (i + u * stride) * 16, v[u]); else st16(dst + (i + u * stride) * 16, v[u]);
+        for (int u = 0; u < U; ++u) {
+          const size_t i = base + (size_t)u * stride;
+          if (i < nPacks) v[u] = McRed<T, OP>::ld(src + i * 16);
         }
-      }
-      for (; i < nPacks; i += stride) {
-        uint4 v = McRed<T, OP>::ld(src + i * 16);
-        if (scale) { PackAcc<T, OP> acc; acc.set(v); v = acc.get(a.scaleMode, a.scaleF, a.scaleD, a.intDiv); }
-        if (a.dstAll) mcSt16(dst + i * 16, v); else st16(dst + i * 16, v);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const size_t i = base + (size_t)u * stride;
+          if (i < nPacks) {
+            if (scale) { PackAcc<T, OP> acc; acc.set(v[u]); v[u] = acc.get(a.scaleMode, a.scaleF, a.scaleD, a.intDiv); }
+            if (a.dstAll) mcSt16(dst + i * 16, v[u]); else st16(dst + i * 16, v[u]);
+          }
+        }
       }
     }
   }
-  bar.sync(true, false);
+  bar.sync(a.dstAll != 0, false);   // only results stored to peers need a release; otherwise: "I have read your input"
   bar.finish();
 }
 

@@ -49,8 +49,9 @@ ncclResult_t memResume(ncclComm* comm) {
   if (cur != comm->cudaDev) CUDACHECK(cudaSetDevice(comm->cudaDev));
   NCCLCHECK(memAlloc(&dp->resBase, dp->resSize, comm->cudaDev));
   CUDACHECK(cudaMemset(dp->resBase, 0, dp->offMailbox));
-  // epochs restart together with the flags they are compared against
-  const size_t privWords = kPrivWords;
+  // epochs, sequence numbers and the consumed-signal table restart together with the flags and
+  // counters of the new window they are compared against (same extent as devPlaneCreate allocates)
+  const size_t privWords = kPrivWords + 2 * kMaxRanks * kSignalsPerPeer;
   CUDACHECK(cudaMemset(dp->priv, 0, privWords * sizeof(uint32_t)));
   CUDACHECK(cudaDeviceSynchronize());
   NCCLCHECK(symWindowRegister(comm, dp->resBase, dp->resSize, &dp->resWin, NCCL_WIN_COLL_SYMMETRIC));

@@ -30,8 +30,8 @@ int tuneCollOfFunc(int func) {
   }
 }
 
-// Grammar: { "<n>": { "<coll>": [ [upto, "ALGO", ctas], ... ], ... }, ... }  with ALGO in
-// LL, P2P, NVLS, PUSH, PULL, MC.
+// Grammar: { "<n>": { "<coll>": [ [upto, "ALGO", ctas], ... ], ... }, ..., "<switch>": number, ... }  with ALGO in
+// LL, P2P, NVLS, NVLS1, PUSH, PULL, MC.
 struct Cursor {
   const char* p;
   void ws() { while (*p && isspace((unsigned char)*p)) ++p; }
@@ -63,7 +63,18 @@ bool tuneParse(TuningTable* t, const std::string& json) {
     std::string nKey;
     if (!c.str(&nKey)) break;
     int n = atoi(nKey.c_str());
-    if (!c.eat(':') || !c.eat('{')) return false;
+    if (!c.eat(':')) return false;
+    if (!isdigit((unsigned char)nKey[0])) {
+      // global switch: "llMcMin": 8, "barrierMcMin": 4, "ceMin": bytes
+      long long v;
+      if (!c.num(&v)) return false;
+      if (nKey == "llMcMin") t->llMcMin = (int)v;
+      else if (nKey == "barrierMcMin") t->barrierMcMin = (int)v;
+      else if (nKey == "ceMin") t->ceMin = (size_t)v;
+      if (!c.eat(',')) break;
+      continue;
+    }
+    if (!c.eat('{')) return false;
     while (true) {
       std::string coll;
       if (!c.str(&coll)) break;
@@ -77,6 +88,7 @@ bool tuneParse(TuningTable* t, const std::string& json) {
         TuneEntry e{(size_t)upto, ALGO_P2P, -1, (int)ctas};
         if (algo == "LL") e.algo = ALGO_LL_ONESHOT;
         else if (algo == "NVLS") e.algo = ALGO_NVLS;
+        else if (algo == "NVLS1") e.algo = ALGO_NVLS_ONESHOT;
         else if (algo == "MC") { e.algo = ALGO_NVLS; e.mode = MODE_MC; }
         else if (algo == "PUSH") e.mode = MODE_PUSH;
         else if (algo == "PULL") e.mode = MODE_PULL;

@@ -93,11 +93,6 @@ static void fillSyncTp(ncclComm* comm, SyncArgs* s) {
 // tiles); in all-gather mode the last CTAs are the comm CTAs. The CTA-pair kernel runs when enabled,
 // when its clusters fit and when every rank's rows split into 256-row tiles.
 static ncclResult_t launchGemm(ncclTpContext* tp, const void* A, const void* W, TpGemmArgs* a, cudaStream_t stream) {
-  static bool attrSet = false;
-  if (!attrSet) {
-    CUDACHECK(cudaFuncSetAttribute(tpGemmKernelFn(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tpGemmSmemBytes()));
-    attrSet = true;
-  }
   const int n = a->nRanks;
   const bool fused = n > 1 && a->mode != TP_MODE_STORE;
   const bool gather = fused && a->mode == TP_MODE_GATHER;
@@ -131,11 +126,6 @@ static ncclResult_t launchGemm(ncclTpContext* tp, const void* A, const void* W, 
 }
 
 static ncclResult_t launchGemmFp8(ncclTpContext* tp, const void* A, const void* W, TpGemmArgs* a, int grid, cudaStream_t stream) {
-  static bool attrSet = false;
-  if (!attrSet) {
-    CUDACHECK(cudaFuncSetAttribute(tpGemmFp8KernelFn(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tpGemmFp8SmemBytes()));
-    attrSet = true;
-  }
   CUtensorMap tmA, tmB;
   NCCLCHECK(makeMap(&tmA, A, a->M, a->K, 128, 1));
   NCCLCHECK(makeMap(&tmB, W, a->N, a->K, 256, 1));
@@ -199,6 +189,7 @@ ncclResult_t ncclTpGemmReduceScatterFp8(ncclTp_t tp, const void* A, const float*
   const int n = comm->nRanks;
   NCCLCHECK(checkShapeFp8(M, N, K, n));
   NCCLCHECK(devPlaneCheckStatus(comm));
+  if (n > 1) NCCLCHECK(devPlaneOrderStreams(comm, stream));   // the fused kernels use the communicator's barrier slots: one kernel of a communicator at a time
   if (n == 1) return ncclTpGemmFp8(tp, A, scaleA, W, scaleW, out, M, N, K, stream);
   const size_t need = (size_t)M * N * 2;
   if (need > tp->accumBytes) { WARN("ncclTpGemmReduceScatterFp8: %d x %d exceeds the context's staging window", M, N); return ncclInvalidArgument; }
@@ -280,6 +271,9 @@ ncclResult_t ncclTpCreate(ncclComm_t comm, size_t maxRows, size_t maxCols, ncclT
   CUDACHECK(cudaGetDevice(&cur));
   if (cur != comm->cudaDev) CUDACHECK(cudaSetDevice(comm->cudaDev));
   CUDACHECK(cudaDeviceGetAttribute(&tp->smCount, cudaDevAttrMultiProcessorCount, comm->cudaDev));
+  // function attributes are per device: set them here, with this context's device current, not once per process
+  CUDACHECK(cudaFuncSetAttribute(tpGemmKernelFn(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tpGemmSmemBytes()));
+  CUDACHECK(cudaFuncSetAttribute(tpGemmFp8KernelFn(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tpGemmFp8SmemBytes()));
   {
     // how many clusters of two CTAs of the pair kernel the device can hold at once: the grid never exceeds it,
     // because its CTAs wait for one another (comm CTAs, cross-GPU barriers)
@@ -369,6 +363,7 @@ ncclResult_t ncclTpGemmReduceScatter(ncclTp_t tp, const void* A, const void* W, 
   const int n = comm->nRanks;
   NCCLCHECK(checkShape(M, N, K, n));
   NCCLCHECK(devPlaneCheckStatus(comm));
+  if (n > 1) NCCLCHECK(devPlaneOrderStreams(comm, stream));   // the fused kernels use the communicator's barrier slots: one kernel of a communicator at a time
   if (n == 1) return ncclTpGemm(tp, A, W, out, M, N, K, stream);
   const size_t need = (size_t)M * N * 2;
   if (need > tp->accumBytes) { WARN("ncclTpGemmReduceScatter: %d x %d exceeds the context's staging window", M, N); return ncclInvalidArgument; }
@@ -397,6 +392,7 @@ ncclResult_t ncclTpAllGatherGemm(ncclTp_t tp, void* gatheredA, const void* W, vo
   const int n = comm->nRanks;
   NCCLCHECK(checkShape(M, N, K, n));
   NCCLCHECK(devPlaneCheckStatus(comm));
+  if (n > 1) NCCLCHECK(devPlaneOrderStreams(comm, stream));   // the fused kernels use the communicator's barrier slots: one kernel of a communicator at a time
   if (n == 1) return ncclTpGemm(tp, gatheredA, W, C, M, N, K, stream);
   auto it = tp->gathered.find(gatheredA);
   if (it == tp->gathered.end() || !it->second) { WARN("ncclTpAllGatherGemm: the activation buffer must come from ncclTpAllocGathered"); return ncclInvalidArgument; }

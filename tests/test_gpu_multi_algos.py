@@ -33,6 +33,75 @@ def test_flagged_lines_with_multicast_stores():
     _check(res, n)
 
 
+@pytest.mark.parametrize("algo", ["NVLS1", "NVLS", "P2P", ""])
+def test_barriers_through_multicast(algo):
+    """Barrier kernels arrive with one multimem.red on the multicast alias of the flag page; the
+    one-shot multimem all-reduce (every rank reads the whole reduced vector) runs on top of it."""
+    n = min(_ngpus(), 8)
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    res = run_ranks(_colls_rank, n, args=(True, algo), env={"NCCL_B200_BARRIER_MC_MIN_RANKS": "2"}, timeout=300)
+    _check(res, n)
+
+
+def test_one_shot_multimem_allreduce_unicast_barrier():
+    n = min(_ngpus(), 8)
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    res = run_ranks(_colls_rank, n, args=(True, "NVLS1"), env={"NCCL_B200_BARRIER_MC_MIN_RANKS": "0"}, timeout=300)
+    _check(res, n)
+
+
+def _back_to_back_rank(rank, nranks, uid, mc):
+    """Many small collectives issued without any host synchronisation in between: with programmatic
+    dependent launch the next kernel is resident while the previous one drains, so this is where a
+    kernel that read an epoch or a buffer too early would show."""
+    import torch
+    torch.cuda.set_device(rank)
+    from nccl_b200 import Communicator
+    comm = Communicator(nranks, rank, uid)
+    n = nranks
+    numel = 2048
+    x = _sym_tensor(comm, numel, torch.float32)
+    y = _sym_tensor(comm, numel, torch.float32)
+    g = _sym_tensor(comm, numel * n, torch.float32)
+    x.fill_(float(rank + 1))
+    torch.cuda.synchronize()
+    bad = 0
+    for rounds in range(3):
+        for i in range(60):
+            # y = sum(x) ; x = y / n' chain: every call consumes the previous call's output
+            comm.all_reduce(x, y)
+            y.mul_(1.0 / n)   # a kernel of the caller between two collectives; keeps the values bounded
+            comm.all_gather(y[:numel // n], g[:numel])
+            comm.reduce_scatter(g[:numel], x[:numel // n])
+            comm.all_reduce(y, x, op="max")
+        torch.cuda.synchronize()
+        # all ranks must agree bit for bit on x after the chain
+        chk = x.clone()
+        comm.all_reduce(chk, op="max")
+        torch.cuda.synchronize()
+        if not torch.equal(chk, x):
+            bad += 1
+        x.fill_(float(rank + 1))
+        torch.cuda.synchronize()
+        comm.all_reduce(x, y)   # re-establish the barrier between the refill and the next round
+        torch.cuda.synchronize()
+    err = comm.async_error()
+    comm.destroy()
+    return {"bad": bad, "err": err}
+
+
+@pytest.mark.parametrize("mc", [0, 2])
+def test_back_to_back_small_collectives(mc):
+    n = min(_ngpus(), 8)
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    res = run_ranks(_back_to_back_rank, n, args=(mc,), env={"NCCL_B200_BARRIER_MC_MIN_RANKS": str(mc), "NCCL_B200_LL_MC_MIN_RANKS": str(mc)}, timeout=300)
+    for r in range(n):
+        assert res[r]["bad"] == 0 and res[r]["err"] == 0, res[r]
+
+
 def _mgmt_rank(rank, nranks, uid):
     import ctypes
     import torch

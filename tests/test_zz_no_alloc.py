@@ -4,8 +4,10 @@ Some callers cannot allocate device memory when they need a reduction (all memor
 to their own pool, or they run inside an allocator callback), so this entry point keeps its
 working memory in a fixed array of the library image. The test calls it through its exported C
 symbol, twice in a row (the second call finds the array as the first one left it), compares each
-result with the regular flagged-line all-reduce of the library, and checks that the amount of free
-device memory did not move and that oversized requests are refused.
+result with the regular flagged-line all-reduce of the library and with a plain fp32 sum computed by
+PyTorch, and checks that every rank received identical bits, that the amount of free device memory
+did not move and that oversized requests are refused. A second test changes the number of ranks
+between calls (2, then 8, then 3), which the shared epoch word of the array has to survive.
 This file sorts last so that a run stopping at the first failure has run everything else before.
 """
 import ctypes
@@ -54,8 +56,11 @@ def test_no_alloc_allreduce_matches_regular_entry_point(n, dtype, code, count):
             assert lib.b200EmuReduce(ctx, 1, 4, code, 0, count, _ptrs(ins[call]), _ptrs(want), 0, 1) == 0
             torch.cuda.synchronize()
             tol = {torch.float32: 1e-6, torch.float16: 2 ** -10, torch.bfloat16: 2 ** -7}[dtype]
+            ref = torch.stack([t.float() for t in ins[call]]).sum(0)   # plain fp32 sum of the same inputs
             for r in range(n):
                 assert torch.allclose(got[r].float(), want[r].float(), rtol=tol, atol=tol), (call, r)
+                assert torch.allclose(got[r].float(), ref, rtol=tol, atol=tol * n), (call, r)
+                assert torch.equal(got[r], got[0]), "every rank must receive identical bits"
         assert torch.cuda.mem_get_info()[0] == free_before, "the entry point must not allocate device memory"
         # beyond the fixed scratch: refused, nothing launched
         es = torch.empty(0, dtype=dtype).element_size()
@@ -63,3 +68,27 @@ def test_no_alloc_allreduce_matches_regular_entry_point(n, dtype, code, count):
         assert fn(9, code, 1, _ptrs(ins[0]), _ptrs(got), None) == 4
     finally:
         lib.b200EmuDestroy(ctx)
+
+
+def test_no_alloc_allreduce_survives_a_changing_rank_count():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from nccl_b200 import _lib
+    lib = _lib.load()
+    fn = lib.b200NoAllocAllReduce
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]
+    torch.cuda.set_device(0)
+    g = torch.Generator().manual_seed(99)
+    count = 777
+    for n in (2, 8, 3, 8, 1, 5):
+        ins = [torch.randn(count, generator=g).cuda() for _ in range(n)]
+        got = [torch.zeros(count, device="cuda") for _ in range(n)]
+        assert fn(n, 7, count, _ptrs(ins), _ptrs(got), None) == 0, n
+        torch.cuda.synchronize()
+        ref = torch.stack(ins).sum(0)
+        for r in range(n):
+            assert torch.allclose(got[r], ref, rtol=1e-6, atol=1e-5), (n, r)
+            assert torch.equal(got[r], got[0])
+    # a count whose size in bytes wraps around must be refused, not reduced to one element
+    assert fn(2, 7, (1 << 62) + 1, _ptrs(ins[:2]), _ptrs(got[:2]), None) == 4
