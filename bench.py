@@ -11,7 +11,13 @@ N > 1 is launched with one process per GPU (torchrun); rank 0 prints one JSON li
               zero, so the n=1 line reports the algorithm bandwidth of the one-rank path instead.
   e2e         the same step through nccl_b200.Communicator.all_reduce including, every step, the
               host->device copy of the input from pinned memory and the device->host copy of the result.
-  sweep       bus bandwidth of all-reduce / all-gather / reduce-scatter / all-to-all at a few sizes.
+  sweep       time and bus bandwidth of all-reduce / all-gather / reduce-scatter / all-to-all /
+              broadcast / send-recv at a few sizes, bf16 and fp32 (20 warm-up + 100 timed calls per
+              point up to 64 MiB, fewer above; the faster of two timed passes).
+  verified    outside the timed regions the headline result and every sweep point are compared on the
+              device with an fp32 PyTorch computation over inputs regenerated from the seeds of all
+              ranks; a mismatch makes the run exit non-zero.
+  --full      the whole configured sweep: 8 B to 8 GiB doubling, both dtypes (slow; not the default).
 
 --impl reference runs the same driver against the library built from the reference sources
 (baseline/_ref/build/lib/libnccl.so.2) through its public C API.
@@ -89,8 +95,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--bytes", type=int, default=1 << 30)
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--full", action="store_true", help="sweep every size from 8 B to --full-max (default 8 GiB), doubling, bf16 and fp32")
+    ap.add_argument("--full-max", type=int, default=8 << 30)
+    ap.add_argument("--full-out", default=None, help="also write the full sweep to this file")
+    ap.add_argument("--env", action="append", default=[], help="KEY=VALUE set before the library is loaded (e.g. NCCL_SYM_TMA_ENABLE=1 for the reference)")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
+    for kv in a.env:
+        k, _, v = kv.partition("=")
+        os.environ[k] = v
 
     if a.impl == "reference" and not os.path.exists(REF_LIB):
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/build/lib/libnccl.so.2 is missing (reference was not built in this checkout)"}))
@@ -98,7 +111,7 @@ def main():
 
     import torch
     from nccl_b200 import _lib
-    from nccl_b200.core import BF16
+    from nccl_b200.core import BF16, FP32
     from nccl_b200.utils import perf
 
     d = perf.Dist()
@@ -108,7 +121,7 @@ def main():
     torch.cuda.set_device(d.local_rank)
     lib = _lib.load(REF_LIB) if a.impl == "reference" else _lib.load()
     nbytes = a.bytes
-    h = perf.Harness(d, lib, max_bytes=nbytes, symmetric=True)
+    h = perf.Harness(d, lib, max_bytes=max(nbytes, a.full_max if a.full else 0), symmetric=True)
     h.fill(BF16)
 
     # ---------------- device-timed headline: K all-reduces back to back
@@ -142,6 +155,10 @@ def main():
     launches = (lib.b200CommLaunchCount(h.comm) - launches0) if count_launches else None
     factor = perf.bus_factor("all_reduce", n)
     value = nbytes / (ms * 1e-3) / 1e9 * factor
+
+    # ---------------- the headline result, checked against the seeds of all ranks (not timed)
+    ver = perf.Verifier(h, BF16, 256 << 20)
+    ver.check("all_reduce", nbytes)
 
     # ---------------- end to end: pinned host -> device, all-reduce through the public API, device -> host
     e2e = None
@@ -182,17 +199,37 @@ def main():
     except Exception as ex:  # noqa: BLE001
         e2e = {"error": str(ex)[:200]}
 
-    # ---------------- short sweep (bus bandwidth at a few sizes, registered buffers)
-    sweep = None
-    if not a.no_sweep and n > 1:
-        sweep = {}
-        sizes = [s for s in (8, 1 << 10, 32 << 10, 1 << 20, 16 << 20, 256 << 20) if s <= nbytes]
-        for coll in ("all_reduce", "all_gather", "reduce_scatter", "all_to_all"):
+    # ---------------- short sweep (time and bus bandwidth at a few sizes, registered buffers), every point verified
+    sweep = sweep32 = full = None
+    colls = ("all_reduce", "all_gather", "reduce_scatter", "all_to_all", "broadcast", "sendrecv")
+
+    def run_sweep(dt, verifier, sizes, iters):
+        res = {}
+        for coll in colls:
             try:
-                rows = perf.sweep(h, coll, BF16, sizes, warmup=5, iters=20)
-                sweep[coll] = {str(r["bytes"]): [r["time_us"], r["busbw_GBps"]] for r in rows}
+                rows = perf.sweep(h, coll, dt, sizes, warmup=20, iters=iters, verifier=verifier)
+                res[coll] = {str(r["bytes"]): [r["time_us"], r["busbw_GBps"]] for r in rows}
             except Exception as ex:  # noqa: BLE001
-                sweep[coll] = {"error": str(ex)[:200]}
+                res[coll] = {"error": str(ex)[:200]}
+        return res
+
+    ver32 = None
+    if not a.no_sweep and n > 1:
+        sizes = [s for s in (8, 1 << 10, 32 << 10, 1 << 20, 16 << 20, 256 << 20) if s <= nbytes]
+        sweep = run_sweep(BF16, ver, sizes, 100)
+        if a.full:
+            full = {"bf16": run_sweep(BF16, ver, [1 << k for k in range(3, 40) if (1 << k) <= a.full_max], 100)}
+        h.fill(FP32)
+        ver32 = perf.Verifier(h, FP32, 256 << 20)
+        sweep32 = run_sweep(FP32, ver32, [s for s in (8, 32 << 10, 1 << 20, 64 << 20) if s <= nbytes], 100)
+        if a.full:
+            full["fp32"] = run_sweep(FP32, ver32, [1 << k for k in range(3, 40) if (1 << k) <= a.full_max], 100)
+    verified = ver.summary()
+    if ver32 is not None:
+        v32 = ver32.summary()
+        verified = {"ok": verified["ok"] and v32["ok"], "points": verified["points"] + v32["points"],
+                    "max_abs_err": {"bf16": verified["max_abs_err"], "fp32": v32["max_abs_err"]}, "failures": (verified["failures"] + v32["failures"])[:4]}
+    ver = ver32 = None
     h.close()
     if d.rank == 0:
         out = {
@@ -204,9 +241,19 @@ def main():
                        "buffers": "ncclMemAlloc + ncclCommWindowRegister(NCCL_WIN_COLL_SYMMETRIC)",
                        "l2": "1 GiB per rank per step: inputs larger than the 126 MB L2, no flush needed",
                        "busbw": "algBW*2(n-1)/n" if n > 1 else "n=1: algBW of the one-rank copy path (the bus factor is 0)"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "sweep_time_us_busbw": sweep,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "verified": verified, "sweep_time_us_busbw": sweep,
+            "sweep_fp32_time_us_busbw": sweep32,
         }
+        if full is not None:
+            out["full_sweep_time_us_busbw"] = full
+            if a.full_out:
+                with open(a.full_out, "w") as f:
+                    json.dump({"impl": a.impl, "n_gpus": n, "env": a.env, "full": full, "verified": verified}, f)
         print(json.dumps(out))
+    if not verified["ok"]:
+        if d.rank == 0:
+            print("bench.py: results do not match the values recomputed from the seeds: %s" % verified["failures"], file=sys.stderr)
+        return 3
     return 0
 
 

@@ -72,6 +72,32 @@ typedef struct {
   ncclResult_t (*getChunkSize)(void* ctx, ncclFunc_t collType, size_t nBytes, int algo, int proto, int nChannels, size_t* chunkSize);
 } ncclTuner_v6_t;
 
+/* Earlier interfaces, still loaded (reference: src/plugin/tuner/tuner_v2.cc ... tuner_v4.cc).
+ * v4 / v3: context comes back from init; v3 has no regBuff argument; v2 names its choice directly. */
+typedef struct {
+  const char* name;
+  ncclResult_t (*init)(size_t nRanks, size_t nNodes, ncclDebugLogger_t logFunction, void** ctx);
+  ncclResult_t (*getCollInfo)(void* ctx, ncclFunc_t collType, size_t nBytes, int numPipeOps, float** collCostTable, int numAlgo, int numProto,
+                              int regBuff, int* nChannels);
+  ncclResult_t (*destroy)(void* ctx);
+} ncclTuner_v4_t;
+
+typedef struct {
+  const char* name;
+  ncclResult_t (*init)(size_t nRanks, size_t nNodes, ncclDebugLogger_t logFunction, void** ctx);
+  ncclResult_t (*getCollInfo)(void* ctx, ncclFunc_t collType, size_t nBytes, int numPipeOps, float** collCostTable, int numAlgo, int numProto,
+                              int* nChannels);
+  ncclResult_t (*destroy)(void* ctx);
+} ncclTuner_v3_t;
+
+typedef struct {
+  const char* name;
+  ncclResult_t (*init)(size_t nRanks, size_t nNodes, ncclDebugLogger_t logFunction, void** ctx);
+  ncclResult_t (*getCollInfo)(void* ctx, ncclFunc_t collType, size_t nBytes, int collNetSupport, int nvlsSupport, int numPipeOps,
+                              int* algorithm, int* protocol, int* nChannels);
+  ncclResult_t (*destroy)(void* ctx);
+} ncclTuner_v2_t;
+
 typedef ncclTuner_v6_t ncclTuner_t;
 #define NCCL_TUNER_PLUGIN_SYMBOL "ncclTunerPlugin_v6"
 

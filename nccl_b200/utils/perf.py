@@ -154,7 +154,7 @@ class Harness:
             return L.ncclGroupEnd()
         raise ValueError(coll)
 
-    def time(self, coll, nbytes, dtype_code=FP32, warmup=20, iters=100, min_warm_ms=3.0):
+    def time(self, coll, nbytes, dtype_code=FP32, warmup=20, iters=100, min_warm_ms=3.0, passes=2):
         """Mean device time per call in microseconds (max over ranks). The warm-up covers at least
         `warmup` calls and roughly `min_warm_ms` of device time: after the host-side barrier between
         two measurements the GPU has been idle and its clocks have dropped, and a window of a few
@@ -163,19 +163,32 @@ class Harness:
         sp = self.stream.cuda_stream
         est_us = 10.0 + nbytes / 3.0e5                       # rough per-call time: 10 us + bytes at 300 GB/s
         warm = max(warmup, min(2000, int(min_warm_ms * 1e3 / est_us) + 1))
-        with torch.cuda.stream(self.stream):
-            self.d.barrier()
-            for _ in range(warm):
-                _lib.check(self.call(coll, nbytes, dtype_code, sp), coll, self.lib)
-            self.stream.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(self.stream)
-            for _ in range(iters):
-                _lib.check(self.call(coll, nbytes, dtype_code, sp), coll, self.lib)
-            e1.record(self.stream)
-            self.stream.synchronize()
-        us = e0.elapsed_time(e1) * 1000.0 / iters
-        return self.d.max(us)
+        # The host issues the calls while the device runs them, so a pause of the interpreter (a
+        # garbage-collection pass takes milliseconds) would be timed as if it were the library's:
+        # collection is off inside the loop, and the loop runs twice with the faster pass reported.
+        import gc
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.stream(self.stream):
+                self.d.barrier()
+                for _ in range(warm):
+                    _lib.check(self.call(coll, nbytes, dtype_code, sp), coll, self.lib)
+                self.stream.synchronize()
+                best = None
+                for _ in range(passes):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(self.stream)
+                    for _ in range(iters):
+                        _lib.check(self.call(coll, nbytes, dtype_code, sp), coll, self.lib)
+                    e1.record(self.stream)
+                    self.stream.synchronize()
+                    us = e0.elapsed_time(e1) * 1000.0 / iters
+                    best = us if best is None else min(best, us)
+        finally:
+            if was_enabled:
+                gc.enable()
+        return self.d.max(best)
 
     def time_host(self, coll, nbytes, dtype_code=FP32, iters=200):
         """Host time per call in microseconds (max over ranks): how long the calling thread spends
@@ -231,7 +244,137 @@ class Harness:
         self.lib.ncclCommDestroy(self.comm)
 
 
-def sweep(h, coll, dtype_code, sizes, warmup=20, iters=100):
+class Verifier:
+    """Checks results on the device against values recomputed from the seeds of all ranks.
+
+    Every rank can regenerate every other rank's input (Harness.fill draws from a generator seeded
+    with 7 + rank in chunks of 2^26 elements), so no data has to travel: the verifier keeps the
+    first `prefix_bytes` of every rank's input and, for messages that reach further, regenerates on
+    demand. A check runs the collective once, then compares windows of the output (the whole output
+    when it is small; otherwise the head, the tail and a stretch around every block boundary) with a
+    plain PyTorch fp32 computation. Nothing of this is inside a timed region."""
+
+    def __init__(self, h, dtype_code, prefix_bytes):
+        self.h = h
+        self.dt = dtype_code
+        self.tdt = torch.bfloat16 if dtype_code == BF16 else torch.float32
+        self.es = TYPE_SIZE[dtype_code]
+        self.prefix = min(prefix_bytes, h.max_bytes) // self.es
+        self._chunk_states = {}
+        self.inputs = [self._regen(p, self.prefix) for p in range(h.n)]
+        self.max_err = 0.0
+        self.points = 0
+        self.failures = []
+
+    def _states(self, p):
+        """Generator state of rank p before each 2^26-element chunk (one pass over the whole buffer, once)."""
+        if p not in self._chunk_states:
+            g = torch.Generator(device="cuda").manual_seed(7 + p)
+            total = self.h.send_bytes // self.es
+            states = []
+            for i in range(0, total, 1 << 26):
+                states.append(g.get_state())
+                torch.rand(min(1 << 26, total - i), generator=g, device="cuda", dtype=torch.float32)
+            self._chunk_states[p] = states
+        return self._chunk_states[p]
+
+    def _regen(self, p, numel, skip=0):
+        """Elements [skip, skip + numel) of rank p's input, drawn exactly as Harness.fill draws them."""
+        total = self.h.send_bytes // self.es
+        step = 1 << 26
+        states = self._states(p)
+        g = torch.Generator(device="cuda")
+        parts = []
+        for ci in range(skip // step, (skip + numel - 1) // step + 1):
+            i = ci * step
+            m = min(step, total - i)
+            g.set_state(states[ci])
+            chunk = (torch.rand(m, generator=g, device="cuda", dtype=torch.float32) * 2 - 1).to(self.tdt)
+            lo, hi = max(skip, i), min(skip + numel, i + m)
+            parts.append(chunk[lo - i:hi - i].clone())
+            del chunk
+        return torch.cat(parts) if len(parts) != 1 else parts[0]
+
+    def _src(self, p, lo, hi):
+        if hi <= self.prefix:
+            return self.inputs[p][lo:hi]
+        return self._regen(p, hi - lo, lo)
+
+    @staticmethod
+    def _windows(numel, edge=1 << 11, whole=1 << 22):
+        if numel <= whole:
+            return [(0, numel)]
+        return [(0, min(numel, 1 << 20)), (numel // 2 - edge, numel // 2 + edge), (numel - edge, numel)]
+
+    def _cmp(self, got, want, exact, what):
+        if exact:
+            ok = torch.equal(got, want)
+            err = 0.0 if ok else float((got.float() - want.float()).abs().max())
+        else:
+            # sums of n values of magnitude <= 1: fp32 accumulation, one rounding to the element type
+            eps = 2.0 ** -7 if self.tdt == torch.bfloat16 else 2.0 ** -20
+            diff = (got.float() - want).abs()
+            err = float(diff.max()) if diff.numel() else 0.0
+            ok = bool((diff <= eps * (1.0 + want.abs())).all())
+        self.max_err = max(self.max_err, err)
+        if not ok:
+            self.failures.append("%s: max abs error %.4g" % (what, err))
+        return ok
+
+    def check(self, coll, nbytes):
+        """Runs `coll` once at this size and checks the output. Returns True when it is right."""
+        h, n, r, es = self.h, self.h.n, self.h.rank, self.es
+        unit = es * (n if coll in ("all_gather", "reduce_scatter", "all_to_all") else 1)
+        nb = max(unit, nbytes // unit * unit)
+        out = h.recv_t.view(self.tdt)
+        out[: max(nb // es, 1)].zero_()
+        torch.cuda.synchronize()
+        with torch.cuda.stream(h.stream):
+            _lib.check(h.call(coll, nb, self.dt, h.stream.cuda_stream), coll, h.lib)
+        torch.cuda.synchronize()
+        ok = True
+        tag = "%s %d B rank %d" % (coll, nb, r)
+        if coll in ("all_reduce", "reduce"):
+            if coll == "reduce" and r != 0:
+                return True
+            for lo, hi in self._windows(nb // es):
+                want = torch.zeros(hi - lo, dtype=torch.float32, device="cuda")
+                for p in range(n):
+                    want += self._src(p, lo, hi).float()
+                ok &= self._cmp(out[lo:hi], want, False, tag)
+        elif coll == "reduce_scatter":
+            blk = nb // es // n
+            for lo, hi in self._windows(blk):
+                want = torch.zeros(hi - lo, dtype=torch.float32, device="cuda")
+                for p in range(n):
+                    want += self._src(p, r * blk + lo, r * blk + hi).float()
+                ok &= self._cmp(out[lo:hi], want, False, tag)
+        elif coll == "all_gather":
+            blk = nb // es // n
+            for p in range(n):
+                for lo, hi in self._windows(blk, whole=1 << 19):
+                    ok &= self._cmp(out[p * blk + lo:p * blk + hi], self._src(p, lo, hi), True, tag)
+        elif coll == "all_to_all":
+            blk = nb // es // n
+            for p in range(n):
+                for lo, hi in self._windows(blk, whole=1 << 19):
+                    ok &= self._cmp(out[p * blk + lo:p * blk + hi], self._src(p, r * blk + lo, r * blk + hi), True, tag)
+        elif coll == "broadcast":
+            for lo, hi in self._windows(nb // es):
+                ok &= self._cmp(out[lo:hi], self._src(0, lo, hi), True, tag)
+        elif coll == "sendrecv":
+            for lo, hi in self._windows(nb // es):
+                ok &= self._cmp(out[lo:hi], self._src((r - 1) % n, lo, hi), True, tag)
+        self.points += 1
+        return ok
+
+    def summary(self):
+        """Agreed over all ranks: {"ok", "points", "max_err", "failures"}."""
+        bad = self.h.d.max(float(len(self.failures)))
+        return {"ok": bad == 0, "points": self.points, "max_abs_err": self.h.d.max(self.max_err), "failures": self.failures[:4]}
+
+
+def sweep(h, coll, dtype_code, sizes, warmup=20, iters=100, verifier=None):
     rows = []
     for nbytes in sizes:
         es = TYPE_SIZE[dtype_code]
@@ -243,7 +386,10 @@ def sweep(h, coll, dtype_code, sizes, warmup=20, iters=100):
         wu = warmup if nb <= (64 << 20) else max(3, warmup // 5)
         us = h.time(coll, nb, dtype_code, wu, it)
         alg = nb / us / 1e3
-        rows.append({"bytes": nb, "time_us": round(us, 2), "algbw_GBps": round(alg, 2), "busbw_GBps": round(alg * bus_factor(coll, h.n), 2)})
+        row = {"bytes": nb, "time_us": round(us, 2), "algbw_GBps": round(alg, 2), "busbw_GBps": round(alg * bus_factor(coll, h.n), 2)}
+        if verifier is not None:
+            row["verified"] = verifier.check(coll, nb)
+        rows.append(row)
     return rows
 
 
@@ -259,6 +405,7 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--iters", type=int, default=100)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--verify", action="store_true", help="check every size against values recomputed from the seeds (outside the timed loops)")
     ap.add_argument("--latency", action="store_true", help="per size: host time per call, device time per call issued eagerly, and replayed from a CUDA graph")
     a = ap.parse_args(argv)
     d = Dist()
@@ -284,10 +431,14 @@ def main(argv=None):
                 row["graph_error"] = str(ex)[:120]
             rows.append(row)
     else:
-        rows = sweep(h, a.coll, dt, sizes, a.warmup, a.iters)
+        ver = Verifier(h, dt, min(a.max, 256 << 20)) if a.verify else None
+        rows = sweep(h, a.coll, dt, sizes, a.warmup, a.iters, ver)
+    verified = ver.summary() if (not a.latency and ver is not None) else None
     h.close()
     if d.rank == 0:
         out = {"coll": a.coll, "dtype": a.dtype, "n_gpus": d.world, "lib": a.lib or "nccl_b200", "symmetric": not a.plain, "rows": rows}
+        if verified is not None:
+            out["verified"] = verified
         text = json.dumps(out)
         print(text)
         if a.out:

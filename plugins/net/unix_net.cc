@@ -181,6 +181,66 @@ ncclResult_t nSetNetAttr(void*, ncclNetAttr_t*) { return ncclSuccess; }
 
 }  // namespace
 
-extern "C" __attribute__((visibility("default"))) const ncclNet_v12_t ncclNetPlugin_v12 = {
+// -DUNIX_NET_ABI=8|9|10|11 builds the same backend behind an earlier interface instead (one table per
+// library), which is how the library's adapters for deployed older plugins are tested.
+#ifndef UNIX_NET_ABI
+#define UNIX_NET_ABI 12
+#endif
+#define EXPORT extern "C" __attribute__((visibility("default")))
+
+#if UNIX_NET_ABI == 12
+EXPORT const ncclNet_v12_t ncclNetPlugin_v12 = {
     "UnixExample", nInit, nDevices, nProps, nListen, nConnect, nAccept, nRegMr, nRegMrDmaBuf, nDeregMr, nIsend, nIrecv, nIflush, nTest,
     nCloseComm, nCloseComm, nCloseListen, nGetDeviceMr, nIrecvConsumed, nMakeVDevice, nFinalize, nSetNetAttr};
+#else
+#include "plugin/nccl_net_compat.h"
+namespace {
+template <typename P> ncclResult_t oldProps(int dev, P* p) {
+  ncclNetProperties_t full;
+  ncclResult_t r = nProps(dev, &full);
+  if (r != ncclSuccess) return r;
+  memset(p, 0, sizeof(*p));
+  p->name = full.name; p->pciPath = full.pciPath; p->guid = full.guid; p->ptrSupport = full.ptrSupport; p->regIsGlobal = full.regIsGlobal;
+  p->speed = full.speed; p->port = full.port; p->latency = full.latency; p->maxComms = full.maxComms; p->maxRecvs = full.maxRecvs;
+  p->netDeviceType = full.netDeviceType; p->netDeviceVersion = full.netDeviceVersion;
+  return ncclSuccess;
+}
+template <typename P> ncclResult_t oldProps9(int dev, P* p) {
+  ncclResult_t r = oldProps(dev, p);
+  if (r == ncclSuccess) { p->vProps.ndevs = 1; p->vProps.devs[0] = dev; p->maxP2pBytes = (size_t)1 << 40; p->maxCollBytes = (size_t)1 << 40; }
+  return r;
+}
+ncclResult_t oInitLog(ncclDebugLogger_t log) { return nInit(nullptr, 0, nullptr, log, nullptr); }
+ncclResult_t oInitLogProf(ncclDebugLogger_t log, ncclProfilerCallback_t prof) { return nInit(nullptr, 0, nullptr, log, prof); }
+ncclResult_t oListen(int dev, void* h, void** lc) { return nListen(nullptr, dev, h, lc); }
+ncclResult_t oConnect(int dev, void* h, void** sc, ncclNetDeviceHandle_t** dh) { return nConnect(nullptr, dev, h, sc, dh); }
+ncclResult_t oConnectCfg(int dev, ncclNetCommConfig_t*, void* h, void** sc, ncclNetDeviceHandle_t** dh) { return nConnect(nullptr, dev, h, sc, dh); }
+ncclResult_t oIsend9(void* sc, void* d, size_t n, int tag, void* mh, void** req) { return nIsend(sc, d, n, tag, mh, nullptr, req); }
+ncclResult_t oIrecv9(void* rc, int n, void** d, size_t* sz, int* tags, void** mhs, void** req) { return nIrecv(rc, n, d, sz, tags, mhs, nullptr, req); }
+ncclResult_t oIsend8(void* sc, void* d, int n, int tag, void* mh, void** req) { return nIsend(sc, d, (size_t)n, tag, mh, nullptr, req); }
+ncclResult_t oIrecv8(void* rc, int n, void** d, int* sz, int* tags, void** mhs, void** req) {
+  size_t wide[NCCL_NET_MAX_REQUESTS];
+  for (int i = 0; i < n; ++i) wide[i] = (size_t)sz[i];
+  return nIrecv(rc, n, d, wide, tags, mhs, nullptr, req);
+}
+}  // namespace
+#if UNIX_NET_ABI == 11
+EXPORT const ncclNet_v11_t ncclNetPlugin_v11 = {
+    "UnixExample", nInit, nDevices, oldProps9<ncclNetProperties_v11_t>, nListen, nConnect, nAccept, nRegMr, nRegMrDmaBuf, nDeregMr, nIsend, nIrecv,
+    nIflush, nTest, nCloseComm, nCloseComm, nCloseListen, nGetDeviceMr, nIrecvConsumed, nMakeVDevice, nFinalize, nSetNetAttr};
+#elif UNIX_NET_ABI == 10
+EXPORT const ncclNet_v10_t ncclNetPlugin_v10 = {
+    "UnixExample", oInitLogProf, nDevices, oldProps9<ncclNetProperties_v10_t>, oListen, oConnectCfg, nAccept, nRegMr, nRegMrDmaBuf, nDeregMr, nIsend,
+    nIrecv, nIflush, nTest, nCloseComm, nCloseComm, nCloseListen, nGetDeviceMr, nIrecvConsumed, nMakeVDevice};
+#elif UNIX_NET_ABI == 9
+EXPORT const ncclNet_v9_t ncclNetPlugin_v9 = {
+    "UnixExample", oInitLog, nDevices, oldProps9<ncclNetProperties_v9_t>, oListen, oConnect, nAccept, nRegMr, nRegMrDmaBuf, nDeregMr, oIsend9, oIrecv9,
+    nIflush, nTest, nCloseComm, nCloseComm, nCloseListen, nGetDeviceMr, nIrecvConsumed, nMakeVDevice};
+#elif UNIX_NET_ABI == 8
+EXPORT const ncclNet_v8_t ncclNetPlugin_v8 = {
+    "UnixExample", oInitLog, nDevices, oldProps<ncclNetProperties_v8_t>, oListen, oConnect, nAccept, nRegMr, nRegMrDmaBuf, nDeregMr, oIsend8, oIrecv8,
+    nIflush, nTest, nCloseComm, nCloseComm, nCloseListen, nGetDeviceMr, nIrecvConsumed};
+#else
+#error "UNIX_NET_ABI must be 8, 9, 10, 11 or 12"
+#endif
+#endif

@@ -527,6 +527,63 @@ static ncclResult_t runReduction(ncclComm* comm, const Task& t) {
   return ncclSuccess;
 }
 
+// ---- several small all-reduces of one group in one launch (flagged lines)
+// A task can join a batch when it is an all-reduce with a built-in operator whose payload the
+// selection table would send down the flagged-line path anyway.
+static size_t llLimit(ncclComm* comm) {
+  DevicePlane* dp = comm->devPlane;
+  const int n = comm->nRanks;
+  size_t lim = dp->tune.arLLMax[n];
+  const std::vector<TuneEntry>& rows = dp->tune.entries[0][n];
+  if (!rows.empty()) lim = rows[0].algo == ALGO_LL_ONESHOT ? rows[0].upto : 0;
+  if (paramLLThreshold() >= 0) lim = (size_t)paramLLThreshold();
+  return std::min(lim, kLLDataBytes / 2);
+}
+
+bool devPlaneBatchable(ncclComm* comm, const Task& t) {
+  if (!comm->devPlane || comm->hostOnly || comm->nRanks < 2 || !comm->lsaAll || comm->tuner) return false;
+  if (t.func != FUNC_ALLREDUCE || t.op >= ncclNumOps || t.count == 0) return false;
+  const int forced = forcedAlgo();
+  if (forced != ALGO_AUTO && forced != ALGO_LL_ONESHOT) return false;
+  return t.count * typeSize(t.type) <= llLimit(comm);
+}
+
+// Tasks must be batchable, of one type, operator and stream. Returns how many of them went into the launch.
+ncclResult_t devPlaneRunLLBatch(ncclComm* comm, const Task* tasks, int count, int* taken) {
+  DevicePlane* dp = comm->devPlane;
+  *taken = 0;
+  NCCLCHECK(devPlaneCheckStatus(comm));
+  int cur = -1;
+  CUDACHECK(cudaGetDevice(&cur));
+  if (cur != comm->cudaDev) CUDACHECK(cudaSetDevice(comm->cudaDev));
+  const Task& t0 = tasks[0];
+  const size_t es = typeSize(t0.type);
+  DevOp op;
+  NCCLCHECK(lowerOp(comm, t0, &op));
+  LLBatchArgs b;
+  baseArgs(comm, &b.c, FUNC_ALLREDUCE);
+  b.c.scaleMode = op.scaleMode; b.c.scaleF = op.scaleF; b.c.scaleD = op.scaleD; b.c.intDiv = op.intDiv;
+  const size_t cap = std::min(llLimit(comm) * 2, kLLDataBytes - 8) / 8;   // lines
+  uint32_t lines = 0;
+  int k = 0;
+  for (; k < count && k < kMaxLLItems; ++k) {
+    const size_t nl = (tasks[k].count * es + 7) / 8;
+    if (lines + nl > cap) break;
+    b.items[k] = LLItem{(long long)(uintptr_t)tasks[k].send, (long long)(uintptr_t)tasks[k].recv, (uint32_t)tasks[k].count, lines};
+    lines += (uint32_t)nl;
+  }
+  if (k == 0) return ncclInternalError;
+  b.nItems = k;
+  b.totalLines = lines;
+  NCCLCHECK(devPlaneOrderStreams(comm, t0.stream));
+  const int ctas = (int)std::min<size_t>(((size_t)lines + kCtaThreads - 1) / kCtaThreads, 64);
+  dp->launches++;
+  ncclResult_t r = launchKernel(llReduceBatchKernelFn(t0.type, op.red), dim3(std::max(ctas, 1)), dim3(kCtaThreads), 0, &b, t0.stream, false, paramLaunchPdl() != 0);
+  if (cur != comm->cudaDev && cur >= 0) cudaSetDevice(cur);
+  *taken = k;
+  return r;
+}
+
 static ncclResult_t runCopyColl(ncclComm* comm, const Task& t) {
   DevicePlane* dp = comm->devPlane;
   const int n = comm->nRanks, me = comm->rank;

@@ -57,6 +57,10 @@ ncclResult_t devPlaneCreate(ncclComm* comm);
 void devPlaneDestroy(ncclComm* comm);
 ncclResult_t devPlaneRun(ncclComm* comm, const Task& t, ncclSimInfo_t* sim = nullptr);
 ncclResult_t devPlaneRunP2pGroup(ncclComm* comm, const std::vector<Task>& tasks);
+// Aggregation of a group's small all-reduces into one launch (flagged lines): whether a task qualifies, and the
+// launch for a run of qualifying tasks of one type, operator and stream (`taken` = how many it carried).
+bool devPlaneBatchable(ncclComm* comm, const Task& t);
+ncclResult_t devPlaneRunLLBatch(ncclComm* comm, const Task* tasks, int count, int* taken);
 // Kernels of one communicator share its barrier slots and epochs, so they run one after the other even
 // when issued on different streams: makes `stream` wait for the communicator's previous launch.
 ncclResult_t devPlaneOrderStreams(ncclComm* comm, cudaStream_t stream);

@@ -133,6 +133,40 @@ int b200EmuReduce(void* ctx, int kernel, int func, int type, int op, size_t coun
   return coopLaunch(reduceKernelFn(kernel, (ncclDataType_t)type, red), ctas, n, &a);
 }
 
+// Several all-reduces in one launch of the flagged-line kernel: item i reduces counts[i] elements found at byte offset
+// sendOff[i] of every rank's sendBase and writes them at recvOff[i] of every rank's recvBase.
+int b200EmuReduceBatch(void* ctx, int type, int op, int nItems, const size_t* counts, const size_t* sendOff, const size_t* recvOff,
+                       const void** sendBase, void** recvBase, int ctas) {
+  EmuCtx* e = (EmuCtx*)ctx;
+  const int n = e->n;
+  if (nItems < 1 || nItems > kMaxLLItems) return ncclInvalidArgument;
+  const size_t es = typeSize((ncclDataType_t)type);
+  LLBatchArgs b;
+  memset(&b, 0, sizeof(b));
+  CollArgs& a = b.c;
+  a.nRanks = n;
+  a.emu = 1;
+  a.func = FUNC_ALLREDUCE;
+  fillSyncEmu(e, &a.sync);
+  int red = op == ncclAvg ? RED_SUM : op;
+  if (op == ncclAvg) { a.scaleMode = SCALE_MUL; a.scaleF = 1.0f / n; a.scaleD = 1.0 / n; }
+  for (int p = 0; p < n; ++p) {
+    a.lsend[p] = sendBase[p];
+    a.lrecv[p] = recvBase[p];
+    a.ll[p] = e->ll[p];
+    a.llEpoch[p] = e->priv[p] + kBarrierSlots;
+  }
+  uint32_t lines = 0;
+  for (int i = 0; i < nItems; ++i) {
+    b.items[i] = LLItem{(long long)sendOff[i], (long long)recvOff[i], (uint32_t)counts[i], lines};
+    lines += (uint32_t)((counts[i] * es + 7) / 8);
+  }
+  if (lines > kLLLines - 1) return ncclInvalidArgument;
+  b.nItems = nItems;
+  b.totalLines = lines;
+  return coopLaunch(llReduceBatchKernelFn((ncclDataType_t)type, red), ctas, n, &b);
+}
+
 // Copy collectives; bytes = size of one block (all-gather: per-rank contribution, ...).
 int b200EmuCopy(void* ctx, int func, int mode, size_t bytes, const void** send, void** recv, int root, int ctas) {
   EmuCtx* e = (EmuCtx*)ctx;

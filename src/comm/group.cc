@@ -109,16 +109,37 @@ static ncclResult_t launchAll(std::vector<Task>& tasks, ncclSimInfo_t* sim) {
       if (paramLaunchRaceFatal()) return ncclInvalidUsage;
     }
     std::vector<Task> p2p;
+    std::vector<Task> batch;   // consecutive small all-reduces of one type / operator / stream: one launch
+    auto flushBatch = [&]() -> ncclResult_t {
+      size_t done = 0;
+      while (done < batch.size()) {
+        if (batch.size() - done == 1) { NCCLCHECK(runTask(comm, batch[done])); ++done; break; }
+        int taken = 0;
+        comm->opCount++;
+        NCCLCHECK(devPlaneRunLLBatch(comm, batch.data() + done, (int)(batch.size() - done), &taken));
+        if (comm->profiler)
+          for (int i = 0; i < taken; ++i) profilerTaskStop(comm, batch[done + i], profilerTaskStart(comm, batch[done + i]), "ONESHOT", "LL", 0);
+        done += taken;
+      }
+      batch.clear();
+      return ncclSuccess;
+    };
     float commUs = 0;
     for (auto& t : tasks) {
       if (t.comm != comm) continue;
       if (sim) { commUs += comm->hostOnly ? 0.f : devPlaneEstimateUs(comm, t); continue; }
-      if (t.func == FUNC_SEND || t.func == FUNC_RECV) { p2p.push_back(t); continue; }
+      if (t.func == FUNC_SEND || t.func == FUNC_RECV) { NCCLCHECK(flushBatch()); p2p.push_back(t); continue; }
       NCCLCHECK(runP2p(comm, p2p));
       p2p.clear();
+      if (!comm->hostOnly && devPlaneBatchable(comm, t)) {
+        if (!batch.empty() && (batch[0].type != t.type || batch[0].op != t.op || batch[0].stream != t.stream)) NCCLCHECK(flushBatch());
+        batch.push_back(t);
+        continue;
+      }
+      NCCLCHECK(flushBatch());
       NCCLCHECK(runTask(comm, t));
     }
-    if (!sim) NCCLCHECK(runP2p(comm, p2p));
+    if (!sim) { NCCLCHECK(flushBatch()); NCCLCHECK(runP2p(comm, p2p)); }
     simUs = std::max(simUs, commUs);  // communicators of one group run concurrently
   }
   if (sim) sim->estimatedTime = simUs;

@@ -96,6 +96,23 @@ struct CollArgs {
   char* llMc;                           // multicast alias of the flagged-line region (null: unicast stores only)
 };
 
+// Several small all-reduces of one group carried by one launch of the flagged-line kernel: item i
+// owns lines [lineOff, lineOff + ceil(count * elemSize / 8)) of every region; buffers are given as
+// byte offsets from lsend[rank] / lrecv[rank] (null bases outside the emulation, so the offsets are
+// plain addresses there).
+struct LLItem {
+  long long sendOff, recvOff;
+  uint32_t count;        // elements
+  uint32_t lineOff;
+};
+constexpr int kMaxLLItems = 64;
+struct LLBatchArgs {
+  CollArgs c;            // c.count unused; func = all-reduce
+  int nItems;
+  uint32_t totalLines;
+  LLItem items[kMaxLLItems];
+};
+
 struct P2pOp {
   int peer;
   int isSend;

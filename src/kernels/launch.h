@@ -27,6 +27,7 @@ bool nvlsReduceSupported(ncclDataType_t type, int op);
 const void* ringKernelFn(ncclDataType_t type, int op);
 const void* treeKernelFn(ncclDataType_t type, int op);
 const void* llReduceKernelFn(ncclDataType_t type, int op);   // all-reduce, reduce-scatter, reduce (a.func)
+const void* llReduceBatchKernelFn(ncclDataType_t type, int op);   // takes LLBatchArgs: several all-reduces of one group
 const void* llCopyKernelFn();
 const void* copyKernelFn();
 const void* p2pKernelFn();

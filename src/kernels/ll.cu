@@ -176,6 +176,76 @@ __global__ void __launch_bounds__(kCtaThreads, 1) llReduceKernel(const __grid_co
   ll.end(a, w, rank, ackTo, ackFrom);
 }
 
+// One launch for a whole group of small all-reduces of one type and operator: the CTAs share the
+// flattened line space of all items, one epoch and one closing step serve them all.
+// Reference parity: the role of src/scheduler/symmetric_sched.cc:227-364 (several tasks per launch).
+template <typename T, int OP>
+__global__ void __launch_bounds__(kCtaThreads, 1) llReduceBatchKernel(const __grid_constant__ LLBatchArgs b) {
+  const CollArgs& a = b.c;
+  const int rank = ctaRank(a.emu, a.rank);
+  const int n = a.nRanks;
+  constexpr int N = 8 / sizeof(T);
+  __shared__ LLItem items[kMaxLLItems];
+  for (int i = threadIdx.x; i < b.nItems; i += blockDim.x) items[i] = b.items[i];
+  pdlEnter();
+  LLCtx ll;
+  ll.begin(a, rank);
+  WaitCtx w{&a.sync, a.sync.status[rank]};
+  __syncthreads();
+  const char* inBase = (const char*)a.lsend[rank];
+  char* outBase = (char*)a.lrecv[rank];
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool mcast = a.llMc != nullptr;
+  auto itemOf = [&](uint32_t L) {
+    int lo = 0, hi = b.nItems - 1;   // last item whose lineOff <= L
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (items[mid].lineOff <= L) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+  };
+  for (size_t L = tid; L < b.totalLines; L += stride) {
+    const LLItem it = items[itemOf((uint32_t)L)];
+    const size_t l = L - it.lineOff;
+    const size_t bytes = (size_t)it.count * sizeof(T);
+    const uint64_t d = llLoad8(inBase + it.sendOff + l * 8, bytes - l * 8);
+    if (mcast) {
+      char* slot = a.llMc + ((size_t)(ll.parity * kMaxRanks + rank) * kLLLines) * 16 + L * 16;
+      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(slot), "r"((uint32_t)d), "r"(ll.epoch), "r"((uint32_t)(d >> 32)),
+                   "r"(ll.epoch) : "memory");
+      continue;
+    }
+    for (int j = 1; j < n; ++j) {
+      const int p = (rank + j) % n;
+      stVolatile16(ll.region(a, p, rank) + L * 16, make_uint4((uint32_t)d, ll.epoch, (uint32_t)(d >> 32), ll.epoch));
+    }
+  }
+  bool ok = true;
+  for (size_t L = tid; L < b.totalLines && ok; L += stride) {
+    const LLItem it = items[itemOf((uint32_t)L)];
+    const size_t l = L - it.lineOff;
+    const size_t bytes = (size_t)it.count * sizeof(T);
+    const size_t valid = bytes - l * 8;
+    typename Elem<T>::Acc acc[N];
+    ok = ll.recvLines(a, w, rank, L, llLoad8(inBase + it.sendOff + l * 8, valid), [&](int s, uint64_t d) {
+      union { uint64_t u; T e[N]; } cv;
+      cv.u = d;
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        typename Elem<T>::Acc x = Elem<T>::ld(cv.e[k]);
+        acc[k] = s == 0 ? x : redApply<OP>(acc[k], x);
+      }
+    });
+    if (!ok) break;
+    union { uint64_t u; T e[N]; } res;
+#pragma unroll
+    for (int k = 0; k < N; ++k) res.e[k] = scalarPost<T, OP>(acc[k], a);
+    llStore8(outBase + it.recvOff + l * 8, res.u, valid);
+  }
+  ll.end(a, w, rank, 0, 0);
+}
+
 // a.count = bytes of one block; a.sendStride / a.recvStride = pitch of blocks in the user buffers.
 __global__ void __launch_bounds__(kCtaThreads, 1) llCopyKernel(const __grid_constant__ CollArgs a) {
   const int rank = ctaRank(a.emu, a.rank);
@@ -243,11 +313,13 @@ __global__ void __launch_bounds__(kCtaThreads, 1) llCopyKernel(const __grid_cons
   ll.end(a, w, rank, ackTo, ackFrom);
 }
 
-template <typename T, int OP> static const void* llFn() { return (const void*)llReduceKernel<T, OP>; }
+template <typename T, int OP> static const void* llFn(bool batch) {
+  return batch ? (const void*)llReduceBatchKernel<T, OP> : (const void*)llReduceKernel<T, OP>;
+}
 #define LL_BY_OP(T, op) \
-  ((op) == RED_SUM ? llFn<T, RED_SUM>() : (op) == RED_PROD ? llFn<T, RED_PROD>() : (op) == RED_MAX ? llFn<T, RED_MAX>() : llFn<T, RED_MIN>())
+  ((op) == RED_SUM ? llFn<T, RED_SUM>(batch) : (op) == RED_PROD ? llFn<T, RED_PROD>(batch) : (op) == RED_MAX ? llFn<T, RED_MAX>(batch) : llFn<T, RED_MIN>(batch))
 
-const void* llReduceKernelFn(ncclDataType_t type, int op) {
+static const void* llAnyFn(ncclDataType_t type, int op, bool batch) {
   switch (type) {
     case ncclInt8: return LL_BY_OP(int8_t, op);
     case ncclUint8: return LL_BY_OP(uint8_t, op);
@@ -264,6 +336,8 @@ const void* llReduceKernelFn(ncclDataType_t type, int op) {
     default: return nullptr;
   }
 }
+const void* llReduceKernelFn(ncclDataType_t type, int op) { return llAnyFn(type, op, false); }
+const void* llReduceBatchKernelFn(ncclDataType_t type, int op) { return llAnyFn(type, op, true); }
 const void* llCopyKernelFn() { return (const void*)llCopyKernel; }
 
 }  // namespace b200

@@ -1,5 +1,5 @@
-// Network backend choice: an external plugin (NCCL_NET_PLUGIN) exporting ncclNetPlugin_v12, or
-// the built-in TCP backend. NCCL_NET=<name> insists on one backend by name.
+// Network backend choice: an external plugin (NCCL_NET_PLUGIN) exporting ncclNetPlugin_v12 (or an
+// earlier table down to v8, wrapped by net_compat.cc), or the built-in TCP backend. NCCL_NET=<name> insists on one backend by name.
 // Reference parity: src/plugin/net.cc:60-495 (external first, then internal backends; name match
 // against NCCL_NET), src/plugin/net/net_v12.cc.
 #include <mutex>
@@ -20,10 +20,15 @@ ncclResult_t netSelect(ncclNet_t** net, bool* external) {
     std::string resolved;
     void* lib = pluginOpen(PLUGIN_NET, &resolved);
     ncclNet_t* ext = lib ? (ncclNet_t*)pluginSymbol(lib, NCCL_NET_PLUGIN_SYMBOL) : nullptr;
+    if (lib && !ext) {
+      int version = 0;
+      ext = netCompatWrap(lib, &version);   // v11 ... v8 behind an adapter with the current signature
+      if (ext) INFO(SUB_NET | SUB_INIT, "net plugin %s speaks interface v%d: loaded through an adapter", resolved.c_str(), version);
+    }
     gCollNet = lib ? (ncclCollNet_t*)pluginSymbol(lib, NCCL_COLLNET_PLUGIN_SYMBOL) : nullptr;
     if (gCollNet) INFO(SUB_NET | SUB_INIT, "net plugin %s offers the collective network %s", resolved.c_str(), gCollNet->name ? gCollNet->name : "?");
     if (lib && !ext && gCollNet) INFO(SUB_NET | SUB_INIT, "net plugin %s has no point-to-point table (%s): point-to-point traffic stays on the built-in backend", resolved.c_str(), NCCL_NET_PLUGIN_SYMBOL);
-    else if (lib && !ext) WARN("net plugin %s does not export %s (older interfaces are not supported); using the built-in backend", resolved.c_str(), NCCL_NET_PLUGIN_SYMBOL);
+    else if (lib && !ext) WARN("net plugin %s exports none of ncclNetPlugin_v12 ... ncclNetPlugin_v8; using the built-in backend", resolved.c_str());
     if (ext && wantName && *wantName && strcasecmp(wantName, ext->name) != 0 && strcasecmp(wantName, netSocketBackend.name) == 0) ext = nullptr;
     if (ext) {
       int ndev = 0;

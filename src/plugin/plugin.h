@@ -27,6 +27,9 @@ const char* pluginKindName(PluginKind kind);
 
 void pluginLogger(ncclDebugLogLevel level, unsigned long flags, const char* file, int line, const char* fmt, ...);
 
+// ---- net plugin of an earlier interface (v11 ... v8): adapter with the current signature, or null (net_compat.cc)
+ncclNet_t* netCompatWrap(void* lib, int* version);
+
 // ---- env plugin: consulted by every parameter read (core/param.cc)
 void envPluginInit();                       // idempotent; called before the first parameter is read
 const char* envPluginGet(const char* name); // value from the plugin, or from getenv() when none is loaded
@@ -37,6 +40,10 @@ struct TunerState {
   void* lib = nullptr;
   ncclTuner_v6_t* v6 = nullptr;
   ncclTuner_v5_t* v5 = nullptr;
+  ncclTuner_v4_t* v4 = nullptr;   // older interfaces: same roles, fewer arguments
+  ncclTuner_v3_t* v3 = nullptr;
+  ncclTuner_v2_t* v2 = nullptr;
+  int version = 0;
   void* ctx = nullptr;
   std::string name;
 };

@@ -6,6 +6,7 @@
 //   PAT                 -> direct peer (two-shot) kernels     channel count -> CTA count
 // Reference parity: src/plugin/tuner.cc:20-118, tuner/tuner_v5.cc, tuner_v6.cc; cost table built
 // the way src/enqueue.cc (getAlgoInfo, updateCollCostTable) does before calling getCollInfo.
+#include "../mem/symmetric.h"
 #include "../topo/topo.h"
 #include "plugin.h"
 
@@ -18,14 +19,18 @@ ncclResult_t tunerLoad(ncclComm* comm) {
   if (!lib) { (void)want; return ncclSuccess; }
   TunerState* ts = new TunerState;
   ts->lib = lib;
-  ts->v6 = (ncclTuner_v6_t*)pluginSymbol(lib, "ncclTunerPlugin_v6");
-  if (!ts->v6) ts->v5 = (ncclTuner_v5_t*)pluginSymbol(lib, "ncclTunerPlugin_v5");
-  if (!ts->v6 && !ts->v5) {
-    WARN("tuner plugin %s exports neither ncclTunerPlugin_v6 nor ncclTunerPlugin_v5 (older interfaces are not supported)", resolved.c_str());
+  // newest interface the library exports, down to v2
+  if ((ts->v6 = (ncclTuner_v6_t*)pluginSymbol(lib, "ncclTunerPlugin_v6"))) ts->version = 6;
+  else if ((ts->v5 = (ncclTuner_v5_t*)pluginSymbol(lib, "ncclTunerPlugin_v5"))) ts->version = 5;
+  else if ((ts->v4 = (ncclTuner_v4_t*)pluginSymbol(lib, "ncclTunerPlugin_v4"))) ts->version = 4;
+  else if ((ts->v3 = (ncclTuner_v3_t*)pluginSymbol(lib, "ncclTunerPlugin_v3"))) ts->version = 3;
+  else if ((ts->v2 = (ncclTuner_v2_t*)pluginSymbol(lib, "ncclTunerPlugin_v2"))) ts->version = 2;
+  if (!ts->version) {
+    WARN("tuner plugin %s exports none of ncclTunerPlugin_v6 ... ncclTunerPlugin_v2", resolved.c_str());
     delete ts;
     return ncclSuccess;
   }
-  ts->name = ts->v6 ? ts->v6->name : ts->v5->name;
+  ts->name = ts->v6 ? ts->v6->name : ts->v5 ? ts->v5->name : ts->v4 ? ts->v4->name : ts->v3 ? ts->v3->name : ts->v2->name;
   ncclNvlDomainInfo_t dom = {comm->nNodes, comm->nRanks / std::max(comm->nNodes, 1), (comm->nRanks + comm->nNodes - 1) / std::max(comm->nNodes, 1)};
   ncclTunerConstants_t k;
   memset(&k, 0, sizeof(k));
@@ -39,15 +44,21 @@ ncclResult_t tunerLoad(ncclComm* comm) {
     k.perChMaxTreeBws[NCCL_BLACKWELL_COMPCAP_IDX][s] = 70.0;
     k.perChMaxNVLSTreeBws[NCCL_BLACKWELL_COMPCAP_IDX][s] = s == 1 ? 96.0 : 80.0;
   }
-  ncclResult_t r = ts->v6 ? ts->v6->init(&ts->ctx, comm->commHash, comm->nRanks, comm->nNodes, pluginLogger, &dom, &k)
-                          : ts->v5->init(&ts->ctx, comm->commHash, comm->nRanks, comm->nNodes, pluginLogger, &dom, &k);
+  ncclResult_t r;
+  switch (ts->version) {
+    case 6: r = ts->v6->init(&ts->ctx, comm->commHash, comm->nRanks, comm->nNodes, pluginLogger, &dom, &k); break;
+    case 5: r = ts->v5->init(&ts->ctx, comm->commHash, comm->nRanks, comm->nNodes, pluginLogger, &dom, &k); break;
+    case 4: r = ts->v4->init(comm->nRanks, comm->nNodes, pluginLogger, &ts->ctx); break;
+    case 3: r = ts->v3->init(comm->nRanks, comm->nNodes, pluginLogger, &ts->ctx); break;
+    default: r = ts->v2->init(comm->nRanks, comm->nNodes, pluginLogger, &ts->ctx); break;
+  }
   if (r != ncclSuccess) {
     WARN("tuner plugin %s failed to initialise (%d); built-in selection stays in charge", ts->name.c_str(), (int)r);
     delete ts;
     return ncclSuccess;
   }
   comm->tuner = ts;
-  INFO(SUB_TUNING, "tuner plugin %s (%s) attached to communicator %llx", ts->name.c_str(), resolved.c_str(), (unsigned long long)comm->commHash);
+  INFO(SUB_TUNING, "tuner plugin %s (%s, interface v%d) attached to communicator %llx", ts->name.c_str(), resolved.c_str(), ts->version, (unsigned long long)comm->commHash);
   return ncclSuccess;
 }
 
@@ -56,6 +67,9 @@ void tunerUnload(ncclComm* comm) {
   if (!ts) return;
   if (ts->v6 && ts->v6->finalize) ts->v6->finalize(ts->ctx);
   else if (ts->v5 && ts->v5->finalize) ts->v5->finalize(ts->ctx);
+  else if (ts->v4 && ts->v4->destroy) ts->v4->destroy(ts->ctx);
+  else if (ts->v3 && ts->v3->destroy) ts->v3->destroy(ts->ctx);
+  else if (ts->v2 && ts->v2->destroy) ts->v2->destroy(ts->ctx);
   delete ts;   // the library stays mapped: other communicators may use it
   comm->tuner = nullptr;
 }
@@ -73,10 +87,28 @@ bool tunerPick(ncclComm* comm, int func, size_t bytes, int numPipeOps, bool regi
     }
   }
   int nChannels = 0;
-  auto fn = ts->v6 ? ts->v6->getCollInfo : ts->v5->getCollInfo;
-  if (fn(ts->ctx, (ncclFunc_t)func, bytes, numPipeOps, rows, NCCL_NUM_ALGORITHMS, NCCL_NUM_PROTOCOLS, registered ? 1 : 0, &nChannels) != ncclSuccess) return false;
   int bestA = -1, bestP = -1;
   float best = 0;
+  ncclResult_t rc;
+  switch (ts->version) {
+    case 6: rc = ts->v6->getCollInfo(ts->ctx, (ncclFunc_t)func, bytes, numPipeOps, rows, NCCL_NUM_ALGORITHMS, NCCL_NUM_PROTOCOLS, registered ? 1 : 0, &nChannels); break;
+    case 5: rc = ts->v5->getCollInfo(ts->ctx, (ncclFunc_t)func, bytes, numPipeOps, rows, NCCL_NUM_ALGORITHMS, NCCL_NUM_PROTOCOLS, registered ? 1 : 0, &nChannels); break;
+    case 4: rc = ts->v4->getCollInfo(ts->ctx, (ncclFunc_t)func, bytes, numPipeOps, rows, NCCL_NUM_ALGORITHMS, NCCL_NUM_PROTOCOLS, registered ? 1 : 0, &nChannels); break;
+    case 3: rc = ts->v3->getCollInfo(ts->ctx, (ncclFunc_t)func, bytes, numPipeOps, rows, NCCL_NUM_ALGORITHMS, NCCL_NUM_PROTOCOLS, &nChannels); break;
+    default: {
+      // v2 answers with one (algorithm, protocol) pair; undefined values leave the choice to the library
+      int a2 = NCCL_ALGO_UNDEF, p2 = NCCL_PROTO_UNDEF;
+      const bool nvls = comm->sym && comm->sym->mcUsable;
+      rc = ts->v2->getCollInfo(ts->ctx, (ncclFunc_t)func, bytes, 0, nvls ? 1 : 0, numPipeOps, &a2, &p2, &nChannels);
+      if (rc == ncclSuccess && (a2 < 0 || a2 >= NCCL_NUM_ALGORITHMS || p2 < 0 || p2 >= NCCL_NUM_PROTOCOLS)) return false;
+      if (rc == ncclSuccess) {
+        for (int a = 0; a < NCCL_NUM_ALGORITHMS; ++a)
+          for (int p = 0; p < NCCL_NUM_PROTOCOLS; ++p) table[a][p] = (a == a2 && p == p2) ? 0.0f : (float)NCCL_ALGO_PROTO_IGNORE;
+      }
+      break;
+    }
+  }
+  if (rc != ncclSuccess) return false;
   for (int a = 0; a < NCCL_NUM_ALGORITHMS; ++a)
     for (int p = 0; p < NCCL_NUM_PROTOCOLS; ++p) {
       if (table[a][p] < 0) continue;

@@ -103,7 +103,18 @@ def _reference(inputs, op, dtype):
     return acc.to(dtype)
 
 
+def _is_fp8(dtype):
+    return dtype in (getattr(torch, "float8_e4m3fn", None), getattr(torch, "float8_e5m2", None))
+
+
 def _close(got, want, dtype):
+    if _is_fp8(dtype):
+        # fp32 accumulation in rank order, one rounding to fp8: the reference rounds the same sum with
+        # PyTorch's conversion, so results agree except where the two roundings break a tie differently
+        # (one fp8 step: 2^-3 relative for e4m3, 2^-2 for e5m2)
+        g, w = got.float(), want.float()
+        step = 2 ** -3 if dtype == torch.float8_e4m3fn else 2 ** -2
+        return bool(((g - w).abs() <= step * w.abs() + 2 ** -9).all())
     if not dtype.is_floating_point or dtype in (torch.float32, torch.float64):
         # identical accumulation order and type: only fused multiply-add contraction can differ
         if dtype.is_floating_point:
@@ -135,7 +146,17 @@ REDUCE_CASES = [
     (8, torch.int8, "min", 333),
     (2, torch.float32, "sum", 1),
     (8, torch.bfloat16, "sum", 7),
-]
+    (8, torch.float16, "max", 30001),
+    (3, torch.float64, "min", 4099),
+    (5, torch.int64, "sum", 20011),
+    (8, torch.float64, "avg", 1025),
+    (6, torch.int64, "prod", 301),
+] + ([
+    (8, torch.float8_e4m3fn, "sum", 65543),
+    (4, torch.float8_e5m2, "sum", 4099),
+    (3, torch.float8_e4m3fn, "max", 1000),
+    (8, torch.float8_e5m2, "min", 515),
+] if hasattr(torch, "float8_e4m3fn") else [])
 
 
 @pytest.mark.parametrize("n,dtype,op,count", REDUCE_CASES)
@@ -375,5 +396,84 @@ def test_flagged_line_copy_collectives(emu_lib, n, nbytes):
             recv = [torch.zeros(nbytes * n, dtype=torch.uint8, device="cuda") for _ in range(n)]
             assert emu_lib.b200EmuCopy(ctx, FUNC_GATHER, MODE_LL, nbytes, _ptrs(send), _ptrs(recv), root, 1) == 0
             assert torch.equal(recv[root], torch.cat(send))
+    finally:
+        emu_lib.b200EmuDestroy(ctx)
+
+
+def _sweep_counts():
+    return list(range(0, 261, 13)) + [1, 2, 3, 7, 8, 9, 15, 16, 17, 255, 256, 257] + list(range(4090, 4101))
+
+
+@pytest.mark.parametrize("n", [2, 3, 5, 8])
+@pytest.mark.parametrize("kernel", [KERNEL_REDUCE_P2P, KERNEL_ALLREDUCE_LL])
+def test_allreduce_count_and_alignment_sweep(emu_lib, n, kernel):
+    """Small counts (0 ... 260 and around 4096) at byte offsets 0 / 2 / 4 / 8 of the inputs and outputs,
+    bf16 and fp32, with a band of a poison pattern on either side of every output: the kernel must
+    write exactly the requested elements."""
+    ctx = emu_lib.b200EmuCreate(n, 5000)
+    assert ctx
+    POISON = 0x5A
+    try:
+        for dtype in (torch.bfloat16, torch.float32):
+            es = torch.empty(0, dtype=dtype).element_size()
+            for count in sorted(set(_sweep_counts())):
+                if count == 0:
+                    continue   # the public API returns before launching anything for empty messages
+                for off_bytes in (0, 2, 4, 8):
+                    if off_bytes % es:
+                        continue
+                    off = off_bytes // es
+                    band = 64 // es
+                    src = _make_inputs(n, count, dtype, 1000 + count + off, "sum")
+                    ins_base = [torch.zeros(count + off + band, dtype=dtype, device="cuda") for _ in range(n)]
+                    ins = [b[off:off + count] for b in ins_base]
+                    for b, x in zip(ins, src):
+                        b.copy_(x)
+                    outs_base = [torch.empty(band + off + count + band, dtype=dtype, device="cuda") for _ in range(n)]
+                    for b in outs_base:
+                        b.view(torch.uint8).fill_(POISON)
+                    outs = [b[band + off:band + off + count] for b in outs_base]
+                    ctas = 2 if kernel == KERNEL_REDUCE_P2P else 1
+                    rc = emu_lib.b200EmuReduce(ctx, kernel, FUNC_ALLREDUCE, _types()[dtype], 0, count, _ptrs(ins), _ptrs(outs), 0, ctas)
+                    assert rc == 0, (count, off_bytes)
+                    want = _reference(src, "sum", dtype)
+                    for r in range(n):
+                        assert _close(outs[r], want, dtype), (str(dtype), count, off_bytes, r)
+                        raw = outs_base[r].view(torch.uint8)
+                        lo = (band + off) * es
+                        hi = lo + count * es
+                        assert bool((raw[:lo] == POISON).all()) and bool((raw[hi:] == POISON).all()), ("wrote outside", str(dtype), count, off_bytes, r)
+    finally:
+        emu_lib.b200EmuDestroy(ctx)
+
+
+@pytest.mark.parametrize("n,dtype,op", [(8, torch.bfloat16, "sum"), (3, torch.float32, "max"), (5, torch.float16, "avg")])
+def test_batched_allreduce_one_launch(emu_lib, n, dtype, op):
+    """A group of small all-reduces (ragged counts, odd offsets) carried by one launch of the flagged-line kernel."""
+    emu_lib.b200EmuReduceBatch.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_size_t),
+                                           ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_void_p),
+                                           ctypes.POINTER(ctypes.c_void_p), ctypes.c_int]
+    ctx = emu_lib.b200EmuCreate(n, 5000)
+    assert ctx
+    try:
+        es = torch.empty(0, dtype=dtype).element_size()
+        counts = [1, 7, 2048, 3, 513, 4096, 33, 1000, 5, 2047] * 3
+        offs, pos = [], 0
+        for c in counts:
+            offs.append(pos)
+            pos += c + 3          # three elements of padding: items start at odd addresses
+        total = pos
+        for rep in range(2):
+            ins = _make_inputs(n, total, dtype, 77 + rep, op)
+            outs = [torch.zeros(total, dtype=dtype, device="cuda") for _ in range(n)]
+            want = _reference(ins, op, dtype)
+            ca = (ctypes.c_size_t * len(counts))(*counts)
+            oa = (ctypes.c_size_t * len(counts))(*[o * es for o in offs])
+            rc = emu_lib.b200EmuReduceBatch(ctx, _types()[dtype], OPS[op], len(counts), ca, oa, oa, _ptrs(ins), _ptrs(outs), 4)
+            assert rc == 0
+            for r in range(n):
+                for c, o in zip(counts, offs):
+                    assert _close(outs[r][o:o + c], want[o:o + c], dtype), (r, c, o)
+                    assert bool((outs[r][o + c:o + c + 3].float() == 0).all()), "padding between items was written"
     finally:
         emu_lib.b200EmuDestroy(ctx)

@@ -102,6 +102,70 @@ def test_back_to_back_small_collectives(mc):
         assert res[r]["bad"] == 0 and res[r]["err"] == 0, res[r]
 
 
+def _types_rank(rank, nranks, uid, algo):
+    """All-reduce and reduce-scatter of every type / operator pair that has a multimem.ld_reduce form
+    (plus one without, which must fall back), on registered buffers, checked on the device."""
+    import os
+    import torch
+    os.environ["NCCL_ALGO"] = algo
+    torch.cuda.set_device(rank)
+    from nccl_b200 import Communicator
+    comm = Communicator(nranks, rank, uid)
+    n = nranks
+    f8 = [torch.float8_e4m3fn, torch.float8_e5m2] if hasattr(torch, "float8_e4m3fn") else []
+    cases = [(torch.float16, "sum"), (torch.float16, "max"), (torch.float16, "min"), (torch.bfloat16, "min"), (torch.float64, "sum"),
+             (torch.int64, "sum"), (torch.int64, "max"), (torch.int64, "min"), (torch.int32, "min"), (torch.float32, "max")] + [(t, "sum") for t in f8]
+    bad = []
+    numel = 8192 * n + 16 * n
+
+    def make(p, dtype):
+        g = torch.Generator().manual_seed(500 + p)
+        if dtype.is_floating_point:
+            return (torch.randn(numel, generator=g).clamp(-2, 2)).to(dtype)
+        return torch.randint(-1000, 1000, (numel,), generator=g).to(dtype)
+
+    for dtype, op in cases:
+        x = _sym_tensor(comm, numel, dtype)
+        y = _sym_tensor(comm, numel, dtype)
+        x.copy_(make(rank, dtype))
+        comm.all_reduce(x, y, op=op)
+        z = _sym_tensor(comm, numel // n, dtype)
+        comm.reduce_scatter(x, z, op=op)
+        torch.cuda.synchronize()
+        ins = [make(p, dtype).cuda() for p in range(n)]
+        acc_t = torch.float64 if dtype == torch.float64 else torch.float32 if dtype.is_floating_point else torch.int64
+        acc = ins[0].to(acc_t)
+        for t in ins[1:]:
+            acc = acc + t.to(acc_t) if op == "sum" else torch.maximum(acc, t.to(acc_t)) if op == "max" else torch.minimum(acc, t.to(acc_t))
+        if dtype in f8:
+            # the switch adds fp8 lanes with an fp16 accumulator: allow one fp8 step plus the accumulator's rounding
+            step = 2 ** -3 if dtype == torch.float8_e4m3fn else 2 ** -2
+            okf = lambda got, want: bool(((got.float() - want).abs() <= step * want.abs() + 2 ** -5).all())   # noqa: E731
+        elif dtype.is_floating_point and op == "sum":
+            tol = {torch.float16: 2 ** -9, torch.float64: 1e-12}[dtype]
+            okf = lambda got, want: torch.allclose(got.to(acc_t), want, rtol=tol, atol=tol)   # noqa: E731
+        else:
+            okf = lambda got, want: torch.equal(got.to(acc_t), want)   # noqa: E731
+        if not okf(y, acc):
+            bad.append(("all_reduce", str(dtype), op))
+        per = numel // n
+        if not okf(z, acc[rank * per:(rank + 1) * per]):
+            bad.append(("reduce_scatter", str(dtype), op))
+    err = comm.async_error()
+    comm.destroy()
+    return {"bad": bad, "err": err}
+
+
+@pytest.mark.parametrize("algo", ["NVLS", "P2P", "LL"])
+def test_reduction_types_on_gpus(algo):
+    n = min(_ngpus(), 8)
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    res = run_ranks(_types_rank, n, args=(algo,), timeout=300)
+    for r in range(n):
+        assert res[r]["bad"] == [] and res[r]["err"] == 0, res[r]
+
+
 def _mgmt_rank(rank, nranks, uid):
     import ctypes
     import torch
@@ -160,6 +224,13 @@ def _mgmt_rank(rank, nranks, uid):
     comm.all_reduce(w)
     torch.cuda.synchronize()
     out["after_resume"] = float(w[0])
+    # signals start again from zero with the new resource window: one more put / signal / wait round
+    src.fill_(200.0 + rank)
+    _lib.check(lib.ncclPutSignal(src.data_ptr(), 1024, FP32, nxt, win, 0, 3, 0, 0, comm.handle, st), "ncclPutSignal", lib)
+    d = Desc(1, prv, 3, 0)
+    _lib.check(lib.ncclWaitSignal(1, ctypes.byref(d), comm.handle, st), "ncclWaitSignal", lib)
+    torch.cuda.synchronize()
+    out["put_after_resume"] = float(win_t[5])
     out["suspendable_before"] = before
     assert comm.async_error() == 0
     comm.destroy()
@@ -180,3 +251,4 @@ def test_split_premul_signals_suspend():
         assert o["put"] == 100.0 + (r - 1) % n
         assert o["suspended_flag"] == 1 and o["suspendable_after"] == 0 and o["suspendable_before"] > 0
         assert o["after_resume"] == float(n)
+        assert o["put_after_resume"] == 200.0 + (r - 1) % n
