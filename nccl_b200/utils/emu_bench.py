@@ -3,7 +3,7 @@
 but every "remote" access stays on this device. Useful to profile a kernel's own overheads.
 
     python -m nccl_b200.utils.emu_bench --ranks 4 --count 262144 --kernel p2p --ctas 16 --iters 100
-    python -m nccl_b200.utils.emu_bench --ranks 4 --count 262144 --kernel push        # all-gather: push | pull | llcopy
+    python -m nccl_b200.utils.emu_bench --ranks 4 --count 262144 --kernel push        # all-gather: push | pull | bpush | bpull | llcopy
     python -m nccl_b200.utils.emu_bench --ranks 4 --count 262144 --kernel sendrecv    # ring of grouped send / receive
 """
 import argparse
@@ -19,8 +19,8 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--ranks", type=int, default=4)
     ap.add_argument("--count", type=int, default=262144, help="fp32 elements per rank")
-    ap.add_argument("--kernel", default="p2p", choices=("p2p", "ll", "push", "pull", "llcopy", "sendrecv"),
-                    help="p2p / ll: all-reduce kernels; push / pull / llcopy: all-gather through the copy kernels; sendrecv: mailbox ring")
+    ap.add_argument("--kernel", default="p2p", choices=("p2p", "ll", "push", "pull", "bpush", "bpull", "llcopy", "sendrecv"),
+                    help="p2p / ll: all-reduce kernels; push / pull / llcopy: all-gather through the copy kernels (bpush / bpull: moved by the bulk-copy engines); sendrecv: mailbox ring")
     ap.add_argument("--ctas", type=int, default=16)
     ap.add_argument("--iters", type=int, default=100)
     a = ap.parse_args(argv)
@@ -43,10 +43,10 @@ def main(argv=None):
                                ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_size_t), ctypes.c_int]
     kernel = 0 if a.kernel == "p2p" else 1
     nbytes = a.count * 4
-    if a.kernel in ("push", "pull", "llcopy"):
+    if a.kernel in ("push", "pull", "bpush", "bpull", "llcopy"):
         gathered = [torch.zeros(a.count * n, device="cuda") for _ in range(n)]
         pgat = (ctypes.c_void_p * n)(*[t.data_ptr() for t in gathered])
-        mode = {"push": MODE_PUSH, "pull": MODE_PULL, "llcopy": MODE_LL}[a.kernel]
+        mode = {"push": MODE_PUSH, "pull": MODE_PULL, "bpush": MODE_PUSH | 4, "bpull": MODE_PULL | 4, "llcopy": MODE_LL}[a.kernel]
 
         def call():
             rc = lib.b200EmuCopy(ctx, 2, mode, nbytes, pin, pgat, 0, a.ctas)   # 2 = all-gather
@@ -80,7 +80,7 @@ def main(argv=None):
         call()
     e1.record()
     torch.cuda.synchronize()
-    if a.kernel in ("push", "pull", "llcopy"):
+    if a.kernel in ("push", "pull", "bpush", "bpull", "llcopy"):
         err = (gathered[n - 1] - torch.cat(ins)).abs().max().item()
     elif a.kernel == "sendrecv":
         err = (outs[0] - ins[n - 1]).abs().max().item()

@@ -4,8 +4,8 @@ the selection table that the library uses to pick a kernel (NCCL_TUNING_FILE for
     torchrun --nproc-per-node N -m nccl_b200.utils.tune --out tuning_nN.json
 
 For each (collective, size) it times: flagged lines (LL), peer loads/stores (P2P: push and pull
-for the copy collectives), multimem (NVLS two-shot, NVLS1 one-shot all-reduce, MC copies), each at
-several CTA counts, on registered symmetric buffers; device-timed, max over ranks. Two switches
+for the copy collectives), multimem (NVLS two-shot, NVLS1 one-shot all-reduce, MC copies), the copy collectives also moved by
+the bulk-copy engines (BPUSH / BPULL / BMC: few CTAs), each at several CTA counts, on registered symmetric buffers; device-timed, max over ranks. Two switches
 that are global per rank count are measured as well: publishing flagged lines with one multimem.st
 ("+mc" variants) and arriving at barriers with one multimem.red ("+mb" variants); each is turned
 on when the variants it affects are faster with it on average. The table then takes, per size, the
@@ -23,7 +23,7 @@ from ..core import BF16, FP32
 from . import perf
 
 ALGO_AUTO, ALGO_LL, ALGO_P2P, ALGO_NVLS, ALGO_NVLS1 = -1, 1, 2, 3, 8
-MODE_PUSH, MODE_PULL, MODE_MC = 0, 1, 2
+MODE_PUSH, MODE_PULL, MODE_MC, MODE_BULK = 0, 1, 2, 4
 
 
 def size_list(limit, fine_lo=64 << 10, fine_hi=128 << 20):
@@ -117,6 +117,12 @@ def main(argv=None):
                             row["PULL/%d%s" % (c, sfx)] = measure(coll, nb, ALGO_P2P, MODE_PULL)
                             if coll in ("all_gather", "broadcast") and block % 16 == 0:
                                 row["MC/%d%s" % (c, sfx)] = measure(coll, nb, ALGO_NVLS, MODE_MC)
+                            # bulk-copy engines: worth it where a CTA has several 32 KiB chunks to stream
+                            if block % 16 == 0 and block >= c * (64 << 10) and c <= 32:
+                                row["BPUSH/%d%s" % (c, sfx)] = measure(coll, nb, ALGO_P2P, MODE_PUSH | MODE_BULK)
+                                row["BPULL/%d%s" % (c, sfx)] = measure(coll, nb, ALGO_P2P, MODE_PULL | MODE_BULK)
+                                if coll in ("all_gather", "broadcast"):
+                                    row["BMC/%d%s" % (c, sfx)] = measure(coll, nb, ALGO_NVLS, MODE_MC | MODE_BULK)
             toggles(False, False)
             best = min(row, key=row.get)
             factor = perf.bus_factor(coll, n)

@@ -27,6 +27,8 @@ B200_PARAM(CopyUnroll, "B200_COPY_UNROLL", 4, "16-byte loads in flight per threa
 B200_PARAM(CopyCtasPerSm, "B200_COPY_CTAS_PER_SM", 16, "Grid size of the local copy kernel in CTAs per SM")
 B200_PARAM(LLMulticast, "B200_LL_MC_MIN_RANKS", -1, "Flagged-line all-reduce / all-gather publish each line with one multimem.st instead of one store per peer from this many ranks on (0 = never, -1 = from the selection table)")
 B200_PARAM(CopyKernel, "B200_COPY_KERNEL", 0, "One-rank copy path: 0 = vector loads and stores, 1 = bulk-copy engines through shared memory (messages of 1 MiB and more)")
+B200_PARAM(StagePipeline, "B200_STAGE_PIPELINE", 1, "Reductions on unregistered buffers overlap the copies through the staging area with the kernels (two halves, side stream)")
+B200_PARAM(StagePipelineMin, "B200_STAGE_PIPELINE_MIN", 134217728, "Smallest message in bytes that is pipelined through the staging area")
 B200_PARAM(LaunchPdl, "B200_PDL", 1, "Launch collectives with programmatic stream serialisation (the next kernel of the stream is scheduled while the previous one drains)")
 B200_PARAM(BarrierMulticast, "B200_BARRIER_MC_MIN_RANKS", -1, "Cross-GPU barriers arrive with one multimem.red on a multicast alias of the flag page from this many ranks on (0 = never, -1 = from the selection table)")
 
@@ -115,8 +117,11 @@ ncclResult_t devPlaneCreate(ncclComm* comm) {
   dp->barrierMcMin = paramBarrierMulticast() >= 0 ? (int)paramBarrierMulticast() : dp->tune.barrierMcMin;
   dp->llMcMin = paramLLMulticast() >= 0 ? (int)paramLLMulticast() : dp->tune.llMcMin;
   CUDACHECK(cudaEventCreateWithFlags(&dp->lastEvent, cudaEventDisableTiming));
+  CUDACHECK(cudaStreamCreateWithFlags(&dp->sideStream, cudaStreamNonBlocking));
+  for (auto& e : dp->pipeEv) CUDACHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   // function attributes are per device: set with this communicator's device current
   CUDACHECK(cudaFuncSetAttribute(localBulkCopyKernelFn(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)localBulkCopySmemBytes()));
+  CUDACHECK(cudaFuncSetAttribute(copyBulkKernelFn(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)copyBulkSmemBytes()));
   const size_t privWords = kPrivWords + 2 * kMaxRanks * kSignalsPerPeer;
   CUDACHECK(cudaMalloc(&dp->priv, privWords * sizeof(uint32_t)));
   CUDACHECK(cudaMemset(dp->priv, 0, privWords * sizeof(uint32_t)));
@@ -168,6 +173,8 @@ void devPlaneDestroy(ncclComm* comm) {
   if (dp->resBase) memFree(dp->resBase);
   if (dp->priv) cudaFree(dp->priv);
   if (dp->lastEvent) cudaEventDestroy(dp->lastEvent);
+  for (auto& e : dp->pipeEv) if (e) cudaEventDestroy(e);
+  if (dp->sideStream) cudaStreamDestroy(dp->sideStream);
   if (dp->hostStage) cudaFreeHost(dp->hostStage);
   (void)cudaGetLastError();
   delete dp;
@@ -322,13 +329,13 @@ static thread_local const char* tLastProto = "SIMPLE";
 static thread_local int tLastCtas = 0;
 
 static ncclResult_t launchColl(ncclComm* comm, const void* fn, CollArgs* a, int ctas, cudaStream_t stream, const char* algo = "P2P",
-                               const char* proto = "SIMPLE") {
+                               const char* proto = "SIMPLE", int threads = kCtaThreads, size_t smem = 0) {
   if (!fn) { WARN("no kernel for this data type / operator"); return ncclInvalidUsage; }
   comm->devPlane->launches++;
   tLastAlgo = algo;
   tLastProto = proto;
   tLastCtas = ctas;
-  return launchKernel(fn, dim3(ctas), dim3(kCtaThreads), 0, a, stream, false, paramLaunchPdl() != 0);
+  return launchKernel(fn, dim3(ctas), dim3(threads), smem, a, stream, false, paramLaunchPdl() != 0);
 }
 
 static ncclResult_t scaleCopy(ncclComm* comm, ncclDataType_t type, const void* src, void* dst, size_t count, const DevOp& op,
@@ -444,16 +451,57 @@ static ncclResult_t runReduction(ncclComm* comm, const Task& t) {
   Aliases recvAl = needRecvAll ? aliasesOf(comm, t.recv, bytes) : Aliases{};
   const bool direct = sendAl.ok && (!needRecvAll || recvAl.ok);
 
-  // work is cut in pieces that fit the staging area when staging is needed
-  const size_t stageElems = dp->stageBytes / es / (16 / es > 0 ? 1 : 1);
+  // Work on buffers outside registered windows goes through the staging area of the resource window in
+  // pieces. Large messages are pipelined over the two halves of the area: a side stream copies piece
+  // k + 1 in (and piece k - 1 out) while the kernel of piece k runs, so the copies cost nothing but
+  // the first and the last one. Each kernel opens with a barrier (every rank's piece is in place) and
+  // closes with one (nobody reads this rank's half any more), which is all the cross-rank ordering
+  // the reuse of a half needs; events order the two local streams.
   size_t pieceTotal = total;        // elements (over all slices) handled per launch
+  bool pipelined = false;
+  size_t halfBytes = 0;
   if (!direct) {
-    size_t cap = stageElems / n * n;  // keep reduce-scatter pieces divisible by n
-    cap = cap / (16 * n) * (16 * n);
+    const size_t stageElems = dp->stageBytes / es;
+    size_t cap = stageElems / (16 * n) * (16 * n);   // reduce-scatter pieces stay divisible by n, slices by 16 bytes
+    pipelined = paramStagePipeline() != 0 && bytes >= (size_t)paramStagePipelineMin() && dp->sideStream != nullptr;
+    if (pipelined) {
+      halfBytes = dp->stageBytes / 2 / 4096 * 4096;
+      cap = halfBytes / es / (16 * n) * (16 * n);
+    }
     if (pieceTotal > cap) pieceTotal = cap;
+    if (pipelined && pieceTotal >= total) pipelined = false;
   }
-  for (size_t done = 0; done < total;) {
+  char* const stageBase = dp->resBase ? (char*)dp->resBase + dp->offStage : nullptr;
+  cudaStream_t side = pipelined ? dp->sideStream : t.stream;
+  // copy-in of the piece that starts at element `done` into the half `h` of the staging area
+  auto copyIn = [&](size_t done, size_t cur, int h, cudaStream_t st) -> ncclResult_t {
+    char* dstp = stageBase + (size_t)h * halfBytes;
+    if (t.func == FUNC_REDUCESCATTER) {
+      const size_t rsPiece = cur / n, rsDone = done / n;
+      // rows of rsPiece elements, one per destination rank, gathered from a pitch of t.count
+      if (op.premul) {
+        for (int r = 0; r < n; ++r)
+          NCCLCHECK(scaleCopy(comm, t.type, (const char*)t.send + ((size_t)r * t.count + rsDone) * es, dstp + (size_t)r * rsPiece * es, rsPiece, op, st));
+      } else {
+        CUDACHECK(cudaMemcpy2DAsync(dstp, rsPiece * es, (const char*)t.send + rsDone * es, t.count * es, rsPiece * es, n, cudaMemcpyDeviceToDevice, st));
+      }
+    } else if (op.premul) {
+      NCCLCHECK(scaleCopy(comm, t.type, (const char*)t.send + done * es, dstp, cur, op, st));
+    } else {
+      CUDACHECK(cudaMemcpyAsync(dstp, (const char*)t.send + done * es, cur * es, cudaMemcpyDeviceToDevice, st));
+    }
+    return ncclSuccess;
+  };
+  if (pipelined) {
+    CUDACHECK(cudaEventRecord(dp->pipeEv[0], t.stream));          // fork: the side stream sees what the caller queued before
+    CUDACHECK(cudaStreamWaitEvent(side, dp->pipeEv[0], 0));
+    NCCLCHECK(copyIn(0, std::min(pieceTotal, total), 0, side));
+    CUDACHECK(cudaEventRecord(dp->pipeEv[1], side));
+  }
+  int piece = 0;
+  for (size_t done = 0; done < total; ++piece) {
     size_t cur = std::min(pieceTotal, total - done);   // all-reduce / reduce: elements; reduce-scatter: n * piece
+    const int h = pipelined ? (piece & 1) : 0;
     CollArgs a;
     baseArgs(comm, &a, t.func);
     a.scaleMode = op.scaleMode; a.scaleF = op.scaleF; a.scaleD = op.scaleD; a.intDiv = op.intDiv;
@@ -466,22 +514,19 @@ static ncclResult_t runReduction(ncclComm* comm, const Task& t) {
       out = recvAl;
       cur = total;
     } else {
-      // copy-in (fused with the pre-multiplication when there is one)
-      in = stageAliases(comm, 0);
+      in = stageAliases(comm, (size_t)h * halfBytes);
       out = in;
-      char* st = (char*)dp->resBase + dp->offStage;
-      if (t.func == FUNC_REDUCESCATTER) {
-        // rows of rsPiece elements, one per destination rank, gathered from a pitch of t.count
-        if (op.premul) {
-          for (int r = 0; r < n; ++r)
-            NCCLCHECK(scaleCopy(comm, t.type, (const char*)t.send + ((size_t)r * t.count + rsDone) * es, st + (size_t)r * rsPiece * es, rsPiece, op, t.stream));
-        } else {
-          CUDACHECK(cudaMemcpy2DAsync(st, rsPiece * es, (const char*)t.send + rsDone * es, t.count * es, rsPiece * es, n, cudaMemcpyDeviceToDevice, t.stream));
+      if (pipelined) {
+        // next piece into the other half, once the kernel that last used that half (piece - 1) is done
+        const size_t nextDone = done + cur;
+        if (nextDone < total) {
+          if (piece >= 1) CUDACHECK(cudaStreamWaitEvent(side, dp->pipeEv[3 + ((piece + 1) & 1)], 0));
+          NCCLCHECK(copyIn(nextDone, std::min(pieceTotal, total - nextDone), (piece + 1) & 1, side));
+          CUDACHECK(cudaEventRecord(dp->pipeEv[1 + ((piece + 1) & 1)], side));
         }
-      } else if (op.premul) {
-        NCCLCHECK(scaleCopy(comm, t.type, (const char*)t.send + done * es, st, cur, op, t.stream));
+        CUDACHECK(cudaStreamWaitEvent(t.stream, dp->pipeEv[1 + h], 0));
       } else {
-        CUDACHECK(cudaMemcpyAsync(st, (const char*)t.send + done * es, cur * es, cudaMemcpyDeviceToDevice, t.stream));
+        NCCLCHECK(copyIn(done, cur, 0, t.stream));
       }
     }
     // slices
@@ -519,10 +564,17 @@ static ncclResult_t runReduction(ncclComm* comm, const Task& t) {
     int ctas = clampCtas(comm, perRankBytes, useNvls ? dp->tune.nvlsCtas : dp->tune.p2pCtas);
     NCCLCHECK(launchColl(comm, reduceKernelFn(useNvls ? KERNEL_REDUCE_NVLS : KERNEL_REDUCE_P2P, t.type, op.red), &a, ctas, t.stream, useNvls ? "NVLS" : "P2P"));
     if (direct) break;
+    if (pipelined) CUDACHECK(cudaEventRecord(dp->pipeEv[3 + h], t.stream));   // kernel of this piece done: its half may be copied out / refilled
     // copy-out of the staged all-reduce
-    if (t.func == FUNC_ALLREDUCE)
-      CUDACHECK(cudaMemcpyAsync((char*)t.recv + done * es, (char*)dp->resBase + dp->offStage, cur * es, cudaMemcpyDeviceToDevice, t.stream));
+    if (t.func == FUNC_ALLREDUCE) {
+      if (pipelined) CUDACHECK(cudaStreamWaitEvent(side, dp->pipeEv[3 + h], 0));
+      CUDACHECK(cudaMemcpyAsync((char*)t.recv + done * es, stageBase + (size_t)h * halfBytes, cur * es, cudaMemcpyDeviceToDevice, side));
+    }
     done += cur;
+  }
+  if (pipelined) {
+    CUDACHECK(cudaEventRecord(dp->pipeEv[5], side));              // join: the caller's stream continues after the last copy
+    CUDACHECK(cudaStreamWaitEvent(t.stream, dp->pipeEv[5], 0));
   }
   return ncclSuccess;
 }
@@ -592,6 +644,7 @@ static ncclResult_t runCopyColl(ncclComm* comm, const Task& t) {
   if (B == 0) return ncclSuccess;
   int forced = forcedAlgo();
   int modeForce = tForceMode;
+  bool bulk = false;
   tPickCtas = 0;
   if (forced == ALGO_AUTO && modeForce < 0 && comm->tuner) {
     int a = ALGO_AUTO, c = 0;
@@ -605,6 +658,7 @@ static ncclResult_t runCopyColl(ncclComm* comm, const Task& t) {
     TunePick pk = tunePick(dp->tune, t.func, n, key);
     if (pk.valid) { forced = pk.algo; modeForce = pk.mode; tPickCtas = pk.ctas; }
   }
+  if (modeForce >= 0 && (modeForce & MODE_BULK)) { bulk = true; modeForce &= ~MODE_BULK; }
   if (forced == ALGO_RING && t.func == FUNC_ALLGATHER) return ringTreeRun(comm, t, forced);
   if (forced == ALGO_CE || (forced == ALGO_AUTO && dp->tune.ceMin && B >= dp->tune.ceMin)) {
     bool handled = false;
@@ -695,7 +749,12 @@ static ncclResult_t runCopyColl(ncclComm* comm, const Task& t) {
     }
     size_t moved = cur * ((t.func == FUNC_BROADCAST && mode != MODE_PUSH) ? 1 : (a.mode == MODE_MC ? 1 : n));
     int ctas = clampCtas(comm, moved, dp->tune.copyCtas);
-    NCCLCHECK(launchColl(comm, copyKernelFn(), &a, ctas, t.stream, a.mode == MODE_MC ? "NVLS" : a.mode == MODE_PULL ? "P2P_PULL" : "P2P_PUSH"));
+    const char* algoName = a.mode == MODE_MC ? "NVLS" : a.mode == MODE_PULL ? "P2P_PULL" : "P2P_PUSH";
+    if (bulk && v16 && cur % 16 == 0) {
+      NCCLCHECK(launchColl(comm, copyBulkKernelFn(), &a, ctas, t.stream, algoName, "BULK", 32, copyBulkSmemBytes()));
+    } else {
+      NCCLCHECK(launchColl(comm, copyKernelFn(), &a, ctas, t.stream, algoName));
+    }
   }
   return ncclSuccess;
 }

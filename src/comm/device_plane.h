@@ -40,6 +40,8 @@ struct DevicePlane {
   uint32_t* p2pSeq = nullptr;
   uint64_t* sigSeen = nullptr;
   cudaEvent_t lastEvent = nullptr;
+  cudaStream_t sideStream = nullptr;  // copies of pipelined staging run here, beside the kernels on the caller's stream
+  cudaEvent_t pipeEv[6] = {};         // fork | piece in place [2 halves] | kernel done [2 halves] | join
   cudaStream_t lastStream = nullptr;
   bool hasLast = false;
   int smCount = 0;

@@ -32,14 +32,14 @@ static void fillSyncEmu(EmuCtx* e, SyncArgs* s) {
   s->timeoutNs = e->timeoutNs;
 }
 
-static int coopLaunch(const void* fn, int ctas, int n, void* args) {
+static int coopLaunch(const void* fn, int ctas, int n, void* args, int threads = kCtaThreads, size_t smem = 0) {
   if (!fn) return ncclInvalidUsage;
   int dev = 0, sms = 0, perSm = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, fn, kCtaThreads, 0);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, fn, threads, smem);
   if (ctas * n > sms * std::max(perSm, 1)) { WARN("emulation: %d x %d CTAs cannot be co-resident", ctas, n); return ncclInvalidArgument; }
-  ncclResult_t r = launchKernel(fn, dim3(ctas, n), dim3(kCtaThreads), 0, args, 0, true);
+  ncclResult_t r = launchKernel(fn, dim3(ctas, n), dim3(threads), smem, args, 0, true);
   if (r != ncclSuccess) return r;
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) { WARN("emulation kernel failed: %s", cudaGetErrorString(e)); return ncclUnhandledCudaError; }
@@ -177,7 +177,8 @@ int b200EmuCopy(void* ctx, int func, int mode, size_t bytes, const void** send, 
   a.emu = 1;
   a.func = func;
   a.root = root;
-  a.mode = mode;
+  const bool bulk = mode >= 0 && mode != 3 && (mode & MODE_BULK);
+  a.mode = bulk ? (mode & ~MODE_BULK) : mode;
   a.count = bytes;
   a.sendStride = bytes;
   a.recvStride = bytes;
@@ -194,6 +195,11 @@ int b200EmuCopy(void* ctx, int func, int mode, size_t bytes, const void** send, 
   if (mode == 3) {  // flagged lines
     for (int p = 0; p < n; ++p) { a.ll[p] = e->ll[p]; a.llEpoch[p] = e->priv[p] + kBarrierSlots; }
     return coopLaunch(llCopyKernelFn(), ctas, n, &a);
+  }
+  if (bulk) {
+    if (!v16) return ncclInvalidArgument;
+    if (cudaFuncSetAttribute(copyBulkKernelFn(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)copyBulkSmemBytes()) != cudaSuccess) return ncclUnhandledCudaError;
+    return coopLaunch(copyBulkKernelFn(), ctas, n, &a, 32, copyBulkSmemBytes());
   }
   return coopLaunch(copyKernelFn(), ctas, n, &a);
 }

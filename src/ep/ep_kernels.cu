@@ -34,9 +34,11 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
   __shared__ int sCnt[kMaxRanks], sOff[kMaxRanks + 1];
   __shared__ int sIsLast;
   const int rank = ctaRank(a.emu, a.rank);
+  if (a.emu && ((a.absent >> rank) & 1u)) return;   // a rank that never joins (tests of the waits that run out)
   const int n = a.nRanks, H = a.hidden, K = a.topk, El = a.expertsPerRank, E = a.numExperts;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nWarps = kEpThreads / 32;
   uint32_t* st = a.state[rank];
+  uint32_t* mask = a.mask[rank];                    // may be null: nobody is ever left out
   const uint32_t epoch = st[0] + 1;
   const size_t slotBytes = epSlotBytes(H, a.fp8);
   const size_t payload = slotBytes - 16;
@@ -50,7 +52,8 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
   const size_t cntOff = (size_t)(epoch & 1) * ((size_t)El * n);
 
   // ---------------------------------------------------------------- send
-  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+  const bool sendPhase = (a.phases & 1) != 0, recvPhase = (a.phases & 2) != 0;
+  for (int t = blockIdx.x; sendPhase && t < T; t += gridDim.x) {
     const __nv_bfloat16* row = x + (size_t)t * H;
     if (a.fp8) {
       float* scales = (float*)(epSmem + H);
@@ -78,6 +81,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
       const long long e = a.topkIdx[rank][(size_t)t * K + k];
       if (e < 0 || e >= E) continue;
       const int dst = (int)(e / El), el = (int)(e % El);
+      if (mask && mask[dst]) continue;   // that rank is left out
       int s = 0;
       if (lane == 0) s = (int)atomicAdd(&st[kStCounters + e], 1u);
       s = __shfl_sync(0xffffffffu, s, 0);
@@ -91,8 +95,11 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
   // every CTA of this rank must be done before the counts go out
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();
-    sIsLast = atomicAdd(&st[1], 1u) == gridDim.x - 1;
+    sIsLast = 0;
+    if (sendPhase) {
+      __threadfence_system();
+      sIsLast = atomicAdd(&st[1], 1u) == gridDim.x - 1;
+    }
   }
   __syncthreads();
   if (sIsLast) {
@@ -101,9 +108,11 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
       const uint32_t c = st[kStCounters + e];
       st[kStCounters + e] = 0;
       const int dst = e / El, el = e % El;
+      if (mask && mask[dst]) continue;
       stReleaseSys64(a.recvCount[dst] + cntOff + (size_t)el * n + rank, ((unsigned long long)epoch << 32) | c);
     }
   }
+  if (!recvPhase) return;   // split-phase call: ncclEpComplete runs the receiving half
 
   // ---------------------------------------------------------------- receive and pack
   const int cap = n * a.maxTokens;
@@ -113,9 +122,16 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
     if (threadIdx.x < n) {
       const unsigned long long* c = a.recvCount[rank] + cntOff + (size_t)el * n + threadIdx.x;
       unsigned long long v = 0;
-      bool got = boundedWait(w, WAIT_TILE, threadIdx.x, epoch, [&] { v = ldRelaxedSys64((const uint64_t*)c); return (uint32_t)(v >> 32) == epoch; });
-      fenceSys();
-      sCnt[threadIdx.x] = got ? (int)(uint32_t)v : -1;
+      int cnt = 0;
+      if (!(mask && mask[threadIdx.x])) {
+        const bool quiet = a.enableMask && mask;
+        bool got = boundedWait(w, WAIT_TILE, threadIdx.x, epoch, [&] { v = ldRelaxedSys64((const uint64_t*)c); return (uint32_t)(v >> 32) == epoch; }, !quiet);
+        fenceSys();
+        if (got) cnt = (int)(uint32_t)v;
+        else if (quiet && !(a.sync.abortFlag && ldRelaxedSys(a.sync.abortFlag))) { mask[threadIdx.x] = 1; cnt = 0; }   // left out from now on; the call goes on without it
+        else cnt = -1;
+      }
+      sCnt[threadIdx.x] = cnt;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -173,9 +189,12 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
 __global__ void __launch_bounds__(kEpThreads, 1) epCombineKernel(const __grid_constant__ EpArgs a) {
   __shared__ int sIsLast, sOk;
   const int rank = ctaRank(a.emu, a.rank);
+  if (a.emu && ((a.absent >> rank) & 1u)) return;
   const int n = a.nRanks, H = a.hidden, K = a.topk, El = a.expertsPerRank;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nWarps = kEpThreads / 32;
   uint32_t* st = a.state[rank];
+  uint32_t* mask = a.mask[rank];
+  const bool sendPhase = (a.phases & 1) != 0, recvPhase = (a.phases & 2) != 0;
   const uint32_t epoch = st[4] + 1;
   const int cap = n * a.maxTokens;
   WaitCtx w{&a.sync, a.sync.status[rank]};
@@ -183,11 +202,12 @@ __global__ void __launch_bounds__(kEpThreads, 1) epCombineKernel(const __grid_co
   const size_t combOff = (size_t)(epoch & 1) * ((size_t)a.maxTokens * K * H * 2);   // two landing zones, by epoch parity
 
   // ---------------------------------------------------------------- send expert outputs home
-  for (int el = 0; el < El; ++el) {
+  for (int el = 0; sendPhase && el < El; ++el) {
     const int total = a.expertCount[rank][el];
     for (int pos = blockIdx.x * nWarps + warp; pos < total; pos += gridDim.x * nWarps) {
       const size_t o = (size_t)el * cap + pos;
       const int2 info = a.srcInfo[rank][o];
+      if (mask && mask[info.x]) continue;
       const char* src = (const char*)(y + o * H);
       char* dst = a.combBuf[info.x] + combOff + (size_t)info.y * H * 2;
       // four independent 16-byte loads in flight per lane before the stores that depend on them
@@ -206,23 +226,31 @@ __global__ void __launch_bounds__(kEpThreads, 1) epCombineKernel(const __grid_co
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();
-    sIsLast = atomicAdd(&st[5], 1u) == gridDim.x - 1;
+    sIsLast = 0;
+    if (sendPhase) {
+      __threadfence_system();
+      sIsLast = atomicAdd(&st[5], 1u) == gridDim.x - 1;
+    }
   }
   __syncthreads();
-  if (sIsLast && threadIdx.x < n) {
+  if (sIsLast && threadIdx.x < n && !(mask && mask[threadIdx.x])) {
     __threadfence();
     stReleaseSys64(a.combFlag[threadIdx.x] + rank, (unsigned long long)epoch);
   }
+  if (!recvPhase) return;
 
   // ---------------------------------------------------------------- wait for everybody's rows, then weighted sum
   if (threadIdx.x == 0) sOk = 1;
   __syncthreads();
-  if (threadIdx.x < n) {
+  if (threadIdx.x < n && !(mask && mask[threadIdx.x])) {
     const unsigned long long* f = a.combFlag[rank] + threadIdx.x;
-    bool got = boundedWait(w, WAIT_TILE, threadIdx.x, epoch, [&] { return (int32_t)((uint32_t)ldRelaxedSys64((const uint64_t*)f) - epoch) >= 0; });
+    const bool quiet = a.enableMask && mask;
+    bool got = boundedWait(w, WAIT_TILE, threadIdx.x, epoch, [&] { return (int32_t)((uint32_t)ldRelaxedSys64((const uint64_t*)f) - epoch) >= 0; }, !quiet);
     fenceSys();
-    if (!got) sOk = 0;
+    if (!got) {
+      if (quiet && !(a.sync.abortFlag && ldRelaxedSys(a.sync.abortFlag))) mask[threadIdx.x] = 1;   // its experts' rows are left out of the sums below
+      else sOk = 0;
+    }
   }
   __syncthreads();
   if (sOk) {
@@ -242,7 +270,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) epCombineKernel(const __grid_co
             v[u] = make_uint4(0, 0, 0, 0);
             if (k < K) {
               const long long e = a.topkIdx[rank][(size_t)t * K + k];
-              if (e >= 0 && e < a.numExperts) {
+              if (e >= 0 && e < a.numExperts && !(mask && mask[e / El])) {
                 wk[u] = a.topkW[rank][(size_t)t * K + k];
                 v[u] = ldLocal16(a.combBuf[rank] + combOff + ((size_t)(t * K + k) * H + (size_t)c * 8) * 2);
               }

@@ -28,6 +28,11 @@ struct EpArgs {
   float* outScales[kMaxRanks];                 // dispatch fp8: [E_local, cap, hidden/128]
   int* expertCount[kMaxRanks];                 // [E_local] tokens received per local expert
   int2* srcInfo[kMaxRanks];                    // [E_local, cap] {source rank, token * topk + k}; written by dispatch, read by combine
+  // split-phase calls and rank masks
+  int phases;                                  // bit 0: sending half of the kernel, bit 1: receiving half (send_only + ncclEpComplete run them apart)
+  int enableMask;                              // a wait on a rank that runs out leaves that rank out from then on instead of failing the call
+  uint32_t* mask[kMaxRanks];                   // mask[r]: rank r's private [nRanks] words; non-zero = that rank is left out (no sends to it, no waits on it)
+  unsigned absent;                             // emulation only: bit r set = rank r never shows up (its CTAs return at once), which makes its peers' waits run out
   SyncArgs sync;
 };
 

@@ -23,6 +23,7 @@ struct ncclEpGroup {
   char* combZone = nullptr;           // 2 zones, allocated with the first handle (needs top-k)
   SymWindow* combWin = nullptr;
   uint32_t* state = nullptr;
+  uint32_t* mask = nullptr;           // [n] device words: non-zero = that rank is left out of dispatch / combine
   int smCount = 0;
   int lastError = 0;
 };
@@ -35,6 +36,12 @@ struct ncclEpHandle {
   const float* topkW = nullptr;
   int2* srcInfo = nullptr;
   int* expertCount = nullptr;
+  // a send_only call leaves its receiving half to ncclEpComplete
+  int pending = 0;                    // 0 nothing, 1 dispatch, 2 combine
+  EpArgs pendingArgs;
+  int pendingCtas = 0;
+  size_t pendingSmem = 0;
+  void* pendingCounters = nullptr;    // layout_info->expert_counters of the pending dispatch
 };
 
 static bool cfgOk(const void* p) {
@@ -65,18 +72,17 @@ static void fillEpArgs(ncclEpGroup* g, EpArgs* a) {
     if (g->combZone) a->combBuf[p] = g->n > 1 ? (char*)g->combWin->host.peerPtr[p] : g->combZone;
   }
   a->state[comm->rank] = g->state;
+  a->mask[comm->rank] = g->mask;
+  a->enableMask = g->cfg.enable_mask ? 1 : 0;
+  a->phases = 3;
   a->sync.status[comm->rank] = comm->devStatusDev;
   a->sync.abortFlag = comm->abortFlagDev;
   a->sync.timeoutNs = g->cfg.timeout_ns ? g->cfg.timeout_ns : (comm->devPlane ? comm->devPlane->timeoutNs : 5000000000ull);
 }
 
 static ncclResult_t launchEp(const void* fn, EpArgs* a, int ctas, int ranksY, size_t smem, cudaStream_t stream, bool coop) {
-  static bool attr[2] = {false, false};
-  int which = fn == epDispatchKernelFn() ? 0 : 1;
-  if (!attr[which] && smem > 40000) {
-    CUDACHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr[which] = true;
-  }
+  // the attribute is per device and cheap to set: no process-wide "done once" flag
+  if (smem > 40000) CUDACHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   return launchKernel(fn, dim3(ctas, ranksY), dim3(512), smem, a, stream, coop);
 }
 
@@ -148,6 +154,8 @@ ncclResult_t ncclEpCreateGroup(ncclEpGroup_t* out, ncclComm_t comm, const ncclEp
   CUDACHECK(cudaMemset(g->ctl, 0, ctlBytes(g->El, n)));
   CUDACHECK(cudaMalloc(&g->state, (8 + g->E) * sizeof(uint32_t)));
   CUDACHECK(cudaMemset(g->state, 0, (8 + g->E) * sizeof(uint32_t)));
+  CUDACHECK(cudaMalloc(&g->mask, kMaxRanks * sizeof(uint32_t)));
+  CUDACHECK(cudaMemset(g->mask, 0, kMaxRanks * sizeof(uint32_t)));
   CUDACHECK(cudaDeviceSynchronize());
   if (n > 1) {
     NCCLCHECK(symWindowRegister(comm, g->recvZone, 2 * g->zoneBytes, &g->recvWin, NCCL_WIN_COLL_SYMMETRIC));
@@ -170,6 +178,7 @@ ncclResult_t ncclEpGroupDestroy(ncclEpGroup_t g) {
   if (g->ctl) memFree(g->ctl);
   if (g->combZone) memFree(g->combZone);
   if (g->state) cudaFree(g->state);
+  if (g->mask) cudaFree(g->mask);
   delete g;
   return ncclSuccess;
 }
@@ -273,10 +282,23 @@ ncclResult_t ncclEpDispatch(ncclEpHandle_t h, const ncclEpDispatchInputs_t* in, 
   a.expertCount[me] = h->expertCount;
   a.srcInfo[me] = h->srcInfo;
   int ctas = g->cfg.max_num_sms ? (int)std::min<unsigned>(g->cfg.max_num_sms, (unsigned)g->smCount) : g->smCount;
+  if (h->pending) { WARN("ncclEpDispatch: a send_only call on this handle is still waiting for ncclEpComplete"); return ncclInvalidUsage; }
+  const bool sendOnly = config && config->send_only;
+  if (sendOnly) a.phases = 1;
   NCCLCHECK(launchEp(epDispatchKernelFn(), &a, ctas, 1, dispatchSmem(g->H, fp8), stream, false));
   if (g->comm->devPlane) g->comm->devPlane->launches++;
-  if (li && li->expert_counters && li->expert_counters->data)
-    CUDACHECK(cudaMemcpyAsync(li->expert_counters->data, h->expertCount, (size_t)g->El * sizeof(int), cudaMemcpyDeviceToDevice, stream));
+  void* counters = (li && li->expert_counters && li->expert_counters->data) ? li->expert_counters->data : nullptr;
+  if (sendOnly) {
+    // tokens and counts are on their way; the receiving half (wait, pack) runs when ncclEpComplete is called
+    h->pending = 1;
+    h->pendingArgs = a;
+    h->pendingArgs.phases = 2;
+    h->pendingCtas = ctas;
+    h->pendingSmem = dispatchSmem(g->H, fp8);
+    h->pendingCounters = counters;
+    return ncclSuccess;
+  }
+  if (counters) CUDACHECK(cudaMemcpyAsync(counters, h->expertCount, (size_t)g->El * sizeof(int), cudaMemcpyDeviceToDevice, stream));
   return ncclSuccess;
 }
 
@@ -309,27 +331,66 @@ ncclResult_t ncclEpCombine(ncclEpHandle_t h, const ncclEpCombineInputs_t* in, co
   a.expertCount[me] = h->expertCount;
   a.srcInfo[me] = h->srcInfo;
   int ctas = g->cfg.max_num_sms ? (int)std::min<unsigned>(g->cfg.max_num_sms, (unsigned)g->smCount) : g->smCount;
+  if (h->pending) { WARN("ncclEpCombine: a send_only call on this handle is still waiting for ncclEpComplete"); return ncclInvalidUsage; }
+  const bool sendOnly = config && config->send_only;
+  if (sendOnly) a.phases = 1;
   NCCLCHECK(launchEp(epCombineKernelFn(), &a, ctas, 1, 0, stream, false));
   if (g->comm->devPlane) g->comm->devPlane->launches++;
+  if (sendOnly) {
+    h->pending = 2;
+    h->pendingArgs = a;
+    h->pendingArgs.phases = 2;
+    h->pendingCtas = ctas;
+    h->pendingSmem = 0;
+  }
   return ncclSuccess;
 }
 
-ncclResult_t ncclEpComplete(ncclEpHandle_t h, const ncclEpCompleteConfig_t*, cudaStream_t) {
-  // dispatch and combine always run both phases in one kernel; nothing is left pending
-  return h ? ncclSuccess : ncclInvalidArgument;
+// Runs the receiving half that a send_only dispatch / combine left open: the sends were issued by the earlier
+// call, so whatever the caller queued in between (for example the previous layer's expert GEMMs) overlapped them.
+// Reference parity: contrib/nccl_ep/nccl_ep.cc:3413.
+ncclResult_t ncclEpComplete(ncclEpHandle_t h, const ncclEpCompleteConfig_t* config, cudaStream_t stream) {
+  if (!h) return ncclInvalidArgument;
+  if (config && !cfgOk(config)) return ncclInvalidArgument;
+  if (!h->pending) return ncclSuccess;
+  ncclEpGroup* g = h->g;
+  NCCLCHECK(devPlaneCheckStatus(g->comm));
+  const void* fn = h->pending == 1 ? epDispatchKernelFn() : epCombineKernelFn();
+  NCCLCHECK(launchEp(fn, &h->pendingArgs, h->pendingCtas, 1, h->pendingSmem, stream, false));
+  if (g->comm->devPlane) g->comm->devPlane->launches++;
+  if (h->pending == 1 && h->pendingCounters)
+    CUDACHECK(cudaMemcpyAsync(h->pendingCounters, h->expertCount, (size_t)g->El * sizeof(int), cudaMemcpyDeviceToDevice, stream));
+  h->pending = 0;
+  return ncclSuccess;
 }
 
-ncclResult_t ncclEpMaskQuery(ncclEpGroup_t g, int* mask_status, cudaStream_t) {
+// Rank masks: a masked rank receives nothing and nobody waits for it. With enable_mask in the group
+// configuration a wait on a rank that runs out (timeout_ns) sets that rank's mask word on the waiting rank
+// instead of failing the call; ncclEpMaskQuery shows the words, ncclEpMaskUpdate sets them (for example after a
+// health check excluded a rank everywhere), ncclEpMaskClean clears them.
+// Reference parity: contrib/nccl_ep/nccl_ep.cc:3430-3545.
+ncclResult_t ncclEpMaskQuery(ncclEpGroup_t g, int* mask_status, cudaStream_t stream) {
   if (!g || !mask_status) return ncclInvalidArgument;
-  for (int r = 0; r < g->n; ++r) mask_status[r] = 0;   // no rank is masked out
+  uint32_t host[kMaxRanks] = {};
+  CUDACHECK(cudaMemcpyAsync(host, g->mask, g->n * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
+  CUDACHECK(cudaStreamSynchronize(stream));
+  for (int r = 0; r < g->n; ++r) mask_status[r] = host[r] ? 1 : 0;
   return ncclSuccess;
 }
-ncclResult_t ncclEpMaskUpdate(ncclEpGroup_t g, const int* mask, cudaStream_t) {
+ncclResult_t ncclEpMaskUpdate(ncclEpGroup_t g, const int* mask, cudaStream_t stream) {
   if (!g || !mask) return ncclInvalidArgument;
-  for (int r = 0; r < g->n; ++r) if (mask[r]) { WARN("ncclEpMaskUpdate: masking ranks out is not implemented"); return ncclInvalidUsage; }
+  if (mask[g->comm->rank]) { WARN("ncclEpMaskUpdate: a rank cannot leave itself out"); return ncclInvalidArgument; }
+  uint32_t host[kMaxRanks] = {};
+  for (int r = 0; r < g->n; ++r) host[r] = mask[r] ? 1u : 0u;
+  CUDACHECK(cudaMemcpyAsync(g->mask, host, g->n * sizeof(uint32_t), cudaMemcpyHostToDevice, stream));
+  CUDACHECK(cudaStreamSynchronize(stream));   // `host` is on this stack frame
   return ncclSuccess;
 }
-ncclResult_t ncclEpMaskClean(ncclEpGroup_t g, cudaStream_t) { return g ? ncclSuccess : ncclInvalidArgument; }
+ncclResult_t ncclEpMaskClean(ncclEpGroup_t g, cudaStream_t stream) {
+  if (!g) return ncclInvalidArgument;
+  CUDACHECK(cudaMemsetAsync(g->mask, 0, kMaxRanks * sizeof(uint32_t), stream));
+  return ncclSuccess;
+}
 
 ncclResult_t ncclEpGetAsyncError(ncclEpGroup_t g, int* error_out) {
   if (!g || !error_out) return ncclInvalidArgument;
@@ -355,6 +416,10 @@ struct EpEmu {
   uint32_t* status[kMaxRanks];
   int2* srcInfo[kMaxRanks];
   int* counts[kMaxRanks];
+  uint32_t* mask[kMaxRanks];
+  int phases = 3, enableMask = 0;
+  unsigned absent = 0;
+  unsigned long long timeoutNs = 3000000000ull;
 };
 
 void* b200EpEmuCreate(int n, int E, int K, int H, int maxTokens) {
@@ -368,8 +433,10 @@ void* b200EpEmuCreate(int n, int E, int K, int H, int maxTokens) {
     bool ok = cudaMalloc(&e->recv[r], 2 * zone) == cudaSuccess && cudaMalloc(&e->ctl[r], ctlBytes(e->El, n)) == cudaSuccess &&
               cudaMalloc(&e->comb[r], 2 * comb) == cudaSuccess && cudaMalloc(&e->state[r], (8 + E) * 4) == cudaSuccess &&
               cudaMalloc(&e->status[r], 16) == cudaSuccess && cudaMalloc(&e->srcInfo[r], (size_t)e->El * n * maxTokens * sizeof(int2)) == cudaSuccess &&
-              cudaMalloc(&e->counts[r], e->El * sizeof(int)) == cudaSuccess;
+              cudaMalloc(&e->counts[r], e->El * sizeof(int)) == cudaSuccess && cudaMalloc(&e->mask[r], kMaxRanks * 4) == cudaSuccess;
     if (!ok) return nullptr;
+    cudaMemset(e->mask[r], 0, kMaxRanks * 4);
+    cudaMemset(e->counts[r], 0, e->El * sizeof(int));
     cudaMemset(e->ctl[r], 0, ctlBytes(e->El, n));
     cudaMemset(e->state[r], 0, (8 + E) * 4);
     cudaMemset(e->status[r], 0, 16);
@@ -380,7 +447,7 @@ void* b200EpEmuCreate(int n, int E, int K, int H, int maxTokens) {
 void b200EpEmuDestroy(void* ctx) {
   EpEmu* e = (EpEmu*)ctx;
   if (!e) return;
-  for (int r = 0; r < e->n; ++r) { cudaFree(e->recv[r]); cudaFree(e->ctl[r]); cudaFree(e->comb[r]); cudaFree(e->state[r]); cudaFree(e->status[r]); cudaFree(e->srcInfo[r]); cudaFree(e->counts[r]); }
+  for (int r = 0; r < e->n; ++r) { cudaFree(e->recv[r]); cudaFree(e->ctl[r]); cudaFree(e->comb[r]); cudaFree(e->state[r]); cudaFree(e->status[r]); cudaFree(e->srcInfo[r]); cudaFree(e->counts[r]); cudaFree(e->mask[r]); }
   delete e;
 }
 static void emuArgs(EpEmu* e, EpArgs* a) {
@@ -395,8 +462,32 @@ static void emuArgs(EpEmu* e, EpArgs* a) {
     a->sync.status[r] = e->status[r];
     a->srcInfo[r] = e->srcInfo[r];
     a->expertCount[r] = e->counts[r];
+    a->mask[r] = e->mask[r];
   }
-  a->sync.timeoutNs = 3000000000ull;
+  a->phases = e->phases;
+  a->enableMask = e->enableMask;
+  a->absent = e->absent;
+  a->sync.timeoutNs = e->timeoutNs;
+}
+// Settings of the following emulated calls: which halves run (1 send, 2 receive, 3 both), which ranks never show up
+// (bit mask), whether waits that run out mask the rank instead of failing, and the budget of one wait.
+int b200EpEmuSet(void* ctx, int phases, unsigned absent, int enableMask, unsigned long long timeoutMs) {
+  EpEmu* e = (EpEmu*)ctx;
+  if (!e || phases < 1 || phases > 3) return ncclInvalidArgument;
+  e->phases = phases;
+  e->absent = absent;
+  e->enableMask = enableMask;
+  if (timeoutMs) e->timeoutNs = timeoutMs * 1000000ull;
+  return 0;
+}
+int b200EpEmuMask(void* ctx, int rank, unsigned int* out) {
+  EpEmu* e = (EpEmu*)ctx;
+  return cudaMemcpy(out, e->mask[rank], e->n * 4, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : 1;
+}
+int b200EpEmuClear(void* ctx) {
+  EpEmu* e = (EpEmu*)ctx;
+  for (int r = 0; r < e->n; ++r) { cudaMemset(e->mask[r], 0, kMaxRanks * 4); cudaMemset(e->status[r], 0, 16); }
+  return 0;
 }
 int b200EpEmuDispatch(void* ctx, int fp8, const int* numTokens, void** x, void** idx, void** outTokens, void** outScales, int** countsOut, int ctas) {
   EpEmu* e = (EpEmu*)ctx;

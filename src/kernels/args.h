@@ -64,6 +64,7 @@ enum CollMode : int {
   MODE_PUSH = 0,     // writer stores into peers' buffers
   MODE_PULL = 1,     // reader loads from peers' buffers
   MODE_MC = 2,       // one multimem.st stream reaches every peer
+  MODE_BULK = 4,     // flag added to a mode when it is forced or tabled: moved by bulk-copy engines (few CTAs) instead of threads
 };
 
 struct CollArgs {

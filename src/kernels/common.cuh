@@ -104,8 +104,10 @@ struct WaitCtx {
   __device__ __forceinline__ bool failed() const { return ldRelaxedSys(status) != DEV_OK; }
 };
 
+// `record = false`: the caller handles a wait that ran out itself (e.g. leaves the peer out from
+// then on) and nothing is written to the status words.
 template <typename Pred>
-__device__ __forceinline__ bool boundedWait(const WaitCtx& w, uint32_t kind, uint32_t peer, uint32_t expected, Pred done) {
+__device__ __forceinline__ bool boundedWait(const WaitCtx& w, uint32_t kind, uint32_t peer, uint32_t expected, Pred done, bool record = true) {
   if (done()) return true;
   unsigned long long start = globalTimerNs();
   uint32_t spins = 0;
@@ -116,6 +118,7 @@ __device__ __forceinline__ bool boundedWait(const WaitCtx& w, uint32_t kind, uin
       if (w.sync->abortFlag && ldRelaxedSys(w.sync->abortFlag)) code = DEV_ABORTED;
       else if (globalTimerNs() - start > w.sync->timeoutNs) code = DEV_TIMEOUT;
       else if (ldRelaxedSys(w.status) != DEV_OK) return false;  // another wait of this rank already failed
+      if (code != DEV_OK && !(record || code == DEV_ABORTED)) return false;
       if (code != DEV_OK) {
         // Status words may live in host-mapped memory: plain stores only; concurrent failing
         // waits write equivalent records, so the race between them is harmless.

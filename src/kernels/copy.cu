@@ -148,6 +148,58 @@ __global__ void __launch_bounds__(kCtaThreads, 1) copyCollKernel(const __grid_co
   bar.finish();
 }
 
+// The same collectives moved by the bulk-copy engine of each SM instead of by its threads: one
+// thread per CTA streams its contiguous share of every segment through a ring of shared-memory
+// stages (cp.async.bulk global -> shared -> global; sources and destinations may be peer memory or
+// the multicast alias; no cluster multicast anywhere). A CTA keeps four 32 KiB loads in flight while
+// earlier chunks drain, so a dozen CTAs fill the links and the other SMs stay with the compute
+// kernels the collective overlaps. Needs 16-byte aligned pointers and a block size that is a
+// multiple of 16 bytes (the host picks the thread kernel otherwise).
+// Reference parity: the TMA variants of src/device/symmetric/all_gather.cuh:277-308.
+constexpr int kCollBulkStages = 6;
+constexpr uint32_t kCollBulkChunk = 32768;
+__global__ void __launch_bounds__(32, 1) copyCollBulkKernel(const __grid_constant__ CollArgs a) {
+  extern __shared__ uint8_t collBulkRaw[];
+  uint8_t* sm = (uint8_t*)(((uintptr_t)collBulkRaw + 127) & ~(uintptr_t)127);
+  uint64_t* bars = (uint64_t*)(sm + (size_t)kCollBulkStages * kCollBulkChunk);
+  const int rank = ctaRank(a.emu, a.rank);
+  pdlEnter();
+  CtaBarrier bar;
+  bar.init(a.sync, rank, a.nRanks, blockIdx.x);
+  bool ok = bar.sync(false, false);
+  __shared__ Seg segs[kMaxRanks];
+  __shared__ int nSeg;
+  if (threadIdx.x == 0) nSeg = buildSegs(a, rank, segs);
+  __syncthreads();
+  const size_t B = a.count;
+  if (threadIdx.x == 0 && ok && nSeg > 0 && B > 0) {
+    for (int s = 0; s < kCollBulkStages; ++s) sm100::mbarInit(sm100::smemAddr(&bars[s]), 1);
+    sm100::mbarInitFence();
+    const size_t chunks = (B + kCollBulkChunk - 1) / kCollBulkChunk;
+    const size_t per = (chunks + gridDim.x - 1) / gridDim.x;
+    const size_t lo = (size_t)blockIdx.x * per * kCollBulkChunk;
+    if (lo < B) {
+      const size_t n = B - lo < per * kCollBulkChunk ? B - lo : per * kCollBulkChunk;
+      uint32_t phaseBits = 0;
+      bool moved = true;
+      // CTAs start on different segments so that no peer is hit by all of them at once
+      for (int si = 0; si < nSeg && moved; ++si) {
+        const Seg sg = segs[(si + blockIdx.x) % nSeg];
+        moved = sm100::bulkPipe<kCollBulkStages, kCollBulkChunk>(sg.dst + lo, sg.src + lo, n, sm100::smemAddr(sm), bars, phaseBits);
+      }
+      if (!moved) {
+        // a load did not arrive within the wait limit: report it like any other wait that ran out
+        uint32_t* st = a.sync.status[rank];
+        if (ldRelaxedSys(st) == DEV_OK) { st[1] = WAIT_TILE; st[2] = (uint32_t)rank; st[3] = 0; __threadfence_system(); stRelaxedSys(st, DEV_TIMEOUT); }
+      }
+    }
+  }
+  bar.sync(true, false);
+  bar.finish();
+}
+const void* copyBulkKernelFn() { return (const void*)copyCollBulkKernel; }
+size_t copyBulkSmemBytes() { return 128 + (size_t)kCollBulkStages * kCollBulkChunk + kCollBulkStages * 8; }
+
 // ------------------------------------------------------------------------- send / recv
 __device__ __forceinline__ void copyChunk(char* dst, const char* src, size_t bytes) {
   if ((((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {

@@ -30,6 +30,8 @@ const void* llReduceKernelFn(ncclDataType_t type, int op);   // all-reduce, redu
 const void* llReduceBatchKernelFn(ncclDataType_t type, int op);   // takes LLBatchArgs: several all-reduces of one group
 const void* llCopyKernelFn();
 const void* copyKernelFn();
+const void* copyBulkKernelFn();              // same arguments as copyKernelFn: bulk-copy engines, 32 threads per CTA, dynamic shared memory
+size_t copyBulkSmemBytes();
 const void* p2pKernelFn();
 const void* scaleKernelFn(ncclDataType_t type);
 const void* localCopyKernelFn(int unroll);   // takes ScaleArgs{src, dst, count = bytes}; unroll 4 or 8

@@ -31,7 +31,7 @@ int tuneCollOfFunc(int func) {
 }
 
 // Grammar: { "<n>": { "<coll>": [ [upto, "ALGO", ctas], ... ], ... }, ..., "<switch>": number, ... }  with ALGO in
-// LL, P2P, NVLS, NVLS1, PUSH, PULL, MC.
+// LL, P2P, NVLS, NVLS1, PUSH, PULL, MC, BPUSH, BPULL, BMC.
 struct Cursor {
   const char* p;
   void ws() { while (*p && isspace((unsigned char)*p)) ++p; }
@@ -92,6 +92,9 @@ bool tuneParse(TuningTable* t, const std::string& json) {
         else if (algo == "MC") { e.algo = ALGO_NVLS; e.mode = MODE_MC; }
         else if (algo == "PUSH") e.mode = MODE_PUSH;
         else if (algo == "PULL") e.mode = MODE_PULL;
+        else if (algo == "BPUSH") e.mode = MODE_PUSH | MODE_BULK;   // bulk-copy engines instead of threads
+        else if (algo == "BPULL") e.mode = MODE_PULL | MODE_BULK;
+        else if (algo == "BMC") { e.algo = ALGO_NVLS; e.mode = MODE_MC | MODE_BULK; }
         rows.push_back(e);
         c.eat(',');
       }

@@ -83,3 +83,110 @@ def test_dispatch_combine(n, E, K, H, T, fp8):
                     assert torch.allclose(outs[r].float(), ref, rtol=2e-2, atol=2e-2), r
     finally:
         lib.b200EpEmuDestroy(ctx)
+
+
+def _lib2():
+    lib = _lib()
+    lib.b200EpEmuSet.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_int, ctypes.c_ulonglong]
+    lib.b200EpEmuMask.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_uint)]
+    lib.b200EpEmuClear.argtypes = [ctypes.c_void_p]
+    return lib
+
+
+def _batch(n, E, K, H, T, g):
+    x = [torch.randn(T, H, generator=g).bfloat16().cuda() for _ in range(n)]
+    idx = [torch.rand(T, E, generator=g).topk(K, dim=1).indices.to(torch.int64).cuda() for _ in range(n)]
+    wts = [torch.rand(T, K, generator=g).cuda() for _ in range(n)]
+    return x, idx, wts
+
+
+def test_split_phase_dispatch_and_combine():
+    """send_only + complete: the sending half and the receiving half of each kernel run as two launches
+    (whatever the caller queues in between overlaps the sends) and give the result of the one-launch call."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    lib = _lib2()
+    n, E, K, H, T = 4, 16, 2, 256, 24
+    El, cap = E // n, n * T
+    ctx = lib.b200EpEmuCreate(n, E, K, H, T)
+    assert ctx
+    g = torch.Generator().manual_seed(5)
+    try:
+        for rep in range(3):
+            x, idx, wts = _batch(n, E, K, H, T, g)
+            ntok = (ctypes.c_int * n)(*([T] * n))
+            out_tok = [torch.zeros(El, cap, H, dtype=torch.bfloat16, device="cuda") for _ in range(n)]
+            counts = [(ctypes.c_int * El)() for _ in range(n)]
+            cptr = (ctypes.POINTER(ctypes.c_int) * n)(*[ctypes.cast(c, ctypes.POINTER(ctypes.c_int)) for c in counts])
+            assert lib.b200EpEmuSet(ctx, 1, 0, 0, 0) == 0
+            assert lib.b200EpEmuDispatch(ctx, 0, ntok, _ptrs(x), _ptrs(idx), _ptrs(out_tok), None, cptr, 4) == 0
+            assert lib.b200EpEmuSet(ctx, 2, 0, 0, 0) == 0
+            assert lib.b200EpEmuDispatch(ctx, 0, ntok, _ptrs(x), _ptrs(idx), _ptrs(out_tok), None, cptr, 3) == 0
+            for r in range(n):
+                for el in range(El):
+                    e = r * El + el
+                    assert counts[r][el] == sum(int((idx[s] == e).sum()) for s in range(n))
+            outs = [torch.zeros(T, H, dtype=torch.bfloat16, device="cuda") for _ in range(n)]
+            assert lib.b200EpEmuSet(ctx, 1, 0, 0, 0) == 0
+            assert lib.b200EpEmuCombine(ctx, ntok, _ptrs(out_tok), _ptrs(idx), _ptrs(wts), _ptrs(outs), 4) == 0
+            assert lib.b200EpEmuSet(ctx, 2, 0, 0, 0) == 0
+            assert lib.b200EpEmuCombine(ctx, ntok, _ptrs(out_tok), _ptrs(idx), _ptrs(wts), _ptrs(outs), 2) == 0
+            for r in range(n):
+                ref = x[r].float() * wts[r].sum(1, keepdim=True)
+                assert torch.allclose(outs[r].float(), ref, rtol=2e-2, atol=2e-2), (rep, r)
+    finally:
+        lib.b200EpEmuDestroy(ctx)
+
+
+def test_rank_that_never_joins_is_masked_out():
+    """One rank never shows up. Without masks its peers' waits run out and the call reports a time-out; with
+    masks enabled the waits leave that rank out, the call completes with what the live ranks sent, the mask
+    shows the missing rank, and later calls neither send to it nor wait for it (so they are fast again)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    import time
+    lib = _lib2()
+    n, E, K, H, T = 4, 8, 2, 128, 8
+    El, cap = E // n, n * T
+    dead = 2
+    ctx = lib.b200EpEmuCreate(n, E, K, H, T)
+    assert ctx
+    g = torch.Generator().manual_seed(9)
+    try:
+        x, idx, wts = _batch(n, E, K, H, T, g)
+        ntok = (ctypes.c_int * n)(*([T] * n))
+        out_tok = [torch.zeros(El, cap, H, dtype=torch.bfloat16, device="cuda") for _ in range(n)]
+        counts = [(ctypes.c_int * El)() for _ in range(n)]
+        cptr = (ctypes.POINTER(ctypes.c_int) * n)(*[ctypes.cast(c, ctypes.POINTER(ctypes.c_int)) for c in counts])
+        # masks off: the wait on the absent rank runs out (200 ms) and is reported
+        assert lib.b200EpEmuSet(ctx, 3, 1 << dead, 0, 200) == 0
+        assert lib.b200EpEmuDispatch(ctx, 0, ntok, _ptrs(x), _ptrs(idx), _ptrs(out_tok), None, cptr, 2) == 8   # ncclTimeout
+        lib.b200EpEmuClear(ctx)
+        lib.b200EpEmuDestroy(ctx)
+        ctx = lib.b200EpEmuCreate(n, E, K, H, T)
+        # masks on: same absence, the call completes
+        assert lib.b200EpEmuSet(ctx, 3, 1 << dead, 1, 200) == 0
+        assert lib.b200EpEmuDispatch(ctx, 0, ntok, _ptrs(x), _ptrs(idx), _ptrs(out_tok), None, cptr, 2) == 0
+        live = [r for r in range(n) if r != dead]
+        for r in live:
+            m = (ctypes.c_uint * n)()
+            assert lib.b200EpEmuMask(ctx, r, m) == 0
+            assert [int(v != 0) for v in m] == [int(q == dead) for q in range(n)], (r, list(m))
+            for el in range(El):
+                e = r * El + el
+                assert counts[r][el] == sum(int((idx[s] == e).sum()) for s in live)
+        # combine: rows owned by the missing rank's experts are left out of the sums
+        outs = [torch.zeros(T, H, dtype=torch.bfloat16, device="cuda") for _ in range(n)]
+        t0 = time.time()
+        assert lib.b200EpEmuCombine(ctx, ntok, _ptrs(out_tok), _ptrs(idx), _ptrs(wts), _ptrs(outs), 2) == 0
+        assert time.time() - t0 < 0.15, "a masked rank must not be waited for"
+        for r in live:
+            alive = ((idx[r] // El) != dead).float()
+            ref = x[r].float() * (wts[r] * alive).sum(1, keepdim=True)
+            assert torch.allclose(outs[r].float(), ref, rtol=2e-2, atol=2e-2), r
+        # the next dispatch does not wait for the masked rank either
+        t0 = time.time()
+        assert lib.b200EpEmuDispatch(ctx, 0, ntok, _ptrs(x), _ptrs(idx), _ptrs(out_tok), None, cptr, 2) == 0
+        assert time.time() - t0 < 0.15
+    finally:
+        lib.b200EpEmuDestroy(ctx)

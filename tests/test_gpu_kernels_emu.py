@@ -15,6 +15,7 @@ KERNEL_REDUCE_P2P, KERNEL_ALLREDUCE_LL = 0, 1
 FUNC_BROADCAST, FUNC_REDUCE, FUNC_ALLGATHER, FUNC_REDUCESCATTER, FUNC_ALLREDUCE = 0, 1, 2, 3, 4
 FUNC_ALLTOALL, FUNC_SCATTER, FUNC_GATHER = 8, 9, 10
 MODE_PUSH, MODE_PULL = 0, 1
+MODE_BULK = 4   # added to a mode: moved by the bulk-copy engines instead of by threads
 
 
 @pytest.fixture(scope="module")
@@ -225,9 +226,11 @@ def test_reduce_scatter_and_reduce(emu_lib, n, dtype, count):
 
 
 @pytest.mark.parametrize("n", [2, 3, 8])
-@pytest.mark.parametrize("mode", [MODE_PUSH, MODE_PULL])
+@pytest.mark.parametrize("mode", [MODE_PUSH, MODE_PULL, MODE_PUSH | MODE_BULK, MODE_PULL | MODE_BULK])
 @pytest.mark.parametrize("nbytes", [16, 4096 + 16, (1 << 20) + 48, 1001])
 def test_copy_collectives(emu_lib, n, mode, nbytes):
+    if (mode & MODE_BULK) and nbytes % 16:
+        pytest.skip("the bulk-copy kernel moves multiples of 16 bytes (the host picks the thread kernel otherwise)")
     ctx = emu_lib.b200EmuCreate(n, 5000)
     try:
         g = torch.Generator().manual_seed(nbytes + n)
