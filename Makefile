@@ -34,6 +34,9 @@ EXAMPLES := $(patsubst examples/%.cu,$(BINDIR)/examples/%,$(wildcard examples/*.
 
 all: $(LIB) $(TOOLS) plugins examples
 
+GIT_VERSION := $(shell git describe --always --dirty 2>/dev/null || echo unknown)
+$(BUILD)/src/core/version.o: CXXFLAGS += -DB200_GIT_VERSION='"$(GIT_VERSION)"'
+
 $(BUILD)/%.o: %.cc $(wildcard include/*.h src/*/*.h)
 	@mkdir -p $(dir $@)
 	$(CXX) $(CXXFLAGS) -c $< -o $@

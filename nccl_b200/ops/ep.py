@@ -49,6 +49,14 @@ class DispOut(ctypes.Structure):
                 ("topk_weights", ctypes.POINTER(EpTensor)), ("scales", ctypes.POINTER(EpTensor)), ("topk_idx", ctypes.POINTER(EpTensor))]
 
 
+class DispCfg(ctypes.Structure):
+    _fields_ = [("size", ctypes.c_uint), ("magic", ctypes.c_uint), ("send_only", ctypes.c_uint), ("round_scales", ctypes.c_uint), ("pass_direction", ctypes.c_int)]
+
+
+class CombCfg(ctypes.Structure):
+    _fields_ = [("size", ctypes.c_uint), ("magic", ctypes.c_uint), ("send_only", ctypes.c_uint), ("pass_direction", ctypes.c_int)]
+
+
 class CombIO(ctypes.Structure):
     _fields_ = [("size", ctypes.c_uint), ("magic", ctypes.c_uint), ("tokens", ctypes.POINTER(EpTensor)), ("topk_weights", ctypes.POINTER(EpTensor))]
 
@@ -67,7 +75,7 @@ def _hdr(s):
 
 
 class ExpertParallel:
-    def __init__(self, comm, num_experts, max_tokens, hidden, max_sms=0, timeout_ms=0):
+    def __init__(self, comm, num_experts, max_tokens, hidden, max_sms=0, timeout_ms=0, enable_mask=False):
         import torch
         self.torch = torch
         self.comm, self.lib = comm, comm.lib
@@ -81,8 +89,12 @@ class ExpertParallel:
         L.ncclEpCreateHandle.argtypes = [pvp, vp, ctypes.c_int, ctypes.POINTER(EpTensor), vp, vp, vp]
         L.ncclEpUpdateHandle.argtypes = [vp, ctypes.POINTER(EpTensor), vp, vp]
         L.ncclEpHandleDestroy.argtypes = [vp]
-        L.ncclEpDispatch.argtypes = [vp, ctypes.POINTER(DispIn), ctypes.POINTER(DispOut), ctypes.POINTER(LayoutInfo), vp, vp]
-        L.ncclEpCombine.argtypes = [vp, ctypes.POINTER(CombIO), ctypes.POINTER(CombIO), vp, vp]
+        L.ncclEpDispatch.argtypes = [vp, ctypes.POINTER(DispIn), ctypes.POINTER(DispOut), ctypes.POINTER(LayoutInfo), ctypes.POINTER(DispCfg), vp]
+        L.ncclEpCombine.argtypes = [vp, ctypes.POINTER(CombIO), ctypes.POINTER(CombIO), ctypes.POINTER(CombCfg), vp]
+        L.ncclEpComplete.argtypes = [vp, vp, vp]
+        L.ncclEpMaskQuery.argtypes = [vp, ctypes.POINTER(ctypes.c_int), vp]
+        L.ncclEpMaskUpdate.argtypes = [vp, ctypes.POINTER(ctypes.c_int), vp]
+        L.ncclEpMaskClean.argtypes = [vp, vp]
         cfg = _hdr(GroupCfg())
         cfg.version = 1
         cfg.num_experts = num_experts
@@ -90,6 +102,7 @@ class ExpertParallel:
         cfg.max_token_bytes = hidden * 2
         cfg.max_num_sms = max_sms
         cfg.timeout_ns = timeout_ms * 1000000
+        cfg.enable_mask = 1 if enable_mask else 0
         g = ctypes.c_void_p()
         _lib.check(L.ncclEpCreateGroup(ctypes.byref(g), comm.handle, ctypes.byref(cfg)), "ncclEpCreateGroup", L)
         self.group = g
@@ -107,7 +120,26 @@ class ExpertParallel:
     def _stream(self):
         return self.torch.cuda.current_stream().cuda_stream
 
-    def dispatch(self, x, topk_idx, topk_weights, fp8=True, toks=None, scales=None, counts=None):
+    def complete(self):
+        """Runs the receiving half of the last ``send_only`` dispatch / combine."""
+        _lib.check(self.lib.ncclEpComplete(self.handle, None, self._stream()), "ncclEpComplete", self.lib)
+
+    def mask(self):
+        """Which ranks this rank leaves out (1 = left out)."""
+        m = (ctypes.c_int * self.n)()
+        _lib.check(self.lib.ncclEpMaskQuery(self.group, m, self._stream()), "ncclEpMaskQuery", self.lib)
+        return list(m)
+
+    def set_mask(self, mask):
+        m = (ctypes.c_int * self.n)(*mask)
+        _lib.check(self.lib.ncclEpMaskUpdate(self.group, m, self._stream()), "ncclEpMaskUpdate", self.lib)
+
+    def clear_mask(self):
+        _lib.check(self.lib.ncclEpMaskClean(self.group, self._stream()), "ncclEpMaskClean", self.lib)
+
+    def dispatch(self, x, topk_idx, topk_weights, fp8=True, toks=None, scales=None, counts=None, send_only=False):
+        """``send_only``: only queue the sends; ``complete()`` then waits for the peers' tokens and packs them
+        (work queued in between overlaps the transfer)."""
         torch, L = self.torch, self.lib
         idx_t = _tensor(topk_idx, INT64)
         if self.handle is None:
@@ -133,16 +165,21 @@ class ExpertParallel:
             dout.scales = ctypes.pointer(sout)
         li = _hdr(LayoutInfo())
         li.expert_counters = ctypes.pointer(cnt_t)
-        _lib.check(L.ncclEpDispatch(self.handle, ctypes.byref(din), ctypes.byref(dout), ctypes.byref(li), None, self._stream()), "ncclEpDispatch", L)
+        dcfg = _hdr(DispCfg())
+        dcfg.send_only = 1 if send_only else 0
+        _lib.check(L.ncclEpDispatch(self.handle, ctypes.byref(din), ctypes.byref(dout), ctypes.byref(li), ctypes.byref(dcfg), self._stream()), "ncclEpDispatch", L)
         self._keep = (topk_idx, topk_weights, idx_t, xin, win, tout, cnt_t, sout)
         self.T = x.shape[0]
         return toks, scales, counts
 
-    def combine(self, y, out=None):
+    def combine(self, y, out=None, send_only=False):
         torch, L = self.torch, self.lib
         out = out if out is not None else torch.empty(self.T, self.H, dtype=torch.bfloat16, device=y.device)
         yin, oout = _tensor(y, BF16), _tensor(out, BF16)
         cin, cout = _hdr(CombIO()), _hdr(CombIO())
         cin.tokens, cout.tokens = ctypes.pointer(yin), ctypes.pointer(oout)
-        _lib.check(L.ncclEpCombine(self.handle, ctypes.byref(cin), ctypes.byref(cout), None, self._stream()), "ncclEpCombine", L)
+        ccfg = _hdr(CombCfg())
+        ccfg.send_only = 1 if send_only else 0
+        _lib.check(L.ncclEpCombine(self.handle, ctypes.byref(cin), ctypes.byref(cout), ctypes.byref(ccfg), self._stream()), "ncclEpCombine", L)
+        self._keep_c = (yin, oout, y, out)
         return out

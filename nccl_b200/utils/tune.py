@@ -22,7 +22,7 @@ from .. import _lib
 from ..core import BF16, FP32
 from . import perf
 
-ALGO_AUTO, ALGO_LL, ALGO_P2P, ALGO_NVLS, ALGO_NVLS1 = -1, 1, 2, 3, 8
+ALGO_AUTO, ALGO_LL, ALGO_P2P, ALGO_NVLS, ALGO_CE, ALGO_NVLS1 = -1, 1, 2, 3, 6, 8
 MODE_PUSH, MODE_PULL, MODE_MC, MODE_BULK = 0, 1, 2, 4
 
 
@@ -124,6 +124,8 @@ def main(argv=None):
                                 if coll in ("all_gather", "broadcast"):
                                     row["BMC/%d%s" % (c, sfx)] = measure(coll, nb, ALGO_NVLS, MODE_MC | MODE_BULK)
             toggles(False, False)
+            if not reduces and coll != "broadcast" and nb >= (1 << 20):
+                row["CE"] = measure(coll, nb, ALGO_CE, -1)   # copy engines: zero SMs
             best = min(row, key=row.get)
             factor = perf.bus_factor(coll, n)
             res[str(nb)] = {"best": best, "time_us": round(row[best], 2), "busbw_GBps": round(nb / row[best] / 1e3 * factor, 2),
@@ -190,8 +192,11 @@ def rows_from(res, use_mc=False, use_mb=False, slack=0.03):
         for key, t in plain.items():   # variants that the switch does not change (no "+mc" / "+mb" twin was measured)
             cand.setdefault(key, t)
         (algo, c), tbest = min(cand.items(), key=lambda kv: kv[1])
-        frugal = [cc for (aa, cc), t in cand.items() if aa == algo and t <= tbest * (1 + slack)]
-        c = min(frugal)
+        if ("CE", 0) in cand and cand[("CE", 0)] <= tbest * (1 + slack):
+            algo, c = "CE", 0                      # as fast as the best kernel and takes no SM
+        else:
+            frugal = [cc for (aa, cc), t in cand.items() if aa == algo and t <= tbest * (1 + slack)]
+            c = min(frugal)
         upto = int((s * sizes[i + 1]) ** 0.5) if i + 1 < len(sizes) else 1 << 40
         row = [upto, algo, c]
         if rows and rows[-1][1] == row[1] and rows[-1][2] == row[2]:

@@ -29,6 +29,7 @@ B200_PARAM(LLMulticast, "B200_LL_MC_MIN_RANKS", -1, "Flagged-line all-reduce / a
 B200_PARAM(CopyKernel, "B200_COPY_KERNEL", 0, "One-rank copy path: 0 = vector loads and stores, 1 = bulk-copy engines through shared memory (messages of 1 MiB and more)")
 B200_PARAM(StagePipeline, "B200_STAGE_PIPELINE", 1, "Reductions on unregistered buffers overlap the copies through the staging area with the kernels (two halves, side stream)")
 B200_PARAM(StagePipelineMin, "B200_STAGE_PIPELINE_MIN", 134217728, "Smallest message in bytes that is pipelined through the staging area")
+B200_PARAM(P2pDirect, "B200_P2P_DIRECT", 1, "Large sends write straight into a receive buffer that lies in a registered window (rendezvous) instead of going through the mailbox")
 B200_PARAM(LaunchPdl, "B200_PDL", 1, "Launch collectives with programmatic stream serialisation (the next kernel of the stream is scheduled while the previous one drains)")
 B200_PARAM(BarrierMulticast, "B200_BARRIER_MC_MIN_RANKS", -1, "Cross-GPU barriers arrive with one multimem.red on a multicast alias of the flag page from this many ranks on (0 = never, -1 = from the selection table)")
 
@@ -46,7 +47,7 @@ void tuningDefaults(TuningTable* t) {
   t->nvlsCtas = 32;
   t->p2pCtas = 64;
   t->copyCtas = 32;
-  t->sendrecvCtas = 8;
+  t->sendrecvCtas = 16;
   t->bytesPerCta = 128 << 10;
 }
 
@@ -136,7 +137,8 @@ ncclResult_t devPlaneCreate(ncclComm* comm) {
     NCCLCHECK(symInit(comm));
     dp->stageBytes = (size_t)paramScratchMb() << 20;
     dp->offLL = kSyncPageBytes;
-    dp->offMailbox = dp->offLL + kLLRegionBytes;
+    dp->offP2pLL = dp->offLL + kLLRegionBytes;
+    dp->offMailbox = dp->offP2pLL + kP2pLLBytes;
     dp->offStage = alignUp(dp->offMailbox + kMailboxBytes, (size_t)(2 << 20));
     dp->resSize = dp->offStage + dp->stageBytes;
     ncclResult_t r = memAlloc(&dp->resBase, dp->resSize, comm->cudaDev);
@@ -908,15 +910,20 @@ ncclResult_t devPlaneRunP2pGroup(ncclComm* comm, const std::vector<Task>& tasks)
     for (int p = 0; p < comm->nRanks; ++p) {
       char* base = (char*)dp->resWin->host.peerPtr[p];
       a.mailbox[p] = base + dp->offMailbox;
+      a.llbox[p] = base + dp->offP2pLL;
       a.ready[p] = (uint32_t*)(base + kOffP2pReady);
       a.ack[p] = (uint32_t*)(base + kOffP2pAck);
     }
     a.seq[comm->rank] = dp->p2pSeq;
     a.nOps[comm->rank] = (int)nOps;
     a.opBase[comm->rank] = 0;
+    for (int p = 0; p < comm->nRanks; ++p) a.rdv[p] = (void*)((char*)dp->resWin->host.peerPtr[p] + kOffP2pRdv);
+    a.opDone[comm->rank] = dp->priv + kPrivP2pDone;
+    a.winTable = paramP2pDirect() && comm->sym ? (void* const*)comm->sym->winTableDev : nullptr;
     int cta = 0;
     int perOpCap = std::max(1, std::min(dp->tune.sendrecvCtas, (int)(std::min(kMaxCtas, dp->smCount) / (int)nOps)));
     uint32_t posted[2][kMaxRanks] = {};   // chunks of earlier ops of this launch per direction and peer
+    int large[2][kMaxRanks] = {};         // large operations so far per direction and peer: their rendezvous line
     for (size_t i = 0; i < nOps; ++i) {
       const Task& t = *remote[first + i];
       P2pOp& o = a.ops[i];
@@ -924,8 +931,26 @@ ncclResult_t devPlaneRunP2pGroup(ncclComm* comm, const std::vector<Task>& tasks)
       o.isSend = t.func == FUNC_SEND;
       o.buf = o.isSend ? (void*)t.send : t.recv;
       o.bytes = t.count * typeSize(t.type);
-      size_t chunks = (o.bytes + kP2pChunkBytes - 1) / kP2pChunkBytes;
+      const size_t cb = p2pChunkOf(o.bytes);
+      size_t chunks = (o.bytes + cb - 1) / cb;
       o.ctaCount = (int)std::max<size_t>(1, std::min<size_t>(chunks, (size_t)perOpCap));
+      o.rdvLine = -1;
+      o.winSlot = -1;
+      o.winOff = 0;
+      if (a.winTable && o.bytes >= kP2pDirectMin) {
+        // both sides count the pair's large operations of this launch the same way (operations match in posting order)
+        int& ord = large[o.isSend ? 0 : 1][o.peer];
+        if (ord < kP2pRdvLines) o.rdvLine = ord;
+        ++ord;
+        if (o.rdvLine >= 0 && !o.isSend) {
+          SymWindow* w = symFindWindow(comm, o.buf, o.bytes);
+          if (w && w->symmetric && w->slot >= 0) {
+            o.winSlot = w->slot;
+            o.winOff = (uintptr_t)o.buf - (uintptr_t)w->host.userPtr;
+            o.ctaCount = 1;   // only waits: the sender writes straight into the buffer
+          }
+        }
+      }
       o.ctaBegin = cta;
       cta += o.ctaCount;
       o.seqOffset = posted[o.isSend ? 0 : 1][o.peer];

@@ -33,7 +33,7 @@ struct DevicePlane {
   void* resBase = nullptr;
   size_t resSize = 0;
   SymWindow* resWin = nullptr;
-  size_t offLL = 0, offMailbox = 0, offStage = 0, stageBytes = 0;
+  size_t offLL = 0, offP2pLL = 0, offMailbox = 0, offStage = 0, stageBytes = 0;
   uint32_t* priv = nullptr;           // private device words: epochs, ll epoch, p2p sequence numbers
   uint32_t* epochs = nullptr;
   uint32_t* llEpoch = nullptr;
@@ -78,6 +78,9 @@ void devPlaneForce(int algo, int mode);
 bool tuneParse(TuningTable* t, const std::string& json);
 void tuneLoadDefaults(TuningTable* t);
 TunePick tunePick(const TuningTable& t, int func, int n, size_t bytes);
+
+// copy-engine collectives (sched/ce_coll.cc): releases their stream waits when the communicator is aborted or revoked
+void ceCollRelease(ncclComm* comm);
 
 // memory manager (mem/memmgr.cc)
 ncclResult_t memSuspend(ncclComm* comm);

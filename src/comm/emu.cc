@@ -16,6 +16,7 @@ struct EmuCtx {
   char* sync[kMaxRanks] = {};      // per-rank sync page
   char* ll[kMaxRanks] = {};
   char* mailbox[kMaxRanks] = {};
+  char* llbox[kMaxRanks] = {};
   uint32_t* priv[kMaxRanks] = {};  // epochs | llEpoch(4) | p2pSeq(2*kMaxRanks+4)
   uint32_t* status[kMaxRanks] = {};
   uint64_t timeoutNs = 5000000000ull;
@@ -60,11 +61,12 @@ void* b200EmuCreate(int nRanks, unsigned long long timeoutMs) {
   const size_t privWords = kPrivWords;
   for (int p = 0; p < nRanks; ++p) {
     bool ok = cudaMalloc(&e->sync[p], kSyncPageBytes) == cudaSuccess && cudaMalloc(&e->ll[p], kLLRegionBytes) == cudaSuccess &&
-              cudaMalloc(&e->mailbox[p], kMailboxBytes) == cudaSuccess && cudaMalloc(&e->priv[p], privWords * 4) == cudaSuccess &&
+              cudaMalloc(&e->mailbox[p], kMailboxBytes) == cudaSuccess && cudaMalloc(&e->llbox[p], kP2pLLBytes) == cudaSuccess && cudaMalloc(&e->priv[p], privWords * 4) == cudaSuccess &&
               cudaMalloc(&e->status[p], 16) == cudaSuccess;
     if (!ok) { WARN("emulation: out of memory"); return nullptr; }
     cudaMemset(e->sync[p], 0, kSyncPageBytes);
     cudaMemset(e->ll[p], 0, kLLRegionBytes);
+    cudaMemset(e->llbox[p], 0, kP2pLLBytes);
     cudaMemset(e->priv[p], 0, privWords * 4);
     cudaMemset(e->status[p], 0, 16);
   }
@@ -75,7 +77,7 @@ void* b200EmuCreate(int nRanks, unsigned long long timeoutMs) {
 void b200EmuDestroy(void* ctx) {
   EmuCtx* e = (EmuCtx*)ctx;
   if (!e) return;
-  for (int p = 0; p < e->n; ++p) { cudaFree(e->sync[p]); cudaFree(e->ll[p]); cudaFree(e->mailbox[p]); cudaFree(e->priv[p]); cudaFree(e->status[p]); }
+  for (int p = 0; p < e->n; ++p) { cudaFree(e->sync[p]); cudaFree(e->ll[p]); cudaFree(e->mailbox[p]); cudaFree(e->llbox[p]); cudaFree(e->priv[p]); cudaFree(e->status[p]); }
   delete e;
 }
 
@@ -216,9 +218,12 @@ int b200EmuP2p(void* ctx, int nOps, const int* opRank, const int* peer, const in
   fillSyncEmu(e, &a.sync);
   for (int p = 0; p < n; ++p) {
     a.mailbox[p] = e->mailbox[p];
+    a.llbox[p] = e->llbox[p];
     a.ready[p] = (uint32_t*)(e->sync[p] + kOffP2pReady);
     a.ack[p] = (uint32_t*)(e->sync[p] + kOffP2pAck);
     a.seq[p] = e->priv[p] + kBarrierSlots + 4;
+    a.rdv[p] = (void*)(e->sync[p] + kOffP2pRdv);
+    a.opDone[p] = e->priv[p] + kPrivP2pDone;
     a.opBase[p] = -1;
   }
   int maxCtas = 1;
@@ -229,8 +234,8 @@ int b200EmuP2p(void* ctx, int nOps, const int* opRank, const int* peer, const in
     if (a.opBase[r] < 0) a.opBase[r] = i;
     a.nOps[r]++;
     uint32_t& before = posted[((size_t)r * 2 + (isSend[i] ? 0 : 1)) * kMaxRanks + peer[i]];
-    a.ops[i] = P2pOp{peer[i], isSend[i], buf[i], bytes[i], nextCta[r], ctasPerOp, before};
-    before += (uint32_t)((bytes[i] + kP2pChunkBytes - 1) / kP2pChunkBytes);
+    a.ops[i] = P2pOp{peer[i], isSend[i], buf[i], bytes[i], nextCta[r], ctasPerOp, before, -1, -1, 0};
+    before += (uint32_t)((bytes[i] + p2pChunkOf(bytes[i]) - 1) / p2pChunkOf(bytes[i]));
     nextCta[r] += ctasPerOp;
     maxCtas = std::max(maxCtas, nextCta[r]);
   }

@@ -395,6 +395,7 @@ ncclResult_t ncclCommAbort(ncclComm_t comm) {
     int cur = -1;
     cudaGetDevice(&cur);
     if (cur != comm->cudaDev) cudaSetDevice(comm->cudaDev);
+    ceCollRelease(comm);       // stream waits of the copy-engine collectives do not see the flag: release them
     cudaDeviceSynchronize();   // kernels leave their waits once they see the flag
     (void)cudaGetLastError();
     if (cur >= 0 && cur != comm->cudaDev) cudaSetDevice(cur);
@@ -413,6 +414,7 @@ ncclResult_t ncclCommRevoke(ncclComm_t comm, int revokeFlags) {
     int cur = -1;
     cudaGetDevice(&cur);
     if (cur != comm->cudaDev) cudaSetDevice(comm->cudaDev);
+    ceCollRelease(comm);
     cudaDeviceSynchronize();
     (void)cudaGetLastError();
     if (cur >= 0 && cur != comm->cudaDev) cudaSetDevice(cur);

@@ -427,6 +427,8 @@ void* b200EpEmuCreate(int n, int E, int K, int H, int maxTokens) {
   EpEmu* e = new EpEmu;
   memset(e, 0, sizeof(*e));
   e->n = n; e->E = E; e->El = E / n; e->K = K; e->H = H; e->maxTokens = maxTokens;
+  e->phases = 3;
+  e->timeoutNs = 3000000000ull;
   size_t zone = (size_t)e->El * n * maxTokens * epSlotBytes(H, 0);
   size_t comb = (size_t)maxTokens * K * H * 2;
   for (int r = 0; r < n; ++r) {

@@ -19,31 +19,42 @@ constexpr int kCtaThreads = 512;
 
 // Layout of the per-rank synchronisation page (first bytes of the resource window).
 constexpr size_t kInboxBytes = kBarrierSlots * kMaxRanks * sizeof(uint32_t);   // 8 KiB
-constexpr int kP2pSlots = 4;                       // mailbox chunks in flight per ordered pair
-constexpr size_t kP2pChunkBytes = 1 << 20;
+constexpr int kP2pSlots = 16;                      // mailbox chunks in flight per ordered pair: 8 MiB, enough for 16 CTAs per operation to keep the links busy
+constexpr size_t kP2pChunkBytes = 512 << 10;
 constexpr size_t kOffP2pReady = kInboxBytes;                                        // [src][slot] u32, written by sender
 constexpr size_t kOffP2pAck = kOffP2pReady + kMaxRanks * kP2pSlots * 4;             // [dst][slot] u32, written by receiver
 constexpr size_t kOffSignals = kOffP2pAck + kMaxRanks * kP2pSlots * 4;              // [src][kSignalsPerPeer] u64
 constexpr int kSignalsPerPeer = 64;
 constexpr size_t kOffSyncEnd = kOffSignals + kMaxRanks * kSignalsPerPeer * 8;
+constexpr size_t kOffP2pRdv = 14 << 10;                                             // [src][kP2pRdvLines] 16-byte rendezvous lines written by receivers
+constexpr int kP2pRdvLines = 4;                                                     // large operations of one ordered pair that one launch can run in rendezvous mode
+constexpr size_t kP2pDirectMin = 256 << 10;                                         // messages from this size on wait for the receiver's descriptor first
+constexpr int kMaxWinSlots = 256;                                                   // windows of a communicator that the device-side table knows
 constexpr size_t kOffMcBarrier = 13 << 10;                                          // [slot] u32: arrival counters of the multicast barrier
 constexpr size_t kOffRingFlags = 16 << 10;                                          // [slot][src] u32: ring step counters
 constexpr size_t kOffTreeFlags = 24 << 10;                                          // [slot][tree 2][src] u32: tree phase counters
 constexpr size_t kSyncPageBytes = 64 << 10;
 static_assert(kOffSyncEnd <= kOffMcBarrier && kOffMcBarrier + kBarrierSlots * 4 <= kOffRingFlags, "sync page overflow");
 static_assert(kOffTreeFlags + kBarrierSlots * 2 * kMaxRanks * 4 <= kSyncPageBytes, "sync page overflow");
+static_assert(kOffP2pRdv + kMaxRanks * kP2pRdvLines * 16 <= kOffRingFlags, "sync page overflow");
 // private per-rank words: barrier epochs | flagged-line epoch (4) | p2p sequence numbers | ring / tree step bases
 constexpr size_t kPrivLLEpoch = kBarrierSlots;
 constexpr size_t kPrivP2pSeq = kPrivLLEpoch + 4;
 constexpr size_t kPrivRingBase = kPrivP2pSeq + 2 * kMaxRanks + 4;
 constexpr size_t kPrivTreeBase = kPrivRingBase + kBarrierSlots;
 constexpr size_t kPrivMcEpoch = kPrivTreeBase + kBarrierSlots;       // epochs of the multicast barrier, per slot
-constexpr size_t kPrivWords = kPrivMcEpoch + kBarrierSlots;
+constexpr size_t kPrivP2pDone = kPrivMcEpoch + kBarrierSlots;        // finished CTAs per operation of a send/recv launch
+constexpr size_t kPrivWords = kPrivP2pDone + 32;
 
 constexpr size_t kLLDataBytes = 1 << 20;                     // largest payload of the flagged-line protocol
 constexpr size_t kLLLines = kLLDataBytes / 8;                // 8 payload bytes per 16-byte line
 constexpr size_t kLLRegionBytes = 2 * kMaxRanks * kLLLines * 16;   // [parity][src][line]
 constexpr size_t kMailboxBytes = (size_t)kMaxRanks * kP2pSlots * kP2pChunkBytes;  // [src][slot][chunk]
+// Small sends travel as flagged 16-byte lines (8 payload bytes + the chunk's sequence number twice): no fence and no
+// separate ready flag. The lines have an area of their own, so a line never holds anything but older lines.
+constexpr size_t kP2pLLMax = 4096;                                               // largest message sent as flagged lines
+constexpr size_t kP2pLLSlotBytes = kP2pLLMax * 2;
+constexpr size_t kP2pLLBytes = (size_t)kMaxRanks * kP2pSlots * kP2pLLSlotBytes;   // [src][slot][line]
 
 enum DevStatus : uint32_t { DEV_OK = 0, DEV_TIMEOUT = 1, DEV_ABORTED = 2 };
 enum DevWaitKind : uint32_t { WAIT_BARRIER = 1, WAIT_LL = 2, WAIT_P2P_READY = 3, WAIT_P2P_ACK = 4, WAIT_SIGNAL = 5, WAIT_TILE = 6 };
@@ -121,8 +132,24 @@ struct P2pOp {
   size_t bytes;
   int ctaBegin, ctaCount;   // CTAs [ctaBegin, ctaBegin+ctaCount) of the grid serve this op
   uint32_t seqOffset;       // mailbox chunks of earlier ops of this launch with the same peer and direction
+  // rendezvous mode (bytes >= kP2pDirectMin and rdvLine >= 0): the receiver tells the sender where the data goes
+  int rdvLine;              // which of the pair's rendezvous lines this op uses (its ordinal among the pair's large ops of the launch), -1: none
+  int winSlot;              // receive side: slot of the window that holds `buf` in the device-side table, -1: not in a peer-mapped window
+  size_t winOff;            // receive side: offset of `buf` inside that window
 };
 constexpr int kMaxP2pOps = 32;
+static_assert(kMaxP2pOps <= 32, "per-operation counters");
+
+// Chunk size of a message in the mailbox protocol: both sides derive it from the byte count. About sixteen
+// chunks per message (so that as many CTAs share it), between 64 KiB and the slot size.
+#if defined(__CUDACC__)
+__host__ __device__
+#endif
+inline size_t p2pChunkOf(size_t bytes) {
+  size_t c = ((bytes + 15) / 16 + 65535) / 65536 * 65536;
+  if (c < 65536) c = 65536;
+  return c > kP2pChunkBytes ? kP2pChunkBytes : c;
+}
 
 struct P2pArgs {
   int rank, nRanks;
@@ -131,9 +158,13 @@ struct P2pArgs {
   P2pOp ops[kMaxP2pOps];                 // emulation packs every rank's ops back to back: opBase[r]
   int opBase[kMaxRanks];
   char* mailbox[kMaxRanks];              // mailbox[p]: rank p's mailbox region [src][slot][chunk]
+  char* llbox[kMaxRanks];                // llbox[p]: rank p's flagged-line area for small messages [src][slot][line]
   uint32_t* ready[kMaxRanks];            // ready[p]: rank p's [src][slot] flags
   uint32_t* ack[kMaxRanks];              // ack[p]: rank p's [dst][slot] flags
   uint32_t* seq[kMaxRanks];              // seq[r]: private counters {send[kMaxRanks], recv[kMaxRanks]}
+  void* rdv[kMaxRanks];                  // rdv[p]: rank p's rendezvous lines [src][kP2pRdvLines], written by the receivers of p's sends
+  uint32_t* opDone[kMaxRanks];           // opDone[r]: private [kMaxP2pOps] counters of finished CTAs per operation
+  void* const* winTable;                 // device table [kMaxWinSlots][kMaxRanks]: where window slot w of rank p is mapped here (null: no rendezvous mode)
   SyncArgs sync;
 };
 

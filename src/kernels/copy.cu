@@ -219,6 +219,35 @@ __device__ __forceinline__ void copyChunk(char* dst, const char* src, size_t byt
   }
 }
 
+// Grid-strided copy of [begin, begin + bytes) by the CTAs `local` of `count` of one operation (16-byte packs when aligned).
+__device__ __forceinline__ void copyShare(char* dst, const char* src, size_t bytes, int local, int count) {
+  if ((((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {
+    const size_t packs = bytes / 16;
+    const size_t stride = (size_t)count * blockDim.x;
+    size_t i = (size_t)local * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < packs; i += 4 * stride) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = ldStream16(src + (i + u * stride) * 16);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) st16(dst + (i + u * stride) * 16, v[u]);
+    }
+    for (; i < packs; i += stride) st16(dst + i * 16, ldStream16(src + i * 16));
+    if (local == 0) for (size_t j = packs * 16 + threadIdx.x; j < bytes; j += blockDim.x) dst[j] = src[j];
+  } else {
+    const size_t stride = (size_t)count * blockDim.x;
+    for (size_t j = (size_t)local * blockDim.x + threadIdx.x; j < bytes; j += stride) dst[j] = src[j];
+  }
+}
+
+// Send / receive. Two protocols, chosen from the byte count (both sides know it) and the receiver's buffer:
+//   mailbox     the sender copies chunks into the receiver's mailbox (slots per ordered pair, ready / ack flags),
+//               the receiver copies them out: works for any buffer, two passes over the data;
+//   rendezvous  (large messages) the receiver first posts a 16-byte descriptor into the sender's flag page: its
+//               buffer lies in a peer-mapped window (slot, offset) or not. If it does, all CTAs of the send write
+//               straight into the receiver's buffer and the last one publishes one flag; the receiver only waits.
+//               If not, the message goes through the mailbox as above.
+// Sequence numbers count chunks per ordered pair in both protocols, so the two sides stay in step whichever ran.
 __global__ void __launch_bounds__(kCtaThreads, 1) p2pKernel(const __grid_constant__ P2pArgs a) {
   const int rank = ctaRank(a.emu, a.rank);
   pdlEnter();
@@ -226,20 +255,110 @@ __global__ void __launch_bounds__(kCtaThreads, 1) p2pKernel(const __grid_constan
   const P2pOp* ops = a.ops + a.opBase[rank];
   WaitCtx w{&a.sync, a.sync.status[rank]};
   uint32_t* seq = a.seq[rank];  // [0,kMaxRanks) send counters, [kMaxRanks,2*kMaxRanks) recv counters, [2*kMaxRanks] finished CTAs
+  __shared__ uint4 sDesc;
   int mine = -1;
   for (int i = 0; i < nOps; ++i)
     if ((int)blockIdx.x >= ops[i].ctaBegin && (int)blockIdx.x < ops[i].ctaBegin + ops[i].ctaCount) mine = i;
   if (mine >= 0) {
     const P2pOp op = ops[mine];
     const int local = blockIdx.x - op.ctaBegin;
-    const size_t nChunks = (op.bytes + kP2pChunkBytes - 1) / kP2pChunkBytes;
+    const size_t chunkBytes = p2pChunkOf(op.bytes);
+    const size_t nChunks = (op.bytes + chunkBytes - 1) / chunkBytes;
     const uint32_t base = (op.isSend ? seq[op.peer] : seq[kMaxRanks + op.peer]) + op.seqOffset;
+    const uint32_t qLast = base + (uint32_t)nChunks - 1;
     bool ok = true;
-    for (size_t c = local; c < nChunks && ok; c += op.ctaCount) {
+    bool direct = false;
+    const bool rdvMode = a.winTable != nullptr && op.rdvLine >= 0 && op.bytes >= kP2pDirectMin;
+    if (rdvMode) {
+      const uint32_t tag = base + 1;
+      if (op.isSend) {
+        // where does the receiver want the data?
+        if (threadIdx.x == 0) {
+          const uint4* line = (const uint4*)a.rdv[rank] + op.peer * kP2pRdvLines + op.rdvLine;
+          uint4 d = make_uint4(0, 0, 0, 0);
+          ok = boundedWait(w, WAIT_P2P_READY, (uint32_t)op.peer, tag, [&] { d = ldVolatile16(line); return d.x == tag; });
+          sDesc = d;
+        }
+        ok = __syncthreads_and(ok);
+        const uint4 d = sDesc;
+        if (ok && d.y != 0) {
+          direct = true;
+          char* dst = (char*)a.winTable[(size_t)(d.y - 1) * kMaxRanks + op.peer] + (((size_t)d.w << 32) | d.z);
+          copyShare(dst, (const char*)op.buf, op.bytes, local, op.ctaCount);
+          __syncthreads();
+          if (threadIdx.x == 0) {
+            fenceSys();   // this CTA's stores are ordered before the counter, and through it before the flag of the last CTA
+            uint32_t* doneCnt = a.opDone[rank] + mine;
+            if (atomicAdd(doneCnt, 1u) == (uint32_t)op.ctaCount - 1) {
+              *doneCnt = 0;
+              fenceSys();
+              stRelaxedSys(a.ready[op.peer] + rank * kP2pSlots + (qLast % kP2pSlots), qLast + 1);
+            }
+          }
+        }
+      } else {
+        direct = op.winSlot >= 0;
+        if (local == 0 && threadIdx.x == 0) {
+          uint4 d = make_uint4(tag, direct ? (uint32_t)op.winSlot + 1 : 0u, (uint32_t)op.winOff, (uint32_t)(op.winOff >> 32));
+          stVolatile16((uint4*)a.rdv[op.peer] + rank * kP2pRdvLines + op.rdvLine, d);
+        }
+        if (direct) {
+          if (threadIdx.x == 0) {
+            const uint32_t* rdy = a.ready[rank] + op.peer * kP2pSlots + (qLast % kP2pSlots);
+            const uint32_t want = qLast + 1;
+            ok = boundedWait(w, WAIT_P2P_READY, (uint32_t)op.peer, want, [&] { return (int32_t)(ldRelaxedSys(rdy) - want) >= 0; });
+            fenceSys();   // acquire: the data behind the flag
+            // the mailbox slots were not used: tell the sender that all of them are free up to this message
+            if (ok && local == 0)
+              for (int sl = 0; sl < kP2pSlots; ++sl) stRelaxedSys(a.ack[op.peer] + rank * kP2pSlots + sl, qLast + 1);
+          }
+          ok = __syncthreads_and(ok);
+        }
+      }
+    }
+    if (!rdvMode && op.bytes <= kP2pLLMax && nChunks == 1 && local == 0) {
+      // ---- small message: flagged lines, one chunk, one CTA
+      const uint32_t q = base, tag = base + 1;
+      const int slot = q % kP2pSlots;
+      const size_t nLines = (op.bytes + 7) / 8;
+      if (op.isSend) {
+        if (threadIdx.x == 0 && q >= (uint32_t)kP2pSlots) {
+          const uint32_t* ackp = a.ack[rank] + op.peer * kP2pSlots + slot;
+          const uint32_t want = q - kP2pSlots + 1;
+          ok = boundedWait(w, WAIT_P2P_ACK, (uint32_t)op.peer, want, [&] { return (int32_t)(ldRelaxedSys(ackp) - want) >= 0; });
+        }
+        ok = __syncthreads_and(ok);
+        char* dst = a.llbox[op.peer] + ((size_t)rank * kP2pSlots + slot) * kP2pLLSlotBytes;
+        const char* src = (const char*)op.buf;
+        for (size_t l = threadIdx.x; ok && l < nLines; l += blockDim.x) {
+          uint64_t d = 0;
+          const size_t valid = op.bytes - l * 8;
+          if (valid >= 8 && (((uintptr_t)src + l * 8) & 7) == 0) d = *(const uint64_t*)(src + l * 8);
+          else for (size_t b = 0; b < 8 && b < valid; ++b) d |= (uint64_t)(uint8_t)src[l * 8 + b] << (8 * b);
+          stVolatile16(dst + l * 16, make_uint4((uint32_t)d, tag, (uint32_t)(d >> 32), tag));
+        }
+      } else {
+        const char* src = a.llbox[rank] + ((size_t)op.peer * kP2pSlots + slot) * kP2pLLSlotBytes;
+        char* dst = (char*)op.buf;
+        for (size_t l = threadIdx.x; ok && l < nLines; l += blockDim.x) {
+          uint4 v = ldVolatile16(src + l * 16);
+          if (v.y != tag || v.w != tag) ok = boundedWait(w, WAIT_P2P_READY, (uint32_t)op.peer, tag, [&] { v = ldVolatile16(src + l * 16); return v.y == tag && v.w == tag; });
+          if (!ok) break;
+          const uint64_t d = (uint64_t)v.x | ((uint64_t)v.z << 32);
+          const size_t valid = op.bytes - l * 8;
+          if (valid >= 8 && (((uintptr_t)dst + l * 8) & 7) == 0) *(uint64_t*)(dst + l * 8) = d;
+          else for (size_t b = 0; b < 8 && b < valid; ++b) dst[l * 8 + b] = (char)(d >> (8 * b));
+        }
+        ok = __syncthreads_and(ok);
+        if (ok && threadIdx.x == 0) stRelaxedSys(a.ack[op.peer] + rank * kP2pSlots + slot, q + 1);   // every line was read before the barrier
+      }
+      direct = true;   // nothing left for the chunk loop
+    }
+    for (size_t c = local; !direct && c < nChunks && ok; c += op.ctaCount) {
       const uint32_t q = base + (uint32_t)c;
       const int slot = q % kP2pSlots;
-      const size_t off = c * kP2pChunkBytes;
-      const size_t len = op.bytes - off < kP2pChunkBytes ? op.bytes - off : kP2pChunkBytes;
+      const size_t off = c * chunkBytes;
+      const size_t len = op.bytes - off < chunkBytes ? op.bytes - off : chunkBytes;
       if (op.isSend) {
         // the slot is free once the receiver has consumed the chunk that used it last (q - slots)
         // (sequence numbers run across calls, so this also covers slots used by the previous call)
@@ -283,7 +402,8 @@ __global__ void __launch_bounds__(kCtaThreads, 1) p2pKernel(const __grid_constan
     if (done == gridDim.x - 1) {
       seq[2 * kMaxRanks] = 0;
       for (int i = 0; i < nOps; ++i) {
-        uint32_t chunks = (uint32_t)((ops[i].bytes + kP2pChunkBytes - 1) / kP2pChunkBytes);
+        const size_t cb = p2pChunkOf(ops[i].bytes);
+        uint32_t chunks = (uint32_t)((ops[i].bytes + cb - 1) / cb);
         if (ops[i].isSend) seq[ops[i].peer] += chunks; else seq[kMaxRanks + ops[i].peer] += chunks;
       }
     }

@@ -34,6 +34,11 @@ ncclResult_t symInit(ncclComm* comm) {
   for (auto& p : comm->peers) { mc = mc && p.mcSupport; vmm = vmm && p.vmmSupport; }
   s->vmmUsable = vmm && comm->lsaAll;
   s->mcUsable = mc && s->vmmUsable && comm->nRanks > 1;
+  if (cudaMalloc(&s->winTableDev, (size_t)kMaxWinSlots * kMaxRanks * sizeof(void*)) != cudaSuccess ||
+      cudaMemset(s->winTableDev, 0, (size_t)kMaxWinSlots * kMaxRanks * sizeof(void*)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    s->winTableDev = nullptr;   // rendezvous send / receive stays off; everything else works
+  }
   comm->sym = s;
   INFO(SUB_INIT, "symmetric runtime: vmm %d multicast %d", (int)s->vmmUsable, (int)s->mcUsable);
   return ncclSuccess;
@@ -78,6 +83,7 @@ void symDestroy(ncclComm* comm) {
     delete w;
   }
   for (auto* seg : s->segments) releaseSegment(comm, seg);
+  if (s->winTableDev) cudaFree(s->winTableDev);
   ipcClose(&s->ipc);
   delete s;
   comm->sym = nullptr;
@@ -386,6 +392,19 @@ ncclResult_t symWindowRegister(ncclComm* comm, void* buff, size_t size, SymWindo
   cudaMemcpy(dev, &w->host, sizeof(ncclWindow_vidmem), cudaMemcpyHostToDevice);
   symWindowPublishHandle(w);
   s->windows.push_back(w);
+  if (w->symmetric && s->winTableDev) {
+    for (int i = 0; i < kMaxWinSlots; ++i)
+      if (!s->slotUsed[i]) { w->slot = i; s->slotUsed[i] = true; break; }
+    if (w->slot >= 0) {
+      void* row[kMaxRanks] = {};
+      for (int p = 0; p < n; ++p) row[p] = w->host.peerPtr[p];
+      if (cudaMemcpy(s->winTableDev + (size_t)w->slot * kMaxRanks, row, sizeof(row), cudaMemcpyHostToDevice) != cudaSuccess) {
+        (void)cudaGetLastError();
+        s->slotUsed[w->slot] = false;
+        w->slot = -1;
+      }
+    }
+  }
   INFO(SUB_REG, "window %p size %zu: %s%s", buff, size, w->symmetric ? (kind == SEG_VMM ? "symmetric (vmm)" : "symmetric (ipc)") : "local only",
        w->host.mcPtr ? " + multicast" : "");
   *out = w;
@@ -415,6 +434,12 @@ ncclResult_t symWindowDeregister(ncclComm* comm, SymWindow* win) {
   auto it = std::find(s->windows.begin(), s->windows.end(), win);
   if (it == s->windows.end()) return ncclInvalidArgument;
   s->windows.erase(it);
+  if (win->slot >= 0) {
+    cudaDeviceSynchronize();   // no kernel may still resolve addresses through this row
+    cudaMemset(s->winTableDev + (size_t)win->slot * kMaxRanks, 0, kMaxRanks * sizeof(void*));
+    s->slotUsed[win->slot] = false;
+    win->slot = -1;
+  }
   if (win->seg && --win->seg->refs == 0) {
     auto sit = std::find(s->segments.begin(), s->segments.end(), win->seg);
     if (sit != s->segments.end()) s->segments.erase(sit);

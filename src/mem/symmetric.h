@@ -47,6 +47,7 @@ struct alignas(4096) SymWindow {
   size_t offset = 0;               // offset of the window inside my allocation
   int flags = 0;
   bool symmetric = false;          // peers are mapped; false = local-only registration
+  int slot = -1;                   // row of this window in the device-side table of peer mappings (same on every rank), -1: none
 };
 
 void symWindowPublishHandle(SymWindow* w);     // after `host` is complete: make &w->host readable from kernels
@@ -62,6 +63,11 @@ struct SymRuntime {
   std::vector<SymWindow*> windows;
   std::vector<std::pair<IpcMsg, int>> stash;   // early datagrams of a later stage
   std::mutex lock;
+  // Device-side table [kMaxWinSlots][kMaxRanks] of where every symmetric window is mapped on this rank: kernels that learn
+  // "window slot, offset" from a peer (send / receive rendezvous) turn it into an address here. Registration is collective and
+  // slots are handed out lowest-free-first, so a window has the same slot on every rank.
+  void** winTableDev = nullptr;
+  bool slotUsed[kMaxWinSlots] = {};
 };
 
 ncclResult_t symInit(ncclComm* comm);

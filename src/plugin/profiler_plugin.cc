@@ -50,7 +50,14 @@ ncclResult_t profilerLoad(ncclComm* comm) {
   void* lib = pluginOpen(PLUGIN_PROFILER, &resolved);
   if (!lib) return ncclSuccess;
   ncclProfiler_v6_t* p = (ncclProfiler_v6_t*)pluginSymbol(lib, NCCL_PROFILER_PLUGIN_SYMBOL);
-  if (!p) { WARN("profiler plugin %s does not export %s (older interfaces are not supported)", resolved.c_str(), NCCL_PROFILER_PLUGIN_SYMBOL); return ncclSuccess; }
+  bool v5 = false;
+  if (!p) {
+    // The v5 table has the same entry points and its event descriptor is the v6 one without the copy-engine events at the
+    // end of the union: a v5 plugin is driven through the same calls with those three event types masked off.
+    p = (ncclProfiler_v6_t*)pluginSymbol(lib, "ncclProfiler_v5");
+    v5 = p != nullptr;
+  }
+  if (!p) { WARN("profiler plugin %s exports neither %s nor ncclProfiler_v5 (older interfaces are not supported)", resolved.c_str(), NCCL_PROFILER_PLUGIN_SYMBOL); return ncclSuccess; }
   ProfilerState* ps = new ProfilerState;
   ps->lib = lib;
   ps->prof = p;
@@ -60,9 +67,10 @@ ncclResult_t profilerLoad(ncclComm* comm) {
   if (m && *m) mask = (int)strtol(m, nullptr, 0);
   ncclResult_t r = p->init(&ps->ctx, comm->commHash, &mask, comm->name.c_str(), comm->nNodes, comm->nRanks, comm->rank, pluginLogger);
   if (r != ncclSuccess) { WARN("profiler plugin %s failed to initialise (%d)", ps->name.c_str(), (int)r); delete ps; return ncclSuccess; }
+  if (v5) mask &= ~(ncclProfileCeColl | ncclProfileCeSync | ncclProfileCeBatch);
   ps->mask = mask;
   comm->profiler = ps;
-  INFO(SUB_PROFILE, "profiler plugin %s (%s) attached, event mask 0x%x", ps->name.c_str(), resolved.c_str(), mask);
+  INFO(SUB_PROFILE, "profiler plugin %s (%s, interface v%d) attached, event mask 0x%x", ps->name.c_str(), resolved.c_str(), v5 ? 5 : 6, mask);
   return ncclSuccess;
 }
 

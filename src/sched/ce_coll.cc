@@ -30,6 +30,25 @@ static ncclResult_t ceBarrier(ncclComm* comm, cudaStream_t stream, uint32_t valu
   return ncclSuccess;
 }
 
+// Stream waits of this path have no time limit of their own and do not look at the abort flag. ncclCommAbort and
+// ncclCommRevoke therefore call this before they drain the device: it writes the newest value that any queued wait
+// of this rank can be waiting for into every word of the copy engines' barrier row (from a stream of its own, since
+// the caller's streams are blocked behind those waits), which releases them; the data behind them is abandoned.
+void ceCollRelease(ncclComm* comm) {
+  DevicePlane* dp = comm->devPlane;
+  const CuApi* cu = cuApi();
+  if (!dp || !cu || !dp->resBase || dp->ceEpoch == 0) return;
+  cudaStream_t s = nullptr;
+  if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) { (void)cudaGetLastError(); return; }
+  for (int p = 0; p < comm->nRanks; ++p) {
+    uint32_t* w = (uint32_t*)dp->resBase + (size_t)kCeSlot * kMaxRanks + p;
+    cu->cuStreamWriteValue32((CUstream)s, (CUdeviceptr)w, (uint32_t)dp->ceEpoch, CU_STREAM_WRITE_VALUE_DEFAULT);
+  }
+  cudaStreamSynchronize(s);
+  cudaStreamDestroy(s);
+  (void)cudaGetLastError();
+}
+
 ncclResult_t ceCollRun(ncclComm* comm, const Task& t, bool* handled) {
   *handled = false;
   DevicePlane* dp = comm->devPlane;

@@ -31,7 +31,7 @@ int tuneCollOfFunc(int func) {
 }
 
 // Grammar: { "<n>": { "<coll>": [ [upto, "ALGO", ctas], ... ], ... }, ..., "<switch>": number, ... }  with ALGO in
-// LL, P2P, NVLS, NVLS1, PUSH, PULL, MC, BPUSH, BPULL, BMC.
+// LL, P2P, NVLS, NVLS1, PUSH, PULL, MC, BPUSH, BPULL, BMC, CE.
 struct Cursor {
   const char* p;
   void ws() { while (*p && isspace((unsigned char)*p)) ++p; }
@@ -90,6 +90,7 @@ bool tuneParse(TuningTable* t, const std::string& json) {
         else if (algo == "NVLS") e.algo = ALGO_NVLS;
         else if (algo == "NVLS1") e.algo = ALGO_NVLS_ONESHOT;
         else if (algo == "MC") { e.algo = ALGO_NVLS; e.mode = MODE_MC; }
+        else if (algo == "CE") e.algo = ALGO_CE;                      // copy engines: no SM at all
         else if (algo == "PUSH") e.mode = MODE_PUSH;
         else if (algo == "PULL") e.mode = MODE_PULL;
         else if (algo == "BPUSH") e.mode = MODE_PUSH | MODE_BULK;   // bulk-copy engines instead of threads

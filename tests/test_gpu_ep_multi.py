@@ -8,7 +8,7 @@ from mp_util import run_ranks  # noqa: E402
 pytestmark = pytest.mark.gpu
 
 
-def _ep_rank(rank, nranks, uid, E, K, H, T):
+def _ep_rank(rank, nranks, uid, E, K, H, T, split=False):
     import torch
     torch.cuda.set_device(rank)
     from nccl_b200 import Communicator
@@ -21,7 +21,11 @@ def _ep_rank(rank, nranks, uid, E, K, H, T):
         x = torch.randn(T, H, generator=g).bfloat16().cuda()
         idx = torch.rand(T, E, generator=g).topk(K, dim=1).indices.to(torch.int64).cuda()
         w = torch.softmax(torch.randn(T, K, generator=g), dim=1).cuda()
-        toks, scales, counts = ep.dispatch(x, idx, w, fp8=bool(rep % 2))
+        toks, scales, counts = ep.dispatch(x, idx, w, fp8=bool(rep % 2), send_only=split)
+        if split:
+            filler = torch.ones(1 << 20, device="cuda").mul_(2.0)   # work of the caller between the two halves
+            ep.complete()
+            del filler
         torch.cuda.synchronize()
         if rep % 2:
             y = (toks.view(torch.float8_e4m3fn).float().view(ep.El, ep.cap, H // 128, 128) * scales.unsqueeze(-1)).view(ep.El, ep.cap, H).bfloat16()
@@ -30,8 +34,11 @@ def _ep_rank(rank, nranks, uid, E, K, H, T):
         # expert e multiplies by (e + 1)
         for el in range(ep.El):
             y[el] *= float(rank * ep.El + el + 1)
-        out = ep.combine(y.contiguous())
+        out = ep.combine(y.contiguous(), send_only=split)
+        if split:
+            ep.complete()
         torch.cuda.synchronize()
+        assert ep.mask() == [0] * nranks
         scale = torch.zeros(T, 1, device="cuda")
         for k in range(K):
             scale[:, 0] += w[:, k] * (idx[:, k] + 1).float()
@@ -44,14 +51,15 @@ def _ep_rank(rank, nranks, uid, E, K, H, T):
     return res
 
 
+@pytest.mark.parametrize("split", [False, True])
 @pytest.mark.parametrize("E,K,H,T", [(16, 2, 256, 32), (64, 8, 1024, 128)])
-def test_ep_roundtrip(E, K, H, T):
+def test_ep_roundtrip(E, K, H, T, split):
     n = min(torch.cuda.device_count() if torch.cuda.is_available() else 0, 8)
     if n < 2:
         pytest.skip("needs at least two GPUs")
     if E % n:
         pytest.skip("experts do not divide over the ranks")
-    res = run_ranks(_ep_rank, n, args=(E, K, H, T), timeout=300)
+    res = run_ranks(_ep_rank, n, args=(E, K, H, T, split), timeout=300)
     for rep in range(3):
         assert sum(res[r]["count%d" % rep] for r in range(n)) == n * T * K
         tol = 0.12 if rep % 2 else 0.03

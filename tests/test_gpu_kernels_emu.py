@@ -480,3 +480,35 @@ def test_batched_allreduce_one_launch(emu_lib, n, dtype, op):
                     assert bool((outs[r][o + c:o + c + 3].float() == 0).all()), "padding between items was written"
     finally:
         emu_lib.b200EmuDestroy(ctx)
+
+
+def test_send_recv_small_and_mixed_sizes_many_rounds(emu_lib):
+    """Forty rounds of a ring exchange whose size changes every round (1 byte ... 1 MiB, at odd offsets): small
+    messages travel as flagged lines, larger ones through the chunked mailbox, and the per-pair sequence numbers,
+    slot reuse and acknowledgements must stay in step across the two protocols."""
+    n = 3
+    ctx = emu_lib.b200EmuCreate(n, 5000)
+    try:
+        g = torch.Generator().manual_seed(17)
+        sizes_cycle = [1, 8, 9, 4096, 4097, 100, 65536 + 3, 7, 4095, (1 << 20) + 5, 16, 3000]
+        for rep in range(40):
+            nbytes = sizes_cycle[rep % len(sizes_cycle)]
+            off = rep % 3   # unaligned user buffers
+            send = [torch.randint(0, 256, (nbytes + off,), generator=g, dtype=torch.uint8).cuda()[off:] for _ in range(n)]
+            recv = [torch.full((nbytes + off + 8,), 0xAB, dtype=torch.uint8, device="cuda") for _ in range(n)]
+            ranks, peers, sends, bufs, sizes = [], [], [], [], []
+            for r in range(n):
+                ranks += [r, r]
+                peers += [(r + 1) % n, (r - 1) % n]
+                sends += [1, 0]
+                bufs += [send[r], recv[r][off:off + nbytes]]
+                sizes += [nbytes, nbytes]
+            k = len(ranks)
+            rc = emu_lib.b200EmuP2p(ctx, k, (ctypes.c_int * k)(*ranks), (ctypes.c_int * k)(*peers), (ctypes.c_int * k)(*sends),
+                                    _ptrs(bufs), (ctypes.c_size_t * k)(*sizes), 2)
+            assert rc == 0, rep
+            for r in range(n):
+                assert torch.equal(recv[r][off:off + nbytes], send[(r - 1) % n]), "rank %d round %d size %d" % (r, rep, nbytes)
+                assert bool((recv[r][:off] == 0xAB).all()) and bool((recv[r][off + nbytes:] == 0xAB).all()), "wrote outside the buffer"
+    finally:
+        emu_lib.b200EmuDestroy(ctx)

@@ -102,6 +102,33 @@ def test_back_to_back_small_collectives(mc):
         assert res[r]["bad"] == 0 and res[r]["err"] == 0, res[r]
 
 
+def test_copy_collectives_on_bulk_engines(tmp_path):
+    """A selection table that sends every copy collective to the bulk-copy kernels (push, pull and multicast forms)."""
+    import json
+    n = min(_ngpus(), 8)
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    big = 1 << 40
+    table = {str(n): {"all_gather": [[big, "BMC", 4]], "all_to_all": [[big, "BPULL", 3]], "broadcast": [[big, "BPUSH", 2]]}}
+    path = tmp_path / "bulk_table.json"
+    path.write_text(json.dumps(table))
+    for registered in (True, False):
+        res = run_ranks(_colls_rank, n, args=(registered, ""), env={"NCCL_TUNING_FILE": str(path)}, timeout=300)
+        _check(res, n)
+
+
+@pytest.mark.parametrize("algo", ["", "P2P"])
+def test_unregistered_reductions_pipelined_through_small_staging(algo):
+    """A 2 MiB staging area and a 1 MiB pipelining threshold: the 4 MiB all-reduce of the battery runs as several
+    pieces whose copies overlap the kernels on a side stream."""
+    n = min(_ngpus(), 8)
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    env = {"NCCL_B200_SCRATCH_MB": "2", "NCCL_B200_STAGE_PIPELINE_MIN": "1048576"}
+    res = run_ranks(_colls_rank, n, args=(False, algo), env=env, timeout=300)
+    _check(res, n)
+
+
 def _types_rank(rank, nranks, uid, algo):
     """All-reduce and reduce-scatter of every type / operator pair that has a multimem.ld_reduce form
     (plus one without, which must fall back), on registered buffers, checked on the device."""
