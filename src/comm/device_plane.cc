@@ -47,7 +47,7 @@ void tuningDefaults(TuningTable* t) {
   t->nvlsCtas = 32;
   t->p2pCtas = 64;
   t->copyCtas = 32;
-  t->sendrecvCtas = 16;
+  t->sendrecvCtas = 32;
   t->bytesPerCta = 128 << 10;
 }
 
@@ -130,6 +130,7 @@ ncclResult_t devPlaneCreate(ncclComm* comm) {
   dp->llEpoch = dp->priv + kBarrierSlots;
   dp->p2pSeq = dp->llEpoch + 4;
   dp->sigSeen = (uint64_t*)(dp->priv + kPrivWords);
+  memTrack(comm, dp->priv, privWords * sizeof(uint32_t), MEM_PERSIST, "epochs and sequence numbers");
   if (comm->nRanks == 1) return ncclSuccess;
 
   int usable = comm->lsaAll ? 1 : 0;
@@ -149,6 +150,15 @@ ncclResult_t devPlaneCreate(ncclComm* comm) {
     }
     if (r == ncclSuccess) r = symWindowRegister(comm, dp->resBase, dp->resSize, &dp->resWin, NCCL_WIN_COLL_SYMMETRIC);
     if (r != ncclSuccess || !dp->resWin || !dp->resWin->symmetric) usable = 0;
+    if (usable) {
+      // the resource window is working memory: a suspend gives it back, a resume maps it again with clean flags
+      // and restarts every epoch and sequence number that is compared against them
+      memTrack(comm, dp->resBase, dp->resSize, MEM_SCRATCH, "resource window", &dp->resWin, NCCL_WIN_COLL_SYMMETRIC, dp->offMailbox, [comm] {
+        DevicePlane* d = comm->devPlane;
+        cudaMemset(d->priv, 0, (kPrivWords + 2 * kMaxRanks * kSignalsPerPeer) * sizeof(uint32_t));
+        d->ceEpoch = 0;
+      });
+    }
   }
   // every rank must reach the same verdict
   std::vector<int> oks(comm->nRanks, 0);

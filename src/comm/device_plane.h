@@ -3,6 +3,8 @@
 // Reference parity: the roles of src/enqueue.cc (plan + launch), src/sym_kernels.cc (kernel choice)
 // and src/scheduler/symmetric_sched.cc in the reference, reduced to one launch per collective.
 #pragma once
+#include <functional>
+
 #include "../kernels/launch.h"
 #include "../mem/symmetric.h"
 #include "comm.h"
@@ -82,7 +84,11 @@ TunePick tunePick(const TuningTable& t, int func, int n, size_t bytes);
 // copy-engine collectives (sched/ce_coll.cc): releases their stream waits when the communicator is aborted or revoked
 void ceCollRelease(ncclComm* comm);
 
-// memory manager (mem/memmgr.cc)
+// memory manager (mem/memmgr.cc): classes of tracked allocations and the tracking calls their owners make
+enum MemClass : int { MEM_PERSIST = 0, MEM_SCRATCH = 1, MEM_OFFLOAD = 2 };
+void memTrack(ncclComm* comm, void* ptr, size_t bytes, int cls, const char* what, SymWindow** win = nullptr, int winFlags = 0,
+              size_t zeroBytes = 0, std::function<void()> afterResume = nullptr);
+void memUntrack(ncclComm* comm, void* ptr);
 ncclResult_t memSuspend(ncclComm* comm);
 ncclResult_t memResume(ncclComm* comm);
 ncclResult_t memStats(ncclComm* comm, int stat, uint64_t* value);

@@ -163,6 +163,11 @@ ncclResult_t ncclEpCreateGroup(ncclEpGroup_t* out, ncclComm_t comm, const ncclEp
     if (!g->recvWin->symmetric || !g->ctlWin->symmetric) { WARN("ncclEpCreateGroup: windows could not be mapped by the peers"); return ncclInternalError; }
     NCCLCHECK(bootstrapBarrier(comm->bootstrap));
   }
+  // landing zones and flags are working memory: a suspended communicator gives them back; flags and epochs restart together
+  memTrack(comm, g->recvZone, 2 * g->zoneBytes, MEM_SCRATCH, "expert-parallel landing zones", n > 1 ? &g->recvWin : nullptr, NCCL_WIN_COLL_SYMMETRIC);
+  memTrack(comm, g->ctl, ctlBytes(g->El, n), MEM_SCRATCH, "expert-parallel counts and flags", n > 1 ? &g->ctlWin : nullptr, NCCL_WIN_COLL_SYMMETRIC,
+           ctlBytes(g->El, n), [g] { cudaMemset(g->state, 0, (8 + g->E) * sizeof(uint32_t)); });
+  memTrack(comm, g->state, (8 + g->E) * sizeof(uint32_t), MEM_PERSIST, "expert-parallel epochs");
   if (cur != comm->cudaDev) cudaSetDevice(cur);
   *out = g;
   return ncclSuccess;
@@ -171,6 +176,10 @@ ncclResult_t ncclEpCreateGroup(ncclEpGroup_t* out, ncclComm_t comm, const ncclEp
 ncclResult_t ncclEpGroupDestroy(ncclEpGroup_t g) {
   if (!g) return ncclSuccess;
   cudaDeviceSynchronize();
+  memUntrack(g->comm, g->recvZone);
+  memUntrack(g->comm, g->ctl);
+  memUntrack(g->comm, g->state);
+  if (g->combZone) memUntrack(g->comm, g->combZone);
   if (g->recvWin) symWindowDeregister(g->comm, g->recvWin);
   if (g->ctlWin) symWindowDeregister(g->comm, g->ctlWin);
   if (g->combWin) symWindowDeregister(g->comm, g->combWin);
@@ -202,6 +211,7 @@ ncclResult_t ncclEpInitHandle(ncclEpHandle_t* out, ncclEpGroup_t g, ncclEpLayout
       NCCLCHECK(symWindowRegister(g->comm, g->combZone, 2 * g->combZoneBytes, &g->combWin, NCCL_WIN_COLL_SYMMETRIC));
       if (!g->combWin->symmetric) return ncclInternalError;
     }
+    memTrack(g->comm, g->combZone, 2 * g->combZoneBytes, MEM_SCRATCH, "expert-parallel combine zones", g->n > 1 ? &g->combWin : nullptr, NCCL_WIN_COLL_SYMMETRIC);
   } else if (g->K != num_topk) {
     WARN("ncclEp: all handles of a group must use the same top-k (%d, got %d)", g->K, num_topk);
     return ncclInvalidUsage;

@@ -52,7 +52,7 @@ constexpr size_t kLLRegionBytes = 2 * kMaxRanks * kLLLines * 16;   // [parity][s
 constexpr size_t kMailboxBytes = (size_t)kMaxRanks * kP2pSlots * kP2pChunkBytes;  // [src][slot][chunk]
 // Small sends travel as flagged 16-byte lines (8 payload bytes + the chunk's sequence number twice): no fence and no
 // separate ready flag. The lines have an area of their own, so a line never holds anything but older lines.
-constexpr size_t kP2pLLMax = 4096;                                               // largest message sent as flagged lines
+constexpr size_t kP2pLLMax = 16384;                                              // largest message sent as flagged lines
 constexpr size_t kP2pLLSlotBytes = kP2pLLMax * 2;
 constexpr size_t kP2pLLBytes = (size_t)kMaxRanks * kP2pSlots * kP2pLLSlotBytes;   // [src][slot][line]
 

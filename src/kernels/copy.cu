@@ -205,12 +205,13 @@ __device__ __forceinline__ void copyChunk(char* dst, const char* src, size_t byt
   if ((((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {
     const size_t packs = bytes / 16;
     size_t i = threadIdx.x;
-    for (; i + 3 * blockDim.x < packs; i += 4 * blockDim.x) {
-      uint4 v[4];
+    // eight independent 16-byte loads in flight per thread: one CTA moves a chunk at a time, so its own queue depth is what counts
+    for (; i + 7 * blockDim.x < packs; i += 8 * blockDim.x) {
+      uint4 v[8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) v[u] = ldStream16(src + (i + u * blockDim.x) * 16);
+      for (int u = 0; u < 8; ++u) v[u] = ldStream16(src + (i + u * blockDim.x) * 16);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) st16(dst + (i + u * blockDim.x) * 16, v[u]);
+      for (int u = 0; u < 8; ++u) st16(dst + (i + u * blockDim.x) * 16, v[u]);
     }
     for (; i < packs; i += blockDim.x) st16(dst + i * 16, ldStream16(src + i * 16));
     for (size_t j = packs * 16 + threadIdx.x; j < bytes; j += blockDim.x) dst[j] = src[j];

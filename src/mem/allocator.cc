@@ -115,16 +115,80 @@ ncclResult_t memFree(void* ptr) {
     if (it == gAllocs.end()) { WARN("ncclMemFree: %p was not allocated by ncclMemAlloc", ptr); return ncclInvalidArgument; }
     m = it->second;
     gAllocs.erase(it);
-    gTotal -= m.size;
+    if (!m.detached) gTotal -= m.size;
   }
   if (m.vmm) {
     const CuApi* cu = cuApi();
-    CUCHECK(cu->cuMemUnmap((CUdeviceptr)m.ptr, m.size));
-    CUCHECK(cu->cuMemRelease(m.handle));
+    if (!m.detached) {
+      CUCHECK(cu->cuMemUnmap((CUdeviceptr)m.ptr, m.size));
+      CUCHECK(cu->cuMemRelease(m.handle));
+    }
     CUCHECK(cu->cuMemAddressFree((CUdeviceptr)m.ptr, m.size));
   } else {
     CUDACHECK(cudaFree(m.ptr));
   }
+  return ncclSuccess;
+}
+
+static ncclResult_t mapPhysical(MemAlloc& m) {
+  const CuApi* cu = cuApi();
+  CUmemAllocationProp prop = {};
+  prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  prop.location.id = m.dev;
+  prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  int rdma = 0;
+  CUdevice cudev;
+  if (cu->cuDeviceGet(&cudev, m.dev) == CUDA_SUCCESS)
+    cu->cuDeviceGetAttribute(&rdma, CU_DEVICE_ATTRIBUTE_GPU_DIRECT_RDMA_WITH_CUDA_VMM_SUPPORTED, cudev);
+  if (rdma) prop.allocFlags.gpuDirectRDMACapable = 1;
+  CUCHECK(cu->cuMemCreate(&m.handle, m.size, &prop, 0));
+  CUresult r = cu->cuMemMap((CUdeviceptr)m.ptr, m.size, 0, m.handle, 0);
+  if (r != CUDA_SUCCESS) { cu->cuMemRelease(m.handle); WARN("cuMemMap (re-attach): %s", cuErrStr(r)); return ncclUnhandledCudaError; }
+  int ndev = 0;
+  cudaGetDeviceCount(&ndev);
+  std::vector<CUmemAccessDesc> acc;
+  for (int d = 0; d < ndev; ++d) {
+    int can = d == m.dev;
+    if (!can) { if (cudaDeviceCanAccessPeer(&can, d, m.dev) != cudaSuccess) { can = 0; (void)cudaGetLastError(); } }
+    if (!can) continue;
+    CUmemAccessDesc ad = {};
+    ad.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+    ad.location.id = d;
+    ad.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    acc.push_back(ad);
+  }
+  r = cu->cuMemSetAccess((CUdeviceptr)m.ptr, m.size, acc.data(), acc.size());
+  if (r != CUDA_SUCCESS) { cu->cuMemUnmap((CUdeviceptr)m.ptr, m.size); cu->cuMemRelease(m.handle); WARN("cuMemSetAccess (re-attach): %s", cuErrStr(r)); return ncclUnhandledCudaError; }
+  return ncclSuccess;
+}
+
+ncclResult_t memDetachPhysical(void* ptr) {
+  std::lock_guard<std::mutex> g(gLock);
+  auto it = gAllocs.find((uintptr_t)ptr);
+  if (it == gAllocs.end()) return ncclInvalidArgument;
+  MemAlloc& m = it->second;
+  if (!m.vmm) return ncclInvalidUsage;
+  if (m.detached) return ncclSuccess;
+  const CuApi* cu = cuApi();
+  CUCHECK(cu->cuMemUnmap((CUdeviceptr)m.ptr, m.size));
+  CUCHECK(cu->cuMemRelease(m.handle));
+  m.handle = 0;
+  m.detached = true;
+  gTotal -= m.size;
+  return ncclSuccess;
+}
+
+ncclResult_t memAttachPhysical(void* ptr) {
+  std::lock_guard<std::mutex> g(gLock);
+  auto it = gAllocs.find((uintptr_t)ptr);
+  if (it == gAllocs.end()) return ncclInvalidArgument;
+  MemAlloc& m = it->second;
+  if (!m.vmm) return ncclInvalidUsage;
+  if (!m.detached) return ncclSuccess;
+  NCCLCHECK(mapPhysical(m));
+  m.detached = false;
+  gTotal += m.size;
   return ncclSuccess;
 }
 

@@ -12,6 +12,7 @@ struct MemAlloc {
   int dev = -1;
   bool vmm = false;       // created with cuMemCreate (exportable, multicast-bindable)
   CUmemGenericAllocationHandle handle = 0;
+  bool detached = false;  // the physical memory was given back (memDetachPhysical); the address range is still reserved
 };
 
 // Granularity used for every shareable allocation on `dev` (covers allocation and multicast minimums).
@@ -21,5 +22,10 @@ ncclResult_t memFree(void* ptr);
 // Allocation of this process that contains `ptr` (null when `ptr` was not returned by memAlloc).
 bool memLookup(const void* ptr, MemAlloc* out);
 uint64_t memTotalBytes();
+// Gives the physical memory behind an allocation back to the driver while keeping its address range reserved, and
+// maps new physical memory at the same addresses later: pointers handed out earlier stay valid across the pair, the
+// contents do not survive. Only for allocations made through the virtual-memory API (ncclInvalidUsage otherwise).
+ncclResult_t memDetachPhysical(void* ptr);
+ncclResult_t memAttachPhysical(void* ptr);
 
 }  // namespace b200

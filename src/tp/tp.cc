@@ -226,6 +226,8 @@ ncclResult_t ncclTpAllocGatheredFp8(ncclTp_t tp, size_t rows, size_t cols, void*
     if (!w->symmetric) { WARN("ncclTpAllocGatheredFp8: window could not be mapped by the peers"); return ncclInternalError; }
   }
   tp->gathered[p] = w;
+  // activations belong to the caller: a suspend saves them to host memory and a resume brings them back
+  memTrack(tp->comm, p, bytes, MEM_OFFLOAD, "gathered activations (fp8)", tp->comm->nRanks > 1 ? &tp->gathered[p] : nullptr, NCCL_WIN_COLL_SYMMETRIC);
   *q = p;
   *scales = (float*)((char*)p + qBytes);
   return ncclSuccess;
@@ -297,6 +299,7 @@ ncclResult_t ncclTpCreate(ncclComm_t comm, size_t maxRows, size_t maxCols, ncclT
       NCCLCHECK(symWindowRegister(comm, tp->accum, tp->accumBytes, &tp->accumWin, NCCL_WIN_COLL_SYMMETRIC));
       if (!tp->accumWin->symmetric) { WARN("ncclTpCreate: accumulation window could not be mapped by the peers"); return ncclInternalError; }
     }
+    memTrack(comm, tp->accum, tp->accumBytes, MEM_SCRATCH, "tensor-parallel partial sums", n > 1 ? &tp->accumWin : nullptr, NCCL_WIN_COLL_SYMMETRIC);
   }
   tp->maxBlocks = maxRows / 128 + 1;
   CUDACHECK(cudaMalloc(&tp->blockFlags, tp->maxBlocks * sizeof(uint32_t)));
@@ -313,6 +316,8 @@ ncclResult_t ncclTpDestroy(ncclTp_t tp) {
     if (kv.second) symWindowDeregister(tp->comm, kv.second);
     memFree(kv.first);
   }
+  if (tp->accum) memUntrack(tp->comm, tp->accum);
+  for (auto& kv : tp->gathered) memUntrack(tp->comm, kv.first);
   if (tp->accumWin) symWindowDeregister(tp->comm, tp->accumWin);
   if (tp->accum) memFree(tp->accum);
   if (tp->blockFlags) cudaFree(tp->blockFlags);
@@ -330,6 +335,7 @@ ncclResult_t ncclTpAllocGathered(ncclTp_t tp, size_t rows, size_t cols, void** p
     if (!w->symmetric) { WARN("ncclTpAllocGathered: window could not be mapped by the peers"); return ncclInternalError; }
   }
   tp->gathered[p] = w;
+  memTrack(tp->comm, p, rows * cols * 2, MEM_OFFLOAD, "gathered activations", tp->comm->nRanks > 1 ? &tp->gathered[p] : nullptr, NCCL_WIN_COLL_SYMMETRIC);
   *ptr = p;
   return ncclSuccess;
 }
@@ -339,6 +345,7 @@ ncclResult_t ncclTpFreeGathered(ncclTp_t tp, void* ptr) {
   auto it = tp->gathered.find(ptr);
   if (it == tp->gathered.end()) return ncclInvalidArgument;
   cudaDeviceSynchronize();
+  memUntrack(tp->comm, ptr);
   if (it->second) symWindowDeregister(tp->comm, it->second);
   memFree(ptr);
   tp->gathered.erase(it);

@@ -490,7 +490,7 @@ def test_send_recv_small_and_mixed_sizes_many_rounds(emu_lib):
     ctx = emu_lib.b200EmuCreate(n, 5000)
     try:
         g = torch.Generator().manual_seed(17)
-        sizes_cycle = [1, 8, 9, 4096, 4097, 100, 65536 + 3, 7, 4095, (1 << 20) + 5, 16, 3000]
+        sizes_cycle = [1, 8, 9, 16384, 16385, 100, 65536 + 3, 7, 16383, (1 << 20) + 5, 16, 3000, 4096]
         for rep in range(40):
             nbytes = sizes_cycle[rep % len(sizes_cycle)]
             off = rep % 3   # unaligned user buffers
