@@ -1,0 +1,49 @@
+"""Programs written against the reference's Python bindings run over this library with their spelling
+(``Communicator.init``, ``allreduce(send, recv, op, stream=)``, ``group()``, ...): two host-memory ranks."""
+import numpy as np
+
+from mp_util import run_ranks
+
+BASE = {"NCCL_B200_HOST_ONLY": "1", "NCCL_SOCKET_IFNAME": "lo"}
+
+
+def _rank(rank, nranks, uid):
+    import nccl_b200.nccl4py.core as nccl
+    comm = nccl.Communicator.init(nranks, rank, nccl.UniqueId(uid))
+    assert comm.is_valid and comm.nranks == nranks and comm.rank == rank
+    x = np.full(1000, rank + 1.0, dtype=np.float32)
+    y = np.zeros_like(x)
+    comm.allreduce(x, y, nccl.SUM)
+    g = np.zeros(nranks * 10, dtype=np.float32)
+    comm.allgather(x[:10], g)
+    r = np.zeros(nranks * 4, dtype=np.float32)
+    comm.reduce(np.arange(nranks * 4, dtype=np.float32), r, nccl.MAX, root=0)
+    rs = np.zeros(5, dtype=np.float32)
+    comm.reduce_scatter(np.ones(nranks * 5, dtype=np.float32) * (rank + 1), rs, nccl.SUM)
+    b = np.full(7, float(rank), dtype=np.float32)
+    comm.broadcast(b, b, root=nranks - 1)
+    peer = (rank + 1) % nranks
+    got = np.zeros(3, dtype=np.float32)
+    with nccl.group():
+        comm.send(np.full(3, 10.0 + rank, dtype=np.float32), peer)
+        comm.recv(got, (rank - 1) % nranks)
+    sub = comm.split(color=0, key=rank)
+    s = np.ones(4, dtype=np.float32)
+    sub.allreduce(s, s, nccl.SUM)
+    sub.destroy()
+    assert comm.get_async_error() == 0
+    version = nccl.get_version()
+    comm.destroy()
+    return float(y[0]), float(g[-1]), float(r[-1]) if rank == 0 else None, float(rs[0]), float(b[0]), float(got[0]), float(s[0]), version
+
+
+def test_reference_binding_spelling_on_host_ranks():
+    n = 2
+    res = run_ranks(_rank, n, env=BASE)
+    tot = n * (n + 1) / 2
+    for r in range(n):
+        y, g, red, rs, b, got, s, version = res[r]
+        assert y == tot and g == n and rs == tot and b == n - 1 and got == 10.0 + (r - 1) % n and s == n
+        assert version >= 23000
+        if r == 0:
+            assert red == n * 4 - 1
