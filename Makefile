@@ -32,7 +32,9 @@ PLUGINS := $(patsubst plugins/%.cc,$(LIBDIR)/plugins/%.so,$(PLUGIN_SRCS))
 
 EXAMPLES := $(patsubst examples/%.cu,$(BINDIR)/examples/%,$(wildcard examples/*.cu))
 
-all: $(LIB) $(TOOLS) plugins examples
+IRLIB := $(LIBDIR)/libnccl_device_c.a
+
+all: $(LIB) $(TOOLS) plugins examples ir
 
 GIT_VERSION := $(shell git describe --always --dirty 2>/dev/null || echo unknown)
 $(BUILD)/src/core/version.o: CXXFLAGS += -DB200_GIT_VERSION='"$(GIT_VERSION)"'
@@ -58,6 +60,13 @@ $(BINDIR)/examples/%: examples/%.cu examples/common.h $(LIB) $(wildcard include/
 	@mkdir -p $(dir $@)
 	$(NVCC) -std=c++17 -O2 -lineinfo $(GENCODE) -Iinclude $< -o $@ -L$(LIBDIR) -lnccl_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../../lib' -Xcompiler -pthread
 
+# device API as C symbols carrying link-time-optimisation IR, for compilers of kernel languages (link with -dlto / nvJitLink)
+ir: $(IRLIB)
+$(IRLIB): bindings/ir/nccl_device_c.cu bindings/ir/nccl_device_c.h $(wildcard include/*.h include/nccl_device/*.h)
+	@mkdir -p $(LIBDIR) $(BUILD)/bindings/ir
+	$(NVCC) -std=c++17 -O3 -gencode arch=compute_100a,code=lto_100a -dc -Iinclude -Ibindings/ir $< -o $(BUILD)/bindings/ir/nccl_device_c.o
+	rm -f $@ && ar rcs $@ $(BUILD)/bindings/ir/nccl_device_c.o
+
 plugins: $(PLUGINS)
 $(LIBDIR)/plugins/%.so: plugins/%.cc $(wildcard include/*.h include/plugin/*.h)
 	@mkdir -p $(dir $@)
@@ -73,6 +82,8 @@ install: all
 	install -m 644 include/*.h $(DESTDIR)$(PREFIX)/include/
 	install -m 644 include/nccl_device/*.h $(DESTDIR)$(PREFIX)/include/nccl_device/
 	install -m 644 include/plugin/*.h $(DESTDIR)$(PREFIX)/include/plugin/
+	install -m 644 $(IRLIB) $(DESTDIR)$(PREFIX)/lib/
+	install -m 644 bindings/ir/nccl_device_c.h $(DESTDIR)$(PREFIX)/include/
 	cp -r $(LIBDIR)/plugins/. $(DESTDIR)$(PREFIX)/lib/nccl_b200/plugins/
 	printf 'prefix=%s\nlibdir=$${prefix}/lib\nincludedir=$${prefix}/include\n\nName: nccl_b200\nDescription: collective communication library for B200 with the NCCL host API\nVersion: 2.30.7\nLibs: -L$${libdir} -lnccl_b200\nCflags: -I$${includedir}\n' '$(PREFIX)' > $(DESTDIR)$(PREFIX)/lib/pkgconfig/nccl_b200.pc
 
