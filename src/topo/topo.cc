@@ -145,7 +145,10 @@ static int classify(const TopoSystem* s, int from, const std::vector<int>& via, 
   for (size_t i = 0; i < via.size(); ++i) {
     int lt = linkTypes[i];
     if (lt != LINK_NVL) allNvl = false;
-    if (lt == LINK_NET) net = true;
+    // the hop between a NIC and its network port says nothing about distance inside the machine: a path that starts
+    // or ends at a NET node is classed by its PCI / NVLink part; only traffic that crosses the network is PATH_NET
+    if (lt == LINK_NET && i != 0 && i + 1 != via.size()) net = true;
+    if (lt == LINK_NET) continue;
     if (lt == LINK_SYS) sys = true;
     if (i + 1 < via.size()) {
       const TopoNode& mid = s->nodes[via[i]];
@@ -156,6 +159,7 @@ static int classify(const TopoSystem* s, int from, const std::vector<int>& via, 
   }
   if (net) return PATH_NET;
   if (allNvl) return gpusBetween ? PATH_NVB : PATH_NVL;
+  if (gpusBetween) return PATH_PXN;   // NVLink to a peer GPU, then that GPU's PCI links (how a GPU reaches a NIC it is not close to)
   if (sys || cpus > 1) return PATH_SYS;
   if (cpus == 1) return PATH_PHB;
   if (pciSwitches > 1) return PATH_PXB;
@@ -299,14 +303,37 @@ ncclResult_t topoInit(ncclComm* comm) {
   if (!st->sys) { WARN("topology: %s", err.c_str()); return ncclInternalError; }
   topoComputePaths(st->sys);
   if (debugLevel() >= LOG_INFO) INFO(SUB_GRAPH, "=== System ===\n%s", topoDescribe(st->sys).c_str());
-  // channel graphs for the three patterns and the analytic model on top of them
+  // channel graphs for the three patterns and the analytic model on top of them; NCCL_GRAPH_FILE replaces the search
+  const bool inter = comm->nNodes > 1;
   st->ring.pattern = PATTERN_RING;
-  topoSearch(st->sys, &st->ring, 1, 32);
-  st->tree = st->ring;
   st->tree.pattern = PATTERN_BALANCED_TREE;
-  st->nvls = st->ring;
   st->nvls.pattern = PATTERN_NVLS;
-  st->nvls.nChannels = (st->sys->byType[TOPO_NVS].empty() || comm->compCap < 90) ? 0 : (comm->compCap >= 100 ? 32 : 16);
+  st->ring.inter = st->tree.inter = st->nvls.inter = inter;
+  std::vector<int> localRanks;
+  for (int gi : st->sys->byType[TOPO_GPU]) localRanks.push_back(st->sys->nodes[gi].rank);
+  bool loaded = false;
+  const char* gfile = getEnv("NCCL_GRAPH_FILE");
+  if (gfile && *gfile) {
+    XmlNode* gx = xmlLoadFile(gfile, &err);
+    TopoGraph* gs[3] = {&st->ring, &st->tree, &st->nvls};
+    loaded = gx != nullptr;
+    for (int i = 0; loaded && i < 3; ++i) {
+      ncclResult_t r = graphFromXml(gx, i, localRanks, gs[i], &err);
+      if (r == ncclInvalidArgument && i == 2) { st->nvls.nChannels = 0; continue; }   // a file without an NVLS graph switches it off
+      if (r != ncclSuccess) loaded = false;
+    }
+    if (!loaded) WARN("NCCL_GRAPH_FILE %s: %s; searching instead", gfile, err.c_str());
+    else INFO(SUB_GRAPH, "Loaded channel graphs from %s", gfile);
+    delete gx;
+  }
+  if (!loaded) {
+    topoSearch(st->sys, &st->ring, 1, 32);
+    // trees share the ring's channel count where the links allow it, so that both serve the same launches
+    topoSearch(st->sys, &st->tree, 1, std::max(1, st->ring.nChannels));
+    st->tree.sameChannels = st->tree.nChannels == st->ring.nChannels;
+    if (!st->sys->byType[TOPO_NVS].empty() && comm->compCap >= 90) topoSearch(st->sys, &st->nvls, 1, 32);
+    else st->nvls.nChannels = 0;
+  }
   topoTuneModel(st->sys, &st->ring, &st->tree, &st->nvls, comm->nRanks, comm->nNodes, comm->compCap, &st->model);
   const char* gdump = getEnv("NCCL_GRAPH_DUMP_FILE");
   if (gdump && *gdump && comm->rank == 0) {
@@ -315,7 +342,8 @@ ncclResult_t topoInit(ncclComm* comm) {
     f << xmlDump(gx);
     delete gx;
   }
-  INFO(SUB_GRAPH, "ring graph: %d channels at %.1f GB/s (%s); NVLS channels %d", st->ring.nChannels, st->ring.bwIntra, topoPathName(st->ring.typeIntra), st->nvls.nChannels);
+  INFO(SUB_GRAPH, "ring graph: %d channels at %.1f GB/s (%s); tree graph: %d at %.1f; NVLS heads %d at %.1f", st->ring.nChannels, st->ring.bwIntra,
+       topoPathName(st->ring.typeIntra), st->tree.nChannels, st->tree.bwIntra, st->nvls.nChannels, st->nvls.bwIntra);
   return ncclSuccess;
 }
 

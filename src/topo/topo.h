@@ -6,6 +6,7 @@
 // predict collective times (ncclGroupSimulateEnd, tuner plugins).
 // Reference parity: src/graph/{xml,topo,paths,search,connect,rings,trees,tuning}.cc.
 #pragma once
+#include <array>
 #include <map>
 #include <string>
 #include <vector>
@@ -86,16 +87,25 @@ std::string topoDescribe(const TopoSystem* sys);
 // ---------------------------------------------------------------- channel graphs (search.cc)
 enum TopoPattern { PATTERN_RING = 4, PATTERN_BALANCED_TREE = 1, PATTERN_SPLIT_TREE = 2, PATTERN_TREE = 3, PATTERN_NVLS = 5 };
 struct TopoGraph {
+  // inputs of the search
   int pattern = PATTERN_RING;
+  bool inter = false;     // the job spans nodes: channels enter and leave through NET nodes
+  int crossNic = 0;       // a ring may leave through another NIC than it entered (NCCL_CROSS_NIC overrides)
+  // results
   int nChannels = 0;
-  float bwIntra = 0, bwInter = 0;
-  int typeIntra = PATH_DIS;
-  std::vector<std::vector<int>> order;   // per channel: ranks in ring order (local GPUs of this node)
+  float bwIntra = 0, bwInter = 0, latencyInter = 0;
+  int typeIntra = PATH_DIS, typeInter = PATH_DIS;
+  int sameChannels = 1;
+  std::vector<std::vector<int>> order;      // per channel: ranks in walk order (local GPUs of this node)
+  std::vector<std::array<int, 2>> nets;     // per channel: NET device entered from / left through (-1 inside one node)
+  std::vector<int> heads;                   // NVLS: head rank of every channel
 };
-// Finds the largest set of channels (rings through all local GPUs) at the highest per-channel
-// bandwidth of the architecture's speed ladder that the links can carry, within a time budget.
+// Finds the largest set of channels of graph->pattern (see search.cc) at the highest per-channel bandwidth of the
+// architecture's speed ladder that the links can carry, within a step budget.
 ncclResult_t topoSearch(const TopoSystem* sys, TopoGraph* graph, int minChannels, int maxChannels);
+// Graph files: ids 0 ring, 1 tree, 2 NVLS in the order topoInit writes them.
 XmlNode* graphToXml(const std::vector<TopoGraph>& graphs);
+ncclResult_t graphFromXml(const XmlNode* root, int id, const std::vector<int>& ranks, TopoGraph* graph, std::string* err);
 
 // rings / trees (rings.cc)
 // Global ring over all ranks from per-node local orders: prev/next of every rank.

@@ -47,6 +47,53 @@ int b200TopoAnalyze(const char* xmlText, char* out, int outLen) {
   return 0;
 }
 
+// Searches the ring, tree and NVLS graphs of a topology (interNode: the job spans nodes, so channels attach to NICs)
+// and writes them as graph XML into out. Returns 0 on success.
+int b200TopoGraphs(const char* xmlText, int interNode, int crossNic, char* out, int outLen) {
+  std::string err;
+  XmlNode* x = xmlParse(xmlText, &err);
+  if (!x) return 1;
+  TopoSystem* s = topoFromXml(x, &err);
+  if (!s) { delete x; return 2; }
+  topoComputePaths(s);
+  TopoGraph ring, tree, nvls;
+  ring.pattern = PATTERN_RING;
+  tree.pattern = PATTERN_BALANCED_TREE;
+  nvls.pattern = PATTERN_NVLS;
+  ring.inter = tree.inter = nvls.inter = interNode != 0;
+  ring.crossNic = tree.crossNic = crossNic;
+  topoSearch(s, &ring, 1, 32);
+  topoSearch(s, &tree, 1, std::max(1, ring.nChannels));
+  topoSearch(s, &nvls, 1, 32);
+  XmlNode* gx = graphToXml({ring, tree, nvls});
+  std::string t = xmlDump(gx);
+  snprintf(out, outLen, "%s", t.c_str());
+  delete gx;
+  delete s;
+  delete x;
+  return (int)t.size() < outLen ? 0 : 3;
+}
+
+// Reads graphs 0..2 of a graph XML for ranks 0..nRanks-1 and writes them out again (the dump of what was understood).
+// Returns 0, or 10 + the id of the first graph that was refused (message in out).
+int b200TopoGraphReload(const char* graphXml, int nRanks, char* out, int outLen) {
+  std::string err;
+  XmlNode* gx = xmlParse(graphXml, &err);
+  if (!gx) { snprintf(out, outLen, "%s", err.c_str()); return 1; }
+  std::vector<int> ranks;
+  for (int r = 0; r < nRanks; ++r) ranks.push_back(r);
+  std::vector<TopoGraph> gs(3);
+  for (int i = 0; i < 3; ++i) {
+    if (graphFromXml(gx, i, ranks, &gs[i], &err) != ncclSuccess) { snprintf(out, outLen, "%s", err.c_str()); delete gx; return 10 + i; }
+  }
+  XmlNode* back = graphToXml(gs);
+  std::string t = xmlDump(back);
+  snprintf(out, outLen, "%s", t.c_str());
+  delete back;
+  delete gx;
+  return 0;
+}
+
 // Probes this machine and writes its topology XML into out (truncated to outLen).
 int b200TopoProbe(char* out, int outLen) {
   XmlNode* x = xmlFromSystem();
