@@ -12,6 +12,7 @@
 // reduce-scatter, all-to-all (n-1)/n; others 1).
 // Reference parity: plugins/profiler/inspector (inspector.cc, inspector_plugin.cc,
 // inspector_json.cc, inspector_prom.cc); metric names from its README.md:164-166.
+#include <algorithm>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -184,9 +185,9 @@ ncclResult_t pState(void* handle, ncclProfilerEventState_t st, ncclProfilerEvent
   Event* e = (Event*)handle;
   if (e && e->type == ncclProfileKernelCh && st == ncclProfilerKernelChStop && a) {
     e->devStop = a->kernelCh.pTimer;
-    if (e->parent) {
-      e->parent->devStart = e->devStart;
-      e->parent->devStop = e->devStop;
+    if (e->parent) {   // the operation spans its CTAs: earliest start, latest stop
+      e->parent->devStart = e->parent->haveDev ? std::min(e->parent->devStart, e->devStart) : e->devStart;
+      e->parent->devStop = e->parent->haveDev ? std::max(e->parent->devStop, e->devStop) : e->devStop;
       e->parent->haveDev = true;
     }
   }

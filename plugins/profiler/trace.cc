@@ -84,6 +84,9 @@ ncclResult_t pStart(void* context, void** handle, ncclProfilerEventDescr_t* d) {
   } else if (d->type == ncclProfileProxyOp) {
     e->name = d->proxyOp.isSend ? "ProxySend" : "ProxyRecv";
     snprintf(buf, sizeof(buf), "\"peer\":%d,\"steps\":%d,\"chunk\":%d", d->proxyOp.peer, d->proxyOp.nSteps, d->proxyOp.chunkSize);
+  } else if (d->type == ncclProfileKernelCh) {
+    e->name = kindName(d->type);
+    snprintf(buf, sizeof(buf), "\"channel\":%d,\"gpu_start_ns\":%llu", d->kernelCh.channelId, (unsigned long long)d->kernelCh.pTimer);
   } else {
     e->name = kindName(d->type);
   }
@@ -101,7 +104,15 @@ ncclResult_t pStop(void* handle) {
   return ncclSuccess;
 }
 
-ncclResult_t pState(void*, ncclProfilerEventState_t, ncclProfilerEventStateArgs_t*) { return ncclSuccess; }
+ncclResult_t pState(void* handle, ncclProfilerEventState_t st, ncclProfilerEventStateArgs_t* a) {
+  Event* e = (Event*)handle;
+  if (e && a && e->type == ncclProfileKernelCh && st == ncclProfilerKernelChStop) {
+    char buf[64];
+    snprintf(buf, sizeof(buf), ",\"gpu_stop_ns\":%llu", (unsigned long long)a->kernelCh.pTimer);
+    e->args += buf;
+  }
+  return ncclSuccess;
+}
 
 ncclResult_t pFinalize(void* context) {
   Ctx* c = (Ctx*)context;

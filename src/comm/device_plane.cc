@@ -252,6 +252,7 @@ static void fillSync(ncclComm* comm, SyncArgs* s) {
   s->status[comm->rank] = comm->devStatusDev;
   s->abortFlag = comm->abortFlagDev;
   s->timeoutNs = dp->timeoutNs;
+  s->stamps = dp->curStamp;
   // every rank takes the same decision: the multicast alias exists on all ranks or on none
   if (dp->resWin->host.mcPtr && dp->barrierMcMin > 0 && comm->nRanks >= dp->barrierMcMin)
     s->mcArrive = (uint32_t*)((char*)dp->resWin->host.mcPtr + kOffMcBarrier);

@@ -53,6 +53,7 @@ struct DevicePlane {
   size_t hostStageBytes = 0;
   uint64_t ceEpoch = 0;
   uint64_t launches = 0;              // kernels launched by this communicator
+  unsigned long long* curStamp = nullptr;   // device-visible time-stamp slot of the task being launched (set by the profiler glue)
   int barrierMcMin = 0;               // barriers arrive by multimem.red from this many ranks on (0 = never)
   int llMcMin = 0;                    // flagged lines are published by multimem.st from this many ranks on (0 = never)
 };

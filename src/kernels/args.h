@@ -66,7 +66,10 @@ struct SyncArgs {
   uint32_t* mcArrive;             // multicast alias of the barrier arrival counters [slot] (null: unicast barrier)
   const uint32_t* abortFlag;      // set by the host to make every wait give up
   unsigned long long timeoutNs;   // budget of one wait
+  unsigned long long* stamps;     // time stamps of this launch for profiler plugins: [kStampCtas][2] = {start, stop} of CTA i in
+                                  // nanoseconds of the GPU's global timer (null: not recorded)
 };
+constexpr int kStampCtas = 32;    // CTAs of a launch that record their start and stop (the first ones of the grid)
 
 enum RedOp : int { RED_SUM = 0, RED_PROD = 1, RED_MAX = 2, RED_MIN = 3 };
 enum ScaleMode : int { SCALE_NONE = 0, SCALE_MUL = 1, SCALE_INTDIV = 2 };

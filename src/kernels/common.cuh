@@ -94,6 +94,24 @@ __device__ __forceinline__ void pdlWait() { asm volatile("griddepcontrol.wait;" 
 __device__ __forceinline__ void pdlLaunchDependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdlEnter() { pdlWait(); pdlLaunchDependents(); }
 
+// Start and stop times of a CTA for profiler plugins, taken on the device: constructed right after pdlEnter() (so the
+// wait for the previous grid is not counted), the stop is written when the kernel body is left, on every path. A
+// task that takes several launches keeps the first start and the last stop.
+// Reference parity: work-counter time stamps of src/device/common.h:323-353 (KernelCh events of the profiler).
+struct KernelStamp {
+  unsigned long long* const& base;   // refers to the launch arguments (constant bank): nothing is kept in registers across the kernel
+  __device__ __forceinline__ bool mine() const { return base != nullptr && threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.x < kStampCtas; }
+  __device__ __forceinline__ explicit KernelStamp(unsigned long long* const& b) : base(b) {
+    if (mine()) {
+      volatile unsigned long long* p = base + 2 * blockIdx.x;
+      if (p[0] == 0) p[0] = globalTimerNs();
+    }
+  }
+  __device__ __forceinline__ ~KernelStamp() {
+    if (mine()) ((volatile unsigned long long*)base)[2 * blockIdx.x + 1] = globalTimerNs();
+  }
+};
+
 // ------------------------------------------------------------------ bounded waits
 // A wait polls until `done()` holds, the host raises the abort flag, or the time budget runs
 // out. On failure it records what it was waiting for in the rank's status words and returns

@@ -100,6 +100,7 @@ constexpr int kTilePacks = kCtaThreads * 4;  // 32 KiB per CTA tile
 __global__ void __launch_bounds__(kCtaThreads, 1) copyCollKernel(const __grid_constant__ CollArgs a) {
   const int rank = ctaRank(a.emu, a.rank);
   pdlEnter();
+  KernelStamp stamp(a.sync.stamps);
   CtaBarrier bar;
   bar.init(a.sync, rank, a.nRanks, blockIdx.x);
   bool ok = bar.sync(false, false);   // every rank's kernel has started: inputs final, outputs free
@@ -164,6 +165,7 @@ __global__ void __launch_bounds__(32, 1) copyCollBulkKernel(const __grid_constan
   uint64_t* bars = (uint64_t*)(sm + (size_t)kCollBulkStages * kCollBulkChunk);
   const int rank = ctaRank(a.emu, a.rank);
   pdlEnter();
+  KernelStamp stamp(a.sync.stamps);
   CtaBarrier bar;
   bar.init(a.sync, rank, a.nRanks, blockIdx.x);
   bool ok = bar.sync(false, false);
@@ -252,6 +254,7 @@ __device__ __forceinline__ void copyShare(char* dst, const char* src, size_t byt
 __global__ void __launch_bounds__(kCtaThreads, 1) p2pKernel(const __grid_constant__ P2pArgs a) {
   const int rank = ctaRank(a.emu, a.rank);
   pdlEnter();
+  KernelStamp stamp(a.sync.stamps);
   const int nOps = a.nOps[rank];
   const P2pOp* ops = a.ops + a.opBase[rank];
   WaitCtx w{&a.sync, a.sync.status[rank]};

@@ -113,6 +113,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) llReduceKernel(const __grid_co
   const int n = a.nRanks;
   constexpr int N = 8 / sizeof(T);
   pdlEnter();
+  KernelStamp stamp(a.sync.stamps);
   LLCtx ll;
   ll.begin(a, rank);
   WaitCtx w{&a.sync, a.sync.status[rank]};
@@ -188,6 +189,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) llReduceBatchKernel(const __gr
   __shared__ LLItem items[kMaxLLItems];
   for (int i = threadIdx.x; i < b.nItems; i += blockDim.x) items[i] = b.items[i];
   pdlEnter();
+  KernelStamp stamp(a.sync.stamps);
   LLCtx ll;
   ll.begin(a, rank);
   WaitCtx w{&a.sync, a.sync.status[rank]};
@@ -251,6 +253,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) llCopyKernel(const __grid_cons
   const int rank = ctaRank(a.emu, a.rank);
   const int n = a.nRanks;
   pdlEnter();
+  KernelStamp stamp(a.sync.stamps);
   LLCtx ll;
   ll.begin(a, rank);
   WaitCtx w{&a.sync, a.sync.status[rank]};

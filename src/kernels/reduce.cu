@@ -18,6 +18,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) reduceP2pKernel(const __grid_c
   const int rank = ctaRank(a.emu, a.rank);
   const int n = a.nRanks;
   pdlEnter();
+  KernelStamp stamp(a.sync.stamps);
   CtaBarrier bar;
   bar.init(a.sync, rank, n, blockIdx.x);
   bool ok = bar.sync(false, false);  // inputs of every rank are final (written by earlier kernels); outputs may be overwritten
@@ -144,6 +145,7 @@ template <typename T, int OP>
 __global__ void __launch_bounds__(kCtaThreads, 1) reduceNvlsKernel(const __grid_constant__ CollArgs a) {
   const int rank = a.rank;
   pdlEnter();
+  KernelStamp stamp(a.sync.stamps);
   CtaBarrier bar;
   bar.init(a.sync, rank, a.nRanks, blockIdx.x);
   bool ok = bar.sync(false, false);

@@ -84,6 +84,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) ringKernel(const __grid_consta
   const int next = (rank + 1) % n, prev = (rank + n - 1) % n;
   constexpr size_t unit = 16 / sizeof(T);
   pdlEnter();
+  KernelStamp stamp(a.sync.stamps);
   CtaBarrier bar;
   bar.init(a.sync, rank, n, slot);
   uint32_t* basePtr = a.sync.epoch[rank] + kPrivRingBase + slot;
@@ -170,6 +171,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) treeKernel(const __grid_consta
   const int slot = blockIdx.x;
   constexpr size_t unit = 16 / sizeof(T);
   pdlEnter();
+  KernelStamp stamp(a.sync.stamps);
   CtaBarrier bar;
   bar.init(a.sync, rank, n, slot);
   uint32_t* basePtr = a.sync.epoch[rank] + kPrivTreeBase + slot;

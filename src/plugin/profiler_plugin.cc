@@ -13,6 +13,8 @@
 #include <deque>
 #include <mutex>
 
+#include "../comm/device_plane.h"
+#include "../kernels/args.h"
 #include "plugin.h"
 #include "profiler.h"
 
@@ -27,13 +29,47 @@ struct PendingKernel {
   void* collHandle;
   void* groupHandle;
   uint64_t hostStartNs;
+  int stampSlot;   // slot of the device time stamps (-1: none)
 };
+
+// Device time stamps: a ring of slots in pinned host memory that the kernels write through a device mapping
+// ([kStampCtas][2] words per slot, see KernelStamp in kernels/common.cuh). A slot belongs to one task from its
+// launch until its stop event has completed and the stamps have been turned into KernelCh events.
+constexpr int kStampSlots = 256;
+constexpr int kStampWords = 2 * kStampCtas;
 
 struct ProfilerExtra {
   std::mutex lock;
   std::deque<PendingKernel> pending;
   std::vector<cudaEvent_t> pool;
+  unsigned long long* stampHost = nullptr;
+  unsigned long long* stampDev = nullptr;
+  std::vector<int> freeSlots;
+  bool stampTried = false;
 };
+
+static int takeStampSlot(ProfilerExtra* ex) {
+  std::lock_guard<std::mutex> g(ex->lock);
+  if (!ex->stampTried) {
+    ex->stampTried = true;
+    void* h = nullptr;
+    void* d = nullptr;
+    if (cudaHostAlloc(&h, sizeof(unsigned long long) * kStampSlots * kStampWords, cudaHostAllocMapped) == cudaSuccess &&
+        cudaHostGetDevicePointer(&d, h, 0) == cudaSuccess) {
+      ex->stampHost = (unsigned long long*)h;
+      ex->stampDev = (unsigned long long*)d;
+      for (int i = kStampSlots - 1; i >= 0; --i) ex->freeSlots.push_back(i);
+    } else {
+      (void)cudaGetLastError();
+      if (h) cudaFreeHost(h);
+    }
+  }
+  if (ex->freeSlots.empty()) return -1;
+  int slot = ex->freeSlots.back();
+  ex->freeSlots.pop_back();
+  memset(ex->stampHost + (size_t)slot * kStampWords, 0, sizeof(unsigned long long) * kStampWords);
+  return slot;
+}
 static std::mutex gExtraLock;
 static std::map<ncclComm*, ProfilerExtra*> gExtra;
 
@@ -84,6 +120,8 @@ void profilerUnload(ncclComm* comm) {
   ProfilerExtra* ex = extraOf(comm, false);
   if (ex) {
     for (cudaEvent_t e : ex->pool) cudaEventDestroy(e);
+    if (ex->stampHost) cudaFreeHost(ex->stampHost);
+    (void)cudaGetLastError();
     {
       std::lock_guard<std::mutex> g(gExtraLock);
       gExtra.erase(comm);
@@ -160,6 +198,7 @@ struct TaskProfile {
   void* launch = nullptr;
   cudaEvent_t start = nullptr, stop = nullptr;
   uint64_t hostStartNs = 0;
+  int stampSlot = -1;
 };
 
 static cudaEvent_t takeEvent(ProfilerExtra* ex) {
@@ -184,7 +223,11 @@ void* profilerTaskStart(ncclComm* comm, const Task& t) {
     ProfilerExtra* ex = extraOf(comm, true);
     tp->start = takeEvent(ex);
     tp->stop = takeEvent(ex);
-    if (tp->start && tp->stop) cudaEventRecord(tp->start, t.stream);
+    if (tp->start && tp->stop) {
+      cudaEventRecord(tp->start, t.stream);
+      tp->stampSlot = takeStampSlot(ex);
+      if (tp->stampSlot >= 0 && comm->devPlane) comm->devPlane->curStamp = ex->stampDev + (size_t)tp->stampSlot * kStampWords;
+    }
   }
   (void)cudaGetLastError();
   return tp;
@@ -194,6 +237,7 @@ void* profilerTaskStart(ncclComm* comm, const Task& t) {
 void profilerTaskStop(ncclComm* comm, const Task& t, void* hv, const char* algo, const char* proto, int nCtas) {
   TaskProfile* tp = (TaskProfile*)hv;
   ProfilerState* ps = comm->profiler;
+  if (comm->devPlane) comm->devPlane->curStamp = nullptr;
   if (!tp) return;
   if (!ps) { delete tp; return; }
   ncclProfilerEventDescr_t d;
@@ -237,7 +281,7 @@ void profilerTaskStop(ncclComm* comm, const Task& t, void* hv, const char* algo,
     cudaEventRecord(tp->stop, t.stream);
     ProfilerExtra* ex = extraOf(comm, true);
     std::lock_guard<std::mutex> g(ex->lock);
-    ex->pending.push_back(PendingKernel{tp->start, tp->stop, tp->coll, tp->group, tp->hostStartNs});
+    ex->pending.push_back(PendingKernel{tp->start, tp->stop, tp->coll, tp->group, tp->hostStartNs, tp->stampSlot});
   } else {
     profStop(comm, tp->coll);
     profStop(comm, tp->group);
@@ -260,25 +304,50 @@ void profilerPoll(ncclComm* comm, bool drain) {
       if (q == cudaErrorNotReady) { (void)cudaGetLastError(); return; }
       ex->pending.pop_front();
     }
-    float ms = 0;
-    if (cudaEventElapsedTime(&ms, pk.start, pk.stop) != cudaSuccess) { (void)cudaGetLastError(); ms = 0; }
-    ncclProfilerEventDescr_t d;
-    memset(&d, 0, sizeof(d));
-    d.type = ncclProfileKernelCh;
-    d.parentObj = pk.collHandle;
-    d.kernelCh.channelId = 0;
-    d.kernelCh.pTimer = pk.hostStartNs;
-    void* h = profStart(comm, &d);
-    ncclProfilerEventStateArgs_t a;
-    memset(&a, 0, sizeof(a));
-    a.kernelCh.pTimer = pk.hostStartNs + (uint64_t)(ms * 1e6);
-    profState(comm, h, ncclProfilerKernelChStop, &a);
-    profStop(comm, h);
+    // one KernelCh event per CTA that stamped its start and stop on the device (GPU global timer, nanoseconds)
+    int stamped = 0;
+    if (pk.stampSlot >= 0) {
+      const unsigned long long* st = ex->stampHost + (size_t)pk.stampSlot * kStampWords;
+      for (int c = 0; c < kStampCtas; ++c) {
+        if (st[2 * c] == 0 || st[2 * c + 1] < st[2 * c]) continue;
+        ncclProfilerEventDescr_t d;
+        memset(&d, 0, sizeof(d));
+        d.type = ncclProfileKernelCh;
+        d.parentObj = pk.collHandle;
+        d.kernelCh.channelId = (uint8_t)c;
+        d.kernelCh.pTimer = st[2 * c];
+        void* h = profStart(comm, &d);
+        ncclProfilerEventStateArgs_t a;
+        memset(&a, 0, sizeof(a));
+        a.kernelCh.pTimer = st[2 * c + 1];
+        profState(comm, h, ncclProfilerKernelChStop, &a);
+        profStop(comm, h);
+        ++stamped;
+      }
+    }
+    if (stamped == 0) {
+      // nothing stamped (copy engines, stream memory operations): one record from the bracketing events on the host clock
+      float ms = 0;
+      if (cudaEventElapsedTime(&ms, pk.start, pk.stop) != cudaSuccess) { (void)cudaGetLastError(); ms = 0; }
+      ncclProfilerEventDescr_t d;
+      memset(&d, 0, sizeof(d));
+      d.type = ncclProfileKernelCh;
+      d.parentObj = pk.collHandle;
+      d.kernelCh.channelId = 0;
+      d.kernelCh.pTimer = pk.hostStartNs;
+      void* h = profStart(comm, &d);
+      ncclProfilerEventStateArgs_t a;
+      memset(&a, 0, sizeof(a));
+      a.kernelCh.pTimer = pk.hostStartNs + (uint64_t)(ms * 1e6);
+      profState(comm, h, ncclProfilerKernelChStop, &a);
+      profStop(comm, h);
+    }
     profStop(comm, pk.collHandle);
     profStop(comm, pk.groupHandle);
     std::lock_guard<std::mutex> g(ex->lock);
     ex->pool.push_back(pk.start);
     ex->pool.push_back(pk.stop);
+    if (pk.stampSlot >= 0) ex->freeSlots.push_back(pk.stampSlot);
   }
 }
 

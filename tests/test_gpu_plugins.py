@@ -53,3 +53,29 @@ def test_tuner_and_inspector(n, tmp_path):
         assert all(r["algo"] == "RING" and r["channels"] == 4 for r in big), big
         small = [r for r in recs if r["count"] == 64]
         assert small and small[0]["algo"] != "RING"   # below the rule's size range: built-in choice
+
+
+def test_kernel_events_carry_device_time_stamps(tmp_path):
+    """Every CTA of a collective kernel stamps its start and stop with the GPU's global timer; the profiler
+    glue turns them into one KernelCh event per CTA under the collective's event."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = {"NCCL_PROFILER_PLUGIN": os.path.join(PLUG, "profiler", "trace.so"), "NCCL_PROFILE_DUMP_FILE": str(tmp_path / "trace")}
+    res = run_ranks(_rank, 2, env=env)
+    assert res[0] == (3.0, 2.0)
+    files = sorted(p for p in os.listdir(tmp_path) if p.endswith(".json"))
+    assert len(files) == 2
+    for f in files:
+        ev = json.load(open(os.path.join(tmp_path, f)))
+        colls = [e for e in ev if e["cat"] == "Coll"]
+        chans = [e for e in ev if e["cat"] == "KernelCh"]
+        assert len(colls) == 4 and len(chans) >= 4
+        ids = set()
+        for e in chans:
+            a = e["args"]
+            ids.add(a["channel"])
+            assert 0 < a["gpu_start_ns"] <= a["gpu_stop_ns"] < a["gpu_start_ns"] + 200_000_000, a
+        assert len(ids) > 1, "the 4 MiB all-reduce runs on several CTAs, each with its own record"
+        # the three large calls ran one after the other on the stream: their device windows do not overlap
+        spans = sorted((e["args"]["gpu_start_ns"], e["args"]["gpu_stop_ns"]) for e in chans if e["args"]["channel"] == 0)
+        assert all(spans[i][1] <= spans[i + 1][0] + 50_000 for i in range(len(spans) - 1)), spans
