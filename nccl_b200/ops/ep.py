@@ -5,6 +5,12 @@
         # toks [E_local, n*max_tokens, hidden] (e4m3 bytes), scales [E_local, n*max_tokens, hidden/128], counts [E_local]
     y = experts(toks, scales, counts)           # bf16 [E_local, n*max_tokens, hidden]
     out = ep.combine(y)                         # bf16 [tokens, hidden]: sum_k w[t,k] * y(expert k of t)
+
+Layouts with one copy of a token per destination rank instead of one per expert (fewer bytes when a token selects
+several experts of one rank): ``layout="rank_major"`` gives toks [n, max_tokens, hidden] (row = source rank, token
+index) and ``layout="flat"`` gives the received tokens packed as [n*max_tokens, hidden]; both also return the routing
+rows ``ep.recv_topk_idx`` (expert ids that are local to this rank, else -1) and ``ep.recv_topk_weights``. The caller
+applies its local experts and the weights and gives one pre-reduced row per received token to ``combine``.
 """
 import ctypes
 
@@ -75,9 +81,13 @@ def _hdr(s):
 
 
 class ExpertParallel:
-    def __init__(self, comm, num_experts, max_tokens, hidden, max_sms=0, timeout_ms=0, enable_mask=False):
+    LAYOUTS = {"expert_major": 1, "rank_major": 2, "flat": 3}
+
+    def __init__(self, comm, num_experts, max_tokens, hidden, max_sms=0, timeout_ms=0, enable_mask=False, layout="expert_major"):
         import torch
         self.torch = torch
+        self.layout = layout
+        self.layout_code = self.LAYOUTS[layout]
         self.comm, self.lib = comm, comm.lib
         self.E, self.n, self.H, self.max_tokens = num_experts, comm.nranks, hidden, max_tokens
         self.El = num_experts // comm.nranks
@@ -144,14 +154,15 @@ class ExpertParallel:
         idx_t = _tensor(topk_idx, INT64)
         if self.handle is None:
             h = ctypes.c_void_p()
-            _lib.check(L.ncclEpCreateHandle(ctypes.byref(h), self.group, 1, ctypes.byref(idx_t), None, None, self._stream()), "ncclEpCreateHandle", L)
+            _lib.check(L.ncclEpCreateHandle(ctypes.byref(h), self.group, self.layout_code, ctypes.byref(idx_t), None, None, self._stream()), "ncclEpCreateHandle", L)
             self.handle = h
         else:
             _lib.check(L.ncclEpUpdateHandle(self.handle, ctypes.byref(idx_t), None, self._stream()), "ncclEpUpdateHandle", L)
+        lead = {"expert_major": (self.El, self.cap), "rank_major": (self.n, self.max_tokens), "flat": (self.cap,)}[self.layout]
         if toks is None:
-            toks = torch.empty(self.El, self.cap, self.H, dtype=torch.uint8 if fp8 else torch.bfloat16, device=x.device)
+            toks = torch.empty(*lead, self.H, dtype=torch.uint8 if fp8 else torch.bfloat16, device=x.device)
         if scales is None and fp8:
-            scales = torch.empty(self.El, self.cap, self.H // 128, dtype=torch.float32, device=x.device)
+            scales = torch.empty(*lead, self.H // 128, dtype=torch.float32, device=x.device)
         if counts is None:
             counts = torch.zeros(self.El, dtype=torch.int32, device=x.device)
         xin, win = _tensor(x, BF16), _tensor(topk_weights, FP32)
@@ -165,10 +176,20 @@ class ExpertParallel:
             dout.scales = ctypes.pointer(sout)
         li = _hdr(LayoutInfo())
         li.expert_counters = ctypes.pointer(cnt_t)
+        extra = None
+        if self.layout != "expert_major":
+            K = topk_idx.shape[1]
+            self.recv_topk_idx = torch.empty(*lead, K, dtype=torch.int64, device=x.device)
+            self.recv_topk_weights = torch.empty(*lead, K, dtype=torch.float32, device=x.device)
+            self.recv_total = torch.zeros(1, dtype=torch.int32, device=x.device)
+            extra = (_tensor(self.recv_topk_idx, INT64), _tensor(self.recv_topk_weights, FP32), _tensor(self.recv_total, INT32))
+            dout.topk_idx, dout.topk_weights = ctypes.pointer(extra[0]), ctypes.pointer(extra[1])
+            if self.layout == "flat":
+                li.recv_total_counter = ctypes.pointer(extra[2])
         dcfg = _hdr(DispCfg())
         dcfg.send_only = 1 if send_only else 0
         _lib.check(L.ncclEpDispatch(self.handle, ctypes.byref(din), ctypes.byref(dout), ctypes.byref(li), ctypes.byref(dcfg), self._stream()), "ncclEpDispatch", L)
-        self._keep = (topk_idx, topk_weights, idx_t, xin, win, tout, cnt_t, sout)
+        self._keep = (topk_idx, topk_weights, idx_t, xin, win, tout, cnt_t, sout, extra)
         self.T = x.shape[0]
         return toks, scales, counts
 

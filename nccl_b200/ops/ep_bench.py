@@ -26,6 +26,8 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--baseline", action="store_true")
+    ap.add_argument("--layout", default="expert_major", choices=["expert_major", "rank_major", "flat"],
+                    help="rank_major / flat: one copy of a token per destination rank instead of one per selected expert")
     a = ap.parse_args(argv)
     from nccl_b200 import Communicator, get_unique_id
     from nccl_b200.ops.ep import ExpertParallel
@@ -42,12 +44,13 @@ def main(argv=None):
     w, idx = torch.softmax(logits, -1).topk(K, dim=-1)
     w = (w / w.sum(-1, keepdim=True)).float().contiguous()
     idx = idx.long().contiguous()
-    ep = ExpertParallel(comm, E, T, H)
+    ep = ExpertParallel(comm, E, T, H, layout=a.layout)
     El, cap = E // n, n * T
-    toks = torch.empty(El, cap, H, dtype=torch.uint8, device="cuda")
-    scales = torch.empty(El, cap, H // 128, dtype=torch.float32, device="cuda")
+    lead = {"expert_major": (El, cap), "rank_major": (n, T), "flat": (cap,)}[a.layout]
+    toks = torch.empty(*lead, H, dtype=torch.uint8, device="cuda")
+    scales = torch.empty(*lead, H // 128, dtype=torch.float32, device="cuda")
     counts = torch.zeros(El, dtype=torch.int32, device="cuda")
-    y = torch.empty(El, cap, H, dtype=torch.bfloat16, device="cuda")
+    y = torch.empty(*lead, H, dtype=torch.bfloat16, device="cuda")
     out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
 
     def timed(fn, sync_before=None):
@@ -66,12 +69,13 @@ def main(argv=None):
     disp_ms = timed(lambda: ep.dispatch(x, idx, w, fp8=True, toks=toks, scales=scales, counts=counts))
     ep.dispatch(x, idx, w, fp8=True, toks=toks, scales=scales, counts=counts)
     torch.cuda.synchronize()
-    recv_tokens = int(counts.sum().item())
+    # rows that crossed: one per (token, selected expert) or, for the per-rank layouts, one per (token, destination rank)
+    recv_tokens = int(counts.sum().item()) if a.layout == "expert_major" else int((ep.recv_topk_idx >= 0).any(-1).sum().item())
     y.zero_()
     comb_ms = timed(lambda: ep.combine(y, out=out))
     both_ms = timed(lambda: (ep.dispatch(x, idx, w, fp8=True, toks=toks, scales=scales, counts=counts), ep.combine(y, out=out)))
     recv_max = d.max(float(recv_tokens))
-    res = {"metric": "ep_dispatch_combine", "n_gpus": n, "tokens_per_rank": T, "hidden": H, "experts": E, "topk": K,
+    res = {"metric": "ep_dispatch_combine", "layout": a.layout, "n_gpus": n, "tokens_per_rank": T, "hidden": H, "experts": E, "topk": K,
            "dispatch_us": disp_ms * 1e3, "combine_us": comb_ms * 1e3, "dispatch_plus_combine_us": both_ms * 1e3,
            "recv_tokens_max": int(recv_max),
            "dispatch_GBps": recv_max * (H + H // 128 * 4) / disp_ms / 1e6, "combine_GBps": recv_max * H * 2 / comb_ms / 1e6}

@@ -77,6 +77,35 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
       for (int i = threadIdx.x; i < H / 8; i += kEpThreads) ((uint4*)epSmem)[i] = ((const uint4*)row)[i];
     }
     __syncthreads();
+    if (a.layout != EP_EXPERT_MAJOR) {
+      // one copy per destination rank: a warp per rank looks whether any of the token's experts lives there
+      const size_t slotR = slotBytes + epMetaBytes(K);
+      const size_t zoneR = (size_t)(epoch & 1) * ((size_t)n * a.maxTokens * slotR);
+      long long eK = -1;
+      float wK = 0.0f;
+      if (lane < K) {
+        eK = a.topkIdx[rank][(size_t)t * K + lane];
+        if (eK < 0 || eK >= E) eK = -1;
+        if (a.topkW[rank]) wK = a.topkW[rank][(size_t)t * K + lane];
+      }
+      for (int dst = warp; dst < n; dst += nWarps) {
+        const bool local = eK >= 0 && (int)(eK / El) == dst;
+        if (__ballot_sync(0xffffffffu, local) == 0u) continue;
+        if (mask && mask[dst]) continue;
+        int s = t;   // rank-major: the row is the token's index
+        if (a.layout == EP_FLAT) {
+          if (lane == 0) s = (int)atomicAdd(&st[kStCounters + dst], 1u);
+          s = __shfl_sync(0xffffffffu, s, 0);
+        }
+        if (s >= a.maxTokens) continue;
+        char* slot = a.recvBuf[dst] + zoneR + ((size_t)rank * a.maxTokens + s) * slotR;
+        if (lane == 0) *(int4*)slot = make_int4(t, (int)epoch, 0, 0);
+        for (size_t i = lane; i < payload / 16; i += 32) st16(slot + 16 + i * 16, ((const uint4*)epSmem)[i]);
+        if (lane < K) *(int2*)(slot + slotBytes + (size_t)lane * 8) = make_int2(local ? (int)eK : -1, __float_as_int(wK));
+      }
+      __syncthreads();
+      continue;
+    }
     for (int k = warp; k < K; k += nWarps) {
       const long long e = a.topkIdx[rank][(size_t)t * K + k];
       if (e < 0 || e >= E) continue;
@@ -102,7 +131,15 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
     }
   }
   __syncthreads();
-  if (sIsLast) {
+  if (sIsLast && a.layout != EP_EXPERT_MAJOR) {
+    __threadfence();
+    if (threadIdx.x < n) {
+      const int dst = threadIdx.x;
+      const uint32_t c = a.layout == EP_FLAT ? st[kStCounters + dst] : (uint32_t)T;   // rank-major: rows [0, T) may be in use
+      st[kStCounters + dst] = 0;
+      if (!(mask && mask[dst])) stReleaseSys64(a.recvCount[dst] + cntOff + rank, ((unsigned long long)epoch << 32) | c);
+    }
+  } else if (sIsLast) {
     __threadfence();
     for (int e = threadIdx.x; e < E; e += kEpThreads) {
       const uint32_t c = st[kStCounters + e];
@@ -118,7 +155,83 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
   const int cap = n * a.maxTokens;
   const size_t rowBytes = a.fp8 ? (size_t)H : (size_t)H * 2;
   bool ok = true;
-  for (int el = blockIdx.x; el < El && ok; el += gridDim.x) {
+  if (a.layout != EP_EXPERT_MAJOR) {
+    // every CTA waits for the n count words (they are local), then the CTAs share the rows
+    const size_t slotR = slotBytes + epMetaBytes(K);
+    const size_t zoneR = (size_t)(epoch & 1) * ((size_t)n * a.maxTokens * slotR);
+    if (threadIdx.x < n) {
+      const unsigned long long* c = a.recvCount[rank] + cntOff + threadIdx.x;
+      unsigned long long v = 0;
+      int cnt = 0;
+      if (!(mask && mask[threadIdx.x])) {
+        const bool quiet = a.enableMask && mask;
+        bool got = boundedWait(w, WAIT_TILE, threadIdx.x, epoch, [&] { v = ldRelaxedSys64((const uint64_t*)c); return (uint32_t)(v >> 32) == epoch; }, !quiet);
+        fenceSys();
+        if (got) cnt = (int)(uint32_t)v;
+        else if (quiet && !(a.sync.abortFlag && ldRelaxedSys(a.sync.abortFlag))) { mask[threadIdx.x] = 1; cnt = 0; }
+        else cnt = -1;
+      }
+      sCnt[threadIdx.x] = cnt;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int off = 0;
+      for (int s = 0; s < n; ++s) { sOff[s] = off; off += sCnt[s] > 0 ? sCnt[s] : 0; if (sCnt[s] < 0) off = -1 << 30; }
+      sOff[n] = off;
+    }
+    __syncthreads();
+    ok = sOff[n] >= 0;
+    if (ok) {
+      const bool flat = a.layout == EP_FLAT;
+      const int total = sOff[n];
+      const int rows = flat ? (a.outSlots < cap ? a.outSlots : cap) : cap;
+      if (flat && blockIdx.x == 0 && threadIdx.x == 0 && a.recvTotal[rank]) *a.recvTotal[rank] = total;
+      for (int pos = blockIdx.x * nWarps + warp; pos < rows; pos += gridDim.x * nWarps) {
+        int s, j;
+        bool valid;
+        if (flat) {
+          s = 0;
+          while (s + 1 < n && pos >= sOff[s + 1]) ++s;
+          j = pos - sOff[s];
+          valid = pos < total;
+        } else {
+          s = pos / a.maxTokens;
+          j = pos - s * a.maxTokens;
+          valid = j < sCnt[s];
+        }
+        const char* slot = a.recvBuf[rank] + zoneR + ((size_t)s * a.maxTokens + j) * slotR;
+        int4 hdr = make_int4(0, 0, 0, 0);
+        if (valid) hdr = *(const int4*)slot;
+        valid = valid && (uint32_t)hdr.y == epoch;   // rank-major: a row that was not written in this call keeps an older epoch
+        if (lane == 0) a.srcInfo[rank][pos] = valid ? make_int2(s, hdr.x) : make_int2(-1, 0);
+        if (lane < K) {
+          int2 meta = valid ? *(const int2*)(slot + slotBytes + (size_t)lane * 8) : make_int2(-1, 0);
+          if (a.outTopkIdx[rank]) a.outTopkIdx[rank][(size_t)pos * K + lane] = meta.x;
+          if (a.outTopkW[rank]) a.outTopkW[rank][(size_t)pos * K + lane] = __int_as_float(meta.y);
+          if (meta.x >= 0 && a.expertCount[rank]) atomicAdd(&a.expertCount[rank][meta.x - rank * El], 1);
+        }
+        if (!valid) continue;
+        char* dstTok = (char*)a.outTokens[rank] + (size_t)pos * rowBytes;
+        const size_t packs = rowBytes / 16;
+        size_t i = lane;
+        for (; i + 96 < packs; i += 128) {
+          uint4 v0 = ldLocal16(slot + 16 + i * 16), v1 = ldLocal16(slot + 16 + (i + 32) * 16);
+          uint4 v2 = ldLocal16(slot + 16 + (i + 64) * 16), v3 = ldLocal16(slot + 16 + (i + 96) * 16);
+          st16(dstTok + i * 16, v0);
+          st16(dstTok + (i + 32) * 16, v1);
+          st16(dstTok + (i + 64) * 16, v2);
+          st16(dstTok + (i + 96) * 16, v3);
+        }
+        for (; i < packs; i += 32) st16(dstTok + i * 16, ldLocal16(slot + 16 + i * 16));
+        if (a.fp8) {
+          const float* sc = (const float*)(slot + 16 + H);
+          float* dsc = a.outScales[rank] + (size_t)pos * (H / 128);
+          for (int q = lane; q < H / 128; q += 32) dsc[q] = sc[q];
+        }
+      }
+    }
+  }
+  for (int el = blockIdx.x; a.layout == EP_EXPERT_MAJOR && el < El && ok; el += gridDim.x) {
     if (threadIdx.x < n) {
       const unsigned long long* c = a.recvCount[rank] + cntOff + (size_t)el * n + threadIdx.x;
       unsigned long long v = 0;
@@ -202,7 +315,29 @@ __global__ void __launch_bounds__(kEpThreads, 1) epCombineKernel(const __grid_co
   const size_t combOff = (size_t)(epoch & 1) * ((size_t)a.maxTokens * K * H * 2);   // two landing zones, by epoch parity
 
   // ---------------------------------------------------------------- send expert outputs home
-  for (int el = 0; sendPhase && el < El; ++el) {
+  if (sendPhase && a.layout != EP_EXPERT_MAJOR) {
+    // one pre-reduced row per received token goes to row (token, this rank) of its source rank
+    const size_t combOffR = (size_t)(epoch & 1) * ((size_t)a.maxTokens * n * H * 2);
+    const int rows = a.layout == EP_FLAT ? (a.outSlots < cap ? a.outSlots : cap) : cap;
+    for (int pos = blockIdx.x * nWarps + warp; pos < rows; pos += gridDim.x * nWarps) {
+      const int2 info = a.srcInfo[rank][pos];
+      if (info.x < 0 || (mask && mask[info.x])) continue;
+      const char* src = (const char*)(y + (size_t)pos * H);
+      char* dst = a.combBuf[info.x] + combOffR + ((size_t)info.y * n + rank) * H * 2;
+      const int packs = H / 8;
+      int i = lane;
+      for (; i + 96 < packs; i += 128) {
+        uint4 v0 = ldLocal16(src + (size_t)i * 16), v1 = ldLocal16(src + (size_t)(i + 32) * 16);
+        uint4 v2 = ldLocal16(src + (size_t)(i + 64) * 16), v3 = ldLocal16(src + (size_t)(i + 96) * 16);
+        st16(dst + (size_t)i * 16, v0);
+        st16(dst + (size_t)(i + 32) * 16, v1);
+        st16(dst + (size_t)(i + 64) * 16, v2);
+        st16(dst + (size_t)(i + 96) * 16, v3);
+      }
+      for (; i < packs; i += 32) st16(dst + (size_t)i * 16, ldLocal16(src + (size_t)i * 16));
+    }
+  }
+  for (int el = 0; sendPhase && a.layout == EP_EXPERT_MAJOR && el < El; ++el) {
     const int total = a.expertCount[rank][el];
     for (int pos = blockIdx.x * nWarps + warp; pos < total; pos += gridDim.x * nWarps) {
       const size_t o = (size_t)el * cap + pos;
@@ -256,7 +391,39 @@ __global__ void __launch_bounds__(kEpThreads, 1) epCombineKernel(const __grid_co
   if (sOk) {
     const int T = a.numTokens[rank];
     __nv_bfloat16* out = (__nv_bfloat16*)a.outTokens[rank];
-    for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    for (int t = blockIdx.x; a.layout != EP_EXPERT_MAJOR && t < T; t += gridDim.x) {
+      // which ranks hold an expert of this token: one row each, already weighted by the caller
+      const size_t combOffR = (size_t)(epoch & 1) * ((size_t)a.maxTokens * n * H * 2);
+      unsigned hit = 0;
+      for (int k = 0; k < K; ++k) {
+        const long long e = a.topkIdx[rank][(size_t)t * K + k];
+        if (e >= 0 && e < a.numExperts && !(mask && mask[e / El])) hit |= 1u << (int)(e / El);
+      }
+      for (int c = threadIdx.x; c < H / 8; c += kEpThreads) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        uint4 v[kMaxRanks];
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) {
+          v[r] = make_uint4(0, 0, 0, 0);
+          if (r < n && ((hit >> r) & 1u)) v[r] = ldLocal16(a.combBuf[rank] + combOffR + (((size_t)t * n + r) * H + (size_t)c * 8) * 2);
+        }
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) {
+          const __nv_bfloat162* p = (const __nv_bfloat162*)&v[r];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            acc[2 * i] += __bfloat162float(p[i].x);
+            acc[2 * i + 1] += __bfloat162float(p[i].y);
+          }
+        }
+        uint4 o;
+        __nv_bfloat162* q = (__nv_bfloat162*)&o;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) q[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+        *(uint4*)(out + (size_t)t * H + (size_t)c * 8) = o;
+      }
+    }
+    for (int t = blockIdx.x; a.layout == EP_EXPERT_MAJOR && t < T; t += gridDim.x) {
       for (int c = threadIdx.x; c < H / 8; c += kEpThreads) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         // the rows of up to eight selected experts are fetched together, then accumulated in slot order

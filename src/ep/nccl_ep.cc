@@ -32,6 +32,7 @@ struct ncclEpHandle {
   ncclEpGroup* g = nullptr;
   ncclEpLayout_t layout;
   int K = 0, T = 0;
+  int outSlots = 0;                   // flat layout: rows of the last dispatch's outputs
   const int64_t* topkIdx = nullptr;
   const float* topkW = nullptr;
   int2* srcInfo = nullptr;
@@ -144,7 +145,8 @@ ncclResult_t ncclEpCreateGroup(ncclEpGroup_t* out, ncclComm_t comm, const ncclEp
   g->H = (int)cfg->max_token_bytes / 2;
   g->maxTokens = (int)cfg->max_dispatch_tokens_per_rank;
   g->slotBytes = epSlotBytes(g->H, 0);   // sized for the larger (bf16) payload
-  g->zoneBytes = (size_t)g->El * n * g->maxTokens * g->slotBytes;
+  // one zone holds either layout: per expert and source (expert-major) or per source with the routing row appended (rank-major, flat)
+  g->zoneBytes = (size_t)n * g->maxTokens * std::max((size_t)g->El * g->slotBytes, g->slotBytes + epMetaBytes(16));
   int cur = -1;
   CUDACHECK(cudaGetDevice(&cur));
   if (cur != comm->cudaDev) CUDACHECK(cudaSetDevice(comm->cudaDev));
@@ -152,6 +154,7 @@ ncclResult_t ncclEpCreateGroup(ncclEpGroup_t* out, ncclComm_t comm, const ncclEp
   NCCLCHECK(memAlloc((void**)&g->recvZone, 2 * g->zoneBytes, comm->cudaDev));
   NCCLCHECK(memAlloc((void**)&g->ctl, ctlBytes(g->El, n), comm->cudaDev));
   CUDACHECK(cudaMemset(g->ctl, 0, ctlBytes(g->El, n)));
+  CUDACHECK(cudaMemset(g->recvZone, 0, 2 * g->zoneBytes));   // rank-major rows are recognised by the epoch in their header: none is valid yet
   CUDACHECK(cudaMalloc(&g->state, (8 + g->E) * sizeof(uint32_t)));
   CUDACHECK(cudaMemset(g->state, 0, (8 + g->E) * sizeof(uint32_t)));
   CUDACHECK(cudaMalloc(&g->mask, kMaxRanks * sizeof(uint32_t)));
@@ -164,7 +167,8 @@ ncclResult_t ncclEpCreateGroup(ncclEpGroup_t* out, ncclComm_t comm, const ncclEp
     NCCLCHECK(bootstrapBarrier(comm->bootstrap));
   }
   // landing zones and flags are working memory: a suspended communicator gives them back; flags and epochs restart together
-  memTrack(comm, g->recvZone, 2 * g->zoneBytes, MEM_SCRATCH, "expert-parallel landing zones", n > 1 ? &g->recvWin : nullptr, NCCL_WIN_COLL_SYMMETRIC);
+  memTrack(comm, g->recvZone, 2 * g->zoneBytes, MEM_SCRATCH, "expert-parallel landing zones", n > 1 ? &g->recvWin : nullptr, NCCL_WIN_COLL_SYMMETRIC,
+           2 * g->zoneBytes);
   memTrack(comm, g->ctl, ctlBytes(g->El, n), MEM_SCRATCH, "expert-parallel counts and flags", n > 1 ? &g->ctlWin : nullptr, NCCL_WIN_COLL_SYMMETRIC,
            ctlBytes(g->El, n), [g] { cudaMemset(g->state, 0, (8 + g->E) * sizeof(uint32_t)); });
   memTrack(comm, g->state, (8 + g->E) * sizeof(uint32_t), MEM_PERSIST, "expert-parallel epochs");
@@ -201,11 +205,13 @@ ncclResult_t ncclEpHandleMemSize(ncclEpGroup_t g, ncclEpLayout_t, const ncclEpHa
 ncclResult_t ncclEpInitHandle(ncclEpHandle_t* out, ncclEpGroup_t g, ncclEpLayout_t layout, const ncclEpHandleConfig_t* config, int num_topk, const ncclEpTensor_t*) {
   if (!out || !g || num_topk <= 0 || num_topk > 16) return ncclInvalidArgument;
   if (config && !cfgOk(config)) return ncclInvalidArgument;
-  if (layout != NCCL_EP_LAYOUT_UNSET && layout != NCCL_EP_LAYOUT_EXPERT_MAJOR) { WARN("ncclEp: only the expert-major layout is implemented"); return ncclInvalidUsage; }
+  if (layout == NCCL_EP_LAYOUT_UNSET) layout = NCCL_EP_LAYOUT_EXPERT_MAJOR;
+  if (layout != NCCL_EP_LAYOUT_EXPERT_MAJOR && layout != NCCL_EP_LAYOUT_RANK_MAJOR && layout != NCCL_EP_LAYOUT_FLAT) return ncclInvalidArgument;
   if (g->K == 0) {
-    // first handle: the combine landing zones depend on top-k (collective, like every handle creation)
+    // first handle: the combine landing zones depend on top-k (collective, like every handle creation); a row per
+    // selected expert (expert-major) or per rank (rank-major, flat), whichever is more
     g->K = num_topk;
-    g->combZoneBytes = (size_t)g->maxTokens * num_topk * g->H * 2;
+    g->combZoneBytes = (size_t)g->maxTokens * std::max(num_topk, g->n) * g->H * 2;
     NCCLCHECK(memAlloc((void**)&g->combZone, 2 * g->combZoneBytes, g->comm->cudaDev));
     if (g->n > 1) {
       NCCLCHECK(symWindowRegister(g->comm, g->combZone, 2 * g->combZoneBytes, &g->combWin, NCCL_WIN_COLL_SYMMETRIC));
@@ -218,7 +224,7 @@ ncclResult_t ncclEpInitHandle(ncclEpHandle_t* out, ncclEpGroup_t g, ncclEpLayout
   }
   ncclEpHandle* h = new ncclEpHandle;
   h->g = g;
-  h->layout = NCCL_EP_LAYOUT_EXPERT_MAJOR;
+  h->layout = layout;
   h->K = num_topk;
   const size_t cap = (size_t)g->n * g->maxTokens;
   CUDACHECK(cudaMalloc(&h->srcInfo, (size_t)g->El * cap * sizeof(int2)));
@@ -265,15 +271,44 @@ ncclResult_t ncclEpDispatch(ncclEpHandle_t h, const ncclEpDispatchInputs_t* in, 
     WARN("ncclEpDispatch: input tokens must be bf16 [%d, %d]", h->T, g->H);
     return ncclInvalidArgument;
   }
-  if (!tensorOk(out->tokens, 3)) { WARN("ncclEpDispatch: output tokens must be [local experts, capacity, hidden]"); return ncclInvalidArgument; }
   const bool fp8 = out->scales != nullptr;
   const size_t cap = (size_t)g->n * g->maxTokens;
-  if ((int)out->tokens->sizes[0] != g->El || out->tokens->sizes[1] != cap || (int)out->tokens->sizes[2] != g->H ||
-      out->tokens->datatype != (fp8 ? ncclFloat8e4m3 : ncclBfloat16)) {
-    WARN("ncclEpDispatch: output tokens must be %s [%d, %zu, %d]", fp8 ? "fp8 e4m3" : "bf16", g->El, cap, g->H);
-    return ncclInvalidArgument;
+  const ncclDataType_t tokType = fp8 ? ncclFloat8e4m3 : ncclBfloat16;
+  size_t outRows = cap;
+  if (h->layout == NCCL_EP_LAYOUT_EXPERT_MAJOR) {
+    if (!tensorOk(out->tokens, 3) || (int)out->tokens->sizes[0] != g->El || out->tokens->sizes[1] != cap || (int)out->tokens->sizes[2] != g->H || out->tokens->datatype != tokType) {
+      WARN("ncclEpDispatch: output tokens must be %s [%d, %zu, %d] (local experts, capacity, hidden)", fp8 ? "fp8 e4m3" : "bf16", g->El, cap, g->H);
+      return ncclInvalidArgument;
+    }
+  } else if (h->layout == NCCL_EP_LAYOUT_RANK_MAJOR) {
+    if (!tensorOk(out->tokens, 3) || (int)out->tokens->sizes[0] != g->n || (int)out->tokens->sizes[1] != g->maxTokens || (int)out->tokens->sizes[2] != g->H || out->tokens->datatype != tokType) {
+      WARN("ncclEpDispatch: output tokens must be %s [%d, %d, %d] (ranks, max tokens per rank, hidden)", fp8 ? "fp8 e4m3" : "bf16", g->n, g->maxTokens, g->H);
+      return ncclInvalidArgument;
+    }
+  } else {
+    if (!tensorOk(out->tokens, 2) || out->tokens->sizes[0] == 0 || (int)out->tokens->sizes[1] != g->H || out->tokens->datatype != tokType) {
+      WARN("ncclEpDispatch: output tokens must be %s [receive slots, %d]", fp8 ? "fp8 e4m3" : "bf16", g->H);
+      return ncclInvalidArgument;
+    }
+    outRows = std::min(cap, out->tokens->sizes[0]);
   }
-  if (fp8 && (!tensorOk(out->scales, 3) || out->scales->datatype != ncclFloat32)) return ncclInvalidArgument;
+  long long* outIdx = nullptr;
+  float* outW = nullptr;
+  if (h->layout != NCCL_EP_LAYOUT_EXPERT_MAJOR) {
+    // the routing row of every received token comes with it: [rows, top-k] (rank-major: [ranks, max tokens, top-k])
+    const unsigned nd = h->layout == NCCL_EP_LAYOUT_RANK_MAJOR ? 3 : 2;
+    auto rowsOf = [&](const ncclEpTensor_t* t) { return nd == 3 ? t->sizes[0] * t->sizes[1] : t->sizes[0]; };
+    if (!tensorOk(out->topk_idx, nd) || out->topk_idx->datatype != ncclInt64 || rowsOf(out->topk_idx) < outRows || (int)out->topk_idx->sizes[nd - 1] != h->K) {
+      WARN("ncclEpDispatch: this layout needs an int64 topk_idx output with %zu rows of %d", outRows, h->K);
+      return ncclInvalidArgument;
+    }
+    outIdx = (long long*)out->topk_idx->data;
+    if (out->topk_weights) {
+      if (!tensorOk(out->topk_weights, nd) || out->topk_weights->datatype != ncclFloat32 || rowsOf(out->topk_weights) < outRows || (int)out->topk_weights->sizes[nd - 1] != h->K) return ncclInvalidArgument;
+      outW = (float*)out->topk_weights->data;
+    }
+  }
+  if (fp8 && (!out->scales || out->scales->magic != NCCL_EP_TENSOR_MAGIC || !out->scales->data || out->scales->datatype != ncclFloat32)) return ncclInvalidArgument;
   if (in->topk_weights) {
     if (!tensorOk(in->topk_weights, 2) || in->topk_weights->datatype != ncclFloat32) return ncclInvalidArgument;
     h->topkW = (const float*)in->topk_weights->data;
@@ -291,10 +326,18 @@ ncclResult_t ncclEpDispatch(ncclEpHandle_t h, const ncclEpDispatchInputs_t* in, 
   a.outScales[me] = fp8 ? (float*)out->scales->data : nullptr;
   a.expertCount[me] = h->expertCount;
   a.srcInfo[me] = h->srcInfo;
+  a.layout = h->layout == NCCL_EP_LAYOUT_RANK_MAJOR ? EP_RANK_MAJOR : h->layout == NCCL_EP_LAYOUT_FLAT ? EP_FLAT : EP_EXPERT_MAJOR;
+  a.outSlots = (int)outRows;
+  a.outTopkIdx[me] = outIdx;
+  a.outTopkW[me] = outW;
+  a.recvTotal[me] = (li && li->recv_total_counter && li->recv_total_counter->data) ? (int*)li->recv_total_counter->data : nullptr;
+  h->outSlots = (int)outRows;
   int ctas = g->cfg.max_num_sms ? (int)std::min<unsigned>(g->cfg.max_num_sms, (unsigned)g->smCount) : g->smCount;
   if (h->pending) { WARN("ncclEpDispatch: a send_only call on this handle is still waiting for ncclEpComplete"); return ncclInvalidUsage; }
   const bool sendOnly = config && config->send_only;
   if (sendOnly) a.phases = 1;
+  // the per-rank layouts count the tokens of every local expert with atomics while they unpack: start from zero
+  if (a.layout != EP_EXPERT_MAJOR && !sendOnly) CUDACHECK(cudaMemsetAsync(h->expertCount, 0, (size_t)g->El * sizeof(int), stream));
   NCCLCHECK(launchEp(epDispatchKernelFn(), &a, ctas, 1, dispatchSmem(g->H, fp8), stream, false));
   if (g->comm->devPlane) g->comm->devPlane->launches++;
   void* counters = (li && li->expert_counters && li->expert_counters->data) ? li->expert_counters->data : nullptr;
@@ -318,9 +361,21 @@ ncclResult_t ncclEpCombine(ncclEpHandle_t h, const ncclEpCombineInputs_t* in, co
   ncclEpGroup* g = h->g;
   NCCLCHECK(devPlaneCheckStatus(g->comm));
   const size_t cap = (size_t)g->n * g->maxTokens;
-  if (!tensorOk(in->tokens, 3) || in->tokens->datatype != ncclBfloat16 || (int)in->tokens->sizes[0] != g->El || in->tokens->sizes[1] != cap || (int)in->tokens->sizes[2] != g->H) {
-    WARN("ncclEpCombine: input tokens must be bf16 [%d, %zu, %d]", g->El, cap, g->H);
-    return ncclInvalidArgument;
+  if (h->layout == NCCL_EP_LAYOUT_EXPERT_MAJOR) {
+    if (!tensorOk(in->tokens, 3) || in->tokens->datatype != ncclBfloat16 || (int)in->tokens->sizes[0] != g->El || in->tokens->sizes[1] != cap || (int)in->tokens->sizes[2] != g->H) {
+      WARN("ncclEpCombine: input tokens must be bf16 [%d, %zu, %d]", g->El, cap, g->H);
+      return ncclInvalidArgument;
+    }
+  } else if (h->layout == NCCL_EP_LAYOUT_RANK_MAJOR) {
+    if (!tensorOk(in->tokens, 3) || in->tokens->datatype != ncclBfloat16 || (int)in->tokens->sizes[0] != g->n || (int)in->tokens->sizes[1] != g->maxTokens || (int)in->tokens->sizes[2] != g->H) {
+      WARN("ncclEpCombine: input tokens must be bf16 [%d, %d, %d]", g->n, g->maxTokens, g->H);
+      return ncclInvalidArgument;
+    }
+  } else {
+    if (!tensorOk(in->tokens, 2) || in->tokens->datatype != ncclBfloat16 || (int)in->tokens->sizes[0] < h->outSlots || (int)in->tokens->sizes[1] != g->H) {
+      WARN("ncclEpCombine: input tokens must be bf16 [>= %d, %d] (the rows of the dispatch output)", h->outSlots, g->H);
+      return ncclInvalidArgument;
+    }
   }
   if (!tensorOk(out->tokens, 2) || out->tokens->datatype != ncclBfloat16 || (int)out->tokens->sizes[0] != h->T || (int)out->tokens->sizes[1] != g->H) {
     WARN("ncclEpCombine: output tokens must be bf16 [%d, %d]", h->T, g->H);
@@ -328,7 +383,8 @@ ncclResult_t ncclEpCombine(ncclEpHandle_t h, const ncclEpCombineInputs_t* in, co
   }
   const float* weights = h->topkW;
   if (in->topk_weights && in->topk_weights->data) weights = (const float*)in->topk_weights->data;
-  if (!weights) { WARN("ncclEpCombine: no top-k weights were given (dispatch inputs or combine inputs)"); return ncclInvalidUsage; }
+  // the per-rank layouts return rows that the caller has already weighted
+  if (!weights && h->layout == NCCL_EP_LAYOUT_EXPERT_MAJOR) { WARN("ncclEpCombine: no top-k weights were given (dispatch inputs or combine inputs)"); return ncclInvalidUsage; }
   EpArgs a;
   fillEpArgs(g, &a);
   const int me = g->comm->rank;
@@ -340,6 +396,8 @@ ncclResult_t ncclEpCombine(ncclEpHandle_t h, const ncclEpCombineInputs_t* in, co
   a.outTokens[me] = out->tokens->data;
   a.expertCount[me] = h->expertCount;
   a.srcInfo[me] = h->srcInfo;
+  a.layout = h->layout == NCCL_EP_LAYOUT_RANK_MAJOR ? EP_RANK_MAJOR : h->layout == NCCL_EP_LAYOUT_FLAT ? EP_FLAT : EP_EXPERT_MAJOR;
+  a.outSlots = h->outSlots;
   int ctas = g->cfg.max_num_sms ? (int)std::min<unsigned>(g->cfg.max_num_sms, (unsigned)g->smCount) : g->smCount;
   if (h->pending) { WARN("ncclEpCombine: a send_only call on this handle is still waiting for ncclEpComplete"); return ncclInvalidUsage; }
   const bool sendOnly = config && config->send_only;
@@ -366,6 +424,7 @@ ncclResult_t ncclEpComplete(ncclEpHandle_t h, const ncclEpCompleteConfig_t* conf
   ncclEpGroup* g = h->g;
   NCCLCHECK(devPlaneCheckStatus(g->comm));
   const void* fn = h->pending == 1 ? epDispatchKernelFn() : epCombineKernelFn();
+  if (h->pending == 1 && h->pendingArgs.layout != EP_EXPERT_MAJOR) CUDACHECK(cudaMemsetAsync(h->expertCount, 0, (size_t)g->El * sizeof(int), stream));
   NCCLCHECK(launchEp(fn, &h->pendingArgs, h->pendingCtas, 1, h->pendingSmem, stream, false));
   if (g->comm->devPlane) g->comm->devPlane->launches++;
   if (h->pending == 1 && h->pendingCounters)
@@ -428,6 +487,10 @@ struct EpEmu {
   int* counts[kMaxRanks];
   uint32_t* mask[kMaxRanks];
   int phases = 3, enableMask = 0;
+  int layout = 0;
+  long long* outIdx[kMaxRanks];
+  float* outW[kMaxRanks];
+  const float* inW[kMaxRanks];
   unsigned absent = 0;
   unsigned long long timeoutNs = 3000000000ull;
 };
@@ -439,14 +502,15 @@ void* b200EpEmuCreate(int n, int E, int K, int H, int maxTokens) {
   e->n = n; e->E = E; e->El = E / n; e->K = K; e->H = H; e->maxTokens = maxTokens;
   e->phases = 3;
   e->timeoutNs = 3000000000ull;
-  size_t zone = (size_t)e->El * n * maxTokens * epSlotBytes(H, 0);
-  size_t comb = (size_t)maxTokens * K * H * 2;
+  size_t zone = (size_t)n * maxTokens * std::max((size_t)e->El * epSlotBytes(H, 0), epSlotBytes(H, 0) + epMetaBytes(16));
+  size_t comb = (size_t)maxTokens * std::max(K, n) * H * 2;
   for (int r = 0; r < n; ++r) {
     bool ok = cudaMalloc(&e->recv[r], 2 * zone) == cudaSuccess && cudaMalloc(&e->ctl[r], ctlBytes(e->El, n)) == cudaSuccess &&
               cudaMalloc(&e->comb[r], 2 * comb) == cudaSuccess && cudaMalloc(&e->state[r], (8 + E) * 4) == cudaSuccess &&
               cudaMalloc(&e->status[r], 16) == cudaSuccess && cudaMalloc(&e->srcInfo[r], (size_t)e->El * n * maxTokens * sizeof(int2)) == cudaSuccess &&
               cudaMalloc(&e->counts[r], e->El * sizeof(int)) == cudaSuccess && cudaMalloc(&e->mask[r], kMaxRanks * 4) == cudaSuccess;
     if (!ok) return nullptr;
+    cudaMemset(e->recv[r], 0, 2 * zone);
     cudaMemset(e->mask[r], 0, kMaxRanks * 4);
     cudaMemset(e->counts[r], 0, e->El * sizeof(int));
     cudaMemset(e->ctl[r], 0, ctlBytes(e->El, n));
@@ -479,6 +543,9 @@ static void emuArgs(EpEmu* e, EpArgs* a) {
   a->phases = e->phases;
   a->enableMask = e->enableMask;
   a->absent = e->absent;
+  a->layout = e->layout;
+  a->outSlots = e->n * e->maxTokens;
+  for (int r = 0; r < e->n; ++r) { a->outTopkIdx[r] = e->outIdx[r]; a->outTopkW[r] = e->outW[r]; a->topkW[r] = e->inW[r]; }
   a->sync.timeoutNs = e->timeoutNs;
 }
 // Settings of the following emulated calls: which halves run (1 send, 2 receive, 3 both), which ranks never show up
@@ -490,6 +557,19 @@ int b200EpEmuSet(void* ctx, int phases, unsigned absent, int enableMask, unsigne
   e->absent = absent;
   e->enableMask = enableMask;
   if (timeoutMs) e->timeoutNs = timeoutMs * 1000000ull;
+  return 0;
+}
+// Layout of the following emulated calls (0 expert-major, 1 rank-major, 2 flat) with, for the per-rank layouts, every
+// rank's outputs for the routing rows ([rows, top-k] int64 and fp32) and the weights that travel with the tokens.
+int b200EpEmuLayout(void* ctx, int layout, void** outIdx, void** outW, void** inW) {
+  EpEmu* e = (EpEmu*)ctx;
+  if (!e || layout < 0 || layout > 2) return ncclInvalidArgument;
+  e->layout = layout;
+  for (int r = 0; r < e->n; ++r) {
+    e->outIdx[r] = outIdx ? (long long*)outIdx[r] : nullptr;
+    e->outW[r] = outW ? (float*)outW[r] : nullptr;
+    e->inW[r] = inW ? (const float*)inW[r] : nullptr;
+  }
   return 0;
 }
 int b200EpEmuMask(void* ctx, int rank, unsigned int* out) {
@@ -513,6 +593,8 @@ int b200EpEmuDispatch(void* ctx, int fp8, const int* numTokens, void** x, void**
     a.outTokens[r] = outTokens[r];
     a.outScales[r] = outScales ? (float*)outScales[r] : nullptr;
   }
+  if (a.layout != EP_EXPERT_MAJOR && (a.phases & 2))
+    for (int r = 0; r < e->n; ++r) cudaMemset(e->counts[r], 0, e->El * sizeof(int));
   ncclResult_t res = launchEp(epDispatchKernelFn(), &a, ctas, e->n, dispatchSmem(e->H, fp8), 0, true);
   if (res != ncclSuccess) return res;
   if (cudaDeviceSynchronize() != cudaSuccess) return ncclUnhandledCudaError;
@@ -529,7 +611,7 @@ int b200EpEmuCombine(void* ctx, const int* numTokens, void** y, void** idx, void
     a.numTokens[r] = numTokens[r];
     a.x[r] = (const __nv_bfloat16*)y[r];
     a.topkIdx[r] = (const int64_t*)idx[r];
-    a.topkW[r] = (const float*)weights[r];
+    a.topkW[r] = weights ? (const float*)weights[r] : nullptr;
     a.outTokens[r] = out[r];
   }
   ncclResult_t res = launchEp(epCombineKernelFn(), &a, ctas, e->n, 0, 0, true);

@@ -190,3 +190,89 @@ def test_rank_that_never_joins_is_masked_out():
         assert time.time() - t0 < 0.15
     finally:
         lib.b200EpEmuDestroy(ctx)
+
+
+@pytest.mark.parametrize("layout", [1, 2])
+@pytest.mark.parametrize("n,E,K,H,T", [(2, 4, 2, 128, 7), (4, 16, 4, 256, 16), (8, 64, 8, 512, 24)])
+@pytest.mark.parametrize("fp8", [0, 1])
+def test_rank_major_and_flat_layouts(layout, n, E, K, H, T, fp8):
+    """One copy of a token per destination rank (not per expert): rank-major puts it at row (source, token), flat packs
+    the received tokens; the routing row travels with the token. The caller pre-reduces its local experts with the
+    weights and combine sums one row per rank."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    lib = _lib2()
+    lib.b200EpEmuLayout.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.POINTER(ctypes.c_void_p)] * 3
+    El, cap = E // n, n * T
+    ctx = lib.b200EpEmuCreate(n, E, K, H, T)
+    assert ctx
+    g = torch.Generator().manual_seed(77 + layout + n)
+    try:
+        for rep in range(3):
+            ntok = [T - (r % 2) for r in range(n)]
+            x = [torch.randn(ntok[r], H, generator=g).bfloat16().cuda() for r in range(n)]
+            idx = [torch.rand(ntok[r], E, generator=g).topk(K, dim=1).indices.to(torch.int64) for r in range(n)]
+            for r in range(n):
+                idx[r][0, 0] = -1          # an unused entry
+            idx = [i.cuda() for i in idx]
+            wts = [torch.rand(ntok[r], K, generator=g).cuda() for r in range(n)]
+            out_tok = [torch.zeros(cap, H, dtype=torch.uint8 if fp8 else torch.bfloat16, device="cuda") for _ in range(n)]
+            out_sc = [torch.zeros(cap, H // 128, device="cuda") for _ in range(n)]
+            out_idx = [torch.full((cap, K), -7, dtype=torch.int64, device="cuda") for _ in range(n)]
+            out_w = [torch.zeros(cap, K, device="cuda") for _ in range(n)]
+            counts = [(ctypes.c_int * El)() for _ in range(n)]
+            cptr = (ctypes.POINTER(ctypes.c_int) * n)(*[ctypes.cast(c, ctypes.POINTER(ctypes.c_int)) for c in counts])
+            assert lib.b200EpEmuLayout(ctx, layout, _ptrs(out_idx), _ptrs(out_w), _ptrs(wts)) == 0
+            assert lib.b200EpEmuDispatch(ctx, fp8, (ctypes.c_int * n)(*ntok), _ptrs(x), _ptrs(idx), _ptrs(out_tok), _ptrs(out_sc) if fp8 else None, cptr, 5) == 0
+            y = []
+            for r in range(n):
+                if fp8:
+                    tok = (out_tok[r].view(torch.float8_e4m3fn).float().view(cap, H // 128, 128) * out_sc[r].unsqueeze(-1)).view(cap, H)
+                else:
+                    tok = out_tok[r].float()
+                valid = (out_idx[r] >= 0).any(1)
+                # expected: which (source, token) pairs have an expert on rank r
+                want = []
+                for s in range(n):
+                    loc = (idx[s] >= 0) & ((idx[s] // El) == r)
+                    for t in torch.nonzero(loc.any(1)).flatten().tolist():
+                        want.append((s, t))
+                assert int(valid.sum()) == len(want), (r, int(valid.sum()), len(want))
+                for el in range(El):
+                    assert counts[r][el] == sum(int((idx[s] == r * El + el).sum()) for s in range(n))
+                if layout == 1:
+                    rows = [s * T + t for s, t in want]
+                    assert sorted(torch.nonzero(valid).flatten().tolist()) == sorted(rows)
+                    pairs = list(zip(rows, want))
+                else:
+                    # packed, grouped by source rank: rows [0, total) are in use; identify every row by its routing row + payload
+                    total = len(want)
+                    assert bool(valid[:total].all()) and not bool(valid[total:].any())
+                    pairs, pos = [], 0
+                    for s in range(n):
+                        mine = [t for ss, t in want if ss == s]
+                        block = tok[pos:pos + len(mine)]
+                        ref = torch.stack([x[s][t].float() for t in mine]) if mine else block
+                        if mine:
+                            nearest = torch.cdist(block, ref).argmin(1).tolist()
+                            assert sorted(nearest) == list(range(len(mine))), (r, s)
+                            pairs += [(pos + i, (s, mine[j])) for i, j in enumerate(nearest)]
+                        pos += len(mine)
+                tol = 0.08 if fp8 else 0.0
+                for row, (s, t) in pairs:
+                    assert torch.allclose(tok[row], x[s][t].float(), rtol=tol, atol=2 * tol), (r, s, t)
+                    loc = (idx[s][t] >= 0) & ((idx[s][t] // El) == r)
+                    assert torch.equal(out_idx[r][row], torch.where(loc, idx[s][t], torch.full_like(idx[s][t], -1)))
+                    assert torch.equal(out_w[r][row], wts[s][t])
+                # the caller's part: expert e multiplies by (e + 1); local experts pre-reduced with the weights
+                scale = (out_w[r] * (out_idx[r] + 1).clamp(min=0).float() * (out_idx[r] >= 0)).sum(1, keepdim=True)
+                y.append((tok * scale).bfloat16().contiguous())
+            outs = [torch.zeros(ntok[r], H, dtype=torch.bfloat16, device="cuda") for r in range(n)]
+            assert lib.b200EpEmuCombine(ctx, (ctypes.c_int * n)(*ntok), _ptrs(y), _ptrs(idx), None, _ptrs(outs), 5) == 0
+            for r in range(n):
+                sc = (wts[r] * (idx[r] + 1).clamp(min=0).float() * (idx[r] >= 0)).sum(1, keepdim=True)
+                ref = x[r].float() * sc
+                tol = 0.1 if fp8 else 0.03
+                assert torch.allclose(outs[r].float(), ref, rtol=tol, atol=tol * ref.abs().max().item()), (rep, r)
+    finally:
+        lib.b200EpEmuDestroy(ctx)

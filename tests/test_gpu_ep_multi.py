@@ -65,3 +65,50 @@ def test_ep_roundtrip(E, K, H, T, split):
         tol = 0.12 if rep % 2 else 0.03
         for r in range(n):
             assert res[r]["err%d" % rep] < tol, (rep, r, res[r])
+
+
+def _ep_rank_layout(rank, nranks, uid, E, K, H, T, layout):
+    import torch
+    torch.cuda.set_device(rank)
+    from nccl_b200 import Communicator
+    from nccl_b200.ops.ep import ExpertParallel
+    comm = Communicator(nranks, rank, uid)
+    ep = ExpertParallel(comm, E, T, H, layout=layout)
+    res = {}
+    for rep in range(3):
+        g = torch.Generator().manual_seed(100 * rep + rank)
+        x = torch.randn(T, H, generator=g).bfloat16().cuda()
+        idx = torch.rand(T, E, generator=g).topk(K, dim=1).indices.to(torch.int64).cuda()
+        w = torch.softmax(torch.randn(T, K, generator=g), dim=1).cuda()
+        toks, scales, counts = ep.dispatch(x, idx, w, fp8=False)
+        torch.cuda.synchronize()
+        ridx, rw = ep.recv_topk_idx, ep.recv_topk_weights
+        # local experts (expert e multiplies by e + 1), pre-reduced with the weights that came with the token
+        scale = (rw * (ridx + 1).clamp(min=0).float() * (ridx >= 0)).sum(-1, keepdim=True)
+        y = (toks.float() * scale).bfloat16().contiguous()
+        out = ep.combine(y)
+        torch.cuda.synchronize()
+        ref = x.float() * (w * (idx + 1).float()).sum(1, keepdim=True)
+        res["err%d" % rep] = float(((out.float() - ref).abs() / (ref.abs() + 1.0)).max())
+        res["count%d" % rep] = int(counts.sum())
+        res["rows%d" % rep] = int((ridx >= 0).any(-1).sum())
+        if layout == "flat":
+            assert int(ep.recv_total[0]) == res["rows%d" % rep]
+    assert comm.async_error() == 0
+    ep.destroy()
+    comm.destroy()
+    return res
+
+
+@pytest.mark.parametrize("layout", ["rank_major", "flat"])
+def test_ep_layouts_with_one_copy_per_rank(layout):
+    n = min(torch.cuda.device_count() if torch.cuda.is_available() else 0, 8)
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    E, K, H, T = 8 * n, 4, 512, 64
+    res = run_ranks(_ep_rank_layout, n, args=(E, K, H, T, layout), timeout=300)
+    for rep in range(3):
+        assert sum(res[r]["count%d" % rep] for r in range(n)) == n * T * K
+        assert sum(res[r]["rows%d" % rep] for r in range(n)) <= n * T * min(K, n)
+        for r in range(n):
+            assert res[r]["err%d" % rep] < 0.03, (rep, r, res[r])
