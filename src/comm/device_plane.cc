@@ -496,7 +496,13 @@ static ncclResult_t runReduction(ncclComm* comm, const Task& t) {
         for (int r = 0; r < n; ++r)
           NCCLCHECK(scaleCopy(comm, t.type, (const char*)t.send + ((size_t)r * t.count + rsDone) * es, dstp + (size_t)r * rsPiece * es, rsPiece, op, st));
       } else {
-        CUDACHECK(cudaMemcpy2DAsync(dstp, rsPiece * es, (const char*)t.send + rsDone * es, t.count * es, rsPiece * es, n, cudaMemcpyDeviceToDevice, st));
+        // long rows go as one plain copy each (full copy bandwidth); a pitched copy only pays off for many short rows
+        if (rsPiece * es >= ((size_t)1 << 20)) {
+          for (int r = 0; r < n; ++r)
+            CUDACHECK(cudaMemcpyAsync(dstp + (size_t)r * rsPiece * es, (const char*)t.send + ((size_t)r * t.count + rsDone) * es, rsPiece * es, cudaMemcpyDeviceToDevice, st));
+        } else {
+          CUDACHECK(cudaMemcpy2DAsync(dstp, rsPiece * es, (const char*)t.send + rsDone * es, t.count * es, rsPiece * es, n, cudaMemcpyDeviceToDevice, st));
+        }
       }
     } else if (op.premul) {
       NCCLCHECK(scaleCopy(comm, t.type, (const char*)t.send + done * es, dstp, cur, op, st));
