@@ -50,6 +50,8 @@ const char* kindName(uint64_t t) {
     case ncclProfileP2pApi: return "P2pApi";
     case ncclProfileKernelLaunch: return "KernelLaunch";
     case ncclProfileCeColl: return "CeColl";
+    case ncclProfileCeSync: return "CeSync";
+    case ncclProfileCeBatch: return "CeBatch";
     default: return "Event";
   }
 }

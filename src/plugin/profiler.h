@@ -24,6 +24,12 @@ void profilerApiStop(void* h);
 // Copies the most recent events (oldest first) into `out`; returns how many.
 int profilerRecentEvents(ApiEvent* out, int max);
 
+// Events of a copy-engine collective (plugin events CeColl / CeSync / CeBatch): the whole call, each of its two
+// stream-memory-operation barriers, and the batch of copies. `what` 0 = the call, 1 = a barrier, 2 = the copies;
+// the returned handle (null when no plugin listens) is closed with profilerCeStop.
+void* profilerCeStart(ncclComm* comm, const Task& t, int what, void* parent, int numOps, size_t totalBytes);
+void profilerCeStop(ncclComm* comm, void* h, int what);
+
 struct ProfilerApiScope {
   void* h;
   ProfilerApiScope(ncclComm* c, const Task& t) : h(profilerApiStart(c, t)) {}

@@ -147,6 +147,49 @@ void profState(ncclComm* comm, void* h, ncclProfilerEventState_t st, ncclProfile
   if (h && comm->profiler && comm->profiler->prof->recordEventState) comm->profiler->prof->recordEventState(h, st, a);
 }
 
+// ---- copy-engine collectives
+// Reference parity: CeColl / CeSync / CeBatch events of src/ce_coll.cc:133-285, :497-717.
+void* profilerCeStart(ncclComm* comm, const Task& t, int what, void* parent, int numOps, size_t totalBytes) {
+  ProfilerState* ps = comm->profiler;
+  if (!ps) return nullptr;
+  ncclProfilerEventDescr_t d;
+  memset(&d, 0, sizeof(d));
+  d.parentObj = parent;
+  if (what == 0) {
+    d.type = ncclProfileCeColl;
+    d.ceColl.seqNumber = t.func < FUNC_COUNT ? ps->seq[t.func]++ : 0;
+    d.ceColl.func = funcName(t.func);
+    d.ceColl.sendBuff = t.send;
+    d.ceColl.recvBuff = t.recv;
+    d.ceColl.count = t.count;
+    d.ceColl.root = t.root;
+    d.ceColl.datatype = typeName(t.type);
+    d.ceColl.syncStrategy = "stream memory operations";
+    d.ceColl.intraBatchSync = false;
+    d.ceColl.batchSize = (uint32_t)numOps;
+    d.ceColl.numBatches = 1;
+    d.ceColl.ceSeqNum = (uint32_t)(comm->devPlane ? comm->devPlane->ceEpoch / 2 : 0);
+    d.ceColl.stream = (void*)t.stream;
+  } else if (what == 1) {
+    d.type = ncclProfileCeSync;
+    d.ceCollSync.isComplete = numOps != 0;   // the closing barrier of the call
+    d.ceCollSync.nRanks = comm->nRanks;
+  } else {
+    d.type = ncclProfileCeBatch;
+    d.ceCollBatch.numOps = numOps;
+    d.ceCollBatch.totalBytes = totalBytes;
+    d.ceCollBatch.useIntraSync = false;
+  }
+  void* h = profStart(comm, &d);
+  if (h) profState(comm, h, what == 0 ? ncclProfilerCeCollStart : what == 1 ? ncclProfilerCeSyncStart : ncclProfilerCeBatchStart, nullptr);
+  return h;
+}
+void profilerCeStop(ncclComm* comm, void* h, int what) {
+  if (!h) return;
+  profState(comm, h, what == 0 ? ncclProfilerCeCollComplete : what == 1 ? ncclProfilerCeSyncComplete : ncclProfilerCeBatchComplete, nullptr);
+  profStop(comm, h);
+}
+
 // ---- public-call events (called through ProfilerApiScope)
 struct ApiPluginHandle {
   ncclComm* comm;

@@ -6,8 +6,11 @@
 // is being captured (a replay would present stale values); the SM kernels take over there.
 // Reference parity: src/ce_coll.cc:93-131 (availability), :133-285 (flag synchronisation),
 // :497-717 (all-gather / all-to-all / scatter / gather).
+#include <vector>
+
 #include "../comm/device_plane.h"
 #include "../core/cudawrap.h"
+#include "../plugin/profiler.h"
 
 namespace b200 {
 
@@ -68,7 +71,9 @@ ncclResult_t ceCollRun(ncclComm* comm, const Task& t, bool* handled) {
   auto peerRecv = [&](int p) { return (char*)w->host.peerPtr[p] + off; };
   // epoch values are even before / odd after, strictly increasing
   const uint32_t before = (uint32_t)(++dp->ceEpoch), after = (uint32_t)(++dp->ceEpoch);
-  NCCLCHECK(ceBarrier(comm, t.stream, before));   // every destination may be overwritten
+  // the copies of this rank: one per block that it owns the source of
+  struct Copy { const char* s; char* d; };
+  std::vector<Copy> copies;
   const char* src = (const char*)t.send;
   for (int j = 0; j < n; ++j) {
     int p = (me + j) % n;
@@ -81,9 +86,29 @@ ncclResult_t ceCollRun(ncclComm* comm, const Task& t, bool* handled) {
       case FUNC_SCATTER: if (me == t.root) { s = src + (size_t)p * B; d = peerRecv(p); } break;
       default: break;
     }
-    if (s && d && s != d) CUDACHECK(cudaMemcpyAsync(d, s, B, cudaMemcpyDeviceToDevice, t.stream));
+    if (s && d && s != d) copies.push_back(Copy{s, d});
   }
-  NCCLCHECK(ceBarrier(comm, t.stream, after));    // everything addressed to me has landed
+  // profiler events cover the issue of the operations on the host (the stream runs them later)
+  void* evColl = profilerCeStart(comm, t, 0, nullptr, (int)copies.size(), 0);
+  void* evSync = profilerCeStart(comm, t, 1, evColl, 0, 0);
+  ncclResult_t res = ceBarrier(comm, t.stream, before);   // every destination may be overwritten
+  profilerCeStop(comm, evSync, 1);
+  if (res != ncclSuccess) { profilerCeStop(comm, evColl, 0); return res; }
+  void* evBatch = profilerCeStart(comm, t, 2, evColl, (int)copies.size(), copies.size() * B);
+  for (const Copy& c : copies) {
+    if (cudaMemcpyAsync(c.d, c.s, B, cudaMemcpyDeviceToDevice, t.stream) != cudaSuccess) {
+      WARN("copy-engine collective: cudaMemcpyAsync failed: %s", cudaGetErrorString(cudaGetLastError()));
+      profilerCeStop(comm, evBatch, 2);
+      profilerCeStop(comm, evColl, 0);
+      return ncclUnhandledCudaError;
+    }
+  }
+  profilerCeStop(comm, evBatch, 2);
+  evSync = profilerCeStart(comm, t, 1, evColl, 1, 0);
+  res = ceBarrier(comm, t.stream, after);    // everything addressed to me has landed
+  profilerCeStop(comm, evSync, 1);
+  profilerCeStop(comm, evColl, 0);
+  NCCLCHECK(res);
   *handled = true;
   return ncclSuccess;
 }
