@@ -123,7 +123,29 @@ typedef struct ncclDevComm {
   int ginCounterCount;
   const uint32_t* abortFlag;           /* host-mapped: non-zero once the communicator is aborted */
   unsigned long long timeoutCycles;    /* default budget of device-side waits */
+  /* Proxy mode of the put / signal surface: operations are queued for a host thread that runs them with the copy
+   * engines (ncclGin in nccl_device/gin.h). All null / zero when puts are peer stores. */
+  struct ncclGinProxyDesc* ginProxyRing;        /* host-mapped ring of descriptors */
+  unsigned long long* ginProxyHead;             /* device word: next slot to claim */
+  const volatile unsigned long long* ginProxyTail;   /* host-mapped: descriptors the host has taken */
+  const volatile unsigned long long* ginProxyDone;   /* device word: operations completed (written in stream order) */
+  unsigned int ginProxyMask;                    /* ring size - 1 */
 } ncclDevComm_t;
+
+/* One queued operation of the proxy mode: an optional copy followed by an optional add on a remote signal word and
+ * on a local completion counter, all resolved to addresses by the issuing thread. `seq` is written last. */
+typedef struct ncclGinProxyDesc {
+  void* dst;
+  const void* src;
+  unsigned long long bytes;
+  unsigned long long* signal;
+  unsigned long long signalAdd;
+  unsigned long long* counter;
+  unsigned long long pad;
+  volatile unsigned long long seq;     /* index of this operation + 1 once the descriptor is complete */
+} ncclGinProxyDesc_t;
+
+typedef enum { NCCL_GIN_TYPE_NONE = 0, NCCL_GIN_TYPE_PROXY = 2, NCCL_GIN_TYPE_GDAKI = 3, NCCL_GIN_TYPE_GPI = 4 } ncclGinType_t;
 
 #ifdef __cplusplus
 extern "C" {

@@ -4,6 +4,10 @@
  * the load/store team the operations are peer stores, `red.add` on signal words of the target's
  * resource window and bounded polls. Peers outside the team report ncclInvalidUsage (no RDMA
  * backend is linked).
+ * Proxy mode (ncclDevCommRequirements_t::ginConnectionType > 0, ginForceEnable, or NCCL_GIN_TYPE=PROXY): put and signal
+ * do not touch the peer from the kernel; one thread queues a descriptor for a host thread, which runs the copy on the
+ * copy engines and the signal / counter updates behind it in stream order (the way a network proxy would post them),
+ * and flush() waits until everything queued so far has completed. The SMs then only pay for the descriptor.
  *   put(peer, dst, src, bytes [, signal])   copy, then optionally bump a signal on the peer
  *   signal(peer, id)                        bump signal `id` on the peer (release ordering)
  *   waitSignal(id, value) / readSignal(id)  bounded wait on / read of a local signal
@@ -74,11 +78,41 @@ struct ncclGin {
     return (unsigned long long*)((char*)comm.resource.peerPtr[comm.lsaRank] + comm.ginCounterOffset) + id;
   }
 
+  /* ---- proxy mode */
+  __device__ bool proxied() const { return comm.ginProxyRing != nullptr; }
+  /* Queues one operation (called by one thread). ncclTimeout when the ring stayed full for the whole budget. */
+  __device__ ncclResult_t proxyPost(void* dst, const void* src, unsigned long long bytes, unsigned long long* sig, unsigned long long add,
+                                    unsigned long long* counter) const {
+    const unsigned long long idx = atomicAdd(comm.ginProxyHead, 1ull);
+    const long long start = clock64();
+    unsigned spins = 0;
+    while (idx - *comm.ginProxyTail > (unsigned long long)comm.ginProxyMask) {
+      if ((++spins & 0xff) == 0 && ((unsigned long long)(clock64() - start) >= comm.timeoutCycles || ncclTestAbort(comm))) return ncclTimeout;
+    }
+    ncclGinProxyDesc* d = comm.ginProxyRing + (idx & comm.ginProxyMask);
+    d->dst = dst; d->src = src; d->bytes = bytes; d->signal = sig; d->signalAdd = add; d->counter = counter;
+    __threadfence_system();
+    d->seq = idx + 1;
+    return ncclSuccess;
+  }
+  /* Waits until every operation queued so far (by any thread of this GPU) has completed. */
+  __device__ ncclResult_t proxyDrain() const {
+    const unsigned long long want = *(volatile unsigned long long*)comm.ginProxyHead;
+    const long long start = clock64();
+    unsigned spins = 0;
+    while (*comm.ginProxyDone < want) {
+      if ((++spins & 0xff) == 0 && ((unsigned long long)(clock64() - start) >= comm.timeoutCycles || ncclTestAbort(comm))) return ncclTimeout;
+    }
+    nccl_device::fenceAcqRelSys();
+    return ncclSuccess;
+  }
+
   /* Everything this thread (and, after a group sync, its group) wrote earlier is visible to the peer
    * once it observes the signal. */
   __device__ ncclResult_t signal(ncclTeam_t team, int peer, int id, unsigned long long add = 1) {
     const int world = ncclTeamRankToWorld(comm, team, peer);
     if (world < 0 || world >= comm.lsaSize || id < 0 || id >= comm.ginSignalCount) return ncclInvalidUsage;
+    if (proxied()) { __threadfence_system(); return proxyPost(nullptr, nullptr, 0, signalWord(world, id), add, nullptr); }
     asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(signalWord(world, id)), "l"(add) : "memory");
     return ncclSuccess;
   }
@@ -90,6 +124,16 @@ struct ncclGin {
     if (world < 0 || world >= comm.lsaSize) return ncclInvalidUsage;
     const char* s = (const char*)ncclGetLocalPointer(srcWin, srcOffset);
     char* d = (char*)ncclGetLsaPointer(dstWin, dstOffset, world);
+    if (proxied()) {
+      // the source must be complete before the host thread starts the copy: the group's writes are fenced, then one thread posts
+      __threadfence_system();
+      coop.sync();
+      ncclResult_t r = ncclSuccess;
+      if (coop.thread_rank() == 0)
+        r = proxyPost(d, s, bytes, signalId >= 0 && signalId < comm.ginSignalCount ? signalWord(world, signalId) : nullptr, 1,
+                      counterId >= 0 && counterId < comm.ginCounterCount ? counterWord(counterId) : nullptr);
+      return r;
+    }
     if ((((uintptr_t)s | (uintptr_t)d) & 15) == 0) {
       for (size_t i = (size_t)coop.thread_rank() * 16; i + 16 <= bytes; i += (size_t)coop.size() * 16) *(uint4*)(d + i) = *(const uint4*)(s + i);
       for (size_t b = bytes / 16 * 16 + coop.thread_rank(); b < bytes; b += coop.size()) d[b] = s[b];
@@ -125,10 +169,19 @@ struct ncclGin {
   }
   __device__ void resetSignal(int id) { *(volatile unsigned long long*)signalWord(comm.lsaRank, id) = 0; }
   __device__ void resetCounter(int id) { *(volatile unsigned long long*)counterWord(id) = 0; }
-  __device__ void flush() { nccl_device::fenceAcqRelSys(); }
+  __device__ void flush() {
+    if (proxied()) { (void)proxyDrain(); return; }
+    nccl_device::fenceAcqRelSys();
+  }
 
   /* ---- the reference's call shapes (team first, actions as typed values, cooperative group last) */
   __device__ void applyRemote(int world, const nccl_device::GinAction& a) const {
+    if (proxied()) {
+      unsigned long long* w = a.signal >= 0 && a.signal < comm.ginSignalCount ? signalWord(world, a.signal)
+                              : a.window ? (unsigned long long*)ncclGetLsaPointer(a.window, a.offset, world) : nullptr;
+      if (w) (void)proxyPost(nullptr, nullptr, 0, w, a.add, nullptr);   // queued behind the put of the same thread: runs after it
+      return;
+    }
     if (a.signal >= 0 && a.signal < comm.ginSignalCount)
       asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(signalWord(world, a.signal)), "l"(a.add) : "memory");
     else if (a.window)
@@ -148,7 +201,9 @@ struct ncclGin {
     const int world = ncclTeamRankToWorld(comm, team, peer);
     if (world < 0 || world >= comm.lsaSize) return;
     if (coop.thread_rank() == 0) {
+      if (proxied()) (void)proxyDrain();   // a direct store must not overtake puts that are still queued
       *(volatile T*)ncclGetLsaPointer(dstWin, dstOffset, world) = value;
+      if (proxied()) __threadfence_system();
       applyRemote(world, nccl_device::ginAction(remoteAction));
     }
   }
@@ -178,7 +233,8 @@ struct ncclGin {
   __device__ uint64_t readCounter(ncclGinCounter_t id, int /*bits*/, cuda::memory_order = cuda::memory_order_acquire) const { return readCounter((int)id); }
   template <typename Coop>
   __device__ void flush(Coop coop, cuda::memory_order = cuda::memory_order_acquire) const {
-    nccl_device::fenceAcqRelSys();
+    if (proxied()) { if (coop.thread_rank() == 0) (void)proxyDrain(); }
+    else nccl_device::fenceAcqRelSys();
     coop.sync();
   }
 };

@@ -32,7 +32,8 @@ class _DevComm(ctypes.Structure):
                 ("llA2ABlockCount", ctypes.c_int), ("llA2ASlotCount", ctypes.c_int), ("barrierEpochs", ctypes.c_void_p),
                 ("llA2AEpochs", ctypes.c_void_p), ("ginSignalOffset", ctypes.c_uint32), ("ginSignalCount", ctypes.c_int),
                 ("ginCounterOffset", ctypes.c_uint32), ("ginCounterCount", ctypes.c_int), ("abortFlag", ctypes.c_void_p),
-                ("timeoutCycles", ctypes.c_ulonglong)]
+                ("timeoutCycles", ctypes.c_ulonglong), ("ginProxyRing", ctypes.c_void_p), ("ginProxyHead", ctypes.c_void_p),
+                ("ginProxyTail", ctypes.c_void_p), ("ginProxyDone", ctypes.c_void_p), ("ginProxyMask", ctypes.c_uint)]
 
 
 class _Requirements(ctypes.Structure):

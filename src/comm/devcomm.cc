@@ -4,10 +4,12 @@
 // Reference parity: src/dev_runtime.cc (ncclDevrInitOnce :221-292, ncclDevCommCreate :1063-1235,
 // ncclCommQueryProperties, ncclGetLsaDevicePointer :1316-1370).
 #include <map>
+#include <strings.h>
 
 #include "../mem/symmetric.h"
 #include "comm.h"
 #include "device_plane.h"
+#include "../contrib/gin_proxy.h"
 #include "nccl_device/core.h"
 
 namespace b200 {
@@ -19,6 +21,7 @@ struct DevCommState {
   size_t bytes = 0;
   ncclWindow_t win = nullptr;
   uint32_t* priv = nullptr;
+  GinProxy* proxy = nullptr;
 };
 static std::mutex gDevLock;
 static std::map<std::pair<ncclComm*, const uint32_t*>, DevCommState> gDevComms;
@@ -41,8 +44,9 @@ ncclResult_t ncclCommQueryProperties(ncclComm_t comm, ncclCommProperties_t* prop
   const bool lsa = !comm->hostOnly && (comm->nRanks == 1 || (comm->lsaAll && comm->sym && comm->nRanks <= kMaxRanks));
   props->deviceApiSupport = lsa ? 1 : 0;
   props->multimemSupport = lsa && comm->sym && comm->sym->mcUsable ? 1 : 0;
-  props->ginType = 0;          // no GPU-initiated network backend
-  props->railedGinType = 0;
+  // the put / signal surface can be served by a host proxy thread (inside the load/store domain); no device-driven NIC backend
+  props->ginType = lsa ? NCCL_GIN_TYPE_PROXY : NCCL_GIN_TYPE_NONE;
+  props->railedGinType = NCCL_GIN_TYPE_NONE;
   props->nLsaTeams = lsa ? 1 : comm->nNodes;
   props->hostRmaSupport = 1;   // ncclPutSignal / ncclSignal / ncclWaitSignal
   return ncclSuccess;
@@ -58,9 +62,16 @@ ncclResult_t ncclDevCommCreate(ncclComm_t comm, const ncclDevCommRequirements_t*
   ncclCommProperties_t props = NCCL_COMM_PROPERTIES_INITIALIZER;
   NCCLCHECK(ncclCommQueryProperties(comm, &props));
   if (!props.deviceApiSupport) { WARN("ncclDevCommCreate : the ranks of this communicator do not share one load/store domain"); return ncclInvalidUsage; }
-  if (reqs->railGinBarrierCount || reqs->worldGinBarrierCount || reqs->ginConnectionType > 0) {
-    WARN("ncclDevCommCreate : network (rail / world) resources were requested but this build serves one NVLink domain without a GPU-initiated network backend");
+  if (reqs->railGinBarrierCount || reqs->worldGinBarrierCount) {
+    WARN("ncclDevCommCreate : rail / world barriers were requested but this build serves one NVLink domain (use the load/store barriers)");
     return ncclInvalidUsage;
+  }
+  // put / signal through the host proxy thread instead of peer stores: asked for by the requirements or by NCCL_GIN_TYPE
+  bool wantProxy = reqs->ginConnectionType > 0 || reqs->ginForceEnable != 0;
+  if (const char* e = getEnv("NCCL_GIN_TYPE")) {
+    if (!strcasecmp(e, "PROXY") || !strcmp(e, "2")) wantProxy = true;
+    else if (!strcasecmp(e, "NONE") || !strcmp(e, "0")) wantProxy = false;
+    else if (*e) { WARN("NCCL_GIN_TYPE=%s: only NONE and PROXY are available (no device-driven NIC backend)", e); return ncclInvalidUsage; }
   }
   if (reqs->lsaMultimem && !props.multimemSupport) { WARN("ncclDevCommCreate : multimem requested but NVLink multicast is not available"); return ncclInvalidUsage; }
   int cur = -1;
@@ -139,6 +150,11 @@ ncclResult_t ncclDevCommCreate(ncclComm_t comm, const ncclDevCommRequirements_t*
   int khz = 0;
   cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, comm->cudaDev);
   out->timeoutCycles = (unsigned long long)paramDevCommTimeoutMs() * (unsigned long long)std::max(khz, 1000000);
+  if (wantProxy) {
+    res = ginProxyCreate(comm->cudaDev, reqs->ginQueueDepth > 0 ? reqs->ginQueueDepth : 1024, &st.proxy, out);
+    if (res != ncclSuccess) { cudaFree(st.priv); ncclCommWindowDeregister(comm, st.win); ncclMemFree(st.buf); return res; }
+    INFO(SUB_INIT, "device communicator: put / signal run through the host proxy thread (%u descriptors)", out->ginProxyMask + 1);
+  }
   {
     std::lock_guard<std::mutex> g(gDevLock);
     gDevComms[{comm, st.priv}] = st;
@@ -159,6 +175,7 @@ ncclResult_t ncclDevCommDestroy(ncclComm_t comm, const ncclDevComm_t* devComm) {
     gDevComms.erase(it);
   }
   cudaDeviceSynchronize();
+  ginProxyDestroy(st.proxy);
   ncclResult_t r = ncclCommWindowDeregister(comm, st.win);
   cudaFree(st.priv);
   ncclMemFree(st.buf);

@@ -40,6 +40,7 @@ const CuApi* cuApi() {
     L(cuStreamWriteValue32); L(cuStreamWaitValue32); L(cuPointerGetAttribute);
 #undef L
     // multicast entry points are optional (older drivers)
+    load(gApi.cuStreamWriteValue64, "cuStreamWriteValue64");
     load(gApi.cuMulticastCreate, "cuMulticastCreate");
     load(gApi.cuMulticastAddDevice, "cuMulticastAddDevice");
     load(gApi.cuMulticastBindMem, "cuMulticastBindMem");

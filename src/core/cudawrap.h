@@ -32,6 +32,7 @@ struct CuApi {
   CUresult (*cuMulticastGetGranularity)(size_t*, const CUmulticastObjectProp*, CUmulticastGranularity_flags);
   CUresult (*cuStreamWriteValue32)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
   CUresult (*cuStreamWaitValue32)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+  CUresult (*cuStreamWriteValue64)(CUstream, CUdeviceptr, cuuint64_t, unsigned int);   // optional
   CUresult (*cuPointerGetAttribute)(void*, CUpointer_attribute, CUdeviceptr);
 };
 

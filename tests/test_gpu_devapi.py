@@ -117,3 +117,39 @@ def test_device_api_multi(n):
     if _ngpus() < n:
         pytest.skip(f"needs {n} GPUs")
     _check(run_ranks(_rank, n), n)
+
+
+def _rank_gin_proxy(rank, nranks, uid):
+    import torch
+    torch.cuda.set_device(rank)
+    from nccl_b200 import Communicator
+    from nccl_b200.ops.devapi import DeviceComm, query_properties
+    comm = Communicator(nranks, rank, uid)
+    assert query_properties(comm)["ginType"] == 2   # served by a host proxy thread
+    dc = DeviceComm(comm, barriers=4, gin_signals=2, gin_counters=1)
+    both = dc.symmetric(2 * 4096, torch.float32)
+    snd, rcv = both[:4096], both[4096:]
+    seen = []
+    for it in range(5):
+        snd.fill_(100.0 * it + rank)
+        torch.cuda.synchronize()
+        comm.all_reduce(torch.zeros(8, device="cuda"))
+        torch.cuda.synchronize()
+        dc.gin_ring(snd, rcv)
+        torch.cuda.synchronize()
+        assert dc.status() == 0
+        seen.append((float(rcv[0]), float(rcv[-1])))
+    dc.destroy()
+    comm.destroy()
+    return seen
+
+
+@pytest.mark.parametrize("n", [1, 2])
+def test_put_and_signal_through_the_host_proxy(n):
+    """NCCL_GIN_TYPE=PROXY: the kernel only queues descriptors; a host thread runs the copies on the copy engines
+    and the signal / counter updates behind them. Same ring exchange as with peer stores, same result."""
+    if _ngpus() < n:
+        pytest.skip(f"needs {n} GPUs")
+    res = run_ranks(_rank_gin_proxy, n, env={"NCCL_GIN_TYPE": "PROXY"})
+    for r in range(n):
+        assert res[r] == [(100.0 * it + (r - 1) % n,) * 2 for it in range(5)], (r, res[r])
