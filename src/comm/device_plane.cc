@@ -3,6 +3,8 @@
 // buffer is not inside a registered window and has to be staged through the resource window).
 // Reference parity: src/enqueue.cc:1989-2180 (algorithm choice), :2479-2583 (reduction operator
 // lowering), src/sym_kernels.cc:599-641 (kernel pick), src/scheduler/symmetric_sched.cc.
+#include <mutex>
+
 #include "device_plane.h"
 #include "../plugin/plugin.h"
 
@@ -27,6 +29,7 @@ B200_PARAM(CopyUnroll, "B200_COPY_UNROLL", 4, "16-byte loads in flight per threa
 B200_PARAM(CopyCtasPerSm, "B200_COPY_CTAS_PER_SM", 16, "Grid size of the local copy kernel in CTAs per SM")
 B200_PARAM(LLMulticast, "B200_LL_MC_MIN_RANKS", -1, "Flagged-line all-reduce / all-gather publish each line with one multimem.st instead of one store per peer from this many ranks on (0 = never, -1 = from the selection table)")
 B200_PARAM(CopyKernel, "B200_COPY_KERNEL", 0, "One-rank copy path: 0 = vector loads and stores, 1 = bulk-copy engines through shared memory (messages of 1 MiB and more)")
+B200_PARAM(PreloadKernels, "B200_PRELOAD_KERNELS", 1, "Load every collective kernel when the first communicator of a device is created (with lazy module loading the first launch of a kernel can otherwise wait for kernels that are running, which may in turn be waiting for that launch on another rank)")
 B200_PARAM(StagePipeline, "B200_STAGE_PIPELINE", 1, "Reductions on unregistered buffers overlap the copies through the staging area with the kernels (two halves, side stream)")
 B200_PARAM(StagePipelineMin, "B200_STAGE_PIPELINE_MIN", 134217728, "Smallest message in bytes that is pipelined through the staging area")
 B200_PARAM(P2pDirect, "B200_P2P_DIRECT", 1, "Large sends write straight into a receive buffer that lies in a registered window (rendezvous) instead of going through the mailbox")
@@ -47,7 +50,7 @@ void tuningDefaults(TuningTable* t) {
   t->nvlsCtas = 32;
   t->p2pCtas = 64;
   t->copyCtas = 32;
-  t->sendrecvCtas = 32;
+  t->sendrecvCtas = 16;   // one CTA per mailbox slot of a pair: 32 measured half the bandwidth of 16 on messages beyond the mailbox size
   t->bytesPerCta = 128 << 10;
 }
 
@@ -104,6 +107,32 @@ ncclResult_t tuningLoadFile(TuningTable* t, const char* path) {
 }
 
 // ------------------------------------------------------------------------------------ set-up
+// Queries the attributes of every kernel the data plane can launch, which loads it. Once per device and process.
+// Reference parity: the loop over all kernels in ncclInitKernelsForDevice (src/enqueue.cc:60-125).
+static void preloadKernels(int dev) {
+  static std::mutex lock;
+  static bool done[64] = {};
+  std::lock_guard<std::mutex> g(lock);
+  if (dev < 0 || dev >= 64 || done[dev] || !paramPreloadKernels()) return;
+  done[dev] = true;
+  cudaFuncAttributes attr;
+  auto touch = [&](const void* fn) { if (fn && cudaFuncGetAttributes(&attr, fn) != cudaSuccess) (void)cudaGetLastError(); };
+  for (const void* fn : {p2pKernelFn(), copyKernelFn(), copyBulkKernelFn(), llCopyKernelFn(), localCopyKernelFn(4), localCopyKernelFn(8), localBulkCopyKernelFn(),
+                         signalKernelFn(), waitSignalKernelFn()})
+    touch(fn);
+  for (int t = 0; t < ncclNumTypes; ++t) {
+    touch(scaleKernelFn((ncclDataType_t)t));
+    for (int op = RED_SUM; op <= RED_MIN; ++op) {
+      touch(reduceKernelFn(KERNEL_REDUCE_P2P, (ncclDataType_t)t, op));
+      touch(reduceKernelFn(KERNEL_REDUCE_NVLS, (ncclDataType_t)t, op));
+      touch(llReduceKernelFn((ncclDataType_t)t, op));
+      touch(llReduceBatchKernelFn((ncclDataType_t)t, op));
+      touch(ringKernelFn((ncclDataType_t)t, op));
+      touch(treeKernelFn((ncclDataType_t)t, op));
+    }
+  }
+}
+
 ncclResult_t devPlaneCreate(ncclComm* comm) {
   DevicePlane* dp = new DevicePlane;
   comm->devPlane = dp;
@@ -123,6 +152,7 @@ ncclResult_t devPlaneCreate(ncclComm* comm) {
   // function attributes are per device: set with this communicator's device current
   CUDACHECK(cudaFuncSetAttribute(localBulkCopyKernelFn(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)localBulkCopySmemBytes()));
   CUDACHECK(cudaFuncSetAttribute(copyBulkKernelFn(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)copyBulkSmemBytes()));
+  preloadKernels(comm->cudaDev);
   const size_t privWords = kPrivWords + 2 * kMaxRanks * kSignalsPerPeer;
   CUDACHECK(cudaMalloc(&dp->priv, privWords * sizeof(uint32_t)));
   CUDACHECK(cudaMemset(dp->priv, 0, privWords * sizeof(uint32_t)));

@@ -82,6 +82,14 @@ ncclResult_t ginProxyCreate(int dev, int depth, GinProxy** out, ncclDevComm_t* d
   ok = ok && cudaMalloc((void**)&p->words, 64) == cudaSuccess && cudaMemset(p->words, 0, 64) == cudaSuccess;
   int lo = 0, hi = 0;
   ok = ok && cudaDeviceGetStreamPriorityRange(&lo, &hi) == cudaSuccess && cudaStreamCreateWithPriority(&p->stream, cudaStreamNonBlocking, hi) == cudaSuccess;
+  // Everything the thread will launch later is launched once now: with lazy module loading the first launch of a
+  // kernel may have to wait for running kernels to finish, and the kernels running then are the ones that wait for us.
+  if (ok) {
+    ginProxyAddKernel<<<1, 1, 0, p->stream>>>(p->words + 2, 1ull);
+    ok = cudaGetLastError() == cudaSuccess && cudaMemcpyAsync(p->words + 4, p->words + 2, 8, cudaMemcpyDeviceToDevice, p->stream) == cudaSuccess;
+    const CuApi* cu = cuApi();
+    if (ok && cu && cu->cuStreamWriteValue64) ok = cu->cuStreamWriteValue64((CUstream)p->stream, (CUdeviceptr)(p->words + 3), 1, CU_STREAM_WRITE_VALUE_DEFAULT) == CUDA_SUCCESS;
+  }
   ok = ok && cudaDeviceSynchronize() == cudaSuccess;
   if (!ok) {
     (void)cudaGetLastError();
