@@ -16,6 +16,7 @@ import argparse
 import ctypes
 import json
 import math
+import time
 import sys
 
 from .. import _lib
@@ -47,6 +48,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--dtype", default="bf16", choices=("bf16", "fp32"))
     ap.add_argument("--slack", type=float, default=0.03, help="prefer the smallest CTA count within this fraction of the fastest")
+    ap.add_argument("--budget", type=float, default=0, help="seconds after which no further size is started (0 = no limit); the table is made from what was measured")
     ap.add_argument("--toggles", default="auto", choices=("auto", "off"), help="auto: also measure the multimem barrier / flagged-line switches when multicast is available")
     a = ap.parse_args(argv)
     d = perf.Dist()
@@ -81,11 +83,19 @@ def main(argv=None):
         finally:
             lib.b200ForceAlgo(ALGO_AUTO, -1)
 
+    t_start = time.time()
+    stopped = False
     for coll in a.colls.split(","):
+        if stopped:
+            break
         res = {}
         div = n if coll in ("all_gather", "reduce_scatter", "all_to_all") else 1
         reduces = coll in ("all_reduce", "reduce_scatter")
         for nb0 in sizes:
+            # every rank takes the same decision: the slowest clock counts
+            if a.budget and d.max(time.time() - t_start) > a.budget:
+                stopped = True
+                break
             unit = 2 * div
             nb = max(unit, nb0 // unit * unit)
             block = nb // div   # bytes per rank block
@@ -134,6 +144,9 @@ def main(argv=None):
                 print("%s %d: best %s %.2f us busbw %.1f | %s" % (coll, nb, best, row[best], nb / row[best] / 1e3 * factor,
                                                                    " ".join("%s=%.1f" % kv for kv in sorted(row.items(), key=lambda kv: kv[1])[:6])), flush=True)
         out["results"][coll] = res
+        if d.rank == 0 and a.out:   # kept up to date: a run that is cut short still leaves what it measured
+            with open(a.out, "w") as f:
+                json.dump(out, f)
     h.close()
     if d.rank == 0:
         use_mc, use_mb = decide_toggles(out["results"])
