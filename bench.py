@@ -9,8 +9,11 @@ N > 1 is launched with one process per GPU (torchrun); rank 0 prints one JSON li
 
   value       nccl-tests bus bandwidth, GB/s: bytes/time * 2(n-1)/n. With one GPU that factor is
               zero, so the n=1 line reports the algorithm bandwidth of the one-rank path instead.
-  e2e         the same step through nccl_b200.Communicator.all_reduce including, every step, the
-              host->device copy of the input from pinned memory and the device->host copy of the result.
+  e2e         the same step from and to pinned host memory: every step copies the 1 GiB input host->device,
+              all-reduces it and copies the result device->host. Our arm makes the library's call for that
+              (Communicator.all_reduce_from_host = ncclAllReduceFromHost: the three stages overlap chunk by
+              chunk); the reference arm issues the three operations one after the other on one stream, which
+              is what its API offers.
   sweep       time and bus bandwidth of all-reduce / all-gather / reduce-scatter / all-to-all /
               broadcast / send-recv at a few sizes, bf16 and fp32 (20 warm-up + 100 timed calls per
               point up to 64 MiB, fewer above; the faster of two timed passes).
@@ -171,10 +174,11 @@ def main():
             api = Communicator(n, d.rank, None, lib=lib, _handle=h.comm)
             send_bf, recv_bf = h.send_t.view(torch.bfloat16), h.recv_t.view(torch.bfloat16)
 
+            hin_bf, hout_bf = host_in.view(torch.bfloat16), host_out.view(torch.bfloat16)
+
             def step():
-                h.send_t.copy_(host_in, non_blocking=True)
-                api.all_reduce(send_bf, recv_bf, op="sum", stream=h.stream)
-                host_out.copy_(h.recv_t, non_blocking=True)
+                # the library's call for host-resident data: copy in, all-reduce and copy out, overlapped chunk by chunk
+                api.all_reduce_from_host(hin_bf, hout_bf, send_bf, recv_bf, op="sum", stream=h.stream)
         else:
             def step():
                 h.send_t.copy_(host_in, non_blocking=True)

@@ -207,6 +207,23 @@ class Communicator:
         _lib.check(self.lib.ncclAllReduce(sp, rp, n, dt, self._op(op), self.handle, _stream_of(send, stream)), "ncclAllReduce", self.lib)
         return recv
 
+    def all_reduce_from_host(self, host_send, host_recv, dev_send, dev_recv=None, op="sum", stream=None, chunk_bytes=0):
+        """All-reduce of pinned host tensors through device staging buffers, chunked so that the copy in, the
+        collective and the copy out of neighbouring chunks overlap (ncclAllReduceFromHost). Work queued on the
+        stream afterwards, and an event recorded on it, comes after the last byte has reached ``host_recv``."""
+        dev_recv = dev_send if dev_recv is None else dev_recv
+        if not (host_send.is_pinned() and host_recv.is_pinned()):
+            raise ValueError("host tensors must be pinned")
+        _, n, dt, _ = describe(dev_send)
+        if host_send.numel() * host_send.element_size() != dev_send.numel() * dev_send.element_size():
+            raise ValueError("host and device buffers differ in size")
+        fn = self.lib.ncclAllReduceFromHost
+        fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int,
+                       ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
+        _lib.check(fn(host_send.data_ptr(), host_recv.data_ptr(), dev_send.data_ptr(), dev_recv.data_ptr(), n, dt, self._op(op), self.handle,
+                      _stream_of(dev_send, stream), chunk_bytes), "ncclAllReduceFromHost", self.lib)
+        return host_recv
+
     def reduce(self, send, recv, root, op="sum", stream=None):
         sp, n, dt, _ = describe(send)
         rp = describe(recv)[0]

@@ -28,7 +28,7 @@ enum Func : int {
 };
 const char* funcName(int f);
 
-// Algorithms of the data plane; chosen per call by the selector (sched/selector.cc).
+// Algorithms of the data plane; chosen per call from the measured selection table (sched/tuning.cc) in comm/device_plane.cc.
 enum Algo : int {
   ALGO_AUTO = -1,
   ALGO_ONERANK = 0,

@@ -418,7 +418,7 @@ static int forcedAlgo() {
   return ALGO_AUTO;
 }
 
-ncclResult_t ringTreeRun(ncclComm* comm, const Task& t, int algo);   // sched/ring_tree.cc
+ncclResult_t ringTreeRun(ncclComm* comm, const Task& t, int algo);   // ring / tree schedules over the staging area, further down in this file
 ncclResult_t ceCollRun(ncclComm* comm, const Task& t, bool* handled); // sched/ce_coll.cc
 
 static ncclResult_t runReduction(ncclComm* comm, const Task& t) {
