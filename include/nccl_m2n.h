@@ -6,10 +6,11 @@
  * axis sharding one tensor dimension and the other replicating; tensors of 1 to 3 dimensions,
  * row-major local tiles.
  *
- * The plan is computed identically on every rank from the two descriptors; data moves as grouped
- * ncclSend / ncclRecv of contiguous runs (replicas of a source slice are dealt round-robin to the
- * destination ranks that need it). `window` may be NULL: it is accepted for source compatibility
- * and not needed by this transport.
+ * The plan is computed identically on every rank from the two descriptors (replicas of a source slice
+ * are dealt round-robin to the destination ranks that need it). With `window` = a registered window
+ * that contains the source tile of every source rank (all ranks pass it, or none), every destination
+ * rank pulls its contiguous runs out of the sources' tiles with peer loads in one kernel. With
+ * `window` = NULL, or on ranks that cannot map each other, the runs move as grouped ncclSend / ncclRecv.
  */
 #ifndef NCCL_M2N_H_
 #define NCCL_M2N_H_

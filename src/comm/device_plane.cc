@@ -214,6 +214,7 @@ void devPlaneDestroy(ncclComm* comm) {
   if (comm->sym) symDestroy(comm);   // releases every window, the resource window included
   if (dp->resBase) memFree(dp->resBase);
   if (dp->priv) cudaFree(dp->priv);
+  if (dp->reshardRuns) cudaFree(dp->reshardRuns);
   if (dp->lastEvent) cudaEventDestroy(dp->lastEvent);
   for (auto& e : dp->pipeEv) if (e) cudaEventDestroy(e);
   if (dp->sideStream) cudaStreamDestroy(dp->sideStream);
@@ -398,6 +399,40 @@ void sliceEven(size_t count, size_t es, int n, size_t* begin, size_t* cnt) {
     begin[r] = b;
     cnt[r] = std::min(per, count - b);
   }
+}
+
+// ------------------------------------------------------------------------------------ mesh-to-mesh reshard
+ncclResult_t devPlaneRunReshard(ncclComm* comm, SymWindow* win, const ReshardRun* runs, int nRuns, const unsigned long long* tileOff, void* dst,
+                                size_t totalBytes, cudaStream_t stream) {
+  DevicePlane* dp = comm->devPlane;
+  if (!dp || !dp->resWin || !win) return ncclInvalidUsage;
+  NCCLCHECK(devPlaneOrderStreams(comm, stream));
+  // the run list travels to device memory in stream order; the buffer grows as needed and lives as long as the communicator
+  const size_t need = std::max<size_t>((size_t)nRuns, 1) * sizeof(ReshardRun);
+  if (need > dp->reshardBytes) {
+    if (dp->reshardRuns) { CUDACHECK(cudaStreamSynchronize(stream)); CUDACHECK(cudaFree(dp->reshardRuns)); dp->reshardRuns = nullptr; }
+    dp->reshardBytes = std::max(need * 2, (size_t)4096);
+    CUDACHECK(cudaMalloc(&dp->reshardRuns, dp->reshardBytes));
+  }
+  if (nRuns) CUDACHECK(cudaMemcpyAsync(dp->reshardRuns, runs, (size_t)nRuns * sizeof(ReshardRun), cudaMemcpyHostToDevice, stream));
+  ReshardArgs a;
+  memset(&a, 0, sizeof(a));
+  a.rank = comm->rank;
+  a.nRanks = comm->nRanks;
+  a.nRuns = nRuns;
+  a.runs = (const ReshardRun*)dp->reshardRuns;
+  for (int p = 0; p < comm->nRanks; ++p) a.winPeer[p] = (const char*)win->host.peerPtr[p];
+  a.tileOff = tileOff;
+  a.dst = (char*)dst;
+  fillSync(comm, &a.sync);
+  // every rank launches the same number of CTAs (the barrier slots pair up CTA by CTA): sized from the largest tile a rank can
+  // receive, which all ranks know
+  int ctas = (int)std::min<size_t>(std::max<size_t>(totalBytes / ((size_t)256 << 10), 1), 32);
+  dp->launches++;
+  tLastAlgo = "PULL";
+  tLastProto = "SIMPLE";
+  tLastCtas = ctas;
+  return launchKernel(reshardKernelFn(), dim3(ctas), dim3(kCtaThreads), 0, &a, stream, false, paramLaunchPdl() != 0);
 }
 
 // ------------------------------------------------------------------------------------ collectives

@@ -53,6 +53,8 @@ struct DevicePlane {
   size_t hostStageBytes = 0;
   uint64_t ceEpoch = 0;
   uint64_t launches = 0;              // kernels launched by this communicator
+  void* reshardRuns = nullptr;        // device copy of the run list of the last mesh-to-mesh reshard
+  size_t reshardBytes = 0;
   unsigned long long* curStamp = nullptr;   // device-visible time-stamp slot of the task being launched (set by the profiler glue)
   int barrierMcMin = 0;               // barriers arrive by multimem.red from this many ranks on (0 = never)
   int llMcMin = 0;                    // flagged lines are published by multimem.st from this many ranks on (0 = never)
@@ -69,6 +71,11 @@ ncclResult_t devPlaneRunLLBatch(ncclComm* comm, const Task* tasks, int count, in
 // Kernels of one communicator share its barrier slots and epochs, so they run one after the other even
 // when issued on different streams: makes `stream` wait for the communicator's previous launch.
 ncclResult_t devPlaneOrderStreams(ncclComm* comm, cudaStream_t stream);
+// Mesh-to-mesh reshard by peer loads (contrib/m2n.cc): `runs` is what this rank pulls, in host memory; the source tiles lie in
+// `win` at the byte offsets that `tileOff` (device memory, one word per rank) holds when the kernel runs.
+struct ReshardRun;
+ncclResult_t devPlaneRunReshard(ncclComm* comm, SymWindow* win, const ReshardRun* runs, int nRuns, const unsigned long long* tileOff, void* dst,
+                                size_t totalBytes, cudaStream_t stream);
 ncclResult_t devPlaneCheckStatus(ncclComm* comm);   // turns a kernel-side time-out into an async error
 void tuningDefaults(TuningTable* t);
 ncclResult_t tuningLoadFile(TuningTable* t, const char* path);

@@ -19,6 +19,7 @@ using namespace b200;
 
 namespace b200 {
 void hostStagedRelease(ncclComm* comm);   // contrib/host_staged.cc
+void m2nCommRelease(ncclComm* comm);      // contrib/m2n.cc
 
 B200_PARAM(CommBlocking, "COMM_BLOCKING", -1, "Override ncclConfig_t::blocking (-1 = keep the program's value)")
 B200_PARAM(CheckMode, "CHECK_MODE", 1, "Argument checking: 0 none, 1 local, 2 local + cross-rank")
@@ -186,6 +187,7 @@ static void freeComm(ncclComm* comm) {
   profilerCommFini(comm);
   tunerUnload(comm);
   hostStagedRelease(comm);
+  m2nCommRelease(comm);
   if (comm->devPlane) {
     int cur = -1;
     cudaGetDevice(&cur);

@@ -1,13 +1,19 @@
-// Mesh-to-mesh resharding over grouped send / receive: see include/nccl_m2n.h.
+// Mesh-to-mesh resharding: see include/nccl_m2n.h. With a window that holds the source tiles every destination rank pulls
+// its runs with one kernel (reshardKernel in kernels/copy.cu); without one the runs move as grouped send / receive.
 // Reference parity: contrib/nccl_m2n (ncclReshardWithWindow, src/nccl_m2n.h:175; mesh / placement
 // model of its README "Concepts"); the reference moves data with one-sided kernels over windows and
 // adds hierarchical routing for multi-node NVLink domains, which a single node does not need.
 #include "nccl_m2n.h"
 
 #include <algorithm>
+#include <map>
+#include <mutex>
 #include <vector>
 
 #include "../comm/comm.h"
+#include "../comm/device_plane.h"
+#include "../kernels/args.h"
+#include "../mem/symmetric.h"
 
 using namespace b200;
 
@@ -105,7 +111,32 @@ size_t elemSize(ncclDataType_t t) {
   }
 }
 
+// Device words of a communicator for the offset exchange: [0] this rank's offset, [8 ..) the gathered table.
+std::mutex gWordsLock;
+std::map<ncclComm*, unsigned long long*> gWords;
+ncclResult_t m2nWords(ncclComm* comm, unsigned long long** out) {
+  std::lock_guard<std::mutex> g(gWordsLock);
+  unsigned long long*& w = gWords[comm];
+  if (!w) {
+    CUDACHECK(cudaMalloc((void**)&w, (8 + kMaxRanks) * sizeof(unsigned long long)));
+    CUDACHECK(cudaMemset(w, 0, (8 + kMaxRanks) * sizeof(unsigned long long)));
+  }
+  *out = w;
+  return ncclSuccess;
+}
+
 }  // namespace
+
+namespace b200 {
+void m2nCommRelease(ncclComm* comm) {
+  std::lock_guard<std::mutex> g(gWordsLock);
+  auto it = gWords.find(comm);
+  if (it == gWords.end()) return;
+  cudaFree(it->second);
+  (void)cudaGetLastError();
+  gWords.erase(it);
+}
+}  // namespace b200
 
 extern "C" {
 
@@ -115,7 +146,7 @@ ncclResult_t ncclM2nInit(ncclM2nConfig_t* config) {
 }
 ncclResult_t ncclM2nFinalize(void) { return ncclSuccess; }
 
-ncclResult_t ncclReshardWithWindow(ncclComm_t comm, ncclWindow_t /*window*/, const ncclDistTensor_t* src, const ncclDistTensor_t* dst, cudaStream_t stream) {
+ncclResult_t ncclReshardWithWindow(ncclComm_t comm, ncclWindow_t window, const ncclDistTensor_t* src, const ncclDistTensor_t* dst, cudaStream_t stream) {
   if (!commValid(comm) || !src || !dst) return ncclInvalidArgument;
   if (src->ndims != dst->ndims || src->dtype != dst->dtype || src->ndims < 1 || src->ndims > NCCL_RESHARD_MAX_TENSOR_DIMS) {
     WARN("ncclReshardWithWindow: source and destination must agree on 1 to 3 dimensions and on the data type");
@@ -138,6 +169,42 @@ ncclResult_t ncclReshardWithWindow(ncclComm_t comm, ncclWindow_t /*window*/, con
   int mySS = -1, mySR = -1, myDS = -1, myDR = -1;
   const bool onS = locate(S, comm->rank, &mySS, &mySR) && src->dataPtr;
   const bool onD = locate(D, comm->rank, &myDS, &myDR) && dst->dataPtr;
+  // ---- with a window that holds the source tiles, on GPUs that map each other: one pull kernel per rank
+  // (every rank passes the window or none does: the choice below must be the same everywhere)
+  if (window && !comm->hostOnly && comm->devPlane && (comm->nRanks == 1 || comm->lsaAll)) {
+    if (window->magic != kWindowMagic || !window->hostState) { WARN("ncclReshardWithWindow: not a window handle"); return ncclInvalidArgument; }
+    SymWindow* w = (SymWindow*)window->hostState;
+    unsigned long long myOff = 0;
+    if (onS) {
+      const char* base = (const char*)w->host.userPtr;
+      size_t tileBytes = es;
+      for (int d = 0; d < nd; ++d) tileBytes *= S.local[d];
+      if ((const char*)src->dataPtr < base || (const char*)src->dataPtr + tileBytes > base + w->host.size) {
+        WARN("ncclReshardWithWindow: the source tile does not lie inside the window");
+        return ncclInvalidArgument;
+      }
+      myOff = (unsigned long long)((const char*)src->dataPtr - base);
+    }
+    std::vector<ReshardRun> pulls;
+    size_t dstTileBytes = es;
+    for (int d = 0; d < nd; ++d) dstTileBytes *= D.local[d];
+    if (onD) {
+      for (int ss = 0; ss < S.shards; ++ss) {
+        const int dr = comm->rank - D.mesh->startRank;
+        const int sRank = rankOf(S, ss, dr % S.replicas);
+        std::vector<Run> runs;
+        runsOf(S, D, nd, gS, ss, myDS, &runs);
+        for (const Run& r : runs) pulls.push_back(ReshardRun{r.srcOff * es, r.dstOff * es, r.count * es, sRank, 0});
+      }
+    }
+    // where every rank's source tile sits inside the window: eight bytes per rank, gathered on the stream
+    unsigned long long* words = nullptr;
+    NCCLCHECK(m2nWords(comm, &words));
+    CUDACHECK(cudaMemcpyAsync(words, &myOff, sizeof(myOff), cudaMemcpyHostToDevice, stream));
+    NCCLCHECK(ncclAllGather(words, words + 8, sizeof(myOff), ncclUint8, comm, stream));
+    return devPlaneRunReshard(comm, w, pulls.data(), (int)pulls.size(), words + 8, onD ? dst->dataPtr : nullptr, dstTileBytes, stream);
+  }
+
   struct Op { bool send; int peer; void* p; size_t count; };
   std::vector<Op> ops;
   // canonical order: destination ranks ascending, then source shards ascending, then runs

@@ -171,6 +171,25 @@ struct P2pArgs {
   SyncArgs sync;
 };
 
+// Mesh-to-mesh resharding by peer loads: every destination rank pulls the runs of its tile straight out of the source
+// ranks' tiles, which lie in a registered window.
+struct ReshardRun {
+  unsigned long long srcOff;   // bytes from the start of the source rank's tile
+  unsigned long long dstOff;   // bytes from the start of this rank's destination tile
+  unsigned long long bytes;
+  int srcRank;
+  int pad;
+};
+struct ReshardArgs {
+  int rank, nRanks, emu;
+  int nRuns;                              // runs this rank pulls
+  const ReshardRun* runs;                 // device memory
+  const char* winPeer[kMaxRanks];         // winPeer[p]: rank p's part of the window as mapped here
+  const unsigned long long* tileOff;      // device memory [nRanks]: byte offset of rank p's source tile inside the window (all-gathered just before)
+  char* dst;                              // this rank's destination tile
+  SyncArgs sync;
+};
+
 struct SignalArgs {
   int rank, nRanks;
   uint64_t* signals[kMaxRanks];          // signals[p]: rank p's [src][kSignalsPerPeer] counters

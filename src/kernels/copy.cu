@@ -414,6 +414,41 @@ __global__ void __launch_bounds__(kCtaThreads, 1) p2pKernel(const __grid_constan
   }
 }
 
+// ------------------------------------------------------------------------- mesh-to-mesh reshard
+// One launch per rank: after a barrier (every rank's kernel has started, so every source tile is final) the CTAs share the
+// 64 KiB tiles of all runs round-robin and copy them with peer loads; a closing barrier tells the sources that nobody
+// reads their tiles any more. No mailbox, no matching of sends and receives.
+// Reference parity: the pull kernels of contrib/nccl_m2n (src/m2n_kernels.cu).
+__global__ void __launch_bounds__(kCtaThreads, 1) reshardKernel(const __grid_constant__ ReshardArgs a) {
+  const int rank = ctaRank(a.emu, a.rank);
+  pdlEnter();
+  KernelStamp stamp(a.sync.stamps);
+  CtaBarrier bar;
+  bar.init(a.sync, rank, a.nRanks, blockIdx.x);
+  const bool ok = bar.sync(false, false);
+  constexpr unsigned long long kTile = 64 << 10;
+  if (ok) {
+    unsigned long long firstTile = 0;   // index of the run's first tile in the round-robin over all runs
+    for (int r = 0; r < a.nRuns; ++r) {
+      const ReshardRun run = a.runs[r];
+      const unsigned long long tiles = (run.bytes + kTile - 1) / kTile;
+      const char* src = a.winPeer[run.srcRank] + a.tileOff[run.srcRank] + run.srcOff;
+      char* dst = a.dst + run.dstOff;
+      // first tile of this run that belongs to this CTA
+      unsigned long long t = ((unsigned long long)blockIdx.x + gridDim.x - firstTile % gridDim.x) % gridDim.x;
+      for (; t < tiles; t += gridDim.x) {
+        const unsigned long long off = t * kTile;
+        const unsigned long long len = run.bytes - off < kTile ? run.bytes - off : kTile;
+        copyChunk(dst + off, src + off, (size_t)len);
+      }
+      firstTile += tiles;
+    }
+  }
+  bar.sync(false, false);
+  bar.finish();
+}
+const void* reshardKernelFn() { return (const void*)reshardKernel; }
+
 // ------------------------------------------------------------------------- local scale
 template <typename T>
 __global__ void scaleKernel(ScaleArgs a) {

@@ -33,6 +33,7 @@ const void* copyKernelFn();
 const void* copyBulkKernelFn();              // same arguments as copyKernelFn: bulk-copy engines, 32 threads per CTA, dynamic shared memory
 size_t copyBulkSmemBytes();
 const void* p2pKernelFn();
+const void* reshardKernelFn();                 // takes ReshardArgs: pulls the runs of a mesh-to-mesh reshard with peer loads
 const void* scaleKernelFn(ncclDataType_t type);
 const void* localCopyKernelFn(int unroll);   // takes ScaleArgs{src, dst, count = bytes}; unroll 4 or 8
 const void* localBulkCopyKernelFn();         // same arguments: one thread per CTA drives cp.async.bulk copies through shared memory
