@@ -198,8 +198,15 @@ def main():
             f1.record(h.stream)
         torch.cuda.synchronize()
         ms2 = d.max(f0.elapsed_time(f1) / k2)
+        # what arrived in host memory is what the device holds (head and tail of the buffer), and the device result is
+        # checked against the seeds like the headline above
+        span = min(nbytes, 64 << 20)
+        same = bool(torch.equal(host_out[:span].cuda(), h.recv_t[:span])) and bool(torch.equal(host_out[nbytes - span:].cuda(), h.recv_t[nbytes - span:nbytes]))
+        ver.check("all_reduce", nbytes)
         e2e = {"value": round(nbytes / (ms2 * 1e-3) / 1e9 * factor, 3), "unit": "GB/s", "ms_per_step": round(ms2, 4), "steps": k2,
-               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
+               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes, "host_result_matches_device": same}
+        if not same:
+            ver.failures.append("e2e: host result differs from the device result")
     except Exception as ex:  # noqa: BLE001
         e2e = {"error": str(ex)[:200]}
 
