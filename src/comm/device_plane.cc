@@ -17,7 +17,7 @@
 
 namespace b200 {
 
-B200_PARAM(ScratchMb, "B200_SCRATCH_MB", 128, "Staging area of the resource window per rank (MiB)")
+B200_PARAM(ScratchMb, "B200_SCRATCH_MB", 256, "Staging area of the resource window per rank (MiB)")
 B200_PARAM(WaitTimeoutMs, "B200_WAIT_TIMEOUT_MS", 30000, "Budget of one device-side wait before the kernel gives up")
 B200_PARAM(MaxCtas, "MAX_CTAS", 0, "Upper bound on CTAs per collective kernel (0 = from the tuning table)")
 B200_PARAM(MinCtas, "MIN_CTAS", 0, "Lower bound on CTAs per collective kernel")
@@ -31,7 +31,7 @@ B200_PARAM(LLMulticast, "B200_LL_MC_MIN_RANKS", -1, "Flagged-line all-reduce / a
 B200_PARAM(CopyKernel, "B200_COPY_KERNEL", 0, "One-rank copy path: 0 = vector loads and stores, 1 = bulk-copy engines through shared memory (messages of 1 MiB and more)")
 B200_PARAM(PreloadKernels, "B200_PRELOAD_KERNELS", 1, "Load every collective kernel when the first communicator of a device is created (with lazy module loading the first launch of a kernel can otherwise wait for kernels that are running, which may in turn be waiting for that launch on another rank)")
 B200_PARAM(StagePipeline, "B200_STAGE_PIPELINE", 1, "Reductions on unregistered buffers overlap the copies through the staging area with the kernels (two halves, side stream)")
-B200_PARAM(StagePipelineMin, "B200_STAGE_PIPELINE_MIN", 134217728, "Smallest message in bytes that is pipelined through the staging area")
+B200_PARAM(StagePipelineMin, "B200_STAGE_PIPELINE_MIN", 67108864, "Smallest message in bytes that is pipelined through the staging area")
 B200_PARAM(P2pDirect, "B200_P2P_DIRECT", 1, "Large sends write straight into a receive buffer that lies in a registered window (rendezvous) instead of going through the mailbox")
 B200_PARAM(LaunchPdl, "B200_PDL", 1, "Launch collectives with programmatic stream serialisation (the next kernel of the stream is scheduled while the previous one drains)")
 B200_PARAM(BarrierMulticast, "B200_BARRIER_MC_MIN_RANKS", -1, "Cross-GPU barriers arrive with one multimem.red on a multicast alias of the flag page from this many ranks on (0 = never, -1 = from the selection table)")
@@ -543,8 +543,11 @@ static ncclResult_t runReduction(ncclComm* comm, const Task& t) {
     size_t cap = stageElems / (16 * n) * (16 * n);   // reduce-scatter pieces stay divisible by n, slices by 16 bytes
     pipelined = paramStagePipeline() != 0 && bytes >= (size_t)paramStagePipelineMin() && dp->sideStream != nullptr;
     if (pipelined) {
+      // at least four pieces, so that the copies of all but the first and the last one hide behind kernels, of 16 MiB or more
       halfBytes = dp->stageBytes / 2 / 4096 * 4096;
-      cap = halfBytes / es / (16 * n) * (16 * n);
+      const size_t unit = (size_t)16 * n;
+      const size_t quarter = std::max<size_t>((total / 4 + unit - 1) / unit * unit, ((size_t)16 << 20) / es / unit * unit);
+      cap = std::min(halfBytes / es / unit * unit, quarter);
     }
     if (pieceTotal > cap) pieceTotal = cap;
     if (pipelined && pieceTotal >= total) pipelined = false;
