@@ -24,7 +24,7 @@ from ..core import BF16, FP32
 from . import perf
 
 ALGO_AUTO, ALGO_LL, ALGO_P2P, ALGO_NVLS, ALGO_CE, ALGO_NVLS1 = -1, 1, 2, 3, 6, 8
-MODE_PUSH, MODE_PULL, MODE_MC, MODE_BULK = 0, 1, 2, 4
+MODE_PUSH, MODE_PULL, MODE_MC, MODE_SPLIT, MODE_BULK = 0, 1, 2, 3, 4
 
 
 def size_list(limit, fine_lo=64 << 10, fine_hi=128 << 20):
@@ -133,6 +133,9 @@ def main(argv=None):
                                 row["BPULL/%d%s" % (c, sfx)] = measure(coll, nb, ALGO_P2P, MODE_PULL | MODE_BULK)
                                 if coll in ("all_gather", "broadcast"):
                                     row["BMC/%d%s" % (c, sfx)] = measure(coll, nb, ALGO_NVLS, MODE_MC | MODE_BULK)
+                            # broadcast shared out among the non-root ranks: worth it where the root's store stream is the limit
+                            if coll == "broadcast" and n >= 3 and block % 16 == 0 and block >= (1 << 20):
+                                row["SPLIT/%d%s" % (c, sfx)] = measure(coll, nb, ALGO_P2P, MODE_SPLIT)
             toggles(False, False)
             if not reduces and coll != "broadcast" and nb >= (1 << 20):
                 row["CE"] = measure(coll, nb, ALGO_CE, -1)   # copy engines: zero SMs

@@ -745,6 +745,8 @@ static ncclResult_t runCopyColl(ncclComm* comm, const Task& t) {
     TunePick pk = tunePick(dp->tune, t.func, n, key);
     if (pk.valid) { forced = pk.algo; modeForce = pk.mode; tPickCtas = pk.ctas; }
   }
+  const bool wantSplit = modeForce == MODE_SPLIT;
+  if (wantSplit) modeForce = -1;
   if (modeForce >= 0 && (modeForce & MODE_BULK)) { bulk = true; modeForce &= ~MODE_BULK; }
   if (forced == ALGO_RING && t.func == FUNC_ALLGATHER) return ringTreeRun(comm, t, forced);
   if (forced == ALGO_CE || (forced == ALGO_AUTO && dp->tune.ceMin && B >= dp->tune.ceMin)) {
@@ -781,6 +783,34 @@ static ncclResult_t runCopyColl(ncclComm* comm, const Task& t) {
   if (recvAl.ok && !(modeForce == MODE_PULL && sendAl.ok)) mode = MODE_PUSH;
   else if (sendAl.ok) mode = MODE_PULL;
   else { mode = MODE_PULL; staged = true; }
+
+  // ---- broadcast with the work shared out among the non-root ranks (see copyCollKernel). Every rank takes this decision
+  // from what all ranks know: the output windows (symmetric offsets) and the size. Whether the root's input can be pulled
+  // is the root's knowledge; it tells the others from inside the kernel.
+  if (wantSplit && t.func == FUNC_BROADCAST && n >= 3 && recvAl.ok && B % 16 == 0 && aligned16(recvAl, n) && comm->sym && comm->sym->winTableDev) {
+    CollArgs a;
+    baseArgs(comm, &a, t.func);
+    a.root = t.root;
+    a.count = B;
+    a.sendStride = a.recvStride = B;
+    a.mode = MODE_SPLIT;
+    a.lsend[me] = t.send;
+    a.lrecv[me] = t.recv;
+    for (int p = 0; p < n; ++p) a.recv[p] = recvAl.peer[p];
+    a.winTable = (void* const*)comm->sym->winTableDev;
+    a.vec16 = 1;
+    if (me == t.root) {
+      SymWindow* w = symFindWindow(comm, t.send, B);
+      if (w && w->symmetric && w->slot >= 0 && ((uintptr_t)t.send & 15) == 0) {
+        a.bcastSlot = w->slot + 1;
+        a.bcastOff = (uintptr_t)t.send - (uintptr_t)w->host.userPtr;
+      } else if ((uintptr_t)t.send & 15) {
+        a.vec16 = 0;   // the root pushes everything itself, byte by byte where it has to
+      }
+    }
+    int ctas = clampCtas(comm, B, dp->tune.copyCtas);
+    return launchColl(comm, copyKernelFn(), &a, ctas, t.stream, "SPLIT");
+  }
 
   // pieces that fit the staging area
   const size_t segsStaged = (t.func == FUNC_ALLTOALL || t.func == FUNC_SCATTER) ? n : 1;

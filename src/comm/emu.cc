@@ -179,8 +179,8 @@ int b200EmuCopy(void* ctx, int func, int mode, size_t bytes, const void** send, 
   a.emu = 1;
   a.func = func;
   a.root = root;
-  const bool bulk = mode >= 0 && mode != 3 && (mode & MODE_BULK);
-  a.mode = bulk ? (mode & ~MODE_BULK) : mode;
+  const bool bulk = mode >= 0 && mode != 3 && mode != 8 && (mode & MODE_BULK);
+  a.mode = mode == 8 ? MODE_SPLIT : bulk ? (mode & ~MODE_BULK) : mode;   // 8: broadcast shared out among the non-root ranks
   a.count = bytes;
   a.sendStride = bytes;
   a.recvStride = bytes;

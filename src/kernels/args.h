@@ -30,6 +30,7 @@ constexpr size_t kOffP2pRdv = 14 << 10;                                         
 constexpr int kP2pRdvLines = 4;                                                     // large operations of one ordered pair that one launch can run in rendezvous mode
 constexpr size_t kP2pDirectMin = 256 << 10;                                         // messages from this size on wait for the receiver's descriptor first
 constexpr int kMaxWinSlots = 256;                                                   // windows of a communicator that the device-side table knows
+constexpr size_t kOffBcastDesc = 15 << 10;                                          // one 16-byte line: where the root's send buffer is (split broadcast)
 constexpr size_t kOffMcBarrier = 13 << 10;                                          // [slot] u32: arrival counters of the multicast barrier
 constexpr size_t kOffRingFlags = 16 << 10;                                          // [slot][src] u32: ring step counters
 constexpr size_t kOffTreeFlags = 24 << 10;                                          // [slot][tree 2][src] u32: tree phase counters
@@ -78,6 +79,7 @@ enum CollMode : int {
   MODE_PUSH = 0,     // writer stores into peers' buffers
   MODE_PULL = 1,     // reader loads from peers' buffers
   MODE_MC = 2,       // one multimem.st stream reaches every peer
+  MODE_SPLIT = 3,    // broadcast only: the other ranks each pull a share of the root's buffer and store it to all of them
   MODE_BULK = 4,     // flag added to a mode when it is forced or tabled: moved by bulk-copy engines (few CTAs) instead of threads
 };
 
@@ -109,6 +111,11 @@ struct CollArgs {
   void* ll[kMaxRanks];                  // ll[p]: rank p's LL region
   uint32_t* llEpoch[kMaxRanks];         // llEpoch[r]: {epoch, finished CTAs} private to rank r
   char* llMc;                           // multicast alias of the flagged-line region (null: unicast stores only)
+  // split broadcast: where the root's send buffer is. The root fills bcastSlot (window slot + 1, 0 = not in a window) and
+  // bcastOff and publishes them from the kernel; the emulation passes send[root] instead and leaves winTable null.
+  void* const* winTable;                // device table [window slot][rank] of peer mappings
+  int bcastSlot;
+  unsigned long long bcastOff;
 };
 
 // Several small all-reduces of one group carried by one launch of the flagged-line kernel: item i

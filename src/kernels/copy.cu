@@ -103,6 +103,88 @@ __global__ void __launch_bounds__(kCtaThreads, 1) copyCollKernel(const __grid_co
   KernelStamp stamp(a.sync.stamps);
   CtaBarrier bar;
   bar.init(a.sync, rank, a.nRanks, blockIdx.x);
+  if (a.func == FUNC_BROADCAST && a.mode == MODE_SPLIT) {
+    // Large broadcast with the work shared out: every rank but the root pulls one share of the root's buffer (one pass
+    // over the root's links) and stores it into its own output and into the other non-root ranks' outputs; the root
+    // copies its output locally. The stores of all GPUs work, not only the root's. The root's buffer is found through the
+    // descriptor that every CTA of the root publishes before the opening barrier (its window slot and offset), since only
+    // the root knows its own send pointer; without a window the root pushes everything itself.
+    const int n = a.nRanks, root = a.root;
+    __shared__ uint4 sDesc;
+    if (rank == root && a.winTable != nullptr && threadIdx.x < n && threadIdx.x != rank) {
+      // Every CTA of the root writes the same line before it arrives at its barrier slot, and the matching CTA of a peer reads
+      // it after that barrier: the line a peer sees is this launch's (the root cannot start the next launch before every
+      // CTA of every peer has arrived at the closing barrier, which comes after the read).
+      uint4 d = make_uint4(1u, (uint32_t)a.bcastSlot, (uint32_t)a.bcastOff, (uint32_t)(a.bcastOff >> 32));
+      stVolatile16((char*)a.sync.inbox[threadIdx.x] + kOffBcastDesc, d);
+    }
+    bool ok = bar.sync(rank == root, rank != root);
+    const char* src = (const char*)a.send[root];   // emulation: given directly
+    if (a.winTable != nullptr && rank != root) {
+      if (threadIdx.x == 0) sDesc = ldVolatile16((const char*)a.sync.inbox[rank] + kOffBcastDesc);
+      __syncthreads();
+      const uint4 d = sDesc;
+      src = d.y ? (const char*)a.winTable[(size_t)(d.y - 1) * kMaxRanks + root] + (((size_t)d.w << 32) | d.z) : nullptr;
+      if (d.x != 1u) ok = false;   // never written: leave the data alone
+    }
+    const bool shared = rank == root ? (a.winTable != nullptr ? a.bcastSlot != 0 : true) : src != nullptr;
+    const size_t B = a.count;
+    const size_t packs = B / 16;
+    const char* ls = (const char*)a.lsend[rank];
+    char* lr = (char*)a.lrecv[rank];
+    if (ok && B > 0 && rank == root && !a.vec16) {
+      // the root's buffer is not 16-byte aligned: nothing is shared out (bcastSlot is 0), the root stores every byte itself
+      for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < B; i += (size_t)gridDim.x * blockDim.x) {
+        const char v = ls[i];
+        for (int j = 0; j < n; ++j) {
+          char* d = j == 0 ? lr : (char*)a.recv[(rank + j) % n];
+          if (d != ls) d[i] = v;
+        }
+      }
+    } else if (ok && B > 0 && a.vec16) {
+      if (rank == root) {
+        // local copy into the root's own output; without a window also the push to everybody
+        const int nDst = shared ? 1 : n;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < packs; i += (size_t)gridDim.x * blockDim.x) {
+          const uint4 v = ldStream16(ls + i * 16);
+          for (int j = 0; j < nDst; ++j) {
+            char* d = j == 0 ? lr : (char*)a.recv[(rank + j) % n];
+            if (d != ls) st16(d + i * 16, v);
+          }
+        }
+      } else if (shared) {
+        const int w = (rank - root - 1 + n) % n;                       // worker index among the n - 1 non-root ranks
+        const size_t share = ((packs + (n - 1) - 1) / (n - 1));        // packs per worker
+        const size_t first = (size_t)w * share, last = first + share < packs ? first + share : packs;
+        const size_t stride = (size_t)gridDim.x * blockDim.x;
+        size_t i = first + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+        for (; i + 3 * stride < last; i += 4 * stride) {
+          uint4 v[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) v[u] = ldStream16(src + (i + u * stride) * 16);
+#pragma unroll
+          for (int j = 0; j < kMaxRanks; ++j) {
+            const int p = (rank + j) % n;
+            if (j < n && p != root) {
+              char* d = p == rank ? lr : (char*)a.recv[p];
+#pragma unroll
+              for (int u = 0; u < 4; ++u) st16(d + (i + u * stride) * 16, v[u]);
+            }
+          }
+        }
+        for (; i < last; i += stride) {
+          const uint4 v = ldStream16(src + i * 16);
+          for (int j = 0; j < n; ++j) {
+            const int p = (rank + j) % n;
+            if (p != root) st16((p == rank ? lr : (char*)a.recv[p]) + i * 16, v);
+          }
+        }
+      }
+    }
+    bar.sync(true, false);
+    bar.finish();
+    return;
+  }
   bool ok = bar.sync(false, false);   // every rank's kernel has started: inputs final, outputs free
   __shared__ Seg segs[kMaxRanks];
   __shared__ int nSeg;

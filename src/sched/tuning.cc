@@ -96,6 +96,7 @@ bool tuneParse(TuningTable* t, const std::string& json) {
         else if (algo == "BPUSH") e.mode = MODE_PUSH | MODE_BULK;   // bulk-copy engines instead of threads
         else if (algo == "BPULL") e.mode = MODE_PULL | MODE_BULK;
         else if (algo == "BMC") { e.algo = ALGO_NVLS; e.mode = MODE_MC | MODE_BULK; }
+        else if (algo == "SPLIT") e.mode = MODE_SPLIT;               // broadcast: the non-root ranks share the work
         rows.push_back(e);
         c.eat(',');
       }

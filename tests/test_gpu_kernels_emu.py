@@ -225,6 +225,29 @@ def test_reduce_scatter_and_reduce(emu_lib, n, dtype, count):
         emu_lib.b200EmuDestroy(ctx)
 
 
+@pytest.mark.parametrize("n", [3, 4, 8])
+@pytest.mark.parametrize("nbytes", [16, 48, 4096 + 16, (1 << 20) + 48, 3 << 20])
+@pytest.mark.parametrize("ctas", [1, 5])
+def test_broadcast_shared_out(emu_lib, n, nbytes, ctas):
+    """Large-broadcast form: every non-root rank pulls one share of the root's buffer and stores it to all non-root
+    ranks; the root copies its own output. In place and out of place, several launches (barrier epochs carry over)."""
+    MODE_SPLIT_EMU = 8
+    ctx = emu_lib.b200EmuCreate(n, 5000)
+    try:
+        g = torch.Generator().manual_seed(nbytes + n)
+        for it, root in enumerate([n - 1, 0, 1]):
+            send = [torch.randint(0, 256, (nbytes,), generator=g, dtype=torch.uint8).cuda() for _ in range(n)]
+            recv = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(n)]
+            if it == 2:
+                recv[root] = send[root]   # in place on the root
+            want = send[root].clone()
+            assert emu_lib.b200EmuCopy(ctx, FUNC_BROADCAST, MODE_SPLIT_EMU, nbytes, _ptrs(send), _ptrs(recv), root, ctas) == 0
+            torch.cuda.synchronize()
+            assert all(torch.equal(r, want) for r in recv), (it, root)
+    finally:
+        emu_lib.b200EmuDestroy(ctx)
+
+
 @pytest.mark.parametrize("n", [2, 3, 8])
 @pytest.mark.parametrize("mode", [MODE_PUSH, MODE_PULL, MODE_PUSH | MODE_BULK, MODE_PULL | MODE_BULK])
 @pytest.mark.parametrize("nbytes", [16, 4096 + 16, (1 << 20) + 48, 1001])
