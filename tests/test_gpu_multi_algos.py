@@ -117,6 +117,22 @@ def test_copy_collectives_on_bulk_engines(tmp_path):
         _check(res, n)
 
 
+def test_broadcast_shared_out_among_the_other_ranks(tmp_path):
+    """A selection table that sends every broadcast to the shared-out form: with registered buffers the non-root ranks
+    pull from the root's window (found through the descriptor the root publishes inside the kernel); with unregistered
+    ones the form does not apply and the default path runs."""
+    import json
+    n = min(_ngpus(), 8)
+    if n < 3:
+        pytest.skip("needs at least three GPUs")
+    table = {str(n): {"broadcast": [[1 << 40, "SPLIT", 6]]}}
+    path = tmp_path / "split_table.json"
+    path.write_text(json.dumps(table))
+    for registered in (True, False):
+        res = run_ranks(_colls_rank, n, args=(registered, ""), env={"NCCL_TUNING_FILE": str(path)}, timeout=300)
+        _check(res, n)
+
+
 @pytest.mark.parametrize("algo", ["", "P2P"])
 def test_unregistered_reductions_pipelined_through_small_staging(algo):
     """A 2 MiB staging area and a 1 MiB pipelining threshold: the 4 MiB all-reduce of the battery runs as several
