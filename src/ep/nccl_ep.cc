@@ -26,6 +26,7 @@ struct ncclEpGroup {
   uint32_t* mask = nullptr;           // [n] device words: non-zero = that rank is left out of dispatch / combine
   int smCount = 0;
   int lastError = 0;
+  int layoutClass = 0;                // 0 none yet, 1 expert-major, 2 per-rank (rank-major / flat)
 };
 
 struct ncclEpHandle {
@@ -207,6 +208,14 @@ ncclResult_t ncclEpInitHandle(ncclEpHandle_t* out, ncclEpGroup_t g, ncclEpLayout
   if (config && !cfgOk(config)) return ncclInvalidArgument;
   if (layout == NCCL_EP_LAYOUT_UNSET) layout = NCCL_EP_LAYOUT_EXPERT_MAJOR;
   if (layout != NCCL_EP_LAYOUT_EXPERT_MAJOR && layout != NCCL_EP_LAYOUT_RANK_MAJOR && layout != NCCL_EP_LAYOUT_FLAT) return ncclInvalidArgument;
+  // The landing zones are laid out per layout class, and the per-rank layouts recognise a used row by the epoch in its
+  // header: rows of the other class left in the zone could be mistaken for one. One class per group.
+  const int cls = layout == NCCL_EP_LAYOUT_EXPERT_MAJOR ? 1 : 2;
+  if (g->layoutClass && g->layoutClass != cls) {
+    WARN("ncclEp: a group serves either expert-major handles or rank-major / flat handles, not both (create a second group)");
+    return ncclInvalidUsage;
+  }
+  g->layoutClass = cls;
   if (g->K == 0) {
     // first handle: the combine landing zones depend on top-k (collective, like every handle creation); a row per
     // selected expert (expert-major) or per rank (rank-major, flat), whichever is more
