@@ -5,6 +5,7 @@
 // Reference parity: the role of src/graph/tuning.cc + src/sym_kernels.cc (cost models) and of the
 // tuner plugin; here the table comes from measurement instead of a model.
 #include <ctype.h>
+#include <stdio.h>
 
 #include "../comm/device_plane.h"
 #include "tuning_defaults.h"
@@ -130,6 +131,17 @@ TunePick tunePick(const TuningTable& t, int func, int n, size_t bytes) {
 }
 
 }  // namespace b200
+
+// Parses a table given as text and looks one choice up: writes "<algo> <mode> <ctas>" (numbers as the data plane uses them)
+// into out. Returns 0, 1 when the text does not parse, 2 when no row covers the request. For tests of the tuner's output.
+extern "C" __attribute__((visibility("default"))) int b200TuningLookup(const char* json, int func, int nRanks, unsigned long long bytes, char* out, int outLen) {
+  b200::TuningTable t;
+  if (!json || !b200::tuneParse(&t, json)) return 1;
+  b200::TunePick pk = b200::tunePick(t, func, nRanks, (size_t)bytes);
+  if (!pk.valid) return 2;
+  snprintf(out, outLen, "%d %d %d", pk.algo, pk.mode, pk.ctas);
+  return 0;
+}
 
 // Parses the built-in table and returns the number of (collective, rank count) cells it fills, or -1 when it does
 // not parse: lets a test without a GPU check the table that every GPU communicator loads.
