@@ -13,7 +13,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 BIN = os.path.join(ROOT, "nccl_b200", "bin", "examples")
 
 
-@pytest.mark.parametrize("name", ["allreduce_all_devices", "sendrecv_ring", "window_allgather", "device_api_allreduce"])
+@pytest.mark.parametrize("name", ["allreduce_all_devices", "sendrecv_ring", "window_allgather", "device_api_allreduce", "host_allreduce"])
 def test_example(name):
     if not torch.cuda.is_available():
         pytest.skip("needs a GPU")
