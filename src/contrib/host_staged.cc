@@ -63,6 +63,10 @@ extern "C" ncclResult_t ncclAllReduceFromHost(const void* hostSend, void* hostRe
   if (!commValid(comm) || !hostSend || !hostRecv || !devSend || !devRecv) return ncclInvalidArgument;
   if ((int)type < 0 || (int)type >= ncclNumTypes) return ncclInvalidArgument;
   if (count == 0) return ncclSuccess;
+  if (groupDepth() > 0) {
+    WARN("ncclAllReduceFromHost: not available between ncclGroupStart and ncclGroupEnd (its collectives must launch where they are issued)");
+    return ncclInvalidUsage;
+  }
   cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
   if (cudaStreamIsCapturing(stream, &cs) == cudaSuccess && cs != cudaStreamCaptureStatusNone) {
     WARN("ncclAllReduceFromHost: not available while the stream is being captured (it uses streams of its own)");

@@ -171,7 +171,7 @@ ncclResult_t ncclReshardWithWindow(ncclComm_t comm, ncclWindow_t window, const n
   const bool onD = locate(D, comm->rank, &myDS, &myDR) && dst->dataPtr;
   // ---- with a window that holds the source tiles, on GPUs that map each other: one pull kernel per rank
   // (every rank passes the window or none does: the choice below must be the same everywhere)
-  if (window && !comm->hostOnly && comm->devPlane && (comm->nRanks == 1 || comm->lsaAll)) {
+  if (window && !comm->hostOnly && comm->devPlane && (comm->nRanks == 1 || comm->lsaAll) && groupDepth() == 0) {
     if (window->magic != kWindowMagic || !window->hostState) { WARN("ncclReshardWithWindow: not a window handle"); return ncclInvalidArgument; }
     SymWindow* w = (SymWindow*)window->hostState;
     unsigned long long myOff = 0;
