@@ -10,6 +10,9 @@
 // Client protocol (line based, the one the ncclras tool speaks):
 //   CLIENT PROTOCOL <n> -> SERVER PROTOCOL 2 | TIMEOUT <s> -> OK | SET FORMAT text|json -> OK
 //   STATUS | VERBOSE STATUS -> report, then the server closes the connection
+//   MONITOR [groups]        -> OK, then one line per event ("<seconds> <group> <text>") until the client goes away;
+//                              groups: comma-separated from lifecycle (communicators come and go), peers (processes
+//                              declared dead), all (default)
 // A status report is a collective over processes: the serving process asks every known process
 // for its communicators (in a worker thread, so the RAS thread keeps answering others), marks
 // the ones that do not answer in time, and compares operation counts across the ranks of each
@@ -25,6 +28,8 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <chrono>
+#include <deque>
 #include <set>
 #include <sstream>
 
@@ -62,8 +67,19 @@ struct Ras {
   std::vector<CommRec> comms;
   std::map<std::string, PeerProc> peers;   // keyed by "ip:port" of the peer's RAS socket
   std::set<std::string> deadNotified;
+  // events for clients in monitor mode: a bounded log with running sequence numbers
+  std::deque<std::pair<uint64_t, std::string>> events;
+  uint64_t nextEvent = 1;
 };
 Ras gRas;
+
+// Appends an event (caller holds gRas.lock). Group is "lifecycle" or "peers".
+void eventLocked(const char* group, const std::string& text) {
+  char head[64];
+  snprintf(head, sizeof(head), "%.3f %s ", (double)std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::system_clock::now().time_since_epoch()).count() / 1e3, group);
+  gRas.events.emplace_back(gRas.nextEvent++, std::string(head) + text);
+  while (gRas.events.size() > 1024) gRas.events.pop_front();
+}
 
 int64_t scaled(int64_t ms) { return ms * std::max<int64_t>(paramRasTimeoutFactor(), 1); }
 
@@ -167,6 +183,7 @@ void markDead(const std::string& key, bool notify) {
     auto it = gRas.peers.find(key);
     if (it == gRas.peers.end() || it->second.dead) return;
     it->second.dead = true;
+    eventLocked("peers", "process " + key + " (pid " + std::to_string(it->second.pid) + ") declared dead");
     if (notify && gRas.deadNotified.insert(key).second)
       for (auto& p : gRas.peers) if (!p.second.dead && sockAddrToString(&p.second.addr) != sockAddrToString(&gRas.peerAddr)) others.push_back(p.second.addr);
   }
@@ -314,6 +331,33 @@ void serveClient(int fd) {
       buildReport(line[0] == 'V', json, timeoutMs, &rep);
       sendAll(fd, rep.data(), rep.size(), 5000);
       break;
+    } else if (line.compare(0, 7, "MONITOR") == 0) {
+      const std::string groups = line.size() > 8 ? line.substr(8) : "all";
+      const bool all = groups.find("all") != std::string::npos;
+      uint64_t seen;
+      { std::lock_guard<std::mutex> g(gRas.lock); seen = gRas.nextEvent - 1; }
+      if (!sendAll(fd, "OK\n", 3, 1000)) break;
+      // events from now on; the loop ends when the client closes its end (the send fails) or RAS stops
+      for (;;) {
+        std::vector<std::string> out;
+        bool stop;
+        {
+          std::lock_guard<std::mutex> g(gRas.lock);
+          stop = gRas.stop;
+          for (auto& e : gRas.events) {
+            if (e.first <= seen) continue;
+            seen = e.first;
+            const size_t sp = e.second.find(' ');
+            const std::string grp = e.second.substr(sp + 1, e.second.find(' ', sp + 1) - sp - 1);
+            if (all || groups.find(grp) != std::string::npos) out.push_back(e.second);
+          }
+        }
+        bool ok = true;
+        for (auto& l : out) ok = ok && sendAll(fd, (l + "\n").data(), l.size() + 1, 1000);
+        char c;
+        if (!ok || stop || (waitFd(fd, POLLIN, 200) && recv(fd, &c, 1, MSG_DONTWAIT) == 0)) break;
+      }
+      break;
     } else if (line.empty()) break;
     else { const char* e = "ERROR: unknown command\n"; sendAll(fd, e, strlen(e), 1000); }
   }
@@ -438,12 +482,21 @@ void rasCommAdd(ncclComm* comm) {
     }
   }
   gRas.comms.push_back(rec);
+  char h[32];
+  snprintf(h, sizeof(h), "%llx", (unsigned long long)rec.hash);
+  eventLocked("lifecycle", std::string("communicator ") + h + " rank " + std::to_string(rec.rank) + " of " + std::to_string(rec.nRanks) + " created");
 }
 
 void rasCommRemove(ncclComm* comm) {
   std::lock_guard<std::mutex> g(gRas.lock);
   for (size_t i = 0; i < gRas.comms.size(); ++i)
-    if (gRas.comms[i].comm == comm) { gRas.comms.erase(gRas.comms.begin() + i); break; }
+    if (gRas.comms[i].comm == comm) {
+      char h[32];
+      snprintf(h, sizeof(h), "%llx", (unsigned long long)gRas.comms[i].hash);
+      eventLocked("lifecycle", std::string("communicator ") + h + " rank " + std::to_string(gRas.comms[i].rank) + " destroyed");
+      gRas.comms.erase(gRas.comms.begin() + i);
+      break;
+    }
 }
 
 void rasShutdown() {

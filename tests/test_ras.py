@@ -97,3 +97,43 @@ def test_dead_process_is_reported(tmp_path):
     assert rep["job"]["dead_processes"] == 1 and rep["job"]["processes"] == 2
     assert rep["communicators"][0]["status"] == "INCOMPLETE" and rep["communicators"][0]["missing_ranks"] == 1
     assert any("DEAD" in e for e in rep["errors"])
+
+
+def _monitor_rank(rank, nranks, uid, port):
+    from nccl_b200 import Communicator
+    comm = Communicator(nranks, rank, uid)
+    comm.all_reduce(np.ones(4, dtype=np.float32))
+    mon = None
+    if rank == 0:
+        mon = subprocess.Popen([NCCLRAS, "--host", "127.0.0.1", "--port", str(port), "--monitor=lifecycle"], stdout=subprocess.PIPE, text=True)
+        time.sleep(0.6)
+    comm.all_reduce(np.ones(4, dtype=np.float32))   # the monitor is connected before anything happens
+    sub = comm.split(0, rank)                        # every process creates and destroys a communicator
+    sub.all_reduce(np.ones(4, dtype=np.float32))
+    sub.destroy()
+    comm.all_reduce(np.ones(4, dtype=np.float32))
+    out = None
+    if rank == 0:
+        time.sleep(0.8)
+        mon.terminate()
+        out = mon.communicate(timeout=10)[0]
+    comm.all_reduce(np.ones(4, dtype=np.float32))
+    comm.destroy()
+    return out
+
+
+def test_monitor_mode_streams_events():
+    """ncclras --monitor keeps its connection and prints one line per event of the serving process."""
+    port = _free_port()
+    env = {"NCCL_B200_HOST_ONLY": "1", "NCCL_SOCKET_IFNAME": "lo", "NCCL_RAS_ADDR": "127.0.0.1:%d" % port}
+    res = run_ranks(_monitor_rank, 2, args=(port,), env=env, timeout=120)
+    lines = [l for l in res[0].splitlines() if l.strip()]
+    assert any(" lifecycle communicator " in l and l.endswith("created") for l in lines), lines
+    assert any(" lifecycle communicator " in l and l.endswith("destroyed") for l in lines), lines
+    assert all(float(l.split()[0]) > 1e9 for l in lines)   # every event carries its wall-clock time
+
+
+def test_client_options():
+    assert "--monitor" in subprocess.run([NCCLRAS, "--help"], capture_output=True, text=True).stdout
+    assert subprocess.run([NCCLRAS, "--version"], capture_output=True, text=True).stdout.startswith("ncclras ")
+    assert subprocess.run([NCCLRAS, "--no-such-option"], capture_output=True, text=True).returncode == 2
