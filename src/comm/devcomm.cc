@@ -14,6 +14,8 @@
 
 namespace b200 {
 
+ncclResult_t windowRegister(ncclComm_t comm, void* buff, size_t size, ncclWindow_t* win, int winFlags);   // mem/register.cc
+
 B200_PARAM(DevCommTimeoutMs, "B200_DEVCOMM_TIMEOUT_MS", 10000, "default budget of device-API waits (barriers, low-latency receives), milliseconds");
 
 struct DevCommState {
@@ -115,7 +117,7 @@ ncclResult_t ncclDevCommCreate(ncclComm_t comm, const ncclDevCommRequirements_t*
   ncclResult_t res = ncclMemAlloc(&st.buf, bytes);
   if (res != ncclSuccess) return res;
   if (cudaMemset(st.buf, 0, bytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) { (void)cudaGetLastError(); ncclMemFree(st.buf); return ncclUnhandledCudaError; }
-  res = ncclCommWindowRegister(comm, st.buf, bytes, &st.win, NCCL_WIN_COLL_SYMMETRIC);
+  res = windowRegister(comm, st.buf, bytes, &st.win, NCCL_WIN_COLL_SYMMETRIC);
   if (res != ncclSuccess || !st.win) { ncclMemFree(st.buf); return res != ncclSuccess ? res : ncclInternalError; }
   const size_t nPriv = (size_t)nBar + llBlocks + 4;
   if (cudaMalloc(&st.priv, nPriv * sizeof(uint32_t)) != cudaSuccess || cudaMemset(st.priv, 0, nPriv * sizeof(uint32_t)) != cudaSuccess) {

@@ -21,6 +21,9 @@ B200_PARAM(ScratchMb, "B200_SCRATCH_MB", 256, "Staging area of the resource wind
 B200_PARAM(WaitTimeoutMs, "B200_WAIT_TIMEOUT_MS", 30000, "Budget of one device-side wait before the kernel gives up")
 B200_PARAM(MaxCtas, "MAX_CTAS", 0, "Upper bound on CTAs per collective kernel (0 = from the tuning table)")
 B200_PARAM(MinCtas, "MIN_CTAS", 0, "Lower bound on CTAs per collective kernel")
+B200_PARAM(MaxNChannels, "MAX_NCHANNELS", 0, "Older name of NCCL_MAX_CTAS (used when that is not set)")
+B200_PARAM(MinNChannels, "MIN_NCHANNELS", 0, "Older name of NCCL_MIN_CTAS (used when that is not set)")
+B200_PARAM(CtaPolicy, "CTA_POLICY", -1, "Overrides ncclConfig_t::CTAPolicy: 0 default, 1 efficiency (half the CTAs the table asks for), 2 zero (copy collectives on registered buffers use the copy engines: no SM)")
 B200_PARAM(LLThreshold, "B200_LL_THRESHOLD", -1, "All-reduce payloads up to this many bytes use the one-shot flagged-line kernel")
 B200_PARAM(NvlsThreshold, "B200_NVLS_THRESHOLD", -1, "All-reduce payloads from this many bytes use multimem")
 B200_PARAM(P2pDisable, "P2P_DISABLE", 0, "Never map peer memory; GPU buffers are staged through host sockets")
@@ -338,6 +341,10 @@ static int clampCtas(ncclComm* comm, size_t bytes, int cap) {
   DevicePlane* dp = comm->devPlane;
   if (tPickCtas > 0) cap = tPickCtas;
   int64_t envMax = paramMaxCtas(), envMin = paramMinCtas();
+  if (envMax <= 0) envMax = paramMaxNChannels();
+  if (envMin <= 0) envMin = paramMinNChannels();
+  const int policy = paramCtaPolicy() >= 0 ? (int)paramCtaPolicy() : comm->config.CTAPolicy;
+  if ((policy & NCCL_CTA_POLICY_EFFICIENCY) && policy != NCCL_CONFIG_UNDEF_INT) { cap = std::max(1, cap / 2); if (tPickCtas > 0) tPickCtas = std::max(1, tPickCtas / 2); }
   if (comm->config.maxCTAs != NCCL_CONFIG_UNDEF_INT && comm->config.maxCTAs > 0) cap = std::min(cap, comm->config.maxCTAs);
   if (envMax > 0) cap = (int)std::min<int64_t>(cap, envMax);
   cap = std::min(cap, std::min(kMaxCtas, dp->smCount));
@@ -749,7 +756,9 @@ static ncclResult_t runCopyColl(ncclComm* comm, const Task& t) {
   if (wantSplit) modeForce = -1;
   if (modeForce >= 0 && (modeForce & MODE_BULK)) { bulk = true; modeForce &= ~MODE_BULK; }
   if (forced == ALGO_RING && t.func == FUNC_ALLGATHER) return ringTreeRun(comm, t, forced);
-  if (forced == ALGO_CE || (forced == ALGO_AUTO && dp->tune.ceMin && B >= dp->tune.ceMin)) {
+  const int ctaPolicy = paramCtaPolicy() >= 0 ? (int)paramCtaPolicy() : comm->config.CTAPolicy;
+  const bool zeroSm = ctaPolicy != NCCL_CONFIG_UNDEF_INT && (ctaPolicy & NCCL_CTA_POLICY_ZERO) && forced == ALGO_AUTO && B >= ((size_t)1 << 20);
+  if (forced == ALGO_CE || zeroSm || (forced == ALGO_AUTO && dp->tune.ceMin && B >= dp->tune.ceMin)) {
     bool handled = false;
     NCCLCHECK(ceCollRun(comm, t, &handled));
     if (handled) return ncclSuccess;

@@ -1,6 +1,8 @@
 // Logging: NCCL_DEBUG level, NCCL_DEBUG_SUBSYS mask, NCCL_DEBUG_FILE (%h host, %p pid),
 // optional timestamps. Reference parity: src/debug.cc:45-110,197-220 (same env names,
 // same "host:pid:tid [dev] NCCL LEVEL msg" line shape).
+#include <pthread.h>
+#include <time.h>
 #include <errno.h>
 #include <stdarg.h>
 #include <stdio.h>
@@ -9,6 +11,7 @@
 #include <unistd.h>
 
 #include <mutex>
+#include <string>
 
 #include "core.h"
 
@@ -20,7 +23,9 @@ static uint64_t gMask = SUB_INIT | SUB_BOOTSTRAP | SUB_ENV;
 static FILE* gFile = nullptr;
 static char gHost[256];
 static int gPid;
-static bool gTimestamps = false;
+// which levels carry a time stamp (bit = LogLevel value), and its strftime format
+static uint32_t gTsLevels = 1u << LOG_WARN;
+static std::string gTsFormat = "[%F %T] ";
 static std::mutex gLock;
 static char gLastError[1024] = "";
 static thread_local char tName[32] = "";
@@ -74,8 +79,60 @@ static void initOnce() {
     FILE* fp = fopen(out.c_str(), "w");
     if (fp) { setvbuf(fp, nullptr, _IOLBF, 0); gFile = fp; }
   }
-  const char* ts = getenv("NCCL_DEBUG_TIMESTAMP_LEVELS");
-  gTimestamps = ts && *ts && strcasecmp(ts, "NONE") != 0;
+  // NCCL_DEBUG_TIMESTAMP_LEVELS: comma list of VERSION, WARN, INFO, ABORT, TRACE or ALL; ^ inverts; empty = none; default WARN
+  gTsLevels = 1u << LOG_WARN;
+  if (const char* ts = getenv("NCCL_DEBUG_TIMESTAMP_LEVELS")) {
+    const bool invert = *ts == '^';
+    uint32_t m = 0;
+    std::string list(ts + (invert ? 1 : 0));
+    size_t pos = 0;
+    while (pos <= list.size()) {
+      size_t c = list.find(',', pos);
+      std::string w = list.substr(pos, c == std::string::npos ? std::string::npos : c - pos);
+      if (!strcasecmp(w.c_str(), "ALL")) m = ~0u;
+      else if (!strcasecmp(w.c_str(), "VERSION")) m |= 1u << LOG_VERSION;
+      else if (!strcasecmp(w.c_str(), "WARN")) m |= 1u << LOG_WARN;
+      else if (!strcasecmp(w.c_str(), "INFO")) m |= 1u << LOG_INFO;
+      else if (!strcasecmp(w.c_str(), "TRACE")) m |= 1u << LOG_TRACE;
+      else if (!strcasecmp(w.c_str(), "ABORT")) m |= 1u << LOG_ABORT;
+      if (c == std::string::npos) break;
+      pos = c + 1;
+    }
+    gTsLevels = invert ? ~m : m;
+  }
+  // NCCL_DEBUG_TIMESTAMP_FORMAT: a strftime format (local time; TZ changes the zone); %Nf with N = 1..9 prints N digits of
+  // the fraction of the second; underscores become spaces; set but empty = no time stamp
+  gTsFormat = "[%F %T] ";
+  if (const char* tf = getenv("NCCL_DEBUG_TIMESTAMP_FORMAT")) {
+    gTsFormat = tf;
+    for (char& ch : gTsFormat) if (ch == '_') ch = ' ';
+  }
+}
+
+// Formats the time stamp of a log line of `level` into out (empty when that level carries none).
+static void formatStamp(int level, char* out, size_t len) {
+  out[0] = 0;
+  if (!(gTsLevels & (1u << level)) || gTsFormat.empty()) return;
+  struct timespec ts;
+  clock_gettime(CLOCK_REALTIME, &ts);
+  // expand %Nf ourselves, hand the rest to strftime
+  std::string fmt;
+  for (size_t i = 0; i < gTsFormat.size(); ++i) {
+    if (gTsFormat[i] == '%' && i + 2 < gTsFormat.size() && gTsFormat[i + 1] >= '1' && gTsFormat[i + 1] <= '9' && gTsFormat[i + 2] == 'f') {
+      char frac[16];
+      snprintf(frac, sizeof(frac), "%09ld", ts.tv_nsec);
+      fmt.append(frac, (size_t)(gTsFormat[i + 1] - '0'));
+      i += 2;
+    } else if (gTsFormat[i] == '%' && i + 1 < gTsFormat.size() && gTsFormat[i + 1] == '%') {
+      fmt += "%%";
+      ++i;
+    } else {
+      fmt += gTsFormat[i];
+    }
+  }
+  struct tm tmv;
+  localtime_r(&ts.tv_sec, &tmv);
+  if (strftime(out, len, fmt.c_str(), &tmv) == 0) out[0] = 0;
 }
 
 int debugLevel() {
@@ -99,6 +156,13 @@ void setThreadName(const char* fmt, ...) {
   va_start(ap, fmt);
   vsnprintf(tName, sizeof(tName), fmt, ap);
   va_end(ap);
+  // NCCL_SET_THREAD_NAME=1: the operating system sees the name too (debuggers, top -H); 15 characters at most
+  static const bool visible = [] { const char* e = getenv("NCCL_SET_THREAD_NAME"); return e && atoi(e) != 0; }();
+  if (visible) {
+    char shortName[16];
+    snprintf(shortName, sizeof(shortName), "%s", tName);
+    pthread_setname_np(pthread_self(), shortName);
+  }
 }
 
 void debugLog(LogLevel level, uint64_t subsys, const char* file, int line, const char* fmt, ...) {
@@ -119,12 +183,8 @@ void debugLog(LogLevel level, uint64_t subsys, const char* file, int line, const
   // cudaGetDevice is cheap and never initialises a context; ignore errors on GPU-less hosts.
   if (cudaGetDevice(&dev) != cudaSuccess) { (void)cudaGetLastError(); dev = -1; }
   long tid = syscall(SYS_gettid);
-  char stamp[48] = "";
-  if (gTimestamps) {
-    struct timeval tv;
-    gettimeofday(&tv, nullptr);
-    snprintf(stamp, sizeof(stamp), "[%ld.%06ld] ", (long)tv.tv_sec, (long)tv.tv_usec);
-  }
+  char stamp[96];
+  formatStamp((int)level, stamp, sizeof(stamp));
   const char* base = strrchr(file, '/');
   base = base ? base + 1 : file;
   std::lock_guard<std::mutex> g(gLock);

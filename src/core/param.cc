@@ -123,6 +123,24 @@ static ParamRegistrar kStrParams[] = {
     {{"NCCL_PROXY_DUMP_SIGNAL", PT_STR, "", "Signal number on which proxy threads log their operations in flight", true}},
     {{"NCCL_NET", PT_STR, "", "Insist on one network backend by name (a plugin's name, or Socket)", true}},
     {{"NCCL_PARAM_DUMP_ALL", PT_BOOL, "0", "Include undocumented parameters in ncclParamDumpAll", true}},
+    {{"NCCL_DEBUG_TIMESTAMP_LEVELS", PT_STR, "WARN", "Log levels that carry a time stamp: comma list of VERSION, WARN, INFO, ABORT, TRACE or ALL; ^ inverts; empty = none", true}},
+    {{"NCCL_DEBUG_TIMESTAMP_FORMAT", PT_STR, "[%F %T] ", "strftime format of the time stamp (local time); %Nf prints N digits of the fraction of the second; underscores become spaces", true}},
+    {{"NCCL_SET_THREAD_NAME", PT_BOOL, "0", "Give the library's threads (proxy, RAS, bootstrap root, init) names the operating system shows", true}},
+    {{"NCCL_RAS_ADDR", PT_STR, "localhost:28028", "Address of the RAS client socket (host:port)", true}},
+    {{"NCCL_SOCKET_FAMILY", PT_STR, "", "AF_INET or AF_INET6: address family of bootstrap and socket-network interfaces", true}},
+    {{"NCCL_P2P_LEVEL", PT_STR, "PHB", "Farthest path class over which GPUs use peer access: LOC, NVL, NVB, PIX, PXB, PXN, PHB, SYS", true}},
+    {{"NCCL_CROSS_NIC", PT_STR, "", "Whether a ring may leave through another NIC than it entered by (channel search for jobs that span nodes): 0, 1 or 2", true}},
+    {{"NCCL_GIN_TYPE", PT_STR, "", "Backend of the GPU-initiated put / signal surface: NONE (peer stores from the kernel) or PROXY (descriptors served by a host thread)", true}},
+    {{"NCCL_PROFILE_EVENT_MASK", PT_STR, "", "Bit mask of the event types handed to the profiler plugin (overrides what the plugin asks for)", true}},
+    // variables of the reference that configure parts this build does not have: accepted and ignored, listed so that a job
+    // script written for the reference explains itself
+    {{"NCCL_IB_DISABLE", PT_STR, "", "No effect: there is no InfiniBand verbs backend (external network plugins load through NCCL_NET_PLUGIN); the same holds for every NCCL_IB_* variable", true}},
+    {{"NCCL_NET_GDR_LEVEL", PT_STR, "", "No effect: the built-in socket backend stages through host memory; a plugin decides about GPUDirect itself", true}},
+    {{"NCCL_MNNVL_ENABLE", PT_STR, "", "No effect: the data plane serves one node (one NVLink domain of up to 8 GPUs)", true}},
+    {{"NCCL_NTHREADS", PT_STR, "", "No effect: the kernels' CTA sizes are fixed per kernel (512 threads, 32 for the bulk-copy forms)", true}},
+    {{"NCCL_BUFFSIZE", PT_STR, "", "No effect: there are no per-channel FIFO buffers; NCCL_B200_SCRATCH_MB sizes the staging area for unregistered buffers", true}},
+    {{"NCCL_LAUNCH_MODE", PT_STR, "", "No effect: every rank launches its own kernels (one process or thread per GPU)", true}},
+    {{"NCCL_RUNTIME_CONNECT", PT_STR, "", "No effect: the symmetric resource window is mapped when the communicator is created", true}},
 };
 
 }  // namespace b200

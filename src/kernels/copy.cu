@@ -650,6 +650,8 @@ const void* p2pKernelFn() { return (const void*)p2pKernel; }
 const void* signalKernelFn() { return (const void*)signalKernel; }
 const void* waitSignalKernelFn() { return (const void*)waitSignalKernel; }
 
+B200_PARAM(MemSyncDomain, "MEM_SYNC_DOMAIN", 1, "Memory synchronisation domain of the communication kernels: 1 = remote (their fences do not wait for the traffic of compute kernels), 0 = default")
+
 ncclResult_t launchKernel(const void* fn, dim3 grid, dim3 block, size_t smem, void* argStruct, cudaStream_t stream,
                           bool cooperative, bool pdl) {
   cudaLaunchConfig_t cfg = {};
@@ -670,9 +672,9 @@ ncclResult_t launchKernel(const void* fn, dim3 grid, dim3 block, size_t smem, vo
     ++na;
   }
   // stores to peers are ordered in the "remote" memory-synchronisation domain so that fences of
-  // this kernel do not wait for unrelated local traffic of concurrent compute kernels
+  // this kernel do not wait for unrelated local traffic of concurrent compute kernels (NCCL_MEM_SYNC_DOMAIN=0: default domain)
   attrs[na].id = cudaLaunchAttributeMemSyncDomain;
-  attrs[na].val.memSyncDomain = cudaLaunchMemSyncDomainRemote;
+  attrs[na].val.memSyncDomain = paramMemSyncDomain() ? cudaLaunchMemSyncDomainRemote : cudaLaunchMemSyncDomainDefault;
   ++na;
   cfg.attrs = attrs;
   cfg.numAttrs = na;

@@ -19,9 +19,28 @@ static ncclResult_t gpuComm(ncclComm_t comm, const char* what) {
   return ncclSuccess;
 }
 
+B200_PARAM(WinEnable, "WIN_ENABLE", 1, "0: ncclCommWindowRegister called by the application registers nothing and returns a null window (its buffers are then staged)")
+
+namespace b200 {
+// Window registration for the library's own needs (device communicators, ncclCommRegister): not subject to NCCL_WIN_ENABLE.
+ncclResult_t windowRegister(ncclComm_t comm, void* buff, size_t size, ncclWindow_t* win, int winFlags);
+}
+
 extern "C" {
 
 ncclResult_t ncclCommWindowRegister(ncclComm_t comm, void* buff, size_t size, ncclWindow_t* win, int winFlags) {
+  if (!win) return ncclInvalidArgument;
+  *win = nullptr;
+  if (!paramWinEnable()) {
+    NCCLCHECK(gpuComm(comm, "ncclCommWindowRegister"));
+    return ncclSuccess;
+  }
+  return b200::windowRegister(comm, buff, size, win, winFlags);
+}
+
+}  // extern "C"
+
+ncclResult_t b200::windowRegister(ncclComm_t comm, void* buff, size_t size, ncclWindow_t* win, int winFlags) {
   if (!win) return ncclInvalidArgument;
   *win = nullptr;
   NCCLCHECK(gpuComm(comm, "ncclCommWindowRegister"));
@@ -58,6 +77,8 @@ ncclResult_t ncclCommWindowRegister(ncclComm_t comm, void* buff, size_t size, nc
   return ncclSuccess;
 }
 
+extern "C" {
+
 ncclResult_t ncclCommWindowDeregister(ncclComm_t comm, ncclWindow_t win) {
   if (!win) return ncclSuccess;
   if (!commValid(comm)) return ncclInvalidArgument;
@@ -89,7 +110,7 @@ ncclResult_t ncclCommRegister(const ncclComm_t comm, void* buff, size_t size, vo
   // Registration is collective here as well: every rank registers its buffer in the same order,
   // which is how symmetric use of registered buffers is written anyway.
   uintptr_t base = (uintptr_t)buff & ~(uintptr_t)(NCCL_WIN_REQUIRED_ALIGNMENT - 1);
-  NCCLCHECK(ncclCommWindowRegister(comm, (void*)base, size + ((uintptr_t)buff - base), &win, NCCL_WIN_DEFAULT));
+  NCCLCHECK(b200::windowRegister(comm, (void*)base, size + ((uintptr_t)buff - base), &win, NCCL_WIN_DEFAULT));
   *handle = win;
   return ncclSuccess;
 }

@@ -117,3 +117,41 @@ print(os.path.exists(path) and "Init COMPLETE" in open(path).read())
 def test_reset_debug_init_rereads_the_environment(tmp_path):
     out = _child(RELOAD, {"LOG_PATH": str(tmp_path / "log.txt"), "NCCL_B200_HOST_ONLY": "1", "NCCL_DEBUG": ""})
     assert out.strip().endswith("True"), out
+
+
+WARN_ONCE = """
+import ctypes
+from nccl_b200 import _lib
+lib = _lib.load()
+w = ctypes.c_void_p()
+lib.ncclCommWindowRegister(None, None, 0, ctypes.byref(w), 0)   # invalid communicator: one WARN line
+"""
+
+
+def _warn_line(env):
+    e = {"NCCL_DEBUG": "WARN"}
+    e.update(env)
+    lines = [l for l in _child(WARN_ONCE, e).splitlines() if "NCCL WARN" in l]
+    assert len(lines) == 1, lines
+    return lines[0]
+
+
+def test_time_stamps_of_log_lines():
+    import re
+    # warnings carry a time stamp by default: local time, seconds
+    assert re.match(r"^\[\d{4}-\d\d-\d\d \d\d:\d\d:\d\d\] \S+:\d+:\d+ ", _warn_line({}))
+    # none at all
+    assert not _warn_line({"NCCL_DEBUG_TIMESTAMP_LEVELS": ""}).startswith("[")
+    assert not _warn_line({"NCCL_DEBUG_TIMESTAMP_LEVELS": "^WARN"}).startswith("[")
+    assert not _warn_line({"NCCL_DEBUG_TIMESTAMP_FORMAT": ""}).startswith("[")
+    assert _warn_line({"NCCL_DEBUG_TIMESTAMP_LEVELS": "INFO,WARN"}).startswith("[")
+    # own format: fraction of the second with %Nf, underscores become spaces
+    assert re.match(r"^<\d\d:\d\d:\d\d\.\d{3}> \S+:\d+", _warn_line({"NCCL_DEBUG_TIMESTAMP_FORMAT": "<%H:%M:%S.%3f>_"}))
+    assert re.match(r"^\d{9}\|", _warn_line({"NCCL_DEBUG_TIMESTAMP_FORMAT": "%9f|"}))
+
+
+def test_reference_variables_without_a_counterpart_are_listed():
+    out = subprocess.run([TOOL, "--all"], capture_output=True, text=True, timeout=60).stdout
+    for name in ("NCCL_IB_DISABLE", "NCCL_MNNVL_ENABLE", "NCCL_BUFFSIZE", "NCCL_MEM_SYNC_DOMAIN", "NCCL_CTA_POLICY", "NCCL_WIN_ENABLE",
+                 "NCCL_MAX_NCHANNELS", "NCCL_SET_THREAD_NAME", "NCCL_DEBUG_TIMESTAMP_FORMAT", "NCCL_CROSS_NIC", "NCCL_P2P_LEVEL", "NCCL_GIN_TYPE"):
+        assert name in out, name
