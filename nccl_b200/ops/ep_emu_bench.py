@@ -24,6 +24,7 @@ def main(argv=None):
     ap.add_argument("--fp8", type=int, default=1)
     ap.add_argument("--ctas", type=int, default=32, help="CTAs per emulated rank (ranks x ctas must fit the GPU)")
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--bulk", type=int, default=-1, help="1 / 0: dispatch through the bulk-copy engines or with the warps; -1: the library's default")
     a = ap.parse_args(argv)
     lib = _lib.load()
     pp = ctypes.POINTER(ctypes.c_void_p)
@@ -33,11 +34,13 @@ def main(argv=None):
     lib.b200EpEmuDispatch.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int), pp, pp, pp, pp, ctypes.POINTER(ctypes.POINTER(ctypes.c_int)), ctypes.c_int]
     lib.b200EpEmuCombine.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int), pp, pp, pp, pp, ctypes.c_int]
     lib.b200EpEmuLayout.argtypes = [ctypes.c_void_p, ctypes.c_int, pp, pp, pp]
+    lib.b200EpEmuBulk.argtypes = [ctypes.c_void_p, ctypes.c_int]
     n, E, K, H, T = a.ranks, a.experts, a.topk, a.hidden, a.tokens
     El, cap = E // n, n * T
     layout = {"expert_major": 0, "rank_major": 1, "flat": 2}[a.layout]
     ctx = lib.b200EpEmuCreate(n, E, K, H, T)
     assert ctx, "emulation context could not be created"
+    lib.b200EpEmuBulk(ctx, a.bulk)
     ptrs = lambda ts: (ctypes.c_void_p * len(ts))(*[t.data_ptr() for t in ts])  # noqa: E731
     g = torch.Generator(device="cuda").manual_seed(1)
     x = [torch.randn(T, H, device="cuda", generator=g).bfloat16() for _ in range(n)]
@@ -72,8 +75,8 @@ def main(argv=None):
         comb.append(e0.elapsed_time(e1) * 1e3)
     lib.b200EpEmuDestroy(ctx)
     recv = sum(sum(c) for c in counts)
-    print("emulated expert parallelism: ranks %d tokens %d hidden %d experts %d top-%d layout %s fp8 %d ctas %d: dispatch %.1f us, combine %.1f us "
-          "(best of %d; %d rows counted over all ranks)" % (n, T, H, E, K, a.layout, a.fp8, a.ctas, min(disp), min(comb), a.iters, recv))
+    print("emulated expert parallelism: ranks %d tokens %d hidden %d experts %d top-%d layout %s fp8 %d ctas %d bulk %d: dispatch %.1f us, combine %.1f us "
+          "(best of %d; %d rows counted over all ranks)" % (n, T, H, E, K, a.layout, a.fp8, a.ctas, a.bulk, min(disp), min(comb), a.iters, recv))
 
 
 if __name__ == "__main__":

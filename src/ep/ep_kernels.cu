@@ -19,6 +19,7 @@
 #include <cuda_fp8.h>
 
 #include "../kernels/common.cuh"
+#include "../tp/gemm_sm100.cuh"
 
 namespace b200 {
 
@@ -53,10 +54,23 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
 
   // ---------------------------------------------------------------- send
   const bool sendPhase = (a.phases & 1) != 0, recvPhase = (a.phases & 2) != 0;
-  for (int t = blockIdx.x; sendPhase && t < T; t += gridDim.x) {
+  // With bulkStages > 0 the packed token is written into one stage of a shared-memory ring and leaves through the bulk-copy
+  // engine (cp.async.bulk shared -> peer memory): lanes of warp 0 claim the slots, store the headers and issue one bulk store
+  // per destination; the warps go on to quantise the next token while earlier ones drain. A stage is reused once the bulk
+  // groups that read it have finished reading.
+  const int nStages = a.bulkStages > 0 ? a.bulkStages : 1;
+  const size_t stageBytes = a.bulkStages > 0 ? epStageBytes(H, a.fp8) : 0;
+  uint8_t* const smBase = (uint8_t*)(((uintptr_t)epSmem + 127) & ~(uintptr_t)127);
+  int iter = 0;
+  for (int t = blockIdx.x; sendPhase && t < T; t += gridDim.x, ++iter) {
+    uint8_t* const stage = smBase + (size_t)(iter % nStages) * stageBytes;
+    if (a.bulkStages > 0 && iter >= nStages) {
+      if (warp == 0) sm100::bulkWaitRead<kEpBulkStages - 1>();   // the groups of the token that used this stage have read it
+      __syncthreads();
+    }
     const __nv_bfloat16* row = x + (size_t)t * H;
     if (a.fp8) {
-      float* scales = (float*)(epSmem + H);
+      float* scales = (float*)(stage + H);
       for (int g = warp; g < H / 128; g += nWarps) {
         uint2 raw = *(const uint2*)(row + g * 128 + lane * 4);
         __nv_bfloat162 p0 = *(__nv_bfloat162*)&raw.x, p1 = *(__nv_bfloat162*)&raw.y;
@@ -70,13 +84,44 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
                           ((uint32_t)__nv_cvt_float_to_fp8(v1 * inv, __NV_SATFINITE, __NV_E4M3) << 8) |
                           ((uint32_t)__nv_cvt_float_to_fp8(v2 * inv, __NV_SATFINITE, __NV_E4M3) << 16) |
                           ((uint32_t)__nv_cvt_float_to_fp8(v3 * inv, __NV_SATFINITE, __NV_E4M3) << 24);
-        *(uint32_t*)(epSmem + g * 128 + lane * 4) = packed;
+        *(uint32_t*)(stage + g * 128 + lane * 4) = packed;
         if (lane == 0) scales[g] = scale;
       }
     } else {
-      for (int i = threadIdx.x; i < H / 8; i += kEpThreads) ((uint4*)epSmem)[i] = ((const uint4*)row)[i];
+      for (int i = threadIdx.x; i < H / 8; i += kEpThreads) ((uint4*)stage)[i] = ((const uint4*)row)[i];
     }
+    if (a.bulkStages > 0) sm100::fenceProxyAsync();   // the bulk-copy engine reads what the threads just wrote
     __syncthreads();
+    if (a.layout != EP_EXPERT_MAJOR && a.bulkStages > 0) {
+      // one copy per destination rank; lane d of warp 0 serves destination d
+      if (warp == 0) {
+        const size_t slotR = slotBytes + epMetaBytes(K);
+        const size_t zoneR = (size_t)(epoch & 1) * ((size_t)n * a.maxTokens * slotR);
+        if (lane < n && !(mask && mask[lane])) {
+          const int dst = lane;
+          bool any = false;
+          for (int k = 0; k < K; ++k) {
+            const long long e = a.topkIdx[rank][(size_t)t * K + k];
+            any = any || (e >= 0 && e < E && (int)(e / El) == dst);
+          }
+          int s = t;
+          if (any && a.layout == EP_FLAT) s = (int)atomicAdd(&st[kStCounters + dst], 1u);
+          if (any && s < a.maxTokens) {
+            char* slot = a.recvBuf[dst] + zoneR + ((size_t)rank * a.maxTokens + s) * slotR;
+            *(int4*)slot = make_int4(t, (int)epoch, 0, 0);
+            sm100::bulkStore(slot + 16, sm100::smemAddr(stage), (uint32_t)payload);
+            for (int k = 0; k < K; ++k) {
+              const long long e = a.topkIdx[rank][(size_t)t * K + k];
+              const bool local = e >= 0 && e < E && (int)(e / El) == dst;
+              const float wk = a.topkW[rank] ? a.topkW[rank][(size_t)t * K + k] : 0.0f;
+              *(int2*)(slot + slotBytes + (size_t)k * 8) = make_int2(local ? (int)e : -1, __float_as_int(wk));
+            }
+          }
+        }
+        sm100::bulkCommit();   // every lane, every token: the number of groups counts the tokens, which is what the stage reuse relies on
+      }
+      continue;
+    }
     if (a.layout != EP_EXPERT_MAJOR) {
       // one copy per destination rank: a warp per rank looks whether any of the token's experts lives there
       const size_t slotR = slotBytes + epMetaBytes(K);
@@ -100,11 +145,30 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
         if (s >= a.maxTokens) continue;
         char* slot = a.recvBuf[dst] + zoneR + ((size_t)rank * a.maxTokens + s) * slotR;
         if (lane == 0) *(int4*)slot = make_int4(t, (int)epoch, 0, 0);
-        for (size_t i = lane; i < payload / 16; i += 32) st16(slot + 16 + i * 16, ((const uint4*)epSmem)[i]);
+        for (size_t i = lane; i < payload / 16; i += 32) st16(slot + 16 + i * 16, ((const uint4*)stage)[i]);
         if (lane < K) *(int2*)(slot + slotBytes + (size_t)lane * 8) = make_int2(local ? (int)eK : -1, __float_as_int(wK));
       }
       __syncthreads();
       continue;
+    }
+    if (a.bulkStages > 0) {
+      // warp 0: lane k serves the token's k-th expert (slot claim, header, one bulk store)
+      if (warp == 0) {
+        const long long e = lane < K ? a.topkIdx[rank][(size_t)t * K + lane] : -1;
+        if (e >= 0 && e < E) {
+          const int dst = (int)(e / El), el = (int)(e % El);
+          if (!(mask && mask[dst])) {
+            const int s = (int)atomicAdd(&st[kStCounters + e], 1u);
+            if (s < a.maxTokens) {
+              char* slot = a.recvBuf[dst] + zoneOff + ((size_t)(el * n + rank) * a.maxTokens + s) * slotBytes;
+              *(int4*)slot = make_int4(t * K + lane, 0, 0, 0);
+              sm100::bulkStore(slot + 16, sm100::smemAddr(stage), (uint32_t)payload);
+            }
+          }
+        }
+        sm100::bulkCommit();   // every lane, every token (empty groups included): groups count tokens
+      }
+      continue;   // no barrier: the next token goes into another stage
     }
     for (int k = warp; k < K; k += nWarps) {
       const long long e = a.topkIdx[rank][(size_t)t * K + k];
@@ -117,10 +181,12 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
       if (s >= a.maxTokens) continue;   // cannot happen while numTokens <= maxTokens
       char* slot = a.recvBuf[dst] + zoneOff + ((size_t)(el * n + rank) * a.maxTokens + s) * slotBytes;
       if (lane == 0) *(int4*)slot = make_int4(t * K + k, 0, 0, 0);
-      for (size_t i = lane; i < payload / 16; i += 32) st16(slot + 16 + i * 16, ((const uint4*)epSmem)[i]);
+      for (size_t i = lane; i < payload / 16; i += 32) st16(slot + 16 + i * 16, ((const uint4*)stage)[i]);
     }
     __syncthreads();
   }
+  // everything this CTA handed to the bulk-copy engine has been written before the counts go out
+  if (a.bulkStages > 0 && sendPhase) sm100::bulkWaitAll();
   // every CTA of this rank must be done before the counts go out
   __syncthreads();
   if (threadIdx.x == 0) {

@@ -13,6 +13,8 @@ struct EpArgs {
   int maxTokens;                               // capacity: tokens a rank may dispatch per call
   int fp8;                                     // dispatch payload: 1 = e4m3 + one fp32 scale per 128 channels, 0 = bf16
   int layout;                                  // EP_EXPERT_MAJOR / EP_RANK_MAJOR / EP_FLAT (see below)
+  int bulkStages;                              // dispatch: > 0 = packed tokens leave through the bulk-copy engine from a ring of this many
+                                               // shared-memory stages (the warps only quantise); 0 = the warps store them
   int outSlots;                                // flat layout: rows of the output tensors (tokens beyond are dropped, the total is still reported)
   int numTokens[kMaxRanks];                    // tokens of rank r in this call
   // rank-private inputs
@@ -59,6 +61,10 @@ __host__ __device__ inline size_t epSlotBytes(int hidden, int fp8) {
   size_t b = fp8 ? (size_t)hidden + (size_t)(hidden / 128) * 4 : (size_t)hidden * 2;
   return (b + 16 + 15) / 16 * 16;              // payload + 16-byte header, 16-byte aligned
 }
+
+constexpr int kEpBulkStages = 4;
+// Bytes of one shared-memory stage of the dispatch kernel (one packed token, 128-byte aligned).
+__host__ __device__ inline size_t epStageBytes(int hidden, int fp8) { return (epSlotBytes(hidden, fp8) - 16 + 127) / 128 * 128; }
 
 const void* epDispatchKernelFn();
 const void* epCombineKernelFn();

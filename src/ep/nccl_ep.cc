@@ -88,7 +88,13 @@ static ncclResult_t launchEp(const void* fn, EpArgs* a, int ctas, int ranksY, si
   return launchKernel(fn, dim3(ctas, ranksY), dim3(512), smem, a, stream, coop);
 }
 
-static size_t dispatchSmem(int H, int fp8) { return fp8 ? (size_t)H + (size_t)(H / 128) * 4 + 16 : (size_t)H * 2; }
+B200_PARAM(EpBulk, "B200_EP_BULK", 1, "Expert-parallel dispatch hands the packed tokens to the bulk-copy engines (a ring of shared-memory stages per CTA) instead of storing them with the warps")
+
+// Dynamic shared memory of the dispatch kernel: one packed token, or the ring of stages of the bulk form.
+static size_t dispatchSmem(int H, int fp8, int bulkStages = 0) {
+  if (bulkStages > 0) return 128 + (size_t)bulkStages * epStageBytes(H, fp8);
+  return 128 + (fp8 ? (size_t)H + (size_t)(H / 128) * 4 + 16 : (size_t)H * 2);
+}
 
 extern "C" {
 
@@ -336,6 +342,7 @@ ncclResult_t ncclEpDispatch(ncclEpHandle_t h, const ncclEpDispatchInputs_t* in, 
   a.expertCount[me] = h->expertCount;
   a.srcInfo[me] = h->srcInfo;
   a.layout = h->layout == NCCL_EP_LAYOUT_RANK_MAJOR ? EP_RANK_MAJOR : h->layout == NCCL_EP_LAYOUT_FLAT ? EP_FLAT : EP_EXPERT_MAJOR;
+  a.bulkStages = paramEpBulk() ? kEpBulkStages : 0;
   a.outSlots = (int)outRows;
   a.outTopkIdx[me] = outIdx;
   a.outTopkW[me] = outW;
@@ -347,7 +354,7 @@ ncclResult_t ncclEpDispatch(ncclEpHandle_t h, const ncclEpDispatchInputs_t* in, 
   if (sendOnly) a.phases = 1;
   // the per-rank layouts count the tokens of every local expert with atomics while they unpack: start from zero
   if (a.layout != EP_EXPERT_MAJOR && !sendOnly) CUDACHECK(cudaMemsetAsync(h->expertCount, 0, (size_t)g->El * sizeof(int), stream));
-  NCCLCHECK(launchEp(epDispatchKernelFn(), &a, ctas, 1, dispatchSmem(g->H, fp8), stream, false));
+  NCCLCHECK(launchEp(epDispatchKernelFn(), &a, ctas, 1, dispatchSmem(g->H, fp8, a.bulkStages), stream, false));
   if (g->comm->devPlane) g->comm->devPlane->launches++;
   void* counters = (li && li->expert_counters && li->expert_counters->data) ? li->expert_counters->data : nullptr;
   if (sendOnly) {
@@ -356,7 +363,7 @@ ncclResult_t ncclEpDispatch(ncclEpHandle_t h, const ncclEpDispatchInputs_t* in, 
     h->pendingArgs = a;
     h->pendingArgs.phases = 2;
     h->pendingCtas = ctas;
-    h->pendingSmem = dispatchSmem(g->H, fp8);
+    h->pendingSmem = dispatchSmem(g->H, fp8, a.bulkStages);
     h->pendingCounters = counters;
     return ncclSuccess;
   }
@@ -497,6 +504,7 @@ struct EpEmu {
   uint32_t* mask[kMaxRanks];
   int phases = 3, enableMask = 0;
   int layout = 0;
+  int bulk = -1;                      // -1: as the parameter says
   long long* outIdx[kMaxRanks];
   float* outW[kMaxRanks];
   const float* inW[kMaxRanks];
@@ -510,6 +518,7 @@ void* b200EpEmuCreate(int n, int E, int K, int H, int maxTokens) {
   memset(e, 0, sizeof(*e));
   e->n = n; e->E = E; e->El = E / n; e->K = K; e->H = H; e->maxTokens = maxTokens;
   e->phases = 3;
+  e->bulk = -1;
   e->timeoutNs = 3000000000ull;
   size_t zone = (size_t)n * maxTokens * std::max((size_t)e->El * epSlotBytes(H, 0), epSlotBytes(H, 0) + epMetaBytes(16));
   size_t comb = (size_t)maxTokens * std::max(K, n) * H * 2;
@@ -553,6 +562,7 @@ static void emuArgs(EpEmu* e, EpArgs* a) {
   a->enableMask = e->enableMask;
   a->absent = e->absent;
   a->layout = e->layout;
+  a->bulkStages = (e->bulk < 0 ? paramEpBulk() != 0 : e->bulk != 0) ? kEpBulkStages : 0;
   a->outSlots = e->n * e->maxTokens;
   for (int r = 0; r < e->n; ++r) { a->outTopkIdx[r] = e->outIdx[r]; a->outTopkW[r] = e->outW[r]; a->topkW[r] = e->inW[r]; }
   a->sync.timeoutNs = e->timeoutNs;
@@ -581,6 +591,13 @@ int b200EpEmuLayout(void* ctx, int layout, void** outIdx, void** outW, void** in
   }
   return 0;
 }
+// 1 / 0: the following emulated dispatches use / do not use the bulk-copy engines; -1: as NCCL_B200_EP_BULK says.
+int b200EpEmuBulk(void* ctx, int bulk) {
+  EpEmu* e = (EpEmu*)ctx;
+  if (!e) return ncclInvalidArgument;
+  e->bulk = bulk;
+  return 0;
+}
 int b200EpEmuMask(void* ctx, int rank, unsigned int* out) {
   EpEmu* e = (EpEmu*)ctx;
   return cudaMemcpy(out, e->mask[rank], e->n * 4, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : 1;
@@ -604,7 +621,7 @@ int b200EpEmuDispatch(void* ctx, int fp8, const int* numTokens, void** x, void**
   }
   if (a.layout != EP_EXPERT_MAJOR && (a.phases & 2))
     for (int r = 0; r < e->n; ++r) cudaMemset(e->counts[r], 0, e->El * sizeof(int));
-  ncclResult_t res = launchEp(epDispatchKernelFn(), &a, ctas, e->n, dispatchSmem(e->H, fp8), 0, true);
+  ncclResult_t res = launchEp(epDispatchKernelFn(), &a, ctas, e->n, dispatchSmem(e->H, fp8, a.bulkStages), 0, true);
   if (res != ncclSuccess) return res;
   if (cudaDeviceSynchronize() != cudaSuccess) return ncclUnhandledCudaError;
   for (int r = 0; r < e->n; ++r) cudaMemcpy(countsOut[r], e->counts[r], e->El * sizeof(int), cudaMemcpyDeviceToHost);

@@ -26,13 +26,18 @@ def _ptrs(ts):
 
 @pytest.mark.parametrize("n,E,K,H,T", [(2, 4, 2, 128, 5), (4, 8, 2, 256, 16), (8, 32, 4, 512, 33), (8, 256, 8, 1024, 64)])
 @pytest.mark.parametrize("fp8", [0, 1])
-def test_dispatch_combine(n, E, K, H, T, fp8):
+@pytest.mark.parametrize("bulk", [1, 0])
+def test_dispatch_combine(n, E, K, H, T, fp8, bulk):
+    """bulk=1: the packed tokens leave through the bulk-copy engines from a ring of shared-memory stages (33 and 64
+    tokens over 4 CTAs wrap the ring several times); bulk=0: the warps store them."""
     if not torch.cuda.is_available():
         pytest.skip("needs a GPU")
     lib = _lib()
+    lib.b200EpEmuBulk.argtypes = [ctypes.c_void_p, ctypes.c_int]
     El, cap = E // n, n * T
     ctx = lib.b200EpEmuCreate(n, E, K, H, T)
     assert ctx
+    assert lib.b200EpEmuBulk(ctx, bulk) == 0
     g = torch.Generator().manual_seed(n * 1000 + E + K + fp8)
     try:
         for rep in range(3):   # landing zones alternate by call parity
@@ -195,7 +200,8 @@ def test_rank_that_never_joins_is_masked_out():
 @pytest.mark.parametrize("layout", [1, 2])
 @pytest.mark.parametrize("n,E,K,H,T", [(2, 4, 2, 128, 7), (4, 16, 4, 256, 16), (8, 64, 8, 512, 24)])
 @pytest.mark.parametrize("fp8", [0, 1])
-def test_rank_major_and_flat_layouts(layout, n, E, K, H, T, fp8):
+@pytest.mark.parametrize("bulk", [1, 0])
+def test_rank_major_and_flat_layouts(layout, n, E, K, H, T, fp8, bulk):
     """One copy of a token per destination rank (not per expert): rank-major puts it at row (source, token), flat packs
     the received tokens; the routing row travels with the token. The caller pre-reduces its local experts with the
     weights and combine sums one row per rank."""
@@ -203,9 +209,11 @@ def test_rank_major_and_flat_layouts(layout, n, E, K, H, T, fp8):
         pytest.skip("needs a GPU")
     lib = _lib2()
     lib.b200EpEmuLayout.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.POINTER(ctypes.c_void_p)] * 3
+    lib.b200EpEmuBulk.argtypes = [ctypes.c_void_p, ctypes.c_int]
     El, cap = E // n, n * T
     ctx = lib.b200EpEmuCreate(n, E, K, H, T)
     assert ctx
+    assert lib.b200EpEmuBulk(ctx, bulk) == 0
     g = torch.Generator().manual_seed(77 + layout + n)
     try:
         for rep in range(3):
