@@ -33,6 +33,7 @@ __device__ __forceinline__ void stReleaseSys64(unsigned long long* p, unsigned l
 __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_constant__ EpArgs a) {
   extern __shared__ uint8_t epSmem[];   // one packed token: payload (+ scales)
   __shared__ int sCnt[kMaxRanks], sOff[kMaxRanks + 1];
+  __shared__ int sCell[kEpMaxCells], sExpOff[kEpMaxLocalExperts + 1];   // expert-major receive: per (expert, source) and per expert
   __shared__ int sIsLast;
   const int rank = ctaRank(a.emu, a.rank);
   if (a.emu && ((a.absent >> rank) & 1u)) return;   // a rank that never joins (tests of the waits that run out)
@@ -297,36 +298,58 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
       }
     }
   }
-  for (int el = blockIdx.x; a.layout == EP_EXPERT_MAJOR && el < El && ok; el += gridDim.x) {
-    if (threadIdx.x < n) {
-      const unsigned long long* c = a.recvCount[rank] + cntOff + (size_t)el * n + threadIdx.x;
+  if (a.layout == EP_EXPERT_MAJOR) {
+    // Every CTA waits for the counts of all (local expert, source) cells (the words are local), then the warps of ALL CTAs
+    // share the rows of all experts: the packing is spread over the whole grid, not over one CTA per expert.
+    const int cells = El * n;
+    for (int c = threadIdx.x; c < cells; c += kEpThreads) {
+      const int s = c % n;
+      const unsigned long long* cw = a.recvCount[rank] + cntOff + c;
       unsigned long long v = 0;
       int cnt = 0;
-      if (!(mask && mask[threadIdx.x])) {
+      if (!(mask && mask[s])) {
         const bool quiet = a.enableMask && mask;
-        bool got = boundedWait(w, WAIT_TILE, threadIdx.x, epoch, [&] { v = ldRelaxedSys64((const uint64_t*)c); return (uint32_t)(v >> 32) == epoch; }, !quiet);
-        fenceSys();
+        bool got = boundedWait(w, WAIT_TILE, (uint32_t)s, epoch, [&] { v = ldRelaxedSys64((const uint64_t*)cw); return (uint32_t)(v >> 32) == epoch; }, !quiet);
         if (got) cnt = (int)(uint32_t)v;
-        else if (quiet && !(a.sync.abortFlag && ldRelaxedSys(a.sync.abortFlag))) { mask[threadIdx.x] = 1; cnt = 0; }   // left out from now on; the call goes on without it
+        else if (quiet && !(a.sync.abortFlag && ldRelaxedSys(a.sync.abortFlag))) { mask[s] = 1; cnt = 0; }   // left out from now on; the call goes on without it
         else cnt = -1;
       }
-      sCnt[threadIdx.x] = cnt;
+      sCell[c] = cnt;
     }
+    fenceSys();   // acquire: the rows behind the counts
     __syncthreads();
     if (threadIdx.x == 0) {
       int off = 0;
-      for (int s = 0; s < n; ++s) { sOff[s] = off; off += sCnt[s] > 0 ? sCnt[s] : 0; if (sCnt[s] < 0) off = -1 << 30; }
-      sOff[n] = off;
-      if (off >= 0) a.expertCount[rank][el] = off;
+      bool bad = false;
+      for (int el = 0; el < El; ++el) {
+        sExpOff[el] = off;
+        int inExp = 0;
+        for (int s = 0; s < n; ++s) {
+          const int c = sCell[el * n + s];
+          if (c < 0) bad = true;
+          sCell[el * n + s] = inExp;            // from now on: first row of this source inside the expert
+          inExp += c > 0 ? c : 0;
+        }
+        if (blockIdx.x == 0 && !bad) a.expertCount[rank][el] = inExp;
+        off += inExp;
+      }
+      sExpOff[El] = bad ? -1 : off;
     }
     __syncthreads();
-    ok = sOff[n] >= 0;
+    ok = sExpOff[El] >= 0;
     if (ok) {
-      const int total = sOff[n];
-      for (int pos = warp; pos < total; pos += nWarps) {
+      const int total = sExpOff[El];
+      for (int g = blockIdx.x * nWarps + warp; g < total; g += gridDim.x * nWarps) {
+        // which expert: the last one whose first row is <= g
+        int lo = 0, hi = El - 1;
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (sExpOff[mid] <= g) lo = mid; else hi = mid - 1;
+        }
+        const int el = lo, pos = g - sExpOff[el];
         int s = 0;
-        while (s + 1 < n && pos >= sOff[s + 1]) ++s;
-        const int j = pos - sOff[s];
+        while (s + 1 < n && pos >= sCell[el * n + s + 1]) ++s;
+        const int j = pos - sCell[el * n + s];
         const char* slot = a.recvBuf[rank] + zoneOff + ((size_t)(el * n + s) * a.maxTokens + j) * slotBytes;
         const size_t o = (size_t)el * cap + pos;
         if (lane == 0) a.srcInfo[rank][o] = make_int2(s, ((const int*)slot)[0]);
@@ -351,7 +374,6 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
         }
       }
     }
-    __syncthreads();
   }
   // the last CTA to finish closes the call
   __syncthreads();

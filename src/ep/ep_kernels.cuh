@@ -63,6 +63,8 @@ __host__ __device__ inline size_t epSlotBytes(int hidden, int fp8) {
 }
 
 constexpr int kEpBulkStages = 4;
+constexpr int kEpMaxLocalExperts = 256;   // experts per rank
+constexpr int kEpMaxCells = 2048;         // experts per rank x ranks
 // Bytes of one shared-memory stage of the dispatch kernel (one packed token, 128-byte aligned).
 __host__ __device__ inline size_t epStageBytes(int hidden, int fp8) { return (epSlotBytes(hidden, fp8) - 16 + 127) / 128 * 128; }
 

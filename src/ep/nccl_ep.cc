@@ -88,7 +88,7 @@ static ncclResult_t launchEp(const void* fn, EpArgs* a, int ctas, int ranksY, si
   return launchKernel(fn, dim3(ctas, ranksY), dim3(512), smem, a, stream, coop);
 }
 
-B200_PARAM(EpBulk, "B200_EP_BULK", 1, "Expert-parallel dispatch hands the packed tokens to the bulk-copy engines (a ring of shared-memory stages per CTA) instead of storing them with the warps")
+B200_PARAM(EpBulk, "B200_EP_BULK", 1, "Expert-parallel dispatch hands the packed tokens to the bulk-copy engines (a ring of shared-memory stages per CTA) instead of storing them with the warps: 0 never, 1 for the expert-major layout, 2 for every layout")
 
 // Dynamic shared memory of the dispatch kernel: one packed token, or the ring of stages of the bulk form.
 static size_t dispatchSmem(int H, int fp8, int bulkStages = 0) {
@@ -143,6 +143,7 @@ ncclResult_t ncclEpCreateGroup(ncclEpGroup_t* out, ncclComm_t comm, const ncclEp
   if (cfg->num_experts == 0 || cfg->num_experts % n) { WARN("ncclEpCreateGroup: %u experts do not divide over %d ranks", cfg->num_experts, n); return ncclInvalidArgument; }
   if (cfg->max_token_bytes == 0 || (cfg->max_token_bytes / 2) % 128) { WARN("ncclEpCreateGroup: hidden size must be a multiple of 128"); return ncclInvalidArgument; }
   if (cfg->max_dispatch_tokens_per_rank == 0) return ncclInvalidArgument;
+  if ((int)cfg->num_experts / n > kEpMaxLocalExperts) { WARN("ncclEpCreateGroup: at most %d experts per rank", kEpMaxLocalExperts); return ncclInvalidArgument; }
   ncclEpGroup* g = new ncclEpGroup;
   g->comm = comm;
   g->cfg = *cfg;
@@ -342,7 +343,8 @@ ncclResult_t ncclEpDispatch(ncclEpHandle_t h, const ncclEpDispatchInputs_t* in, 
   a.expertCount[me] = h->expertCount;
   a.srcInfo[me] = h->srcInfo;
   a.layout = h->layout == NCCL_EP_LAYOUT_RANK_MAJOR ? EP_RANK_MAJOR : h->layout == NCCL_EP_LAYOUT_FLAT ? EP_FLAT : EP_EXPERT_MAJOR;
-  a.bulkStages = paramEpBulk() ? kEpBulkStages : 0;
+  // the rank-major / flat forms measured slower through the bulk engines (one lane per destination writes the routing rows)
+  a.bulkStages = (paramEpBulk() == 1 && a.layout == EP_EXPERT_MAJOR) || paramEpBulk() == 2 ? kEpBulkStages : 0;
   a.outSlots = (int)outRows;
   a.outTopkIdx[me] = outIdx;
   a.outTopkW[me] = outW;
@@ -513,7 +515,7 @@ struct EpEmu {
 };
 
 void* b200EpEmuCreate(int n, int E, int K, int H, int maxTokens) {
-  if (n < 1 || n > kMaxRanks || E % n || H % 128) return nullptr;
+  if (n < 1 || n > kMaxRanks || E % n || H % 128 || E / n > kEpMaxLocalExperts) return nullptr;
   EpEmu* e = new EpEmu;
   memset(e, 0, sizeof(*e));
   e->n = n; e->E = E; e->El = E / n; e->K = K; e->H = H; e->maxTokens = maxTokens;
@@ -562,7 +564,7 @@ static void emuArgs(EpEmu* e, EpArgs* a) {
   a->enableMask = e->enableMask;
   a->absent = e->absent;
   a->layout = e->layout;
-  a->bulkStages = (e->bulk < 0 ? paramEpBulk() != 0 : e->bulk != 0) ? kEpBulkStages : 0;
+  a->bulkStages = (e->bulk < 0 ? ((paramEpBulk() == 1 && e->layout == EP_EXPERT_MAJOR) || paramEpBulk() == 2) : e->bulk != 0) ? kEpBulkStages : 0;
   a->outSlots = e->n * e->maxTokens;
   for (int r = 0; r < e->n; ++r) { a->outTopkIdx[r] = e->outIdx[r]; a->outTopkW[r] = e->outW[r]; a->topkW[r] = e->inW[r]; }
   a->sync.timeoutNs = e->timeoutNs;
