@@ -2,10 +2,10 @@
 # Builds the reference's expert-parallel extension (contrib/nccl_ep) from a copy of the reference tree and the small
 # client baseline/ref_ep_bench.cu against it. Needs the core reference library already built into
 # baseline/_ref/build (see the design record). Output: baseline/_ref/ep/{libnccl_ep.so*, ref_ep_bench}.
-#   baseline/build_ref_ep.sh <reference-tree>
+#   baseline/build_ref_ep.sh [reference-tree]     (default: the directory "reference" next to this repository)
 set -e
-REF=${1:-/root/reference}
 ROOT=$(cd "$(dirname "$0")/.." && pwd)
+REF=${1:-$(dirname "$ROOT")/reference}
 WORK=$(mktemp -d)
 mkdir -p "$WORK/contrib" "$ROOT/baseline/_ref/ep"
 cp -r "$REF/makefiles" "$WORK/"

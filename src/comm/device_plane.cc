@@ -193,7 +193,7 @@ ncclResult_t devPlaneCreate(ncclComm* comm) {
       });
     }
   }
-  // every rank must reach the same verdict
+  // every rank must reach the same decision
   std::vector<int> oks(comm->nRanks, 0);
   oks[comm->rank] = usable;
   NCCLCHECK(bootstrapAllGather(comm->bootstrap, oks.data(), sizeof(int)));

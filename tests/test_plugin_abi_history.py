@@ -14,7 +14,8 @@ import pytest
 from mp_util import run_ranks
 from test_plugins import BASE, ROOT, _check, _rank
 
-REF = "/root/reference/plugins"
+# the reference tree, when it is checked out next to this repository (or named by NCCL_REFERENCE_DIR)
+REF = os.path.join(os.environ.get("NCCL_REFERENCE_DIR", os.path.join(os.path.dirname(ROOT), "reference")), "plugins")
 CUDA_INC = "/usr/local/cuda/include"
 
 pytestmark = pytest.mark.skipif(shutil.which("g++") is None, reason="needs a C++ compiler")
