@@ -244,3 +244,23 @@ EXPORT const ncclNet_v8_t ncclNetPlugin_v8 = {
 #error "UNIX_NET_ABI must be 8, 9, 10, 11 or 12"
 #endif
 #endif
+
+#ifdef UNIX_NET_GIN
+// With -DUNIX_NET_GIN the library also exports a table for GPU-initiated networking: enough of it for a loader to learn
+// what the plugin offers (one device, plain signals); the data entry points report that nothing is connected.
+#include "plugin/nccl_gin.h"
+static ncclResult_t gInit(void** ctx, uint64_t, ncclDebugLogger_t) { *ctx = (void*)1; return ncclSuccess; }
+static ncclResult_t gDevices(int* n) { *n = 1; return ncclSuccess; }
+static ncclResult_t gProps(ncclGinProperties_v14_t* p) { p->supportsStrongSignals = true; p->supportsVASignals = false; return ncclSuccess; }
+static ncclResult_t gNetProps(int dev, ncclNetProperties_t* p) { return nProps(dev, p); }
+static ncclResult_t gListen(void*, int, void*, void**) { return ncclInternalError; }
+static ncclResult_t gConnect(void*, void*[], int, int, void*, void**) { return ncclInternalError; }
+static ncclResult_t gCreate(void*, ncclGinConfig_v14_t*, void**, void**) { return ncclInternalError; }
+static ncclResult_t gReg(void*, void*, size_t, int, uint64_t, void**, void**) { return ncclInternalError; }
+static ncclResult_t gRegDma(void*, void*, size_t, int, uint64_t, int, uint64_t, void**, void**) { return ncclInternalError; }
+static ncclResult_t gClose(void*) { return ncclSuccess; }
+static ncclResult_t gDeReg(void*, void*) { return ncclSuccess; }
+static ncclResult_t gErr(void*, bool* e) { *e = false; return ncclSuccess; }
+EXPORT const ncclGin_v14_t ncclGinPlugin_v14 = {"UnixExampleGin", gInit, gDevices, gProps, gNetProps, gListen, gConnect, gCreate, gReg, gRegDma, gDeReg,
+                                                gClose, gClose, gClose, gClose, gErr, gClose};
+#endif

@@ -10,6 +10,7 @@
 #include "comm.h"
 #include "device_plane.h"
 #include "../contrib/gin_proxy.h"
+#include "../plugin/plugin.h"
 #include "nccl_device/core.h"
 
 namespace b200 {
@@ -48,7 +49,10 @@ ncclResult_t ncclCommQueryProperties(ncclComm_t comm, ncclCommProperties_t* prop
   props->multimemSupport = lsa && comm->sym && comm->sym->mcUsable ? 1 : 0;
   // the put / signal surface can be served by a host proxy thread (inside the load/store domain); no device-driven NIC backend
   props->ginType = lsa ? NCCL_GIN_TYPE_PROXY : NCCL_GIN_TYPE_NONE;
-  props->railedGinType = NCCL_GIN_TYPE_NONE;
+  // a network plugin with a table for GPU-initiated networking is reported here (its kind is the plugin's business: the
+  // proxy kind is the conservative answer); nothing in this build hands traffic to it
+  const GinPluginInfo* gp = comm->nNodes > 1 ? netGinPluginInfo() : nullptr;
+  props->railedGinType = gp && gp->present && gp->devices > 0 ? NCCL_GIN_TYPE_PROXY : NCCL_GIN_TYPE_NONE;
   props->nLsaTeams = lsa ? 1 : comm->nNodes;
   props->hostRmaSupport = 1;   // ncclPutSignal / ncclSignal / ncclWaitSignal
   return ncclSuccess;

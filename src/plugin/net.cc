@@ -6,6 +6,7 @@
 
 #include "../transport/net.h"
 #include "plugin.h"
+#include "plugin/nccl_gin.h"
 
 namespace b200 {
 
@@ -13,6 +14,9 @@ static std::once_flag gNetOnce;
 static ncclNet_t* gNet = nullptr;
 static bool gNetExternal = false;
 static ncclCollNet_t* gCollNet = nullptr;
+// A table for GPU-initiated networking in the network plugin library: initialised once to learn what it offers (devices,
+// signal kinds); this build has no network to hand it (one NVLink domain), so it is reported and finalised.
+static GinPluginInfo gGin;
 
 ncclResult_t netSelect(ncclNet_t** net, bool* external) {
   std::call_once(gNetOnce, [] {
@@ -27,6 +31,25 @@ ncclResult_t netSelect(ncclNet_t** net, bool* external) {
     }
     gCollNet = lib ? (ncclCollNet_t*)pluginSymbol(lib, NCCL_COLLNET_PLUGIN_SYMBOL) : nullptr;
     if (gCollNet) INFO(SUB_NET | SUB_INIT, "net plugin %s offers the collective network %s", resolved.c_str(), gCollNet->name ? gCollNet->name : "?");
+    if (ncclGin_t* gin = lib ? (ncclGin_t*)pluginSymbol(lib, NCCL_GIN_PLUGIN_SYMBOL) : nullptr) {
+      void* gctx = nullptr;
+      int ndev = 0;
+      ncclGinProperties_t gp = {false, false};
+      if (gin->init && gin->init(&gctx, 0, pluginLogger) == ncclSuccess) {
+        if (gin->devices) gin->devices(&ndev);
+        if (gin->getGinProperties) gin->getGinProperties(&gp);
+        if (gin->finalize) gin->finalize(gctx);
+        gGin.present = true;
+        gGin.name = gin->name ? gin->name : "?";
+        gGin.devices = ndev;
+        gGin.strongSignals = gp.supportsStrongSignals;
+        gGin.vaSignals = gp.supportsVASignals;
+        INFO(SUB_NET | SUB_INIT, "net plugin %s offers GPU-initiated networking %s: %d device(s), strong signals %d, VA signals %d; not used: this build moves GPU-initiated traffic inside one NVLink domain",
+             resolved.c_str(), gGin.name.c_str(), ndev, (int)gp.supportsStrongSignals, (int)gp.supportsVASignals);
+      } else {
+        WARN("net plugin %s: %s failed to initialise", resolved.c_str(), NCCL_GIN_PLUGIN_SYMBOL);
+      }
+    }
     if (lib && !ext && gCollNet) INFO(SUB_NET | SUB_INIT, "net plugin %s has no point-to-point table (%s): point-to-point traffic stays on the built-in backend", resolved.c_str(), NCCL_NET_PLUGIN_SYMBOL);
     else if (lib && !ext) WARN("net plugin %s exports none of ncclNetPlugin_v12 ... ncclNetPlugin_v8; using the built-in backend", resolved.c_str());
     if (ext && wantName && *wantName && strcasecmp(wantName, ext->name) != 0 && strcasecmp(wantName, netSocketBackend.name) == 0) ext = nullptr;
@@ -51,6 +74,12 @@ ncclResult_t netSelect(ncclNet_t** net, bool* external) {
   *net = gNet;
   if (external) *external = gNetExternal;
   return gNet ? ncclSuccess : ncclInternalError;
+}
+
+const GinPluginInfo* netGinPluginInfo() {
+  ncclNet_t* net;
+  if (netSelect(&net, nullptr) != ncclSuccess) return nullptr;
+  return &gGin;
 }
 
 ncclCollNet_t* netCollNetTable() {

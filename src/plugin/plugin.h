@@ -30,6 +30,15 @@ void pluginLogger(ncclDebugLogLevel level, unsigned long flags, const char* file
 // ---- net plugin of an earlier interface (v11 ... v8): adapter with the current signature, or null (net_compat.cc)
 ncclNet_t* netCompatWrap(void* lib, int* version);
 
+// ---- table for GPU-initiated networking found in the network plugin library (net.cc): what it reported
+struct GinPluginInfo {
+  bool present = false;
+  std::string name;
+  int devices = 0;
+  bool strongSignals = false, vaSignals = false;
+};
+const GinPluginInfo* netGinPluginInfo();
+
 // ---- env plugin: consulted by every parameter read (core/param.cc)
 void envPluginInit();                       // idempotent; called before the first parameter is read
 const char* envPluginGet(const char* name); // value from the plugin, or from getenv() when none is loaded

@@ -173,3 +173,20 @@ def test_proxy_state_dump_on_signal(tmp_path):
     assert res[0] == 3.0 and res[1] == 3.0
     logs = "".join(open(os.path.join(tmp_path, p)).read() for p in os.listdir(tmp_path))
     assert "proxy state of rank 0" in logs and "recv from peer 1" in logs
+
+
+def test_gpu_initiated_networking_table_is_reported(tmp_path):
+    """A network plugin library that also exports a table for GPU-initiated networking: the loader initialises it,
+    reports what it offers and leaves the traffic where it is."""
+    import shutil
+    import subprocess
+    if shutil.which("g++") is None:
+        pytest.skip("needs a C++ compiler")
+    so = str(tmp_path / "libunix_gin.so")
+    subprocess.check_call(["g++", "-std=c++17", "-O1", "-fPIC", "-shared", "-DUNIX_NET_GIN", "-I" + os.path.join(ROOT, "include"),
+                           "-I/usr/local/cuda/include", os.path.join(ROOT, "plugins", "net", "unix_net.cc"), "-o", so])
+    env = dict(BASE, NCCL_NET_PLUGIN=so, NCCL_DEBUG="INFO", NCCL_DEBUG_SUBSYS="NET,INIT", NCCL_DEBUG_FILE=str(tmp_path / "log.%p"))
+    _check(run_ranks(_rank, 2, args=(1,), env=env), 2)
+    logs = "".join(open(os.path.join(tmp_path, p)).read() for p in os.listdir(tmp_path) if p.startswith("log."))
+    assert "offers GPU-initiated networking UnixExampleGin: 1 device(s), strong signals 1, VA signals 0" in logs
+    assert "network backend: plugin UnixExample" in logs
