@@ -63,6 +63,8 @@ extern "C" ncclResult_t ncclAllReduceFromHost(const void* hostSend, void* hostRe
   if (!commValid(comm) || !hostSend || !hostRecv || !devSend || !devRecv) return ncclInvalidArgument;
   if ((int)type < 0 || (int)type >= ncclNumTypes) return ncclInvalidArgument;
   if (count == 0) return ncclSuccess;
+  NCCLCHECK(commEnsureReady(comm));
+  if (comm->hostOnly) { WARN("ncclAllReduceFromHost: needs a GPU communicator (a host-memory communicator reduces host buffers with ncclAllReduce itself)"); return ncclInvalidUsage; }
   if (groupDepth() > 0) {
     WARN("ncclAllReduceFromHost: not available between ncclGroupStart and ncclGroupEnd (its collectives must launch where they are issued)");
     return ncclInvalidUsage;

@@ -145,3 +145,26 @@ def test_scalable_init_with_two_roots():
     res = run_ranks(_scalable, n, env=ENV, make_uid=lambda: get_unique_id() + get_unique_id(), timeout=120)
     for r in range(n):
         assert res[r] == float(sum(range(n)))
+
+
+def _host_staged_rank(rank, nranks, uid):
+    import ctypes
+    import numpy as np
+    from nccl_b200 import Communicator
+    comm = Communicator(nranks, rank, uid)
+    buf = np.ones(16, dtype=np.float32)
+    fn = comm.lib.ncclAllReduceFromHost
+    fn.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_size_t, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
+    p = buf.ctypes.data
+    rc = fn(p, p, p, p, 16, 7, 0, comm.handle, None, 0)
+    comm.all_reduce(buf.copy(), buf)   # the communicator is still usable
+    comm.destroy()
+    return rc
+
+
+def test_host_staged_allreduce_needs_a_gpu_communicator():
+    """ncclAllReduceFromHost stages through device memory: a host-memory communicator refuses it (its own
+    ncclAllReduce already works on host buffers)."""
+    from mp_util import run_ranks
+    res = run_ranks(_host_staged_rank, 2, env={"NCCL_B200_HOST_ONLY": "1", "NCCL_SOCKET_IFNAME": "lo"})
+    assert res[0] == 5 and res[1] == 5   # ncclInvalidUsage
