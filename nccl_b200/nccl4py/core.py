@@ -196,6 +196,34 @@ class Communicator:
     def split(self, color, key=0, config=None):
         return self._wrap(self._c.split(-1 if color is None else color, key))
 
+    @classmethod
+    def init_all(cls, devices=None):
+        """One communicator per listed device of this process (all visible devices by default): ncclCommInitAll."""
+        lib = _lib.load()
+        if devices is None:
+            import torch
+            devices = list(range(torch.cuda.device_count()))
+        n = len(devices)
+        handles = (ctypes.c_void_p * n)()
+        lib.ncclCommInitAll.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
+        _lib.check(lib.ncclCommInitAll(handles, n, (ctypes.c_int * n)(*devices)), "ncclCommInitAll", lib)
+        return [cls._wrap(_core.Communicator(n, r, None, lib=lib, _handle=ctypes.c_void_p(handles[r]))) for r in range(n)]
+
+    def grow(self, nranks, unique_id=None, rank=-1, config=None):
+        """ncclCommGrow: the ranks of this communicator (which pass rank = -1 and, except the one that made it, no id)
+        and new ranks (which pass their rank and the id, on a communicator object without a parent) form a larger one."""
+        lib = _lib.load() if self._c is None else self._c.lib
+        new = ctypes.c_void_p()
+        uid = None
+        if unique_id is not None:
+            uid = _lib.ncclUniqueId.from_buffer_copy(bytes(unique_id))
+        lib.ncclCommGrow.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]
+        parent = self._c.handle if self._c is not None else None
+        _lib.check(lib.ncclCommGrow(parent, nranks, ctypes.byref(uid) if uid is not None else None, rank, ctypes.byref(new), None), "ncclCommGrow", lib)
+        r = ctypes.c_int()
+        lib.ncclCommUserRank(new, ctypes.byref(r))
+        return self._wrap(_core.Communicator(nranks, r.value, None, lib=lib, _handle=new))
+
     def shrink(self, exclude_ranks, config=None, flags=0):
         return self._wrap(self._c.shrink(list(exclude_ranks), abort=bool(flags)))
 
@@ -264,6 +292,35 @@ class Communicator:
         return d.value
 
     @property
+    def device(self):
+        """CUDA device ordinal of this rank (the reference returns a device object; the ordinal identifies it)."""
+        return self.cuda_dev
+
+    def _properties(self):
+        from ..ops.devapi import query_properties
+        return query_properties(self._c)
+
+    @property
+    def nvml_dev(self):
+        return self._properties()["nvmlDev"]
+
+    @property
+    def gin_type(self):
+        return self._properties()["ginType"]
+
+    @property
+    def railed_gin_type(self):
+        return self._properties()["railedGinType"]
+
+    @property
+    def n_lsa_teams(self):
+        return self._properties()["nLsaTeams"]
+
+    @property
+    def host_rma_support(self):
+        return bool(self._properties()["hostRmaSupport"])
+
+    @property
     def multimem_support(self):
         fn = self._c.lib.b200CommHasMulticast
         fn.argtypes = [ctypes.c_void_p]
@@ -295,6 +352,47 @@ class Communicator:
     def recv(self, recvbuf, peer, *, stream=None):
         self._check_valid("recv")
         self._c.recv(recvbuf, peer, stream=stream)
+
+    def put_signal(self, sendbuf, peer, peer_window, peer_offset=0, *, sig_idx=0, ctx=0, flags=0, stream=None):
+        """One-sided: copies ``sendbuf`` into ``peer``'s part of a registered window and bumps its signal ``sig_idx``."""
+        self._check_valid("put_signal")
+        ptr, n, dt, _ = _core.describe(sendbuf)
+        lib = self._c.lib
+        lib.ncclPutSignal.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int,
+                                      ctypes.c_int, ctypes.c_uint, ctypes.c_void_p, ctypes.c_void_p]
+        win = getattr(peer_window, "handle", peer_window)
+        _lib.check(lib.ncclPutSignal(ptr, n, dt, peer, win, peer_offset, sig_idx, ctx, flags, self._c.handle, _core._stream_of(sendbuf, stream)),
+                   "ncclPutSignal", lib)
+
+    def signal(self, peer, *, sig_idx=0, ctx=0, flags=0, stream=None):
+        self._check_valid("signal")
+        lib = self._c.lib
+        lib.ncclSignal.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_uint, ctypes.c_void_p, ctypes.c_void_p]
+        _lib.check(lib.ncclSignal(peer, sig_idx, ctx, flags, self._c.handle, _core._stream_of(None, stream)), "ncclSignal", lib)
+
+    def wait_signal(self, descs, *, stream=None):
+        """``descs``: iterable of (peer, op_count[, sig_idx[, ctx]]): waits until each peer has signalled that many times more."""
+        self._check_valid("wait_signal")
+
+        class _Desc(ctypes.Structure):
+            _fields_ = [("opCnt", ctypes.c_int), ("peer", ctypes.c_int), ("sigIdx", ctypes.c_int), ("ctx", ctypes.c_int)]
+
+        items = []
+        for d in descs:
+            d = tuple(d) + (0, 0)
+            items.append(_Desc(int(d[1]), int(d[0]), int(d[2]), int(d[3])))
+        arr = (_Desc * len(items))(*items)
+        lib = self._c.lib
+        lib.ncclWaitSignal.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        _lib.check(lib.ncclWaitSignal(len(items), arr, self._c.handle, _core._stream_of(None, stream)), "ncclWaitSignal", lib)
+
+    def create_dev_comm(self, **requirements):
+        """A device communicator for kernels written with the device API (``nccl_b200.ops.devapi.DeviceComm`` keywords:
+        barriers, ll_blocks, ll_slots, gin_signals, gin_counters, multimem)."""
+        from ..ops.devapi import DeviceComm
+        dc = DeviceComm(self._c, **requirements)
+        self._resources.append(type("DevCommResource", (), {"close": lambda s, d=dc: d.destroy()})())
+        return dc
 
     # ------------------------------------------------------------------ collectives
     def reduce(self, sendbuf, recvbuf, op, *, root=None, stream=None):

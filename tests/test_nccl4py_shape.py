@@ -47,3 +47,40 @@ def test_reference_binding_spelling_on_host_ranks():
         assert version >= 23000
         if r == 0:
             assert red == n * 4 - 1
+
+
+REFERENCE_METHODS = """init init_all initialize split shrink get_unique_id grow destroy abort finalize revoke suspend resume ptr is_valid nranks
+device rank cuda_dev nvml_dev device_api_support multimem_support gin_type n_lsa_teams host_rma_support railed_gin_type send recv wait_signal
+signal put_signal allreduce broadcast reduce allgather reduce_scatter alltoall gather scatter register_buffer register_window
+create_pre_mul_sum create_dev_comm close_all_resources get_last_error get_async_error get_mem_stat""".split()
+
+
+def test_every_public_name_of_the_reference_communicator_exists():
+    """The public methods and properties of the reference's ``nccl.core.Communicator`` (listed above; re-read from the
+    reference tree when it is checked out next to this repository) all exist here under the same names."""
+    import os
+    import re
+    import nccl_b200.nccl4py.core as nccl
+    names = set(REFERENCE_METHODS)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = os.path.join(os.environ.get("NCCL_REFERENCE_DIR", os.path.join(os.path.dirname(root), "reference")), "bindings", "nccl4py", "nccl", "core",
+                       "communicator.py")
+    if os.path.exists(src):
+        names |= {m for m in re.findall(r"^    def ([a-z][a-z0-9_]*)\(", open(src).read(), re.M)}
+    missing = sorted(n for n in names if not hasattr(nccl.Communicator, n))
+    assert not missing, missing
+
+
+def _props_rank(rank, nranks, uid):
+    import nccl_b200.nccl4py.core as nccl
+    comm = nccl.Communicator.init(nranks, rank, nccl.UniqueId(uid))
+    out = (comm.n_lsa_teams, comm.gin_type, comm.railed_gin_type, comm.host_rma_support, comm.device_api_support)
+    comm.destroy()
+    return out
+
+
+def test_property_queries_on_host_ranks():
+    res = run_ranks(_props_rank, 2, env=BASE)
+    for r in range(2):
+        n_lsa, gin, railed, rma, devapi = res[r]
+        assert gin == 0 and railed == 0 and not devapi and n_lsa >= 1 and rma in (True, False)
