@@ -9,6 +9,8 @@ Programs written against the reference's bindings keep their spelling::
     with nccl.group():
         comm.send(a, peer=1); comm.recv(b, peer=1)
 
-Reference parity: bindings/nccl4py/nccl/core/{communicator,group,memory,utils,constants}.py.
+``nccl_b200.nccl4py.ep`` has the shapes of the reference's ``nccl.ep`` (groups, handles, tensor descriptors) and is imported on demand.
+
+Reference parity: bindings/nccl4py/nccl/core/{communicator,group,memory,utils,constants}.py, bindings/nccl4py/nccl/ep/.
 """
 from . import core  # noqa: F401

@@ -29,6 +29,18 @@ struct ncclEpGroup {
   int layoutClass = 0;                // 0 none yet, 1 expert-major, 2 per-rank (rank-major / flat)
 };
 
+// Buffers that only this rank touches come from the group's allocator hooks when the configuration gives them
+// (ncclEpGroupConfig_t::alloc); memory that peers map stays with the library's own allocator, which makes it exportable.
+static cudaError_t epAlloc(const ncclEpAllocConfig_t& a, void** p, size_t bytes) {
+  if (a.alloc_fn) return a.alloc_fn(p, bytes, a.context);
+  return cudaMalloc(p, bytes);
+}
+static void epFree(const ncclEpAllocConfig_t& a, void* p) {
+  if (!p) return;
+  if (a.alloc_fn) a.free_fn(p, a.context);
+  else cudaFree(p);
+}
+
 struct ncclEpHandle {
   ncclEpGroup* g = nullptr;
   ncclEpLayout_t layout;
@@ -38,6 +50,7 @@ struct ncclEpHandle {
   const float* topkW = nullptr;
   int2* srcInfo = nullptr;
   int* expertCount = nullptr;
+  ncclEpAllocConfig_t alloc = {};     // the group's hooks, kept here so that a handle can outlive its group's record
   // a send_only call leaves its receiving half to ncclEpComplete
   int pending = 0;                    // 0 nothing, 1 dispatch, 2 combine
   EpArgs pendingArgs;
@@ -143,6 +156,7 @@ ncclResult_t ncclEpCreateGroup(ncclEpGroup_t* out, ncclComm_t comm, const ncclEp
   if (cfg->num_experts == 0 || cfg->num_experts % n) { WARN("ncclEpCreateGroup: %u experts do not divide over %d ranks", cfg->num_experts, n); return ncclInvalidArgument; }
   if (cfg->max_token_bytes == 0 || (cfg->max_token_bytes / 2) % 128) { WARN("ncclEpCreateGroup: hidden size must be a multiple of 128"); return ncclInvalidArgument; }
   if (cfg->max_dispatch_tokens_per_rank == 0) return ncclInvalidArgument;
+  if ((cfg->alloc.alloc_fn == nullptr) != (cfg->alloc.free_fn == nullptr)) { WARN("ncclEpCreateGroup: alloc_fn and free_fn come as a pair"); return ncclInvalidArgument; }
   if ((int)cfg->num_experts / n > kEpMaxLocalExperts) { WARN("ncclEpCreateGroup: at most %d experts per rank", kEpMaxLocalExperts); return ncclInvalidArgument; }
   ncclEpGroup* g = new ncclEpGroup;
   g->comm = comm;
@@ -163,9 +177,9 @@ ncclResult_t ncclEpCreateGroup(ncclEpGroup_t* out, ncclComm_t comm, const ncclEp
   NCCLCHECK(memAlloc((void**)&g->ctl, ctlBytes(g->El, n), comm->cudaDev));
   CUDACHECK(cudaMemset(g->ctl, 0, ctlBytes(g->El, n)));
   CUDACHECK(cudaMemset(g->recvZone, 0, 2 * g->zoneBytes));   // rank-major rows are recognised by the epoch in their header: none is valid yet
-  CUDACHECK(cudaMalloc(&g->state, (8 + g->E) * sizeof(uint32_t)));
+  CUDACHECK(epAlloc(g->cfg.alloc, (void**)&g->state, (8 + g->E) * sizeof(uint32_t)));
   CUDACHECK(cudaMemset(g->state, 0, (8 + g->E) * sizeof(uint32_t)));
-  CUDACHECK(cudaMalloc(&g->mask, kMaxRanks * sizeof(uint32_t)));
+  CUDACHECK(epAlloc(g->cfg.alloc, (void**)&g->mask, kMaxRanks * sizeof(uint32_t)));
   CUDACHECK(cudaMemset(g->mask, 0, kMaxRanks * sizeof(uint32_t)));
   CUDACHECK(cudaDeviceSynchronize());
   if (n > 1) {
@@ -198,8 +212,8 @@ ncclResult_t ncclEpGroupDestroy(ncclEpGroup_t g) {
   if (g->recvZone) memFree(g->recvZone);
   if (g->ctl) memFree(g->ctl);
   if (g->combZone) memFree(g->combZone);
-  if (g->state) cudaFree(g->state);
-  if (g->mask) cudaFree(g->mask);
+  epFree(g->cfg.alloc, g->state);
+  epFree(g->cfg.alloc, g->mask);
   delete g;
   return ncclSuccess;
 }
@@ -242,9 +256,10 @@ ncclResult_t ncclEpInitHandle(ncclEpHandle_t* out, ncclEpGroup_t g, ncclEpLayout
   h->g = g;
   h->layout = layout;
   h->K = num_topk;
+  h->alloc = g->cfg.alloc;
   const size_t cap = (size_t)g->n * g->maxTokens;
-  CUDACHECK(cudaMalloc(&h->srcInfo, (size_t)g->El * cap * sizeof(int2)));
-  CUDACHECK(cudaMalloc(&h->expertCount, (size_t)g->El * sizeof(int)));
+  CUDACHECK(epAlloc(h->alloc, (void**)&h->srcInfo, (size_t)g->El * cap * sizeof(int2)));
+  CUDACHECK(epAlloc(h->alloc, (void**)&h->expertCount, (size_t)g->El * sizeof(int)));
   CUDACHECK(cudaMemset(h->expertCount, 0, (size_t)g->El * sizeof(int)));
   *out = h;
   return ncclSuccess;
@@ -270,8 +285,8 @@ ncclResult_t ncclEpCreateHandle(ncclEpHandle_t* out, ncclEpGroup_t g, ncclEpLayo
 ncclResult_t ncclEpHandleDestroy(ncclEpHandle_t h) {
   if (!h) return ncclSuccess;
   cudaDeviceSynchronize();
-  if (h->srcInfo) cudaFree(h->srcInfo);
-  if (h->expertCount) cudaFree(h->expertCount);
+  epFree(h->alloc, h->srcInfo);
+  epFree(h->alloc, h->expertCount);
   delete h;
   return ncclSuccess;
 }

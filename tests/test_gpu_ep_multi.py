@@ -112,3 +112,48 @@ def test_ep_layouts_with_one_copy_per_rank(layout):
         assert sum(res[r]["rows%d" % rep] for r in range(n)) <= n * T * min(K, n)
         for r in range(n):
             assert res[r]["err%d" % rep] < 0.03, (rep, r, res[r])
+
+
+def _ep_rank_bindings_shape(rank, nranks, uid, E, K, H, T):
+    """The same round trip written against the module with the reference bindings' call shapes."""
+    import torch
+    torch.cuda.set_device(rank)
+    import nccl_b200.nccl4py.core as nccl
+    import nccl_b200.nccl4py.ep as ep
+    comm = nccl.Communicator.init(nranks, rank, nccl.UniqueId(uid))
+    group = ep.Group.create(comm, ep.GroupConfig(num_experts=E, max_dispatch_tokens_per_rank=T, max_token_bytes=2 * H))
+    El, cap = E // nranks, nranks * T
+    stream = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator().manual_seed(rank)
+    x = torch.randn(T, H, generator=g).bfloat16().cuda()
+    idx = torch.rand(T, E, generator=g).topk(K, dim=1).indices.to(torch.int64).cuda()
+    w = torch.softmax(torch.randn(T, K, generator=g), dim=1).cuda()
+    toks = torch.empty(El, cap, H, dtype=torch.bfloat16, device="cuda")
+    counts = torch.zeros(El, dtype=torch.int32, device="cuda")
+    out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+    handle = group.create_handle(ep.Layout.EXPERT_MAJOR, ep.Tensor(idx), stream=stream)
+    handle.dispatch(ep.DispatchInputs(tokens=ep.Tensor(x), topk_weights=ep.Tensor(w)), ep.DispatchOutputs(tokens=ep.Tensor(toks)),
+                    layout_info=ep.LayoutInfo(expert_counters=ep.Tensor(counts)), config=ep.DispatchConfig(), stream=stream)
+    torch.cuda.synchronize()
+    for el in range(El):
+        toks[el] *= float(rank * El + el + 1)
+    handle.combine(ep.CombineInputs(tokens=ep.Tensor(toks)), ep.CombineOutputs(tokens=ep.Tensor(out)), config=ep.CombineConfig(), stream=stream)
+    torch.cuda.synchronize()
+    ref = x.float() * (w * (idx + 1).float()).sum(1, keepdim=True)
+    err = float(((out.float() - ref).abs() / (ref.abs() + 1.0)).max())
+    total = int(counts.sum())
+    handle.destroy()
+    group.destroy()
+    comm.destroy()
+    return err, total
+
+
+def test_ep_roundtrip_through_the_bindings_shaped_module():
+    n = min(torch.cuda.device_count() if torch.cuda.is_available() else 0, 8)
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    E, K, H, T = 8 * n, 4, 512, 64
+    res = run_ranks(_ep_rank_bindings_shape, n, args=(E, K, H, T), timeout=300)
+    assert sum(res[r][1] for r in range(n)) == n * T * K
+    for r in range(n):
+        assert res[r][0] < 0.03, res[r]

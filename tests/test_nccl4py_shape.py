@@ -84,3 +84,66 @@ def test_property_queries_on_host_ranks():
     for r in range(2):
         n_lsa, gin, railed, rma, devapi = res[r]
         assert gin == 0 and railed == 0 and not devapi and n_lsa >= 1 and rma in (True, False)
+
+
+EP_NAMES = """Algorithm AllocConfig AllocFn CombineConfig CombineInputs CombineOutputs DispatchConfig DispatchInputs DispatchOutputs FreeFn
+get_lib_path get_lib_version Group GroupConfig Handle HandleConfig Layout LayoutInfo PassDir Tensor""".split()
+
+
+def test_expert_parallel_module_has_the_reference_names():
+    """Every name the reference's ``nccl.ep`` exports exists in ``nccl_b200.nccl4py.ep``, with the same record fields and the
+    same methods on groups and handles (re-read from the reference tree when it is checked out next to this repository)."""
+    import dataclasses
+    import os
+    import re
+    import nccl_b200.nccl4py.ep as ep
+    names = set(EP_NAMES)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref = os.path.join(os.environ.get("NCCL_REFERENCE_DIR", os.path.join(os.path.dirname(root), "reference")), "bindings", "nccl4py", "nccl", "ep")
+    methods = {"Group": {"create", "create_handle", "destroy", "ptr"}, "Handle": {"update", "dispatch", "combine", "complete", "destroy", "ptr"}}
+    if os.path.isdir(ref):
+        m = re.search(r"__all__ = \[(.*?)\]", open(os.path.join(ref, "__init__.py")).read(), re.S)
+        names |= set(re.findall(r'"(\w+)"', m.group(1)))
+        for cls, f in (("Group", "group.py"), ("Handle", "handle.py")):
+            methods[cls] |= set(re.findall(r"^    def ([a-z][a-z0-9_]*)\(", open(os.path.join(ref, f)).read(), re.M))
+    assert not sorted(n for n in names if not hasattr(ep, n))
+    for cls, ms in methods.items():
+        assert not sorted(m for m in ms if not hasattr(getattr(ep, cls), m)), cls
+    assert [f.name for f in dataclasses.fields(ep.GroupConfig)] == ["algorithm", "num_experts", "max_dispatch_tokens_per_rank", "max_recv_tokens_per_rank",
+        "max_token_bytes", "rdma_buffer_size", "num_qp_per_rank", "num_channels", "max_num_sms", "alloc", "enable_mask", "timeout_ns"]
+    assert [f.name for f in dataclasses.fields(ep.DispatchOutputs)] == ["tokens", "topk_weights", "scales", "topk_idx"]
+    assert [f.name for f in dataclasses.fields(ep.LayoutInfo)] == ["expert_counters", "src_rank_counters", "expert_offsets", "recv_total_counter"]
+    assert (ep.Layout.EXPERT_MAJOR, ep.Layout.RANK_MAJOR, ep.Layout.FLAT) == (1, 2, 3) and ep.Algorithm.LOW_LATENCY == 0 and ep.PassDir.BWD == 1
+
+
+def test_expert_parallel_tensor_descriptor_and_version():
+    import numpy as np
+    import nccl_b200.nccl4py.ep as ep
+    a = np.zeros((6, 8), dtype=np.int64)
+    t = ep.Tensor(a)
+    assert t.ndim == 2 and t.sizes == (6, 8) and t.data == a.ctypes.data and t.ptr != 0 and t.buffer is a
+    major, minor, patch = ep.get_lib_version()
+    assert (major, minor, patch) >= (0, 1, 0)
+    assert ep.get_lib_path().name == "libnccl_b200.so"
+    li = ep.LayoutInfo(expert_counters=t)._struct()
+    assert li.expert_counters.contents.data == a.ctypes.data and not li.expert_offsets
+
+
+def test_expert_parallel_group_refuses_host_communicators():
+    """Creating a group goes through ncclEpCreateGroup with the record's fields; on a host-memory communicator the library refuses."""
+    res = run_ranks(_ep_group_rank, 2, env=BASE)
+    assert res[0] == res[1] == "refused"
+
+
+def _ep_group_rank(rank, nranks, uid):
+    import nccl_b200.nccl4py.core as nccl
+    import nccl_b200.nccl4py.ep as ep
+    from nccl_b200._lib import NcclError
+    comm = nccl.Communicator.init(nranks, rank, nccl.UniqueId(uid))
+    try:
+        ep.Group.create(comm, ep.GroupConfig(num_experts=8, max_dispatch_tokens_per_rank=16, max_token_bytes=256))
+        out = "created"
+    except NcclError:
+        out = "refused"
+    comm.destroy()
+    return out
