@@ -13,6 +13,7 @@
 
 #include "../core/bootstrap.h"
 #include "../core/core.h"
+#include "mnnvl.h"
 
 struct ncclWindow_vidmem;
 
@@ -57,6 +58,7 @@ struct PeerInfo {
   uint64_t totalMem;
   int version;
   int hostOnly;        // rank has no GPU (host-memory communicator)
+  FabricInfo fabric;   // NVLink fabric identity of the GPU (multi-node NVLink)
 };
 
 struct UserRedOp {
@@ -101,7 +103,9 @@ struct ncclComm {
   int cudaDev = -1, nvmlDev = -1;
   int compCap = 0;
   bool hostOnly = false;          // no GPU: buffers are host memory, data moves over sockets
-  bool lsaAll = false;            // every rank is load/store reachable (one NVLink domain, one host)
+  bool lsaAll = false;            // every rank is load/store reachable (one NVLink domain: one host, or one fabric clique across hosts)
+  bool mnnvl = false;             // device memory is shared through fabric handles (the ranks' GPUs share an NVLink fabric across hosts)
+  b200::Clique clique;                  // ranks of this rank's fabric clique (filled when the fabric is up on every rank)
   int node = 0, nNodes = 1, localRank = 0, localRanks = 1;
   uint64_t commHash = 0;
   ncclConfig_t config;

@@ -104,6 +104,7 @@ static void fillPeerInfo(ncclComm* comm, PeerInfo* pi) {
     }
     pi->vmmSupport = cuMemSupported(comm->cudaDev);
     pi->mcSupport = cuMulticastSupported(comm->cudaDev);
+    fabricInfoQuery(busId[0] ? busId : nullptr, &pi->fabric);
   }
 }
 
@@ -144,7 +145,9 @@ static ncclResult_t commSetup(ncclComm* comm) {
       }
     }
     comm->compCap = comm->peers[comm->rank].cudaCompCap;
-    comm->lsaAll = comm->nNodes == 1 && n <= kMaxRanks && !paramP2pDisable();
+    NCCLCHECK(mnnvlCheck(comm));
+    const bool oneDomain = comm->nNodes == 1 || (comm->mnnvl && (int)comm->clique.ranks.size() == n);
+    comm->lsaAll = oneDomain && n <= kMaxRanks && !paramP2pDisable();
     NCCLCHECK(topoInit(comm));   // topology detection + graphs (feeds the model, the dumps and fallbacks)
   }
   if (comm->hostOnly) {

@@ -2,6 +2,8 @@
 // Reference parity: src/misc/cudawrap.cc (driver table through cudaGetDriverEntryPoint).
 #include "cudawrap.h"
 
+#include <atomic>
+
 #include <mutex>
 
 namespace b200 {
@@ -74,6 +76,12 @@ bool cuMemSupported(int cudaDev) {
   return devAttr(cudaDev, CU_DEVICE_ATTRIBUTE_VIRTUAL_MEMORY_MANAGEMENT_SUPPORTED) &&
          devAttr(cudaDev, CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR_SUPPORTED);
 }
+
+bool cuFabricSupported(int cudaDev) { return cuMemSupported(cudaDev) && devAttr(cudaDev, CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_FABRIC_SUPPORTED); }
+
+static std::atomic<int> gHandleType{(int)CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR};
+CUmemAllocationHandleType memHandleType() { return (CUmemAllocationHandleType)gHandleType.load(std::memory_order_relaxed); }
+void memSetHandleType(CUmemAllocationHandleType t) { gHandleType.store((int)t, std::memory_order_relaxed); }
 
 bool cuMulticastSupported(int cudaDev) {
   if (!paramNvlsEnable()) return false;

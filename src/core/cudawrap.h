@@ -41,6 +41,11 @@ const CuApi* cuApi();
 const char* cuErrStr(CUresult r);
 bool cuMemSupported(int cudaDev);       // VMM with POSIX-fd handles (NCCL_CUMEM_ENABLE, default on)
 bool cuMulticastSupported(int cudaDev); // NVLS multicast objects (NCCL_NVLS_ENABLE, default on)
+bool cuFabricSupported(int cudaDev);    // memory can be created with fabric handles (multi-node NVLink)
+// Handle type that shareable device memory is created with: POSIX file descriptors, or fabric handles once a
+// communicator found that its ranks share an NVLink fabric across hosts (process-wide, like the allocations it governs).
+CUmemAllocationHandleType memHandleType();
+void memSetHandleType(CUmemAllocationHandleType t);
 
 #define CUCHECK(call)                                                                  \
   do {                                                                                 \

@@ -34,6 +34,7 @@ const NvmlApi* nvmlApi() {
     load((void**)&gNvml.deviceGetNvLinkRemotePciInfo, "nvmlDeviceGetNvLinkRemotePciInfo_v2", "nvmlDeviceGetNvLinkRemotePciInfo");
     load((void**)&gNvml.deviceGetP2PStatus, "nvmlDeviceGetP2PStatus", nullptr);
     load((void**)&gNvml.deviceGetCudaComputeCapability, "nvmlDeviceGetCudaComputeCapability", nullptr);
+    gNvml.deviceGetGpuFabricInfoV = (int (*)(nvmlDevice_t, void*))dlsym(h, "nvmlDeviceGetGpuFabricInfoV");
     if (ok) gActive = &gNvml;
   });
   return gActive;

@@ -22,6 +22,7 @@ struct NvmlApi {
   int (*deviceGetNvLinkRemotePciInfo)(nvmlDevice_t, unsigned int, nvmlPciInfo_t*);
   int (*deviceGetP2PStatus)(nvmlDevice_t, nvmlDevice_t, int, int*);
   int (*deviceGetCudaComputeCapability)(nvmlDevice_t, int*, int*);
+  int (*deviceGetGpuFabricInfoV)(nvmlDevice_t, void* /* nvmlGpuFabricInfoV_t */);   // optional: null with older drivers
 };
 
 // Null when NVML is not installed or fails to initialise.

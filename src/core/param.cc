@@ -136,7 +136,7 @@ static ParamRegistrar kStrParams[] = {
     // script written for the reference explains itself
     {{"NCCL_IB_DISABLE", PT_STR, "", "No effect: there is no InfiniBand verbs backend (external network plugins load through NCCL_NET_PLUGIN); the same holds for every NCCL_IB_* variable", true}},
     {{"NCCL_NET_GDR_LEVEL", PT_STR, "", "No effect: the built-in socket backend stages through host memory; a plugin decides about GPUDirect itself", true}},
-    {{"NCCL_MNNVL_ENABLE", PT_STR, "", "No effect: the data plane serves one node (one NVLink domain of up to 8 GPUs)", true}},
+    {{"NCCL_MNNVL_CROSS_CLIQUE", PT_STR, "", "No effect: ranks of other fabric cliques are reached through the network transport only", true}},
     {{"NCCL_NTHREADS", PT_STR, "", "No effect: the kernels' CTA sizes are fixed per kernel (512 threads, 32 for the bulk-copy forms)", true}},
     {{"NCCL_BUFFSIZE", PT_STR, "", "No effect: there are no per-channel FIFO buffers; NCCL_B200_SCRATCH_MB sizes the staging area for unregistered buffers", true}},
     {{"NCCL_LAUNCH_MODE", PT_STR, "", "No effect: every rank launches its own kernels (one process or thread per GPU)", true}},

@@ -1,4 +1,5 @@
-// ncclMemAlloc / ncclMemFree: physical memory from cuMemCreate with a POSIX-fd shareable handle,
+// ncclMemAlloc / ncclMemFree: physical memory from cuMemCreate with a shareable handle (POSIX fd; fabric
+// handles when multi-node NVLink is in use),
 // mapped read-write for every device that can reach it, so that windows over it can be mapped by
 // peers and bound to NVLink multicast objects. Falls back to cudaMalloc without the VMM API.
 // Reference parity: src/allocator.cc:17-139.
@@ -21,14 +22,14 @@ size_t shareableGranularity(int dev) {
   prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
   prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
   prop.location.id = dev;
-  prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  prop.requestedHandleTypes = memHandleType();
   size_t g = 0;
   if (cu->cuMemGetAllocationGranularity(&g, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED) == CUDA_SUCCESS && g > gran) gran = g;
   if (cuMulticastSupported(dev)) {
     CUmulticastObjectProp mp = {};
     mp.numDevices = 2;
     mp.size = gran;
-    mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+    mp.handleTypes = memHandleType();
     size_t mg = 0;
     if (cu->cuMulticastGetGranularity(&mg, &mp, CU_MULTICAST_GRANULARITY_MINIMUM) == CUDA_SUCCESS && mg > gran) gran = mg;
   }
@@ -52,13 +53,14 @@ ncclResult_t memAlloc(void** ptr, size_t size, int dev) {
     prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
     prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
     prop.location.id = dev;
-    prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+    prop.requestedHandleTypes = memHandleType();
     int rdma = 0;
     CUdevice cudev;
     if (cu->cuDeviceGet(&cudev, dev) == CUDA_SUCCESS)
       cu->cuDeviceGetAttribute(&rdma, CU_DEVICE_ATTRIBUTE_GPU_DIRECT_RDMA_WITH_CUDA_VMM_SUPPORTED, cudev);
     if (rdma) prop.allocFlags.gpuDirectRDMACapable = 1;
     CUCHECK(cu->cuMemCreate(&m.handle, m.size, &prop, 0));
+    m.handleType = (int)prop.requestedHandleTypes;
     CUdeviceptr va = 0;
     CUresult r = cu->cuMemAddressReserve(&va, m.size, gran, 0, 0);
     if (r != CUDA_SUCCESS) { cu->cuMemRelease(m.handle); WARN("cuMemAddressReserve: %s", cuErrStr(r)); return ncclUnhandledCudaError; }
@@ -136,13 +138,14 @@ static ncclResult_t mapPhysical(MemAlloc& m) {
   prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
   prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
   prop.location.id = m.dev;
-  prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  prop.requestedHandleTypes = memHandleType();
   int rdma = 0;
   CUdevice cudev;
   if (cu->cuDeviceGet(&cudev, m.dev) == CUDA_SUCCESS)
     cu->cuDeviceGetAttribute(&rdma, CU_DEVICE_ATTRIBUTE_GPU_DIRECT_RDMA_WITH_CUDA_VMM_SUPPORTED, cudev);
   if (rdma) prop.allocFlags.gpuDirectRDMACapable = 1;
   CUCHECK(cu->cuMemCreate(&m.handle, m.size, &prop, 0));
+    m.handleType = (int)prop.requestedHandleTypes;
   CUresult r = cu->cuMemMap((CUdeviceptr)m.ptr, m.size, 0, m.handle, 0);
   if (r != CUDA_SUCCESS) { cu->cuMemRelease(m.handle); WARN("cuMemMap (re-attach): %s", cuErrStr(r)); return ncclUnhandledCudaError; }
   int ndev = 0;

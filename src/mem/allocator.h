@@ -12,6 +12,7 @@ struct MemAlloc {
   int dev = -1;
   bool vmm = false;       // created with cuMemCreate (exportable, multicast-bindable)
   CUmemGenericAllocationHandle handle = 0;
+  int handleType = 0;     // CUmemAllocationHandleType the physical memory was created with
   bool detached = false;  // the physical memory was given back (memDetachPhysical); the address range is still reserved
 };
 

@@ -33,6 +33,7 @@ ncclResult_t symInit(ncclComm* comm) {
   bool mc = true, vmm = true;
   for (auto& p : comm->peers) { mc = mc && p.mcSupport; vmm = vmm && p.vmmSupport; }
   s->vmmUsable = vmm && comm->lsaAll;
+  s->fabric = comm->mnnvl;   // the ranks span hosts: descriptors cannot travel over UNIX sockets, fabric handles are plain bytes
   s->mcUsable = mc && s->vmmUsable && comm->nRanks > 1;
   if (cudaMalloc(&s->winTableDev, (size_t)kMaxWinSlots * kMaxRanks * sizeof(void*)) != cudaSuccess ||
       cudaMemset(s->winTableDev, 0, (size_t)kMaxWinSlots * kMaxRanks * sizeof(void*)) != cudaSuccess) {
@@ -89,6 +90,28 @@ void symDestroy(ncclComm* comm) {
   comm->sym = nullptr;
 }
 
+// A shareable form of an allocation handle: a file descriptor (one host; travels over UNIX sockets) or a fabric handle
+// (64 plain bytes; travels over the bootstrap network, valid on every host of the NVLink fabric).
+struct ShareHandle {
+  int fd = -1;
+  CUmemFabricHandle fabric = {};
+};
+static CUmemAllocationHandleType shareType(const SymRuntime* s) { return s->fabric ? CU_MEM_HANDLE_TYPE_FABRIC : CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR; }
+static CUresult exportHandle(const SymRuntime* s, CUmemGenericAllocationHandle h, ShareHandle* out) {
+  const CuApi* cu = cuApi();
+  if (s->fabric) return cu->cuMemExportToShareableHandle(&out->fabric, h, CU_MEM_HANDLE_TYPE_FABRIC, 0);
+  return cu->cuMemExportToShareableHandle(&out->fd, h, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0);
+}
+static CUresult importHandle(const SymRuntime* s, CUmemGenericAllocationHandle* h, const ShareHandle* in) {
+  const CuApi* cu = cuApi();
+  if (s->fabric) return cu->cuMemImportFromShareableHandle(h, (void*)&in->fabric, CU_MEM_HANDLE_TYPE_FABRIC);
+  return cu->cuMemImportFromShareableHandle(h, (void*)(uintptr_t)in->fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+}
+static void closeHandle(const SymRuntime* s, ShareHandle* h) {
+  if (!s->fabric && h->fd >= 0) close(h->fd);
+  h->fd = -1;
+}
+
 // Describes the allocation behind `buff` for the other ranks.
 static void describeLocal(ncclComm* comm, void* buff, size_t size, RegDesc* d, CUmemGenericAllocationHandle* handle,
                           bool* retained) {
@@ -103,7 +126,7 @@ static void describeLocal(ncclComm* comm, void* buff, size_t size, RegDesc* d, C
     d->base = (uint64_t)m.ptr;
     d->allocSize = m.size;
     d->offset = (uintptr_t)buff - (uintptr_t)m.ptr;
-    if (m.vmm && comm->sym->vmmUsable) {
+    if (m.vmm && comm->sym->vmmUsable && m.handleType == (int)shareType(comm->sym)) {
       d->kind = SEG_VMM;
       *handle = m.handle;
       return;
@@ -118,9 +141,9 @@ static void describeLocal(ncclComm* comm, void* buff, size_t size, RegDesc* d, C
     // Memory created by somebody else's cuMemCreate can be shared when it carries a POSIX-fd handle
     // type; exporting tells (memory of cudaMalloc has no generic handle at all).
     if (comm->sym->vmmUsable && cu->cuMemRetainAllocationHandle(handle, (void*)base) == CUDA_SUCCESS) {
-      int fd = -1;
-      if (cu->cuMemExportToShareableHandle(&fd, *handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0) == CUDA_SUCCESS) {
-        close(fd);
+      ShareHandle sh;
+      if (exportHandle(comm->sym, *handle, &sh) == CUDA_SUCCESS) {
+        closeHandle(comm->sym, &sh);
         d->kind = SEG_VMM;
         *retained = true;
         return;
@@ -129,15 +152,16 @@ static void describeLocal(ncclComm* comm, void* buff, size_t size, RegDesc* d, C
     }
   }
   if (!d->base || d->offset + size > d->allocSize) return;
+  if (comm->sym->fabric) return;   // legacy handles do not cross hosts
   // legacy inter-process handle: works for cudaMalloc memory
   if (cudaIpcGetMemHandle(&d->ipc, (void*)d->base) == cudaSuccess) d->kind = SEG_IPC;
   else (void)cudaGetLastError();
 }
 
-static ncclResult_t mapPeerVmm(ncclComm* comm, SymSegment* seg, int p, int fd, size_t allocSize) {
+static ncclResult_t mapPeerVmm(ncclComm* comm, SymSegment* seg, int p, const ShareHandle* sh, size_t allocSize) {
   const CuApi* cu = cuApi();
   CUmemGenericAllocationHandle h;
-  CUCHECK(cu->cuMemImportFromShareableHandle(&h, (void*)(uintptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR));
+  CUCHECK(importHandle(comm->sym, &h, sh));
   size_t gran = shareableGranularity(comm->cudaDev);
   size_t mapSize = alignUp(allocSize, (size_t)(2 << 20));
   CUdeviceptr va = 0;
@@ -204,6 +228,22 @@ static ncclResult_t exchangeFds(ncclComm* comm, int tag, int myFd, uint64_t a, i
   return ncclSuccess;
 }
 
+// Every rank's shareable handle of its allocation, at every rank.
+static ncclResult_t exchangeHandles(ncclComm* comm, int tag, const ShareHandle* mine, uint64_t a, ShareHandle* all /* [nRanks] */) {
+  const int n = comm->nRanks, me = comm->rank;
+  if (comm->sym->fabric) {
+    std::vector<CUmemFabricHandle> fh(n);
+    fh[me] = mine->fabric;
+    NCCLCHECK(bootstrapAllGather(comm->bootstrap, fh.data(), sizeof(CUmemFabricHandle)));
+    for (int p = 0; p < n; ++p) { all[p].fd = -1; all[p].fabric = fh[p]; }
+    return ncclSuccess;
+  }
+  std::vector<int> fds(n, -1);
+  NCCLCHECK(exchangeFds(comm, tag, mine->fd, a, fds.data()));
+  for (int p = 0; p < n; ++p) all[p].fd = fds[p];
+  return ncclSuccess;
+}
+
 static ncclResult_t setupMulticast(ncclComm* comm, SymSegment* seg, const RegDesc* all, int tag) {
   const CuApi* cu = cuApi();
   SymRuntime* s = comm->sym;
@@ -213,7 +253,7 @@ static ncclResult_t setupMulticast(ncclComm* comm, SymSegment* seg, const RegDes
   for (int p = 1; p < n; ++p) common = std::min<size_t>(common, all[p].allocSize);
   CUmulticastObjectProp mp = {};
   mp.numDevices = n;
-  mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  mp.handleTypes = shareType(s);
   mp.size = common;
   size_t mg = 0;
   if (cu->cuMulticastGetGranularity(&mg, &mp, CU_MULTICAST_GRANULARITY_MINIMUM) != CUDA_SUCCESS || mg == 0) return ncclSuccess;
@@ -221,7 +261,23 @@ static ncclResult_t setupMulticast(ncclComm* comm, SymSegment* seg, const RegDes
   if (common % mg != 0) { INFO(SUB_NVLS, "multicast skipped: common size %zu is not a multiple of %zu", common, mg); return ncclSuccess; }
   mp.size = common;
   int okLocal = 1;
-  if (me == 0) {
+  if (s->fabric) {
+    // the object's fabric handle is plain bytes: rank 0's copy reaches everybody through one gather
+    struct McMsg { int ok; CUmemFabricHandle h; };
+    std::vector<McMsg> msgs(n);
+    memset(msgs.data(), 0, n * sizeof(McMsg));
+    if (me == 0) {
+      CUresult r = cu->cuMulticastCreate(&seg->mcHandle, &mp);
+      if (r == CUDA_SUCCESS) r = cu->cuMemExportToShareableHandle(&msgs[0].h, seg->mcHandle, CU_MEM_HANDLE_TYPE_FABRIC, 0);
+      if (r != CUDA_SUCCESS) { INFO(SUB_NVLS, "multicast object creation failed: %s", cuErrStr(r)); okLocal = 0; }
+      msgs[0].ok = okLocal;
+    }
+    NCCLCHECK(bootstrapAllGather(comm->bootstrap, msgs.data(), sizeof(McMsg)));
+    if (me != 0) {
+      if (!msgs[0].ok) okLocal = 0;
+      else if (cu->cuMemImportFromShareableHandle(&seg->mcHandle, (void*)&msgs[0].h, CU_MEM_HANDLE_TYPE_FABRIC) != CUDA_SUCCESS) okLocal = 0;
+    }
+  } else if (me == 0) {
     CUresult r = cu->cuMulticastCreate(&seg->mcHandle, &mp);
     int fd = -1;
     if (r == CUDA_SUCCESS) r = cu->cuMemExportToShareableHandle(&fd, seg->mcHandle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0);
@@ -336,17 +392,18 @@ ncclResult_t symWindowRegister(ncclComm* comm, void* buff, size_t size, SymWindo
       seg->peerBase[me] = (void*)mine.base;
       ncclResult_t res = ncclSuccess;
       if (kind == SEG_VMM) {
-        const CuApi* cu = cuApi();
-        int myFd = -1;
-        CUresult r = cu->cuMemExportToShareableHandle(&myFd, myHandle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0);
+        ShareHandle mySh;
+        CUresult r = exportHandle(s, myHandle, &mySh);
         if (r != CUDA_SUCCESS) { WARN("export of window memory failed: %s", cuErrStr(r)); res = ncclUnhandledCudaError; }
-        std::vector<int> fds(n, -1);
-        if (res == ncclSuccess) res = exchangeFds(comm, 2 * tag, myFd, mine.allocSize, fds.data());
-        if (myFd >= 0) close(myFd);
+        std::vector<ShareHandle> shs(n);
+        // every rank takes part in the exchange even after a failed export (an invalid handle fails at the importer)
+        if (res == ncclSuccess || s->fabric) { ncclResult_t xr = exchangeHandles(comm, 2 * tag, &mySh, mine.allocSize, shs.data()); if (res == ncclSuccess) res = xr; }
+        closeHandle(s, &mySh);
         for (int p = 0; p < n; ++p) {
-          if (p == me || fds[p] < 0) continue;
-          if (res == ncclSuccess) res = mapPeerVmm(comm, seg, p, fds[p], all[p].allocSize);
-          close(fds[p]);
+          if (p == me) continue;
+          if (!s->fabric && shs[p].fd < 0) continue;
+          if (res == ncclSuccess) res = mapPeerVmm(comm, seg, p, &shs[p], all[p].allocSize);
+          closeHandle(s, &shs[p]);
         }
         if (res == ncclSuccess && s->mcUsable) res = setupMulticast(comm, seg, all.data(), 2 * tag + 1);
       } else {

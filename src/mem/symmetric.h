@@ -58,6 +58,7 @@ struct SymRuntime {
   IpcSocket ipc;
   bool mcUsable = false;           // every rank supports multicast
   bool vmmUsable = false;
+  bool fabric = false;             // handles are fabric handles exchanged over the bootstrap network (multi-node NVLink)
   int regSeq = 0;
   std::vector<SymSegment*> segments;
   std::vector<SymWindow*> windows;
