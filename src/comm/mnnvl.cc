@@ -34,8 +34,9 @@ void fabricInfoQuery(const char* busId, FabricInfo* out) {
   const NvmlApi* nv = nvmlApi();
   nvmlDevice_t dev;
   if (nv && nv->deviceGetGpuFabricInfoV && busId && nv->deviceGetHandleByPciBusId(busId, &dev) == 0) {
-    NvmlFabricInfoV fi;
-    memset(&fi, 0, sizeof(fi));
+    union { NvmlFabricInfoV fi; unsigned char room[128]; } u;   // room to spare should a driver write a later, longer version
+    memset(&u, 0, sizeof(u));
+    NvmlFabricInfoV& fi = u.fi;
     fi.version = kNvmlFabricInfoV2;
     if (nv->deviceGetGpuFabricInfoV(dev, &fi) == 0) {
       memcpy(out->clusterUuid, fi.clusterUuid, kFabricUuidLen);
