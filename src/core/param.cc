@@ -134,8 +134,11 @@ static ParamRegistrar kStrParams[] = {
     {{"NCCL_PROFILE_EVENT_MASK", PT_STR, "", "Bit mask of the event types handed to the profiler plugin (overrides what the plugin asks for)", true}},
     // variables of the reference that configure parts this build does not have: accepted and ignored, listed so that a job
     // script written for the reference explains itself
-    {{"NCCL_IB_DISABLE", PT_STR, "", "No effect: there is no InfiniBand verbs backend (external network plugins load through NCCL_NET_PLUGIN); the same holds for every NCCL_IB_* variable", true}},
-    {{"NCCL_NET_GDR_LEVEL", PT_STR, "", "No effect: the built-in socket backend stages through host memory; a plugin decides about GPUDirect itself", true}},
+    {{"NCCL_IB_HCA", PT_STR, "", "Verbs devices the InfiniBand backend may use: name prefixes with optional :port, comma separated; =name wants the exact name, a leading ^ excludes", true}},
+    {{"NCCL_IB_ADDR_FAMILY", PT_STR, "AF_INET", "Address family preferred when the RoCE GID index is chosen automatically: AF_INET or AF_INET6", true}},
+    {{"NCCL_B200_IBV_LIB", PT_STR, "libibverbs.so.1", "Verbs library that the InfiniBand backend opens at run time", true}},
+    {{"NCCL_IB_QPS_PER_CONNECTION", PT_STR, "", "No effect: the InfiniBand backend uses one queue pair per connection; the same holds for NCCL_IB_SPLIT_DATA_ON_QPS, NCCL_IB_AR_THRESHOLD, NCCL_IB_MERGE_NICS and the resiliency settings", true}},
+    {{"NCCL_NET_GDR_LEVEL", PT_STR, "", "No effect: the proxy stages through host memory on the built-in backends; a plugin decides about GPUDirect itself", true}},
     {{"NCCL_MNNVL_CROSS_CLIQUE", PT_STR, "", "No effect: ranks of other fabric cliques are reached through the network transport only", true}},
     {{"NCCL_NTHREADS", PT_STR, "", "No effect: the kernels' CTA sizes are fixed per kernel (512 threads, 32 for the bulk-copy forms)", true}},
     {{"NCCL_BUFFSIZE", PT_STR, "", "No effect: there are no per-channel FIFO buffers; NCCL_B200_SCRATCH_MB sizes the staging area for unregistered buffers", true}},

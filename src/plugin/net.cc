@@ -52,7 +52,8 @@ ncclResult_t netSelect(ncclNet_t** net, bool* external) {
     }
     if (lib && !ext && gCollNet) INFO(SUB_NET | SUB_INIT, "net plugin %s has no point-to-point table (%s): point-to-point traffic stays on the built-in backend", resolved.c_str(), NCCL_NET_PLUGIN_SYMBOL);
     else if (lib && !ext) WARN("net plugin %s exports none of ncclNetPlugin_v12 ... ncclNetPlugin_v8; using the built-in backend", resolved.c_str());
-    if (ext && wantName && *wantName && strcasecmp(wantName, ext->name) != 0 && strcasecmp(wantName, netSocketBackend.name) == 0) ext = nullptr;
+    if (ext && wantName && *wantName && strcasecmp(wantName, ext->name) != 0 &&
+        (strcasecmp(wantName, netSocketBackend.name) == 0 || strcasecmp(wantName, netIbBackend.name) == 0)) ext = nullptr;
     if (ext) {
       int ndev = 0;
       void* ctx = nullptr;
@@ -66,7 +67,18 @@ ncclResult_t netSelect(ncclNet_t** net, bool* external) {
       }
       WARN("net plugin %s found no usable device; using the built-in backend", ext->name);
     }
-    if (wantName && *wantName && strcasecmp(wantName, netSocketBackend.name) != 0)
+    const bool wantSocket = wantName && *wantName && strcasecmp(wantName, netSocketBackend.name) == 0;
+    if (!wantSocket) {
+      int ndev = 0;
+      void* ctx = nullptr;
+      ncclNetCommConfig_t cfg = {NCCL_NET_TRAFFIC_CLASS_UNDEF};
+      if (netIbBackend.init(&ctx, 0, &cfg, pluginLogger, nullptr) == ncclSuccess && netIbBackend.devices(&ndev) == ncclSuccess && ndev > 0) {
+        gNet = &netIbBackend;
+        INFO(SUB_NET | SUB_INIT, "network backend: built-in %s, %d device(s)", netIbBackend.name, ndev);
+        return;
+      }
+    }
+    if (wantName && *wantName && !wantSocket)
       WARN("NCCL_NET=%s does not match any available backend; using %s", wantName, netSocketBackend.name);
     gNet = &netSocketBackend;
     INFO(SUB_NET | SUB_INIT, "network backend: built-in %s", gNet->name);

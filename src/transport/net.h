@@ -17,8 +17,10 @@
 namespace b200 {
 
 extern ncclNet_t netSocketBackend;                 // transport/net_socket.cc
+extern ncclNet_t netIbBackend;                     // transport/net_ib.cc (no device unless libibverbs and an active port are there)
 
-// Resolves the network backend once per process: NCCL_NET_PLUGIN (library), NCCL_NET (name).
+// Resolves the network backend once per process: NCCL_NET_PLUGIN (library), NCCL_NET (name); without either, the
+// InfiniBand backend when it finds a device, else TCP sockets.
 ncclResult_t netSelect(ncclNet_t** net, bool* external);
 ncclCollNet_t* netCollNetTable();                  // collective-network table of the loaded plugin, or nullptr
 

@@ -195,38 +195,51 @@ ncclResult_t proxyCreate(ncclComm* comm) {
     NCCLCHECKGOTO(bootstrapAllGather(comm->bootstrap, handles.data(), NCCL_NET_HANDLE_MAXSIZE), res, fail);
     p->sendComm.assign(n, nullptr);
     p->recvComm.assign(n, nullptr);
-    // Connects land in the peer's listen queue, so dialling everyone before accepting cannot
-    // deadlock. Each accepted connection says who dialled with a first 4-byte message.
-    for (int r = 0; r < n; ++r) {
-      if (r == me) continue;
-      void* sc = nullptr;
-      while (!sc) {
-        NCCLCHECKGOTO(p->net->connect(p->netCtx, p->dev, handles.data() + (size_t)r * NCCL_NET_HANDLE_MAXSIZE, &sc, nullptr), res, fail);
-        if (flagSet(comm->abortFlag)) { res = ncclInternalError; goto fail; }
+    // A backend may finish a connection only after several calls (connect / accept return no object until the other side has
+    // answered), so dialling and accepting take turns until the whole mesh stands. Backends whose connect lands in the peer's
+    // listen queue and whose accept waits (TCP) get through the same loop: every rank dials everybody before its first accept.
+    {
+      std::vector<int> toDial;
+      std::vector<void*> accepted;
+      for (int r = 0; r < n; ++r) if (r != me) toDial.push_back(r);
+      while (!toDial.empty() || (int)accepted.size() < n - 1) {
+        for (size_t i = 0; i < toDial.size();) {
+          void* sc = nullptr;
+          NCCLCHECKGOTO(p->net->connect(p->netCtx, p->dev, handles.data() + (size_t)toDial[i] * NCCL_NET_HANDLE_MAXSIZE, &sc, nullptr), res, fail);
+          if (sc) { p->sendComm[toDial[i]] = sc; toDial.erase(toDial.begin() + i); } else ++i;
+        }
+        if ((int)accepted.size() < n - 1) {
+          void* rc = nullptr;
+          NCCLCHECKGOTO(p->net->accept(p->listenComm, &rc, nullptr), res, fail);
+          if (rc) accepted.push_back(rc);
+        }
+        if (flagSet(comm->abortFlag)) { for (void* rc : accepted) p->net->closeRecv(rc); res = ncclInternalError; goto fail; }
       }
-      p->sendComm[r] = sc;
-      int hello = me, done = 0;
-      void* req = nullptr;
-      while (!req) NCCLCHECKGOTO(p->net->isend(sc, &hello, sizeof(hello), 0, nullptr, nullptr, &req), res, fail);
-      while (!done) NCCLCHECKGOTO(p->net->test(req, &done, nullptr), res, fail);
-    }
-    for (int k = 0; k < n - 1; ++k) {
-      void* rc = nullptr;
-      while (!rc) {
-        NCCLCHECKGOTO(p->net->accept(p->listenComm, &rc, nullptr), res, fail);
-        if (flagSet(comm->abortFlag)) { res = ncclInternalError; goto fail; }
+      // Each accepted connection says who dialled with a first 4-byte message (small enough to complete at the sender without a
+      // matching receive on every backend).
+      for (int r = 0; r < n; ++r) {
+        if (r == me) continue;
+        int hello = me, done = 0;
+        void* req = nullptr;
+        while (!req) NCCLCHECKGOTO(p->net->isend(p->sendComm[r], &hello, sizeof(hello), 0, nullptr, nullptr, &req), res, fail);
+        while (!done) NCCLCHECKGOTO(p->net->test(req, &done, nullptr), res, fail);
       }
-      int hello = -1, done = 0;
-      void* req = nullptr;
-      void* ptrs[1] = {&hello};
-      size_t sizes[1] = {sizeof(hello)};
-      int tags[1] = {0};
-      void* mh[1] = {nullptr};
-      void* ph[1] = {nullptr};
-      while (!req) NCCLCHECKGOTO(p->net->irecv(rc, 1, ptrs, sizes, tags, mh, ph, &req), res, fail);
-      while (!done) NCCLCHECKGOTO(p->net->test(req, &done, nullptr), res, fail);
-      if (hello < 0 || hello >= n || hello == me || p->recvComm[hello]) { WARN("proxy: unexpected peer %d on the network mesh", hello); res = ncclInternalError; goto fail; }
-      p->recvComm[hello] = rc;
+      for (size_t k = 0; k < accepted.size(); ++k) {
+        void* rc = accepted[k];
+        int hello = -1, done = 0;
+        void* req = nullptr;
+        void* ptrs[1] = {&hello};
+        size_t sizes[1] = {sizeof(hello)};
+        int tags[1] = {0};
+        void* mh[1] = {nullptr};
+        void* ph[1] = {nullptr};
+        ncclResult_t hr = ncclSuccess;
+        while (!req && hr == ncclSuccess) hr = p->net->irecv(rc, 1, ptrs, sizes, tags, mh, ph, &req);
+        while (!done && hr == ncclSuccess) hr = p->net->test(req, &done, nullptr);
+        if (hr == ncclSuccess && (hello < 0 || hello >= n || hello == me || p->recvComm[hello])) { WARN("proxy: unexpected peer %d on the network mesh", hello); hr = ncclInternalError; }
+        if (hr != ncclSuccess) { for (size_t j = k; j < accepted.size(); ++j) p->net->closeRecv(accepted[j]); res = hr; goto fail; }
+        p->recvComm[hello] = rc;
+      }
     }
   }
   p->thread = std::thread(proxyMain, p);

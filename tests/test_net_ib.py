@@ -1,0 +1,78 @@
+"""InfiniBand / RoCE backend on CPU ranks against a stand-in for libibverbs (tests/data/fake_ibverbs.cc: queue pairs
+whose traffic travels over UNIX sockets, with key, bounds and state checks). The host collectives of several processes
+go through the backend and the proxy thread; the stand-in counts protocol violations."""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from mp_util import run_ranks
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BASE = {"NCCL_B200_HOST_ONLY": "1", "NCCL_SOCKET_IFNAME": "lo", "NCCL_B200_HOST_NET": "1"}
+
+
+@pytest.fixture(scope="module")
+def fake_lib(tmp_path_factory):
+    out = str(tmp_path_factory.mktemp("fakeib") / "libfakeibverbs.so")
+    subprocess.run(["g++", "-std=c++17", "-O1", "-shared", "-fPIC", "-I" + os.path.join(ROOT, "src", "transport"),
+                    os.path.join(ROOT, "tests", "data", "fake_ibverbs.cc"), "-o", out, "-pthread"], check=True)
+    return out
+
+
+def _rank(rank, nranks, uid, sizes):
+    import ctypes
+    from nccl_b200 import Communicator, group
+    comm = Communicator(nranks, rank, uid)
+    out = []
+    for n in sizes:
+        x = (np.arange(n, dtype=np.float32) % 251) + rank
+        y = np.zeros_like(x)
+        comm.all_reduce(x, y)
+        ref = (np.arange(n, dtype=np.float32) % 251) * nranks + nranks * (nranks - 1) / 2
+        out.append(bool(np.array_equal(y, ref)))
+    peer, src = (rank + 1) % nranks, (rank - 1) % nranks
+    for n in sizes:
+        s = np.full(n, rank + 1, dtype=np.float32)
+        r = np.zeros(n, dtype=np.float32)
+        with group():
+            comm.send(s, peer)
+            comm.recv(r, src)
+        out.append(bool((r == src + 1).all()))
+    comm.destroy()
+    errs = ctypes.CDLL(os.environ["NCCL_B200_IBV_LIB"]).fake_ib_errors()
+    return out, errs
+
+
+@pytest.mark.parametrize("link", ["ETH", "IB"])
+def test_host_collectives_over_the_verbs_backend(fake_lib, tmp_path, link):
+    env = dict(BASE, NCCL_NET="IB", NCCL_B200_IBV_LIB=fake_lib, FAKE_IB_LINK=link, NCCL_DEBUG="INFO", NCCL_DEBUG_SUBSYS="NET,INIT",
+               NCCL_DEBUG_FILE=str(tmp_path / "log.%p"))
+    # 1 element (inline), 1000 floats (eager through the staging ring), 64 Ki and 1 Mi floats (credits + RDMA writes, several slices)
+    res = run_ranks(_rank, 3, args=([1, 1000, 1 << 16, 1 << 20],), env=env, timeout=300)
+    for r in range(3):
+        ok, errs = res[r]
+        assert all(ok), (r, ok)
+        assert errs == 0
+    text = "".join(open(tmp_path / f).read() for f in os.listdir(tmp_path))
+    assert "network backend: built-in IB, 2 device(s)" in text
+    assert ("RoCE" if link == "ETH" else "InfiniBand") in text
+
+
+def test_device_filter_and_fallback_to_sockets(fake_lib, tmp_path):
+    env = dict(BASE, NCCL_B200_IBV_LIB=fake_lib, NCCL_IB_HCA="^fakeib", NCCL_DEBUG="INFO", NCCL_DEBUG_SUBSYS="NET,INIT", NCCL_DEBUG_FILE=str(tmp_path / "log.%p"))
+    res = run_ranks(_rank, 2, args=([1 << 12],), env=env, timeout=200)
+    assert all(all(res[r][0]) for r in range(2))
+    text = "".join(open(tmp_path / f).read() for f in os.listdir(tmp_path))
+    assert "built-in IB" not in text
+
+
+def test_one_device_selected_by_name(fake_lib, tmp_path):
+    env = dict(BASE, NCCL_B200_IBV_LIB=fake_lib, NCCL_IB_HCA="=fakeib1:1", NCCL_DEBUG="INFO", NCCL_DEBUG_SUBSYS="NET,INIT", NCCL_DEBUG_FILE=str(tmp_path / "log.%p"),
+               NCCL_B200_IB_EAGER_BYTES="256", NCCL_IB_USE_INLINE="0")
+    res = run_ranks(_rank, 2, args=([3, 64, 100, 5000],), env=env, timeout=200)
+    for r in range(2):
+        assert all(res[r][0]) and res[r][1] == 0
+    text = "".join(open(tmp_path / f).read() for f in os.listdir(tmp_path))
+    assert "built-in IB, 1 device(s)" in text and "fakeib1:1" in text and "fakeib0" not in text
