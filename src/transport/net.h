@@ -46,6 +46,8 @@ struct ProxyOp {
   int head = 0, tail = 0;   // ring of requests in flight
   std::atomic<int> state{0};   // 0 running, 1 done, <0 failed (ncclResult_t negated)
   void* profHandle = nullptr;
+  void* mhandle = nullptr;   // the backend's registration of [data, data+bytes), made when the operation starts
+  bool regTried = false;
 };
 
 struct Proxy {

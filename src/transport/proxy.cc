@@ -40,20 +40,36 @@ static void profProxyOp(Proxy* p, ProxyOp* op, bool start) {
   }
 }
 
+// The whole buffer of an operation is registered once with the backend (a no-op for sockets, a memory region for verbs), so
+// that its slices do not register one by one.
+static void opRegister(Proxy* p, ProxyOp* op) {
+  op->regTried = true;
+  void* comm = op->isSend ? p->sendComm[op->peer] : p->recvComm[op->peer];
+  if (!p->net->regMr || !comm || op->bytes == 0) return;
+  if (p->net->regMr(comm, op->data, op->bytes, NCCL_PTR_HOST, &op->mhandle) != ncclSuccess) op->mhandle = nullptr;
+}
+static void opRelease(Proxy* p, ProxyOp* op) {
+  if (!op->mhandle) return;
+  void* comm = op->isSend ? p->sendComm[op->peer] : p->recvComm[op->peer];
+  if (p->net->deregMr && comm) p->net->deregMr(comm, op->mhandle);
+  op->mhandle = nullptr;
+}
+
 static ncclResult_t progressOp(Proxy* p, ProxyOp* op) {
   ncclNet_t* net = p->net;
+  if (!op->regTried) opRegister(p, op);
   // post new slices
   while (op->posted < op->bytes && op->tail - op->head < p->maxInflight) {
     size_t n = std::min(p->sliceBytes, op->bytes - op->posted);
     void* req = nullptr;
     char* ptr = op->data + op->posted;
     if (op->isSend) {
-      NCCLCHECK(net->isend(p->sendComm[op->peer], ptr, n, 0, nullptr, nullptr, &req));
+      NCCLCHECK(net->isend(p->sendComm[op->peer], ptr, n, 0, op->mhandle, nullptr, &req));
     } else {
       void* ptrs[1] = {ptr};
       size_t sizes[1] = {n};
       int tags[1] = {0};
-      void* mh[1] = {nullptr};
+      void* mh[1] = {op->mhandle};
       void* ph[1] = {nullptr};
       NCCLCHECK(net->irecv(p->recvComm[op->peer], 1, ptrs, sizes, tags, mh, ph, &req));
     }
@@ -152,6 +168,7 @@ static void proxyMain(Proxy* p) {
       else if (!blocked) r = progressOp(p, op);
       if (op->completed + op->posted != before) progressed = true;
       if (r != ncclSuccess) {
+        opRelease(p, op);
         profProxyOp(p, op, false);
         op->state.store(-(int)r, std::memory_order_release);
         active.erase(active.begin() + i);
@@ -159,6 +176,7 @@ static void proxyMain(Proxy* p) {
         continue;
       }
       if (!blocked && opFinished(op)) {
+        opRelease(p, op);
         profProxyOp(p, op, false);
         p->opsDone++;
         op->state.store(1, std::memory_order_release);

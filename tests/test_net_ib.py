@@ -76,3 +76,26 @@ def test_one_device_selected_by_name(fake_lib, tmp_path):
         assert all(res[r][0]) and res[r][1] == 0
     text = "".join(open(tmp_path / f).read() for f in os.listdir(tmp_path))
     assert "built-in IB, 1 device(s)" in text and "fakeib1:1" in text and "fakeib0" not in text
+
+
+def _many_rank(rank, nranks, uid):
+    import ctypes
+    from nccl_b200 import Communicator, group
+    comm = Communicator(nranks, rank, uid)
+    peer, src = (rank + 1) % nranks, (rank - 1) % nranks
+    sizes = [1, 3000, 17, 40000, 2048, 2049, 70000, 5] * 12      # 96 messages per direction: the credit table and the eager buffers wrap three times
+    sends = [np.full(n, (i % 97) + rank, dtype=np.float32) for i, n in enumerate(sizes)]
+    recvs = [np.zeros(n, dtype=np.float32) for n in sizes]
+    with group():
+        for s, r in zip(sends, recvs):
+            comm.send(s, peer)
+            comm.recv(r, src)
+    ok = all(bool((r == (i % 97) + src).all()) for i, r in enumerate(recvs))
+    comm.destroy()
+    return ok, ctypes.CDLL(os.environ["NCCL_B200_IBV_LIB"]).fake_ib_errors()
+
+
+def test_many_messages_in_flight_keep_their_order(fake_lib):
+    env = dict(BASE, NCCL_NET="IB", NCCL_B200_IBV_LIB=fake_lib, NCCL_B200_IB_EAGER_BYTES="8192")
+    res = run_ranks(_many_rank, 2, env=env, timeout=300)
+    assert res[0] == (True, 0) and res[1] == (True, 0)
