@@ -14,3 +14,4 @@ Programs written against the reference's bindings keep their spelling::
 Reference parity: bindings/nccl4py/nccl/core/{communicator,group,memory,utils,constants}.py, bindings/nccl4py/nccl/ep/.
 """
 from . import core  # noqa: F401
+from ._show_versions import LibraryInfo, VersionInfo, get_version, show_versions  # noqa: F401

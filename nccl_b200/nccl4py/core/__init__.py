@@ -12,8 +12,8 @@ import contextlib
 import ctypes
 import enum
 
-from .. import _lib
-from .. import core as _core
+from ... import _lib
+from ... import core as _core
 
 __all__ = ["Communicator", "NCCLConfig", "UniqueId", "NcclRedOp", "SUM", "PROD", "MAX", "MIN", "AVG", "NcclCommMemStat", "CommSuspendFlag",
            "WindowFlag", "get_unique_id", "get_version", "group", "group_start", "group_end", "mem_alloc", "mem_free", "NcclError"]
@@ -297,7 +297,7 @@ class Communicator:
         return self.cuda_dev
 
     def _properties(self):
-        from ..ops.devapi import query_properties
+        from ...ops.devapi import query_properties
         return query_properties(self._c)
 
     @property
@@ -389,7 +389,7 @@ class Communicator:
     def create_dev_comm(self, **requirements):
         """A device communicator for kernels written with the device API (``nccl_b200.ops.devapi.DeviceComm`` keywords:
         barriers, ll_blocks, ll_slots, gin_signals, gin_counters, multimem)."""
-        from ..ops.devapi import DeviceComm
+        from ...ops.devapi import DeviceComm
         dc = DeviceComm(self._c, **requirements)
         self._resources.append(type("DevCommResource", (), {"close": lambda s, d=dc: d.destroy()})())
         return dc

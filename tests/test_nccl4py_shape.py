@@ -1,6 +1,7 @@
 """Programs written against the reference's Python bindings run over this library with their spelling
 (``Communicator.init``, ``allreduce(send, recv, op, stream=)``, ``group()``, ...): two host-memory ranks."""
 import numpy as np
+import pytest
 
 from mp_util import run_ranks
 
@@ -147,3 +148,55 @@ def _ep_group_rank(rank, nranks, uid):
         out = "refused"
     comm.destroy()
     return out
+
+
+def test_version_report_names_the_loaded_library(capsys):
+    import nccl_b200.nccl4py as nccl
+    v = nccl.get_version()
+    assert v.nccl is not None and v.nccl.version >= (2, 30, 0) and v.nccl.path.name == "libnccl_b200.so"
+    assert v.nccl.cuda_variant is not None and v.nccl.cuda_variant[0] >= 12
+    assert v.nccl_ep is not None and v.nccl_ep.version >= (0, 1, 0)
+    nccl.show_versions()
+    out = capsys.readouterr().out
+    assert "libnccl" in out and "+cuda" in out and "libnccl_b200.so" in out
+
+
+def test_interop_modules_describe_tensors_and_report_missing_frameworks():
+    import pytest
+    import torch
+    from nccl_b200.nccl4py.core.interop import torch as nt
+    from nccl_b200.nccl4py.core.interop import cupy as nc
+    t = torch.zeros(3, 5, dtype=torch.bfloat16)
+    ptr, n, dt, dev = nt.resolve_tensor(t)
+    assert (ptr, n, dt, dev) == (t.data_ptr(), 15, 9, -1)
+    with pytest.raises(ValueError):
+        nt.resolve_tensor(torch.zeros(4, 4)[:, ::2])
+    with pytest.raises(ValueError):
+        nt.empty(4, morder="X")
+    try:
+        import cupy  # noqa: F401
+    except ImportError:
+        with pytest.raises(ModuleNotFoundError):
+            nc.empty((4,))
+
+
+@pytest.mark.gpu
+def test_torch_tensor_in_library_memory_can_be_registered():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    import nccl_b200.nccl4py.core as nccl
+    from nccl_b200.nccl4py.core.interop import torch as nt
+    x = nt.empty(1024, 256, dtype=torch.float32)
+    f = nt.empty(8, 4, dtype=torch.float16, morder="F")
+    assert x.is_cuda and x.shape == (1024, 256) and x.is_contiguous() and f.stride() == (1, 8)
+    x.fill_(3.0)
+    comm = nccl.Communicator.init(1, 0, nccl.get_unique_id())
+    win = comm.register_window(x)
+    y = nt.empty(1024, 256, dtype=torch.float32)
+    comm.allreduce(x, y, nccl.SUM)
+    torch.cuda.synchronize()
+    assert float(y.sum()) == 3.0 * 1024 * 256
+    win.close()
+    comm.destroy()
+    del x, y, f
