@@ -36,6 +36,7 @@ B200_PARAM(PreloadKernels, "B200_PRELOAD_KERNELS", 1, "Load every collective ker
 B200_PARAM(StagePipeline, "B200_STAGE_PIPELINE", 1, "Reductions on unregistered buffers overlap the copies through the staging area with the kernels (two halves, side stream)")
 B200_PARAM(StagePipelineMin, "B200_STAGE_PIPELINE_MIN", 67108864, "Smallest message in bytes that is pipelined through the staging area")
 B200_PARAM(P2pDirect, "B200_P2P_DIRECT", 1, "Large sends write straight into a receive buffer that lies in a registered window (rendezvous) instead of going through the mailbox")
+B200_PARAM(LLCtas, "B200_LL_CTAS", 0, "CTAs of the flagged-line kernels (0: one per 512 lines, at most 64)")
 B200_PARAM(LaunchPdl, "B200_PDL", 1, "Launch collectives with programmatic stream serialisation (the next kernel of the stream is scheduled while the previous one drains)")
 B200_PARAM(BarrierMulticast, "B200_BARRIER_MC_MIN_RANKS", -1, "Cross-GPU barriers arrive with one multimem.red on a multicast alias of the flag page from this many ranks on (0 = never, -1 = from the selection table)")
 
@@ -503,6 +504,7 @@ static ncclResult_t runReduction(ncclComm* comm, const Task& t) {
       a.scaleMode = op.scaleMode; a.scaleF = op.scaleF; a.scaleD = op.scaleD; a.intDiv = op.intDiv;
       size_t lines = (recvBytes + 7) / 8;
       int ctas = (int)std::min<size_t>((lines + kCtaThreads - 1) / kCtaThreads, 64);
+      if (paramLLCtas() > 0) ctas = (int)std::min<int64_t>(paramLLCtas(), 64);
       return launchColl(comm, llReduceKernelFn(t.type, op.red), &a, std::max(ctas, 1), t.stream, "ONESHOT", "LL");
     }
   }
@@ -775,6 +777,7 @@ static ncclResult_t runCopyColl(ncclComm* comm, const Task& t) {
     a.lrecv[me] = t.recv;
     size_t items = ((B + 7) / 8) * (size_t)(n - 1);
     int ctas = (int)std::min<size_t>((items + kCtaThreads - 1) / kCtaThreads, 64);
+    if (paramLLCtas() > 0) ctas = (int)std::min<int64_t>(paramLLCtas(), 64);
     return launchColl(comm, llCopyKernelFn(), &a, std::max(ctas, 1), t.stream, "ONESHOT", "LL");
   }
   size_t sendBytes = B, recvBytes = B;
