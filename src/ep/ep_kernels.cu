@@ -220,13 +220,24 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
       if (!(mask && mask[dst])) stReleaseSys64(a.recvCount[dst] + cntOff + rank, ((unsigned long long)epoch << 32) | c);
     }
   } else if (sIsLast) {
+    // The count of a destination's LAST local expert is the word its receivers poll: it goes out after the counts of the
+    // other experts (one word to watch per source instead of one per expert and source).
     __threadfence();
     for (int e = threadIdx.x; e < E; e += kEpThreads) {
+      const int dst = e / El, el = e % El;
+      if (el == El - 1) continue;
       const uint32_t c = st[kStCounters + e];
       st[kStCounters + e] = 0;
-      const int dst = e / El, el = e % El;
       if (mask && mask[dst]) continue;
       stReleaseSys64(a.recvCount[dst] + cntOff + (size_t)el * n + rank, ((unsigned long long)epoch << 32) | c);
+    }
+    __threadfence_system();
+    __syncthreads();   // sIsLast is the same for the whole CTA
+    if (threadIdx.x < n) {
+      const int dst = threadIdx.x, e = dst * El + El - 1;
+      const uint32_t c = st[kStCounters + e];
+      st[kStCounters + e] = 0;
+      if (!(mask && mask[dst])) stReleaseSys64(a.recvCount[dst] + cntOff + (size_t)(El - 1) * n + rank, ((unsigned long long)epoch << 32) | c);
     }
   }
   if (!recvPhase) return;   // split-phase call: ncclEpComplete runs the receiving half
@@ -245,7 +256,12 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
       int cnt = 0;
       if (!(mask && mask[threadIdx.x])) {
         const bool quiet = a.enableMask && mask;
-        bool got = boundedWait(w, WAIT_TILE, threadIdx.x, epoch, [&] { v = ldRelaxedSys64((const uint64_t*)c); return (uint32_t)(v >> 32) == epoch; }, !quiet);
+        bool got = boundedWait(w, WAIT_TILE, threadIdx.x, epoch, [&] {
+          v = ldRelaxedSys64((const uint64_t*)c);
+          if ((uint32_t)(v >> 32) == epoch) return true;
+          __nanosleep(200);
+          return false;
+        }, !quiet);
         fenceSys();
         if (got) cnt = (int)(uint32_t)v;
         else if (quiet && !(a.sync.abortFlag && ldRelaxedSys(a.sync.abortFlag))) { mask[threadIdx.x] = 1; cnt = 0; }
@@ -315,17 +331,35 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
     // Every CTA waits for the counts of all (local expert, source) cells (the words are local), then the warps of ALL CTAs
     // share the rows of all experts: the packing is spread over the whole grid, not over one CTA per expert.
     const int cells = El * n;
-    for (int c = threadIdx.x; c < cells; c += kEpThreads) {
-      const int s = c % n;
-      const unsigned long long* cw = a.recvCount[rank] + cntOff + c;
-      unsigned long long v = 0;
-      int cnt = 0;
+    // One thread per source watches the count of the last local expert (the sender writes it after all others), with a pause
+    // between polls: thousands of threads spinning on these words would compete with the rows that are still arriving.
+    if (threadIdx.x < n) {
+      const int s = threadIdx.x;
+      const unsigned long long* cw = a.recvCount[rank] + cntOff + (size_t)(El - 1) * n + s;
+      int state = 0;   // 1: counts are there, 0: source is left out, -1: the wait failed
       if (!(mask && mask[s])) {
         const bool quiet = a.enableMask && mask;
-        bool got = boundedWait(w, WAIT_TILE, (uint32_t)s, epoch, [&] { v = ldRelaxedSys64((const uint64_t*)cw); return (uint32_t)(v >> 32) == epoch; }, !quiet);
-        if (got) cnt = (int)(uint32_t)v;
-        else if (quiet && !(a.sync.abortFlag && ldRelaxedSys(a.sync.abortFlag))) { mask[s] = 1; cnt = 0; }   // left out from now on; the call goes on without it
-        else cnt = -1;
+        unsigned long long v = 0;
+        bool got = boundedWait(w, WAIT_TILE, (uint32_t)s, epoch, [&] {
+          v = ldRelaxedSys64((const uint64_t*)cw);
+          if ((uint32_t)(v >> 32) == epoch) return true;
+          __nanosleep(200);
+          return false;
+        }, !quiet);
+        if (got) state = 1;
+        else if (quiet && !(a.sync.abortFlag && ldRelaxedSys(a.sync.abortFlag))) { mask[s] = 1; state = 0; }   // left out from now on; the call goes on without it
+        else state = -1;
+      }
+      sCnt[s] = state;
+    }
+    fenceSys();
+    __syncthreads();
+    for (int c = threadIdx.x; c < cells; c += kEpThreads) {
+      const int s = c % n;
+      int cnt = sCnt[s] > 0 ? 0 : sCnt[s];
+      if (sCnt[s] > 0) {
+        const unsigned long long v = ldRelaxedSys64((const uint64_t*)(a.recvCount[rank] + cntOff + c));
+        cnt = (uint32_t)(v >> 32) == epoch ? (int)(uint32_t)v : -1;   // written before the word that was polled: anything else is a protocol error
       }
       sCell[c] = cnt;
     }
@@ -402,6 +436,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
 
 __global__ void __launch_bounds__(kEpThreads, 1) epCombineKernel(const __grid_constant__ EpArgs a) {
   __shared__ int sIsLast, sOk;
+  __shared__ int sExpOffC[kEpMaxLocalExperts + 1];
   const int rank = ctaRank(a.emu, a.rank);
   if (a.emu && ((a.absent >> rank) & 1u)) return;
   const int n = a.nRanks, H = a.hidden, K = a.topk, El = a.expertsPerRank;
@@ -438,10 +473,22 @@ __global__ void __launch_bounds__(kEpThreads, 1) epCombineKernel(const __grid_co
       for (; i < packs; i += 32) st16(dst + (size_t)i * 16, ldLocal16(src + (size_t)i * 16));
     }
   }
-  for (int el = 0; sendPhase && a.layout == EP_EXPERT_MAJOR && el < El; ++el) {
-    const int total = a.expertCount[rank][el];
-    for (int pos = blockIdx.x * nWarps + warp; pos < total; pos += gridDim.x * nWarps) {
-      const size_t o = (size_t)el * cap + pos;
+  if (sendPhase && a.layout == EP_EXPERT_MAJOR) {
+    // the rows of all local experts form one list that the warps of all CTAs share (an expert with few rows costs no round of its own)
+    if (threadIdx.x == 0) {
+      int off = 0;
+      for (int el = 0; el < El; ++el) { sExpOffC[el] = off; off += a.expertCount[rank][el]; }
+      sExpOffC[El] = off;
+    }
+    __syncthreads();
+    const int total = sExpOffC[El];
+    for (int g = blockIdx.x * nWarps + warp; g < total; g += gridDim.x * nWarps) {
+      int lo = 0, hi = El - 1;   // the last expert whose first row is <= g
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (sExpOffC[mid] <= g) lo = mid; else hi = mid - 1;
+      }
+      const size_t o = (size_t)lo * cap + (g - sExpOffC[lo]);
       const int2 info = a.srcInfo[rank][o];
       if (mask && mask[info.x]) continue;
       const char* src = (const char*)(y + o * H);
@@ -481,7 +528,11 @@ __global__ void __launch_bounds__(kEpThreads, 1) epCombineKernel(const __grid_co
   if (threadIdx.x < n && !(mask && mask[threadIdx.x])) {
     const unsigned long long* f = a.combFlag[rank] + threadIdx.x;
     const bool quiet = a.enableMask && mask;
-    bool got = boundedWait(w, WAIT_TILE, threadIdx.x, epoch, [&] { return (int32_t)((uint32_t)ldRelaxedSys64((const uint64_t*)f) - epoch) >= 0; }, !quiet);
+    bool got = boundedWait(w, WAIT_TILE, threadIdx.x, epoch, [&] {
+      if ((int32_t)((uint32_t)ldRelaxedSys64((const uint64_t*)f) - epoch) >= 0) return true;
+      __nanosleep(200);   // a pause between polls: every CTA of the rank watches these words while rows are still arriving
+      return false;
+    }, !quiet);
     fenceSys();
     if (!got) {
       if (quiet && !(a.sync.abortFlag && ldRelaxedSys(a.sync.abortFlag))) mask[threadIdx.x] = 1;   // its experts' rows are left out of the sums below
