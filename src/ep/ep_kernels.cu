@@ -434,9 +434,14 @@ __global__ void __launch_bounds__(kEpThreads, 1) epDispatchKernel(const __grid_c
   }
 }
 
+constexpr int kCombStaged = 64;   // tokens of one CTA whose routing is staged in shared memory
+constexpr int kCombMaxK = 16;
+
 __global__ void __launch_bounds__(kEpThreads, 1) epCombineKernel(const __grid_constant__ EpArgs a) {
   __shared__ int sIsLast, sOk;
   __shared__ int sExpOffC[kEpMaxLocalExperts + 1];
+  __shared__ float sCombW[kCombStaged * kCombMaxK];
+  __shared__ unsigned char sCombUse[kCombStaged * kCombMaxK];
   const int rank = ctaRank(a.emu, a.rank);
   if (a.emu && ((a.absent >> rank) & 1u)) return;
   const int n = a.nRanks, H = a.hidden, K = a.topk, El = a.expertsPerRank;
@@ -575,7 +580,23 @@ __global__ void __launch_bounds__(kEpThreads, 1) epCombineKernel(const __grid_co
         *(uint4*)(out + (size_t)t * H + (size_t)c * 8) = o;
       }
     }
-    for (int t = blockIdx.x; a.layout == EP_EXPERT_MAJOR && t < T; t += gridDim.x) {
+    // The routing (which of a token's experts count, and their weights) of the first kCombStaged tokens of this CTA goes to shared
+    // memory first: the loop below then waits for one trip to memory per token (the rows) instead of two (routing, then rows).
+    int staged = 0;
+    if (a.layout == EP_EXPERT_MAJOR && K <= kCombMaxK) {
+      const int mine = T > (int)blockIdx.x ? (T - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+      staged = mine < kCombStaged ? mine : kCombStaged;
+      for (int i = threadIdx.x; i < staged * K; i += kEpThreads) {
+        const int t = (int)blockIdx.x + (i / K) * (int)gridDim.x, k = i % K;
+        const long long e = a.topkIdx[rank][(size_t)t * K + k];
+        const bool use = e >= 0 && e < a.numExperts && !(mask && mask[e / El]);
+        sCombUse[i] = use ? 1 : 0;
+        sCombW[i] = use ? a.topkW[rank][(size_t)t * K + k] : 0.0f;
+      }
+      __syncthreads();
+    }
+    int j = 0;
+    for (int t = blockIdx.x; a.layout == EP_EXPERT_MAJOR && t < T; t += gridDim.x, ++j) {
       for (int c = threadIdx.x; c < H / 8; c += kEpThreads) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         // the rows of up to eight selected experts are fetched together, then accumulated in slot order
@@ -588,9 +609,18 @@ __global__ void __launch_bounds__(kEpThreads, 1) epCombineKernel(const __grid_co
             wk[u] = 0.0f;
             v[u] = make_uint4(0, 0, 0, 0);
             if (k < K) {
-              const long long e = a.topkIdx[rank][(size_t)t * K + k];
-              if (e >= 0 && e < a.numExperts && !(mask && mask[e / El])) {
-                wk[u] = a.topkW[rank][(size_t)t * K + k];
+              bool use;
+              float wgt;
+              if (j < staged) {
+                use = sCombUse[j * K + k] != 0;
+                wgt = sCombW[j * K + k];
+              } else {
+                const long long e = a.topkIdx[rank][(size_t)t * K + k];
+                use = e >= 0 && e < a.numExperts && !(mask && mask[e / El]);
+                wgt = use ? a.topkW[rank][(size_t)t * K + k] : 0.0f;
+              }
+              if (use) {
+                wk[u] = wgt;
                 v[u] = ldLocal16(a.combBuf[rank] + combOff + ((size_t)(t * K + k) * H + (size_t)c * 8) * 2);
               }
             }

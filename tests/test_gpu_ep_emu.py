@@ -24,12 +24,13 @@ def _ptrs(ts):
     return (ctypes.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
 
 
-@pytest.mark.parametrize("n,E,K,H,T", [(2, 4, 2, 128, 5), (4, 8, 2, 256, 16), (8, 32, 4, 512, 33), (8, 256, 8, 1024, 64)])
+@pytest.mark.parametrize("n,E,K,H,T", [(2, 4, 2, 128, 5), (4, 8, 2, 256, 16), (8, 32, 4, 512, 33), (8, 256, 8, 1024, 64), (2, 4, 2, 128, 300)])
 @pytest.mark.parametrize("fp8", [0, 1])
 @pytest.mark.parametrize("bulk", [1, 0])
 def test_dispatch_combine(n, E, K, H, T, fp8, bulk):
     """bulk=1: the packed tokens leave through the bulk-copy engines from a ring of shared-memory stages (33 and 64
-    tokens over 4 CTAs wrap the ring several times); bulk=0: the warps store them."""
+    tokens over 4 CTAs wrap the ring several times); bulk=0: the warps store them. 300 tokens over 4 CTAs: more tokens per
+    CTA than the combine stages routing data for in shared memory, so both of its paths run."""
     if not torch.cuda.is_available():
         pytest.skip("needs a GPU")
     lib = _lib()
