@@ -42,7 +42,8 @@ setup(
     name="nccl_b200",
     version="2.30.7",
     description="Collective communication library for B200 GPUs with the NCCL host API, and its Python bindings",
-    packages=["nccl_b200", "nccl_b200.ops", "nccl_b200.parallel", "nccl_b200.models", "nccl_b200.utils", "nccl_b200.nccl4py"],
+    packages=["nccl_b200", "nccl_b200.ops", "nccl_b200.parallel", "nccl_b200.models", "nccl_b200.utils", "nccl_b200.nccl4py", "nccl_b200.nccl4py.core",
+              "nccl_b200.nccl4py.core.interop"],
     package_data={"nccl_b200": native_files()},
     python_requires=">=3.9",
     cmdclass={"build_py": BuildWithNative},

@@ -37,10 +37,16 @@ B200_PARAM(StagePipeline, "B200_STAGE_PIPELINE", 1, "Reductions on unregistered 
 B200_PARAM(StagePipelineMin, "B200_STAGE_PIPELINE_MIN", 67108864, "Smallest message in bytes that is pipelined through the staging area")
 B200_PARAM(P2pDirect, "B200_P2P_DIRECT", 1, "Large sends write straight into a receive buffer that lies in a registered window (rendezvous) instead of going through the mailbox")
 B200_PARAM(LLCtas, "B200_LL_CTAS", 0, "CTAs of the flagged-line kernels (0: one per 512 lines, at most 64)")
-B200_PARAM(LaunchPdl, "B200_PDL", 1, "Programmatic stream serialisation of collective launches (a kernel is scheduled while the previous one of the stream drains): 0 never, 1 for launches of up to NCCL_B200_PDL_MAX_CTAS CTAs, 2 always")
-B200_PARAM(LaunchPdlMaxCtas, "B200_PDL_MAX_CTAS", 4, "Largest grid that is launched with programmatic stream serialisation: measured between two flagged-line kernels, the gap is 1.5 us against 2.4 us without it for one CTA, about equal at four CTAs, and 3 to 3.5 us from eight CTAs on")
-// Whether a launch of `ctas` CTAs asks for programmatic stream serialisation.
-static inline bool pdlFor(int ctas) { return paramLaunchPdl() == 2 || (paramLaunchPdl() == 1 && ctas <= paramLaunchPdlMaxCtas()); }
+B200_PARAM(LaunchPdl, "B200_PDL", 1, "Programmatic stream serialisation of collective launches (a kernel is scheduled while the previous one of the stream drains): 0 never, 1 yes, but for the flagged-line kernels only up to NCCL_B200_PDL_MAX_CTAS CTAs, 2 always")
+B200_PARAM(LaunchPdlMaxCtas, "B200_PDL_MAX_CTAS", 4, "Largest grid of a flagged-line kernel that is launched with programmatic stream serialisation: measured between two such kernels, the gap is 1.5 us against 2.4 us without it for one CTA, about equal at four CTAs, and 3 to 3.5 us from eight CTAs on")
+// Whether a launch of `ctas` CTAs asks for programmatic stream serialisation. The flagged-line kernels (`shortKernel`) last a few
+// microseconds, so the gap to the next kernel is a large part of a call: there the attribute is dropped for the grids where it
+// was measured to widen the gap. Kernels that run for tens of microseconds and more keep it as they were measured with it.
+static inline bool pdlFor(int ctas, bool shortKernel) {
+  if (paramLaunchPdl() == 2) return true;
+  if (paramLaunchPdl() == 0) return false;
+  return !shortKernel || ctas <= paramLaunchPdlMaxCtas();
+}
 B200_PARAM(BarrierMulticast, "B200_BARRIER_MC_MIN_RANKS", -1, "Cross-GPU barriers arrive with one multimem.red on a multicast alias of the flag page from this many ranks on (0 = never, -1 = from the selection table)")
 
 // ------------------------------------------------------------------------------------ tuning
@@ -385,12 +391,13 @@ static thread_local int tLastCtas = 0;
 
 static ncclResult_t launchColl(ncclComm* comm, const void* fn, CollArgs* a, int ctas, cudaStream_t stream, const char* algo = "P2P",
                                const char* proto = "SIMPLE", int threads = kCtaThreads, size_t smem = 0) {
+  const bool shortKernel = proto && proto[0] == 'L';   // "LL": the flagged-line kernels
   if (!fn) { WARN("no kernel for this data type / operator"); return ncclInvalidUsage; }
   comm->devPlane->launches++;
   tLastAlgo = algo;
   tLastProto = proto;
   tLastCtas = ctas;
-  return launchKernel(fn, dim3(ctas), dim3(threads), smem, a, stream, false, pdlFor(ctas));
+  return launchKernel(fn, dim3(ctas), dim3(threads), smem, a, stream, false, pdlFor(ctas, shortKernel));
 }
 
 static ncclResult_t scaleCopy(ncclComm* comm, ncclDataType_t type, const void* src, void* dst, size_t count, const DevOp& op,
@@ -443,7 +450,7 @@ ncclResult_t devPlaneRunReshard(ncclComm* comm, SymWindow* win, const ReshardRun
   tLastAlgo = "PULL";
   tLastProto = "SIMPLE";
   tLastCtas = ctas;
-  return launchKernel(reshardKernelFn(), dim3(ctas), dim3(kCtaThreads), 0, &a, stream, false, pdlFor(ctas));
+  return launchKernel(reshardKernelFn(), dim3(ctas), dim3(kCtaThreads), 0, &a, stream, false, pdlFor(ctas, false));
 }
 
 // ------------------------------------------------------------------------------------ collectives
@@ -729,7 +736,7 @@ ncclResult_t devPlaneRunLLBatch(ncclComm* comm, const Task* tasks, int count, in
   NCCLCHECK(devPlaneOrderStreams(comm, t0.stream));
   const int ctas = (int)std::min<size_t>(((size_t)lines + kCtaThreads - 1) / kCtaThreads, 64);
   dp->launches++;
-  ncclResult_t r = launchKernel(llReduceBatchKernelFn(t0.type, op.red), dim3(std::max(ctas, 1)), dim3(kCtaThreads), 0, &b, t0.stream, false, pdlFor(std::max(ctas, 1)));
+  ncclResult_t r = launchKernel(llReduceBatchKernelFn(t0.type, op.red), dim3(std::max(ctas, 1)), dim3(kCtaThreads), 0, &b, t0.stream, false, pdlFor(std::max(ctas, 1), true));
   if (cur != comm->cudaDev && cur >= 0) cudaSetDevice(cur);
   *taken = k;
   return r;
@@ -1087,7 +1094,7 @@ ncclResult_t devPlaneRunP2pGroup(ncclComm* comm, const std::vector<Task>& tasks)
       posted[o.isSend ? 0 : 1][o.peer] += (uint32_t)chunks;
     }
     dp->launches++;
-    res = launchKernel(p2pKernelFn(), dim3(cta), dim3(kCtaThreads), 0, &a, stream, false, pdlFor(cta));
+    res = launchKernel(p2pKernelFn(), dim3(cta), dim3(kCtaThreads), 0, &a, stream, false, pdlFor(cta, false));
   }
 out:
   if (cur != comm->cudaDev && cur >= 0) cudaSetDevice(cur);

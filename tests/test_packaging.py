@@ -36,7 +36,7 @@ def test_wheel_carries_the_native_library(tmp_path):
     wheels = [f for f in os.listdir(tmp_path) if f.endswith(".whl")]
     assert len(wheels) == 1 and "none-any" not in wheels[0], wheels   # platform wheel: it holds a shared library
     names = set(zipfile.ZipFile(os.path.join(tmp_path, wheels[0])).namelist())
-    for want in ("nccl_b200/__init__.py", "nccl_b200/core.py", "nccl_b200/ops/ep.py", "nccl_b200/nccl4py/core.py", "nccl_b200/lib/libnccl_b200.so",
+    for want in ("nccl_b200/__init__.py", "nccl_b200/core.py", "nccl_b200/ops/ep.py", "nccl_b200/nccl4py/core/__init__.py", "nccl_b200/nccl4py/core/interop/torch.py", "nccl_b200/nccl4py/ep.py", "nccl_b200/lib/libnccl_b200.so",
                  "nccl_b200/lib/plugins/tuner/csv_tuner.so", "nccl_b200/bin/ncclparam", "nccl_b200/include/nccl.h", "nccl_b200/include/nccl_device/core.h"):
         assert want in names, want
     assert not os.path.exists(os.path.join(ROOT, "nccl_b200.egg-info"))
