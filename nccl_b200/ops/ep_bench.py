@@ -28,6 +28,7 @@ def main(argv=None):
     ap.add_argument("--baseline", action="store_true")
     ap.add_argument("--layout", default="expert_major", choices=["expert_major", "rank_major", "flat"],
                     help="rank_major / flat: one copy of a token per destination rank instead of one per selected expert")
+    ap.add_argument("--phases", action="store_true", help="also time the sending and the receiving half of each call on their own (send_only + complete)")
     a = ap.parse_args(argv)
     from nccl_b200 import Communicator, get_unique_id
     from nccl_b200.ops.ep import ExpertParallel
@@ -74,6 +75,34 @@ def main(argv=None):
     y.zero_()
     comb_ms = timed(lambda: ep.combine(y, out=out))
     both_ms = timed(lambda: (ep.dispatch(x, idx, w, fp8=True, toks=toks, scales=scales, counts=counts), ep.combine(y, out=out)))
+    phases = None
+    if a.phases:
+        # The halves of a call as two kernels: when their sum is far below the time of the whole call, the two sides get in each
+        # other's way inside one kernel (e.g. receivers polling while rows still arrive), not the copies themselves.
+        def halves(first):
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            s_us, r_us = [], []
+            for _ in range(a.warmup + a.iters):
+                if first is ep.combine:
+                    ep.dispatch(x, idx, w, fp8=True, toks=toks, scales=scales, counts=counts)
+                torch.cuda.synchronize()
+                d.barrier()
+                ev[0].record()
+                if first is ep.combine:
+                    ep.combine(y, out=out, send_only=True)
+                else:
+                    ep.dispatch(x, idx, w, fp8=True, toks=toks, scales=scales, counts=counts, send_only=True)
+                ev[1].record()
+                ep.complete()
+                ev[2].record()
+                torch.cuda.synchronize()
+                s_us.append(ev[0].elapsed_time(ev[1]) * 1e3)
+                r_us.append(ev[1].elapsed_time(ev[2]) * 1e3)
+            k = a.warmup
+            return d.max(sum(s_us[k:]) / len(s_us[k:])), d.max(sum(r_us[k:]) / len(r_us[k:]))
+        ds, dr = halves(ep.dispatch)
+        cs, cr = halves(ep.combine)
+        phases = {"dispatch_send_us": ds, "dispatch_receive_us": dr, "combine_send_us": cs, "combine_receive_us": cr}
     recv_max = d.max(float(recv_tokens))
     res = {"metric": "ep_dispatch_combine", "layout": a.layout, "n_gpus": n, "tokens_per_rank": T, "hidden": H, "experts": E, "topk": K,
            "dispatch_us": disp_ms * 1e3, "combine_us": comb_ms * 1e3, "dispatch_plus_combine_us": both_ms * 1e3,
@@ -85,6 +114,8 @@ def main(argv=None):
     res["roofline_fraction"] = {"dispatch": round(res["dispatch_GBps"] * (n - 1) / n / link, 3) if n > 1 else None,
                                 "combine": round(res["combine_GBps"] * (n - 1) / n / link, 3) if n > 1 else None}
     res["peaks"] = {"nvlink_gbs": link}
+    if phases is not None:
+        res["phases"] = phases
     assert comm.async_error() == 0
     ep.destroy()
 
