@@ -36,6 +36,28 @@ void* pluginOpen(PluginKind kind, std::string* resolved) {
     }
     if (v && *v) INFO(SUB_INIT, "%s plugin: could not open %s: %s", kKindNames[kind], t.c_str(), dlerror());
   }
+  // A library may carry several plugins: a tuner that was not asked for by name is looked for in the library that
+  // NCCL_NET_PLUGIN names (the caller then finds its symbol there or not).
+  if (kind == PLUGIN_TUNER && !(v && *v)) {
+    const char* net = envPluginGet(kKindEnv[PLUGIN_NET]);
+    if (net && *net && strcasecmp(net, "none") != 0) {
+      std::string s(net);
+      std::vector<std::string> netTries;
+      if (s.find('/') != std::string::npos || s.find(".so") != std::string::npos) netTries.push_back(s);
+      else { netTries.push_back("libnccl-net-" + s + ".so"); netTries.push_back("libnccl-net.so"); }
+      for (auto& t : netTries) {
+        void* h = dlopen(t.c_str(), RTLD_NOW | RTLD_LOCAL);
+        if (!h) continue;
+        if (dlsym(h, "ncclTunerPlugin_v6") || dlsym(h, "ncclTunerPlugin_v5") || dlsym(h, "ncclTunerPlugin_v4") || dlsym(h, "ncclTunerPlugin_v3") ||
+            dlsym(h, "ncclTunerPlugin_v2")) {
+          if (resolved) *resolved = t;
+          INFO(SUB_INIT, "tuner plugin: found in the network plugin's library %s", t.c_str());
+          return h;
+        }
+        dlclose(h);
+      }
+    }
+  }
   if (v && *v) WARN("%s plugin \"%s\" was requested with %s but could not be loaded; using the built-in implementation", kKindNames[kind], v, kKindEnv[kind]);
   return nullptr;
 }

@@ -190,3 +190,17 @@ def test_gpu_initiated_networking_table_is_reported(tmp_path):
     logs = "".join(open(os.path.join(tmp_path, p)).read() for p in os.listdir(tmp_path) if p.startswith("log."))
     assert "offers GPU-initiated networking UnixExampleGin: 1 device(s), strong signals 1, VA signals 0" in logs
     assert "network backend: plugin UnixExample" in logs
+
+
+def test_one_library_with_network_and_tuner_plugins(tmp_path):
+    """Only NCCL_NET_PLUGIN names the library: the network backend comes from it, and so does the tuner (a tuner that is
+    not named by NCCL_TUNER_PLUGIN is looked for in the network plugin's library)."""
+    conf = tmp_path / "tuner.conf"
+    conf.write_text("allreduce,0,1000000000,ring,simple,2\nallgather,0,4096,ring,ll,-1\n")
+    env = dict(BASE, NCCL_NET_PLUGIN=os.path.join(PLUG, "mixed", "mixed_plugin.so"), NCCL_TUNER_CONFIG_FILE=str(conf), NCCL_DEBUG="INFO",
+               NCCL_DEBUG_SUBSYS="NET,INIT,TUNING", NCCL_DEBUG_FILE=str(tmp_path / "log.%p"))
+    _check(run_ranks(_rank, 2, args=(1,), env=env), 2)
+    text = "".join(open(tmp_path / f).read() for f in os.listdir(tmp_path) if f.startswith("log."))
+    assert "network backend: plugin" in text and "mixed_plugin.so" in text
+    assert "tuner plugin: found in the network plugin's library" in text
+    assert "2 rule" in text     # the tuner's own line after reading the configuration file
