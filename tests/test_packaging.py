@@ -40,3 +40,10 @@ def test_wheel_carries_the_native_library(tmp_path):
                  "nccl_b200/lib/plugins/tuner/csv_tuner.so", "nccl_b200/bin/ncclparam", "nccl_b200/include/nccl.h", "nccl_b200/include/nccl_device/core.h"):
         assert want in names, want
     assert not os.path.exists(os.path.join(ROOT, "nccl_b200.egg-info"))
+
+
+def test_every_example_program_is_built():
+    """`make` turns every examples/*.cu into a program under nccl_b200/bin/examples (they run in the GPU suite)."""
+    src = sorted(f[:-3] for f in os.listdir(os.path.join(ROOT, "examples")) if f.endswith(".cu"))
+    built = set(os.listdir(os.path.join(ROOT, "nccl_b200", "bin", "examples")))
+    assert src and not [s for s in src if s not in built]
