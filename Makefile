@@ -34,7 +34,14 @@ EXAMPLES := $(patsubst examples/%.cu,$(BINDIR)/examples/%,$(wildcard examples/*.
 
 IRLIB := $(LIBDIR)/libnccl_device_c.a
 
-all: $(LIB) $(TOOLS) plugins examples ir
+PERFLOOP := $(LIBDIR)/libperf_loop.so
+
+all: $(LIB) $(TOOLS) plugins examples ir $(PERFLOOP)
+
+# the loop of collective calls that the timing harness runs outside the interpreter (knows no library: entry points come in as addresses)
+$(PERFLOOP): tools/perf_loop.c
+	@mkdir -p $(LIBDIR)
+	$(CC) -O2 -fPIC -shared -fvisibility=hidden $< -o $@
 
 GIT_VERSION := $(shell git describe --always --dirty 2>/dev/null || echo unknown)
 $(BUILD)/src/core/version.o: CXXFLAGS += -DB200_GIT_VERSION='"$(GIT_VERSION)"'

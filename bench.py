@@ -251,7 +251,9 @@ def main():
                        "bytes_per_rank": nbytes, "global_batch": n, "seq_len": nbytes // 2, "parallelism": "dp%d" % n,
                        "buffers": "ncclMemAlloc + ncclCommWindowRegister(NCCL_WIN_COLL_SYMMETRIC)",
                        "l2": "1 GiB per rank per step: inputs larger than the 126 MB L2, no flush needed",
-                       "busbw": "algBW*2(n-1)/n" if n > 1 else "n=1: algBW of the one-rank copy path (the bus factor is 0)"},
+                       "busbw": "algBW*2(n-1)/n" if n > 1 else "n=1: algBW of the one-rank copy path (the bus factor is 0)",
+                       "sweep_call_loop": "C loop over the library's entry points (tools/perf_loop.c), the same for both arms" if h._native_loop() is not None
+                       else "interpreter loop (ctypes call per collective)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "verified": verified, "sweep_time_us_busbw": sweep,
             "sweep_fp32_time_us_busbw": sweep32,
         }

@@ -154,6 +154,48 @@ class Harness:
             return L.ncclGroupEnd()
         raise ValueError(coll)
 
+    _KINDS = {"all_reduce": (0, ("ncclAllReduce",)), "reduce_scatter": (0, ("ncclReduceScatter",)), "all_gather": (1, ("ncclAllGather",)),
+              "all_to_all": (1, ("ncclAlltoAll",)), "broadcast": (2, ("ncclBroadcast",)), "reduce": (3, ("ncclReduce",)),
+              "sendrecv": (4, ("ncclGroupStart", "ncclSend", "ncclRecv", "ncclGroupEnd"))}
+
+    def _native_loop(self):
+        """The loop of calls outside the interpreter (tools/perf_loop.c), or None when it is not built or switched off with
+        NCCL_B200_PERF_PYTHON_LOOP=1. It gets the entry points of the library under test as addresses."""
+        if not hasattr(self, "_loop"):
+            self._loop = None
+            path = os.path.join(os.path.dirname(_lib.LIB_PATH), "libperf_loop.so")
+            if os.environ.get("NCCL_B200_PERF_PYTHON_LOOP", "0") != "1" and os.path.exists(path):
+                try:
+                    fn = ctypes.CDLL(path).perfLoop
+                    fn.restype = ctypes.c_int
+                    fn.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int,
+                                   ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
+                    self._loop = fn
+                except (OSError, AttributeError):
+                    self._loop = None
+        return self._loop
+
+    def calls(self, coll, nbytes, dtype_code, stream_ptr, iters):
+        """Issues `iters` calls of one collective back to back; returns the first result that is not ncclSuccess, else 0."""
+        loop = self._native_loop()
+        if loop is not None and coll in self._KINDS:
+            kind, names = self._KINDS[coll]
+            key = (coll,)
+            if not hasattr(self, "_fns"):
+                self._fns = {}
+            if key not in self._fns:
+                self._fns[key] = (ctypes.c_void_p * len(names))(*[ctypes.cast(getattr(self.lib, nm), ctypes.c_void_p).value for nm in names])
+            es = TYPE_SIZE[dtype_code]
+            count = nbytes // es // (self.n if coll in ("all_gather", "reduce_scatter", "all_to_all") else 1)
+            comm = self.comm if isinstance(self.comm, ctypes.c_void_p) else ctypes.c_void_p(getattr(self.comm, "value", self.comm))
+            return loop(kind, self._fns[key], self.send_ptr, self.recv_ptr, count, dtype_code, 0, 0, (self.rank + 1) % self.n, (self.rank - 1) % self.n,
+                        comm, stream_ptr, iters)
+        for _ in range(iters):
+            r = self.call(coll, nbytes, dtype_code, stream_ptr)
+            if r != 0:
+                return r
+        return 0
+
     def time(self, coll, nbytes, dtype_code=FP32, warmup=20, iters=100, min_warm_ms=3.0, passes=2):
         """Mean device time per call in microseconds (max over ranks). The warm-up covers at least
         `warmup` calls and roughly `min_warm_ms` of device time: after the host-side barrier between
@@ -172,15 +214,13 @@ class Harness:
         try:
             with torch.cuda.stream(self.stream):
                 self.d.barrier()
-                for _ in range(warm):
-                    _lib.check(self.call(coll, nbytes, dtype_code, sp), coll, self.lib)
+                _lib.check(self.calls(coll, nbytes, dtype_code, sp, warm), coll, self.lib)
                 self.stream.synchronize()
                 best = None
                 for _ in range(passes):
                     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     e0.record(self.stream)
-                    for _ in range(iters):
-                        _lib.check(self.call(coll, nbytes, dtype_code, sp), coll, self.lib)
+                    _lib.check(self.calls(coll, nbytes, dtype_code, sp, iters), coll, self.lib)
                     e1.record(self.stream)
                     self.stream.synchronize()
                     us = e0.elapsed_time(e1) * 1000.0 / iters
@@ -197,12 +237,10 @@ class Harness:
         sp = self.stream.cuda_stream
         with torch.cuda.stream(self.stream):
             self.d.barrier()
-            for _ in range(20):
-                _lib.check(self.call(coll, nbytes, dtype_code, sp), coll, self.lib)
+            _lib.check(self.calls(coll, nbytes, dtype_code, sp, 20), coll, self.lib)
             self.stream.synchronize()
             t0 = _time.perf_counter()
-            for _ in range(iters):
-                self.call(coll, nbytes, dtype_code, sp)
+            self.calls(coll, nbytes, dtype_code, sp, iters)
             t1 = _time.perf_counter()
             self.stream.synchronize()
         return self.d.max((t1 - t0) * 1e6 / iters)
