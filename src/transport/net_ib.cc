@@ -20,6 +20,7 @@
 // memory is offered only when a peer-memory kernel module or dma-buf registration is present), resiliency / port fail-over.
 #include <arpa/inet.h>
 #include <dlfcn.h>
+#include <errno.h>
 #include <limits.h>
 #include <poll.h>
 #include <stdlib.h>
@@ -315,6 +316,7 @@ struct Comm {
   std::deque<Request*> waiting;   // receives in order
   std::deque<Arrival> arrived;    // completed receives of the queue pair, in order
   int creditWrites = 0;           // signalled credit writes not yet polled
+  uint32_t idlePolls = 0;         // polls since something last completed (liveness check of the side channel)
 };
 
 struct ListenComm {
@@ -602,6 +604,16 @@ ncclResult_t ibDeregMr(void*, void* mhandle) {
   return ncclSuccess;
 }
 
+// A queue pair says nothing while nothing moves: when the other end's process dies between two messages, a sender waits for a
+// credit and a receiver for data that will never come. The TCP side channel of the connection stays open for its whole life,
+// so its end-of-file is the sign that the peer is gone; it is looked at once in a while when a request makes no progress.
+bool peerGone(Comm* c) {
+  if ((++c->idlePolls & 0x3fff) != 0 || c->sock.fd < 0) return false;
+  char b;
+  ssize_t n = recv(c->sock.fd, &b, 1, MSG_PEEK | MSG_DONTWAIT);
+  return n == 0 || (n < 0 && errno != EAGAIN && errno != EWOULDBLOCK && errno != EINTR);
+}
+
 ncclResult_t ibIsend(void* sendComm, void* data, size_t size, int tag, void* mhandle, void*, void** request) {
   Comm* c = (Comm*)sendComm;
   *request = nullptr;
@@ -629,7 +641,11 @@ ncclResult_t ibIsend(void* sendComm, void* data, size_t size, int tag, void* mha
     }
   } else {
     Credit* cr = &c->credits[slot];
-    if (cr->seq != c->seq + 1) return ncclSuccess;   // the matching receive has not been posted yet
+    if (cr->seq != c->seq + 1) {   // the matching receive has not been posted yet
+      if (peerGone(c)) { WARN("NET/IB : the process at the other end of a connection on %s is gone", c->dev->name.c_str()); c->failed = true; return ncclRemoteError; }
+      return ncclSuccess;
+    }
+    c->idlePolls = 0;
     __sync_synchronize();
     if (size > cr->capacity) { WARN("NET/IB : a send of %zu bytes meets a receive of %u bytes", size, cr->capacity); return ncclInvalidUsage; }
     if (mhandle) sge.lkey = ((MrHandle*)mhandle)->mr->lkey;
@@ -766,7 +782,15 @@ ncclResult_t ibTest(void* request, int* done, int* sizes) {
   Request* r = (Request*)request;
   *done = 0;
   if (!r->done) NCCLCHECK(progress(r->comm));
-  if (!r->done) return ncclSuccess;
+  if (!r->done) {
+    if (peerGone(r->comm)) {
+      WARN("NET/IB : the process at the other end of a connection on %s is gone", r->comm->dev->name.c_str());
+      r->comm->failed = true;
+      return ncclRemoteError;
+    }
+    return ncclSuccess;
+  }
+  r->comm->idlePolls = 0;
   *done = 1;
   if (sizes) sizes[0] = (int)r->size;
   if (r->tmpMr) mrPut(r->comm->dev, r->tmpMr);

@@ -99,3 +99,29 @@ def test_many_messages_in_flight_keep_their_order(fake_lib):
     env = dict(BASE, NCCL_NET="IB", NCCL_B200_IBV_LIB=fake_lib, NCCL_B200_IB_EAGER_BYTES="8192")
     res = run_ranks(_many_rank, 2, env=env, timeout=300)
     assert res[0] == (True, 0) and res[1] == (True, 0)
+
+
+def _peer_leaves(rank, nranks, uid):
+    import time
+    from nccl_b200 import Communicator, _lib
+    comm = Communicator(nranks, rank, uid)
+    x = np.ones(1 << 14, dtype=np.float32)
+    comm.all_reduce(x)          # one good step over the verbs backend
+    if rank == 1:
+        os._exit(0)             # leaves between steps: its queue pairs and sockets are gone
+    t0 = time.time()
+    try:
+        comm.all_reduce(x)
+        return "ok", 0, time.time() - t0
+    except _lib.NcclError as e:
+        return "error", e.code, time.time() - t0
+
+
+def test_peer_that_leaves_turns_into_an_error_over_verbs(fake_lib):
+    """The other end's process is gone: the send completes with an error status (the stand-in reports what a real port reports
+    after its retries run out), the proxy fails the operation and the collective returns an error instead of waiting forever."""
+    env = dict(BASE, NCCL_NET="IB", NCCL_B200_IBV_LIB=fake_lib, NCCL_B200_SOCKET_TIMEOUT_MS="3000")
+    res = run_ranks(_peer_leaves, 2, env=env, timeout=90, may_exit=(1,))
+    status, code, dt = res[0]
+    assert status == "error" and code in (2, 3, 6), res[0]
+    assert dt < 30
