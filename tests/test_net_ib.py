@@ -125,3 +125,27 @@ def test_peer_that_leaves_turns_into_an_error_over_verbs(fake_lib):
     status, code, dt = res[0]
     assert status == "error" and code in (2, 3, 6), res[0]
     assert dt < 30
+
+
+def _two_node_rank(rank, nranks, uid):
+    os.environ["NCCL_HOSTID"] = "node-a" if rank < nranks // 2 else "node-b"   # two ranks per simulated host
+    from nccl_b200 import Communicator
+    comm = Communicator(nranks, rank, uid)
+    x = np.full(50000, rank + 1, dtype=np.float32)
+    y = np.zeros_like(x)
+    comm.all_reduce(x, y)
+    g = np.zeros(nranks * 100, dtype=np.float32)
+    comm.all_gather(x[:100], g)
+    comm.destroy()
+    return float(y[0]), float(y[-1]), [float(g[i * 100]) for i in range(nranks)]
+
+
+def test_ranks_on_two_simulated_hosts_over_verbs(fake_lib, tmp_path):
+    """NCCL_HOSTID gives the ranks two host identities: the communicator counts two nodes with two local ranks each, and its
+    traffic goes through the verbs backend."""
+    env = dict(BASE, NCCL_NET="IB", NCCL_B200_IBV_LIB=fake_lib, NCCL_DEBUG="INFO", NCCL_DEBUG_SUBSYS="INIT,NET", NCCL_DEBUG_FILE=str(tmp_path / "log.%p"))
+    res = run_ranks(_two_node_rank, 4, env=env, timeout=300)
+    for r in range(4):
+        assert res[r] == (10.0, 10.0, [1.0, 2.0, 3.0, 4.0])
+    text = "".join(open(tmp_path / f).read() for f in os.listdir(tmp_path))
+    assert "nodes 2 localRanks 2" in text and "built-in IB" in text
