@@ -559,6 +559,8 @@ ncclResult_t ibAccept(void* listenComm, void** recvComm, ncclNetDeviceHandle_t**
     PeerInfo theirs, mine;
     ncclResult_t r = sockAccept(&c->sock, &lc->sock);
     if (r == ncclSuccess) r = sockRecv(&c->sock, &theirs, sizeof(theirs));
+    // both ends use the smaller of their eager sizes (the receiver posts no credit for a buffer that the sender would fill eagerly)
+    if (r == ncclSuccess && theirs.eagerBytes >= 64) c->eagerBytes = std::min<size_t>(c->eagerBytes, theirs.eagerBytes);
     if (r == ncclSuccess) r = commWire(c, theirs);
     for (int i = 0; i < kSlots && r == ncclSuccess; ++i) r = postBounce(c, i);
     c->remoteCreditAddr = theirs.creditAddr;
