@@ -149,3 +149,16 @@ def test_ranks_on_two_simulated_hosts_over_verbs(fake_lib, tmp_path):
         assert res[r] == (10.0, 10.0, [1.0, 2.0, 3.0, 4.0])
     text = "".join(open(tmp_path / f).read() for f in os.listdir(tmp_path))
     assert "nodes 2 localRanks 2" in text and "built-in IB" in text
+
+
+def _uneven_eager_rank(rank, nranks, uid, sizes):
+    os.environ["NCCL_B200_IB_EAGER_BYTES"] = "512" if rank == 0 else "16384"
+    return _rank(rank, nranks, uid, sizes)
+
+
+def test_ends_with_different_eager_sizes_agree_on_the_smaller(fake_lib):
+    """A message between the two eager sizes must not be sent eagerly by one end and awaited by credit at the other."""
+    env = dict(BASE, NCCL_NET="IB", NCCL_B200_IBV_LIB=fake_lib)
+    res = run_ranks(_uneven_eager_rank, 2, args=([100, 500, 2000, 5000],), env=env, timeout=200)
+    for r in range(2):
+        assert all(res[r][0]) and res[r][1] == 0
