@@ -7,6 +7,10 @@
 // :1713), src/transport/net.cc (sendProxyProgress :1304-1468, recvProxyProgress :1470-1765).
 #include <signal.h>
 
+#include <ctype.h>
+#include <limits.h>
+#include <stdlib.h>
+
 #include "net.h"
 
 #include <sched.h>
@@ -192,6 +196,38 @@ static void proxyMain(Proxy* p) {
   }
 }
 
+// Which device of the backend this rank uses: the one whose PCI path shares the longest prefix with the GPU's (the NIC behind
+// the same switch), and among equals the ranks of a host take turns, so that several NICs carry the traffic of several ranks.
+// Ranks without a GPU, and devices without a PCI path (virtual interfaces), only take turns.
+static int chooseNetDev(ncclComm* comm, ncclNet_t* net, int ndev) {
+  if (ndev <= 1) return 0;
+  char gpuPath[PATH_MAX] = "";
+  if (!comm->hostOnly) {
+    char busId[32], link[PATH_MAX];
+    int64ToBusId(comm->peers[comm->rank].busId, busId);
+    for (char* c = busId; *c; ++c) *c = (char)tolower(*c);
+    snprintf(link, sizeof(link), "/sys/bus/pci/devices/%s", busId);
+    if (!realpath(link, gpuPath)) gpuPath[0] = 0;
+  }
+  std::vector<int> score(ndev, 0);
+  int best = 0;
+  for (int d = 0; d < ndev; ++d) {
+    ncclNetProperties_t props;
+    memset(&props, 0, sizeof(props));
+    if (net->getProperties(d, &props) != ncclSuccess || !props.pciPath || !gpuPath[0]) continue;
+    int common = 0;
+    while (props.pciPath[common] && props.pciPath[common] == gpuPath[common]) ++common;
+    while (common > 0 && props.pciPath[common - 1] != '/') --common;   // whole path components only
+    score[d] = common;
+    best = std::max(best, common);
+  }
+  std::vector<int> nearest;
+  for (int d = 0; d < ndev; ++d) if (score[d] == best) nearest.push_back(d);
+  const int dev = nearest[(size_t)comm->localRank % nearest.size()];
+  INFO(SUB_NET | SUB_INIT, "proxy of rank %d (local rank %d): network device %d of %d", comm->rank, comm->localRank, dev, ndev);
+  return dev;
+}
+
 ncclResult_t proxyCreate(ncclComm* comm) {
   Proxy* p = new Proxy;
   p->comm = comm;
@@ -205,7 +241,7 @@ ncclResult_t proxyCreate(ncclComm* comm) {
     int ndev = 0;
     NCCLCHECKGOTO(p->net->devices(&ndev), res, fail);
     if (ndev <= 0) { WARN("network backend %s has no device", p->net->name); res = ncclSystemError; goto fail; }
-    p->dev = 0;
+    p->dev = chooseNetDev(comm, p->net, ndev);
     p->sliceBytes = (size_t)std::max<int64_t>(paramNetSliceKb(), 4) << 10;
     p->maxInflight = (int)std::min<int64_t>(std::max<int64_t>(paramNetInflight(), 1), NCCL_NET_MAX_REQUESTS);
     std::vector<char> handles((size_t)n * NCCL_NET_HANDLE_MAXSIZE, 0);

@@ -149,6 +149,8 @@ def test_ranks_on_two_simulated_hosts_over_verbs(fake_lib, tmp_path):
         assert res[r] == (10.0, 10.0, [1.0, 2.0, 3.0, 4.0])
     text = "".join(open(tmp_path / f).read() for f in os.listdir(tmp_path))
     assert "nodes 2 localRanks 2" in text and "built-in IB" in text
+    # the two ranks of a host take turns over the two devices
+    assert text.count("network device 0 of 2") == 2 and text.count("network device 1 of 2") == 2
 
 
 def _uneven_eager_rank(rank, nranks, uid, sizes):
