@@ -137,7 +137,7 @@ static ParamRegistrar kStrParams[] = {
     {{"NCCL_IB_HCA", PT_STR, "", "Verbs devices the InfiniBand backend may use: name prefixes with optional :port, comma separated; =name wants the exact name, a leading ^ excludes", true}},
     {{"NCCL_IB_ADDR_FAMILY", PT_STR, "AF_INET", "Address family preferred when the RoCE GID index is chosen automatically: AF_INET or AF_INET6", true}},
     {{"NCCL_B200_IBV_LIB", PT_STR, "libibverbs.so.1", "Verbs library that the InfiniBand backend opens at run time", true}},
-    {{"NCCL_IB_QPS_PER_CONNECTION", PT_STR, "", "No effect: the InfiniBand backend uses one queue pair per connection; the same holds for NCCL_IB_SPLIT_DATA_ON_QPS, NCCL_IB_AR_THRESHOLD, NCCL_IB_MERGE_NICS and the resiliency settings", true}},
+    {{"NCCL_IB_SPLIT_DATA_ON_QPS", PT_STR, "", "No effect: with several queue pairs per connection every RDMA-write message is split over them; NCCL_IB_AR_THRESHOLD, NCCL_IB_MERGE_NICS and the resiliency settings have no effect either", true}},
     {{"NCCL_NET_GDR_LEVEL", PT_STR, "", "No effect: the proxy stages through host memory on the built-in backends; a plugin decides about GPUDirect itself", true}},
     {{"NCCL_MNNVL_CROSS_CLIQUE", PT_STR, "", "No effect: ranks of other fabric cliques are reached through the network transport only", true}},
     {{"NCCL_NTHREADS", PT_STR, "", "No effect: the kernels' CTA sizes are fixed per kernel (512 threads, 32 for the bulk-copy forms)", true}},

@@ -15,9 +15,12 @@
 //     with one RDMA write with immediate (the byte count) straight into the user buffer.
 // Buffers passed without a registration handle are registered on the fly through a reference-counted cache of
 // page-aligned regions per device.
-// Reference parity: src/transport/net_ib/{init,connect,p2p,reg}.cc, src/misc/ibvwrap.cc. Left out: several queue pairs
-// per connection and adaptive-routing splits, grouped receives (maxRecvs is 1), NIC fusion, the GPUDirect flush (device
-// memory is offered only when a peer-memory kernel module or dma-buf registration is present), resiliency / port fail-over.
+// With NCCL_IB_QPS_PER_CONNECTION > 1 a connection has several queue pairs: eager messages and credits stay on the first, a
+// message that travels by RDMA write is cut into one part per queue pair (each with its own write with immediate), and the
+// receiver completes it when every queue pair has delivered its part.
+// Reference parity: src/transport/net_ib/{init,connect,p2p,reg}.cc, src/misc/ibvwrap.cc. Left out: grouped receives (maxRecvs is
+// 1), NIC fusion, the GPUDirect flush (device memory is offered only when a peer-memory kernel module or dma-buf registration is
+// present), resiliency / port fail-over.
 #include <arpa/inet.h>
 #include <dlfcn.h>
 #include <errno.h>
@@ -45,6 +48,7 @@ B200_PARAM(IbSl, "IB_SL", 0, "InfiniBand service level")
 B200_PARAM(IbTc, "IB_TC", 0, "Traffic class of the global route (RoCE)")
 B200_PARAM(IbPkey, "IB_PKEY", 0, "Partition key index")
 B200_PARAM(IbUseInline, "IB_USE_INLINE", 1, "Send messages and credit entries that fit as inline data of the work request")
+B200_PARAM(IbQps, "IB_QPS_PER_CONNECTION", 1, "Queue pairs per connection (1 to 8; both ends use the smaller of their settings): messages that travel by RDMA write are split evenly over them")
 B200_PARAM(IbEagerBytes, "B200_IB_EAGER_BYTES", 8192, "Largest message that travels eagerly (SEND into pre-posted buffers) instead of by receiver-driven RDMA write")
 
 namespace {
@@ -52,6 +56,7 @@ namespace {
 constexpr int kSlots = 32;                 // messages in flight per connection and direction
 constexpr int kMaxReqs = 2 * kSlots;
 constexpr int kMaxIbDevs = 32;
+constexpr int kMaxQps = 8;                // queue pairs of one connection
 constexpr uint64_t kIbMagic = 0x4942564242323030ull;   // "IBVBB200"
 constexpr uint64_t kCreditWrId = ~0ull;    // work-request id of credit-table writes (no request behind them)
 constexpr size_t kPage = 4096;
@@ -262,7 +267,8 @@ struct Handle {              // what listen() hands out; the dialling side keeps
 static_assert(sizeof(Handle) <= NCCL_NET_HANDLE_MAXSIZE, "handle too large");
 
 struct PeerInfo {            // exchanged over the side channel, both directions
-  uint32_t qpn;
+  uint32_t nQps;             // dialling side: what it offers; listening side: what both will use
+  uint32_t qpn[kMaxQps];
   uint16_t lid;
   uint8_t linkLayer, mtu;
   ibv_gid gid;
@@ -285,6 +291,7 @@ struct Request {
   char* data = nullptr;
   ibv_mr* tmpMr = nullptr;   // registered for this request only
   uint32_t seq = 0;
+  int pending = 0;           // send: completions still to come (one per queue pair that carries a part)
 };
 
 struct Arrival { bool eager; uint32_t bytes; uint32_t seq; int buffer; };
@@ -294,7 +301,8 @@ struct Comm {
   bool isSend = false;
   Socket sock;
   ibv_cq* cq = nullptr;
-  ibv_qp* qp = nullptr;
+  ibv_qp* qps[kMaxQps] = {};   // qps[0] carries eager messages, credits and the first part of every RDMA-write message
+  int nQps = 1;
   int maxInline = 0;
   size_t eagerBytes = 0;
   Request reqs[kMaxReqs];
@@ -314,7 +322,7 @@ struct Comm {
   uint64_t remoteCreditAddr = 0;
   uint32_t remoteCreditKey = 0;
   std::deque<Request*> waiting;   // receives in order
-  std::deque<Arrival> arrived;    // completed receives of the queue pair, in order
+  std::deque<Arrival> arrived[kMaxQps];   // completed receives of each queue pair, in order
   int creditWrites = 0;           // signalled credit writes not yet polled
   uint32_t idlePolls = 0;         // polls since something last completed (liveness check of the side channel)
 };
@@ -337,7 +345,7 @@ void* pageAlloc(size_t bytes) {
 
 void commFree(Comm* c) {
   if (!c) return;
-  if (c->qp) ibv.destroy_qp(c->qp);
+  for (ibv_qp* q : c->qps) if (q) ibv.destroy_qp(q);
   if (c->cq) ibv.destroy_cq(c->cq);
   for (auto& r : c->reqs) if (r.used && r.tmpMr) mrPut(c->dev, r.tmpMr);
   for (ibv_mr* m : {c->creditMr, c->stageMr, c->bounceMr, c->outCreditMr}) if (m) ibv.dereg_mr(m);
@@ -352,30 +360,34 @@ ncclResult_t commCreate(IbDev* d, bool isSend, size_t eagerBytes, Comm** out) {
   c->dev = d;
   c->isSend = isSend;
   c->eagerBytes = eagerBytes;
-  c->cq = ibv.create_cq(d->ctx, 4 * kSlots, nullptr, nullptr, 0);
+  c->cq = ibv.create_cq(d->ctx, 4 * kSlots * kMaxQps, nullptr, nullptr, 0);
   if (!c->cq) { WARN("NET/IB : cannot create a completion queue on %s", d->name.c_str()); commFree(c); return ncclSystemError; }
-  ibv_qp_init_attr ia;
-  memset(&ia, 0, sizeof(ia));
-  ia.send_cq = ia.recv_cq = c->cq;
-  ia.qp_type = IBV_QPT_RC;
-  ia.cap.max_send_wr = 2 * kSlots;
-  ia.cap.max_recv_wr = isSend ? 1 : kSlots;
-  ia.cap.max_send_sge = ia.cap.max_recv_sge = 1;
-  ia.cap.max_inline_data = paramIbUseInline() ? (uint32_t)sizeof(Credit) : 0;
-  c->qp = ibv.create_qp(d->pd, &ia);
-  if (!c->qp && ia.cap.max_inline_data) { ia.cap.max_inline_data = 0; c->qp = ibv.create_qp(d->pd, &ia); }
-  if (!c->qp) { WARN("NET/IB : cannot create a queue pair on %s", d->name.c_str()); commFree(c); return ncclSystemError; }
-  c->maxInline = paramIbUseInline() ? (int)ia.cap.max_inline_data : 0;
-  ibv_qp_attr a;
-  memset(&a, 0, sizeof(a));
-  a.qp_state = IBV_QPS_INIT;
-  a.pkey_index = (uint16_t)paramIbPkey();
-  a.port_num = (uint8_t)d->port;
-  a.qp_access_flags = IBV_ACCESS_LOCAL_WRITE | IBV_ACCESS_REMOTE_WRITE;
-  if (ibv.modify_qp(c->qp, &a, IBV_QP_STATE | IBV_QP_PKEY_INDEX | IBV_QP_PORT | IBV_QP_ACCESS_FLAGS) != 0) {
-    WARN("NET/IB : queue pair to INIT failed on %s", d->name.c_str());
-    commFree(c);
-    return ncclSystemError;
+  c->nQps = (int)std::min<int64_t>(std::max<int64_t>(paramIbQps(), 1), kMaxQps);
+  c->maxInline = 0;
+  for (int i = 0; i < c->nQps; ++i) {
+    ibv_qp_init_attr ia;
+    memset(&ia, 0, sizeof(ia));
+    ia.send_cq = ia.recv_cq = c->cq;
+    ia.qp_type = IBV_QPT_RC;
+    ia.cap.max_send_wr = 2 * kSlots;
+    ia.cap.max_recv_wr = isSend ? 1 : kSlots;
+    ia.cap.max_send_sge = ia.cap.max_recv_sge = 1;
+    ia.cap.max_inline_data = paramIbUseInline() && i == 0 ? (uint32_t)sizeof(Credit) : 0;
+    c->qps[i] = ibv.create_qp(d->pd, &ia);
+    if (!c->qps[i] && ia.cap.max_inline_data) { ia.cap.max_inline_data = 0; c->qps[i] = ibv.create_qp(d->pd, &ia); }
+    if (!c->qps[i]) { WARN("NET/IB : cannot create a queue pair on %s", d->name.c_str()); commFree(c); return ncclSystemError; }
+    if (i == 0) c->maxInline = paramIbUseInline() ? (int)ia.cap.max_inline_data : 0;
+    ibv_qp_attr a;
+    memset(&a, 0, sizeof(a));
+    a.qp_state = IBV_QPS_INIT;
+    a.pkey_index = (uint16_t)paramIbPkey();
+    a.port_num = (uint8_t)d->port;
+    a.qp_access_flags = IBV_ACCESS_LOCAL_WRITE | IBV_ACCESS_REMOTE_WRITE;
+    if (ibv.modify_qp(c->qps[i], &a, IBV_QP_STATE | IBV_QP_PKEY_INDEX | IBV_QP_PORT | IBV_QP_ACCESS_FLAGS) != 0) {
+      WARN("NET/IB : queue pair to INIT failed on %s", d->name.c_str());
+      commFree(c);
+      return ncclSystemError;
+    }
   }
   const int plain = IBV_ACCESS_LOCAL_WRITE, remote = IBV_ACCESS_LOCAL_WRITE | IBV_ACCESS_REMOTE_WRITE;
   bool ok = true;
@@ -397,7 +409,8 @@ ncclResult_t commCreate(IbDev* d, bool isSend, size_t eagerBytes, Comm** out) {
 
 void myInfo(Comm* c, PeerInfo* pi) {
   memset(pi, 0, sizeof(*pi));
-  pi->qpn = c->qp->qp_num;
+  pi->nQps = (uint32_t)c->nQps;
+  for (int i = 0; i < c->nQps; ++i) pi->qpn[i] = c->qps[i]->qp_num;
   pi->lid = c->dev->attr.lid;
   pi->linkLayer = c->dev->attr.link_layer;
   pi->mtu = (uint8_t)c->dev->attr.active_mtu;
@@ -409,38 +422,42 @@ void myInfo(Comm* c, PeerInfo* pi) {
 ncclResult_t commWire(Comm* c, const PeerInfo& peer) {
   IbDev* d = c->dev;
   if (peer.linkLayer != d->attr.link_layer) { WARN("NET/IB : %s is %s and the peer's port is not", d->name.c_str(), d->attr.link_layer == IBV_LINK_LAYER_ETHERNET ? "RoCE" : "InfiniBand"); return ncclSystemError; }
-  ibv_qp_attr a;
-  memset(&a, 0, sizeof(a));
-  a.qp_state = IBV_QPS_RTR;
-  a.path_mtu = std::min<int>(d->attr.active_mtu, peer.mtu);
-  a.dest_qp_num = peer.qpn;
-  a.rq_psn = 0;
-  a.max_dest_rd_atomic = 1;
-  a.min_rnr_timer = 12;
-  a.ah_attr.port_num = (uint8_t)d->port;
-  a.ah_attr.sl = (uint8_t)paramIbSl();
-  a.ah_attr.dlid = peer.lid;
-  if (d->attr.link_layer == IBV_LINK_LAYER_ETHERNET || peer.gid.global.subnet_prefix != d->gid.global.subnet_prefix) {
-    a.ah_attr.is_global = 1;
-    a.ah_attr.grh.dgid = peer.gid;
-    a.ah_attr.grh.sgid_index = (uint8_t)d->gidIndex;
-    a.ah_attr.grh.hop_limit = 255;
-    a.ah_attr.grh.traffic_class = (uint8_t)paramIbTc();
-  }
-  if (ibv.modify_qp(c->qp, &a, IBV_QP_STATE | IBV_QP_AV | IBV_QP_PATH_MTU | IBV_QP_DEST_QPN | IBV_QP_RQ_PSN | IBV_QP_MAX_DEST_RD_ATOMIC | IBV_QP_MIN_RNR_TIMER) != 0) {
-    WARN("NET/IB : queue pair to RTR failed on %s", d->name.c_str());
-    return ncclSystemError;
-  }
-  memset(&a, 0, sizeof(a));
-  a.qp_state = IBV_QPS_RTS;
-  a.timeout = (uint8_t)paramIbTimeout();
-  a.retry_cnt = (uint8_t)paramIbRetryCnt();
-  a.rnr_retry = 7;
-  a.sq_psn = 0;
-  a.max_rd_atomic = 1;
-  if (ibv.modify_qp(c->qp, &a, IBV_QP_STATE | IBV_QP_TIMEOUT | IBV_QP_RETRY_CNT | IBV_QP_RNR_RETRY | IBV_QP_SQ_PSN | IBV_QP_MAX_QP_RD_ATOMIC) != 0) {
-    WARN("NET/IB : queue pair to RTS failed on %s", d->name.c_str());
-    return ncclSystemError;
+  // both ends use the smaller number of queue pairs; the ones beyond it stay unconnected until the connection is closed
+  c->nQps = (int)std::min<uint32_t>((uint32_t)c->nQps, std::max<uint32_t>(peer.nQps, 1));
+  for (int i = 0; i < c->nQps; ++i) {
+    ibv_qp_attr a;
+    memset(&a, 0, sizeof(a));
+    a.qp_state = IBV_QPS_RTR;
+    a.path_mtu = std::min<int>(d->attr.active_mtu, peer.mtu);
+    a.dest_qp_num = peer.qpn[i];
+    a.rq_psn = 0;
+    a.max_dest_rd_atomic = 1;
+    a.min_rnr_timer = 12;
+    a.ah_attr.port_num = (uint8_t)d->port;
+    a.ah_attr.sl = (uint8_t)paramIbSl();
+    a.ah_attr.dlid = peer.lid;
+    if (d->attr.link_layer == IBV_LINK_LAYER_ETHERNET || peer.gid.global.subnet_prefix != d->gid.global.subnet_prefix) {
+      a.ah_attr.is_global = 1;
+      a.ah_attr.grh.dgid = peer.gid;
+      a.ah_attr.grh.sgid_index = (uint8_t)d->gidIndex;
+      a.ah_attr.grh.hop_limit = 255;
+      a.ah_attr.grh.traffic_class = (uint8_t)paramIbTc();
+    }
+    if (ibv.modify_qp(c->qps[i], &a, IBV_QP_STATE | IBV_QP_AV | IBV_QP_PATH_MTU | IBV_QP_DEST_QPN | IBV_QP_RQ_PSN | IBV_QP_MAX_DEST_RD_ATOMIC | IBV_QP_MIN_RNR_TIMER) != 0) {
+      WARN("NET/IB : queue pair to RTR failed on %s", d->name.c_str());
+      return ncclSystemError;
+    }
+    memset(&a, 0, sizeof(a));
+    a.qp_state = IBV_QPS_RTS;
+    a.timeout = (uint8_t)paramIbTimeout();
+    a.retry_cnt = (uint8_t)paramIbRetryCnt();
+    a.rnr_retry = 7;
+    a.sq_psn = 0;
+    a.max_rd_atomic = 1;
+    if (ibv.modify_qp(c->qps[i], &a, IBV_QP_STATE | IBV_QP_TIMEOUT | IBV_QP_RETRY_CNT | IBV_QP_RNR_RETRY | IBV_QP_SQ_PSN | IBV_QP_MAX_QP_RD_ATOMIC) != 0) {
+      WARN("NET/IB : queue pair to RTS failed on %s", d->name.c_str());
+      return ncclSystemError;
+    }
   }
   return ncclSuccess;
 }
@@ -452,7 +469,16 @@ ncclResult_t postBounce(Comm* c, int i) {
   wr.wr_id = (uint64_t)i;
   wr.sg_list = &sge;
   wr.num_sge = 1;
-  if (ibv_post_recv(c->qp, &wr, &bad) != 0) { WARN("NET/IB : posting a receive failed"); return ncclSystemError; }
+  if (ibv_post_recv(c->qps[0], &wr, &bad) != 0) { WARN("NET/IB : posting a receive failed"); return ncclSystemError; }
+  return ncclSuccess;
+}
+
+// Queue pairs beyond the first only carry RDMA writes with immediate: their receives have no buffer.
+ncclResult_t postEmpty(Comm* c, int qp, int i) {
+  ibv_recv_wr wr, *bad = nullptr;
+  memset(&wr, 0, sizeof(wr));
+  wr.wr_id = (uint64_t)i;
+  if (ibv_post_recv(c->qps[qp], &wr, &bad) != 0) { WARN("NET/IB : posting a receive failed"); return ncclSystemError; }
   return ncclSuccess;
 }
 
@@ -563,6 +589,8 @@ ncclResult_t ibAccept(void* listenComm, void** recvComm, ncclNetDeviceHandle_t**
     if (r == ncclSuccess && theirs.eagerBytes >= 64) c->eagerBytes = std::min<size_t>(c->eagerBytes, theirs.eagerBytes);
     if (r == ncclSuccess) r = commWire(c, theirs);
     for (int i = 0; i < kSlots && r == ncclSuccess; ++i) r = postBounce(c, i);
+    for (int q = 1; q < c->nQps; ++q)
+      for (int i = 0; i < kSlots && r == ncclSuccess; ++i) r = postEmpty(c, q, i);
     c->remoteCreditAddr = theirs.creditAddr;
     c->remoteCreditKey = theirs.creditKey;
     myInfo(c, &mine);
@@ -665,11 +693,26 @@ ncclResult_t ibIsend(void* sendComm, void* data, size_t size, int tag, void* mha
   r->seq = c->seq;
   wr.wr_id = (uint64_t)(r - c->reqs);
   (void)tag;
-  if (ibv_post_send(c->qp, &wr, &bad) != 0) {
-    WARN("NET/IB : posting a send of %zu bytes failed", size);
-    if (tmp) mrPut(c->dev, tmp);
-    r->used = false;
-    return ncclSystemError;
+  const int parts = wr.opcode == IBV_WR_RDMA_WRITE_WITH_IMM ? c->nQps : 1;
+  r->pending = parts;
+  // a message that travels by RDMA write is cut into one part per queue pair (the later ones may be empty: every queue pair
+  // sees exactly one write with immediate per such message, which is what the receiver counts); the first carries the size
+  const size_t per = parts > 1 ? ((size + parts - 1) / parts + 127) & ~(size_t)127 : size;
+  for (int q = 0; q < parts; ++q) {
+    if (parts > 1) {
+      const size_t off = std::min(size, (size_t)q * per), len = std::min(per, size - off);
+      sge.addr = (uint64_t)(uintptr_t)data + off;
+      sge.length = (uint32_t)len;
+      wr.num_sge = len ? 1 : 0;
+      wr.wr.rdma.remote_addr = c->credits[slot].addr + off;
+      wr.imm_data = htonl(q == 0 ? (uint32_t)size : (uint32_t)len);
+    }
+    if (ibv_post_send(c->qps[q], &wr, &bad) != 0) {
+      WARN("NET/IB : posting a send of %zu bytes failed", size);
+      c->failed = true;   // parts already posted cannot be taken back
+      if (q == 0) { if (tmp) mrPut(c->dev, tmp); r->used = false; }
+      return ncclSystemError;
+    }
   }
   c->seq++;
   c->inflight++;
@@ -714,7 +757,7 @@ ncclResult_t ibIrecv(void* recvComm, int n, void** data, size_t* sizes, int* tag
     wr.send_flags = IBV_SEND_SIGNALED | ((int)sizeof(Credit) <= c->maxInline ? IBV_SEND_INLINE : 0);
     wr.wr.rdma.remote_addr = c->remoteCreditAddr + (uint64_t)slot * sizeof(Credit);
     wr.wr.rdma.rkey = c->remoteCreditKey;
-    if (ibv_post_send(c->qp, &wr, &bad) != 0) {
+    if (ibv_post_send(c->qps[0], &wr, &bad) != 0) {
       WARN("NET/IB : posting a credit failed");
       if (r->tmpMr) mrPut(c->dev, r->tmpMr);
       r->used = false;
@@ -748,33 +791,48 @@ ncclResult_t progress(Comm* c) {
         return ncclRemoteError;
       }
       if (wc.opcode & IBV_WC_RECV) {
+        int q = 0;
+        while (q < c->nQps && c->qps[q]->qp_num != wc.qp_num) ++q;
+        if (q == c->nQps) { WARN("NET/IB : completion of an unknown queue pair %u", wc.qp_num); c->failed = true; return ncclInternalError; }
         Arrival a;
         a.eager = wc.opcode == IBV_WC_RECV;
         a.bytes = a.eager ? wc.byte_len : ntohl(wc.imm_data);
         a.seq = a.eager ? ntohl(wc.imm_data) : 0;
         a.buffer = (int)wc.wr_id;
-        c->arrived.push_back(a);
+        c->arrived[q].push_back(a);
       } else if (wc.wr_id == kCreditWrId) {
         c->creditWrites--;
       } else if (wc.wr_id < (uint64_t)kMaxReqs) {
         Request* r = &c->reqs[wc.wr_id];
-        r->done = true;
-        c->inflight--;
+        if (--r->pending <= 0) {
+          r->done = true;
+          c->inflight--;
+        }
       }
     }
   }
-  while (!c->isSend && !c->arrived.empty() && !c->waiting.empty()) {
-    Arrival a = c->arrived.front();
+  // The oldest receive meets the oldest arrival of the first queue pair; a message that came by RDMA write is complete once
+  // every other queue pair has delivered its part of it as well (their arrivals are in message order too).
+  while (!c->isSend && !c->arrived[0].empty() && !c->waiting.empty()) {
+    Arrival a = c->arrived[0].front();
     Request* r = c->waiting.front();
     if (a.eager) {
       if (a.seq != r->seq) { WARN("NET/IB : eager message %u arrived where %u was expected", a.seq, r->seq); c->failed = true; return ncclInternalError; }
       if (a.bytes > r->size) { WARN("NET/IB : a message of %u bytes meets a receive of %zu bytes", a.bytes, r->size); c->failed = true; return ncclInvalidUsage; }
       if (a.bytes) memcpy(r->data, c->bounce + (size_t)a.buffer * c->eagerBytes, a.bytes);
+    } else {
+      bool all = true;
+      for (int q = 1; q < c->nQps; ++q) all = all && !c->arrived[q].empty();
+      if (!all) break;
+      for (int q = 1; q < c->nQps; ++q) {
+        NCCLCHECK(postEmpty(c, q, c->arrived[q].front().buffer));
+        c->arrived[q].pop_front();
+      }
     }
     NCCLCHECK(postBounce(c, a.buffer));
     r->size = a.bytes;
     r->done = true;
-    c->arrived.pop_front();
+    c->arrived[0].pop_front();
     c->waiting.pop_front();
   }
   return ncclSuccess;

@@ -164,3 +164,24 @@ def test_ends_with_different_eager_sizes_agree_on_the_smaller(fake_lib):
     res = run_ranks(_uneven_eager_rank, 2, args=([100, 500, 2000, 5000],), env=env, timeout=200)
     for r in range(2):
         assert all(res[r][0]) and res[r][1] == 0
+
+
+def _qps_rank(rank, nranks, uid, sizes, per_rank):
+    os.environ["NCCL_IB_QPS_PER_CONNECTION"] = str(per_rank[rank])
+    return _rank(rank, nranks, uid, sizes)
+
+
+@pytest.mark.parametrize("per_rank", [(4, 4, 4), (8, 2, 3)])
+def test_messages_split_over_several_queue_pairs(fake_lib, per_rank):
+    """RDMA-write messages are cut into one part per queue pair; ends that ask for different numbers use the smaller one.
+    Sizes: eager, just above eager (parts of the tail are empty), a size that does not divide evenly, several slices."""
+    env = dict(BASE, NCCL_NET="IB", NCCL_B200_IBV_LIB=fake_lib)
+    res = run_ranks(_qps_rank, 3, args=([3, 2100, 33333, 1 << 20], per_rank), env=env, timeout=300)
+    for r in range(3):
+        assert all(res[r][0]) and res[r][1] == 0, res[r]
+
+
+def test_many_messages_over_several_queue_pairs(fake_lib):
+    env = dict(BASE, NCCL_NET="IB", NCCL_B200_IBV_LIB=fake_lib, NCCL_IB_QPS_PER_CONNECTION="3")
+    res = run_ranks(_many_rank, 2, env=env, timeout=300)
+    assert res[0] == (True, 0) and res[1] == (True, 0)
