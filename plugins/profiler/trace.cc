@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "plugin/nccl_profiler.h"
+#include "plugin/nccl_profiler_net.h"
 
 namespace {
 
@@ -89,6 +90,22 @@ ncclResult_t pStart(void* context, void** handle, ncclProfilerEventDescr_t* d) {
   } else if (d->type == ncclProfileKernelCh) {
     e->name = kindName(d->type);
     snprintf(buf, sizeof(buf), "\"channel\":%d,\"gpu_start_ns\":%llu", d->kernelCh.channelId, (unsigned long long)d->kernelCh.pTimer);
+  } else if (d->type == ncclProfileNetPlugin) {
+    // the backend's own record: which backend and which version of its record is in the plugin id
+    const unsigned id = (unsigned)d->netPlugin.id, ver = id & NCCL_PROFILER_NET_VER_MASK;
+    if ((id & NCCL_PROFILER_NET_TYPE_MASK) == NCCL_PROFILER_NET_TYPE_IB && ver == NCCL_PROFILER_NET_IB_VER && d->netPlugin.data) {
+      const ncclProfilerNetIbDescr_v1_t* n = (const ncclProfilerNetIbDescr_v1_t*)d->netPlugin.data;
+      e->name = "NetIb Qp";
+      snprintf(buf, sizeof(buf), "\"device\":%d,\"qp\":%d,\"opcode\":%d,\"wr_id\":%llu,\"bytes\":%zu", n->qp.device, n->qp.qpNum, n->qp.opcode,
+               (unsigned long long)n->qp.wr_id, n->qp.length);
+    } else if ((id & NCCL_PROFILER_NET_TYPE_MASK) == NCCL_PROFILER_NET_TYPE_SOCK && ver == NCCL_PROFILER_NET_SOCKET_VER && d->netPlugin.data) {
+      const ncclProfilerNetSockDescr_v1_t* n = (const ncclProfilerNetSockDescr_v1_t*)d->netPlugin.data;
+      e->name = n->sock.op ? "NetSock Recv" : "NetSock Send";
+      snprintf(buf, sizeof(buf), "\"fd\":%d,\"bytes\":%zu", n->sock.fd, n->sock.length);
+    } else {
+      e->name = kindName(d->type);
+      snprintf(buf, sizeof(buf), "\"plugin_id\":%u", id);
+    }
   } else {
     e->name = kindName(d->type);
   }

@@ -75,6 +75,11 @@ ncclResult_t profilerLoad(ncclComm* comm);
 void profilerUnload(ncclComm* comm);
 void* profStart(ncclComm* comm, ncclProfilerEventDescr_t* d);   // nullptr when the type is not enabled
 void profStop(ncclComm* comm, void* handle);
+// What the proxy hands to a network backend as the profiler handle of a send / receive (`phandle`): the backend passes it back
+// through the callback below when it starts an event of its own, which then hangs under `parent`.
+struct ProfNetParent { ncclComm* comm; void* parent; };
+// The ncclProfilerCallback_t given to network backends at init (start / stop / update of ncclProfileNetPlugin events).
+ncclResult_t profilerNetCallback(void** eHandle, int type, void* pHandle, int64_t pluginId, void* extData);
 void profState(ncclComm* comm, void* handle, ncclProfilerEventState_t st, ncclProfilerEventStateArgs_t* a);
 // Task events of the data plane (profiler_plugin.cc).
 void* profilerTaskStart(ncclComm* comm, const Task& t);

@@ -147,6 +147,41 @@ void profState(ncclComm* comm, void* h, ncclProfilerEventState_t st, ncclProfile
   if (h && comm->profiler && comm->profiler->prof->recordEventState) comm->profiler->prof->recordEventState(h, st, a);
 }
 
+// ---- events of network backends
+// A handle of such an event remembers its communicator (stop and update arrive with the handle only).
+struct NetEvent { ncclComm* comm; void* handle; };
+ncclResult_t profilerNetCallback(void** eHandle, int type, void* pHandle, int64_t pluginId, void* extData) {
+  if (!eHandle) return ncclSuccess;
+  if (type == ncclProfilerNetEventStart) {
+    *eHandle = nullptr;
+    ProfNetParent* pp = (ProfNetParent*)pHandle;
+    if (!pp || !pp->comm || !pp->comm->profiler) return ncclSuccess;
+    ncclProfilerEventDescr_t d;
+    memset(&d, 0, sizeof(d));
+    d.type = ncclProfileNetPlugin;
+    d.parentObj = pp->parent;
+    d.netPlugin.id = pluginId;
+    d.netPlugin.data = extData;
+    void* h = profStart(pp->comm, &d);
+    if (h) *eHandle = new NetEvent{pp->comm, h};
+    return ncclSuccess;
+  }
+  NetEvent* ev = (NetEvent*)*eHandle;
+  if (!ev) return ncclSuccess;
+  if (type == ncclProfilerNetEventUpdate || type == ncclProfilerNetEventUpdateAndStop) {
+    ncclProfilerEventStateArgs_t a;
+    memset(&a, 0, sizeof(a));
+    a.netPlugin.data = extData;
+    profState(ev->comm, ev->handle, ncclProfilerNetPluginUpdate, &a);
+  }
+  if (type == ncclProfilerNetEventStop || type == ncclProfilerNetEventUpdateAndStop) {
+    profStop(ev->comm, ev->handle);
+    delete ev;
+    *eHandle = nullptr;
+  }
+  return ncclSuccess;
+}
+
 // ---- copy-engine collectives
 // Reference parity: CeColl / CeSync / CeBatch events of src/ce_coll.cc:133-285, :497-717.
 void* profilerCeStart(ncclComm* comm, const Task& t, int what, void* parent, int numOps, size_t totalBytes) {

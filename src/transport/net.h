@@ -12,7 +12,9 @@
 #include <vector>
 
 #include "../comm/comm.h"
+#include "../plugin/plugin.h"
 #include "plugin/nccl_net.h"
+#include "plugin/nccl_profiler_net.h"
 
 namespace b200 {
 
@@ -46,6 +48,7 @@ struct ProxyOp {
   int head = 0, tail = 0;   // ring of requests in flight
   std::atomic<int> state{0};   // 0 running, 1 done, <0 failed (ncclResult_t negated)
   void* profHandle = nullptr;
+  ProfNetParent profParent = {nullptr, nullptr};   // handed to the backend with every slice of this operation
   void* mhandle = nullptr;   // the backend's registration of [data, data+bytes), made when the operation starts
   bool regTried = false;
 };

@@ -63,6 +63,7 @@ constexpr size_t kPage = 4096;
 
 IbvApi ibv;
 ncclDebugLogger_t gLog = nullptr;
+ncclProfilerCallback_t gProf = nullptr;
 
 struct MrEntry { uintptr_t start; size_t bytes; ibv_mr* mr; int refs; };
 
@@ -292,6 +293,8 @@ struct Request {
   ibv_mr* tmpMr = nullptr;   // registered for this request only
   uint32_t seq = 0;
   int pending = 0;           // send: completions still to come (one per queue pair that carries a part)
+  void* prof = nullptr;      // event of this request at the profiler
+  ncclProfilerNetIbDescr_v1_t profDescr;
 };
 
 struct Arrival { bool eager; uint32_t bytes; uint32_t seq; int buffer; };
@@ -347,7 +350,10 @@ void commFree(Comm* c) {
   if (!c) return;
   for (ibv_qp* q : c->qps) if (q) ibv.destroy_qp(q);
   if (c->cq) ibv.destroy_cq(c->cq);
-  for (auto& r : c->reqs) if (r.used && r.tmpMr) mrPut(c->dev, r.tmpMr);
+  for (auto& r : c->reqs) {
+    if (r.used && r.prof && gProf) gProf(&r.prof, ncclProfilerNetEventStop, nullptr, 0, nullptr);
+    if (r.used && r.tmpMr) mrPut(c->dev, r.tmpMr);
+  }
   for (ibv_mr* m : {c->creditMr, c->stageMr, c->bounceMr, c->outCreditMr}) if (m) ibv.dereg_mr(m);
   free(c->credits); free(c->stage); free(c->bounce); free(c->outCredits);
   sockClose(&c->sock);
@@ -488,8 +494,9 @@ Request* reqGet(Comm* c) {
   return nullptr;
 }
 
-ncclResult_t ibInit(void** ctx, uint64_t, ncclNetCommConfig_t*, ncclDebugLogger_t log, ncclProfilerCallback_t) {
+ncclResult_t ibInit(void** ctx, uint64_t, ncclNetCommConfig_t*, ncclDebugLogger_t log, ncclProfilerCallback_t prof) {
   gLog = log;
+  if (prof) gProf = prof;
   loadDevices();
   if (ctx) *ctx = nullptr;
   return ncclSuccess;
@@ -634,6 +641,18 @@ ncclResult_t ibDeregMr(void*, void* mhandle) {
   return ncclSuccess;
 }
 
+// One profiler event per request: the work request on the first queue pair stands for the message.
+void profRequest(Request* r, void* phandle, int opcode, size_t length) {
+  if (!gProf || !phandle) return;
+  r->profDescr.type = ncclProfileQp;
+  r->profDescr.qp.device = (int)(r->comm->dev - gDevs);
+  r->profDescr.qp.wr_id = (uint64_t)(r - r->comm->reqs);
+  r->profDescr.qp.opcode = opcode;
+  r->profDescr.qp.qpNum = (int)r->comm->qps[0]->qp_num;
+  r->profDescr.qp.length = length;
+  gProf(&r->prof, ncclProfilerNetEventStart, phandle, NCCL_PROFILER_NET_TYPE_IB | NCCL_PROFILER_NET_IB_VER, &r->profDescr);
+}
+
 // A queue pair says nothing while nothing moves: when the other end's process dies between two messages, a sender waits for a
 // credit and a receiver for data that will never come. The TCP side channel of the connection stays open for its whole life,
 // so its end-of-file is the sign that the peer is gone; it is looked at once in a while when a request makes no progress.
@@ -644,7 +663,7 @@ bool peerGone(Comm* c) {
   return n == 0 || (n < 0 && errno != EAGAIN && errno != EWOULDBLOCK && errno != EINTR);
 }
 
-ncclResult_t ibIsend(void* sendComm, void* data, size_t size, int tag, void* mhandle, void*, void** request) {
+ncclResult_t ibIsend(void* sendComm, void* data, size_t size, int tag, void* mhandle, void* phandle, void** request) {
   Comm* c = (Comm*)sendComm;
   *request = nullptr;
   if (c->failed) return ncclRemoteError;
@@ -714,13 +733,14 @@ ncclResult_t ibIsend(void* sendComm, void* data, size_t size, int tag, void* mha
       return ncclSystemError;
     }
   }
+  profRequest(r, phandle, wr.opcode, size);
   c->seq++;
   c->inflight++;
   *request = r;
   return ncclSuccess;
 }
 
-ncclResult_t ibIrecv(void* recvComm, int n, void** data, size_t* sizes, int* tags, void** mhandles, void**, void** request) {
+ncclResult_t ibIrecv(void* recvComm, int n, void** data, size_t* sizes, int* tags, void** mhandles, void** phandles, void** request) {
   Comm* c = (Comm*)recvComm;
   *request = nullptr;
   if (n != 1) { WARN("NET/IB : grouped receives are not offered (maxRecvs is 1)"); return ncclInvalidArgument; }
@@ -765,6 +785,7 @@ ncclResult_t ibIrecv(void* recvComm, int n, void** data, size_t* sizes, int* tag
     }
     c->creditWrites++;
   }
+  profRequest(r, phandles ? phandles[0] : nullptr, IBV_WC_RECV, sizes[0]);
   c->seq++;
   c->waiting.push_back(r);
   *request = r;
@@ -853,6 +874,7 @@ ncclResult_t ibTest(void* request, int* done, int* sizes) {
   r->comm->idlePolls = 0;
   *done = 1;
   if (sizes) sizes[0] = (int)r->size;
+  if (r->prof && gProf) gProf(&r->prof, ncclProfilerNetEventStop, nullptr, 0, nullptr);
   if (r->tmpMr) mrPut(r->comm->dev, r->tmpMr);
   r->tmpMr = nullptr;
   r->used = false;

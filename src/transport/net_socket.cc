@@ -55,9 +55,22 @@ struct Request {
   int headerOff = 0;
   uint64_t off = 0;
   bool headerDone = false;
+  void* prof = nullptr;                       // event of this request at the profiler (through the callback given at init)
+  ncclProfilerNetSockDescr_v1_t profDescr;
 };
 
-ncclResult_t sInit(void** ctx, uint64_t, ncclNetCommConfig_t*, ncclDebugLogger_t, ncclProfilerCallback_t) {
+ncclProfilerCallback_t gProf = nullptr;
+void profRequest(Request* r, void* phandle) {
+  if (!gProf || !phandle) return;
+  r->profDescr.type = ncclProfileSocket;
+  r->profDescr.sock.fd = r->comm->sock.fd;
+  r->profDescr.sock.op = r->isSend ? 0 : 1;
+  r->profDescr.sock.length = r->size;
+  gProf(&r->prof, ncclProfilerNetEventStart, phandle, NCCL_PROFILER_NET_TYPE_SOCK | NCCL_PROFILER_NET_SOCKET_VER, &r->profDescr);
+}
+
+ncclResult_t sInit(void** ctx, uint64_t, ncclNetCommConfig_t*, ncclDebugLogger_t, ncclProfilerCallback_t prof) {
+  if (prof) gProf = prof;
   loadDevices();
   if (ctx) *ctx = nullptr;
   return ncclSuccess;
@@ -139,7 +152,7 @@ ncclResult_t sRegMr(void*, void*, size_t, int type, void** mhandle) {
 ncclResult_t sRegMrDmaBuf(void*, void*, size_t, int, uint64_t, int, void**) { return ncclInvalidUsage; }
 ncclResult_t sDeregMr(void*, void*) { return ncclSuccess; }
 
-ncclResult_t sIsend(void* sendComm, void* data, size_t size, int, void*, void*, void** request) {
+ncclResult_t sIsend(void* sendComm, void* data, size_t size, int, void*, void* phandle, void** request) {
   Request* r = new Request;
   r->comm = (Comm*)sendComm;
   r->isSend = true;
@@ -147,11 +160,12 @@ ncclResult_t sIsend(void* sendComm, void* data, size_t size, int, void*, void*, 
   r->size = size;
   r->header = size;
   r->comm->queue.push_back(r);
+  profRequest(r, phandle);
   *request = r;
   return ncclSuccess;
 }
 
-ncclResult_t sIrecv(void* recvComm, int n, void** data, size_t* sizes, int*, void**, void**, void** request) {
+ncclResult_t sIrecv(void* recvComm, int n, void** data, size_t* sizes, int*, void**, void** phandles, void** request) {
   if (n != 1) return ncclInvalidArgument;
   Request* r = new Request;
   r->comm = (Comm*)recvComm;
@@ -160,6 +174,7 @@ ncclResult_t sIrecv(void* recvComm, int n, void** data, size_t* sizes, int*, voi
   r->size = sizes[0];
   r->header = 0;
   r->comm->queue.push_back(r);
+  profRequest(r, phandles ? phandles[0] : nullptr);
   *request = r;
   return ncclSuccess;
 }
@@ -190,6 +205,7 @@ ncclResult_t sTest(void* request, int* done, int* sizes) {
   *done = 1;
   if (sizes) sizes[0] = (int)std::min<uint64_t>(r->size, 0x7fffffff);
   r->comm->queue.pop_front();
+  if (r->prof && gProf) gProf(&r->prof, ncclProfilerNetEventStop, nullptr, 0, nullptr);
   delete r;
   return ncclSuccess;
 }
@@ -197,7 +213,7 @@ ncclResult_t sTest(void* request, int* done, int* sizes) {
 ncclResult_t sCloseComm(void* comm) {
   Comm* c = (Comm*)comm;
   if (c) {
-    for (Request* r : c->queue) delete r;
+    for (Request* r : c->queue) { if (r->prof && gProf) gProf(&r->prof, ncclProfilerNetEventStop, nullptr, 0, nullptr); delete r; }
     sockClose(&c->sock);
     delete c;
   }

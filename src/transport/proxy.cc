@@ -38,6 +38,7 @@ static void profProxyOp(Proxy* p, ProxyOp* op, bool start) {
     d.proxyOp.chunkSize = (int)std::min<size_t>(p->sliceBytes, op->bytes);
     d.proxyOp.isSend = op->isSend ? 1 : 0;
     op->profHandle = profStart(comm, &d);
+    op->profParent = ProfNetParent{comm, op->profHandle};
   } else if (op->profHandle) {
     profStop(comm, op->profHandle);
     op->profHandle = nullptr;
@@ -68,13 +69,13 @@ static ncclResult_t progressOp(Proxy* p, ProxyOp* op) {
     void* req = nullptr;
     char* ptr = op->data + op->posted;
     if (op->isSend) {
-      NCCLCHECK(net->isend(p->sendComm[op->peer], ptr, n, 0, op->mhandle, nullptr, &req));
+      NCCLCHECK(net->isend(p->sendComm[op->peer], ptr, n, 0, op->mhandle, op->profHandle ? &op->profParent : nullptr, &req));
     } else {
       void* ptrs[1] = {ptr};
       size_t sizes[1] = {n};
       int tags[1] = {0};
       void* mh[1] = {op->mhandle};
-      void* ph[1] = {nullptr};
+      void* ph[1] = {op->profHandle ? (void*)&op->profParent : nullptr};
       NCCLCHECK(net->irecv(p->recvComm[op->peer], 1, ptrs, sizes, tags, mh, ph, &req));
     }
     if (!req) break;   // the backend is out of request slots: try again later
@@ -236,7 +237,7 @@ ncclResult_t proxyCreate(ncclComm* comm) {
   const int n = comm->nRanks, me = comm->rank;
   ncclNetCommConfig_t cfg = {NCCL_NET_TRAFFIC_CLASS_UNDEF};
   if (comm->config.trafficClass != NCCL_CONFIG_UNDEF_INT) cfg.trafficClass = comm->config.trafficClass;
-  NCCLCHECKGOTO(p->net->init(&p->netCtx, comm->commHash, &cfg, pluginLogger, nullptr), res, fail);
+  NCCLCHECKGOTO(p->net->init(&p->netCtx, comm->commHash, &cfg, pluginLogger, profilerNetCallback), res, fail);
   {
     int ndev = 0;
     NCCLCHECKGOTO(p->net->devices(&ndev), res, fail);

@@ -185,3 +185,17 @@ def test_many_messages_over_several_queue_pairs(fake_lib):
     env = dict(BASE, NCCL_NET="IB", NCCL_B200_IBV_LIB=fake_lib, NCCL_IB_QPS_PER_CONNECTION="3")
     res = run_ranks(_many_rank, 2, env=env, timeout=300)
     assert res[0] == (True, 0) and res[1] == (True, 0)
+
+
+def test_verbs_requests_are_events_at_the_profiler(fake_lib, tmp_path):
+    import json
+    plug = os.path.join(ROOT, "nccl_b200", "lib", "plugins", "profiler", "trace.so")
+    env = dict(BASE, NCCL_NET="IB", NCCL_B200_IBV_LIB=fake_lib, NCCL_PROFILER_PLUGIN=plug, NCCL_PROFILE_DUMP_FILE=str(tmp_path / "trace"))
+    res = run_ranks(_rank, 2, args=([1000, 1 << 16],), env=env, timeout=200)
+    assert all(all(res[r][0]) for r in range(2))
+    files = [p for p in os.listdir(tmp_path) if p.endswith(".json")]
+    ev = json.load(open(os.path.join(tmp_path, files[0])))
+    qp = [e for e in ev if e["name"] == "NetIb Qp"]
+    assert qp and all(e["cat"] == "NetPlugin" and e["args"]["qp"] > 0 for e in qp)
+    # sends by RDMA write with immediate (opcode 1), eager sends (3) and receives (128) all show up
+    assert {1, 3, 128} <= {e["args"]["opcode"] for e in qp}

@@ -204,3 +204,16 @@ def test_one_library_with_network_and_tuner_plugins(tmp_path):
     assert "network backend: plugin" in text and "mixed_plugin.so" in text
     assert "tuner plugin: found in the network plugin's library" in text
     assert "2 rule" in text     # the tuner's own line after reading the configuration file
+
+
+def test_network_backends_report_their_requests_to_the_profiler(tmp_path):
+    """Traffic through the proxy: every slice the socket backend moves is an event of the backend's own kind under the proxy
+    operation it belongs to (the backend gets a callback at init and a parent handle with every send / receive)."""
+    env = dict(BASE, NCCL_B200_HOST_NET="1", NCCL_PROFILER_PLUGIN=os.path.join(PLUG, "profiler", "trace.so"), NCCL_PROFILE_DUMP_FILE=str(tmp_path / "trace"))
+    _check(run_ranks(_rank, 2, args=(1,), env=env), 2)
+    files = [p for p in os.listdir(tmp_path) if p.endswith(".json")]
+    ev = json.load(open(os.path.join(tmp_path, files[0])))
+    net = [e for e in ev if e["cat"] == "NetPlugin"]
+    assert net and {e["name"] for e in net} == {"NetSock Send", "NetSock Recv"}
+    assert all(e["args"]["bytes"] > 0 and e["args"]["fd"] >= 0 and e["dur"] >= 0 for e in net)
+    assert any(e["cat"] == "ProxyOp" for e in ev)
