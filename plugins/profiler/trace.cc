@@ -28,6 +28,7 @@ struct Event {
   uint64_t type;
   std::string name, args;
   double t0, t1 = 0;
+  int sleeps = 0, appended = 0;   // ProxyCtrl: states seen
 };
 struct Ctx {
   uint64_t commId;
@@ -118,6 +119,11 @@ ncclResult_t pStop(void* handle) {
   Event* e = (Event*)handle;
   if (!e) return ncclSuccess;
   e->t1 = nowUs();
+  if (e->type == ncclProfileProxyCtrl) {
+    char buf[64];
+    snprintf(buf, sizeof(buf), "\"sleeps\":%d,\"operations\":%d", e->sleeps, e->appended);
+    e->args = buf;
+  }
   std::lock_guard<std::mutex> g(e->ctx->lock);
   e->ctx->done.push_back(e);
   return ncclSuccess;
@@ -125,10 +131,17 @@ ncclResult_t pStop(void* handle) {
 
 ncclResult_t pState(void* handle, ncclProfilerEventState_t st, ncclProfilerEventStateArgs_t* a) {
   Event* e = (Event*)handle;
+  char buf[64];
   if (e && a && e->type == ncclProfileKernelCh && st == ncclProfilerKernelChStop) {
-    char buf[64];
     snprintf(buf, sizeof(buf), ",\"gpu_stop_ns\":%llu", (unsigned long long)a->kernelCh.pTimer);
     e->args += buf;
+  } else if (e && a && e->type == ncclProfileProxyStep && (st == ncclProfilerProxyStepSendWait || st == ncclProfilerProxyStepRecvWait)) {
+    snprintf(buf, sizeof(buf), "%s\"bytes\":%zu", e->args.empty() ? "" : ",", a->proxyStep.transSize);
+    e->args += buf;
+  } else if (e && e->type == ncclProfileProxyCtrl) {
+    // how often the proxy thread went to sleep and how many operations it was handed
+    if (st == ncclProfilerProxyCtrlSleep) e->sleeps++;
+    if (st == ncclProfilerProxyCtrlActive && a) e->appended += a->proxyCtrl.appendedProxyOps;
   }
   return ncclSuccess;
 }

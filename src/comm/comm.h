@@ -160,6 +160,7 @@ void checkpointCommRemove(ncclComm* comm);
 // host data plane ---------------------------------------------------------------------------
 ncclResult_t hostPlaneCreate(ncclComm* comm);
 void hostPlaneDestroy(ncclComm* comm);
+void proxyQuiesce(ncclComm* comm);   // transport/proxy.cc: ends the progress thread of the network proxy, if there is one
 ncclResult_t hostPlaneRun(ncclComm* comm, const Task& t);           // blocking, host pointers
 ncclResult_t hostPlaneRunP2pGroup(ncclComm* comm, const std::vector<Task>& tasks);
 

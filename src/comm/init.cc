@@ -187,6 +187,7 @@ static void freeComm(ncclComm* comm) {
   if (comm->initThread) { if (comm->initThread->joinable()) comm->initThread->join(); delete comm->initThread; }
   rasCommRemove(comm);
   checkpointCommRemove(comm);
+  proxyQuiesce(comm);   // its events belong to the profiler that goes next
   profilerCommFini(comm);
   tunerUnload(comm);
   hostStagedRelease(comm);

@@ -48,7 +48,12 @@ struct ProxyOp {
   int head = 0, tail = 0;   // ring of requests in flight
   std::atomic<int> state{0};   // 0 running, 1 done, <0 failed (ncclResult_t negated)
   void* profHandle = nullptr;
-  ProfNetParent profParent = {nullptr, nullptr};   // handed to the backend with every slice of this operation
+  // One event per slice (ncclProfileProxyStep) under the operation's; the backend's own events hang under the slice's. A slice
+  // whose post was refused ("not yet") keeps its event for the next try.
+  void* stepHandle[NCCL_NET_MAX_REQUESTS] = {};
+  ProfNetParent stepParent[NCCL_NET_MAX_REQUESTS] = {};
+  void* nextStep = nullptr;
+  int stepsStarted = 0;
   void* mhandle = nullptr;   // the backend's registration of [data, data+bytes), made when the operation starts
   bool regTried = false;
 };
@@ -73,6 +78,7 @@ struct Proxy {
 
 ncclResult_t proxyCreate(ncclComm* comm);      // collective: listen, exchange handles, connect the full mesh, start the thread
 void proxyDestroy(ncclComm* comm);
+void proxyQuiesce(ncclComm* comm);   // ends the progress thread; connections stay until proxyDestroy
 // Posts an operation; the proxy thread progresses it. proxyWait blocks until every op given is done.
 ProxyOp* proxyPost(Proxy* p, bool isSend, int peer, void* data, size_t bytes);
 ncclResult_t proxyWait(Proxy* p, ProxyOp** ops, int n);

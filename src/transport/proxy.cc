@@ -38,8 +38,9 @@ static void profProxyOp(Proxy* p, ProxyOp* op, bool start) {
     d.proxyOp.chunkSize = (int)std::min<size_t>(p->sliceBytes, op->bytes);
     d.proxyOp.isSend = op->isSend ? 1 : 0;
     op->profHandle = profStart(comm, &d);
-    op->profParent = ProfNetParent{comm, op->profHandle};
   } else if (op->profHandle) {
+    for (void*& h : op->stepHandle) if (h) { profStop(comm, h); h = nullptr; }
+    if (op->nextStep) { profStop(comm, op->nextStep); op->nextStep = nullptr; }
     profStop(comm, op->profHandle);
     op->profHandle = nullptr;
   }
@@ -68,20 +69,38 @@ static ncclResult_t progressOp(Proxy* p, ProxyOp* op) {
     size_t n = std::min(p->sliceBytes, op->bytes - op->posted);
     void* req = nullptr;
     char* ptr = op->data + op->posted;
+    const int slot = op->tail % NCCL_NET_MAX_REQUESTS;
+    if (op->profHandle && !op->nextStep) {
+      ncclProfilerEventDescr_t d;
+      memset(&d, 0, sizeof(d));
+      d.type = ncclProfileProxyStep;
+      d.parentObj = op->profHandle;
+      d.proxyStep.step = op->stepsStarted++;
+      op->nextStep = profStart(p->comm, &d);
+    }
+    op->stepParent[slot] = ProfNetParent{p->comm, op->nextStep ? op->nextStep : op->profHandle};
+    void* ph = op->profHandle ? (void*)&op->stepParent[slot] : nullptr;
     if (op->isSend) {
-      NCCLCHECK(net->isend(p->sendComm[op->peer], ptr, n, 0, op->mhandle, op->profHandle ? &op->profParent : nullptr, &req));
+      NCCLCHECK(net->isend(p->sendComm[op->peer], ptr, n, 0, op->mhandle, ph, &req));
     } else {
       void* ptrs[1] = {ptr};
       size_t sizes[1] = {n};
       int tags[1] = {0};
       void* mh[1] = {op->mhandle};
-      void* ph[1] = {op->profHandle ? (void*)&op->profParent : nullptr};
-      NCCLCHECK(net->irecv(p->recvComm[op->peer], 1, ptrs, sizes, tags, mh, ph, &req));
+      void* phs[1] = {ph};
+      NCCLCHECK(net->irecv(p->recvComm[op->peer], 1, ptrs, sizes, tags, mh, phs, &req));
     }
     if (!req) break;   // the backend is out of request slots: try again later
-    int slot = op->tail % NCCL_NET_MAX_REQUESTS;
     op->requests[slot] = req;
     op->reqBytes[slot] = n;
+    op->stepHandle[slot] = op->nextStep;
+    op->nextStep = nullptr;
+    if (op->stepHandle[slot]) {
+      ncclProfilerEventStateArgs_t a;
+      memset(&a, 0, sizeof(a));
+      a.proxyStep.transSize = n;
+      profState(p->comm, op->stepHandle[slot], op->isSend ? ncclProfilerProxyStepSendWait : ncclProfilerProxyStepRecvWait, &a);
+    }
     op->tail++;
     op->posted += n;
     p->steps++;
@@ -92,6 +111,7 @@ static ncclResult_t progressOp(Proxy* p, ProxyOp* op) {
     int done = 0, size = 0;
     NCCLCHECK(net->test(op->requests[slot], &done, &size));
     if (!done) break;
+    if (op->stepHandle[slot]) { profStop(p->comm, op->stepHandle[slot]); op->stepHandle[slot] = nullptr; }
     op->completed += op->reqBytes[slot];
     p->bytesMoved += op->reqBytes[slot];
     op->head++;
@@ -147,16 +167,42 @@ static void proxyMain(Proxy* p) {
   std::vector<ProxyOp*> active;
   uint64_t idle = 0;
   unsigned dumpsSeen = gDumpRequests.load(std::memory_order_relaxed);
+  // One ncclProfileProxyCtrl event spans the life of the thread; its states say when the thread slept for lack of work and
+  // when operations were handed to it.
+  void* ctrl = nullptr;
+  bool ctrlTried = false;
   for (;;) {
     {
       std::unique_lock<std::mutex> lk(p->lock);
-      if (active.empty()) p->wake.wait(lk, [&] { return p->stop || !p->ops.empty(); });
+      // the profiler is attached to the communicator after this thread has started: look once work has arrived
+      if (!ctrlTried && p->comm->profiler && (!p->ops.empty() || !active.empty())) {
+        ctrlTried = true;
+        ncclProfilerEventDescr_t d;
+        memset(&d, 0, sizeof(d));
+        d.type = ncclProfileProxyCtrl;
+        ctrl = profStart(p->comm, &d);
+      }
+      if (active.empty() && p->ops.empty() && !p->stop) {
+        if (ctrl) profState(p->comm, ctrl, ncclProfilerProxyCtrlSleep, nullptr);
+        p->wake.wait(lk, [&] { return p->stop || !p->ops.empty(); });
+      }
+      int appended = 0;
       while (!p->ops.empty()) {
         active.push_back(p->ops.front());
         p->ops.pop_front();
         profProxyOp(p, active.back(), true);
+        ++appended;
       }
-      if (p->stop && active.empty()) return;
+      if (ctrl && appended) {
+        ncclProfilerEventStateArgs_t a;
+        memset(&a, 0, sizeof(a));
+        a.proxyCtrl.appendedProxyOps = appended;
+        profState(p->comm, ctrl, ncclProfilerProxyCtrlActive, &a);
+      }
+      if (p->stop && active.empty()) {
+        if (ctrl) profStop(p->comm, ctrl);
+        return;
+      }
     }
     const bool aborted = p->comm->abortFlag && __atomic_load_n(p->comm->abortFlag, __ATOMIC_RELAXED);
     const unsigned dumps = gDumpRequests.load(std::memory_order_relaxed);
@@ -305,6 +351,19 @@ fail:
   comm->proxy = p;
   proxyDestroy(comm);
   return res;
+}
+
+// Ends the proxy thread (its profiler events end with it) while the communicator's profiler is still attached; the
+// connections stay until proxyDestroy.
+void proxyQuiesce(ncclComm* comm) {
+  Proxy* p = comm->proxy;
+  if (!p || !p->thread.joinable()) return;
+  {
+    std::lock_guard<std::mutex> g(p->lock);
+    p->stop = true;
+  }
+  p->wake.notify_all();
+  p->thread.join();
 }
 
 void proxyDestroy(ncclComm* comm) {

@@ -217,3 +217,7 @@ def test_network_backends_report_their_requests_to_the_profiler(tmp_path):
     assert net and {e["name"] for e in net} == {"NetSock Send", "NetSock Recv"}
     assert all(e["args"]["bytes"] > 0 and e["args"]["fd"] >= 0 and e["dur"] >= 0 for e in net)
     assert any(e["cat"] == "ProxyOp" for e in ev)
+    steps = [e for e in ev if e["cat"] == "ProxyStep"]
+    assert steps and all(e["args"]["bytes"] > 0 for e in steps) and len(steps) == len(net)   # one backend request per slice
+    ctrl = [e for e in ev if e["cat"] == "ProxyCtrl"]
+    assert len(ctrl) == 1 and ctrl[0]["args"]["operations"] >= 2 and ctrl[0]["args"]["sleeps"] >= 1
