@@ -199,3 +199,17 @@ def test_verbs_requests_are_events_at_the_profiler(fake_lib, tmp_path):
     assert qp and all(e["cat"] == "NetPlugin" and e["args"]["qp"] > 0 for e in qp)
     # sends by RDMA write with immediate (opcode 1), eager sends (3) and receives (128) all show up
     assert {1, 3, 128} <= {e["args"]["opcode"] for e in qp}
+
+
+def test_split_and_shrink_build_new_meshes_over_verbs(fake_lib):
+    """Every communicator made by split or shrink gets a connection mesh of its own on the verbs backend."""
+    import test_api_host
+    env = dict(BASE, NCCL_NET="IB", NCCL_B200_IBV_LIB=fake_lib)
+    n = 4
+    res = run_ranks(test_api_host._splits, n, env=env, timeout=200)
+    for r in range(n):
+        o = res[r]
+        members = [q for q in range(n) if q % 2 == r % 2]
+        assert o["sub"][0] == len(members) and o["sub_sum"] == float(sum(members))
+        if r != n - 1:
+            assert o["shrunk"] == (n - 1, float(n - 1))
