@@ -27,6 +27,8 @@
 namespace {
 
 std::atomic<int> gErrors{0};
+// attributes of the last state changes, for tests of how the caller's settings reach the queue pair
+std::atomic<int> gLastPkey{-1}, gLastSgid{-1}, gLastTc{-1}, gLastSl{-1}, gLastTimeout{-1}, gLastRetry{-1}, gLastMtu{-1};
 void fail(const char* what) {
   gErrors++;
   fprintf(stderr, "fake_ibverbs[%d]: %s\n", (int)getpid(), what);
@@ -263,6 +265,13 @@ bool linkIsIb() { const char* e = getenv("FAKE_IB_LINK"); return e && strcmp(e, 
 extern "C" {
 
 int fake_ib_errors() { return gErrors.load(); }
+// what: 0 pkey index, 1 source GID index, 2 traffic class, 3 service level, 4 time-out, 5 retry count, 6 path MTU
+int fake_ib_last(int what) {
+  switch (what) {
+    case 0: return gLastPkey; case 1: return gLastSgid; case 2: return gLastTc; case 3: return gLastSl; case 4: return gLastTimeout; case 5: return gLastRetry;
+    case 6: return gLastMtu; default: return -1;
+  }
+}
 
 ibv_device** ibv_get_device_list(int* n) {
   makeDevices();
@@ -382,7 +391,11 @@ int ibv_modify_qp(ibv_qp* q, ibv_qp_attr* a, int mask) {
                   to == IBV_QPS_ERR || to == IBV_QPS_RESET;
   if (!ok) { fail("queue pair state change out of order"); return EINVAL; }
   if (to == IBV_QPS_INIT && (mask & (IBV_QP_PKEY_INDEX | IBV_QP_PORT | IBV_QP_ACCESS_FLAGS)) != (IBV_QP_PKEY_INDEX | IBV_QP_PORT | IBV_QP_ACCESS_FLAGS)) { fail("INIT without port, key index and access flags"); return EINVAL; }
+  if (to == IBV_QPS_INIT) gLastPkey = a->pkey_index;
   if (to == IBV_QPS_RTR) {
+    gLastSl = a->ah_attr.sl;
+    gLastMtu = a->path_mtu;
+    if (a->ah_attr.is_global) { gLastSgid = a->ah_attr.grh.sgid_index; gLastTc = a->ah_attr.grh.traffic_class; }
     const int need = IBV_QP_AV | IBV_QP_PATH_MTU | IBV_QP_DEST_QPN | IBV_QP_RQ_PSN | IBV_QP_MAX_DEST_RD_ATOMIC | IBV_QP_MIN_RNR_TIMER;
     if ((mask & need) != need) { fail("RTR without its required attributes"); return EINVAL; }
     qp->destQpn = a->dest_qp_num;
@@ -395,6 +408,8 @@ int ibv_modify_qp(ibv_qp* q, ibv_qp_attr* a, int mask) {
     }
   }
   if (to == IBV_QPS_RTS) {
+    gLastTimeout = a->timeout;
+    gLastRetry = a->retry_cnt;
     const int need = IBV_QP_TIMEOUT | IBV_QP_RETRY_CNT | IBV_QP_RNR_RETRY | IBV_QP_SQ_PSN | IBV_QP_MAX_QP_RD_ATOMIC;
     if ((mask & need) != need) { fail("RTS without its required attributes"); return EINVAL; }
   }

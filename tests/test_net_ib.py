@@ -213,3 +213,24 @@ def test_split_and_shrink_build_new_meshes_over_verbs(fake_lib):
         assert o["sub"][0] == len(members) and o["sub_sum"] == float(sum(members))
         if r != n - 1:
             assert o["shrunk"] == (n - 1, float(n - 1))
+
+
+def _settings_rank(rank, nranks, uid):
+    import ctypes
+    from nccl_b200 import Communicator
+    comm = Communicator(nranks, rank, uid)
+    x = np.ones(8, dtype=np.float32)
+    comm.all_reduce(x)
+    fake = ctypes.CDLL(os.environ["NCCL_B200_IBV_LIB"])
+    out = [fake.fake_ib_last(i) for i in range(7)]
+    comm.destroy()
+    return out
+
+
+def test_queue_pair_settings_come_from_the_environment(fake_lib):
+    env = dict(BASE, NCCL_NET="IB", NCCL_B200_IBV_LIB=fake_lib, NCCL_IB_PKEY="3", NCCL_IB_GID_INDEX="2", NCCL_IB_TC="106", NCCL_IB_SL="5",
+               NCCL_IB_TIMEOUT="18", NCCL_IB_RETRY_CNT="4")
+    res = run_ranks(_settings_rank, 2, env=env, timeout=120)
+    for r in range(2):
+        pkey, sgid, tc, sl, timeout, retry, mtu = res[r]
+        assert (pkey, sgid, tc, sl, timeout, retry) == (3, 2, 106, 5, 18, 4) and mtu == 5   # 5: 4096-byte path MTU of the stand-in's ports
