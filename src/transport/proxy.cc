@@ -161,8 +161,55 @@ static void proxyDump(Proxy* p, const std::vector<ProxyOp*>& active) {
          op->bytes, op->completed, op->tail - op->head);
 }
 
+B200_PARAM(IgnoreCpuAffinity, "IGNORE_CPU_AFFINITY", 0, "1: the proxy thread may also use the CPUs near its GPU that are outside the affinity mask of the process")
+
+// "0-15,32-47" -> CPU numbers. Returns how many were written (at most `max`).
+static int parseCpuList(const char* text, int* out, int max) {
+  int n = 0;
+  const char* p = text;
+  while (p && *p && n < max) {
+    char* end = nullptr;
+    long lo = strtol(p, &end, 10);
+    if (end == p) break;
+    long hi = lo;
+    p = end;
+    if (*p == '-') { hi = strtol(p + 1, &end, 10); if (end == p + 1) break; p = end; }
+    for (long c = lo; c <= hi && n < max; ++c) if (c >= 0) out[n++] = (int)c;
+    while (*p == ',' || *p == ' ' || *p == '\n') ++p;
+  }
+  return n;
+}
+
+// The proxy thread of a GPU rank runs on the CPUs next to that GPU (its PCI device's local_cpulist), restricted to the CPUs the
+// process may use unless NCCL_IGNORE_CPU_AFFINITY=1: the staging copies and the network adapter then sit on one socket.
+// Reference parity: ncclTopoGetCpuAffinity (src/graph/topo.cc) applied to the proxy threads (src/proxy.cc).
+static void proxySetAffinity(Proxy* p) {
+  ncclComm* comm = p->comm;
+  if (comm->hostOnly) return;
+  char busId[32], path[PATH_MAX], text[1024] = "";
+  int64ToBusId(comm->peers[comm->rank].busId, busId);
+  for (char* c = busId; *c; ++c) *c = (char)tolower(*c);
+  snprintf(path, sizeof(path), "/sys/bus/pci/devices/%s/local_cpulist", busId);
+  FILE* f = fopen(path, "r");
+  if (!f) return;
+  if (!fgets(text, sizeof(text), f)) text[0] = 0;
+  fclose(f);
+  int cpus[1024];
+  const int n = parseCpuList(text, cpus, 1024);
+  cpu_set_t allowed, want;
+  CPU_ZERO(&want);
+  if (sched_getaffinity(0, sizeof(allowed), &allowed) != 0) return;
+  int kept = 0;
+  for (int i = 0; i < n; ++i)
+    if (cpus[i] < CPU_SETSIZE && (paramIgnoreCpuAffinity() || CPU_ISSET(cpus[i], &allowed))) { CPU_SET(cpus[i], &want); ++kept; }
+  if (!kept) return;
+  if (pthread_setaffinity_np(pthread_self(), sizeof(want), &want) == 0)
+    INFO(SUB_INIT | SUB_PROXY, "proxy of rank %d runs on %d CPU(s) next to GPU %s", comm->rank, kept, busId);
+}
+
 static void proxyMain(Proxy* p) {
   setThreadName("NCCL Proxy %d", p->comm->rank);
+  proxySetAffinity(p);
   proxyInstallDumpSignal();
   std::vector<ProxyOp*> active;
   uint64_t idle = 0;
@@ -419,3 +466,6 @@ ncclResult_t proxyWait(Proxy* p, ProxyOp** ops, int n) {
 }
 
 }  // namespace b200
+
+// Test hook: the CPU-list parser of the proxy's affinity set-up.
+extern "C" int b200ParseCpuList(const char* text, int* out, int max) { return b200::parseCpuList(text, out, max); }

@@ -155,3 +155,21 @@ def test_reference_variables_without_a_counterpart_are_listed():
     for name in ("NCCL_IB_DISABLE", "NCCL_MNNVL_ENABLE", "NCCL_BUFFSIZE", "NCCL_MEM_SYNC_DOMAIN", "NCCL_CTA_POLICY", "NCCL_WIN_ENABLE",
                  "NCCL_MAX_NCHANNELS", "NCCL_SET_THREAD_NAME", "NCCL_DEBUG_TIMESTAMP_FORMAT", "NCCL_CROSS_NIC", "NCCL_P2P_LEVEL", "NCCL_GIN_TYPE"):
         assert name in out, name
+
+
+def test_cpu_list_parser_of_the_proxy_affinity():
+    """Lists in the form of the kernel's local_cpulist files: ranges, single CPUs, separators, malformed tails."""
+    import ctypes
+    from nccl_b200 import _lib
+    lib = _lib.load()
+    out = (ctypes.c_int * 64)()
+
+    def parse(text, cap=64):
+        n = lib.b200ParseCpuList(text, out, cap)
+        return list(out[:n])
+
+    assert parse(b"0-3,8-9\n") == [0, 1, 2, 3, 8, 9]
+    assert parse(b"5") == [5] and parse(b"") == [] and parse(b"2-1") == []
+    assert parse(b"0-2, 7") == [0, 1, 2, 7]
+    assert parse(b"0-63,64-127", cap=4) == [0, 1, 2, 3]
+    assert parse(b"3,x") == [3]
