@@ -7,12 +7,19 @@
 // multi-socket striping, which a loopback / single-NIC host path does not need.
 #include <string.h>
 
+#include <atomic>
 #include <deque>
+#include <map>
+#include <unistd.h>
 
 #include "../core/socket.h"
 #include "net.h"
 
 namespace b200 {
+
+B200_PARAM(SocketNthreads, "SOCKET_NTHREADS", 1, "With NCCL_NSOCKS_PERTHREAD: their product is the number of TCP connections per send / receive pair of the socket backend (1 to 16); no extra threads are created, the proxy thread moves all of them")
+B200_PARAM(NsocksPerThread, "NSOCKS_PERTHREAD", 1, "See NCCL_SOCKET_NTHREADS")
+
 namespace {
 
 constexpr int kMaxIfs = 16;
@@ -39,13 +46,23 @@ struct Handle {            // what listen() hands to the sender; fits NCCL_NET_H
 };
 static_assert(sizeof(Handle) <= NCCL_NET_HANDLE_MAXSIZE, "handle too large");
 
-struct ListenComm { Socket sock; };
 struct Request;
 struct Comm {
-  Socket sock;
+  Socket sock;                  // first connection: carries the 8-byte length of every message and the first part of its payload
+  std::vector<Socket> extra;    // further connections of the same comm (NCCL_SOCKET_NTHREADS x NCCL_NSOCKS_PERTHREAD in all)
   bool isSend;
-  std::deque<Request*> queue;   // requests share one byte stream: only the oldest may move bytes
+  std::deque<Request*> queue;   // requests share the byte streams: only the oldest may move bytes
+  int nSocks() const { return 1 + (int)extra.size(); }
+  Socket* socket(int i) { return i == 0 ? &sock : &extra[i - 1]; }
 };
+struct Hello { uint64_t token; int32_t index, total; };   // first bytes on every connection: which comm it belongs to
+struct Partial { Comm* comm; int have; };
+struct ListenComm {
+  Socket sock;
+  std::map<uint64_t, Partial> partial;   // comms whose connections have not all arrived yet
+};
+constexpr int kMaxSocks = 16;
+constexpr uint64_t kMinPart = 64 << 10;   // smaller messages travel on the first connection only
 struct Request {
   Comm* comm;
   bool isSend;
@@ -53,7 +70,7 @@ struct Request {
   uint64_t size;        // send: bytes to send; recv: capacity, then bytes received
   uint64_t header;
   int headerOff = 0;
-  uint64_t off = 0;
+  uint64_t off[kMaxSocks] = {};   // bytes moved per connection
   bool headerDone = false;
   void* prof = nullptr;                       // event of this request at the profiler (through the callback given at init)
   ncclProfilerNetSockDescr_v1_t profDescr;
@@ -120,14 +137,32 @@ ncclResult_t sListen(void*, int dev, void* handle, void** listenComm) {
   return ncclSuccess;
 }
 
+// How a message of `size` bytes is cut over `n` connections: equal parts of at least kMinPart, rounded up to 4 KiB; both
+// ends compute the same cut from the size in the header.
+inline uint64_t partBytes(uint64_t size, int n) {
+  if (n <= 1 || size <= kMinPart) return size;
+  uint64_t per = std::max<uint64_t>((size + n - 1) / n, kMinPart);
+  return (per + 4095) & ~(uint64_t)4095;
+}
+
 ncclResult_t sConnect(void*, int, void* handle, void** sendComm, ncclNetDeviceHandle_t** devComm) {
   Handle h;
   memcpy(&h, handle, sizeof(h));
   Comm* c = new Comm;
   c->isSend = true;
-  NCCLCHECK(sockInit(&c->sock, &h.addr, h.magic, SOCK_NET));
-  ncclResult_t r = sockConnect(&c->sock);
-  if (r != ncclSuccess) { delete c; return r; }
+  const int total = (int)std::min<int64_t>(std::max<int64_t>(paramSocketNthreads() * paramNsocksPerThread(), 1), kMaxSocks);
+  static std::atomic<uint64_t> counter{0};
+  const uint64_t token = ((uint64_t)getpid() << 40) ^ ((uint64_t)(uintptr_t)c << 8) ^ ++counter;
+  c->extra.resize(total - 1);
+  ncclResult_t r = ncclSuccess;
+  for (int i = 0; i < total && r == ncclSuccess; ++i) {
+    Socket* sk = c->socket(i);
+    r = sockInit(sk, &h.addr, h.magic, SOCK_NET);
+    if (r == ncclSuccess) r = sockConnect(sk);
+    Hello hello = {token, i, total};
+    if (r == ncclSuccess) r = sockSend(sk, &hello, sizeof(hello));
+  }
+  if (r != ncclSuccess) { for (int i = 0; i < total; ++i) sockClose(c->socket(i)); delete c; return r; }
   *sendComm = c;
   if (devComm) *devComm = nullptr;
   return ncclSuccess;
@@ -135,13 +170,30 @@ ncclResult_t sConnect(void*, int, void* handle, void** sendComm, ncclNetDeviceHa
 
 ncclResult_t sAccept(void* listenComm, void** recvComm, ncclNetDeviceHandle_t** devComm) {
   ListenComm* l = (ListenComm*)listenComm;
-  Comm* c = new Comm;
-  c->isSend = false;
-  ncclResult_t r = sockAccept(&c->sock, &l->sock);
-  if (r != ncclSuccess) { delete c; return r; }
-  *recvComm = c;
   if (devComm) *devComm = nullptr;
-  return ncclSuccess;
+  // connections of several dialling comms may arrive interleaved: they are sorted by the token in their first bytes until one
+  // comm has all of its connections
+  for (;;) {
+    Socket sk;
+    NCCLCHECK(sockAccept(&sk, &l->sock));
+    Hello hello;
+    ncclResult_t r = sockRecv(&sk, &hello, sizeof(hello));
+    if (r != ncclSuccess || hello.total < 1 || hello.total > kMaxSocks || hello.index < 0 || hello.index >= hello.total) { sockClose(&sk); if (r != ncclSuccess) return r; continue; }
+    Partial& pa = l->partial[hello.token];
+    if (!pa.comm) {
+      pa.comm = new Comm;
+      pa.comm->isSend = false;
+      pa.comm->extra.resize(hello.total - 1);
+      pa.have = 0;
+    }
+    if (pa.comm->nSocks() != hello.total) { sockClose(&sk); continue; }
+    *pa.comm->socket(hello.index) = sk;
+    if (++pa.have == hello.total) {
+      *recvComm = pa.comm;
+      l->partial.erase(hello.token);
+      return ncclSuccess;
+    }
+  }
 }
 
 ncclResult_t sRegMr(void*, void*, size_t, int type, void** mhandle) {
@@ -196,12 +248,19 @@ ncclResult_t sTest(void* request, int* done, int* sizes) {
       r->size = r->header;
     }
   }
-  while (r->off < r->size) {
-    int chunk = (int)std::min<uint64_t>(r->size - r->off, 1u << 30), moved = 0;
-    NCCLCHECK(sockProgress(kind, &r->comm->sock, r->data + r->off, chunk, &moved));
-    r->off += moved;
-    if (moved < chunk) return ncclSuccess;
+  const int n = r->comm->nSocks();
+  const uint64_t per = partBytes(r->size, n);
+  bool all = true;
+  for (int i = 0; i < n; ++i) {
+    const uint64_t lo = std::min<uint64_t>(r->size, (uint64_t)i * per), len = std::min<uint64_t>(per, r->size - lo);
+    while (r->off[i] < len) {
+      int chunk = (int)std::min<uint64_t>(len - r->off[i], 1u << 30), moved = 0;
+      NCCLCHECK(sockProgress(kind, r->comm->socket(i), r->data + lo + r->off[i], chunk, &moved));
+      r->off[i] += moved;
+      if (moved < chunk) { all = false; break; }
+    }
   }
+  if (!all) return ncclSuccess;
   *done = 1;
   if (sizes) sizes[0] = (int)std::min<uint64_t>(r->size, 0x7fffffff);
   r->comm->queue.pop_front();
@@ -214,14 +273,18 @@ ncclResult_t sCloseComm(void* comm) {
   Comm* c = (Comm*)comm;
   if (c) {
     for (Request* r : c->queue) { if (r->prof && gProf) gProf(&r->prof, ncclProfilerNetEventStop, nullptr, 0, nullptr); delete r; }
-    sockClose(&c->sock);
+    for (int i = 0; i < c->nSocks(); ++i) sockClose(c->socket(i));
     delete c;
   }
   return ncclSuccess;
 }
 ncclResult_t sCloseListen(void* listenComm) {
   ListenComm* l = (ListenComm*)listenComm;
-  if (l) { sockClose(&l->sock); delete l; }
+  if (l) {
+    for (auto& kv : l->partial) { for (int i = 0; i < kv.second.comm->nSocks(); ++i) sockClose(kv.second.comm->socket(i)); delete kv.second.comm; }
+    sockClose(&l->sock);
+    delete l;
+  }
   return ncclSuccess;
 }
 ncclResult_t sGetDeviceMr(void*, void*, void**) { return ncclInvalidUsage; }

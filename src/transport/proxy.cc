@@ -221,6 +221,10 @@ static void proxyMain(Proxy* p) {
   for (;;) {
     {
       std::unique_lock<std::mutex> lk(p->lock);
+      if (active.empty() && p->ops.empty() && !p->stop) {
+        if (ctrl) profState(p->comm, ctrl, ncclProfilerProxyCtrlSleep, nullptr);
+        p->wake.wait(lk, [&] { return p->stop || !p->ops.empty(); });
+      }
       // the profiler is attached to the communicator after this thread has started: look once work has arrived
       if (!ctrlTried && p->comm->profiler && (!p->ops.empty() || !active.empty())) {
         ctrlTried = true;
@@ -228,10 +232,6 @@ static void proxyMain(Proxy* p) {
         memset(&d, 0, sizeof(d));
         d.type = ncclProfileProxyCtrl;
         ctrl = profStart(p->comm, &d);
-      }
-      if (active.empty() && p->ops.empty() && !p->stop) {
-        if (ctrl) profState(p->comm, ctrl, ncclProfilerProxyCtrlSleep, nullptr);
-        p->wake.wait(lk, [&] { return p->stop || !p->ops.empty(); });
       }
       int appended = 0;
       while (!p->ops.empty()) {

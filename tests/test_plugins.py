@@ -220,4 +220,32 @@ def test_network_backends_report_their_requests_to_the_profiler(tmp_path):
     steps = [e for e in ev if e["cat"] == "ProxyStep"]
     assert steps and all(e["args"]["bytes"] > 0 for e in steps) and len(steps) == len(net)   # one backend request per slice
     ctrl = [e for e in ev if e["cat"] == "ProxyCtrl"]
-    assert len(ctrl) == 1 and ctrl[0]["args"]["operations"] >= 2 and ctrl[0]["args"]["sleeps"] >= 1
+    assert len(ctrl) == 1 and ctrl[0]["args"]["operations"] == sum(1 for e in ev if e["cat"] == "ProxyOp") and ctrl[0]["args"]["sleeps"] >= 1
+
+
+@pytest.mark.parametrize("nthreads,nsocks", [(2, 2), (1, 3)])
+def test_socket_backend_stripes_messages_over_several_connections(nthreads, nsocks):
+    """NCCL_SOCKET_NTHREADS x NCCL_NSOCKS_PERTHREAD connections per comm: large messages are cut over them, small ones stay on the
+    first; three ranks dial each other at the same time, so connections of different comms arrive interleaved at a listener."""
+    env = dict(BASE, NCCL_B200_HOST_NET="1", NCCL_SOCKET_NTHREADS=str(nthreads), NCCL_NSOCKS_PERTHREAD=str(nsocks))
+    res = run_ranks(_stripe_rank, 3, env=env, timeout=200)
+    assert all(res[r] for r in range(3))
+
+
+def _stripe_rank(rank, nranks, uid):
+    from nccl_b200 import Communicator, group
+    comm = Communicator(nranks, rank, uid)
+    ok = True
+    for n in (3, 20000, 70001, 1 << 20):      # below the striping threshold, around it, not a multiple of the part size, several slices
+        x = (np.arange(n, dtype=np.float32) % 113) + rank
+        y = np.zeros_like(x)
+        comm.all_reduce(x, y)
+        ok = ok and bool(np.array_equal(y, (np.arange(n, dtype=np.float32) % 113) * nranks + nranks * (nranks - 1) / 2))
+        s = np.full(n, rank + 1, dtype=np.float32)
+        r = np.zeros(n, dtype=np.float32)
+        with group():
+            comm.send(s, (rank + 1) % nranks)
+            comm.recv(r, (rank - 1) % nranks)
+        ok = ok and bool((r == (rank - 1) % nranks + 1).all())
+    comm.destroy()
+    return ok
