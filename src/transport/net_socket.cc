@@ -1,10 +1,11 @@
 // Built-in network backend "Socket": the ncclNet_t table over TCP.
-// One TCP connection per send/receive pair. A message travels as an 8-byte length followed by
-// the payload; isend / irecv only record the request and test() moves whatever the kernel
-// accepts without blocking, so one proxy thread can keep many transfers in flight.
-// Reference parity: src/transport/net_socket.cc (devices/properties :50-346, listen/connect/
-// accept :408-540, test :608-720, isend/irecv :728-757); the reference adds helper threads and
-// multi-socket striping, which a loopback / single-NIC host path does not need.
+// A send / receive pair has one TCP connection, or several (NCCL_SOCKET_NTHREADS x NCCL_NSOCKS_PERTHREAD): a message travels as
+// an 8-byte length on the first connection followed by the payload, cut into equal parts over the connections when it is
+// larger than 64 KiB. isend / irecv only record the request and test() moves whatever the kernel accepts without blocking, so one
+// proxy thread keeps many transfers and all connections in flight (no helper threads are created). Connections of several
+// dialling comms may reach a listener interleaved; each announces its comm with a token in its first bytes.
+// Reference parity: src/transport/net_socket.cc (devices/properties :50-346, listen/connect/accept :408-540, test :608-720,
+// isend/irecv :757; multi-socket striping with its two variables).
 #include <string.h>
 
 #include <atomic>
