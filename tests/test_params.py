@@ -173,3 +173,15 @@ def test_cpu_list_parser_of_the_proxy_affinity():
     assert parse(b"0-2, 7") == [0, 1, 2, 7]
     assert parse(b"0-63,64-127", cap=4) == [0, 1, 2, 3]
     assert parse(b"3,x") == [3]
+
+
+def test_environment_reference_lists_every_registered_parameter():
+    """docs/env.md is generated from the registry (python docs/gen_env.py): every variable that `ncclparam --all` prints has its row."""
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([os.path.join(root, "nccl_b200", "bin", "ncclparam"), "--all"], capture_output=True, text=True, check=True).stdout
+    names = [line.split("=", 1)[0].strip() for line in out.splitlines() if "=" in line and "#" in line]
+    doc = open(os.path.join(root, "docs", "env.md")).read()
+    missing = [n for n in names if "`%s`" % n not in doc]
+    assert len(names) > 80 and not missing, missing
