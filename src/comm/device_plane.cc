@@ -23,6 +23,8 @@ B200_PARAM(MaxCtas, "MAX_CTAS", 0, "Upper bound on CTAs per collective kernel (0
 B200_PARAM(MinCtas, "MIN_CTAS", 0, "Lower bound on CTAs per collective kernel")
 B200_PARAM(MaxNChannels, "MAX_NCHANNELS", 0, "Older name of NCCL_MAX_CTAS (used when that is not set)")
 B200_PARAM(MinNChannels, "MIN_NCHANNELS", 0, "Older name of NCCL_MIN_CTAS (used when that is not set)")
+B200_PARAM(MaxNRings, "MAX_NRINGS", 0, "Oldest name of NCCL_MAX_CTAS (used when neither that nor NCCL_MAX_NCHANNELS is set)")
+B200_PARAM(MinNRings, "MIN_NRINGS", 0, "Oldest name of NCCL_MIN_CTAS (used when neither that nor NCCL_MIN_NCHANNELS is set)")
 B200_PARAM(CtaPolicy, "CTA_POLICY", -1, "Overrides ncclConfig_t::CTAPolicy: 0 default, 1 efficiency (half the CTAs the table asks for), 2 zero (copy collectives on registered buffers use the copy engines: no SM)")
 B200_PARAM(LLThreshold, "B200_LL_THRESHOLD", -1, "All-reduce payloads up to this many bytes use the one-shot flagged-line kernel")
 B200_PARAM(NvlsThreshold, "B200_NVLS_THRESHOLD", -1, "All-reduce payloads from this many bytes use multimem")
@@ -353,6 +355,8 @@ static int clampCtas(ncclComm* comm, size_t bytes, int cap) {
   int64_t envMax = paramMaxCtas(), envMin = paramMinCtas();
   if (envMax <= 0) envMax = paramMaxNChannels();
   if (envMin <= 0) envMin = paramMinNChannels();
+  if (envMax <= 0) envMax = paramMaxNRings();   // the oldest spelling
+  if (envMin <= 0) envMin = paramMinNRings();
   const int policy = paramCtaPolicy() >= 0 ? (int)paramCtaPolicy() : comm->config.CTAPolicy;
   if ((policy & NCCL_CTA_POLICY_EFFICIENCY) && policy != NCCL_CONFIG_UNDEF_INT) { cap = std::max(1, cap / 2); if (tPickCtas > 0) tPickCtas = std::max(1, tPickCtas / 2); }
   if (comm->config.maxCTAs != NCCL_CONFIG_UNDEF_INT && comm->config.maxCTAs > 0) cap = std::min(cap, comm->config.maxCTAs);

@@ -134,6 +134,11 @@ static ParamRegistrar kStrParams[] = {
     {{"NCCL_PROFILE_EVENT_MASK", PT_STR, "", "Bit mask of the event types handed to the profiler plugin (overrides what the plugin asks for)", true}},
     // variables of the reference that configure parts this build does not have: accepted and ignored, listed so that a job
     // script written for the reference explains itself
+    {{"NCCL_IBVERBS_LIB", PT_STR, "", "The reference's name of NCCL_B200_IBV_LIB (used when that is not set)", true}},
+    {{"NCCL_PROXY_CPUSET", PT_STR, "", "CPUs of the proxy threads, in the form of the kernel's cpulist files (0-7,16-23); default: the CPUs next to the rank's GPU", true}},
+    {{"NCCL_TOPO_DUMP_FILE_RANK", PT_STR, "", "Rank that writes NCCL_TOPO_DUMP_FILE (default: local rank 0 of every host)", true}},
+    {{"NCCL_GRAPH_DUMP_FILE_RANK", PT_STR, "", "Rank that writes NCCL_GRAPH_DUMP_FILE (default 0)", true}},
+    {{"NCCL_SHM_DISABLE", PT_STR, "", "1: ranks of one host never use shared-memory rings (they are opt-in here: NCCL_B200_HOST_SHM)", true}},
     {{"NCCL_IB_HCA", PT_STR, "", "Verbs devices the InfiniBand backend may use: name prefixes with optional :port, comma separated; =name wants the exact name, a leading ^ excludes", true}},
     {{"NCCL_IB_ADDR_FAMILY", PT_STR, "AF_INET", "Address family preferred when the RoCE GID index is chosen automatically: AF_INET or AF_INET6", true}},
     {{"NCCL_B200_IBV_LIB", PT_STR, "libibverbs.so.1", "Verbs library that the InfiniBand backend opens at run time", true}},

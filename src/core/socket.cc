@@ -172,9 +172,14 @@ ncclResult_t sockInit(Socket* s, const SockAddr* addr, uint64_t magic, SockType 
   return ncclSuccess;
 }
 
+B200_PARAM(SocketRcvBuf, "SOCKET_RCVBUF", -1, "Receive buffer of every TCP socket in bytes (-1: the system's default)")
+B200_PARAM(SocketSndBuf, "SOCKET_SNDBUF", -1, "Send buffer of every TCP socket in bytes (-1: the system's default)")
+
 static void setFdOptions(int fd) {
   int one = 1;
   setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+  if (paramSocketRcvBuf() > 0) { int v = (int)paramSocketRcvBuf(); setsockopt(fd, SOL_SOCKET, SO_RCVBUF, &v, sizeof(v)); }
+  if (paramSocketSndBuf() > 0) { int v = (int)paramSocketSndBuf(); setsockopt(fd, SOL_SOCKET, SO_SNDBUF, &v, sizeof(v)); }
   int fl = fcntl(fd, F_GETFL);
   fcntl(fd, F_SETFL, fl | O_NONBLOCK);
   fcntl(fd, F_SETFD, FD_CLOEXEC);

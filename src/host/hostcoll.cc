@@ -67,7 +67,8 @@ static ncclResult_t hostPlaneCreateLinks(ncclComm* comm) {
   int n = comm->nRanks, me = comm->rank;
   hp->peer.resize(n);
   hp->abortFlag = comm->abortFlag;
-  if (paramHostShm() && comm->nNodes == 1) {
+  const char* shmOff = getEnv("NCCL_SHM_DISABLE");
+  if (paramHostShm() && comm->nNodes == 1 && !(shmOff && atoi(shmOff) == 1)) {
     hp->shmIn.resize(n);
     hp->shmOut.resize(n);
     char base[96];

@@ -295,7 +295,8 @@ ncclResult_t topoInit(ncclComm* comm) {
     }
   }
   const char* dump = getEnv("NCCL_TOPO_DUMP_FILE");
-  if (dump && *dump && comm->localRank == 0) {
+  const char* dumpRank = getEnv("NCCL_TOPO_DUMP_FILE_RANK");
+  if (dump && *dump && (dumpRank && *dumpRank ? comm->rank == atoi(dumpRank) : comm->localRank == 0)) {
     std::ofstream f(dump);
     f << xmlDump(st->xml);
   }
@@ -336,7 +337,8 @@ ncclResult_t topoInit(ncclComm* comm) {
   }
   topoTuneModel(st->sys, &st->ring, &st->tree, &st->nvls, comm->nRanks, comm->nNodes, comm->compCap, &st->model);
   const char* gdump = getEnv("NCCL_GRAPH_DUMP_FILE");
-  if (gdump && *gdump && comm->rank == 0) {
+  const char* gdumpRank = getEnv("NCCL_GRAPH_DUMP_FILE_RANK");
+  if (gdump && *gdump && comm->rank == (gdumpRank && *gdumpRank ? atoi(gdumpRank) : 0)) {
     XmlNode* gx = graphToXml({st->ring, st->tree, st->nvls});
     std::ofstream f(gdump);
     f << xmlDump(gx);

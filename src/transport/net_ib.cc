@@ -48,6 +48,7 @@ B200_PARAM(IbSl, "IB_SL", 0, "InfiniBand service level")
 B200_PARAM(IbTc, "IB_TC", 0, "Traffic class of the global route (RoCE)")
 B200_PARAM(IbPkey, "IB_PKEY", 0, "Partition key index")
 B200_PARAM(IbUseInline, "IB_USE_INLINE", 1, "Send messages and credit entries that fit as inline data of the work request")
+B200_PARAM(IbRelaxedOrdering, "IB_PCI_RELAXED_ORDERING", 0, "1: memory regions are registered with relaxed PCIe ordering (falls back to strict ordering where the adapter refuses it)")
 B200_PARAM(IbQps, "IB_QPS_PER_CONNECTION", 1, "Queue pairs per connection (1 to 8; both ends use the smaller of their settings): messages that travel by RDMA write are split evenly over them")
 B200_PARAM(IbEagerBytes, "B200_IB_EAGER_BYTES", 8192, "Largest message that travels eagerly (SEND into pre-posted buffers) instead of by receiver-driven RDMA write")
 
@@ -90,6 +91,7 @@ bool gPeerMem = false;
 
 bool loadVerbs() {
   const char* path = getEnv("NCCL_B200_IBV_LIB");
+  if (!path || !*path) path = getEnv("NCCL_IBVERBS_LIB");   // the reference's name of the same setting
   void* h = dlopen(path && *path ? path : "libibverbs.so.1", RTLD_NOW | RTLD_LOCAL);
   if (!h) return false;
   bool ok = true;
@@ -244,7 +246,9 @@ ncclResult_t mrGet(IbDev* d, const void* p, size_t bytes, ibv_mr** out) {
   std::lock_guard<std::mutex> g(d->lock);
   for (auto& e : d->mrs)
     if (e.start <= start && start + len <= e.start + e.bytes) { e.refs++; *out = e.mr; return ncclSuccess; }
-  ibv_mr* mr = ibv.reg_mr(d->pd, (void*)start, len, IBV_ACCESS_LOCAL_WRITE | IBV_ACCESS_REMOTE_WRITE | IBV_ACCESS_REMOTE_READ);
+  const int access = IBV_ACCESS_LOCAL_WRITE | IBV_ACCESS_REMOTE_WRITE | IBV_ACCESS_REMOTE_READ;
+  ibv_mr* mr = paramIbRelaxedOrdering() ? ibv.reg_mr(d->pd, (void*)start, len, access | IBV_ACCESS_RELAXED_ORDERING) : nullptr;
+  if (!mr) mr = ibv.reg_mr(d->pd, (void*)start, len, access);
   if (!mr) { WARN("NET/IB : registration of %zu bytes at %p failed on %s (locked-memory limit?)", len, (void*)start, d->name.c_str()); return ncclSystemError; }
   d->mrs.push_back(MrEntry{start, len, mr, 1});
   *out = mr;

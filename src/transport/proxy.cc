@@ -185,8 +185,18 @@ static int parseCpuList(const char* text, int* out, int max) {
 // Reference parity: ncclTopoGetCpuAffinity (src/graph/topo.cc) applied to the proxy threads (src/proxy.cc).
 static void proxySetAffinity(Proxy* p) {
   ncclComm* comm = p->comm;
+  char busId[32] = "", path[PATH_MAX], text[1024] = "";
+  // NCCL_PROXY_CPUSET names the CPUs of every proxy thread outright (same list form as the kernel's cpulist files)
+  if (const char* forced = getEnv("NCCL_PROXY_CPUSET")) {
+    int cpus[1024];
+    const int n = parseCpuList(forced, cpus, 1024);
+    cpu_set_t want;
+    CPU_ZERO(&want);
+    for (int i = 0; i < n; ++i) if (cpus[i] < CPU_SETSIZE) CPU_SET(cpus[i], &want);
+    if (n > 0 && pthread_setaffinity_np(pthread_self(), sizeof(want), &want) == 0) INFO(SUB_INIT | SUB_PROXY, "proxy of rank %d runs on the CPUs of NCCL_PROXY_CPUSET=%s", comm->rank, forced);
+    return;
+  }
   if (comm->hostOnly) return;
-  char busId[32], path[PATH_MAX], text[1024] = "";
   int64ToBusId(comm->peers[comm->rank].busId, busId);
   for (char* c = busId; *c; ++c) *c = (char)tolower(*c);
   snprintf(path, sizeof(path), "/sys/bus/pci/devices/%s/local_cpulist", busId);

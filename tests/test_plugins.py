@@ -249,3 +249,11 @@ def _stripe_rank(rank, nranks, uid):
         ok = ok and bool((r == (rank - 1) % nranks + 1).all())
     comm.destroy()
     return ok
+
+
+def test_proxy_threads_run_on_the_named_cpus(tmp_path):
+    env = dict(BASE, NCCL_B200_HOST_NET="1", NCCL_PROXY_CPUSET="0", NCCL_SOCKET_RCVBUF="262144", NCCL_SOCKET_SNDBUF="262144", NCCL_DEBUG="INFO",
+               NCCL_DEBUG_SUBSYS="INIT,PROXY", NCCL_DEBUG_FILE=str(tmp_path / "log.%p"))
+    _check(run_ranks(_rank, 2, args=(1,), env=env), 2)
+    text = "".join(open(tmp_path / f).read() for f in os.listdir(tmp_path))
+    assert text.count("runs on the CPUs of NCCL_PROXY_CPUSET=0") == 2
