@@ -145,6 +145,15 @@ static ParamRegistrar kStrParams[] = {
     {{"NCCL_IB_SPLIT_DATA_ON_QPS", PT_STR, "", "No effect: with several queue pairs per connection every RDMA-write message is split over them; NCCL_IB_AR_THRESHOLD, NCCL_IB_MERGE_NICS and the resiliency settings have no effect either", true}},
     {{"NCCL_NET_GDR_LEVEL", PT_STR, "", "No effect: the proxy stages through host memory on the built-in backends; a plugin decides about GPUDirect itself", true}},
     {{"NCCL_MNNVL_CROSS_CLIQUE", PT_STR, "", "No effect: ranks of other fabric cliques are reached through the network transport only", true}},
+    {{"NCCL_GDRCOPY_ENABLE", PT_STR, "", "No effect: no GDRCopy mappings are used (flags and credits live in device or pinned host memory that both sides map); the other NCCL_GDRCOPY_* variables likewise", true}},
+    {{"NCCL_LL_BUFFSIZE", PT_STR, "", "No effect: the flagged-line regions have a fixed size in the resource window; NCCL_LL128_BUFFSIZE, NCCL_LL128_NTHREADS and NCCL_LL128_C2C have no counterpart (there is no LL128 protocol)", true}},
+    {{"NCCL_P2P_NVL_CHUNKSIZE", PT_STR, "", "No effect: send / receive moves data in mailbox chunks sized by the message (NCCL_P2P_PCI_CHUNKSIZE, NCCL_P2P_NET_CHUNKSIZE, NCCL_CHUNK_SIZE, NCCL_NVLS_CHUNKSIZE likewise)", true}},
+    {{"NCCL_WORK_FIFO_BYTES", PT_STR, "", "No effect: every launch carries its arguments in the kernel parameters (no work FIFO; NCCL_WORK_ARGS_BYTES likewise)", true}},
+    {{"NCCL_GRAPH_REGISTER", PT_STR, "", "No effect: buffers are registered only by ncclCommRegister / ncclCommWindowRegister (NCCL_LOCAL_REGISTER, NCCL_LEGACY_CUDA_REGISTER likewise)", true}},
+    {{"NCCL_SYM_CTAS", PT_STR, "", "No effect: CTA counts come from the selection table, NCCL_MAX_CTAS / NCCL_MIN_CTAS and the communicator's configuration (NCCL_NVLS_NCHANNELS, NCCL_MAX_P2P_NCHANNELS likewise)", true}},
+    {{"NCCL_PXN_DISABLE", PT_STR, "", "No effect: the channel search classifies relayed NIC paths, but traffic between NVLink domains is not relayed through peer GPUs (NCCL_P2P_PXN_LEVEL, NCCL_PXN_C2C likewise)", true}},
+    {{"NCCL_IB_ADAPTIVE_ROUTING", PT_STR, "", "No effect in the verbs backend; neither have NCCL_IB_ECE_ENABLE, NCCL_IB_SUBNET_AWARE_ROUTING, NCCL_IB_DATA_DIRECT, NCCL_IB_OOO_RQ and the NCCL_IB_RESILIENCY_* family", true}},
+    {{"NCCL_GIN_ENABLE", PT_STR, "", "No effect: GPU-initiated put / signal serves the NVLink domain (NCCL_GIN_TYPE chooses peer stores or the host proxy); the NCCL_GIN_GDAKI_* and NCCL_RMA_* variables have no counterpart", true}},
     {{"NCCL_NTHREADS", PT_STR, "", "No effect: the kernels' CTA sizes are fixed per kernel (512 threads, 32 for the bulk-copy forms)", true}},
     {{"NCCL_BUFFSIZE", PT_STR, "", "No effect: there are no per-channel FIFO buffers; NCCL_B200_SCRATCH_MB sizes the staging area for unregistered buffers", true}},
     {{"NCCL_LAUNCH_MODE", PT_STR, "", "No effect: every rank launches its own kernels (one process or thread per GPU)", true}},
